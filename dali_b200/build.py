@@ -1,0 +1,89 @@
+"""Builds libdali_b200.so in-tree (dali_b200/lib/).
+
+Host C++ goes through g++, CUDA sources through nvcc for sm_100a only
+(-gencode arch=compute_100a,code=sm_100a).  The device prelude that is spliced
+in front of every run-time generated kernel is embedded as a string literal.
+Run as `python -m dali_b200.build` or through __graft_entry__.build().
+"""
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIBDIR = os.path.join(HERE, "lib")
+CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+LIB = os.path.join(LIBDIR, "libdali_b200.so")
+
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-Wno-sign-compare", "-I" + os.path.join(CUDA_HOME, "include")]
+
+
+def _embed_prelude():
+    src = open(os.path.join(CSRC, "prelude.cuh")).read()
+    assert ')DALIPRELUDE"' not in src
+    out = os.path.join(CSRC, "prelude_embed.inc")
+    text = 'R"DALIPRELUDE(' + src + ')DALIPRELUDE"\n'
+    if not os.path.exists(out) or open(out).read() != text:
+        with open(out, "w") as f:
+            f.write(text)
+
+
+def _newer(target, sources):
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(s) > t for s in sources)
+
+
+def _run(cmd, log=None):
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if log:
+        with open(log, "w") as f:
+            f.write(" ".join(cmd) + "\n" + r.stdout)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout)
+        raise RuntimeError("build step failed: " + " ".join(cmd))
+    return r.stdout
+
+
+def build(force=False, verbose=False):
+    os.makedirs(LIBDIR, exist_ok=True)
+    objdir = os.path.join(LIBDIR, "obj")
+    os.makedirs(objdir, exist_ok=True)
+    _embed_prelude()
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh", ".inc"))]
+    headers += [os.path.join(HERE, "..", "include", f) for f in os.listdir(os.path.join(HERE, "..", "include"))]
+    for sub in ("host",):
+        d = os.path.join(CSRC, sub)
+        if os.path.isdir(d):
+            headers += [os.path.join(d, f) for f in os.listdir(d) if f.endswith(".h")]
+    objs = []
+    srcs = []
+    for root, _, files in os.walk(CSRC):
+        for f in sorted(files):
+            if f.endswith((".cc", ".cu")):
+                srcs.append(os.path.join(root, f))
+    for src in srcs:
+        obj = os.path.join(objdir, os.path.relpath(src, CSRC).replace(os.sep, "_") + ".o")
+        objs.append(obj)
+        if not force and not _newer(obj, [src] + headers):
+            continue
+        if src.endswith(".cu"):
+            cmd = [os.path.join(CUDA_HOME, "bin", "nvcc")] + NVCC_FLAGS + ["-I" + CSRC, "-c", src, "-o", obj]
+            out = _run(cmd, log=obj + ".ptxas.log")   # registers / spills / shared memory per kernel
+            if verbose:
+                print(out)
+        else:
+            _run(["g++"] + CXX_FLAGS + ["-I" + CSRC, "-c", src, "-o", obj])
+    if force or _newer(LIB, objs):
+        libdir = os.path.join(CUDA_HOME, "lib64")
+        _run(["g++", "-shared", "-o", LIB] + objs +
+             ["-L" + libdir, "-lcudart_static", "-lnvrtc", "-ldl", "-lrt", "-lpthread",
+              "-Wl,-rpath," + libdir, "-Wl,--no-undefined"])
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -1,0 +1,205 @@
+"""ctypes binding of include/dali_b200.h -- test / benchmark plumbing only.
+
+Nothing here computes: every call goes into libdali_b200.so, and loading fails
+loudly when the library has not been built.
+"""
+import ctypes
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libdali_b200.so")
+
+F32, F64, I32, BF16 = 0, 1, 2, 3
+_NP_DTYPE = {F32: np.float32, F64: np.float64, I32: np.int32}
+
+c_i64p = ctypes.POINTER(ctypes.c_int64)
+
+
+class DaliB200Error(RuntimeError):
+    def __init__(self, status, message):
+        super().__init__("dali_b200 status %d: %s" % (status, message))
+        self.status = status
+
+
+def _i64_array(values):
+    return (ctypes.c_int64 * len(values))(*[int(v) for v in values])
+
+
+class Library:
+    """Thin wrapper: one method per C entry point, errors raised as exceptions."""
+
+    def __init__(self, path=LIB_PATH):
+        if not os.path.exists(path):
+            raise ImportError("libdali_b200.so is not built (%s); run __graft_entry__.build()" % path)
+        self.path = path
+        self.c = ctypes.CDLL(path)
+        c = self.c
+        c.dalib200_last_error.restype = ctypes.c_size_t
+        c.dalib200_last_error.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
+        c.dalib200_last_variant.restype = ctypes.c_size_t
+        c.dalib200_last_variant.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
+        c.dalib200_cache_get_dir.restype = ctypes.c_size_t
+        c.dalib200_cache_get_dir.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
+        c.dalib200_compile.argtypes = [ctypes.c_uint64, ctypes.c_char_p, ctypes.c_size_t]
+        c.dalib200_is_loaded.argtypes = [ctypes.c_uint64]
+        c.dalib200_precompile.argtypes = [ctypes.c_uint64, c_i64p, ctypes.c_int, ctypes.POINTER(ctypes.c_void_p),
+                                          c_i64p, ctypes.POINTER(c_i64p), ctypes.c_int,
+                                          ctypes.POINTER(ctypes.c_size_t)]
+        c.dalib200_launch.argtypes = [ctypes.c_uint64, ctypes.c_int, ctypes.c_void_p, c_i64p, ctypes.c_int,
+                                      ctypes.POINTER(ctypes.c_void_p), c_i64p, ctypes.POINTER(c_i64p), ctypes.c_int,
+                                      ctypes.POINTER(ctypes.c_void_p), ctypes.c_int]
+        c.dalib200_launch_host.argtypes = [ctypes.c_uint64, ctypes.c_int, c_i64p, ctypes.c_int,
+                                           ctypes.POINTER(ctypes.c_void_p), c_i64p, c_i64p, ctypes.POINTER(c_i64p),
+                                           ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int]
+        c.dalib200_alloc.argtypes = [ctypes.c_int, ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p)]
+        c.dalib200_free.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t]
+        for name in ("dalib200_memcpy_h2d", "dalib200_memcpy_d2h", "dalib200_memcpy_d2d"):
+            getattr(c, name).argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t,
+                                         ctypes.c_void_p]
+        c.dalib200_memset.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t, ctypes.c_void_p]
+        c.dalib200_sync.argtypes = [ctypes.c_int, ctypes.c_void_p]
+        c.dalib200_cache_set_dir.argtypes = [ctypes.c_char_p]
+        c.dalib200_cache_stats.argtypes = [ctypes.POINTER(ctypes.c_uint64)]
+        self._next_hash = 0x0da11b200
+
+    # -- errors ---------------------------------------------------------------
+    def last_error(self):
+        buf = ctypes.create_string_buffer(1 << 16)
+        self.c.dalib200_last_error(buf, len(buf))
+        return buf.value.decode(errors="replace")
+
+    def last_variant(self):
+        buf = ctypes.create_string_buffer(1 << 12)
+        self.c.dalib200_last_variant(buf, len(buf))
+        return buf.value.decode()
+
+    def check(self, status):
+        if status != 0:
+            raise DaliB200Error(status, self.last_error())
+
+    # -- lifecycle ------------------------------------------------------------
+    def abi_version(self):
+        return self.c.dalib200_abi_version()
+
+    def init(self, n_gpus=0):
+        self.check(self.c.dalib200_init(n_gpus))
+
+    def device_count(self):
+        return self.c.dalib200_device_count()
+
+    def cache_set_dir(self, path):
+        self.check(self.c.dalib200_cache_set_dir(path.encode()))
+
+    def cache_get_dir(self):
+        buf = ctypes.create_string_buffer(4096)
+        self.c.dalib200_cache_get_dir(buf, len(buf))
+        return buf.value.decode()
+
+    def cache_clear(self, remove_files=False):
+        self.check(self.c.dalib200_cache_clear(int(remove_files)))
+
+    def cache_stats(self):
+        s = (ctypes.c_uint64 * 5)()
+        self.check(self.c.dalib200_cache_stats(s))
+        return dict(zip(("programs", "kernels", "compilations", "disk_hits", "launches"), [int(x) for x in s]))
+
+    # -- compile / launch -----------------------------------------------------
+    def compile(self, ir, hash_=None):
+        """Registers `ir`; returns the hash it is registered under."""
+        if hash_ is None:
+            h = 1469598103934665603
+            for ch in ir.encode():
+                h = ((h ^ ch) * 1099511628211) & 0xFFFFFFFFFFFFFFFF
+            hash_ = h
+        data = ir.encode()
+        self.check(self.c.dalib200_compile(ctypes.c_uint64(hash_), data, len(data)))
+        return hash_
+
+    def is_loaded(self, hash_):
+        return bool(self.c.dalib200_is_loaded(ctypes.c_uint64(hash_)))
+
+    @staticmethod
+    def _strides_arg(strides, n):
+        keep = []
+        if strides is None:
+            return None, keep
+        arr = (c_i64p * n)()
+        for i, s in enumerate(strides):
+            if s is None:
+                arr[i] = None
+            else:
+                a = _i64_array(s)
+                keep.append(a)
+                arr[i] = ctypes.cast(a, c_i64p)
+        return arr, keep
+
+    def precompile(self, hash_, space, n_arrays, strides=None, pointers=None, offsets=None):
+        ptrs = (ctypes.c_void_p * n_arrays)(*[(pointers[i] if pointers else 4096) for i in range(n_arrays)])
+        offs = _i64_array(offsets if offsets else [0] * n_arrays)
+        st, keep = self._strides_arg(strides, n_arrays)
+        size = ctypes.c_size_t(0)
+        self.check(self.c.dalib200_precompile(ctypes.c_uint64(hash_), _i64_array(space), len(space), ptrs, offs, st,
+                                              n_arrays, ctypes.byref(size)))
+        return size.value
+
+    @staticmethod
+    def _scalars_arg(scalars):
+        keep = [np.ascontiguousarray(s) for s in (scalars or [])]
+        arr = (ctypes.c_void_p * max(len(keep), 1))(*[k.ctypes.data for k in keep])
+        return arr, keep
+
+    def launch(self, hash_, space, arrays, strides=None, offsets=None, scalars=None, device=0, stream=None):
+        """arrays: device pointers (ints) or objects with data_ptr() (torch CUDA tensors)."""
+        n = len(arrays)
+        ptrs = (ctypes.c_void_p * n)(*[(a.data_ptr() if hasattr(a, "data_ptr") else int(a)) for a in arrays])
+        offs = _i64_array(offsets if offsets else [0] * n)
+        st, keep = self._strides_arg(strides, n)
+        sc, keep2 = self._scalars_arg(scalars)
+        self.check(self.c.dalib200_launch(ctypes.c_uint64(hash_), device, ctypes.c_void_p(stream or 0),
+                                          _i64_array(space), len(space), ptrs, offs, st, n, sc,
+                                          len(scalars or [])))
+
+    def launch_host(self, hash_, space, arrays, strides=None, offsets=None, scalars=None, device=0):
+        """arrays: numpy arrays (whole buffers, C-contiguous); written ones are updated in place."""
+        n = len(arrays)
+        for a in arrays:
+            assert a.flags["C_CONTIGUOUS"]
+        ptrs = (ctypes.c_void_p * n)(*[a.ctypes.data for a in arrays])
+        ext = _i64_array([a.size for a in arrays])
+        offs = _i64_array(offsets if offsets else [0] * n)
+        st, keep = self._strides_arg(strides, n)
+        sc, keep2 = self._scalars_arg(scalars)
+        self.check(self.c.dalib200_launch_host(ctypes.c_uint64(hash_), device, _i64_array(space), len(space), ptrs,
+                                               ext, offs, st, n, sc, len(scalars or [])))
+
+    # -- memory ---------------------------------------------------------------
+    def alloc(self, nbytes, device=0):
+        p = ctypes.c_void_p()
+        self.check(self.c.dalib200_alloc(device, nbytes, ctypes.byref(p)))
+        return p.value
+
+    def free(self, ptr, nbytes, device=0):
+        self.check(self.c.dalib200_free(device, ctypes.c_void_p(ptr), nbytes))
+
+    def h2d(self, dst, src_np, device=0, stream=None):
+        self.check(self.c.dalib200_memcpy_h2d(device, ctypes.c_void_p(dst), src_np.ctypes.data, src_np.nbytes,
+                                              ctypes.c_void_p(stream or 0)))
+
+    def d2h(self, dst_np, src, device=0, stream=None):
+        self.check(self.c.dalib200_memcpy_d2h(device, dst_np.ctypes.data, ctypes.c_void_p(src), dst_np.nbytes,
+                                              ctypes.c_void_p(stream or 0)))
+
+    def sync(self, device=0, stream=None):
+        self.check(self.c.dalib200_sync(device, ctypes.c_void_p(stream or 0)))
+
+
+_LIB = None
+
+
+def load_library():
+    global _LIB
+    if _LIB is None:
+        _LIB = Library()
+    return _LIB

@@ -1,0 +1,845 @@
+// Kernel skeletons + expression splicing (see codegen.h).
+#include "codegen.h"
+
+#include <algorithm>
+#include <set>
+#include <sstream>
+
+namespace dalib {
+
+const char* Variant::kind_name() const {
+    switch (kind) {
+        case K_MAP: return "map";
+        case K_ROW: return "row";
+        case K_COL: return "col";
+        case K_ALL: return "all";
+    }
+    return "?";
+}
+
+std::string Variant::key() const {
+    std::ostringstream s;
+    s << kind_name() << ".o" << nout << ".i" << nin << ".v" << vec << ".nt" << threads << ".T" << T
+      << ".p" << vpt << ".u" << unroll << ".x" << tx << ".y" << ty << "." << cls << "." << ocls;
+    return s.str();
+}
+
+ParamLayout::ParamLayout(const Program& p, const Variant& v) {
+    w_ishape = w_oshape + v.nout;
+    w_args = w_ishape + v.nin;
+    arg_words = 2 + v.nout + v.nin;
+    w_scalars = w_args + (int)p.args.size() * arg_words;
+    total = w_scalars + (int)p.scalars.size();
+    if (total < 8) total = 8;
+}
+
+int scratch_slot_bytes(const Program& p) {
+    // widest partial: ArgPair<double> = 16 bytes; plain values <= 8.
+    int b = 4;
+    for (const Stmt& s : p.stmts) {
+        if (s.kind == S_ARGRED) b = 16;
+        else if (s.kind == S_RED && dtype_size(s.dtype) > b && b < 16) b = dtype_size(s.dtype);
+    }
+    return b;
+}
+
+namespace {
+
+const char* red_struct(const std::string& n) {
+    if (n == "sum") return "RSum";
+    if (n == "prod") return "RProd";
+    if (n == "max") return "RMax";
+    return "RMin";
+}
+
+struct Gen {
+    const Program& p;
+    const Variant& v;
+    ParamLayout L;
+    std::ostringstream o;
+    std::set<int> need_inv;          // R-level f32 values whose reciprocal is precomputed
+    std::vector<int> reds;           // stmt indices of reductions, program order
+    std::vector<int> red_slot;       // per stmt index -> position in `reds`, or -1
+
+    Gen(const Program& p_, const Variant& v_) : p(p_), v(v_), L(p_, v_) {
+        red_slot.assign(p.stmts.size(), -1);
+        for (size_t i = 0; i < p.stmts.size(); ++i) {
+            const Stmt& s = p.stmts[i];
+            if (s.kind == S_RED || s.kind == S_ARGRED) {
+                red_slot[i] = (int)reds.size();
+                reds.push_back((int)i);
+            }
+            if (s.kind == S_OP && s.name == "eltdiv" && s.dtype == F32 && s.elem) {
+                const Stmt& d = val(s.in[1]);
+                if (!d.elem) need_inv.insert(d.id);
+            }
+        }
+    }
+
+    const Stmt& val(int id) const { return p.stmts[p.value_stmt[id]]; }
+    std::string W(int w) const { return "p.w[" + std::to_string(w) + "]"; }
+    std::string ct(DType t) const { return dtype_c_name(t); }
+    std::string vn(int id) const { return std::string(val(id).elem ? "e" : "r") + std::to_string(id); }
+    std::string argT(int a) const { return ct(p.args[a].dtype); }
+    bool arg_elem(int a) const { return p.nreduce == 0 ? true : p.args[a].elem_level; }
+
+    std::string literal(const Stmt& s) const {
+        const std::string t = ct(s.dtype);
+        if (s.literal == "inf") return "(" + t + ")__longlong_as_double(0x7ff0000000000000LL)";
+        if (s.literal == "-inf") return "(" + t + ")__longlong_as_double(0xfff0000000000000LL)";
+        if (s.literal == "nan") return "(" + t + ")__longlong_as_double(0x7ff8000000000000LL)";
+        std::string lit = s.literal;
+        if (s.dtype != I32 && lit.find_first_of(".eEn") == std::string::npos) lit += ".0";
+        return "(" + t + ")(" + lit + ")";
+    }
+
+    // expression for a non-load, non-reduction value
+    std::string expr(const Stmt& s) const {
+        switch (s.kind) {
+            case S_CONST: return literal(s);
+            case S_SC: return "*reinterpret_cast<const " + ct(s.dtype) + "*>(&" + W(L.w_scalars + s.arg) + ")";
+            case S_CAST: return "(" + ct(s.dtype) + ")(" + vn(s.in[0]) + ")";
+            case S_OP: {
+                if (s.name == "round" || s.name == "ceiling")
+                    return "f_" + s.name + "<" + ct(s.dtype) + ">(" + vn(s.in[0]) + ")";
+                if (s.name == "eltdiv" && s.in.size() == 2 && need_inv.count(s.in[1]) && s.elem && s.dtype == F32)
+                    return vn(s.in[0]) + " * rinv" + std::to_string(s.in[1]);
+                std::string e = "f_" + s.name + "(" + vn(s.in[0]);
+                if (s.in.size() > 1) e += ", " + vn(s.in[1]);
+                return e + ")";
+            }
+            default: return "/*?*/";
+        }
+    }
+
+    std::string assign_rhs(AssignOp op, const std::string& old, const std::string& val_) const {
+        switch (op) {
+            case A_ASSIGN: return val_;
+            case A_ADD: return old + " + " + val_;
+            case A_SUB: return old + " - " + val_;
+            case A_MUL: return old + " * " + val_;
+            case A_DIV: return old + " / " + val_;
+        }
+        return val_;
+    }
+
+    // ---- common kernel prologue
+    void header() {
+        o << "// dali_b200 generated kernel: " << v.key() << "\n";
+        o << "struct P { long long w[" << L.total << "]; };\n";
+        o << "#define NT " << v.threads << "\n#define VEC " << v.vec << "\n#define UNROLL " << v.unroll << "\n";
+        o << "extern \"C\" __global__ void __launch_bounds__(NT) dali_kernel(const __grid_constant__ P p) {\n";
+        o << "  const i64 R = " << W(L.w_R) << "; const i64 C = " << W(L.w_C) << ";\n";
+        o << "  const int tid = threadIdx.x;\n";
+        for (size_t a = 0; a < p.args.size(); ++a) {
+            bool ro = !p.args[a].written;
+            o << "  " << (ro ? "const " : "") << argT((int)a) << "* const a" << a << " = reinterpret_cast<"
+              << (ro ? "const " : "") << argT((int)a) << "*>(" << W(L.arg_ptr((int)a)) << ");\n";
+        }
+        // uniform values: scalars and constants (and functors of only those at stage 0 are
+        // left to the row scope; they are cheap)
+        for (const Stmt& s : p.stmts) {
+            if (s.kind == S_SC || s.kind == S_CONST) {
+                o << "  const " << ct(s.dtype) << " " << vn(s.id) << " = " << expr(s) << ";\n";
+                if (need_inv.count(s.id)) o << "  const float rinv" << s.id << " = 1.0f / " << vn(s.id) << ";\n";
+            }
+        }
+    }
+
+    // ---- outer (row) offsets: defines i64 ro<a> for every arg, given row index expr `r`
+    void row_offsets(const std::string& ind, const std::string& r) {
+        if (v.nout == 0) {
+            for (size_t a = 0; a < p.args.size(); ++a) o << ind << "const i64 ro" << a << " = 0;\n";
+            return;
+        }
+        if (v.nout == 1) {
+            for (size_t a = 0; a < p.args.size(); ++a)
+                o << ind << "const i64 ro" << a << " = " << r << " * " << W(L.arg_rs((int)a, 0)) << ";\n";
+            return;
+        }
+        for (size_t a = 0; a < p.args.size(); ++a) o << ind << "i64 ro" << a << " = 0;\n";
+        o << ind << "{ i64 t_ = " << r << ";\n";
+        for (int k = v.nout - 1; k >= 0; --k) {
+            o << ind << "  { const i64 q_ = t_ / " << W(L.w_oshape + k) << "; const i64 i_ = t_ - q_ * "
+              << W(L.w_oshape + k) << "; t_ = q_;\n";
+            for (size_t a = 0; a < p.args.size(); ++a)
+                o << ind << "    ro" << a << " += i_ * " << W(L.arg_rs((int)a, k)) << ";\n";
+            o << ind << "  }\n";
+        }
+        o << ind << "}\n";
+    }
+
+    // inner offset expression of arg a at inner index `c` (+ lane j); for nin > 1 the
+    // caller has emitted col_decompose() which defines co<a>.
+    std::string col_off(int a, const std::string& c) const {
+        if (v.nin > 1) return "co" + std::to_string(a);
+        char k = v.cls[a];
+        if (k == 'u') return "(" + c + ")";
+        if (k == 'z') return "0";
+        return "(" + c + ") * " + W(L.arg_cs(a, 0, v.nout));
+    }
+    void col_decompose(const std::string& ind, const std::string& c) {
+        if (v.nin <= 1) return;
+        for (size_t a = 0; a < p.args.size(); ++a) o << ind << "i64 co" << a << " = 0;\n";
+        o << ind << "{ i64 t_ = " << c << ";\n";
+        for (int k = v.nin - 1; k >= 0; --k) {
+            o << ind << "  { const i64 q_ = t_ / " << W(L.w_ishape + k) << "; const i64 i_ = t_ - q_ * "
+              << W(L.w_ishape + k) << "; t_ = q_;\n";
+            for (size_t a = 0; a < p.args.size(); ++a)
+                o << ind << "    co" << a << " += i_ * " << W(L.arg_cs((int)a, k, v.nout)) << ";\n";
+            o << ind << "  }\n";
+        }
+        o << ind << "}\n";
+    }
+
+    // ---- pass analysis ------------------------------------------------------
+    // number of element passes: reductions of result stage q+1 fold in pass q,
+    // element-level stores of stage q happen in pass q.
+    int n_passes() const {
+        int n = 0;
+        for (const Stmt& s : p.stmts) {
+            if ((s.kind == S_RED || s.kind == S_ARGRED)) n = std::max(n, s.stage);
+            if ((s.kind == S_ST || s.kind == S_STX) && s.elem) n = std::max(n, s.stage + 1);
+        }
+        return n;
+    }
+
+    // stmt indices that are sinks of element pass q
+    std::vector<int> pass_sinks(int q) const {
+        std::vector<int> out;
+        for (size_t i = 0; i < p.stmts.size(); ++i) {
+            const Stmt& s = p.stmts[i];
+            if ((s.kind == S_RED || s.kind == S_ARGRED) && s.stage == q + 1) out.push_back((int)i);
+            if ((s.kind == S_ST || s.kind == S_STX) && s.elem && s.stage == q) out.push_back((int)i);
+        }
+        return out;
+    }
+
+    // element-level value ids needed in pass q.  With `cut` true, traversal stops at
+    // element values of an earlier stage (they come from register caches); those are
+    // returned in *cuts.
+    std::set<int> pass_needed(int q, bool cut, std::set<int>* cuts) const {
+        std::set<int> need;
+        std::vector<int> stack;
+        for (int si : pass_sinks(q))
+            for (int in : p.stmts[si].in) stack.push_back(in);
+        while (!stack.empty()) {
+            int id = stack.back();
+            stack.pop_back();
+            const Stmt& s = val(id);
+            if (!s.elem) continue;
+            if (cut && s.stage < q && s.kind != S_LD) {
+                if (cuts) cuts->insert(id);
+                continue;
+            }
+            if (!need.insert(id).second) continue;
+            for (int in : s.in) stack.push_back(in);
+        }
+        return need;
+    }
+
+    // ---- one vector group of element work ----------------------------------------
+    // Emits: loads of the element-level args used, the lane loop computing `need`
+    // values in program order, reduction accumulation and element stores of pass q.
+    //   c        name of the inner index variable of lane 0 (int or i64)
+    //   slot     text appended to cached-array names ("[i]") or "" when nothing is cached
+    //   cached   element loads come from / go to register arrays LQ<a>slot
+    //   loaded   args whose LQ<a> arrays already hold data (updated)
+    //   cuts_rd  value caches to read, cuts_wr value caches to write (CV<id>[i*VEC+j])
+    struct GroupCtx {
+        std::string ind, c, slot;
+        bool cached = false;
+        std::set<int>* loaded = nullptr;
+        std::set<int> cuts_rd, cuts_wr;
+        std::string acc_suffix;    // "" or "[j]" (col kind keeps VEC accumulators)
+        std::string argred_index;  // expression of the reduced-dim index of lane j
+        bool skip_loads = false;   // loads were hoisted by the caller (map / all unrolling)
+        std::string hoist_idx;     // "[u]" when loads were hoisted into arrays
+    };
+
+    std::set<int> args_loaded_in(const std::set<int>& need, int q) const {
+        std::set<int> as;
+        for (int id : need) if (val(id).kind == S_LD) as.insert(val(id).arg);
+        for (int si : pass_sinks(q)) {
+            const Stmt& s = p.stmts[si];
+            if (s.kind == S_ST && s.aop != A_ASSIGN) as.insert(s.arg);
+        }
+        return as;
+    }
+
+    // load of the vector group of arg a into variable `dst`
+    void emit_arg_load(const std::string& ind, int a, const std::string& dst, const std::string& c, bool declare) {
+        const std::string T = argT(a);
+        char k = v.nin > 1 ? 's' : v.cls[a];
+        if (declare) o << ind << "Vec<" << T << ", VEC> " << dst << ";\n";
+        if (v.vec > 1 && k == 'u') {
+            o << ind << dst << " = vload<" << T << ", VEC>(a" << a << " + ro" << a << " + " << c << ");\n";
+        } else if (k == 'z' && v.nin == 1) {
+            o << ind << "{ const " << T << " t_ = a" << a << "[ro" << a << "];\n" << ind
+              << "  _Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) " << dst << ".x[j] = t_; }\n";
+        } else if (v.nin > 1) {
+            o << ind << dst << ".x[0] = a" << a << "[ro" << a << " + co" << a << "];\n";
+        } else {
+            o << ind << "_Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) " << dst << ".x[j] = a" << a << "[ro" << a
+              << " + " << col_off(a, c + " + j") << "];\n";
+        }
+    }
+
+    void emit_arg_store(const std::string& ind, int a, const std::string& src, const std::string& c) {
+        const std::string T = argT(a);
+        char k = v.nin > 1 ? 's' : v.cls[a];
+        if (v.vec > 1 && k == 'u') {
+            o << ind << "vstore<" << T << ", VEC>(a" << a << " + ro" << a << " + " << c << ", " << src << ");\n";
+        } else if (v.nin > 1) {
+            o << ind << "a" << a << "[ro" << a << " + co" << a << "] = " << src << ".x[0];\n";
+        } else if (k == 'z') {
+            // every lane targets the same element; the last lane wins, as a serial loop would
+            o << ind << "a" << a << "[ro" << a << "] = " << src << ".x[VEC - 1];\n";
+        } else {
+            o << ind << "_Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) a" << a << "[ro" << a << " + "
+              << col_off(a, c + " + j") << "] = " << src << ".x[j];\n";
+        }
+    }
+
+    void emit_group(int q, const std::set<int>& need, GroupCtx& g) {
+        const std::string& ind = g.ind;
+        std::set<int> largs = args_loaded_in(need, q);
+        if (v.nin > 1) col_decompose(ind, g.c);
+        // loads
+        for (int a : largs) {
+            const std::string name = g.cached ? "LQ" + std::to_string(a) + g.slot
+                                              : (g.skip_loads ? "q" + std::to_string(a) + g.hoist_idx
+                                                              : "q" + std::to_string(a));
+            if (g.skip_loads) continue;
+            if (g.cached) {
+                // an arg that is also stored in this pass with an operator must be re-read
+                if (g.loaded->count(a)) continue;
+                emit_arg_load(ind, a, name, g.c, false);
+                g.loaded->insert(a);
+            } else {
+                emit_arg_load(ind, a, name, g.c, true);
+            }
+        }
+        auto argvec = [&](int a) {
+            return g.cached ? "LQ" + std::to_string(a) + g.slot
+                            : "q" + std::to_string(a) + (g.skip_loads ? g.hoist_idx : "");
+        };
+        // output staging
+        std::vector<int> sinks = pass_sinks(q);
+        for (int si : sinks) {
+            const Stmt& s = p.stmts[si];
+            if (s.kind == S_ST) o << ind << "Vec<" << argT(s.arg) << ", VEC> out" << si << ";\n";
+        }
+        o << ind << "_Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) {\n";
+        const std::string in2 = ind + "  ";
+        for (int id : g.cuts_rd) {
+            const Stmt& s = val(id);
+            o << in2 << "const " << ct(s.dtype) << " " << vn(id) << " = CV" << id << g.slot.substr(0, g.slot.size() ? g.slot.size() - 1 : 0)
+              << (g.slot.empty() ? "[j]" : " * VEC + j]") << ";\n";
+        }
+        for (const Stmt& s : p.stmts) {
+            if (s.id < 0 || !need.count(s.id)) continue;
+            if (s.kind == S_LD) {
+                o << in2 << "const " << ct(s.dtype) << " " << vn(s.id) << " = " << argvec(s.arg) << ".x[j];\n";
+            } else if (s.kind == S_LDX) {
+                o << in2 << "const " << ct(s.dtype) << " " << vn(s.id) << " = a" << s.arg << "[ro" << s.arg << " + "
+                  << (arg_elem(s.arg) ? col_off(s.arg, g.c + " + j") : std::string("0")) << " + (i64)" << vn(s.in[0])
+                  << " * " << W(L.arg_xs(s.arg)) << "];\n";
+            } else {
+                o << in2 << "const " << ct(s.dtype) << " " << vn(s.id) << " = " << expr(s) << ";\n";
+            }
+            if (g.cuts_wr.count(s.id))
+                o << in2 << "CV" << s.id << g.slot.substr(0, g.slot.size() ? g.slot.size() - 1 : 0)
+                  << (g.slot.empty() ? "[j]" : " * VEC + j]") << " = " << vn(s.id) << ";\n";
+        }
+        for (int si : sinks) {
+            const Stmt& s = p.stmts[si];
+            if (s.kind == S_RED) {
+                o << in2 << "acc" << si << g.acc_suffix << " = " << red_struct(s.name) << "::apply(acc" << si
+                  << g.acc_suffix << ", " << vn(s.in[0]) << ");\n";
+            } else if (s.kind == S_ARGRED) {
+                const Stmt& src = val(s.in[0]);
+                o << in2 << "arg_take<" << red_struct(s.name) << ", " << ct(src.dtype) << ">(acc" << si << g.acc_suffix
+                  << ", " << vn(s.in[0]) << ", (i64)(" << g.argred_index << "));\n";
+            } else if (s.kind == S_ST) {
+                std::string old = argvec(s.arg) + ".x[j]";
+                o << in2 << "out" << si << ".x[j] = " << assign_rhs(s.aop, old, vn(s.in[0])) << ";\n";
+            } else if (s.kind == S_STX) {
+                const std::string addr = "&a" + std::to_string(s.arg) + "[ro" + std::to_string(s.arg) + " + " +
+                                         col_off(s.arg, g.c + " + j") + " + (i64)" + vn(s.in[0]) + " * " +
+                                         W(L.arg_xs(s.arg)) + "]";
+                const std::string val_ = vn(s.in[1]);
+                switch (s.aop) {
+                    case A_ASSIGN: o << in2 << "atomic_exch(" << addr << ", " << val_ << ");\n"; break;
+                    case A_ADD: o << in2 << "atomic_add(" << addr << ", " << val_ << ");\n"; break;
+                    case A_SUB: o << in2 << "atomic_add(" << addr << ", -" << val_ << ");\n"; break;
+                    case A_MUL: o << in2 << "atomic_exch(" << addr << ", *" << addr << " * " << val_ << ");\n"; break;
+                    case A_DIV: o << in2 << "atomic_exch(" << addr << ", *" << addr << " / " << val_ << ");\n"; break;
+                }
+            }
+        }
+        o << ind << "}\n";
+        for (int si : sinks) {
+            const Stmt& s = p.stmts[si];
+            if (s.kind == S_ST) emit_arg_store(ind, s.arg, "out" + std::to_string(si), g.c);
+        }
+    }
+
+    // ---- row-level statements of stage q (loads of R args, functors, stores) ----
+    // `valid` guards memory accesses; `oidx` is appended to nothing (row kinds keep
+    // scalars).  Reduction results must already be in r<id>.
+    void emit_row_values(const std::string& ind, int q, const std::string& valid, bool leader_only_stores,
+                         const std::string& leader) {
+        for (size_t i = 0; i < p.stmts.size(); ++i) {
+            const Stmt& s = p.stmts[i];
+            if (s.elem || s.stage != q) continue;
+            if (s.kind == S_LD) {
+                o << ind << "const " << ct(s.dtype) << " " << vn(s.id) << " = " << valid << " ? a" << s.arg << "[ro"
+                  << s.arg << "] : (" << ct(s.dtype) << ")0;\n";
+            } else if (s.kind == S_LDX) {
+                o << ind << "const " << ct(s.dtype) << " " << vn(s.id) << " = " << valid << " ? a" << s.arg << "[ro"
+                  << s.arg << " + (i64)" << vn(s.in[0]) << " * " << W(L.arg_xs(s.arg)) << "] : (" << ct(s.dtype)
+                  << ")0;\n";
+            } else if (s.kind == S_OP || s.kind == S_CAST) {
+                o << ind << "const " << ct(s.dtype) << " " << vn(s.id) << " = " << expr(s) << ";\n";
+            } else if (s.kind == S_ST) {
+                const std::string dst = "a" + std::to_string(s.arg) + "[ro" + std::to_string(s.arg) + "]";
+                o << ind << "if (" << valid << (leader_only_stores ? " && " + leader : "") << ") " << dst << " = "
+                  << assign_rhs(s.aop, dst, vn(s.in[0])) << ";\n";
+                continue;
+            } else if (s.kind == S_STX) {
+                const std::string addr = "&a" + std::to_string(s.arg) + "[ro" + std::to_string(s.arg) + " + (i64)" +
+                                         vn(s.in[0]) + " * " + W(L.arg_xs(s.arg)) + "]";
+                o << ind << "if (" << valid << (leader_only_stores ? " && " + leader : "") << ") ";
+                switch (s.aop) {
+                    case A_ASSIGN: o << "atomic_exch(" << addr << ", " << vn(s.in[1]) << ");\n"; break;
+                    case A_ADD: o << "atomic_add(" << addr << ", " << vn(s.in[1]) << ");\n"; break;
+                    case A_SUB: o << "atomic_add(" << addr << ", -" << vn(s.in[1]) << ");\n"; break;
+                    case A_MUL: o << "atomic_exch(" << addr << ", *" << addr << " * " << vn(s.in[1]) << ");\n"; break;
+                    case A_DIV: o << "atomic_exch(" << addr << ", *" << addr << " / " << vn(s.in[1]) << ");\n"; break;
+                }
+                continue;
+            } else {
+                continue;  // SC / CONST emitted in header, reductions by the caller
+            }
+            if (need_inv.count(s.id)) o << ind << "const float rinv" << s.id << " = 1.0f / " << vn(s.id) << ";\n";
+        }
+    }
+
+    std::string acc_type(const Stmt& s) const {
+        if (s.kind == S_ARGRED) return "ArgPair<" + ct(val(s.in[0]).dtype) + ">";
+        return ct(s.dtype);
+    }
+    std::string acc_init(const Stmt& s) const {
+        if (s.kind == S_ARGRED)
+            return "arg_init<" + std::string(red_struct(s.name)) + ", " + ct(val(s.in[0]).dtype) + ">()";
+        return std::string(red_struct(s.name)) + "::init<" + ct(s.dtype) + ">()";
+    }
+    std::string acc_merge(const Stmt& s, const std::string& a, const std::string& b) const {
+        if (s.kind == S_ARGRED)
+            return "arg_merge<" + std::string(red_struct(s.name)) + ", " + ct(val(s.in[0]).dtype) + ">(" + a + ", " + b + ")";
+        return std::string(red_struct(s.name)) + "::apply(" + a + ", " + b + ")";
+    }
+    // final value of a reduction from its accumulator
+    std::string acc_result(const Stmt& s, const std::string& a) const {
+        if (s.kind == S_ARGRED) return "(int)" + a + ".i";
+        return a;
+    }
+
+    // ======================================================================= MAP
+    bool gen_map(std::string* err) {
+        if (p.nreduce != 0) { *err = "map skeleton needs nreduce = 0"; return false; }
+        header();
+        std::set<int> need = pass_needed(0, false, nullptr);
+        std::set<int> largs = args_loaded_in(need, 0);
+        o << "  const int txl = (int)" << W(L.w_aux0) << ";\n";
+        o << "  const int TX = 1 << txl, TY = NT >> txl;\n";
+        o << "  const int tx = tid & (TX - 1), ty = tid >> txl;\n";
+        o << "  const i64 cbase = ((i64)blockIdx.x * UNROLL * TX + tx) * VEC;\n";
+        o << "  const i64 cstep = (i64)TX * VEC;\n";
+        o << "  for (i64 r = (i64)blockIdx.y * TY + ty; r < R; r += (i64)gridDim.y * TY) {\n";
+        row_offsets("    ", "r");
+        bool hoist = v.nin == 1 && v.unroll > 1;
+        if (hoist) {
+            for (int a : largs) o << "    Vec<" << argT(a) << ", VEC> q" << a << "[UNROLL];\n";
+            o << "    _Pragma(\"unroll\") for (int u = 0; u < UNROLL; ++u) {\n";
+            o << "      const i64 c = cbase + u * cstep;\n      if (c < C) {\n";
+            for (int a : largs) emit_arg_load("        ", a, "q" + std::to_string(a) + "[u]", "c", false);
+            o << "      }\n    }\n";
+        }
+        o << "    _Pragma(\"unroll\") for (int u = 0; u < UNROLL; ++u) {\n";
+        o << "      const i64 c = cbase + u * cstep;\n      if (c < C) {\n";
+        GroupCtx g;
+        g.ind = "        ";
+        g.c = "c";
+        g.skip_loads = hoist;
+        g.hoist_idx = "[u]";
+        emit_group(0, need, g);
+        o << "      }\n    }\n  }\n}\n";
+        return true;
+    }
+
+    // ======================================================================= ROW
+    bool gen_row(std::string* err) {
+        if (p.nreduce == 0) { *err = "row skeleton needs nreduce > 0"; return false; }
+        const int T = v.T;
+        const bool cached = v.vpt > 0;
+        header();
+        o << "#define TROW " << T << "\n#define RPC (NT / TROW)\n#define VPT " << std::max(v.vpt, 1) << "\n";
+        o << "  const int lane = tid % TROW;\n  const int sub = tid / TROW;\n";
+        const int npass = n_passes();
+        // shared buffers: one per reduction, double-buffered by row-iteration parity
+        for (int si : reds) {
+            const Stmt& s = p.stmts[si];
+            if (T > 32) o << "  __shared__ " << acc_type(s) << " sm" << si << "[2][NT / 32];\n";
+        }
+        // cut analysis for the cached variant
+        std::vector<std::set<int>> cuts(npass + 1);
+        std::set<int> all_cuts;
+        if (cached)
+            for (int q = 0; q < npass; ++q) {
+                pass_needed(q, true, &cuts[q]);
+                all_cuts.insert(cuts[q].begin(), cuts[q].end());
+            }
+        o << "  int parity = 0;\n";
+        o << "  for (i64 rbase = (i64)blockIdx.x * RPC; rbase < R; rbase += (i64)gridDim.x * RPC, parity ^= 1) {\n";
+        o << "    const i64 r = rbase + sub;\n    const bool rv = r < R;\n";
+        o << "    const i64 rr = rv ? r : 0;\n";
+        row_offsets("    ", "rr");
+        if (cached) {
+            std::set<int> eargs;
+            for (const Stmt& s : p.stmts)
+                if (s.kind == S_LD && s.elem) eargs.insert(s.arg);
+            for (const Stmt& s : p.stmts)
+                if (s.kind == S_ST && s.elem && s.aop != A_ASSIGN) eargs.insert(s.arg);
+            for (int a : eargs) o << "    Vec<" << argT(a) << ", VEC> LQ" << a << "[VPT];\n";
+            for (int id : all_cuts) o << "    " << ct(val(id).dtype) << " CV" << id << "[VPT * VEC];\n";
+        }
+        std::set<int> loaded;
+        for (int q = 0; q <= npass; ++q) {
+            o << "    // ---- stage " << q << "\n";
+            emit_row_values("    ", q, "rv", true, "lane == 0");
+            if (q == npass) break;
+            std::vector<int> sinks = pass_sinks(q);
+            if (sinks.empty()) continue;
+            for (int si : sinks) {
+                const Stmt& s = p.stmts[si];
+                if (s.kind == S_RED || s.kind == S_ARGRED)
+                    o << "    " << acc_type(s) << " acc" << si << " = " << acc_init(s) << ";\n";
+            }
+            std::set<int> need = pass_needed(q, cached, nullptr);
+            // values of this stage that later passes read from the cache must be computed here
+            std::set<int> wr;
+            if (cached) {
+                for (int id : all_cuts)
+                    if (val(id).stage == q) {
+                        wr.insert(id);
+                        // make sure it (and what it needs) is computed in this pass
+                        std::vector<int> stack(1, id);
+                        while (!stack.empty()) {
+                            int x = stack.back();
+                            stack.pop_back();
+                            const Stmt& s = val(x);
+                            if (!s.elem) continue;
+                            if (s.stage < q && s.kind != S_LD) { cuts[q].insert(x); continue; }
+                            if (!need.insert(x).second) continue;
+                            for (int in : s.in) stack.push_back(in);
+                        }
+                    }
+            }
+            GroupCtx g;
+            g.argred_index = "c + j";
+            if (cached) {
+                o << "    _Pragma(\"unroll\") for (int i = 0; i < VPT; ++i) {\n";
+                o << "      const int c = (i * TROW + lane) * VEC;\n      if (rv && c < (int)C) {\n";
+                g.ind = "        ";
+                g.c = "c";
+                g.slot = "[i]";
+                g.cached = true;
+                g.loaded = &loaded;
+                g.cuts_rd = cuts[q];
+                g.cuts_wr = wr;
+                // an arg cached by an earlier pass is not reloaded; emit_group consults `loaded`
+                std::set<int> before = loaded;
+                emit_group(q, need, g);
+                o << "      }\n    }\n";
+            } else {
+                o << "    if (rv) for (int c = lane * VEC; c < (int)C; c += TROW * VEC) {\n";
+                g.ind = "      ";
+                g.c = "c";
+                emit_group(q, need, g);
+                o << "    }\n";
+            }
+            // combine across the T threads of the row
+            for (int si : sinks) {
+                const Stmt& s = p.stmts[si];
+                if (s.kind != S_RED && s.kind != S_ARGRED) continue;
+                const std::string buf = T > 32 ? "sm" + std::to_string(si) + "[parity]" : "nullptr";
+                const std::string bufT = T > 32 ? buf : "(" + acc_type(s) + "*)nullptr";
+                if (s.kind == S_RED)
+                    o << "    const " << ct(s.dtype) << " " << vn(s.id) << " = row_reduce<" << red_struct(s.name)
+                      << ", TROW>(acc" << si << ", " << bufT << ");\n";
+                else
+                    o << "    const int " << vn(s.id) << " = (int)row_arg_reduce<" << red_struct(s.name) << ", TROW>(acc"
+                      << si << ", " << bufT << ").i;\n";
+                if (need_inv.count(s.id)) o << "    const float rinv" << s.id << " = 1.0f / " << vn(s.id) << ";\n";
+            }
+        }
+        o << "  }\n}\n";
+        (void)err;
+        return true;
+    }
+
+    // ======================================================================= ALL
+    bool gen_all(std::string* err) {
+        if (p.nreduce != p.rank) { *err = "all skeleton needs nreduce = rank"; return false; }
+        if (p.max_stage > 1) { *err = "all skeleton handles one level of reductions"; return false; }
+        for (const Stmt& s : p.stmts)
+            if ((s.kind == S_ST || s.kind == S_STX) && s.elem) { *err = "all skeleton has no element stores"; return false; }
+        header();
+        for (size_t a = 0; a < p.args.size(); ++a) o << "  const i64 ro" << a << " = 0;\n";
+        for (int si : reds) {
+            const Stmt& s = p.stmts[si];
+            o << "  __shared__ " << acc_type(s) << " sm" << si << "[NT / 32];\n";
+            o << "  " << acc_type(s) << " acc" << si << " = " << acc_init(s) << ";\n";
+        }
+        // row-level values of stage 0 that feed the element work (loads of R args, functors)
+        std::set<int> need = pass_needed(0, false, nullptr);
+        std::set<int> largs = args_loaded_in(need, 0);
+        // stage-0 row values are needed both before (operands) and after; emit those without
+        // side effects now, stores later
+        for (const Stmt& s : p.stmts) {
+            if (s.elem || s.stage != 0) continue;
+            if (s.kind == S_LD)
+                o << "  const " << ct(s.dtype) << " " << vn(s.id) << " = a" << s.arg << "[0];\n";
+            else if (s.kind == S_OP || s.kind == S_CAST)
+                o << "  const " << ct(s.dtype) << " " << vn(s.id) << " = " << expr(s) << ";\n";
+            else continue;
+            if (need_inv.count(s.id)) o << "  const float rinv" << s.id << " = 1.0f / " << vn(s.id) << ";\n";
+        }
+        o << "  const i64 chunk = (i64)NT * VEC * UNROLL;\n";
+        o << "  for (i64 cb = (i64)blockIdx.x * chunk; cb < C; cb += (i64)gridDim.x * chunk) {\n";
+        bool hoist = v.nin == 1 && v.unroll > 1;
+        if (hoist) {
+            for (int a : largs) o << "    Vec<" << argT(a) << ", VEC> q" << a << "[UNROLL];\n";
+            o << "    _Pragma(\"unroll\") for (int u = 0; u < UNROLL; ++u) {\n";
+            o << "      const i64 c = cb + ((i64)u * NT + tid) * VEC;\n      if (c < C) {\n";
+            for (int a : largs) emit_arg_load("        ", a, "q" + std::to_string(a) + "[u]", "c", false);
+            o << "      }\n    }\n";
+        }
+        o << "    _Pragma(\"unroll\") for (int u = 0; u < UNROLL; ++u) {\n";
+        o << "      const i64 c = cb + ((i64)u * NT + tid) * VEC;\n      if (c < C) {\n";
+        GroupCtx g;
+        g.ind = "        ";
+        g.c = "c";
+        g.skip_loads = hoist;
+        g.hoist_idx = "[u]";
+        g.argred_index = "c + j";
+        emit_group(0, need, g);
+        o << "      }\n    }\n  }\n";
+        // CTA partials
+        for (int si : reds) {
+            const Stmt& s = p.stmts[si];
+            if (s.kind == S_RED)
+                o << "  acc" << si << " = block_reduce<" << red_struct(s.name) << ", NT>(acc" << si << ", sm" << si << ");\n";
+            else
+                o << "  acc" << si << " = block_arg_reduce<" << red_struct(s.name) << ", NT>(acc" << si << ", sm" << si << ");\n";
+        }
+        // cross-CTA exchange through scratch; the last CTA to arrive finishes
+        o << "  if (gridDim.x > 1) {\n";
+        o << "    __shared__ bool is_last;\n";
+        o << "    char* const scratch = reinterpret_cast<char*>(" << W(L.w_scratch) << ");\n";
+        o << "    u32* const counter = reinterpret_cast<u32*>(" << W(L.w_counter) << ");\n";
+        size_t off = 0;
+        std::vector<size_t> offs;
+        for (int si : reds) {
+            offs.push_back(off);
+            off += 16;   // one 16-byte slot per reduction per CTA
+        }
+        o << "    const i64 stride = " << off << ";\n";
+        o << "    if (tid == 0) {\n";
+        for (size_t k = 0; k < reds.size(); ++k) {
+            const Stmt& s = p.stmts[reds[k]];
+            o << "      *reinterpret_cast<" << acc_type(s) << "*>(scratch + blockIdx.x * stride + " << offs[k]
+              << ") = acc" << reds[k] << ";\n";
+        }
+        o << "      __threadfence();\n";
+        o << "      const u32 t = atomicInc(counter, gridDim.x - 1);\n";
+        o << "      is_last = (t == gridDim.x - 1);\n    }\n";
+        o << "    __syncthreads();\n    if (!is_last) return;\n    __threadfence();\n";
+        for (size_t k = 0; k < reds.size(); ++k) {
+            const Stmt& s = p.stmts[reds[k]];
+            int si = reds[k];
+            o << "    acc" << si << " = " << acc_init(s) << ";\n";
+            o << "    for (u32 b = tid; b < gridDim.x; b += NT) acc" << si << " = "
+              << acc_merge(s, "acc" + std::to_string(si),
+                           "ld_cg(reinterpret_cast<const " + acc_type(s) + "*>(scratch + b * stride + " +
+                               std::to_string(offs[k]) + "))")
+              << ";\n";
+            o << "    __syncthreads();\n";
+            if (s.kind == S_RED)
+                o << "    acc" << si << " = block_reduce<" << red_struct(s.name) << ", NT>(acc" << si << ", sm" << si << ");\n";
+            else
+                o << "    acc" << si << " = block_arg_reduce<" << red_struct(s.name) << ", NT>(acc" << si << ", sm" << si << ");\n";
+        }
+        o << "  }\n";
+        for (int si : reds) {
+            const Stmt& s = p.stmts[si];
+            o << "  const " << ct(s.dtype) << " " << vn(s.id) << " = " << acc_result(s, "acc" + std::to_string(si)) << ";\n";
+            if (need_inv.count(s.id)) o << "  const float rinv" << s.id << " = 1.0f / " << vn(s.id) << ";\n";
+        }
+        // stage-0 stores (rare) and stage-1 row values + stores
+        for (const Stmt& s : p.stmts) {
+            if (s.elem || s.stage != 0 || (s.kind != S_ST && s.kind != S_STX)) continue;
+            const std::string dst = "a" + std::to_string(s.arg) + "[0]";
+            if (s.kind == S_ST) o << "  if (tid == 0) " << dst << " = " << assign_rhs(s.aop, dst, vn(s.in[0])) << ";\n";
+        }
+        emit_row_values("  ", 1, "true", true, "tid == 0");
+        o << "}\n";
+        return true;
+    }
+
+    // ======================================================================= COL
+    bool gen_col(std::string* err) {
+        if (p.nreduce == 0 || v.nout != 1 || v.nin != 1) { *err = "col skeleton needs one outer and one reduced dim"; return false; }
+        if (p.max_stage > 1) { *err = "col skeleton handles one level of reductions"; return false; }
+        if (p.has_indirect) { *err = "col skeleton has no indirect access"; return false; }
+        for (const Stmt& s : p.stmts)
+            if ((s.kind == S_ST || s.kind == S_STX) && s.elem) { *err = "col skeleton has no element stores"; return false; }
+        header();
+        o << "#define TXO " << v.tx << "\n#define TYI " << v.ty << "\n";
+        o << "  const int tx = tid % TXO, ty = tid / TXO;\n";
+        o << "  const i64 o0 = ((i64)blockIdx.x * TXO + tx) * VEC;\n";
+        o << "  const bool ov = o0 < R;\n";
+        o << "  const i64 per = " << W(L.w_aux0) << ";\n";
+        o << "  const i64 c0 = (i64)blockIdx.y * per;\n";
+        o << "  const i64 c1 = (c0 + per < C) ? c0 + per : C;\n";
+        for (int si : reds) {
+            const Stmt& s = p.stmts[si];
+            o << "  __shared__ " << acc_type(s) << " sm" << si << "[TYI][TXO * VEC];\n";
+            o << "  " << acc_type(s) << " acc" << si << "[VEC];\n";
+            o << "  _Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) acc" << si << "[j] = " << acc_init(s) << ";\n";
+        }
+        // per-arg base along the outer dim: ro<a> points at outer index o0
+        for (size_t a = 0; a < p.args.size(); ++a)
+            o << "  const i64 ro" << a << " = (ov ? o0 : 0) * " << W(L.arg_rs((int)a, 0)) << ";\n";
+        std::set<int> need = pass_needed(0, false, nullptr);
+        std::set<int> largs = args_loaded_in(need, 0);
+        // row-level stage-0 values used inside the loop must not vary with the outer
+        // index here unless they come from R args; those are loaded per lane below
+        std::set<int> r0_in_loop;
+        for (int id : need)
+            for (int in : val(id).in)
+                if (!val(in).elem && val(in).kind != S_SC && val(in).kind != S_CONST) r0_in_loop.insert(in);
+        if (!r0_in_loop.empty()) { *err = "col skeleton: element work may not use row-level loads"; return false; }
+        o << "  if (ov) {\n";
+        o << "    _Pragma(\"unroll " << v.unroll << "\") for (i64 c = c0 + ty; c < c1; c += TYI) {\n";
+        for (int a : largs) {
+            const std::string T = argT(a);
+            char oc = v.ocls[a];
+            const std::string coff = v.cls[a] == 'z' ? "0" : (v.cls[a] == 'u' ? "c" : "c * " + W(L.arg_cs(a, 0, v.nout)));
+            o << "      Vec<" << T << ", VEC> q" << a << ";\n";
+            if (v.vec > 1 && oc == 'u')
+                o << "      q" << a << " = vload<" << T << ", VEC>(a" << a << " + ro" << a << " + " << coff << ");\n";
+            else if (oc == 'z')
+                o << "      { const " << T << " t_ = a" << a << "[" << coff << "]; _Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) q"
+                  << a << ".x[j] = t_; }\n";
+            else
+                o << "      _Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) q" << a << ".x[j] = a" << a << "[ro" << a
+                  << " + j * " << W(L.arg_rs(a, 0)) << " + " << coff << "];\n";
+        }
+        {
+            GroupCtx g;
+            g.ind = "      ";
+            g.c = "c";
+            g.skip_loads = true;
+            g.hoist_idx = "";
+            g.acc_suffix = "[j]";
+            g.argred_index = "c";
+            // emit_group's lane loop walks j over the OUTER lanes here
+            emit_group(0, need, g);
+        }
+        o << "    }\n  }\n";
+        // fold the TYI slices of the CTA
+        for (int si : reds) {
+            const Stmt& s = p.stmts[si];
+            o << "  _Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) sm" << si << "[ty][tx * VEC + j] = acc" << si << "[j];\n";
+            (void)s;
+        }
+        o << "  __syncthreads();\n";
+        o << "  if (ty == 0) {\n";
+        for (int si : reds) {
+            const Stmt& s = p.stmts[si];
+            o << "    _Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) {\n      " << acc_type(s) << " t_ = sm" << si
+              << "[0][tx * VEC + j];\n      for (int k = 1; k < TYI; ++k) t_ = "
+              << acc_merge(s, "t_", "sm" + std::to_string(si) + "[k][tx * VEC + j]") << ";\n      acc" << si
+              << "[j] = t_;\n    }\n";
+        }
+        o << "  }\n";
+        // cross-CTA: slices of the reduced dim meet in scratch, last CTA of the tile finishes
+        o << "  if (gridDim.y > 1) {\n";
+        o << "    __shared__ bool is_last;\n";
+        o << "    char* const scratch = reinterpret_cast<char*>(" << W(L.w_scratch) << ");\n";
+        o << "    u32* const counter = reinterpret_cast<u32*>(" << W(L.w_counter) << ");\n";
+        o << "    const i64 Rpad = (i64)gridDim.x * TXO * VEC;\n";
+        for (size_t k = 0; k < reds.size(); ++k) {
+            const Stmt& s = p.stmts[reds[k]];
+            o << "    " << acc_type(s) << "* const part" << reds[k] << " = reinterpret_cast<" << acc_type(s)
+              << "*>(scratch + " << k << " * (i64)gridDim.y * Rpad * 16);\n";
+        }
+        o << "    if (ty == 0) {\n";
+        for (int si : reds)
+            o << "      _Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) part" << si << "[(i64)blockIdx.y * Rpad + o0 + j] = acc" << si
+              << "[j];\n";
+        o << "    }\n";
+        o << "    __threadfence();\n    __syncthreads();\n";
+        o << "    if (tid == 0) { const u32 t = atomicInc(counter + blockIdx.x, gridDim.y - 1); is_last = (t == gridDim.y - 1); }\n";
+        o << "    __syncthreads();\n    if (!is_last) return;\n    __threadfence();\n";
+        o << "    if (ty == 0) {\n";
+        for (int si : reds) {
+            const Stmt& s = p.stmts[si];
+            o << "      _Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) {\n        " << acc_type(s) << " t_ = "
+              << acc_init(s) << ";\n        for (u32 sl = 0; sl < gridDim.y; ++sl) t_ = "
+              << acc_merge(s, "t_", "ld_cg(&part" + std::to_string(si) + "[(i64)sl * Rpad + o0 + j])")
+              << ";\n        acc" << si << "[j] = t_;\n      }\n";
+        }
+        o << "    }\n  }\n";
+        // finish: row-level values and stores per outer index
+        o << "  if (ty == 0 && ov) {\n";
+        o << "    _Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) {\n";
+        for (size_t a = 0; a < p.args.size(); ++a)
+            o << "      const i64 fo" << a << " = (o0 + j) * " << W(L.arg_rs((int)a, 0)) << ";\n";
+        // shadow ro<a> with the per-lane offsets for emit_row_values
+        o << "      {\n";
+        for (size_t a = 0; a < p.args.size(); ++a) o << "        const i64 ro" << a << " = fo" << a << ";\n";
+        for (int si : reds) {
+            const Stmt& s = p.stmts[si];
+            o << "        const " << ct(s.dtype) << " " << vn(s.id) << " = "
+              << acc_result(s, "acc" + std::to_string(si) + "[j]") << ";\n";
+            if (need_inv.count(s.id)) o << "        const float rinv" << s.id << " = 1.0f / " << vn(s.id) << ";\n";
+        }
+        emit_row_values("        ", 0, "true", false, "");
+        emit_row_values("        ", 1, "true", false, "");
+        o << "      }\n    }\n  }\n}\n";
+        return true;
+    }
+};
+
+}  // namespace
+
+bool generate_kernel(const Program& p, const Variant& v, std::string* src, std::string* err) {
+    if ((int)v.cls.size() != (int)p.args.size()) { *err = "variant: one inner-stride class per arg expected"; return false; }
+    if (v.kind == K_COL && v.ocls.size() != p.args.size()) { *err = "variant: one outer-stride class per arg expected"; return false; }
+    Gen g(p, v);
+    bool ok = false;
+    switch (v.kind) {
+        case K_MAP: ok = g.gen_map(err); break;
+        case K_ROW: ok = g.gen_row(err); break;
+        case K_ALL: ok = g.gen_all(err); break;
+        case K_COL: ok = g.gen_col(err); break;
+    }
+    if (ok) *src = g.o.str();
+    return ok;
+}
+
+}  // namespace dalib

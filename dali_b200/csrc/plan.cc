@@ -1,0 +1,320 @@
+// Launch planning: from run-time shapes/strides to a kernel variant + geometry.
+//
+// Takes over what JITRunnerImpl::run does before it calls the compiled module
+// (dali/array/jit/jit.cpp:1146-1164: rank collapse via min_computation_rank /
+// jit_right_fit_ndim, :1227-1251) and what the emitted host code does to size
+// the grid (:716-772), with 64-bit extents.
+#include <algorithm>
+#include <cstring>
+#include <sstream>
+
+#include "runtime.h"
+
+namespace dalib {
+
+namespace {
+
+const int kSMs = 148;   // B200
+
+struct Dim {
+    long long extent;
+    std::vector<long long> stride;   // per arg
+};
+
+// drop extent-1 dims, then merge neighbours that every arg walks contiguously
+void collapse(std::vector<Dim>* dims) {
+    std::vector<Dim> out;
+    for (const Dim& d : *dims)
+        if (d.extent != 1) out.push_back(d);
+    bool merged = true;
+    while (merged && out.size() > 1) {
+        merged = false;
+        for (size_t i = 0; i + 1 < out.size(); ++i) {
+            bool ok = true;
+            for (size_t a = 0; a < out[i].stride.size(); ++a)
+                ok = ok && out[i].stride[a] == out[i + 1].stride[a] * out[i + 1].extent;
+            if (ok) {
+                out[i + 1].extent *= out[i].extent;
+                out.erase(out.begin() + i);
+                merged = true;
+                break;
+            }
+        }
+    }
+    *dims = out;
+}
+
+int pow2_ceil(long long x) {
+    int p = 1;
+    while (p < x && p < (1 << 30)) p <<= 1;
+    return p;
+}
+
+int ilog2(int x) {
+    int l = 0;
+    while ((1 << l) < x) ++l;
+    return l;
+}
+
+}  // namespace
+
+std::string LaunchPlan::describe() const {
+    std::ostringstream s;
+    s << variant.key() << " grid=" << grid_x << "x" << grid_y << " R=" << (words.size() > 0 ? words[0] : 0)
+      << " C=" << (words.size() > 1 ? words[1] : 0);
+    return s.str();
+}
+
+bool plan_launch(const Program& p, const int64_t* space, int rank,
+                 void* const* array_data, const int64_t* offsets,
+                 const int64_t* const* strides, int n_arrays,
+                 const void* const* scalars, int n_scalars,
+                 LaunchPlan* plan, std::string* err) {
+    if (rank != p.rank) { *err = "launch: space rank differs from the program's"; return false; }
+    if (n_arrays != (int)p.args.size()) { *err = "launch: wrong number of arrays"; return false; }
+    if (n_scalars != (int)p.scalars.size()) { *err = "launch: wrong number of scalars"; return false; }
+    const int nargs = n_arrays;
+    long long total = 1;
+    for (int d = 0; d < rank; ++d) {
+        if (space[d] < 0) { *err = "launch: negative extent"; return false; }
+        total *= space[d];
+    }
+    LaunchPlan out;
+    if (total == 0) {
+        if (p.nreduce > 0) { *err = "launch: reduction over an empty space"; return false; }
+        out.empty = true;
+        *plan = out;
+        return true;
+    }
+
+    // per-arg strides in space coordinates
+    std::vector<std::vector<long long>> st(nargs, std::vector<long long>(rank, 0));
+    const int n_outer_dims = rank - p.nreduce;
+    for (int a = 0; a < nargs; ++a) {
+        const bool elem = p.nreduce == 0 ? true : p.args[a].elem_level;
+        const int used = elem ? rank : n_outer_dims;
+        if (strides && strides[a]) {
+            for (int d = 0; d < used; ++d) st[a][d] = strides[a][d];
+        } else {
+            long long s = 1;
+            for (int d = used - 1; d >= 0; --d) { st[a][d] = s; s *= space[d]; }
+        }
+        for (int d = 0; d < rank; ++d) if (space[d] == 1) st[a][d] = 0;
+    }
+
+    // split into outer / inner groups and collapse each
+    std::vector<Dim> outer, inner;
+    for (int d = 0; d < rank; ++d) {
+        Dim dim;
+        dim.extent = space[d];
+        for (int a = 0; a < nargs; ++a) dim.stride.push_back(st[a][d]);
+        if (p.nreduce == 0 || d < n_outer_dims) outer.push_back(dim);
+        else inner.push_back(dim);
+    }
+    collapse(&outer);
+    collapse(&inner);
+    if (p.nreduce == 0) {
+        // map: the innermost collapsed dim becomes the inner group
+        if (!outer.empty()) { inner.push_back(outer.back()); outer.pop_back(); }
+    }
+    if (inner.empty()) {
+        Dim one;
+        one.extent = 1;
+        one.stride.assign(nargs, 0);
+        inner.push_back(one);
+    }
+    if (outer.size() > 8 || inner.size() > 8) { *err = "launch: more than 8 non-collapsible dims"; return false; }
+
+    Variant v;
+    v.nout = (int)outer.size();
+    v.nin = (int)inner.size();
+    long long R = 1, C = 1;
+    for (const Dim& d : outer) R *= d.extent;
+    for (const Dim& d : inner) C *= d.extent;
+
+    // stride classes along the (single) inner dim / (single) outer dim
+    std::vector<char*> ptr(nargs);
+    for (int a = 0; a < nargs; ++a)
+        ptr[a] = (char*)array_data[a] + (offsets ? offsets[a] : 0) * dtype_size(p.args[a].dtype);
+    v.cls.assign(nargs, 's');
+    v.ocls.assign(nargs, 's');
+    for (int a = 0; a < nargs; ++a) {
+        if (v.nin == 1) {
+            long long s = inner[0].stride[a];
+            v.cls[a] = (s == 1 || C == 1) ? 'u' : (s == 0 ? 'z' : 's');
+            if (C == 1 && s == 0) v.cls[a] = 'z';
+        }
+        if (v.nout == 1) {
+            long long s = outer[0].stride[a];
+            v.ocls[a] = s == 1 ? 'u' : (s == 0 ? 'z' : 's');
+        }
+    }
+
+    auto arg_elem = [&](int a) { return p.nreduce == 0 ? true : p.args[a].elem_level; };
+    int max_item = 4;
+    int n_elem_args = 0;
+    for (int a = 0; a < nargs; ++a)
+        if (arg_elem(a) && !p.args[a].indirect) {
+            max_item = std::max(max_item, dtype_size(p.args[a].dtype));
+            ++n_elem_args;
+        }
+
+    // ---------------------------------------------------------------- skeleton choice
+    bool elem_stores = false;
+    for (const Stmt& s : p.stmts)
+        if ((s.kind == S_ST || s.kind == S_STX) && s.elem) elem_stores = true;
+    bool col_ok = p.nreduce > 0 && v.nout == 1 && v.nin == 1 && p.max_stage <= 1 && !elem_stores &&
+                  !p.has_indirect && p.n_reductions > 0;
+    if (col_ok) {
+        // threads should run along the outer dim when that is the contiguous one
+        bool any_unit_outer = false, all_fit = true;
+        for (int a = 0; a < nargs; ++a) {
+            if (!arg_elem(a) || !p.args[a].read) continue;
+            if (v.ocls[a] == 'u' && v.cls[a] != 'u') any_unit_outer = true;
+            else if (v.ocls[a] == 'z' || (v.ocls[a] == 'u' && C == 1)) {}
+            else all_fit = false;
+        }
+        col_ok = any_unit_outer && all_fit;
+        // element work must not read row-level loads (they would vary per lane)
+        for (const Stmt& s : p.stmts) {
+            if (!s.elem) continue;
+            for (int in : s.in) {
+                const Stmt& src = p.stmts[p.value_stmt[in]];
+                if (!src.elem && src.kind != S_SC && src.kind != S_CONST) col_ok = false;
+            }
+        }
+    }
+    bool all_ok = p.nreduce == p.rank && p.nreduce > 0 && p.max_stage <= 1 && !elem_stores && p.n_reductions > 0;
+
+    if (p.nreduce == 0) v.kind = K_MAP;
+    else if (all_ok) v.kind = K_ALL;
+    else if (col_ok) v.kind = K_COL;
+    else v.kind = K_ROW;
+
+    // ---------------------------------------------------------------- vector width
+    auto aligned = [&](int a, int vec, bool along_outer) {
+        const int bytes = dtype_size(p.args[a].dtype) * vec;
+        if (((uintptr_t)ptr[a]) % bytes != 0) return false;
+        const std::vector<Dim>& other = along_outer ? inner : outer;
+        for (const Dim& d : other)
+            if (d.stride[a] % vec != 0) return false;
+        return true;
+    };
+    int vec = 16 / max_item;
+    if (v.kind == K_COL) {
+        if (R % vec != 0) vec = 1;
+        for (int a = 0; a < nargs && vec > 1; ++a) {
+            if (!arg_elem(a)) continue;
+            if (v.ocls[a] == 'z') continue;
+            if (v.ocls[a] != 'u' || !aligned(a, vec, true)) vec = 1;
+        }
+    } else {
+        if (v.nin != 1 || C % vec != 0) vec = 1;
+        for (int a = 0; a < nargs && vec > 1; ++a) {
+            if (!arg_elem(a)) continue;
+            if (p.args[a].indirect) continue;   // scalar access through the index
+            if (v.cls[a] == 'z') continue;
+            if (v.cls[a] != 'u' || !aligned(a, vec, false)) vec = 1;
+        }
+    }
+    v.vec = vec;
+
+    // ---------------------------------------------------------------- geometry
+    long long aux0 = 0, aux1 = 0;
+    const long long groups = (C + vec - 1) / vec;
+    if (v.kind == K_MAP) {
+        v.threads = 256;
+        v.unroll = groups >= 1024 ? 4 : 1;
+        int TX = (int)std::min<long long>(256, pow2_ceil((groups + v.unroll - 1) / v.unroll));
+        int TY = 256 / TX;
+        aux0 = ilog2(TX);
+        long long gx = (groups + (long long)TX * v.unroll - 1) / ((long long)TX * v.unroll);
+        long long gy = std::min<long long>((R + TY - 1) / TY, 65535);
+        if (gx > 2147483647LL) { *err = "launch: inner extent too large"; return false; }
+        out.grid_x = (unsigned)gx;
+        out.grid_y = (unsigned)gy;
+        v.T = 0; v.vpt = 0; v.tx = 0; v.ty = 0;
+    } else if (v.kind == K_ROW) {
+        if (C > 2147483647LL) { *err = "launch: reduced extent too large for the row skeleton"; return false; }
+        const int target = vec > 1 ? 2 : 4;          // vector groups per thread
+        int T = 1;
+        while (T < 1024 && (groups + T - 1) / T > target) T <<= 1;
+        int vpt = (int)((groups + T - 1) / T);
+        int n_cached = n_elem_args + p.n_reductions;  // leaf arrays + value caches (upper bound)
+        bool cached = v.nin == 1 && (long long)vpt * vec * n_cached <= 64;
+        v.T = T;
+        v.vpt = cached ? vpt : 0;
+        v.threads = T > 256 ? T : 256;
+        // few rows: smaller CTAs spread them over more SMs
+        while (v.threads > T && v.threads > 64 && R * T / v.threads < 2 * kSMs) v.threads >>= 1;
+        if (v.threads < 32) v.threads = 32;
+        if (v.threads < T) v.threads = T;
+        int rpc = v.threads / T;
+        long long gx = (R + rpc - 1) / rpc;
+        out.grid_x = (unsigned)std::min<long long>(gx, (long long)kSMs * 32);
+        v.unroll = 1; v.tx = 0; v.ty = 0;
+    } else if (v.kind == K_ALL) {
+        v.threads = 256;
+        v.unroll = 4;
+        long long chunk = (long long)v.threads * vec * v.unroll;
+        long long gx = (C + chunk - 1) / chunk;
+        out.grid_x = (unsigned)std::min<long long>(gx, (long long)kSMs * 8);
+        out.scratch_bytes = (size_t)out.grid_x * 16 * std::max(1, p.n_reductions);
+        out.counters = 1;
+        v.T = 0; v.vpt = 0; v.tx = 0; v.ty = 0;
+    } else {  // K_COL
+        v.threads = 256;
+        v.tx = 32;
+        v.ty = 8;
+        v.unroll = 4;
+        long long tiles = (R + (long long)v.tx * vec - 1) / ((long long)v.tx * vec);
+        long long S = ((long long)kSMs * 8 + tiles - 1) / tiles;
+        long long maxS = std::max<long long>(1, C / (v.ty * 8));
+        S = std::max<long long>(1, std::min<long long>(std::min<long long>(S, maxS), 256));
+        long long per = (C + S - 1) / S;
+        S = (C + per - 1) / per;
+        aux0 = per;
+        if (tiles > 2147483647LL) { *err = "launch: outer extent too large"; return false; }
+        out.grid_x = (unsigned)tiles;
+        out.grid_y = (unsigned)S;
+        if (S > 1) {
+            out.scratch_bytes = (size_t)std::max(1, p.n_reductions) * (size_t)S * (size_t)tiles * v.tx * vec * 16;
+            out.counters = (size_t)tiles;
+        }
+        v.T = 0; v.vpt = 0;
+    }
+
+    // ---------------------------------------------------------------- parameter words
+    ParamLayout L(p, v);
+    out.words.assign(L.total, 0);
+    out.words[L.w_R] = R;
+    out.words[L.w_C] = C;
+    out.words[L.w_aux0] = aux0;
+    out.words[L.w_aux1] = aux1;
+    for (int k = 0; k < v.nout; ++k) out.words[L.w_oshape + k] = outer[k].extent;
+    for (int k = 0; k < v.nin; ++k) out.words[L.w_ishape + k] = inner[k].extent;
+    for (int a = 0; a < nargs; ++a) {
+        out.words[L.arg_ptr(a)] = (long long)(uintptr_t)ptr[a];
+        // lead stride of an indirectly addressed arg travels as one extra stride
+        // entry after the `rank` space strides
+        long long xs = 0;
+        if (p.args[a].indirect) {
+            if (!strides || !strides[a]) { *err = "launch: indirect arg needs explicit strides (rank + 1 entries)"; return false; }
+            xs = strides[a][rank];
+        }
+        out.words[L.arg_xs(a)] = xs;
+        for (int k = 0; k < v.nout; ++k) out.words[L.arg_rs(a, k)] = outer[k].stride[a];
+        for (int k = 0; k < v.nin; ++k) out.words[L.arg_cs(a, k, v.nout)] = inner[k].stride[a];
+    }
+    for (int j = 0; j < n_scalars; ++j) {
+        long long w = 0;
+        if (!scalars || !scalars[j]) { *err = "launch: null scalar"; return false; }
+        std::memcpy(&w, scalars[j], dtype_size(p.scalars[j]));
+        out.words[L.w_scalars + j] = w;
+    }
+    out.variant = v;
+    *plan = out;
+    return true;
+}
+
+}  // namespace dalib

@@ -1,0 +1,262 @@
+// Device-side prelude spliced in front of every generated kernel (compiled by
+// NVRTC for sm_100a; no host headers are available there).
+//
+// Functors restate dali/array/functor.h:27-495 as the reference's CPU path
+// evaluates them (EXP_F = std::exp etc., functor.h:16-23); int32 operands go
+// through double and truncate back, as the templates there do when
+// instantiated with R = int.  Reducers restate dali/array/jit/reducer_kernels.h:
+// 58-170 (initial values -FLT_MAX / FLT_MAX / 0 / 1, :10-54).
+
+typedef long long i64;
+typedef unsigned int u32;
+#define DEV __device__ __forceinline__
+#define DALI_F32_MAX 3.402823466e+38f
+#define DALI_F64_MAX 1.7976931348623158e+308
+#define DALI_I32_MAX 2147483647
+#define DALI_I32_MIN (-2147483647 - 1)
+#define DALI_EPS 1e-6
+
+// ---------------------------------------------------------------- functors
+template <typename T> DEV T f_identity(T a) { return a; }
+template <typename T> DEV T f_negate(T a) { return -a; }
+template <typename T> DEV T f_square(T a) { return a * a; }
+template <typename T> DEV T f_cube(T a) { return a * a * a; }
+template <typename T> DEV T f_add(T a, T b) { return a + b; }
+template <typename T> DEV T f_subtract(T a, T b) { return a - b; }
+template <typename T> DEV T f_eltmul(T a, T b) { return a * b; }
+template <typename T> DEV T f_eltdiv(T a, T b) { return a / b; }
+template <typename T> DEV T f_equals(T a, T b) { return a == b ? (T)1 : (T)0; }
+template <typename T> DEV T f_fill(T a, T b) { return b; }
+template <typename T> DEV T f_div_grad(T a, T b) { return a / (b * b); }
+template <typename T> DEV T f_threshold(T a, T b) { return a < b ? (T)1 : (T)0; }
+template <typename T> DEV T f_max_scalar(T a, T b) { return a > b ? a : b; }
+template <typename T> DEV T f_min_scalar(T a, T b) { return a < b ? a : b; }
+template <typename T> DEV T f_lessthanequal(T a, T b) { return a <= b ? (T)1 : (T)0; }
+template <typename T> DEV T f_greaterthanequal(T a, T b) { return a >= b ? (T)1 : (T)0; }
+template <typename T> DEV T f_dsigmoid(T a) { return a * ((T)1 - a); }
+template <typename T> DEV T f_relu(T a) { return a > (T)0 ? a : (T)0; }
+template <typename T> DEV T f_relu_backward(T a) { return a > (T)0 ? (T)1 : (T)0; }
+template <typename T> DEV T f_sign(T a) { return a > (T)0 ? (T)1 : (T)-1; }
+template <typename T> DEV T f_clipped_relu(T x, T c) { return x > (T)0 ? (x > c ? c : x) : (T)0; }
+template <typename T> DEV T f_clipped_relu_backward(T x, T c) { return x > (T)0 ? (x > c ? (T)0 : (T)1) : (T)0; }
+template <typename T> DEV T f_clip(T x, T c) { return x > c ? c : (x < -c ? -c : x); }
+template <typename T> DEV T f_prelu(T x, T w) { return x > (T)0 ? x : w * x; }
+template <typename T> DEV T f_prelu_backward_weights(T x, T g) { return x > (T)0 ? (T)0 : x * g; }
+template <typename T> DEV T f_prelu_backward_inputs(T x, T w) { return x > (T)0 ? (T)1 : w; }
+template <typename T> DEV T f_steep_sigmoid_backward(T x, T a) { return a * (x - x * x); }
+
+DEV float f_abs(float a) { return fabsf(a); }
+DEV double f_abs(double a) { return fabs(a); }
+DEV int f_abs(int a) { return a < 0 ? -a : a; }
+
+DEV float f_sqrt_f(float a) { return sqrtf(a); }
+DEV double f_sqrt_f(double a) { return sqrt(a); }
+DEV int f_sqrt_f(int a) { return (int)sqrt((double)a); }
+
+DEV float f_rsqrt(float a) { return (float)(1.0 / (double)sqrtf(a)); }
+DEV double f_rsqrt(double a) { return 1.0 / sqrt(a); }
+DEV int f_rsqrt(int a) { return (int)(1.0 / sqrt((double)a)); }
+
+DEV float f_inv(float a) { return 1.0f / a; }
+DEV double f_inv(double a) { return 1.0 / a; }
+DEV int f_inv(int a) { return 1 / a; }
+
+DEV float f_exp(float a) { return expf(a); }
+DEV double f_exp(double a) { return exp(a); }
+DEV int f_exp(int a) { return (int)exp((double)a); }
+
+DEV float f_log(float a) { return logf(a); }
+DEV double f_log(double a) { return log(a); }
+DEV int f_log(int a) { return (int)log((double)a); }
+
+DEV float f_negative_log(float a) { return -logf(a); }
+DEV double f_negative_log(double a) { return -log(a); }
+DEV int f_negative_log(int a) { return (int)(-log((double)a)); }
+
+DEV float f_log_or_zero(float a) { return a > 0.0f ? logf(a) : 0.0f; }
+DEV double f_log_or_zero(double a) { return a > 0.0 ? log(a) : 0.0; }
+DEV int f_log_or_zero(int a) { return a > 0 ? (int)log((double)a) : 0; }
+
+DEV float f_safe_entropy_log(float a) {
+    const float lo = (float)DALI_EPS, hi = (float)(1.0 - DALI_EPS);
+    a = a > hi ? hi : a;
+    a = a < lo ? lo : a;
+    return logf(a);
+}
+DEV double f_safe_entropy_log(double a) {
+    const double lo = DALI_EPS, hi = 1.0 - DALI_EPS;
+    a = a > hi ? hi : a;
+    a = a < lo ? lo : a;
+    return log(a);
+}
+DEV int f_safe_entropy_log(int a) { return (int)f_safe_entropy_log((double)a); }
+
+// 1 / (1 + exp(-a)): the denominator is in [1, inf], where the approximate
+// reciprocal is within 1 ulp and needs no slow path.
+DEV float f_sigmoid(float a) { return __fdividef(1.0f, 1.0f + expf(-a)); }
+DEV double f_sigmoid(double a) { return 1.0 / (1.0 + exp(-a)); }
+DEV int f_sigmoid(int a) { return (int)(1.0 / (1.0 + exp((double)-a))); }
+
+DEV float f_steep_sigmoid(float x, float g) { return __fdividef(1.0f, 1.0f + expf(-g * x)); }
+DEV double f_steep_sigmoid(double x, double g) { return 1.0 / (1.0 + exp(-g * x)); }
+DEV int f_steep_sigmoid(int x, int g) { return (int)(1.0 / (1.0 + exp((double)(-g * x)))); }
+
+DEV float f_tanh(float a) { return tanhf(a); }
+DEV double f_tanh(double a) { return tanh(a); }
+DEV int f_tanh(int a) { return (int)tanh((double)a); }
+
+DEV float f_dtanh(float a) { return 1.0f - a * a; }
+DEV double f_dtanh(double a) { return 1.0 - a * a; }
+DEV int f_dtanh(int a) { return 1 - a * a; }
+
+DEV float f_inverse_tanh(float a) { return (logf(1.0f + a) - logf(1.0f - a)) * 0.5f; }
+DEV double f_inverse_tanh(double a) { return (log(1.0 + a) - log(1.0 - a)) * 0.5; }
+DEV int f_inverse_tanh(int a) { return (int)((log(1.0 + a) - log(1.0 - a)) * 0.5); }
+
+DEV float f_power(float a, float b) { return powf(a, b); }
+DEV double f_power(double a, double b) { return pow(a, b); }
+DEV int f_power(int a, int b) { return (int)pow((double)a, (double)b); }
+
+DEV float f_softplus(float x) { return x > 20.0f ? x : logf(1.0f + expf(x)); }
+DEV double f_softplus(double x) { return x > 20.0 ? x : log(1.0 + exp(x)); }
+DEV int f_softplus(int x) { return x > 20 ? x : (int)log(1.0 + exp((double)x)); }
+
+DEV float f_softplus_backward(float x) { if (x > 20.0f) return 1.0f; float e = expf(x); return e / (1.0f + e); }
+DEV double f_softplus_backward(double x) { if (x > 20.0) return 1.0; double e = exp(x); return e / (1.0 + e); }
+DEV int f_softplus_backward(int x) { return (int)f_softplus_backward((double)x); }
+
+DEV float f_isnotanumber(float a) { return isnan(a) ? 1.0f : 0.0f; }
+DEV double f_isnotanumber(double a) { return isnan(a) ? 1.0 : 0.0; }
+DEV int f_isnotanumber(int a) { return 0; }
+DEV float f_isinfinity(float a) { return isinf(a) ? 1.0f : 0.0f; }
+DEV double f_isinfinity(double a) { return isinf(a) ? 1.0 : 0.0; }
+DEV int f_isinfinity(int a) { return 0; }
+
+DEV float f_binary_cross_entropy(float x, float t) { return -(t * logf(x) + (1.0f - t) * logf(1.0f - x)); }
+DEV double f_binary_cross_entropy(double x, double t) { return -(t * log(x) + (1.0 - t) * log(1.0 - x)); }
+DEV int f_binary_cross_entropy(int x, int t) { return (int)f_binary_cross_entropy((double)x, (double)t); }
+DEV float f_binary_cross_entropy_grad(float x, float t) { return (t - x) / (x * (x - 1.0f)); }
+DEV double f_binary_cross_entropy_grad(double x, double t) { return (t - x) / (x * (x - 1.0)); }
+DEV int f_binary_cross_entropy_grad(int x, int t) { return (int)f_binary_cross_entropy_grad((double)x, (double)t); }
+
+// functor::round is floor(a + 0.5), functor::ceil is ceil(a); both convert.
+template <typename R> DEV R f_round(float a) { return (R)floorf(a + 0.5f); }
+template <typename R> DEV R f_round(double a) { return (R)floor(a + 0.5); }
+template <typename R> DEV R f_round(int a) { return (R)a; }
+template <typename R> DEV R f_ceiling(float a) { return (R)ceilf(a); }
+template <typename R> DEV R f_ceiling(double a) { return (R)ceil(a); }
+template <typename R> DEV R f_ceiling(int a) { return (R)a; }
+
+// ---------------------------------------------------------------- reducers
+template <typename T> struct Lim;
+template <> struct Lim<float> { static DEV float lo() { return -DALI_F32_MAX; } static DEV float hi() { return DALI_F32_MAX; } };
+template <> struct Lim<double> { static DEV double lo() { return -DALI_F64_MAX; } static DEV double hi() { return DALI_F64_MAX; } };
+template <> struct Lim<int> { static DEV int lo() { return DALI_I32_MIN; } static DEV int hi() { return DALI_I32_MAX; } };
+
+struct RSum { template <typename T> static DEV T init() { return (T)0; } template <typename T> static DEV T apply(T a, T b) { return a + b; } };
+struct RProd { template <typename T> static DEV T init() { return (T)1; } template <typename T> static DEV T apply(T a, T b) { return a * b; } };
+struct RMax {
+    template <typename T> static DEV T init() { return Lim<T>::lo(); }
+    template <typename T> static DEV T apply(T a, T b) { return a > b ? a : b; }
+    static DEV float apply(float a, float b) { return fmaxf(a, b); }
+    template <typename T> static DEV bool better(T a, T b) { return a > b; }
+};
+struct RMin {
+    template <typename T> static DEV T init() { return Lim<T>::hi(); }
+    template <typename T> static DEV T apply(T a, T b) { return a < b ? a : b; }
+    static DEV float apply(float a, float b) { return fminf(a, b); }
+    template <typename T> static DEV bool better(T a, T b) { return a < b; }
+};
+
+// (value, index) for argmax / argmin.  The reference keeps the FIRST index at
+// which the running value strictly improves (tmp != res after Reduce,
+// dali/array/jit/all_reduce_kernel_utils.cpp:123-140,210-223) and starts from
+// index 0: `take` reproduces that for one element, `merge` for two partial
+// results (equal values -> lower index).
+template <typename T> struct ArgPair { T v; i64 i; };
+template <typename Op, typename T> DEV ArgPair<T> arg_init() { ArgPair<T> p; p.v = Op::template init<T>(); p.i = 0; return p; }
+template <typename Op, typename T> DEV void arg_take(ArgPair<T>& acc, T v, i64 i) {
+    if (Op::better(v, acc.v)) { acc.v = v; acc.i = i; }
+}
+template <typename Op, typename T> DEV ArgPair<T> arg_merge(ArgPair<T> a, ArgPair<T> b) {
+    const bool take_b = Op::better(b.v, a.v) || (b.v == a.v && b.i < a.i);
+    return take_b ? b : a;
+}
+
+// Loads that bypass L1: partial results written by other CTAs of the same launch.
+template <typename T> DEV T ld_cg(const T* p) { return __ldcg(p); }
+template <typename T> DEV ArgPair<T> ld_cg(const ArgPair<T>* p) {
+    ArgPair<T> r;
+    r.v = __ldcg(&p->v);
+    r.i = __ldcg(&p->i);
+    return r;
+}
+
+template <typename T> DEV T shfl_xor(T v, int m) { return __shfl_xor_sync(0xffffffffu, v, m); }
+template <typename T> DEV ArgPair<T> shfl_xor(ArgPair<T> p, int m) {
+    ArgPair<T> q;
+    q.v = __shfl_xor_sync(0xffffffffu, p.v, m);
+    q.i = __shfl_xor_sync(0xffffffffu, p.i, m);
+    return q;
+}
+
+// Butterfly over the W (<= 32, power of two) adjacent lanes of a warp that
+// share a row; every lane ends with the result.
+template <typename Op, int W, typename T> DEV T group_reduce(T v) {
+#pragma unroll
+    for (int m = W / 2; m > 0; m >>= 1) v = Op::apply(v, shfl_xor(v, m));
+    return v;
+}
+template <typename Op, int W, typename T> DEV ArgPair<T> group_arg_reduce(ArgPair<T> v) {
+#pragma unroll
+    for (int m = W / 2; m > 0; m >>= 1) v = arg_merge<Op, T>(v, shfl_xor(v, m));
+    return v;
+}
+
+// Reduction over the T threads that share a row.  T <= 32: shuffles only.
+// T > 32: one partial per warp through shared memory (`buf` holds NT/32
+// entries and must not be reused before the next __syncthreads), then every
+// thread folds its row's T/32 partials in warp order -- deterministic.
+template <typename Op, int T_, typename T> DEV T row_reduce(T v, T* buf) {
+    if (T_ <= 32) return group_reduce<Op, (T_ <= 32 ? T_ : 32)>(v);
+    v = group_reduce<Op, 32>(v);
+    const int warp = threadIdx.x >> 5;
+    if ((threadIdx.x & 31) == 0) buf[warp] = v;
+    __syncthreads();
+    const int first = (warp / (T_ / 32)) * (T_ / 32);
+    T r = buf[first];
+#pragma unroll
+    for (int k = 1; k < T_ / 32; ++k) r = Op::apply(r, buf[first + k]);
+    return r;
+}
+template <typename Op, int T_, typename T> DEV ArgPair<T> row_arg_reduce(ArgPair<T> v, ArgPair<T>* buf) {
+    if (T_ <= 32) return group_arg_reduce<Op, (T_ <= 32 ? T_ : 32)>(v);
+    v = group_arg_reduce<Op, 32>(v);
+    const int warp = threadIdx.x >> 5;
+    if ((threadIdx.x & 31) == 0) buf[warp] = v;
+    __syncthreads();
+    const int first = (warp / (T_ / 32)) * (T_ / 32);
+    ArgPair<T> r = buf[first];
+#pragma unroll
+    for (int k = 1; k < T_ / 32; ++k) r = arg_merge<Op, T>(r, buf[first + k]);
+    return r;
+}
+
+// Whole-CTA reduction (NT threads, NT a multiple of 32); result valid in every
+// thread.  `buf` holds NT/32 entries.
+template <typename Op, int NT, typename T> DEV T block_reduce(T v, T* buf) { return row_reduce<Op, NT>(v, buf); }
+template <typename Op, int NT, typename T> DEV ArgPair<T> block_arg_reduce(ArgPair<T> v, ArgPair<T>* buf) { return row_arg_reduce<Op, NT>(v, buf); }
+
+// Atomics for scatter-assign through gather (the reference maps = += -= to
+// atomicExch / atomicAdd, dali/array/op/gather.cpp:14-28).
+DEV void atomic_add(float* p, float v) { atomicAdd(p, v); }
+DEV void atomic_add(double* p, double v) { atomicAdd(p, v); }
+DEV void atomic_add(int* p, int v) { atomicAdd(p, v); }
+DEV void atomic_exch(float* p, float v) { atomicExch(p, v); }
+DEV void atomic_exch(int* p, int v) { atomicExch(p, v); }
+DEV void atomic_exch(double* p, double v) { atomicExch((unsigned long long*)p, (unsigned long long)__double_as_longlong(v)); }
+
+// 128-bit global access; callers guarantee 16-byte alignment.
+template <typename T, int N> struct alignas(sizeof(T) * N) Vec { T x[N]; };
+template <typename T, int N> DEV Vec<T, N> vload(const T* p) { return *reinterpret_cast<const Vec<T, N>*>(p); }
+template <typename T, int N> DEV void vstore(T* p, const Vec<T, N>& v) { *reinterpret_cast<Vec<T, N>*>(p) = v; }

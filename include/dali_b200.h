@@ -1,0 +1,165 @@
+/* dali_b200 -- C ABI of the B200 (sm_100a) back end for Dali's lazy
+ * expression -> optimize -> compile -> cache -> run path.
+ *
+ * The reference has no foreign-function interface; the seam this library
+ * replaces is the one between the expression graph and the code it used to
+ * generate:
+ *   - the compiled-module entry point
+ *       extern "C" void maker(void** array_data, const int* offsets,
+ *                             const int** sizes, const int** strides,
+ *                             const void** scalar_arguments, const int** shapes)
+ *     (dali/utils/compiler.cpp:181-200, argument list dali/array/jit/jit.cpp:1030-1038),
+ *   - the compile-or-load step Compiler::load / Compiler::compile keyed by a
+ *     64-bit hash (dali/utils/compiler.h:91-173, dali/array/jit/jit.cpp:1011-1039),
+ *   - the GEMM implementation registered for op::MatMul
+ *     (dali/array/gemm/cublas_gemm.cu:110-198).
+ *
+ * Everything here is plain C: pointers, sizes, integer status codes.  Every
+ * function returns DALIB200_OK (0) or a negative status; the message of the
+ * last failure on the calling thread is read with dalib200_last_error().
+ * There is no CPU fallback: without a CUDA device every compute entry point
+ * fails with DALIB200_ERR_NO_DEVICE.
+ */
+#ifndef DALI_B200_H
+#define DALI_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DALIB200_ABI_VERSION 1
+
+enum dalib200_status {
+    DALIB200_OK = 0,
+    DALIB200_ERR_INVALID = -1,     /* bad argument / malformed IR / shape mismatch */
+    DALIB200_ERR_NO_DEVICE = -2,   /* no CUDA device or driver */
+    DALIB200_ERR_COMPILE = -3,     /* NVRTC rejected the generated kernel (log in last_error) */
+    DALIB200_ERR_CUDA = -4,        /* a CUDA runtime/driver call failed */
+    DALIB200_ERR_NOT_FOUND = -5,   /* unknown kernel hash */
+    DALIB200_ERR_UNSUPPORTED = -6, /* valid request the back end has no kernel for */
+    DALIB200_ERR_TOO_LARGE = -7    /* size beyond a documented fixed limit */
+};
+
+/* element types.  0..2 are the reference's DType values
+ * (dali/array/dtype.h:6-10); bf16 exists only as a GEMM operand/output. */
+enum dalib200_dtype {
+    DALIB200_F32 = 0,
+    DALIB200_F64 = 1,
+    DALIB200_I32 = 2,
+    DALIB200_BF16 = 3
+};
+
+/* Copies the calling thread's last error message (NUL-terminated, truncated
+ * to `capacity`) into `buffer`; returns the full length. */
+size_t dalib200_last_error(char* buffer, size_t capacity);
+
+/* Library / ABI version (DALIB200_ABI_VERSION). */
+int dalib200_abi_version(void);
+
+/* Binds the library to the first `n_gpus` visible CUDA devices (n_gpus <= 0:
+ * all of them), creates their primary contexts and per-device scratch
+ * arenas.  Idempotent.  Replaces the reference's implicit device set-up in
+ * memory::allocate (dali/array/memory/memory_ops.cu.cpp:59-75). */
+int dalib200_init(int n_gpus);
+
+/* Number of devices bound by dalib200_init (0 before it / without a GPU). */
+int dalib200_device_count(void);
+
+/* ---- compile cache -------------------------------------------------------
+ * Replaces Compiler::load / is_loaded / compile
+ * (dali/utils/compiler.h:91-173, dali/utils/compiler.cpp:68-227).           */
+
+/* Registers the fused-expression program `ir` (text, see dali_b200/csrc/ir.h)
+ * under the caller's structural hash (the reference's kernel key,
+ * dali/array/jit/jit.cpp:1017-1021).  Parses and validates it; kernels are
+ * generated per concrete layout on first launch (or by dalib200_precompile)
+ * and kept in memory and on disk.  Registering the same hash again with the
+ * same text is a no-op; with different text it fails (hash collision). */
+int dalib200_compile(uint64_t hash, const char* ir, size_t ir_len);
+
+/* 1 if `hash` is registered in this process, else 0. */
+int dalib200_is_loaded(uint64_t hash);
+
+/* Generates and NVRTC-compiles (sm_100a) the kernel of `hash` for the layout
+ * described exactly as in dalib200_launch, without launching.  Works without
+ * a GPU.  On success *cubin_size (if non-NULL) receives the image size. */
+int dalib200_precompile(uint64_t hash,
+                        const int64_t* space, int space_rank,
+                        void* const* array_data, const int64_t* offsets,
+                        const int64_t* const* strides, int n_arrays,
+                        size_t* cubin_size);
+
+/* Directory of the on-disk cache (<dir>/<key>.cubin, .cu, .log).  Default:
+ * $DALI_CACHE_DIR, else ~/.dali_b200/cache/ (reference default ~/.dali/cache/,
+ * dali/utils/compiler.cpp:234-238).  Setting DALI_JIT_ALWAYS_RECOMPILE=true
+ * ignores cached images once per process, as dali/array/jit/jit.cpp:27-47. */
+int dalib200_cache_set_dir(const char* dir);
+size_t dalib200_cache_get_dir(char* buffer, size_t capacity);
+/* Drops every in-memory module (and with remove_files != 0 the files too). */
+int dalib200_cache_clear(int remove_files);
+/* Counters: [0] programs registered, [1] kernels in memory, [2] NVRTC
+ * compilations, [3] disk hits, [4] launches. */
+int dalib200_cache_stats(uint64_t stats[5]);
+
+/* ---- launch ----------------------------------------------------------------
+ * Replaces the call `compiled_self(data_ptrs, offsets, shapes, strides,
+ * scalars, shapes_for_nodes)` (dali/array/jit/jit.cpp:1216-1223).
+ *
+ *  device      index among the devices bound by dalib200_init
+ *  stream      a cudaStream_t / CUstream (NULL = the legacy default stream)
+ *  space       extents of the program's iteration space, outermost first;
+ *              space_rank must equal the rank the program declares
+ *  array_data  DEVICE base pointer of the i-th distinct buffer, in the order
+ *              the program declares its args (first-visit order, as
+ *              SymbolTable::declare_array, dali/array/jit/jit.cpp:75-87)
+ *  offsets     element offset of each view into its buffer
+ *  strides     per arg, `space_rank` element strides of the view expressed in
+ *              iteration-space coordinates (0 = broadcast along that dim);
+ *              a NULL entry means "contiguous over the whole space"
+ *  scalars     pointer to each scalar argument's value in HOST memory, read
+ *              at launch (as ScalarView, dali/array/jit/scalar_view.cpp:44)
+ * The call is asynchronous on `stream`; it never allocates caller-visible
+ * memory and never frees caller memory. */
+int dalib200_launch(uint64_t hash, int device, void* stream,
+                    const int64_t* space, int space_rank,
+                    void* const* array_data, const int64_t* offsets,
+                    const int64_t* const* strides, int n_arrays,
+                    const void* const* scalars, int n_scalars);
+
+/* Same computation with HOST arrays: copies every read arg to the device,
+ * launches, copies every written arg back and synchronises.  `extents[i]` is
+ * the number of elements of buffer i.  This is the path a caller holding
+ * host memory pays for (the reference pays it inside
+ * SynchronizedMemory::move_to, dali/array/memory/synchronized_memory.cpp:237-269). */
+int dalib200_launch_host(uint64_t hash, int device,
+                         const int64_t* space, int space_rank,
+                         void* const* host_data, const int64_t* extents,
+                         const int64_t* offsets,
+                         const int64_t* const* strides, int n_arrays,
+                         const void* const* scalars, int n_scalars);
+
+/* Name of the kernel skeleton ("map", "row", "col", "all") and launch
+ * geometry the last dalib200_launch / _precompile on this thread selected;
+ * for tests and profiles. */
+size_t dalib200_last_variant(char* buffer, size_t capacity);
+
+/* ---- device memory ---------------------------------------------------------
+ * Replaces memory::bank::allocate / deposit / clear
+ * (dali/array/memory/memory_bank.cpp:41-81) and memory::copy / clear
+ * (dali/array/memory/memory_ops.cu.cpp:77-131), with 64-bit byte counts.     */
+int dalib200_alloc(int device, size_t bytes, void** out);
+int dalib200_free(int device, void* ptr, size_t bytes);      /* returns the block to the pool */
+int dalib200_pool_clear(int device);                        /* cudaFree everything pooled */
+int dalib200_memcpy_h2d(int device, void* dst, const void* src, size_t bytes, void* stream);
+int dalib200_memcpy_d2h(int device, void* dst, const void* src, size_t bytes, void* stream);
+int dalib200_memcpy_d2d(int device, void* dst, const void* src, size_t bytes, void* stream);
+int dalib200_memset(int device, void* dst, int byte, size_t bytes, void* stream);
+int dalib200_sync(int device, void* stream);                /* stream == (void*)-1: whole device */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DALI_B200_H */

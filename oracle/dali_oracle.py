@@ -1,0 +1,198 @@
+"""TEST INFRASTRUCTURE ONLY: numpy-facing wrapper of oracle/dali_oracle.c.
+
+Imported by tests/, __graft_entry__.smoke() and bench.py's CPU-baseline legs,
+never by the dali_b200 package.  Builds libdali_oracle.so with gcc on first use.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "libdali_oracle.so")
+_lib = None
+
+_DT = {np.dtype(np.float32): 0, np.dtype(np.float64): 1, np.dtype(np.int32): 2}
+_SUF = {0: "f32", 1: "f64", 2: "i32"}
+_KIND = {"sum": 0, "prod": 1, "max": 2, "min": 3}
+
+
+def build():
+    src = os.path.join(_HERE, "dali_oracle.c")
+    if not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-C", _HERE, "libdali_oracle.so"], stdout=subprocess.DEVNULL)
+    return _SO
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = ctypes.CDLL(build())
+    return _lib
+
+
+def _p(a):
+    return ctypes.c_void_p(a.ctypes.data)
+
+
+def _i64(v):
+    return ctypes.c_int64(int(v))
+
+
+def unary(name, x):
+    x = np.ascontiguousarray(x)
+    y = np.empty_like(x)
+    rc = lib().oracle_unary(name.encode(), _DT[x.dtype], _p(x), _p(y), _i64(x.size))
+    if rc != 0:
+        raise KeyError(name)
+    return y
+
+
+def binary(name, a, b):
+    """b may be a 0-d / 1-element array (scalar operand) or have a's shape."""
+    a = np.ascontiguousarray(a)
+    b = np.ascontiguousarray(b, dtype=a.dtype)
+    stride = 0 if b.size == 1 else 1
+    if stride:
+        assert b.shape == a.shape
+    y = np.empty_like(a)
+    rc = lib().oracle_binary(name.encode(), _DT[a.dtype], _p(a), _p(b), _i64(stride), _p(y), _i64(a.size))
+    if rc != 0:
+        raise KeyError(name)
+    return y
+
+
+def round_to_int(x):
+    x = np.ascontiguousarray(x)
+    y = np.empty(x.shape, np.int32)
+    fn = lib().oracle_round_f32_i32 if x.dtype == np.float32 else lib().oracle_round_f64_i32
+    fn(_p(x), _p(y), _i64(x.size))
+    return y
+
+
+def _as_rows(x, axis):
+    """View of x as [rows, cols] (element strides) with `axis` (or all) reduced."""
+    x = np.ascontiguousarray(x)
+    if axis is None:
+        return x, 1, x.size, x.size, 1, ()
+    axis = axis % x.ndim
+    moved = np.ascontiguousarray(np.moveaxis(x, axis, -1))
+    cols = moved.shape[-1]
+    rows = moved.size // cols
+    return moved, rows, cols, cols, 1, moved.shape[:-1]
+
+
+def reduce(kind, x, axis=None):
+    """Sequential left-to-right fold in x's own dtype (the reference's CPU loop)."""
+    m, rows, cols, rs, cs, oshape = _as_rows(x, axis)
+    out = np.empty(rows, m.dtype)
+    fn = getattr(lib(), "oracle_reduce_" + _SUF[_DT[m.dtype]])
+    fn(_KIND[kind], _p(m), _i64(rows), _i64(cols), _i64(rs), _i64(cs), _p(out))
+    return out.reshape(oshape)
+
+
+def argreduce(kind, x, axis=None):
+    m, rows, cols, rs, cs, oshape = _as_rows(x, axis)
+    out = np.empty(rows, np.int32)
+    fn = getattr(lib(), "oracle_argreduce_" + _SUF[_DT[m.dtype]])
+    fn(_KIND[kind], _p(m), _i64(rows), _i64(cols), _i64(rs), _i64(cs), _p(out))
+    return out.reshape(oshape)
+
+
+def sum_f64acc(x, axis=None):
+    """(double-accumulated sum, sum of |x|) of a float32 array along axis."""
+    m, rows, cols, rs, cs, oshape = _as_rows(x.astype(np.float32, copy=False), axis)
+    out = np.empty(rows, np.float64)
+    out_abs = np.empty(rows, np.float64)
+    lib().oracle_sum_f64acc_f32(_p(m), _i64(rows), _i64(cols), _i64(rs), _i64(cs), _p(out), _p(out_abs))
+    return out.reshape(oshape), out_abs.reshape(oshape)
+
+
+def softmax(a):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    cols = a.shape[-1]
+    out = np.empty_like(a)
+    lib().oracle_softmax_f32(_p(a), _i64(a.size // cols), _i64(cols), _p(out))
+    return out
+
+
+def gather(src, idx):
+    src = np.ascontiguousarray(src)
+    idx = np.ascontiguousarray(idx, dtype=np.int32)
+    row_len = int(np.prod(src.shape[1:], dtype=np.int64))
+    out = np.empty(idx.shape + src.shape[1:], src.dtype)
+    lib().oracle_gather(_p(src), _p(idx), _i64(idx.size), _i64(row_len), src.itemsize, _p(out))
+    return out
+
+
+def gather_from_rows(src, idx):
+    src = np.ascontiguousarray(src)
+    idx = np.ascontiguousarray(idx, dtype=np.int32)
+    inner = int(np.prod(src.shape[2:], dtype=np.int64))
+    out = np.empty((src.shape[0],) + src.shape[2:], src.dtype)
+    lib().oracle_gather_from_rows(_p(src), _p(idx), _i64(src.shape[0]), _i64(src.shape[1]), _i64(inner),
+                                  src.itemsize, _p(out))
+    return out
+
+
+def scatter_add(dest, idx, upd):
+    dest = np.array(dest, copy=True, order="C")
+    idx = np.ascontiguousarray(idx, dtype=np.int32)
+    upd = np.ascontiguousarray(np.broadcast_to(upd, idx.shape + dest.shape[1:]), dtype=dest.dtype)
+    row_len = int(np.prod(dest.shape[1:], dtype=np.int64))
+    fn = lib().oracle_scatter_add_f32 if dest.dtype == np.float32 else lib().oracle_scatter_add_i32
+    fn(_p(dest), _p(idx), _p(upd), _i64(idx.size), _i64(row_len))
+    return dest
+
+
+def gemm(a, b):
+    """Row-major a @ b with a double accumulator (float32) or exact (int32)."""
+    if a.dtype == np.int32:
+        a = np.ascontiguousarray(a)
+        b = np.ascontiguousarray(b)
+        c = np.empty((a.shape[0], b.shape[1]), np.int32)
+        lib().oracle_gemm_i32(_p(a), _p(b), _p(c), _i64(a.shape[0]), _i64(b.shape[1]), _i64(a.shape[1]))
+        return c
+    a = np.asarray(a, dtype=np.float32)
+    b = np.asarray(b, dtype=np.float32)
+    c = np.empty((a.shape[0], b.shape[1]), np.float32)
+    es = a.itemsize
+    lib().oracle_gemm_f32(_p(a), _i64(a.strides[0] // es), _i64(a.strides[1] // es), _p(b), _i64(b.strides[0] // es),
+                          _i64(b.strides[1] // es), _p(c), _i64(a.shape[0]), _i64(b.shape[1]), _i64(a.shape[1]))
+    return c
+
+
+def lstm_gating(gates, c):
+    gates = np.ascontiguousarray(gates, dtype=np.float32)
+    c = np.ascontiguousarray(c, dtype=np.float32)
+    B, H = c.shape
+    cn = np.empty_like(c)
+    hn = np.empty_like(c)
+    lib().oracle_lstm_gating_f32(_p(gates), _p(c), _i64(B), _i64(H), _p(cn), _p(hn))
+    return cn, hn
+
+
+def lstm_cell(x, h, c, Wx, Wh, b):
+    gates = gemm(x, Wx) + gemm(h, Wh)          # float32 adds, as the reference's fused add kernel
+    gates = (gates + np.asarray(b, np.float32).reshape(1, -1)).astype(np.float32)
+    return lstm_gating(gates, c)
+
+
+def chain_sum(x, w, b):
+    """(reference-order fp32 sum, double-accumulated sum, sum |y|) of sigmoid(x*w+b)*exp(-x*x)."""
+    x = np.ascontiguousarray(x, dtype=np.float32).ravel()
+    s32 = ctypes.c_float()
+    s64 = ctypes.c_double()
+    sabs = ctypes.c_double()
+    lib().oracle_chain_sum_f32(_p(x), _i64(x.size), ctypes.c_float(w), ctypes.c_float(b), ctypes.byref(s32),
+                               ctypes.byref(s64), ctypes.byref(sabs))
+    return s32.value, s64.value, sabs.value
+
+
+def bias_tanh(x, bias):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    bias = np.ascontiguousarray(bias, dtype=np.float32)
+    out = np.empty_like(x)
+    lib().oracle_bias_tanh_f32(_p(x), _p(bias), _i64(x.shape[0]), _i64(x.shape[1]), _p(out))
+    return out

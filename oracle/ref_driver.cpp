@@ -60,7 +60,14 @@ static Array load(const char* path) {
 }
 
 static void save(const char* path, const Array& a) {
-    Array::save(std::string(path), a);
+    // the reference's npy writer does not take rank-0 arrays: store scalars as shape {1}
+    // (and it crashes on an evaluated node that is not a plain buffer, which is
+    // what op::gather leaves behind: copy those through an identity first)
+    Array out = a;
+    out.eval();
+    if (!out.is_buffer()) { out = op::identity(out); out.eval(); }
+    if (out.ndim() == 0) out = out.reshape({1});
+    Array::save(std::string(path), out);
 }
 
 typedef Array (*unary_fn)(Array);

@@ -1,0 +1,158 @@
+"""Pins the CPU oracle (oracle/dali_oracle.c) against
+  * outputs of the reference's own CPU path, committed as
+    tests/golden/reference_cpu.npz by tests/golden/make_golden.py, and
+  * the known-answer cases of the reference's own test-suite
+    (dali/array/tests/tests.cpp:1120-1361, dot_tests.cpp:10-67).
+CPU only."""
+import numpy as np
+import pytest
+
+import dali_oracle as oracle
+
+# op:: name (dali/array/op/unary.cpp, binary.cpp) -> functor name (dali/array/functor.h)
+FUNCTOR = {"sqrt": "sqrt_f", "eltinv": "inv", "pow": "power", "maximum": "max_scalar", "minimum": "min_scalar",
+           "isnan": "isnotanumber", "isinf": "isinfinity"}
+
+
+def names(golden, prefix):
+    return sorted({k.split("/")[1] for k in golden.files if k.startswith(prefix + "/")})
+
+
+def test_unary_bit_exact(golden):
+    for n in names(golden, "unary"):
+        x, y = golden["unary/%s/x" % n], golden["unary/%s/y" % n]
+        got = oracle.unary(FUNCTOR.get(n, n), x)
+        np.testing.assert_array_equal(got, y, err_msg=n)
+
+
+def test_unary_int_and_double(golden):
+    for pre in ("unary_i32", "unary_f64"):
+        for n in names(golden, pre):
+            x, y = golden["%s/%s/x" % (pre, n)], golden["%s/%s/y" % (pre, n)]
+            got = oracle.unary(FUNCTOR.get(n, n), x)
+            assert got.dtype == y.dtype
+            np.testing.assert_array_equal(got, y, err_msg=pre + n)
+
+
+def test_binary_bit_exact(golden):
+    for n in names(golden, "binary"):
+        a, b, y = (golden["binary/%s/%s" % (n, k)] for k in "aby")
+        got = oracle.binary(FUNCTOR.get(n, n), a, b)
+        np.testing.assert_array_equal(got, y, err_msg=n)
+
+
+@pytest.mark.parametrize("ax", ["-1", "0", "all"])
+def test_float_reductions(golden, ax):
+    x = golden["reduce/x"]
+    axis = None if ax == "all" else int(ax)
+    for opn in ("sum", "prod", "max", "min"):
+        want = golden["reduce/%s/%s" % (opn, ax)]
+        got = oracle.reduce(opn, x, axis)
+        np.testing.assert_array_equal(got.reshape(want.shape), want, err_msg=opn)
+    n = x.size if axis is None else x.shape[axis]
+    mean = oracle.binary("eltdiv", oracle.reduce("sum", x, axis), np.float32(n))
+    np.testing.assert_array_equal(mean.reshape(-1), golden["reduce/mean/%s" % ax].reshape(-1))
+    l2 = oracle.unary("sqrt_f", oracle.reduce("sum", oracle.unary("square", x), axis))
+    np.testing.assert_array_equal(l2.reshape(-1), golden["reduce/l2/%s" % ax].reshape(-1))
+    # double-accumulated sum is within 1e-5 * sum|x| of the reference's own fp32 fold
+    s64, sabs = oracle.sum_f64acc(x, axis)
+    assert np.all(np.abs(s64.reshape(-1) - golden["reduce/sum/%s" % ax].reshape(-1)) <= 1e-5 * sabs.reshape(-1))
+
+
+@pytest.mark.parametrize("ax", ["-1", "0"])
+def test_float_axis_argreduce(golden, ax):
+    x = golden["reduce/x"]
+    for opn, kind in (("argmax", "max"), ("argmin", "min")):
+        want = golden["reduce/%s/%s" % (opn, ax)]
+        assert want.dtype == np.int32
+        np.testing.assert_array_equal(oracle.argreduce(kind, x, int(ax)), want)
+
+
+def test_all_axis_argreduce_reference_returns_float(golden):
+    """The reference types the all-axis argmax of a float array as float
+    (dali/array/op/reducer_operation.cpp:681-684); the value still is the first
+    occurrence.  The oracle (and the library) return it as int32."""
+    x = golden["reduce/x"]
+    for opn, kind in (("argmax", "max"), ("argmin", "min")):
+        want = golden["reduce/%s/all" % opn]
+        assert want.dtype == np.float32
+        got = oracle.argreduce(kind, x, None)
+        assert got.dtype == np.int32
+        assert int(got) == int(want.reshape(-1)[0])
+
+
+@pytest.mark.parametrize("ax", ["-1", "0", "1", "all"])
+def test_int_reductions(golden, ax):
+    x = golden["reduce_i32/x"]
+    axis = None if ax == "all" else int(ax)
+    for opn in ("sum", "max", "min"):
+        np.testing.assert_array_equal(oracle.reduce(opn, x, axis).reshape(-1),
+                                      golden["reduce_i32/%s/%s" % (opn, ax)].reshape(-1))
+    if ax in ("-1", "0"):
+        x2 = golden["reduce_i32_2d/x"]
+        for opn, kind in (("argmax", "max"), ("argmin", "min")):
+            np.testing.assert_array_equal(oracle.argreduce(kind, x2, axis),
+                                          golden["reduce_i32_2d/%s/%s" % (opn, ax)])
+
+
+def test_softmax(golden):
+    a = golden["softmax/a"]
+    np.testing.assert_array_equal(oracle.softmax(a), golden["softmax/op"])
+    np.testing.assert_array_equal(oracle.softmax(a), golden["softmax/naive"])
+    np.testing.assert_array_equal(oracle.softmax(golden["softmax2/a"]), golden["softmax2/naive"])
+
+
+def test_gather(golden):
+    src, idx = golden["gather/src"], golden["gather/idx"]
+    np.testing.assert_array_equal(oracle.gather(src, idx), golden["gather/out"])
+    np.testing.assert_array_equal(oracle.gather(golden["gather/src2d"], idx), golden["gather/out2d"])
+    np.testing.assert_array_equal(oracle.gather_from_rows(src, golden["gather_rows/idx"]), golden["gather_rows/out"])
+    got = oracle.scatter_add(np.zeros(3, np.int32), golden["scatter/idx"], np.ones(6, np.int32))
+    np.testing.assert_array_equal(got, golden["scatter/out"])
+    np.testing.assert_array_equal(got, [2, 3, 1])          # tests.cpp:1318-1331
+
+
+def test_dot_and_fused_configs(golden):
+    A, B, bias = golden["dot/A"], golden["dot/B"], golden["dot/bias"]
+    # CBLAS is third-party and unpinned: agree to fp32 rounding of a K=20 dot product
+    np.testing.assert_allclose(oracle.gemm(A, B), golden["dot/out"], rtol=1e-5, atol=1e-6)
+    np.testing.assert_array_equal(oracle.bias_tanh(golden["dot/out"], bias), golden["dot/gemm_tanh"])
+    cn, hn = oracle.lstm_cell(*(golden["lstm/" + k] for k in ("x", "h", "c", "Wx", "Wh", "b")))
+    np.testing.assert_allclose(cn, golden["lstm/c_new"], rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(hn, golden["lstm/h_new"], rtol=1e-5, atol=1e-6)
+    s32, s64, sabs = oracle.chain_sum(golden["chain/x"], 0.5, 0.1)
+    assert np.float32(s32) == golden["chain/sum"].reshape(-1)[0]
+    assert abs(s64 - s32) <= 1e-5 * sabs
+
+
+# ---- known answers of the reference's own suite --------------------------------------
+def test_known_answers_reducers():
+    a = np.arange(50, dtype=np.float32).reshape(5, 10)
+    assert int(oracle.reduce("sum", a)) == 50 * 49 // 2                      # tests.cpp:1120-1126
+    assert int(oracle.reduce("prod", np.arange(1, 6, dtype=np.int32))) == 120  # :1128-1132
+    r = np.arange(-100, 42, dtype=np.int32)
+    assert int(oracle.reduce("max", r)) == 41 and int(oracle.reduce("min", r)) == -100   # :1134-1139
+    assert int(oracle.argreduce("max", r)) == 141 and int(oracle.argreduce("min", r)) == 0  # :1141-1146
+    a = np.arange(20, dtype=np.int32).reshape(4, 5)
+    np.testing.assert_array_equal(oracle.argreduce("max", a, 0), np.full(5, 3))   # :1148-1157
+    np.testing.assert_array_equal(oracle.argreduce("max", a, 1), np.full(4, 4))
+    np.testing.assert_array_equal(oracle.argreduce("min", -a, 0), np.full(5, 3))
+    np.testing.assert_array_equal(oracle.argreduce("min", -a, 1), np.full(4, 4))
+    a4 = np.arange(120, dtype=np.int32).reshape(2, 3, 4, 5)
+    assert int(oracle.argreduce("max", a4)) == 119 and int(oracle.argreduce("min", a4)) == 0   # :1159-1164
+    ones = np.ones((2, 3, 4, 5), np.int32)
+    np.testing.assert_array_equal(oracle.reduce("sum", ones, -1), np.full((2, 3, 4), 5))      # :1215-1221
+    np.testing.assert_array_equal(oracle.reduce("sum", ones, 0), np.full((3, 4, 5), 2))       # :1223-1229
+    s = np.arange(50, dtype=np.float32).reshape(5, 10)[:, ::2]                                # :1188-1202
+    assert int(oracle.reduce("sum", np.ascontiguousarray(s))) == sum(k for k in range(50) if (k % 10) % 2 == 0)
+
+
+def test_known_answers_gather_and_dot():
+    src = np.arange(5 * 6 * 7, dtype=np.int32).reshape(5, 6, 7)
+    out = oracle.gather_from_rows(src, np.arange(5, dtype=np.int32))          # tests.cpp:1296-1315
+    np.testing.assert_array_equal(out[1], np.arange(49, 56))
+    np.testing.assert_array_equal(out[4], np.arange(196, 203))
+    a = np.arange(6, dtype=np.int32).reshape(2, 3)
+    b = np.arange(12, dtype=np.int32).reshape(3, 4)
+    np.testing.assert_array_equal(oracle.gemm(a, b), a @ b)                    # dot_tests.cpp:37-67
+    np.testing.assert_array_equal(oracle.gemm(a.astype(np.float32), b.astype(np.float32)), (a @ b).astype(np.float32))
