@@ -1,0 +1,111 @@
+"""Tiny builder for the fused-expression IR text (dali_b200/csrc/ir.h).
+
+Harness-side convenience for tests and benchmarks that drive the C ABI
+directly; the C++ Array / op:: layer emits the same text from expression
+graphs."""
+
+
+class IRBuilder:
+    def __init__(self, rank, nreduce=0):
+        self.rank, self.nreduce = rank, nreduce
+        self.args, self.scalars, self.body = [], [], []
+        self.types = []
+
+    def arg(self, dtype="f32", level="E"):
+        self.args.append((dtype, level))
+        return len(self.args) - 1
+
+    def scalar(self, dtype="f32"):
+        self.scalars.append(dtype)
+        return len(self.scalars) - 1
+
+    def _val(self, dtype, text):
+        k = len(self.types)
+        self.types.append(dtype)
+        self.body.append("v%d %s %s" % (k, dtype, text))
+        return k
+
+    def ld(self, arg):
+        return self._val(self.args[arg][0], "ld %d" % arg)
+
+    def ldx(self, arg, index):
+        return self._val(self.args[arg][0], "ldx %d v%d" % (arg, index))
+
+    def sc(self, j):
+        return self._val(self.scalars[j], "sc %d" % j)
+
+    def const(self, dtype, literal):
+        return self._val(dtype, "const %s" % literal)
+
+    def op(self, name, *vals, dtype=None):
+        return self._val(dtype or self.types[vals[0]], "op %s %s" % (name, " ".join("v%d" % v for v in vals)))
+
+    def cast(self, dtype, v):
+        return self._val(dtype, "cast v%d" % v)
+
+    def red(self, kind, v):
+        return self._val(self.types[v], "red %s v%d" % (kind, v))
+
+    def argred(self, kind, v):
+        return self._val("i32", "argred %s v%d" % (kind, v))
+
+    def st(self, arg, v, op="assign"):
+        self.body.append("st %d %s v%d" % (arg, op, v))
+
+    def stx(self, arg, index, v, op="assign"):
+        self.body.append("stx %d %s v%d v%d" % (arg, op, index, v))
+
+    def text(self):
+        lines = ["dali-ir 1", "space %d %d" % (self.rank, self.nreduce)]
+        lines += ["arg %d %s %s" % (i, d, l) for i, (d, l) in enumerate(self.args)]
+        lines += ["scalar %d %s" % (j, d) for j, d in enumerate(self.scalars)]
+        return "\n".join(lines + self.body + ["end"]) + "\n"
+
+
+# ---- the fused expressions of the benchmark configurations ---------------------------
+def softmax_ir():
+    """exp(a - max(a,{-1},true)) / sum(exped,{-1},true) over [rows, cols]: args (out, a)."""
+    b = IRBuilder(2, 1)
+    out, a = b.arg("f32"), b.arg("f32")
+    x = b.ld(a)
+    m = b.red("max", x)
+    e = b.op("exp", b.op("subtract", x, m))
+    s = b.red("sum", e)
+    b.st(out, b.op("eltdiv", e, s))
+    return b.text()
+
+
+def chain_sum_ir():
+    """sum(sigmoid(x*w+b) * exp(-x*x)) over all elements: args (out scalar, x), scalars (w, b)."""
+    b = IRBuilder(1, 1)
+    out, x = b.arg("f32", "R"), b.arg("f32")
+    w, bb = b.scalar("f32"), b.scalar("f32")
+    v = b.ld(x)
+    sig = b.op("sigmoid", b.op("add", b.op("eltmul", v, b.sc(w)), b.sc(bb)))
+    ex = b.op("exp", b.op("eltmul", b.op("negate", v), v))
+    b.st(out, b.red("sum", b.op("eltmul", sig, ex)))
+    return b.text()
+
+
+def reduce_ir(kind, dtype="f32", rank=2, nreduce=1, arg=False):
+    """out = reduce(x) over the innermost `nreduce` dims: args (out, x)."""
+    b = IRBuilder(rank, nreduce)
+    out, x = b.arg("i32" if arg else dtype, "R"), b.arg(dtype)
+    v = b.ld(x)
+    b.st(out, b.argred(kind, v) if arg else b.red(kind, v))
+    return b.text()
+
+
+def lstm_gating_ir():
+    """c' = sigmoid(f)*c + sigmoid(i)*tanh(g); h' = sigmoid(o)*tanh(c') over [B, H]:
+    args (c_new, h_new, i, f, o, g, c) -- the four gate operands are column slices
+    of one [B, 4H] buffer."""
+    b = IRBuilder(2, 0)
+    cn, hn = b.arg("f32"), b.arg("f32")
+    gi, gf, go, gg, c = (b.arg("f32") for _ in range(5))
+    i, f, o = (b.op("sigmoid", b.ld(a)) for a in (gi, gf, go))
+    g = b.op("tanh", b.ld(gg))
+    cnew = b.op("add", b.op("eltmul", f, b.ld(c)), b.op("eltmul", i, g))
+    b.st(cn, cnew)
+    b.st(hn, b.op("eltmul", o, b.op("tanh", cnew)))
+    return b.text()

@@ -39,18 +39,24 @@ static double ms(clk::time_point a, clk::time_point b) {
     return std::chrono::duration<double, std::milli>(b - a).count();
 }
 
-// run f once (JIT compile / cache load included), then `reps` more times
+// run f once (JIT compile / cache load included), then `reps` more times;
+// prints the first, the best and every repeat so callers can drop warm-ups
 static void timed(int reps, const std::function<void()>& f) {
     auto t0 = clk::now(); f(); auto t1 = clk::now();
     double best = ms(t0, t1);
     bool any = false;
+    std::string all;
     for (int r = 0; r < reps; ++r) {
         auto a = clk::now(); f(); auto b = clk::now();
         double t = ms(a, b);
         if (!any || t < best) best = t;
         any = true;
+        char buf[64];
+        std::snprintf(buf, sizeof buf, " %.6f", t);
+        all += buf;
     }
     std::printf("TIME_MS first=%.6f best=%.6f reps=%d\n", ms(t0, t1), best, reps);
+    std::printf("TIMES_MS%s\n", all.c_str());
 }
 
 static Array load(const char* path) {
