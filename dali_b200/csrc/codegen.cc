@@ -795,13 +795,24 @@ struct Gen {
         o << "    __threadfence();\n    __syncthreads();\n";
         o << "    if (tid == 0) { const u32 t = atomicInc(counter + blockIdx.x, gridDim.y - 1); is_last = (t == gridDim.y - 1); }\n";
         o << "    __syncthreads();\n    if (!is_last) return;\n    __threadfence();\n";
+        // every thread folds the slices sl = ty, ty + TYI, ... of its outer lanes (independent
+        // loads in flight instead of one serial chain), then the TYI partial folds meet in
+        // shared memory in slice order
+        for (int si : reds) {
+            const Stmt& s = p.stmts[si];
+            o << "    _Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) {\n      " << acc_type(s) << " t_ = "
+              << acc_init(s) << ";\n      if (ov) { _Pragma(\"unroll 4\") for (u32 sl = ty; sl < gridDim.y; sl += TYI) t_ = "
+              << acc_merge(s, "t_", "ld_cg(&part" + std::to_string(si) + "[(i64)sl * Rpad + o0 + j])")
+              << "; }\n      sm" << si << "[ty][tx * VEC + j] = t_;\n    }\n";
+        }
+        o << "    __syncthreads();\n";
         o << "    if (ty == 0) {\n";
         for (int si : reds) {
             const Stmt& s = p.stmts[si];
-            o << "      _Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) {\n        " << acc_type(s) << " t_ = "
-              << acc_init(s) << ";\n        for (u32 sl = 0; sl < gridDim.y; ++sl) t_ = "
-              << acc_merge(s, "t_", "ld_cg(&part" + std::to_string(si) + "[(i64)sl * Rpad + o0 + j])")
-              << ";\n        acc" << si << "[j] = t_;\n      }\n";
+            o << "      _Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) {\n        " << acc_type(s) << " t_ = sm" << si
+              << "[0][tx * VEC + j];\n        for (int k = 1; k < TYI; ++k) t_ = "
+              << acc_merge(s, "t_", "sm" + std::to_string(si) + "[k][tx * VEC + j]") << ";\n        acc" << si
+              << "[j] = t_;\n      }\n";
         }
         o << "    }\n  }\n";
         // finish: row-level values and stores per outer index

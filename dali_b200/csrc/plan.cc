@@ -5,6 +5,7 @@
 // jit_right_fit_ndim, :1227-1251) and what the emitted host code does to size
 // the grid (:716-772), with 64-bit extents.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <sstream>
 
@@ -48,6 +49,12 @@ int pow2_ceil(long long x) {
     int p = 1;
     while (p < x && p < (1 << 30)) p <<= 1;
     return p;
+}
+
+// tuning overrides for experiments: DALI_B200_<NAME>=<int>
+int env_int(const char* name, int fallback) {
+    const char* e = std::getenv(name);
+    return e && *e ? std::atoi(e) : fallback;
 }
 
 int ilog2(int x) {
@@ -152,11 +159,11 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
 
     auto arg_elem = [&](int a) { return p.nreduce == 0 ? true : p.args[a].elem_level; };
     int max_item = 4;
-    int n_elem_args = 0;
+    int n_elem_args = 0;   // element-level args that are read (their rows may be kept in registers)
     for (int a = 0; a < nargs; ++a)
         if (arg_elem(a) && !p.args[a].indirect) {
             max_item = std::max(max_item, dtype_size(p.args[a].dtype));
-            ++n_elem_args;
+            if (p.args[a].read) ++n_elem_args;
         }
 
     // ---------------------------------------------------------------- skeleton choice
@@ -236,15 +243,24 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
         v.T = 0; v.vpt = 0; v.tx = 0; v.ty = 0;
     } else if (v.kind == K_ROW) {
         if (C > 2147483647LL) { *err = "launch: reduced extent too large for the row skeleton"; return false; }
-        const int target = vec > 1 ? 2 : 4;          // vector groups per thread
-        int T = 1;
-        while (T < 1024 && (groups + T - 1) / T > target) T <<= 1;
+        // Threads per row.  A warp per row (no shared memory, no barrier, 8 vector loads in
+        // flight per thread) while the row fits 8 vector groups per lane and there are enough
+        // rows to fill the machine; wider otherwise.
+        // Measured on [4096,1024] softmax: 4 vector groups per lane (T = 64) beats 8 (T = 32) and
+        // 2 (T = 128); single-pass reductions ([8192,8192] sums) run best with 8.
+        const int max_vpt = (p.max_stage <= 1 && !elem_stores) ? 8 : 4;
+        int T = 32;
+        while (T < 1024 && (groups + T - 1) / T > max_vpt) T <<= 1;
+        while (T > 1 && groups <= T / 2) T >>= 1;                       // short rows: sub-warp groups
+        while (T < 1024 && (groups + T - 1) / T > 1 && R * T < (long long)kSMs * 512) T <<= 1;  // few rows
+        T = env_int("DALI_B200_ROW_T", T);
         int vpt = (int)((groups + T - 1) / T);
         int n_cached = n_elem_args + p.n_reductions;  // leaf arrays + value caches (upper bound)
-        bool cached = v.nin == 1 && (long long)vpt * vec * n_cached <= 64;
+        bool cached = v.nin == 1 && (long long)vpt * vec * n_cached <= 96;
         v.T = T;
         v.vpt = cached ? vpt : 0;
-        v.threads = T > 256 ? T : 256;
+        v.threads = T > 128 ? T : 128;
+        v.threads = env_int("DALI_B200_ROW_THREADS", v.threads);
         // few rows: smaller CTAs spread them over more SMs
         while (v.threads > T && v.threads > 64 && R * T / v.threads < 2 * kSMs) v.threads >>= 1;
         if (v.threads < 32) v.threads = 32;
@@ -254,21 +270,21 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
         out.grid_x = (unsigned)std::min<long long>(gx, (long long)kSMs * 32);
         v.unroll = 1; v.tx = 0; v.ty = 0;
     } else if (v.kind == K_ALL) {
-        v.threads = 256;
-        v.unroll = 4;
+        v.threads = env_int("DALI_B200_ALL_THREADS", 256);
+        v.unroll = env_int("DALI_B200_ALL_UNROLL", 4);
         long long chunk = (long long)v.threads * vec * v.unroll;
         long long gx = (C + chunk - 1) / chunk;
-        out.grid_x = (unsigned)std::min<long long>(gx, (long long)kSMs * 8);
+        out.grid_x = (unsigned)std::min<long long>(gx, (long long)kSMs * env_int("DALI_B200_ALL_CTAS_PER_SM", 8));
         out.scratch_bytes = (size_t)out.grid_x * 16 * std::max(1, p.n_reductions);
         out.counters = 1;
         v.T = 0; v.vpt = 0; v.tx = 0; v.ty = 0;
     } else {  // K_COL
-        v.threads = 256;
-        v.tx = 32;
-        v.ty = 8;
-        v.unroll = 4;
+        v.tx = env_int("DALI_B200_COL_TX", 64);
+        v.ty = env_int("DALI_B200_COL_TY", 4);
+        v.threads = v.tx * v.ty;
+        v.unroll = env_int("DALI_B200_COL_UNROLL", 8);
         long long tiles = (R + (long long)v.tx * vec - 1) / ((long long)v.tx * vec);
-        long long S = ((long long)kSMs * 8 + tiles - 1) / tiles;
+        long long S = ((long long)kSMs * env_int("DALI_B200_COL_CTAS_PER_SM", 8) + tiles - 1) / tiles;
         long long maxS = std::max<long long>(1, C / (v.ty * 8));
         S = std::max<long long>(1, std::min<long long>(std::min<long long>(S, maxS), 256));
         long long per = (C + S - 1) / S;

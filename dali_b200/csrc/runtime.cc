@@ -174,8 +174,10 @@ static bool always_recompile_locked() {
 
 static std::string kernel_key(uint64_t hash, const Variant& v) {
     std::ostringstream k;
+    // the device prelude is part of every kernel: its text is part of the key
+    static const uint64_t prelude_hash = fnv1a(kPrelude);
     k << std::hex << hash << "_" << fnv1a(v.key() + "|sm_100a|" + kCodegenVersion + "|abi" +
-                                            std::to_string(DALIB200_ABI_VERSION));
+                                            std::to_string(DALIB200_ABI_VERSION) + "|" + std::to_string(prelude_hash));
     return k.str();
 }
 
