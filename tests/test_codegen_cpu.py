@@ -76,7 +76,7 @@ def variant_of(L, ir, space, n, strides=None, pointers=None, offsets=None):
 
 def test_skeleton_choice_and_nvrtc(L):
     v = variant_of(L, softmax_ir(), (4096, 1024), 2)
-    assert v.startswith("row.") and ".v4." in v and ".T32.p8." in v            # a warp per row, row kept in registers
+    assert v.startswith("row.") and ".v4." in v and ".T64.p4." in v            # two warps per row, row kept in registers
     assert variant_of(L, softmax_ir(), (33, 1001), 2).startswith("row.o1.i1.v1.")
     assert ".p0." in variant_of(L, softmax_ir(), (3, 40000), 2)                # streaming fallback
     assert variant_of(L, softmax_ir(), (300, 7), 2).startswith("row.")
