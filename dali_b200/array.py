@@ -1,0 +1,348 @@
+"""Python face of the C++ Array / op:: front end (include/dali_b200_array.h).
+
+Harness only: every object here is a handle to a C++ `Array`; expressions are
+built, fused, compiled, cached and run inside libdali_b200.so exactly as for a
+C++ caller.  Lets tests and benchmarks be written the way the reference's own
+tests are:
+
+    from dali_b200.array import Array, op
+    a = Array(np_a)
+    s = op.exp(a - op.max(a, [-1], True)) / op.sum(exped, [-1], True)
+    s.numpy()
+"""
+import ctypes
+
+import numpy as np
+
+from .capi import load_library
+
+DTYPE_FLOAT, DTYPE_DOUBLE, DTYPE_INT32 = 0, 1, 2
+_NP2D = {np.dtype(np.float32): 0, np.dtype(np.float64): 1, np.dtype(np.int32): 2}
+_D2NP = {0: np.float32, 1: np.float64, 2: np.int32}
+_H = ctypes.c_void_p
+_lib = None
+
+
+def _c():
+    global _lib
+    if _lib is None:
+        L = load_library()
+        c = L.c
+        c.dali_array_expression_name.restype = ctypes.c_size_t
+        c.dali_lazy_last_ir.restype = ctypes.c_size_t
+        c.dali_lazy_last_variant.restype = ctypes.c_size_t
+        c.dali_array_free.argtypes = [_H]
+        c.dali_array_ndim.argtypes = [_H]
+        c.dali_array_dtype.argtypes = [_H]
+        c.dali_array_is_buffer.argtypes = [_H]
+        c.dali_array_scalar.argtypes = [ctypes.c_double, ctypes.c_int, ctypes.POINTER(_H)]
+        _lib = L
+    return _lib
+
+
+def _check(rc):
+    _c().check(rc)
+
+
+def _shape_arg(shape):
+    return (ctypes.c_int64 * max(len(shape), 1))(*[int(s) for s in shape])
+
+
+class Array:
+    """Handle to a lazy C++ Array."""
+    __array_priority__ = 1000
+
+    def __init__(self, value=None, dtype=None, _handle=None):
+        self._h = None
+        if _handle is not None:
+            self._h = _handle
+            return
+        L = _c()
+        h = _H()
+        if isinstance(value, Array):
+            raise TypeError("copy an Array with op.identity(a)")
+        if np.isscalar(value):
+            if dtype is None:
+                dtype = DTYPE_INT32 if isinstance(value, (int, np.integer)) else DTYPE_DOUBLE if isinstance(value, float) else DTYPE_FLOAT
+            _check(L.c.dali_array_scalar(float(value), int(dtype), ctypes.byref(h)))
+        else:
+            arr = np.ascontiguousarray(value, dtype=_D2NP[dtype] if dtype is not None else None)
+            if arr.dtype not in _NP2D:
+                arr = arr.astype(np.float32 if arr.dtype.kind == "f" else np.int32)
+            _check(L.c.dali_array_from_host(ctypes.c_void_p(arr.ctypes.data), _shape_arg(arr.shape), arr.ndim,
+                                            _NP2D[arr.dtype], ctypes.byref(h)))
+        self._h = h
+
+    def __del__(self):
+        if self._h is not None and _lib is not None:
+            _lib.c.dali_array_free(self._h)
+            self._h = None
+
+    # ---- construction -----------------------------------------------------------------
+    @staticmethod
+    def _new(fn, *args):
+        h = _H()
+        _check(fn(*args, ctypes.byref(h)))
+        return Array(_handle=h)
+
+    @staticmethod
+    def zeros(shape, dtype=DTYPE_FLOAT):
+        return Array._new(_c().c.dali_array_zeros, _shape_arg(shape), len(shape), int(dtype))
+
+    @staticmethod
+    def empty(shape, dtype=DTYPE_FLOAT):
+        return Array._new(_c().c.dali_array_empty, _shape_arg(shape), len(shape), int(dtype))
+
+    @staticmethod
+    def ones(shape, dtype=DTYPE_FLOAT):
+        out = Array.empty(shape, dtype)
+        out.assign(Array(1, dtype))
+        return out
+
+    @staticmethod
+    def from_device(ptr, shape, dtype=DTYPE_FLOAT, gpu=0):
+        """Wraps device memory owned by the caller (e.g. a torch CUDA tensor's data_ptr())."""
+        return Array._new(_c().c.dali_array_from_device, ctypes.c_void_p(int(ptr)), _shape_arg(shape), len(shape),
+                          int(dtype), int(gpu))
+
+    # ---- inspection ---------------------------------------------------------------------
+    @property
+    def ndim(self):
+        return _c().c.dali_array_ndim(self._h)
+
+    @property
+    def dtype(self):
+        return _c().c.dali_array_dtype(self._h)
+
+    @property
+    def shape(self):
+        n = self.ndim
+        s = (ctypes.c_int64 * max(n, 1))()
+        _check(_c().c.dali_array_shape(self._h, s))
+        return tuple(int(s[i]) for i in range(n))
+
+    def is_buffer(self):
+        return bool(_c().c.dali_array_is_buffer(self._h))
+
+    def expression_name(self):
+        buf = ctypes.create_string_buffer(1 << 16)
+        _c().c.dali_array_expression_name(self._h, buf, len(buf))
+        return buf.value.decode()
+
+    # ---- evaluation ---------------------------------------------------------------------
+    def eval(self, wait=True):
+        _check(_c().c.dali_array_eval(self._h, int(wait)))
+        return self
+
+    def numpy(self):
+        out = np.empty(self.shape, _D2NP[self.dtype])
+        _check(_c().c.dali_array_to_host(self._h, ctypes.c_void_p(out.ctypes.data), out.nbytes))
+        return out
+
+    def item(self):
+        v = ctypes.c_double()
+        _check(_c().c.dali_array_item(self._h, ctypes.byref(v)))
+        return v.value
+
+    def __float__(self):
+        return self.item()
+
+    def __int__(self):
+        return int(self.item())
+
+    def device_ptr(self, gpu=0):
+        p = ctypes.c_void_p()
+        _check(_c().c.dali_array_device_ptr(self._h, gpu, ctypes.byref(p)))
+        return p.value
+
+    # ---- views --------------------------------------------------------------------------
+    def pluck_axis(self, axis, idx):
+        c = _c().c
+        if isinstance(idx, slice):
+            n = self.shape[axis]
+            start, stop, step = idx.indices(n)
+            if step < 0:   # python [hi:lo:-s] -> Slice(lo + 1, hi + 1, -s), which walks that range backwards
+                start, stop = stop + 1, start + 1
+            return Array._new(c.dali_array_slice, self._h, axis, start, stop, step)
+        return Array._new(c.dali_array_index, self._h, axis, int(idx))
+
+    def __getitem__(self, key):
+        if isinstance(key, Array):
+            return op.gather(self, key)
+        if not isinstance(key, tuple):
+            key = (key,)
+        out, axis = self, 0
+        for k in key:
+            if k is None:
+                out = out.expand_dims(axis)
+                axis += 1
+            elif isinstance(k, slice):
+                if k != slice(None):
+                    out = out.pluck_axis(axis, k)
+                axis += 1
+            else:
+                out = out.pluck_axis(axis, k)
+        return out
+
+    def expand_dims(self, axis):
+        return Array._new(_c().c.dali_array_expand_dims, self._h, axis)
+
+    def squeeze(self, axis):
+        return Array._new(_c().c.dali_array_squeeze, self._h, axis)
+
+    def transpose(self, axes=None):
+        axes = list(axes or [])
+        arr = (ctypes.c_int * max(len(axes), 1))(*axes)
+        return Array._new(_c().c.dali_array_transpose, self._h, arr, len(axes))
+
+    @property
+    def T(self):
+        return self.transpose()
+
+    def broadcast_to_shape(self, shape):
+        return Array._new(_c().c.dali_array_broadcast_to, self._h, _shape_arg(shape), len(shape))
+
+    def reshape(self, shape):
+        return Array._new(_c().c.dali_array_reshape, self._h, _shape_arg(shape), len(shape))
+
+    def astype(self, dtype):
+        return Array._new(_c().c.dali_array_astype, self._h, int(dtype))
+
+    # ---- assignment -----------------------------------------------------------------------
+    def assign(self, other):
+        return self._inplace(0, other)
+
+    def _inplace(self, code, other):
+        value = _wrap(other)          # keep the temporary alive across the call
+        _check(_c().c.dali_array_assign(self._h, code, value._h))
+        return self
+
+    def __iadd__(self, o): return self._inplace(1, o)
+    def __isub__(self, o): return self._inplace(2, o)
+    def __imul__(self, o): return self._inplace(3, o)
+    def __itruediv__(self, o): return self._inplace(4, o)
+    def __ilshift__(self, o): return self._inplace(5, o)
+
+    # ---- arithmetic ------------------------------------------------------------------------
+    def __add__(self, o): return op.add(self, o)
+    def __radd__(self, o): return op.add(o, self)
+    def __sub__(self, o): return op.subtract(self, o)
+    def __rsub__(self, o): return op.subtract(o, self)
+    def __mul__(self, o): return op.eltmul(self, o)
+    def __rmul__(self, o): return op.eltmul(o, self)
+    def __truediv__(self, o): return op.eltdiv(self, o)
+    def __rtruediv__(self, o): return op.eltdiv(o, self)
+    def __neg__(self): return op._unary("negate", self)
+
+    def sum(self, axes=None, keepdims=False): return op.sum(self, axes, keepdims)
+    def max(self, axes=None, keepdims=False): return op.max(self, axes, keepdims)
+    def min(self, axes=None, keepdims=False): return op.min(self, axes, keepdims)
+    def mean(self, axes=None, keepdims=False): return op.mean(self, axes, keepdims)
+    def exp(self): return op.exp(self)
+    def dot(self, o): return op.dot(self, o)
+    def gather_from_rows(self, idx): return op.gather_from_rows(self, idx)
+
+
+def _wrap(x):
+    if isinstance(x, Array):
+        return x
+    if isinstance(x, (np.floating,)):
+        return Array(float(x), DTYPE_FLOAT if x.dtype == np.float32 else DTYPE_DOUBLE)
+    if np.isscalar(x):
+        return Array(x)
+    return Array(np.asarray(x))
+
+
+class _Op:
+    """namespace op:: of the reference (dali/array/op.h)."""
+
+    def _unary(self, name, a):
+        a = _wrap(a)
+        return Array._new(_c().c.dali_op_unary, name.encode(), a._h)
+
+    def _binary(self, name, a, b):
+        a, b = _wrap(a), _wrap(b)
+        return Array._new(_c().c.dali_op_binary, name.encode(), a._h, b._h)
+
+    def _reduce(self, name, a, axes, keepdims):
+        if axes is None:
+            return Array._new(_c().c.dali_op_reduce, name.encode(), a._h, None, -1, int(keepdims))
+        axes = [int(x) for x in axes]
+        arr = (ctypes.c_int * max(len(axes), 1))(*axes)
+        return Array._new(_c().c.dali_op_reduce, name.encode(), a._h, arr, len(axes), int(keepdims))
+
+    def sum(self, a, axes=None, keepdims=False): return self._reduce("sum", a, axes, keepdims)
+    def prod(self, a, axes=None, keepdims=False): return self._reduce("prod", a, axes, keepdims)
+    def max(self, a, axes=None, keepdims=False): return self._reduce("max", a, axes, keepdims)
+    def min(self, a, axes=None, keepdims=False): return self._reduce("min", a, axes, keepdims)
+    def mean(self, a, axes=None, keepdims=False): return self._reduce("mean", a, axes, keepdims)
+    def L2_norm(self, a, axes=None, keepdims=False): return self._reduce("L2_norm", a, axes, keepdims)
+
+    def argmax(self, a, axis=None):
+        return Array._new(_c().c.dali_op_argreduce, b"argmax", a._h, int(axis or 0), int(axis is None))
+
+    def argmin(self, a, axis=None):
+        return Array._new(_c().c.dali_op_argreduce, b"argmin", a._h, int(axis or 0), int(axis is None))
+
+    def gather(self, source, indices):
+        indices = _wrap(indices)
+        return Array._new(_c().c.dali_op_gather, source._h, indices._h)
+
+    def gather_from_rows(self, source, indices):
+        indices = _wrap(indices)
+        return Array._new(_c().c.dali_op_gather_from_rows, source._h, indices._h)
+
+    def softmax(self, logits, axis=-1):
+        return Array._new(_c().c.dali_op_softmax, logits._h, int(axis))
+
+    def dot(self, a, b):
+        return Array._new(_c().c.dali_op_dot, a._h, b._h)
+
+    def arange(self, start, stop=None, step=1):
+        if stop is None:
+            start, stop = 0, start
+        return Array._new(_c().c.dali_array_arange, int(start), int(stop), int(step))
+
+    def astype(self, a, dtype):
+        return a.astype(dtype)
+
+    def __getattr__(self, name):
+        unary = {"identity", "sqrt", "square", "abs", "sigmoid", "dsigmoid", "tanh", "dtanh", "relu", "relu_backward",
+                 "eltinv", "exp", "log", "log_or_zero", "sign", "softplus", "softplus_backward", "cube", "rsqrt",
+                 "isnan", "isinf", "inverse_tanh", "round", "ceil"}
+        binary = {"add", "subtract", "eltmul", "eltdiv", "equals", "pow", "steep_sigmoid", "steep_sigmoid_backward",
+                  "clipped_relu", "clipped_relu_backward", "prelu", "prelu_backward_weights", "prelu_backward_inputs",
+                  "lessthanequal", "greaterthanequal", "maximum", "minimum", "clip", "binary_cross_entropy",
+                  "binary_cross_entropy_grad", "all_equals"}
+        if name in unary:
+            return lambda a: self._unary(name, a)
+        if name in binary:
+            return lambda a, b: self._binary(name, a, b)
+        raise AttributeError(name)
+
+
+op = _Op()
+
+
+def lazy_stats():
+    """(kernels, gemms, temporaries) launched by this thread's evaluations so far."""
+    s = (ctypes.c_int64 * 3)()
+    _c().c.dali_lazy_stats(s)
+    return {"kernels": int(s[0]), "gemms": int(s[1]), "temporaries": int(s[2])}
+
+
+def set_dry_run(on):
+    """Lower and compile only (no device work, results undefined): inspect fusion without a GPU."""
+    _c().c.dali_lazy_set_dry_run(int(bool(on)))
+
+
+def last_ir():
+    buf = ctypes.create_string_buffer(1 << 16)
+    _c().c.dali_lazy_last_ir(buf, len(buf))
+    return buf.value.decode()
+
+
+def last_variant():
+    buf = ctypes.create_string_buffer(1 << 12)
+    _c().c.dali_lazy_last_variant(buf, len(buf))
+    return buf.value.decode()

@@ -17,7 +17,8 @@ LIB = os.path.join(LIBDIR, "libdali_b200.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
-CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-Wno-sign-compare", "-I" + os.path.join(CUDA_HOME, "include")]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-Wno-sign-compare", "-I" + os.path.join(CUDA_HOME, "include"),
+             "-I" + os.path.join(HERE, "host", "include")]
 
 
 def _embed_prelude():
@@ -55,8 +56,7 @@ def build(force=False, verbose=False):
     _embed_prelude()
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh", ".inc"))]
     headers += [os.path.join(HERE, "..", "include", f) for f in os.listdir(os.path.join(HERE, "..", "include"))]
-    for sub in ("host",):
-        d = os.path.join(CSRC, sub)
+    for d in (os.path.join(CSRC, "host"), os.path.join(HERE, "host", "include", "dali", "array")):
         if os.path.isdir(d):
             headers += [os.path.join(d, f) for f in os.listdir(d) if f.endswith(".h")]
     objs = []

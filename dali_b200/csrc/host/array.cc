@@ -1,0 +1,762 @@
+// class Array: handle to a lazily evaluated expression (reference:
+// dali/array/array.cpp).  View algebra on evaluated buffers follows
+// dali/array/expression/buffer.cpp:113-286; on lazy nodes it composes View
+// index maps instead of inserting reshape nodes.
+#include <algorithm>
+#include <climits>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <sstream>
+
+#include "../../../include/dali_b200.h"
+#include "dali/array/op.h"
+#include "expression.h"
+
+// ------------------------------------------------------------------ dtype helpers
+int size_of_dtype(DType dtype) { return dtype == DTYPE_DOUBLE ? 8 : 4; }
+std::string dtype_to_name(DType dtype) {
+    switch (dtype) {
+        case DTYPE_FLOAT: return "float";
+        case DTYPE_DOUBLE: return "double";
+        case DTYPE_INT32: return "int32";
+    }
+    return "unknown";
+}
+std::ostream& operator<<(std::ostream& os, const DType& d) { return os << dtype_to_name(d); }
+template <> DType template_to_dtype<float>() { return DTYPE_FLOAT; }
+template <> DType template_to_dtype<double>() { return DTYPE_DOUBLE; }
+template <> DType template_to_dtype<int>() { return DTYPE_INT32; }
+
+static std::string shape_str(const std::vector<int>& s) {
+    std::ostringstream o;
+    o << "[";
+    for (size_t i = 0; i < s.size(); ++i) o << (i ? ", " : "") << s[i];
+    o << "]";
+    return o.str();
+}
+
+// ------------------------------------------------------------------ Slice
+Slice Slice::normalize_and_check(const Slice& s, int dim) {
+    DALI_ASSERT(s.step != 0, "slice step cannot be zero");
+    Slice r;
+    r.step = s.step;
+    r.has_start = r.has_end = true;
+    if (s.step > 0) {
+        r.start = s.has_start ? s.start : 0;
+        r.end = s.has_end ? s.end : dim;
+    } else {
+        // a negative step walks [start, end) backwards, as the reference's Slice does
+        r.start = s.has_start ? s.start : 0;
+        r.end = s.has_end ? s.end : dim;
+    }
+    if (r.start < 0) r.start += dim;
+    if (r.end < 0) r.end += dim;
+    DALI_ASSERT(r.start >= 0 && r.start <= dim && r.end >= 0 && r.end <= dim && r.start <= r.end,
+                "slice [" + std::to_string(s.start) + ":" + std::to_string(s.end) + "] out of range for dimension of size " +
+                    std::to_string(dim));
+    return r;
+}
+int Slice::size() const {
+    int span = end - start;
+    int st = step > 0 ? step : -step;
+    return (span + st - 1) / st;
+}
+
+// ------------------------------------------------------------------ Expression helpers
+std::string Expression::full_name() const {
+    std::string s = name();
+    if (!arguments_.empty()) {
+        s += "(";
+        for (size_t i = 0; i < arguments_.size(); ++i) s += (i ? ", " : "") + arguments_[i].full_expression_name();
+        s += ")";
+    }
+    return s;
+}
+
+BufferView::BufferView(std::shared_ptr<memory::SynchronizedMemory> memory, const std::vector<int>& shape, DType dtype,
+                       int64_t offset, const std::vector<int>& strides)
+    : Expression(N_BUFFER, shape, dtype, {}), memory_(memory), offset_(offset), strides_(strides) {
+    DALI_ASSERT(strides.empty() || strides.size() == shape.size(), "strides must be empty or match the shape's rank");
+    for (int s : shape) DALI_ASSERT(s >= 0, "negative dimension in shape " + shape_str(shape));
+    if (contiguous()) strides_.clear();
+}
+
+std::shared_ptr<BufferView> BufferView::create(const std::vector<int>& shape, DType dtype, memory::Device device) {
+    int64_t n = 1;
+    for (int s : shape) {
+        DALI_ASSERT(s >= 0, "negative dimension in shape " + shape_str(shape));
+        n *= s;
+    }
+    auto mem = std::make_shared<memory::SynchronizedMemory>((size_t)n * size_of_dtype(dtype),
+                                                            shape.empty() ? 1 : shape.back(), device);
+    return std::make_shared<BufferView>(mem, shape, dtype, 0, std::vector<int>());
+}
+
+std::vector<int> BufferView::normalized_strides() const {
+    if (!strides_.empty()) return strides_;
+    std::vector<int> st(shape_.size());
+    int64_t s = 1;
+    for (int d = (int)shape_.size() - 1; d >= 0; --d) { st[d] = (int)s; s *= shape_[d]; }
+    return st;
+}
+
+bool BufferView::contiguous() const {
+    if (strides_.empty()) return true;
+    int64_t s = 1;
+    for (int d = (int)shape_.size() - 1; d >= 0; --d) {
+        if (shape_[d] != 1 && strides_[d] != s) return false;
+        s *= shape_[d];
+    }
+    return true;
+}
+
+Reduce::Reduce(const std::string& reducer, const Array& a, int nreduce, bool arg, DType dtype)
+    : Expression(N_REDUCE, std::vector<int>(a.shape().begin(), a.shape().end() - nreduce), dtype, {a}),
+      reducer_(reducer), nreduce_(nreduce), arg_(arg) {}
+
+static std::vector<int> gather_shape(const Array& source, const Array& indices) {
+    std::vector<int> s = indices.shape();
+    s.insert(s.end(), source.shape().begin() + 1, source.shape().end());
+    return s;
+}
+Gather::Gather(const Array& source, const Array& indices)
+    : Expression(N_GATHER, gather_shape(source, indices), source.dtype(), {source, indices}) {}
+
+static std::vector<int> gather_rows_shape(const Array& source, const Array& indices) {
+    std::vector<int> s = indices.shape();
+    s.insert(s.end(), source.shape().begin() + 2, source.shape().end());
+    return s;
+}
+GatherFromRows::GatherFromRows(const Array& source, const Array& indices)
+    : Expression(N_GATHER_ROWS, gather_rows_shape(source, indices), source.dtype(), {source, indices}) {}
+
+MatMul::MatMul(const Array& left, const Array& right)
+    : Expression(N_MATMUL, {left.shape()[0], right.shape()[1]}, left.dtype(), {left, right}) {}
+
+// ------------------------------------------------------------------ construction
+Array::Array() {}
+Array::Array(expression_ptr e) : state_(std::make_shared<ArrayState>(e)) {}
+Array::Array(const std::vector<int>& shape, DType dtype, memory::Device dev)
+    : state_(std::make_shared<ArrayState>(BufferView::create(shape, dtype, dev))) {}
+Array::Array(std::initializer_list<int> shape, DType dtype, memory::Device dev)
+    : Array(std::vector<int>(shape), dtype, dev) {}
+Array::Array(const std::vector<int>& shape, std::shared_ptr<memory::SynchronizedMemory> mem, const int& offset,
+             const std::vector<int>& strides, DType dtype)
+    : state_(std::make_shared<ArrayState>(std::make_shared<BufferView>(mem, shape, dtype, offset, strides))) {}
+Array::Array(const Array& other, bool copy_memory) {
+    if (copy_memory && !other.is_stateless()) {
+        Array fresh(other.shape(), other.dtype(), other.preferred_device());
+        fresh.assign(other);
+        fresh.eval();
+        state_ = fresh.state_;
+    } else {
+        state_ = other.state_;
+    }
+}
+Array::Array(const int& v) : Array(std::make_shared<ScalarValue>((double)v, DTYPE_INT32)) {}
+Array::Array(const double& v) : Array(std::make_shared<ScalarValue>(v, DTYPE_DOUBLE)) {}
+Array::Array(const float& v) : Array(std::make_shared<ScalarValue>((double)v, DTYPE_FLOAT)) {}
+Array::Array(const int& v, DType d) : Array(std::make_shared<ScalarValue>((double)v, d)) {}
+Array::Array(const double& v, DType d) : Array(std::make_shared<ScalarValue>(v, d)) {}
+Array::Array(const float& v, DType d) : Array(std::make_shared<ScalarValue>((double)v, d)) {}
+
+Array Array::zeros(const std::vector<int>& shape, DType dtype, memory::Device dev) {
+    Array out(shape, dtype, dev);
+    as<BufferView>(out)->memory_->clear();   // zero on first touch
+    return out;
+}
+Array Array::zeros_like(const Array& o) { return zeros(o.shape(), o.dtype(), o.preferred_device()); }
+Array Array::empty_like(const Array& o) { return Array(o.shape(), o.dtype(), o.preferred_device()); }
+Array Array::ones(const std::vector<int>& shape, DType dtype, memory::Device dev) {
+    Array out(shape, dtype, dev);
+    out = 1;
+    return out;
+}
+Array Array::ones_like(const Array& o) { return ones(o.shape(), o.dtype(), o.preferred_device()); }
+
+Array Array::adopt_buffer(void* buffer, const std::vector<int>& shape, DType dtype, memory::Device loc,
+                          const std::vector<int>& strides) {
+    int64_t span = 1;   // elements the view can reach
+    if (strides.empty()) {
+        for (int s : shape) span *= s;
+    } else {
+        span = 1;
+        for (size_t d = 0; d < shape.size(); ++d) span += (int64_t)(shape[d] - 1) * std::abs(strides[d]);
+    }
+    auto mem = std::make_shared<memory::SynchronizedMemory>((size_t)span * size_of_dtype(dtype),
+                                                            shape.empty() ? 1 : shape.back(),
+                                                            loc.is_gpu() ? loc : memory::default_preferred_device);
+    mem->adopt_buffer(loc, buffer);
+    return Array(shape, mem, 0, strides, dtype);
+}
+void Array::disown_buffer(memory::Device loc) { memory()->disown_buffer(loc); }
+
+// ------------------------------------------------------------------ state
+expression_ptr Array::expression() const { return state_ ? state_->expression_ : nullptr; }
+void Array::set_expression(expression_ptr e) const {
+    if (!state_) state_ = std::make_shared<ArrayState>(e);
+    else state_->expression_ = e;
+}
+std::string Array::expression_name() const { return is_stateless() ? "" : expression()->name(); }
+std::string Array::full_expression_name() const { return is_stateless() ? "" : expression()->full_name(); }
+bool Array::is_stateless() const { return !state_ || !state_->expression_; }
+bool Array::is_scalar() const { return ndim() == 0; }
+bool Array::is_vector() const { return ndim() == 1; }
+bool Array::is_matrix() const { return ndim() == 2; }
+bool Array::is_buffer() const { return !is_stateless() && expression()->kind_ == N_BUFFER; }
+bool Array::is_assignment() const { return !is_stateless() && expression()->kind_ == N_ASSIGN; }
+bool Array::is_assignable() const {
+    if (is_stateless()) return false;
+    NodeKind k = expression()->kind_;
+    if (k == N_BUFFER || k == N_ASSIGN) return true;
+    if (k == N_GATHER || k == N_GATHER_ROWS) return expression()->arguments_[0].is_assignable();
+    return false;
+}
+
+static void require_state(const Array& a, const char* what) {
+    DALI_ASSERT(!a.is_stateless(), std::string(what) + " called on a stateless Array");
+}
+const std::vector<int>& Array::shape() const { require_state(*this, "shape()"); return expression()->shape_; }
+DType Array::dtype() const { require_state(*this, "dtype()"); return expression()->dtype_; }
+int Array::ndim() const { return is_stateless() ? 0 : expression()->ndim(); }
+int64_t Array::numel() const { return is_stateless() ? 0 : expression()->numel(); }
+int Array::number_of_elements() const {
+    int64_t n = numel();
+    DALI_ASSERT(n <= INT_MAX, "number_of_elements() overflows int; use numel()");
+    return (int)n;
+}
+std::vector<int> Array::subshape() const {
+    if (ndim() == 0) return {};
+    return std::vector<int>(shape().begin() + 1, shape().end());
+}
+
+void Array::eval(bool wait) const {
+    require_state(*this, "eval()");
+    expression_ptr e = expression();
+    if (e->kind_ == N_BUFFER) return;
+    if (e->kind_ == N_ASSIGN) {
+        Assignment* a = static_cast<Assignment*>(e.get());
+        Array dest = a->arguments_[0];
+        lazy::run_assignment(dest, a->operator_t_, a->arguments_[1]);
+        // the node is replaced by its destination: evaluated once, remembered
+        if (dest.is_assignment()) dest.eval(false);
+        if (dest.is_buffer()) set_expression(dest.expression());
+        else {
+            // scatter through a gather: what remains is the (lazy) gather of the updated source
+            set_expression(dest.expression());
+        }
+    } else if (e->kind_ == N_SCALAR) {
+        ScalarValue* s = static_cast<ScalarValue*>(e.get());
+        Array dest(std::vector<int>(), s->dtype_, memory::default_preferred_device);
+        lazy::run_assignment(dest, OPERATOR_T_EQL, *this);
+        set_expression(dest.expression());
+    } else {
+        Array dest(e->shape_, e->dtype_, preferred_device());
+        lazy::run_assignment(dest, OPERATOR_T_EQL, Array(e));
+        set_expression(dest.expression());
+    }
+    if (wait && !lazy::dry_run()) {
+        memory::Device d = preferred_device();
+        if (d.is_gpu()) lazy::check(dalib200_sync(lazy::device_index(d), nullptr), "dalib200_sync");
+    }
+}
+
+std::shared_ptr<memory::SynchronizedMemory> Array::memory() const {
+    require_state(*this, "memory()");
+    if (!is_buffer()) eval();
+    DALI_ASSERT(is_buffer(), "memory(): expression did not evaluate to a buffer");
+    return as<BufferView>(*this)->memory_;
+}
+int Array::offset() const { memory(); return (int)as<BufferView>(*this)->offset_; }
+const std::vector<int>& Array::strides() const { memory(); return as<BufferView>(*this)->strides_; }
+std::vector<int> Array::normalized_strides() const { memory(); return as<BufferView>(*this)->normalized_strides(); }
+bool Array::contiguous_memory() const { memory(); return as<BufferView>(*this)->contiguous(); }
+bool Array::spans_entire_memory() const {
+    memory();
+    BufferView* b = as<BufferView>(*this);
+    return b->contiguous() && b->offset_ == 0 && (size_t)b->numel() * size_of_dtype(b->dtype_) == b->memory_->total_memory;
+}
+bool Array::is_transpose() const {
+    if (!is_buffer() || ndim() <= 1) return ndim() <= 1;
+    BufferView* b = as<BufferView>(*this);
+    if (b->strides_.empty()) return false;
+    std::vector<int> rs(b->shape_.rbegin(), b->shape_.rend());
+    int64_t s = 1;
+    for (int d = 0; d < ndim(); ++d) {   // strides ascending: contiguous in reversed dim order
+        if (b->shape_[d] != 1 && b->strides_[d] != s) return false;
+        s *= b->shape_[d];
+    }
+    return true;
+}
+
+static memory::Device device_of(const expression_ptr& e) {
+    if (!e) return memory::default_preferred_device;
+    if (e->kind_ == N_BUFFER) return static_cast<BufferView*>(e.get())->memory_->preferred_device;
+    for (const Array& a : e->arguments_) {
+        if (a.is_stateless()) continue;
+        if (a.expression()->kind_ == N_SCALAR) continue;
+        return device_of(a.expression());
+    }
+    return memory::default_preferred_device;
+}
+memory::Device Array::preferred_device() const {
+    memory::Device d = device_of(expression());
+    // computing happens on a GPU; the host is only a staging place
+    return d.is_gpu() ? d : (memory::default_preferred_device.is_gpu() ? memory::default_preferred_device : memory::Device::gpu(0));
+}
+void Array::to_device(memory::Device device) const { memory()->to_device(device); }
+
+DType type_promotion(const Array& a, const Array& b) {
+    if (a.dtype() == b.dtype()) return a.dtype();
+    if (a.dtype() == DTYPE_DOUBLE || b.dtype() == DTYPE_DOUBLE) return DTYPE_DOUBLE;
+    return DTYPE_FLOAT;
+}
+memory::Device device_promotion(const Array& a, const Array& b) {
+    memory::Device da = a.preferred_device(), db = b.preferred_device();
+    return da == db ? da : memory::default_preferred_device;
+}
+
+// ------------------------------------------------------------------ views
+// result[i...] = a[off_k + step_k * i_{src_k}] with the given output shape
+static Array make_view(const Array& a, const std::vector<int>& shape, const std::vector<ViewDim>& dims) {
+    require_state(a, "view");
+    DALI_ASSERT((int)dims.size() == a.ndim(), "internal: view map rank mismatch");
+    expression_ptr e = a.expression();
+    if (e->kind_ == N_ASSIGN) { a.eval(); e = a.expression(); }
+    if (e->kind_ == N_BUFFER) {
+        BufferView* b = static_cast<BufferView*>(e.get());
+        std::vector<int> st = b->normalized_strides();
+        int64_t off = b->offset_;
+        std::vector<int> nst(shape.size(), 0);
+        for (size_t k = 0; k < dims.size(); ++k) {
+            off += dims[k].off * st[k];
+            if (dims[k].src >= 0) nst[dims[k].src] += (int)(dims[k].step * st[k]);
+        }
+        // (the constructor drops the strides again when they are the contiguous ones)
+        return Array(std::make_shared<BufferView>(b->memory_, shape, b->dtype_, off, nst));
+    }
+    if (e->kind_ == N_SCALAR) {
+        return a;   // a scalar broadcasts by itself wherever it is used
+    }
+    if (e->kind_ == N_VIEW) {
+        View* v = static_cast<View*>(e.get());
+        std::vector<ViewDim> composed(v->dims_.size());
+        for (size_t k = 0; k < v->dims_.size(); ++k) {
+            const ViewDim& inner = v->dims_[k];        // arg dim k <- v's out dim inner.src
+            if (inner.src < 0) { composed[k] = inner; continue; }
+            const ViewDim& outer = dims[inner.src];    // v's out dim <- new out dim
+            composed[k].off = inner.off + inner.step * outer.off;
+            composed[k].step = inner.step * outer.step;
+            composed[k].src = outer.src;
+            if (outer.src < 0) composed[k].step = 0;
+        }
+        return Array(std::make_shared<View>(v->arguments_[0], shape, composed));
+    }
+    return Array(std::make_shared<View>(a, shape, dims));
+}
+
+static std::vector<ViewDim> identity_map(int n) {
+    std::vector<ViewDim> d(n);
+    for (int k = 0; k < n; ++k) d[k] = ViewDim{k, 0, 1};
+    return d;
+}
+
+Array Array::pluck_axis(int axis, const Slice& slice_unnormalized) const {
+    const int n = ndim();
+    if (axis < 0) axis += n;
+    DALI_ASSERT(axis >= 0 && axis < n, "pluck_axis dimension (" + std::to_string(axis) + ") must be less than the dimensionality of plucked array (" + std::to_string(n) + ").");
+    Slice s = Slice::normalize_and_check(slice_unnormalized, shape()[axis]);
+    std::vector<int> nshape = shape();
+    nshape[axis] = s.size();
+    std::vector<ViewDim> dims = identity_map(n);
+    if (s.step > 0) dims[axis] = ViewDim{axis, s.start, s.step};
+    else dims[axis] = ViewDim{axis, s.end - 1, s.step};
+    return make_view(*this, nshape, dims);
+}
+
+Array Array::pluck_axis(const int& axis_, const int& idx_) const {
+    const int n = ndim();
+    int axis = axis_ < 0 ? axis_ + n : axis_;
+    DALI_ASSERT(axis >= 0 && axis < n, "pluck_axis dimension (" + std::to_string(axis) + ") must be less than the dimensionality of plucked array (" + std::to_string(n) + ").");
+    int idx = idx_ < 0 ? idx_ + shape()[axis] : idx_;
+    DALI_ASSERT(idx >= 0 && idx < shape()[axis], "index " + std::to_string(idx_) + " out of range for dimension " + std::to_string(axis) + " of size " + std::to_string(shape()[axis]));
+    std::vector<int> nshape;
+    std::vector<ViewDim> dims(n);
+    for (int k = 0; k < n; ++k) {
+        if (k == axis) { dims[k] = ViewDim{-1, idx, 0}; continue; }
+        dims[k] = ViewDim{(int)nshape.size(), 0, 1};
+        nshape.push_back(shape()[k]);
+    }
+    return make_view(*this, nshape, dims);
+}
+
+Array Array::operator[](const int& idx) const {
+    DALI_ASSERT(ndim() > 0, "Slicing a scalar array is not allowed.");
+    return pluck_axis(0, idx);
+}
+Array Array::operator[](const Array& indices) const { return op::gather(*this, indices); }
+Array Array::gather_from_rows(const Array& indices) const { return op::gather_from_rows(*this, indices); }
+SlicingInProgress<Array> Array::operator[](const Slice& s) const { return SlicingInProgress<Array>(*this)[s]; }
+SlicingInProgress<Array> Array::operator[](const Broadcast& b) const { return SlicingInProgress<Array>(*this)[b]; }
+
+Array Array::operator()(int idx) const {
+    int64_t n = numel();
+    DALI_ASSERT(idx >= 0 && idx < n, "Index " + std::to_string(idx) + " must be in [0," + std::to_string(n) + "].");
+    std::vector<ViewDim> dims(ndim());
+    int64_t rem = idx;
+    for (int d = ndim() - 1; d >= 0; --d) {
+        dims[d] = ViewDim{-1, rem % shape()[d], 0};
+        rem /= shape()[d];
+    }
+    return make_view(*this, {}, dims);
+}
+
+Array Array::expand_dims(int new_axis) const {
+    const int n = ndim();
+    if (new_axis < 0) new_axis += n + 1;
+    DALI_ASSERT(new_axis >= 0 && new_axis <= n, "expand_dims new_axis argument must be strictly positive and at most the dimensionality of the array (got new_axis = " + std::to_string(new_axis) + ", ndim = " + std::to_string(n) + ").");
+    std::vector<int> nshape = shape();
+    nshape.insert(nshape.begin() + new_axis, 1);
+    std::vector<ViewDim> dims(n);
+    for (int k = 0; k < n; ++k) dims[k] = ViewDim{k < new_axis ? k : k + 1, 0, 1};
+    return make_view(*this, nshape, dims);
+}
+
+Array Array::squeeze(int axis) const {
+    const int n = ndim();
+    if (axis < 0) axis += n;
+    DALI_ASSERT(axis >= 0 && axis < n, "squeeze dimension (" + std::to_string(axis) + ") must be less the dimensionality of compacted tensor (" + std::to_string(n) + ").");
+    DALI_ASSERT(shape()[axis] == 1, "cannot select an axis to squeeze out which has size not equal to one (got axis = " + std::to_string(axis) + ", shape[" + std::to_string(axis) + "] = " + std::to_string(shape()[axis]) + ").");
+    return pluck_axis(axis, 0);
+}
+
+Array Array::broadcast_scalar_to_ndim(const int& target) const {
+    DALI_ASSERT(target >= 0, "broadcast_scalar_to_ndim expected a non-negative integer (got " + std::to_string(target) + ").");
+    if (!is_scalar()) return *this;
+    Array res = *this;
+    for (int i = 0; i < target; ++i) res = res.expand_dims(0);
+    return res;
+}
+
+Array Array::right_fit_ndim(int target) const {
+    Array res = *this;
+    while (res.ndim() < target) res = res.expand_dims(0);
+    return res;
+}
+
+Array Array::dimshuffle(const std::vector<int>& pattern) const {
+    const int n = ndim();
+    DALI_ASSERT((int)pattern.size() == n, "number of dimensions in dimshuffle does not correspond to the dimensionality of the array (got pattern of length " + std::to_string(pattern.size()) + " and ndim = " + std::to_string(n) + ").");
+    std::vector<bool> seen(n, false);
+    std::vector<int> nshape(n);
+    std::vector<ViewDim> dims(n);
+    for (int d = 0; d < n; ++d) {
+        int p = pattern[d] < 0 ? pattern[d] + n : pattern[d];
+        DALI_ASSERT(p >= 0 && p < n && !seen[p], "dimshuffle pattern must be a permutation of the axes (got " + shape_str(pattern) + ").");
+        seen[p] = true;
+        nshape[d] = shape()[p];
+        dims[p] = ViewDim{d, 0, 1};
+    }
+    return make_view(*this, nshape, dims);
+}
+Array Array::transpose() const {
+    std::vector<int> p(ndim());
+    for (int d = 0; d < ndim(); ++d) p[d] = ndim() - 1 - d;
+    return dimshuffle(p);
+}
+Array Array::transpose(const std::vector<int>& axes) const { return dimshuffle(axes); }
+Array Array::swapaxes(int a1, int a2) const {
+    const int n = ndim();
+    if (a1 < 0) a1 += n;
+    if (a2 < 0) a2 += n;
+    DALI_ASSERT(a1 >= 0 && a1 < n && a2 >= 0 && a2 < n, "swapaxes axes must be less than ndim (got " + std::to_string(a1) + ", " + std::to_string(a2) + ", ndim = " + std::to_string(n) + ").");
+    std::vector<int> p(n);
+    for (int d = 0; d < n; ++d) p[d] = d;
+    std::swap(p[a1], p[a2]);
+    return dimshuffle(p);
+}
+
+Array Array::broadcast_to_shape(const std::vector<int>& target) const {
+    const int n = ndim();
+    DALI_ASSERT((int)target.size() == n, "broadcast_to_shape must receive a shape (" + shape_str(target) + ") with the same dimensionality as the array (current shape = " + shape_str(shape()) + ").");
+    std::vector<ViewDim> dims(n);
+    bool changed = false;
+    for (int d = 0; d < n; ++d) {
+        if (shape()[d] == target[d]) { dims[d] = ViewDim{d, 0, 1}; continue; }
+        DALI_ASSERT(shape()[d] == 1, "broadcast_to_shape cannot reshape broadcasted dimension " + std::to_string(d) + " from current size " + std::to_string(shape()[d]) + " to " + std::to_string(target[d]) + " (current shape = " + shape_str(shape()) + ", new shape = " + shape_str(target) + ").");
+        dims[d] = ViewDim{-1, 0, 0};
+        changed = true;
+    }
+    if (!changed) return *this;
+    return make_view(*this, target, dims);
+}
+
+Array Array::reshape(const std::vector<int>& new_shape_) const {
+    std::vector<int> ns = new_shape_;
+    int64_t known = 1;
+    int unknown = -1;
+    for (size_t d = 0; d < ns.size(); ++d) {
+        if (ns[d] < 0) {
+            DALI_ASSERT(unknown < 0, "can only specify one unknown dimension (-1) for reshape.");
+            unknown = (int)d;
+        } else {
+            known *= ns[d];
+        }
+    }
+    if (unknown >= 0) {
+        DALI_ASSERT(known > 0 && numel() % known == 0, "cannot deduce unknown dimension (" + shape_str(ns) + ") for array with " + std::to_string(numel()) + " elements.");
+        ns[unknown] = (int)(numel() / known);
+        known *= ns[unknown];
+    }
+    DALI_ASSERT(known == numel(), "New shape (" + shape_str(ns) + ") must have the same number of elements as previous shape (" + shape_str(shape()) + ")");
+    if (ns == shape()) return *this;
+    Array src = *this;
+    if (!src.is_buffer()) src.eval(false);
+    if (!src.contiguous_memory()) src = src.ascontiguousarray();
+    BufferView* b = as<BufferView>(src);
+    return Array(std::make_shared<BufferView>(b->memory_, ns, b->dtype_, b->offset_, std::vector<int>()));
+}
+Array Array::ravel() const { return reshape({-1}); }
+
+Array Array::ascontiguousarray() const {
+    if (is_buffer() && as<BufferView>(*this)->contiguous()) return *this;
+    Array out(shape(), dtype(), preferred_device());
+    lazy::run_assignment(out, OPERATOR_T_EQL, *this);
+    return out;
+}
+
+void Array::initialize(const std::vector<int>& shape, DType dtype, memory::Device dev) {
+    set_expression(BufferView::create(shape, dtype, dev));
+}
+Array& Array::reset() { state_.reset(); return *this; }
+
+Array Array::astype(DType d) const { return op::astype(*this, d); }
+
+// ------------------------------------------------------------------ member shortcuts
+Array Array::sum() const { return op::sum(*this); }
+Array Array::mean() const { return op::mean(*this); }
+Array Array::min() const { return op::min(*this); }
+Array Array::max() const { return op::max(*this); }
+Array Array::L2_norm() const { return op::L2_norm(*this); }
+Array Array::abs() const { return op::abs(*this); }
+Array Array::exp() const { return op::exp(*this); }
+Array Array::tanh() const { return op::tanh(*this); }
+Array Array::sigmoid() const { return op::sigmoid(*this); }
+Array Array::sum(const std::vector<int>& axes, bool k) const { return op::sum(*this, axes, k); }
+Array Array::mean(const std::vector<int>& axes, bool k) const { return op::mean(*this, axes, k); }
+Array Array::min(const std::vector<int>& axes, bool k) const { return op::min(*this, axes, k); }
+Array Array::max(const std::vector<int>& axes, bool k) const { return op::max(*this, axes, k); }
+Array Array::L2_norm(const std::vector<int>& axes, bool k) const { return op::L2_norm(*this, axes, k); }
+Array Array::argmin(const int& axis) const { return op::argmin(*this, axis); }
+Array Array::argmin() const { return op::argmin(*this); }
+Array Array::argmax(const int& axis) const { return op::argmax(*this, axis); }
+Array Array::argmax() const { return op::argmax(*this); }
+Array Array::dot(const Array& other) const { return op::dot(*this, other); }
+Array Array::operator-() const { return op::elementwise(*this, "negate"); }
+bool Array::any_isnan() const { return (int)Array(op::any_isnan(*this)) != 0; }
+bool Array::any_isinf() const { return (int)Array(op::any_isinf(*this)) != 0; }
+
+// ------------------------------------------------------------------ host access
+template <typename T>
+T Array::scalar_value() const {
+    DALI_ASSERT(numel() == 1, "Scalar cast must only be called on an Array with a single element (got shape = " + shape_str(shape()) + ").");
+    Array src = *this;
+    src.eval();
+    BufferView* b = as<BufferView>(src);
+    const char* base = (const char*)b->memory_->readonly_data(memory::Device::cpu());
+    base += b->offset_ * size_of_dtype(b->dtype_);
+    switch (b->dtype_) {
+        case DTYPE_FLOAT: return (T)(*(const float*)base);
+        case DTYPE_DOUBLE: return (T)(*(const double*)base);
+        case DTYPE_INT32: return (T)(*(const int*)base);
+    }
+    return T();
+}
+Array::operator float() const { return scalar_value<float>(); }
+Array::operator double() const { return scalar_value<double>(); }
+Array::operator int() const { return scalar_value<int>(); }
+
+// ------------------------------------------------------------------ assignment
+Array& Array::assign(const Array& other) {
+    require_state(other, "assign");
+    if (is_stateless()) {
+        Array fresh(other.shape(), other.dtype(), other.preferred_device());
+        state_ = fresh.state_;
+    }
+    Array dest(expression());    // a new handle on what this Array is now
+    set_expression(std::make_shared<Assignment>(dest, OPERATOR_T_EQL, other));
+    return *this;
+}
+void Array::copy_from(const Array& other) { assign(other); eval(false); }
+Array& Array::operator=(const int& v) { return assign(Array(v)); }
+Array& Array::operator=(const float& v) { return assign(Array(v)); }
+Array& Array::operator=(const double& v) { return assign(Array(v)); }
+void Array::clear() {
+    if (is_buffer() && spans_entire_memory()) as<BufferView>(*this)->memory_->clear();
+    else assign(Array(0.0));
+}
+
+static Array& inplace(Array& left, OPERATOR_T op, const Array& right) {
+    DALI_ASSERT(!left.is_stateless(), "in-place operation on a stateless Array");
+    if (op == OPERATOR_T_LSE) {
+        Array r = op::autoreduce_assign(left, right);
+        left.set_expression(r.expression());
+        return left;
+    }
+    if (!left.is_assignable()) {
+        // a lazy value, not a place: fold the operator into the expression
+        // (dali/array/jit/jit.cpp:1052-1078, replace_assign_with_inplace)
+        Array cur(left.expression());
+        Array res;
+        switch (op) {
+            case OPERATOR_T_ADD: res = op::add(cur, right); break;
+            case OPERATOR_T_SUB: res = op::subtract(cur, right); break;
+            case OPERATOR_T_MUL: res = op::eltmul(cur, right); break;
+            case OPERATOR_T_DIV: res = op::eltdiv(cur, right); break;
+            default: res = right;
+        }
+        left.set_expression(res.expression());
+        return left;
+    }
+    Array dest(left.expression());
+    left.set_expression(std::make_shared<Assignment>(dest, op, right));
+    return left;
+}
+#define DALI_DEFINE_INPLACE(SYMBOL, OP)                                                             \
+    Array& operator SYMBOL(Array& left, const Array& right) { return inplace(left, OP, right); }    \
+    void operator SYMBOL(Array&& left, const Array& right) { Array l(left); inplace(l, OP, right); l.eval(false); }
+DALI_DEFINE_INPLACE(+=, OPERATOR_T_ADD)
+DALI_DEFINE_INPLACE(-=, OPERATOR_T_SUB)
+DALI_DEFINE_INPLACE(*=, OPERATOR_T_MUL)
+DALI_DEFINE_INPLACE(/=, OPERATOR_T_DIV)
+DALI_DEFINE_INPLACE(<<=, OPERATOR_T_LSE)
+
+#define DALI_DEFINE_INTERACTION(SYMBOL, FN)                                                         \
+    Array operator SYMBOL(const Array& l, const Array& r) { return op::FN(l, r); }                  \
+    Array operator SYMBOL(const Array& l, double r) { return op::FN(l, Array(r)); }                 \
+    Array operator SYMBOL(const Array& l, float r) { return op::FN(l, Array(r)); }                  \
+    Array operator SYMBOL(const Array& l, int r) { return op::FN(l, Array(r)); }                    \
+    Array operator SYMBOL(double l, const Array& r) { return op::FN(Array(l), r); }                 \
+    Array operator SYMBOL(float l, const Array& r) { return op::FN(Array(l), r); }                  \
+    Array operator SYMBOL(int l, const Array& r) { return op::FN(Array(l), r); }
+DALI_DEFINE_INTERACTION(+, add)
+DALI_DEFINE_INTERACTION(-, subtract)
+DALI_DEFINE_INTERACTION(*, eltmul)
+DALI_DEFINE_INTERACTION(/, eltdiv)
+
+// ------------------------------------------------------------------ comparison, printing, IO
+bool Array::equals(const Array& l, const Array& r) {
+    if (l.is_stateless() && r.is_stateless()) return true;
+    if (l.is_stateless() || r.is_stateless()) return false;
+    if (l.shape() != r.shape()) return false;
+    return (int)Array(op::all_equals(l, r)) != 0;
+}
+bool Array::allclose(const Array& l, const Array& r, const double& atol) {
+    if (l.is_stateless() && r.is_stateless()) return true;
+    if (l.is_stateless() || r.is_stateless()) return false;
+    if (l.shape() != r.shape()) return false;
+    return (int)Array(op::all_close(l, r, Array(atol))) != 0;
+}
+bool operator==(const Array& l, const Array& r) { return Array::equals(l, r); }
+
+void Array::print(std::basic_ostream<char>& stream, const int& indent, const bool& add_newlines, const bool& print_comma) const {
+    Array c = ascontiguousarray();
+    c.eval();
+    BufferView* b = as<BufferView>(c);
+    const char* base = (const char*)b->memory_->readonly_data(memory::Device::cpu()) + b->offset_ * size_of_dtype(b->dtype_);
+    auto at = [&](int64_t i) -> double {
+        switch (b->dtype_) {
+            case DTYPE_FLOAT: return ((const float*)base)[i];
+            case DTYPE_DOUBLE: return ((const double*)base)[i];
+            default: return ((const int*)base)[i];
+        }
+    };
+    std::string pad(indent, ' ');
+    if (ndim() == 0) {
+        stream << pad << at(0);
+    } else if (ndim() == 1) {
+        stream << pad << "[";
+        for (int i = 0; i < shape()[0]; ++i) stream << (i ? " " : "") << at(i);
+        stream << "]";
+    } else {
+        stream << pad << "[\n";
+        for (int i = 0; i < shape()[0]; ++i) (*this)[i].print(stream, indent + 4, true, i + 1 < shape()[0]);
+        stream << pad << "]";
+    }
+    if (print_comma) stream << ",";
+    if (add_newlines) stream << "\n";
+}
+
+// minimal .npy (format 1.0) reader / writer for <f4 <f8 <i4
+Array Array::load(const std::string& fname) {
+    std::ifstream f(fname, std::ios::binary);
+    DALI_ASSERT(f.good(), "npy_load: Error! Unable to open file " + fname);
+    char magic[10];
+    f.read(magic, 10);
+    DALI_ASSERT(f.good() && std::memcmp(magic, "\x93NUMPY", 6) == 0, "npy_load: " + fname + " is not a .npy file");
+    size_t hlen = (unsigned char)magic[8] | ((unsigned char)magic[9] << 8);
+    if (magic[6] >= 2) {
+        char extra[2];
+        f.read(extra, 2);
+        hlen |= ((size_t)(unsigned char)extra[0] << 16) | ((size_t)(unsigned char)extra[1] << 24);
+    }
+    std::string header(hlen, ' ');
+    f.read(&header[0], (std::streamsize)hlen);
+    auto find_val = [&](const std::string& key) {
+        size_t p = header.find(key);
+        DALI_ASSERT(p != std::string::npos, "npy_load: malformed header in " + fname);
+        return header.substr(header.find(':', p) + 1);
+    };
+    std::string descr = find_val("'descr'");
+    DType dtype;
+    if (descr.find("f4") != std::string::npos) dtype = DTYPE_FLOAT;
+    else if (descr.find("f8") != std::string::npos) dtype = DTYPE_DOUBLE;
+    else if (descr.find("i4") != std::string::npos) dtype = DTYPE_INT32;
+    else throw std::runtime_error("can only load numpy arrays with dtype float, double or int32 (" + fname + ")");
+    bool fortran = find_val("'fortran_order'").find("True") < 8;
+    std::string shp = find_val("'shape'");
+    shp = shp.substr(shp.find('(') + 1, shp.find(')') - shp.find('(') - 1);
+    std::vector<int> shape;
+    std::istringstream ss(shp);
+    std::string tok;
+    while (std::getline(ss, tok, ',')) {
+        bool digits = false;
+        for (char c : tok) digits = digits || (c >= '0' && c <= '9');
+        if (digits) shape.push_back(std::atoi(tok.c_str()));
+    }
+    int64_t n = 1;
+    for (int s : shape) n *= s;
+    void* buf = std::malloc((size_t)n * size_of_dtype(dtype) + 1);
+    f.read((char*)buf, (std::streamsize)(n * size_of_dtype(dtype)));
+    DALI_ASSERT(f.gcount() == (std::streamsize)(n * size_of_dtype(dtype)), "npy_load: truncated file " + fname);
+    if (fortran) {
+        std::vector<int> rs(shape.rbegin(), shape.rend());
+        return Array::adopt_buffer(buf, rs, dtype).transpose();
+    }
+    return Array::adopt_buffer(buf, shape, dtype);
+}
+
+void Array::save(const std::string& fname, const Array& arr) {
+    Array c = arr.ascontiguousarray();
+    c.eval();
+    BufferView* b = as<BufferView>(c);
+    const char* base = (const char*)b->memory_->readonly_data(memory::Device::cpu()) + b->offset_ * size_of_dtype(b->dtype_);
+    std::string descr = b->dtype_ == DTYPE_FLOAT ? "<f4" : (b->dtype_ == DTYPE_DOUBLE ? "<f8" : "<i4");
+    std::ostringstream h;
+    h << "{'descr': '" << descr << "', 'fortran_order': False, 'shape': (";
+    for (int d = 0; d < c.ndim(); ++d) h << c.shape()[d] << (c.ndim() == 1 || d + 1 < c.ndim() ? "," : "") << (d + 1 < c.ndim() ? " " : "");
+    h << "), }";
+    std::string header = h.str();
+    while ((10 + header.size() + 1) % 64 != 0) header += ' ';
+    header += '\n';
+    std::ofstream f(fname, std::ios::binary);
+    DALI_ASSERT(f.good(), "cannot open " + fname + " for writing");
+    f.write("\x93NUMPY\x01\x00", 8);
+    unsigned short len = (unsigned short)header.size();
+    f.write((const char*)&len, 2);
+    f.write(header.data(), (std::streamsize)header.size());
+    f.write(base, (std::streamsize)(c.numel() * size_of_dtype(b->dtype_)));
+}

@@ -1,0 +1,561 @@
+// Lowering of lazy expression trees to fused kernels.
+//
+// Stands where canonical() + jit_merge + JITRunnerImpl::run stand in the
+// reference (dali/array/expression/optimization.cpp:151-158,
+// dali/array/jit/jit.cpp:1080-1142 and :1144-1225): it decides what fuses into
+// one kernel, numbers the distinct buffers and scalars in first-visit order,
+// derives the structural key, compiles on first use and launches.  Differences
+// by design:
+//   * a whole assignment -- elementwise work, broadcasts, reductions over the
+//     trailing dims and the elementwise work after them -- becomes ONE
+//     fused-expression IR program (dali_b200/csrc/ir.h); the reference splits
+//     the same tree into one loop nest per reduction / broadcast with a
+//     temporary between them (dali/array/jit/reshape.cpp:100-102);
+//   * views of lazy nodes are affine index maps that fold into leaf strides;
+//   * temporaries appear only where a subtree cannot share the root's
+//     iteration space (a reduction over other dims, a MatMul, a gather from a
+//     lazy source): that subtree is evaluated first, by the same machinery.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <map>
+#include <sstream>
+
+#include "../../../include/dali_b200.h"
+#include "../runtime.h"
+#include "dali/array/op.h"
+#include "expression.h"
+
+namespace lazy {
+
+static thread_local Stats tl_stats;
+static thread_local bool tl_dry_run = false;
+Stats& stats() { return tl_stats; }
+void set_dry_run(bool on) { tl_dry_run = on; }
+bool dry_run() { return tl_dry_run; }
+
+void check(int status, const char* what) {
+    if (status == DALIB200_OK) return;
+    char buf[8192];
+    dalib200_last_error(buf, sizeof buf);
+    throw std::runtime_error(std::string(what) + " failed (status " + std::to_string(status) + "): " + buf);
+}
+
+void ensure_backend() {
+    static bool ready = false;
+    if (ready) return;
+    check(dalib200_init(0), "dalib200_init");
+    ready = true;
+}
+
+int device_index(const memory::Device& d) {
+    DALI_ASSERT(d.is_gpu(), "computation needs a GPU device (there is no CPU compute path)");
+    ensure_backend();
+    DALI_ASSERT(d.number() >= 0 && d.number() < dalib200_device_count(), "GPU " + std::to_string(d.number()) + " is not available");
+    return d.number();
+}
+
+namespace {
+
+const char* ir_dtype(DType d) { return d == DTYPE_FLOAT ? "f32" : (d == DTYPE_DOUBLE ? "f64" : "i32"); }
+const char* ir_assign(OPERATOR_T op) {
+    switch (op) {
+        case OPERATOR_T_ADD: return "add";
+        case OPERATOR_T_SUB: return "sub";
+        case OPERATOR_T_MUL: return "mul";
+        case OPERATOR_T_DIV: return "div";
+        default: return "assign";
+    }
+}
+
+// node dim j = off + mult * space[src]   (src = -1: the constant `off`)
+struct DimMap { int src; int64_t mult; int64_t off; };
+typedef std::vector<DimMap> IndexMap;
+
+IndexMap identity_map(int n) {
+    IndexMap m(n);
+    for (int j = 0; j < n; ++j) m[j] = DimMap{j, 1, 0};
+    return m;
+}
+
+std::string map_key(const IndexMap& m) {
+    std::ostringstream o;
+    for (const DimMap& d : m) o << d.src << ":" << d.mult << ":" << d.off << ",";
+    return o.str();
+}
+
+struct Leaf {
+    std::shared_ptr<memory::SynchronizedMemory> memory;
+    DType dtype;
+    int64_t offset;                   // elements
+    std::vector<int64_t> strides;     // `rank` space strides (+ 1 lead stride when indirect)
+    bool elem_level, written, read, indirect;
+};
+
+struct Lowerer {
+    std::vector<int64_t> space;
+    int rank, nreduce, n_outer;
+    memory::Device device;
+    std::vector<std::string> body;
+    std::vector<DType> types;            // per value
+    std::vector<bool> elem;              // per value: varies over the reduced dims?
+    std::vector<Leaf> leaves;
+    std::vector<std::pair<DType, double>> scalars;
+    std::map<std::pair<const Expression*, std::string>, int> memo;
+    std::map<const Expression*, int> scalar_slot;
+    std::vector<Array> keep_alive;
+
+    Lowerer(const std::vector<int64_t>& space_, int nreduce_, memory::Device dev)
+        : space(space_), rank((int)space_.size()), nreduce(nreduce_), n_outer(rank - nreduce_), device(dev) {}
+
+    int new_value(DType t, bool is_elem, const std::string& text) {
+        int id = (int)types.size();
+        types.push_back(t);
+        elem.push_back(is_elem);
+        body.push_back("v" + std::to_string(id) + " " + ir_dtype(t) + " " + text);
+        return id;
+    }
+
+    // leaf strides of a buffer seen through map m
+    int leaf_for(BufferView* b, const IndexMap& m, bool written, bool indirect, int64_t lead_stride, int skip_dims_from,
+                 int skip_count) {
+        std::vector<int> st = b->normalized_strides();
+        Leaf L;
+        L.memory = b->memory_;
+        L.dtype = b->dtype_;
+        L.offset = b->offset_;
+        L.strides.assign(rank, 0);
+        L.indirect = indirect;
+        int mj = 0;
+        for (int k = 0; k < (int)st.size(); ++k) {
+            if (k >= skip_dims_from && k < skip_dims_from + skip_count) continue;   // dim addressed through the index
+            const DimMap& d = m[mj++];
+            L.offset += d.off * st[k];
+            if (d.src >= 0) L.strides[d.src] += d.mult * st[k];
+        }
+        for (int d = 0; d < rank; ++d) if (space[d] == 1) L.strides[d] = 0;
+        L.elem_level = nreduce == 0;
+        for (int d = n_outer; d < rank; ++d) if (L.strides[d] != 0) L.elem_level = true;
+        if (indirect) L.strides.push_back(lead_stride);
+        L.written = written;
+        L.read = !written;
+        for (size_t i = 0; i < leaves.size(); ++i) {
+            Leaf& o = leaves[i];
+            if (o.memory == L.memory && o.dtype == L.dtype && o.offset == L.offset && o.strides == L.strides &&
+                o.indirect == L.indirect && o.elem_level == L.elem_level) {
+                o.written = o.written || written;
+                o.read = o.read || !written;
+                return (int)i;
+            }
+        }
+        leaves.push_back(L);
+        return (int)leaves.size() - 1;
+    }
+
+    Array materialize(const Array& a) {
+        Array t(a.expression());
+        t.eval(false);
+        ++tl_stats.temporaries;
+        // remember the result in the node's own handle too, so a second visit reuses it
+        a.set_expression(t.expression());
+        keep_alive.push_back(t);
+        return t;
+    }
+
+    bool reduce_fits(const Reduce* r, const IndexMap& m) const {
+        if (nreduce == 0 || r->nreduce_ != nreduce) return false;
+        if (r->ndim() != n_outer) return false;
+        for (int j = 0; j < r->ndim(); ++j)
+            if (m[j].src != j || m[j].mult != 1 || m[j].off != 0) return false;
+        const std::vector<int>& as_ = r->arguments_[0].shape();
+        for (int k = 0; k < nreduce; ++k)
+            if (as_[r->ndim() + k] != space[n_outer + k]) return false;
+        for (int j = 0; j < n_outer; ++j)
+            if (as_[j] != space[j]) return false;
+        return true;
+    }
+
+    int visit(const Array& a, const IndexMap& m) {
+        DALI_ASSERT(!a.is_stateless(), "expression refers to a stateless Array");
+        expression_ptr e = a.expression();
+        if (e->kind_ == N_ASSIGN) { a.eval(false); e = a.expression(); }
+        DALI_ASSERT((int)m.size() == e->ndim(), "internal: index map rank mismatch at " + e->name());
+        auto key = std::make_pair((const Expression*)e.get(), map_key(m));
+        auto it = memo.find(key);
+        if (it != memo.end()) return it->second;
+        int id = -1;
+        switch (e->kind_) {
+            case N_BUFFER: {
+                BufferView* b = static_cast<BufferView*>(e.get());
+                int leaf = leaf_for(b, m, false, false, 0, 0, 0);
+                keep_alive.push_back(a);
+                id = new_value(b->dtype_, leaves[leaf].elem_level, "ld " + std::to_string(leaf));
+                break;
+            }
+            case N_SCALAR: {
+                ScalarValue* s = static_cast<ScalarValue*>(e.get());
+                auto sit = scalar_slot.find(s);
+                int slot;
+                if (sit == scalar_slot.end()) {
+                    slot = (int)scalars.size();
+                    scalars.push_back(std::make_pair(s->dtype_, s->value_));
+                    scalar_slot[s] = slot;
+                } else {
+                    slot = sit->second;
+                }
+                id = new_value(s->dtype_, false, "sc " + std::to_string(slot));
+                break;
+            }
+            case N_ELEMENTWISE: {
+                Elementwise* w = static_cast<Elementwise*>(e.get());
+                std::vector<int> in;
+                bool is_elem = false;
+                for (const Array& arg : w->arguments_) {
+                    int v = arg.ndim() == 0 ? visit(arg, IndexMap()) : visit(arg, m);
+                    in.push_back(v);
+                    is_elem = is_elem || elem[v];
+                }
+                if (w->functor_ == "cast") {
+                    id = new_value(w->dtype_, is_elem, "cast v" + std::to_string(in[0]));
+                } else {
+                    // operands are promoted to the node's type, except for the converting functors
+                    bool converts = w->functor_ == "round" || w->functor_ == "ceiling";
+                    std::string text = "op " + w->functor_;
+                    for (int v : in) {
+                        if (!converts && types[v] != w->dtype_) v = new_value(w->dtype_, elem[v], "cast v" + std::to_string(v));
+                        text += " v" + std::to_string(v);
+                    }
+                    id = new_value(w->dtype_, is_elem, text);
+                }
+                break;
+            }
+            case N_VIEW: {
+                View* v = static_cast<View*>(e.get());
+                const Array& arg = v->arguments_[0];
+                IndexMap am(v->dims_.size());
+                for (size_t k = 0; k < v->dims_.size(); ++k) {
+                    const ViewDim& d = v->dims_[k];
+                    if (d.src < 0) { am[k] = DimMap{-1, 0, d.off}; continue; }
+                    const DimMap& o = m[d.src];
+                    am[k] = DimMap{o.src, d.step * o.mult, d.off + d.step * o.off};
+                    if (o.src < 0) am[k].mult = 0;
+                }
+                id = visit(arg, am);
+                break;
+            }
+            case N_REDUCE: {
+                Reduce* r = static_cast<Reduce*>(e.get());
+                if (!reduce_fits(r, m)) {
+                    id = visit(materialize(a), m);
+                    break;
+                }
+                int v = visit(r->arguments_[0], identity_map(rank));
+                if (r->arg_) id = new_value(DTYPE_INT32, false, "argred " + r->reducer_ + " v" + std::to_string(v));
+                else id = new_value(r->dtype_, false, "red " + r->reducer_ + " v" + std::to_string(v));
+                break;
+            }
+            case N_GATHER:
+            case N_GATHER_ROWS: {
+                const bool rows = e->kind_ == N_GATHER_ROWS;
+                Array source = e->arguments_[0];
+                const Array& indices = e->arguments_[1];
+                if (!source.is_buffer()) source = materialize(source);
+                BufferView* sb = as<BufferView>(source);
+                keep_alive.push_back(source);
+                const int ri = indices.ndim();
+                IndexMap im(m.begin(), m.begin() + ri);
+                int vi = visit(indices, im);
+                std::vector<int> sst = sb->normalized_strides();
+                // map for the source dims that are NOT addressed through the index
+                IndexMap sm;
+                if (rows) {
+                    sm.push_back(m[0]);                                     // source dim 0 <- out dim 0
+                    for (int t = 1; t < (int)m.size(); ++t) sm.push_back(m[t]);   // source dims 2.. <- out dims 1..
+                } else {
+                    for (int t = ri; t < (int)m.size(); ++t) sm.push_back(m[t]);  // source dims 1.. <- out dims ri..
+                }
+                int leaf = leaf_for(sb, sm, false, true, sst[rows ? 1 : 0], rows ? 1 : 0, 1);
+                bool is_elem = elem[vi] || leaves[leaf].elem_level;
+                id = new_value(sb->dtype_, is_elem, "ldx " + std::to_string(leaf) + " v" + std::to_string(vi));
+                break;
+            }
+            case N_MATMUL: {
+                id = visit(materialize(a), m);
+                break;
+            }
+            default:
+                throw std::runtime_error("cannot lower expression node " + e->name());
+        }
+        memo[key] = id;
+        return id;
+    }
+
+    std::string ir_text() const {
+        std::ostringstream o;
+        o << "dali-ir 1\nspace " << rank << " " << nreduce << "\n";
+        for (size_t i = 0; i < leaves.size(); ++i)
+            o << "arg " << i << " " << ir_dtype(leaves[i].dtype) << " " << (leaves[i].elem_level || nreduce == 0 ? "E" : "R") << "\n";
+        for (size_t j = 0; j < scalars.size(); ++j) o << "scalar " << j << " " << ir_dtype(scalars[j].first) << "\n";
+        for (const std::string& line : body) o << line << "\n";
+        o << "end\n";
+        return o.str();
+    }
+
+    void launch() {
+        const std::string text = ir_text();
+        const uint64_t hash = dalib::fnv1a(text);
+        if (!dalib200_is_loaded(hash)) check(dalib200_compile(hash, text.c_str(), text.size()), "dalib200_compile");
+        const int n = (int)leaves.size();
+        if (tl_dry_run) {
+            // lower + compile only: aligned stand-in pointers, nothing touches a device
+            std::vector<void*> fake(n);
+            std::vector<int64_t> offs(n);
+            std::vector<const int64_t*> st(n);
+            for (int i = 0; i < n; ++i) { fake[i] = (void*)(uintptr_t)4096; offs[i] = leaves[i].offset; st[i] = leaves[i].strides.data(); }
+            check(dalib200_precompile(hash, space.data(), rank, fake.data(), offs.data(), st.data(), n, nullptr), "dalib200_precompile");
+            ++tl_stats.kernels;
+            tl_stats.last_ir = text;
+            char vbuf[512];
+            dalib200_last_variant(vbuf, sizeof vbuf);
+            tl_stats.last_variant = vbuf;
+            return;
+        }
+        const int dev = device_index(device);
+        std::vector<void*> ptrs(n);
+        std::vector<int64_t> offsets(n);
+        std::vector<const int64_t*> strides(n);
+        // readers first, writers last, so the freshness flags end up describing the result
+        for (int pass = 0; pass < 2; ++pass)
+            for (int i = 0; i < n; ++i) {
+                if ((pass == 1) != leaves[i].written) continue;
+                ptrs[i] = leaves[i].memory->data(device, leaves[i].written ? memory::AM_MUTABLE : memory::AM_READONLY);
+                offsets[i] = leaves[i].offset;
+                strides[i] = leaves[i].strides.data();
+            }
+        std::vector<double> sd(scalars.size());
+        std::vector<float> sf(scalars.size());
+        std::vector<int> si(scalars.size());
+        std::vector<const void*> sp(scalars.size());
+        for (size_t j = 0; j < scalars.size(); ++j) {
+            sd[j] = scalars[j].second;
+            sf[j] = (float)scalars[j].second;
+            si[j] = (int)scalars[j].second;
+            sp[j] = scalars[j].first == DTYPE_DOUBLE ? (const void*)&sd[j]
+                                                    : (scalars[j].first == DTYPE_FLOAT ? (const void*)&sf[j] : (const void*)&si[j]);
+        }
+        check(dalib200_launch(hash, dev, nullptr, space.data(), rank, ptrs.data(), offsets.data(), strides.data(), n,
+                              sp.data(), (int)sp.size()),
+              "dalib200_launch");
+        ++tl_stats.kernels;
+        tl_stats.last_ir = text;
+        char buf[512];
+        dalib200_last_variant(buf, sizeof buf);
+        tl_stats.last_variant = buf;
+    }
+};
+
+// first reduction reachable from `a` through elementwise nodes and views
+struct FoundReduce { const Reduce* node = nullptr; bool through_view = false; };
+void find_reduce(const Array& a, bool through_view, FoundReduce* out) {
+    if (out->node || a.is_stateless()) return;
+    Expression* e = a.expression().get();
+    switch (e->kind_) {
+        case N_REDUCE:
+            out->node = static_cast<Reduce*>(e);
+            out->through_view = through_view;
+            return;
+        case N_ELEMENTWISE:
+            for (const Array& arg : e->arguments_) find_reduce(arg, through_view, out);
+            return;
+        case N_VIEW:
+            find_reduce(e->arguments_[0], true, out);
+            return;
+        default:
+            return;
+    }
+}
+
+// dest (op)= left . right through the GEMM entry point of the C ABI (reference:
+// CublasGemmImpl::run, dali/array/gemm/cublas_gemm.cu:112-185, which ignores the
+// operator and always overwrites; here += and -= accumulate as
+// MatMul::supports_operator advertises, dali/array/op/dot.cpp:41-45).
+void run_matmul(const Array& dest, OPERATOR_T op, MatMul* mm) {
+    Array left = mm->arguments_[0], right = mm->arguments_[1];
+    if (!left.is_buffer()) left.eval(false);
+    if (!right.is_buffer()) right.eval(false);
+    if (op == OPERATOR_T_MUL || op == OPERATOR_T_DIV) {
+        Array tmp(dest.shape(), dest.dtype(), dest.preferred_device());
+        run_matmul(tmp, OPERATOR_T_EQL, mm);
+        run_assignment(dest, op, tmp);
+        return;
+    }
+    DALI_ASSERT(dest.dtype() == left.dtype() && dest.dtype() == right.dtype(), "matmul operands and destination must share a dtype");
+    BufferView* a = as<BufferView>(left);
+    BufferView* b = as<BufferView>(right);
+    BufferView* c = as<BufferView>(dest);
+    const int64_t m = a->shape_[0], k = a->shape_[1], n = b->shape_[1];
+    DALI_ASSERT(c->shape_.size() == 2 && c->shape_[0] == m && c->shape_[1] == n, "matmul destination has the wrong shape");
+    if (m == 0 || n == 0) return;
+    if (tl_dry_run) { ++tl_stats.gemms; return; }
+    memory::Device device = dest.preferred_device();
+    const int dev = device_index(device);
+    std::vector<int> as_ = a->normalized_strides(), bs = b->normalized_strides(), cs = c->normalized_strides();
+    const int item = size_of_dtype(dest.dtype());
+    const char* pa = (const char*)a->memory_->data(device, memory::AM_READONLY) + a->offset_ * item;
+    const char* pb = (const char*)b->memory_->data(device, memory::AM_READONLY) + b->offset_ * item;
+    char* pc = (char*)c->memory_->data(device, memory::AM_MUTABLE) + c->offset_ * item;
+    double alpha = op == OPERATOR_T_SUB ? -1.0 : 1.0;
+    double beta = op == OPERATOR_T_EQL ? 0.0 : 1.0;
+    check(dalib200_gemm(dev, nullptr, (int)dest.dtype(), m, n, k, pa, as_[0], as_[1], pb, bs[0], bs[1], pc, cs[0], cs[1],
+                        alpha, beta),
+          "dalib200_gemm");
+    ++tl_stats.gemms;
+}
+
+}  // namespace
+
+void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) {
+    DALI_ASSERT(!dest_in.is_stateless() && !value_in.is_stateless(), "assignment with a stateless Array");
+    DALI_ASSERT(op != OPERATOR_T_LSE, "internal: <<= must be rewritten before it runs");
+    Array dest = dest_in;
+    Array value = value_in;
+    if (dest.is_assignment()) dest.eval(false);
+    if (value.is_assignment()) value.eval(false);
+
+    // ---- peel pure re-indexing views off the root: dest = view(x)  ->  inverse_view(dest) = x
+    while (value.expression()->kind_ == N_VIEW && dest.is_buffer()) {
+        View* v = static_cast<View*>(value.expression().get());
+        bool pure = true;
+        std::vector<int> used(v->ndim(), -1);
+        for (size_t k = 0; k < v->dims_.size(); ++k) {
+            const ViewDim& d = v->dims_[k];
+            if (d.src < 0 || d.off != 0 || d.step != 1 || used[d.src] >= 0) { pure = false; break; }
+            used[d.src] = (int)k;
+        }
+        for (int d = 0; pure && d < v->ndim(); ++d)
+            if (used[d] < 0 && v->shape_[d] != 1) pure = false;
+        if (!pure || dest.shape() != v->shape_) break;
+        // dest'[arg dims] : arg dim k reads dest dim v->dims_[k].src; dims not covered are size 1
+        Array d2 = dest;
+        std::vector<int> perm;   // build through pluck (size-1 dims) + dimshuffle
+        for (int d = v->ndim() - 1; d >= 0; --d)
+            if (used[d] < 0) d2 = d2.pluck_axis(d, 0);
+        // remaining dest dims, in order, correspond to arg dims sorted by src
+        std::vector<std::pair<int, int>> order;   // (src, arg dim)
+        for (size_t k = 0; k < v->dims_.size(); ++k) order.push_back(std::make_pair(v->dims_[k].src, (int)k));
+        std::sort(order.begin(), order.end());
+        std::vector<int> pos_of_arg(v->dims_.size());
+        for (size_t i = 0; i < order.size(); ++i) pos_of_arg[order[i].second] = (int)i;
+        std::vector<int> pattern(v->dims_.size());
+        for (size_t k = 0; k < v->dims_.size(); ++k) pattern[k] = pos_of_arg[k];
+        if (!pattern.empty()) d2 = d2.dimshuffle(pattern);
+        dest = d2;
+        value = v->arguments_[0];
+        if (value.is_assignment()) value.eval(false);
+    }
+
+    // ---- MatMul at the root goes to the GEMM entry point
+    if (value.expression()->kind_ == N_MATMUL && dest.is_buffer()) {
+        run_matmul(dest, op, static_cast<MatMul*>(value.expression().get()));
+        return;
+    }
+
+    // ---- destination: a buffer view, or a gather of one (scatter)
+    const bool scatter = !dest.is_buffer();
+    if (scatter) {
+        DALI_ASSERT(dest.expression()->kind_ == N_GATHER || dest.expression()->kind_ == N_GATHER_ROWS,
+                    "assignment destination must be a buffer or a gather of one (got " + dest.expression_name() + ")");
+        DALI_ASSERT(dest.expression()->arguments_[0].is_assignable(), "cannot scatter into a value that is not stored anywhere");
+    }
+    if (ScalarValue* sv = as<ScalarValue>(value)) {
+        // a host scalar takes the destination's type before it becomes a kernel argument
+        if (sv->dtype_ != dest.dtype()) {
+            double x = sv->value_;
+            if (dest.dtype() == DTYPE_INT32) x = std::floor(x + 0.5);
+            value = Array(std::make_shared<ScalarValue>(x, dest.dtype()));
+        }
+    }
+    if (value.ndim() != 0 && value.shape() != dest.shape()) {
+        DALI_ASSERT(value.ndim() == dest.ndim(), "cannot assign an array of shape rank " + std::to_string(value.ndim()) +
+                                                     " to a destination of rank " + std::to_string(dest.ndim()));
+        value = value.broadcast_to_shape(dest.shape());
+    }
+    if (dest.numel() == 0) return;
+    memory::Device device = dest.preferred_device();
+
+    // ---- iteration space
+    FoundReduce fr;
+    find_reduce(value, false, &fr);
+    std::vector<int64_t> space;
+    int nreduce = 0;
+    bool row_level_root = false;
+    if (fr.node && !fr.through_view && !scatter) {
+        // the root lives at reduction-result level: iterate over the reduction's operand
+        for (int s : fr.node->arguments_[0].shape()) space.push_back(s);
+        nreduce = fr.node->nreduce_;
+        row_level_root = true;
+        if ((int)space.size() - nreduce != dest.ndim()) {   // shapes disagree (should not happen): no fusion
+            space.clear();
+            nreduce = 0;
+            row_level_root = false;
+        }
+    }
+    if (space.empty()) {
+        for (int s : dest.shape()) space.push_back(s);
+        if (fr.node && fr.through_view) {
+            const int k = fr.node->nreduce_;
+            const std::vector<int>& as_ = fr.node->arguments_[0].shape();
+            bool fits = k < (int)space.size() && (int)as_.size() == (int)space.size();
+            for (int d = 0; fits && d < (int)space.size(); ++d) fits = as_[d] == space[d];
+            if (fits) nreduce = k;    // reductions over the trailing dims fuse with the elementwise root
+        }
+        if (space.empty()) space.push_back(1);   // rank-0 destination
+    }
+    const int rank = (int)space.size();
+    const bool rank0_dest = dest.ndim() == 0 && !row_level_root;
+
+    Lowerer L(space, nreduce, device);
+    // ---- value
+    IndexMap root_map = rank0_dest ? IndexMap() : identity_map(row_level_root ? rank - nreduce : (int)dest.shape().size());
+    int v = value.ndim() == 0 ? L.visit(value, IndexMap()) : L.visit(value, root_map);
+    if (L.types[v] != dest.dtype()) {
+        // assignment converts; towards int32 it rounds, as op::astype does
+        if (dest.dtype() == DTYPE_INT32) v = L.new_value(DTYPE_INT32, L.elem[v], "op round v" + std::to_string(v));
+        else v = L.new_value(dest.dtype(), L.elem[v], "cast v" + std::to_string(v));
+    }
+    // ---- store
+    if (!scatter) {
+        BufferView* db = as<BufferView>(dest);
+        int leaf = L.leaf_for(db, root_map, true, false, 0, 0, 0);
+        if (nreduce > 0 && !row_level_root) L.leaves[leaf].elem_level = true;
+        if (op != OPERATOR_T_EQL) L.leaves[leaf].read = true;
+        L.keep_alive.push_back(dest);
+        L.body.push_back("st " + std::to_string(leaf) + " " + ir_assign(op) + " v" + std::to_string(v));
+    } else {
+        Expression* g = dest.expression().get();
+        const bool rows = g->kind_ == N_GATHER_ROWS;
+        Array source = g->arguments_[0];
+        if (!source.is_buffer()) source.eval(false);
+        DALI_ASSERT(source.is_buffer(), "scatter destination must evaluate to a buffer");
+        BufferView* sb = as<BufferView>(source);
+        const Array& indices = g->arguments_[1];
+        const int ri = indices.ndim();
+        IndexMap im(root_map.begin(), root_map.begin() + ri);
+        int vi = L.visit(indices, im);
+        IndexMap sm;
+        if (rows) {
+            sm.push_back(root_map[0]);
+            for (int t = 1; t < (int)root_map.size(); ++t) sm.push_back(root_map[t]);
+        } else {
+            for (int t = ri; t < (int)root_map.size(); ++t) sm.push_back(root_map[t]);
+        }
+        std::vector<int> sst = sb->normalized_strides();
+        int leaf = L.leaf_for(sb, sm, true, true, sst[rows ? 1 : 0], rows ? 1 : 0, 1);
+        L.leaves[leaf].elem_level = true;
+        L.keep_alive.push_back(source);
+        L.body.push_back("stx " + std::to_string(leaf) + " " + ir_assign(op) + " v" + std::to_string(vi) + " v" + std::to_string(v));
+    }
+    L.launch();
+}
+
+}  // namespace lazy

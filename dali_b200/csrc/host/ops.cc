@@ -1,0 +1,374 @@
+// op:: free functions: build lazy expression nodes (reference:
+// dali/array/op/{unary,binary,reducers,reducer_operation,elementwise_operation,
+// gather,gather_from_rows,softmax,dot,arange}.cpp).
+#include <algorithm>
+#include <map>
+#include <sstream>
+
+#include "dali/array/op.h"
+#include "expression.h"
+
+static std::string shape_str(const std::vector<int>& s) {
+    std::ostringstream o;
+    o << "[";
+    for (size_t i = 0; i < s.size(); ++i) o << (i ? ", " : "") << s[i];
+    o << "]";
+    return o.str();
+}
+
+namespace op {
+
+static std::string strip(const std::string& functor_name) {
+    const std::string pre = "functor::";
+    std::string n = functor_name.compare(0, pre.size(), pre) == 0 ? functor_name.substr(pre.size()) : functor_name;
+    if (n == "isnotanumber" || n == "isinfinity") return n;
+    return n;
+}
+
+// ---------------------------------------------------------------- elementwise
+Array elementwise(Array a, const std::string& functor_name) {
+    DALI_ASSERT(!a.is_stateless(), "elementwise operation on a stateless Array");
+    return Array(std::make_shared<Elementwise>(strip(functor_name), std::vector<Array>({a}), a.shape(), a.dtype()));
+}
+
+// common shape of two same-rank operands: every dim equal or one of them 1
+static std::vector<int> common_shape(const Array& a, const Array& b, const std::string& what) {
+    if (a.ndim() == 0) return b.shape();
+    if (b.ndim() == 0) return a.shape();
+    std::vector<int> out(a.ndim());
+    for (int d = 0; d < a.ndim(); ++d) {
+        int x = a.shape()[d], y = b.shape()[d];
+        DALI_ASSERT(x == y || x == 1 || y == 1,
+                    "Arguments to binary operation '" + what + "' must have compatible shapes (got left.shape = " +
+                        shape_str(a.shape()) + ", right.shape = " + shape_str(b.shape()) + ").");
+        out[d] = x == 1 ? y : x;
+    }
+    return out;
+}
+
+std::tuple<Array, Array> ensure_arguments_compatible(Array a, Array b, const std::string& functor_name, bool update_shape) {
+    DALI_ASSERT(!a.is_stateless() && !b.is_stateless(), "binary operation on a stateless Array");
+    if (update_shape) {
+        DALI_ASSERT(a.ndim() == 0 || b.ndim() == 0 || a.ndim() == b.ndim(),
+                    "Arguments to binary operation '" + functor_name + "' must have the same rank (got left.ndim = " +
+                        std::to_string(a.ndim()) + ", left.shape = " + shape_str(a.shape()) + ", and right.ndim = " +
+                        std::to_string(b.ndim()) + ", right.shape = " + shape_str(b.shape()) + ").");
+    }
+    if (a.dtype() != b.dtype()) {
+        DType t = type_promotion(a, b);
+        a = astype(a, t);
+        b = astype(b, t);
+    }
+    if (update_shape && a.shape() != b.shape()) {
+        std::vector<int> cs = common_shape(a, b, functor_name);
+        if (a.ndim() != 0) a = a.broadcast_to_shape(cs);
+        if (b.ndim() != 0) b = b.broadcast_to_shape(cs);
+    }
+    return std::tuple<Array, Array>(a, b);
+}
+
+Array elementwise(Array a, Array b, const std::string& functor_name) {
+    std::tie(a, b) = ensure_arguments_compatible(a, b, functor_name, true);
+    const std::vector<int>& shape = a.ndim() == 0 ? b.shape() : a.shape();
+    return Array(std::make_shared<Elementwise>(strip(functor_name), std::vector<Array>({a, b}), shape, a.dtype()));
+}
+
+Array unsafe_cast(Array a, DType type) {
+    if (a.dtype() == type) return a;
+    if (ScalarValue* s = as<ScalarValue>(a)) {
+        double v = s->value_;
+        if (type == DTYPE_INT32) v = (double)(int)v;
+        return Array(std::make_shared<ScalarValue>(v, type));
+    }
+    return Array(std::make_shared<Elementwise>("cast", std::vector<Array>({a}), a.shape(), type));
+}
+Array round(Array a) {
+    if (a.dtype() == DTYPE_INT32) return a;
+    return Array(std::make_shared<Elementwise>("round", std::vector<Array>({a}), a.shape(), DTYPE_INT32));
+}
+Array ceil(Array a) {
+    if (a.dtype() == DTYPE_INT32) return a;
+    return Array(std::make_shared<Elementwise>("ceiling", std::vector<Array>({a}), a.shape(), DTYPE_INT32));
+}
+Array astype(Array a, DType type) { return type == DTYPE_INT32 ? round(a) : unsafe_cast(a, type); }
+
+Array identity(Array x) { return elementwise(x, "identity"); }
+Array identity(int x) { return Array(x); }
+Array identity(float x) { return Array(x); }
+Array identity(double x) { return Array(x); }
+#define DALI_UNARY(NAME, FUNCTOR) Array NAME(Array x) { return elementwise(x, FUNCTOR); }
+DALI_UNARY(sqrt, "sqrt_f")
+DALI_UNARY(square, "square")
+DALI_UNARY(abs, "abs")
+DALI_UNARY(sigmoid, "sigmoid")
+DALI_UNARY(dsigmoid, "dsigmoid")
+DALI_UNARY(tanh, "tanh")
+DALI_UNARY(dtanh, "dtanh")
+DALI_UNARY(relu, "relu")
+DALI_UNARY(relu_backward, "relu_backward")
+DALI_UNARY(eltinv, "inv")
+DALI_UNARY(exp, "exp")
+DALI_UNARY(log, "log")
+DALI_UNARY(log_or_zero, "log_or_zero")
+DALI_UNARY(sign, "sign")
+DALI_UNARY(softplus, "softplus")
+DALI_UNARY(softplus_backward, "softplus_backward")
+DALI_UNARY(cube, "cube")
+DALI_UNARY(rsqrt, "rsqrt")
+DALI_UNARY(isnan, "isnotanumber")
+DALI_UNARY(isinf, "isinfinity")
+DALI_UNARY(inverse_tanh, "inverse_tanh")
+
+#define DALI_BINARY(NAME, FUNCTOR) Array NAME(Array a, Array b) { return elementwise(a, b, FUNCTOR); }
+DALI_BINARY(add, "add")
+DALI_BINARY(subtract, "subtract")
+DALI_BINARY(eltmul, "eltmul")
+DALI_BINARY(eltdiv, "eltdiv")
+DALI_BINARY(equals, "equals")
+DALI_BINARY(pow, "power")
+DALI_BINARY(steep_sigmoid, "steep_sigmoid")
+DALI_BINARY(steep_sigmoid_backward, "steep_sigmoid_backward")
+DALI_BINARY(clipped_relu, "clipped_relu")
+DALI_BINARY(clipped_relu_backward, "clipped_relu_backward")
+DALI_BINARY(prelu, "prelu")
+DALI_BINARY(prelu_backward_weights, "prelu_backward_weights")
+DALI_BINARY(prelu_backward_inputs, "prelu_backward_inputs")
+DALI_BINARY(lessthanequal, "lessthanequal")
+DALI_BINARY(greaterthanequal, "greaterthanequal")
+DALI_BINARY(maximum, "max_scalar")
+DALI_BINARY(minimum, "min_scalar")
+DALI_BINARY(clip, "clip")
+DALI_BINARY(binary_cross_entropy, "binary_cross_entropy")
+DALI_BINARY(binary_cross_entropy_grad, "binary_cross_entropy_grad")
+
+Array all_equals(Array l, Array r) { return op::prod(op::equals(l, r)); }
+Array close(Array l, Array r, Array atol) { return op::lessthanequal(op::abs(op::subtract(l, r)), atol); }
+Array all_close(Array l, Array r, Array atol) { return op::prod(op::close(l, r, atol)); }
+
+Array add(const std::vector<Array>& arrays, bool) {
+    DALI_ASSERT(!arrays.empty(), "add must have at least one Array to add but got 0.");
+    Array out = arrays[0];
+    for (size_t i = 1; i < arrays.size(); ++i) out = op::add(out, arrays[i]);
+    return out;
+}
+
+Array fill(const Array& x, double value) {
+    return Array(std::make_shared<Elementwise>("fill", std::vector<Array>({x, Array(value, x.dtype())}), x.shape(), x.dtype()));
+}
+
+// ---------------------------------------------------------------- reducers
+static std::string reducer_short(const std::string& name) {
+    const std::string pre = "reducers::";
+    std::string n = name.compare(0, pre.size(), pre) == 0 ? name.substr(pre.size()) : name;
+    if (n == "maximum") return "max";
+    if (n == "minimum") return "min";
+    if (n == "product") return "prod";
+    return n;
+}
+
+Array all_reduce(const Array& a, const std::string& reducer_name) {
+    DALI_ASSERT(!a.is_stateless(), "reduction of a stateless Array");
+    if (a.ndim() == 0) return a;
+    return Array(std::make_shared<Reduce>(reducer_short(reducer_name), a, a.ndim(), false, a.dtype()));
+}
+
+Array axis_reduce(const Array& a, const std::string& reducer_name, const std::vector<int>& axes, bool keepdims) {
+    DALI_ASSERT(!a.is_stateless(), "reduction of a stateless Array");
+    if (axes.empty()) return a;
+    const int ndim = a.ndim();
+    if (ndim == 0) return a;
+    std::vector<int> norm(axes);
+    std::vector<bool> reduced(ndim, false);
+    for (int& axis : norm) {
+        if (axis < 0) axis += ndim;
+        DALI_ASSERT(axis >= 0 && axis < ndim,
+                    "Reduction axis must strictly positive and less than the number of dimensions of the input (got axis=" +
+                        std::to_string(axes[0]) + ", ndim=" + std::to_string(ndim) + ", input.shape = " + shape_str(a.shape()) + ").");
+    }
+    std::sort(norm.begin(), norm.end());
+    for (int axis : norm) {
+        DALI_ASSERT(!reduced[axis], "axis_reduce received duplicate axes to operate on (axis=" + std::to_string(axis) + ").");
+        reduced[axis] = true;
+    }
+    Array res;
+    if ((int)norm.size() == ndim) {
+        res = all_reduce(a, reducer_name);
+    } else {
+        // kept axes first, reduced axes last (a view -- no data moves), then fold the tail
+        std::vector<int> order;
+        for (int d = 0; d < ndim; ++d) if (!reduced[d]) order.push_back(d);
+        for (int d = 0; d < ndim; ++d) if (reduced[d]) order.push_back(d);
+        bool is_identity = true;
+        for (int d = 0; d < ndim; ++d) is_identity = is_identity && order[d] == d;
+        Array moved = is_identity ? a : a.transpose(order);
+        res = Array(std::make_shared<Reduce>(reducer_short(reducer_name), moved, (int)norm.size(), false, a.dtype()));
+    }
+    if (keepdims) for (int axis : norm) res = res.expand_dims(axis);
+    return res;
+}
+
+Array argument_all_reduce(const Array& a, const std::string& reducer_name) {
+    DALI_ASSERT(!a.is_stateless(), "reduction of a stateless Array");
+    if (a.ndim() == 0) return Array(0);
+    // int32, where the reference mistypes the result as the input's dtype
+    // (dali/array/op/reducer_operation.cpp:681-684)
+    return Array(std::make_shared<Reduce>(reducer_short(reducer_name), a, a.ndim(), true, DTYPE_INT32));
+}
+
+Array argument_axis_reduce(const Array& a, const std::string& reducer_name, const int& axis) {
+    const int ndim = a.ndim();
+    if (ndim == 0) return Array(0);
+    int norm = axis < 0 ? axis + ndim : axis;
+    DALI_ASSERT(norm >= 0 && norm < ndim,
+                "Reduction axis must strictly positive and less than the number of dimensions of the input (got axis=" +
+                    std::to_string(norm) + ", ndim=" + std::to_string(ndim) + ").");
+    if (ndim == 1) return argument_all_reduce(a, reducer_name);
+    Array moved = a;
+    if (norm != ndim - 1) {
+        // kept axes stay in order, the searched axis goes last
+        std::vector<int> order;
+        for (int d = 0; d < ndim; ++d) if (d != norm) order.push_back(d);
+        order.push_back(norm);
+        moved = a.transpose(order);
+    }
+    return Array(std::make_shared<Reduce>(reducer_short(reducer_name), moved, 1, true, DTYPE_INT32));
+}
+
+Array sum(const Array& x) { return all_reduce(x, "sum"); }
+Array sum(const Array& x, const std::vector<int>& axes, bool k) { return axis_reduce(x, "sum", axes, k); }
+Array prod(const Array& x) { return all_reduce(x, "prod"); }
+Array prod(const Array& x, const std::vector<int>& axes, bool k) { return axis_reduce(x, "prod", axes, k); }
+Array max(const Array& x) { return all_reduce(x, "max"); }
+Array max(const Array& x, const std::vector<int>& axes, bool k) { return axis_reduce(x, "max", axes, k); }
+Array min(const Array& x) { return all_reduce(x, "min"); }
+Array min(const Array& x, const std::vector<int>& axes, bool k) { return axis_reduce(x, "min", axes, k); }
+Array mean(const Array& x) {
+    Array s = all_reduce(x, "sum");
+    if (s.dtype() == DTYPE_INT32) s = astype(s, DTYPE_DOUBLE);
+    return op::eltdiv(s, Array((int)x.numel()));
+}
+Array mean(const Array& x, const std::vector<int>& axes, bool k) {
+    Array s = axis_reduce(x, "sum", axes, k);
+    if (s.dtype() == DTYPE_INT32) s = astype(s, DTYPE_DOUBLE);
+    return op::eltdiv(s, Array((int)(x.numel() / std::max<int64_t>(1, s.numel()))));
+}
+Array L2_norm(const Array& x) {
+    Array s = all_reduce(op::square(x), "sum");
+    if (s.dtype() == DTYPE_INT32) s = astype(s, DTYPE_DOUBLE);
+    return op::sqrt(s);
+}
+Array L2_norm(const Array& x, const std::vector<int>& axes, bool k) {
+    Array s = axis_reduce(op::square(x), "sum", axes, k);
+    if (s.dtype() == DTYPE_INT32) s = astype(s, DTYPE_DOUBLE);
+    return op::sqrt(s);
+}
+Array argmax(const Array& x) { return argument_all_reduce(x, "max"); }
+Array argmax(const Array& x, const int& axis) { return argument_axis_reduce(x, "max", axis); }
+Array argmin(const Array& x) { return argument_all_reduce(x, "min"); }
+Array argmin(const Array& x, const int& axis) { return argument_axis_reduce(x, "min", axis); }
+Array any_isnan(const Array& a) { return op::max(op::isnan(a)); }
+Array any_isinf(const Array& a) { return op::max(op::isinf(a)); }
+Array any_isnan(const Array& a, const std::vector<int>& axes, bool k) { return op::max(op::isnan(a), axes, k); }
+Array any_isinf(const Array& a, const std::vector<int>& axes, bool k) { return op::max(op::isinf(a), axes, k); }
+
+// ---------------------------------------------------------------- index ops
+Array gather(const Array& source, const Array& indices) {
+    DALI_ASSERT(source.ndim() > 0, "gather must be called on source with ndim >= 1 (got ndim=" + std::to_string(source.ndim()) + ").");
+    DALI_ASSERT(indices.dtype() == DTYPE_INT32, "indices must be integers (got dtype=" + dtype_to_name(indices.dtype()) + ").");
+    return Array(std::make_shared<Gather>(source, indices));
+}
+Array gather_from_rows(const Array& source, const Array& indices) {
+    DALI_ASSERT(source.ndim() > 1, "gather_from_rows must be called on source with ndim >= 2 (got ndim=" + std::to_string(source.ndim()) + ").");
+    DALI_ASSERT(indices.dtype() == DTYPE_INT32, "indices must be integers (got dtype=" + dtype_to_name(indices.dtype()) + ").");
+    DALI_ASSERT(indices.ndim() <= 1, "indices must have rank 1 or lower [Note: support for higher ranks coming soon] (got indices.ndim=" + std::to_string(indices.ndim()) + ").");
+    Array idx = indices;
+    if (idx.ndim() == 0) idx = idx.expand_dims(0).broadcast_to_shape({source.shape()[0]});
+    DALI_ASSERT(idx.shape()[0] <= source.shape()[0], "indices cannot have a larger first dimension than source");
+    Array src = source;
+    if (idx.shape()[0] < source.shape()[0]) src = source.pluck_axis(0, Slice(0, idx.shape()[0]));
+    return Array(std::make_shared<GatherFromRows>(src, idx));
+}
+
+// ---------------------------------------------------------------- compositions
+Array softmax(const Array& logits, int axis) {
+    Array exped = op::exp(logits - op::max(logits, {axis}, true));
+    return exped / op::sum(exped, {axis}, true);
+}
+Array softmax_temperature(const Array& logits, const Array&, int axis) {
+    // the reference ignores its temperature argument (dali/array/op/softmax.cpp:10-13)
+    return softmax(logits, axis);
+}
+
+// ---------------------------------------------------------------- dot
+Array matmul(Array a, Array b) {
+    DALI_ASSERT(a.ndim() == 2 && b.ndim() == 2, "matmul inputs must be matrices (got left.ndim = " + std::to_string(a.ndim()) + ", right.ndim = " + std::to_string(b.ndim()) + ").");
+    DALI_ASSERT(a.shape()[1] == b.shape()[0] || a.shape()[1] == 1 || b.shape()[0] == 1,
+                "shapes " + shape_str(a.shape()) + " and " + shape_str(b.shape()) + " not aligned: " +
+                    std::to_string(a.shape()[1]) + " (dim 1) != " + std::to_string(b.shape()[0]) + " (dim 0)");
+    if (a.shape()[1] != b.shape()[0]) {
+        // a size-1 inner dim broadcasts (dali/array/op/dot.cpp:47-61)
+        if (a.shape()[1] == 1) a = a.broadcast_to_shape({a.shape()[0], b.shape()[0]});
+        else b = b.broadcast_to_shape({a.shape()[1], b.shape()[1]});
+    }
+    if (a.dtype() != b.dtype()) {
+        DType t = type_promotion(a, b);
+        a = astype(a, t);
+        b = astype(b, t);
+    }
+    return Array(std::make_shared<MatMul>(a, b));
+}
+Array matrix_vector_dot(const Array& a, const Array& b) {
+    if (a.ndim() == 1 && b.ndim() == 2) return matmul(a.expand_dims(0), b).squeeze(0);
+    DALI_ASSERT(a.ndim() == 2 && b.ndim() == 1, "matrix_vector_dot takes a matrix and a vector");
+    return matmul(a, b.expand_dims(1)).squeeze(1);
+}
+Array inner(const Array& a, const Array& b) {
+    DALI_ASSERT(a.ndim() == 1 && b.ndim() == 1, "inner takes two vectors");
+    return matmul(a.expand_dims(0), b.expand_dims(1)).squeeze(1).squeeze(0);
+}
+Array dot(const Array& a, const Array& b) {
+    int an = a.ndim(), bn = b.ndim();
+    if (an == 0 || bn == 0) return a * b;
+    if (an == 1 && bn == 1) return inner(a, b);
+    if (an == 2 && bn == 2) return matmul(a, b);
+    if ((an == 1 && bn == 2) || (an == 2 && bn == 1)) return matrix_vector_dot(a, b);
+    throw std::runtime_error("dot of arrays with rank above 2 (tensordot) is not part of this back end");
+}
+
+// ---------------------------------------------------------------- arange
+Array arange(int start, int stop, int step) {
+    DALI_ASSERT(step != 0, "arange's step cannot be zero.");
+    int n = step > 0 ? (stop - start + step - 1) / step : (start - stop - step - 1) / (-step);
+    DALI_ASSERT(n > 0, "arange's start, stop and step values lead to an empty array.");
+    int* buf = (int*)std::malloc(sizeof(int) * (size_t)n);
+    for (int i = 0; i < n; ++i) buf[i] = start + i * step;
+    return Array::adopt_buffer(buf, {n}, DTYPE_INT32);
+}
+Array arange(int start, int stop) { return arange(start, stop, 1); }
+Array arange(int stop) { return arange(0, stop, 1); }
+
+// ---------------------------------------------------------------- assignment
+Array assign(const Array& left, OPERATOR_T op, const Array& right) {
+    if (op == OPERATOR_T_LSE) return autoreduce_assign(left, right);
+    return Array(std::make_shared<Assignment>(left, op, right));
+}
+Array autoreduce_assign(const Array& left, const Array& right) {
+    DALI_ASSERT(left.ndim() == right.ndim(),
+                "destination for autoreduce_assign must have the same dimensionality as the input (destination.ndim = " +
+                    std::to_string(left.ndim()) + " vs input.ndim = " + std::to_string(right.ndim()));
+    std::vector<int> axes;
+    for (int d = 0; d < right.ndim(); ++d) {
+        if (left.shape()[d] != right.shape()[d]) {
+            DALI_ASSERT(left.shape()[d] == 1, "Could not autoreduce_assign: destination must have all dimensions equal input dimensions or equal 1, but destination.shape[" + std::to_string(d) + "] = " + std::to_string(left.shape()[d]) + " vs input.shape[" + std::to_string(d) + "] = " + std::to_string(right.shape()[d]));
+            axes.push_back(d);
+        }
+    }
+    Array r = axes.empty() ? right : op::sum(right, axes, true);
+    return Array(std::make_shared<Assignment>(Array(left.expression()), OPERATOR_T_ADD, r));
+}
+Array to_assignment(const Array& node) {
+    return Array(std::make_shared<Assignment>(Array(node.shape(), node.dtype(), node.preferred_device()), OPERATOR_T_EQL,
+                                              Array(node.expression())));
+}
+
+}  // namespace op

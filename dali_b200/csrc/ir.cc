@@ -292,7 +292,9 @@ bool parse_program(const std::string& text, Program* out, std::string* err) {
                 break;
             case S_OP:
             case S_CAST:
-                s.elem = false;
+                // without reductions there is no row scope: everything but scalars and
+                // constants is computed per element
+                s.elem = p.nreduce == 0;
                 s.stage = 0;
                 for (size_t i = 0; i < s.in.size(); ++i) {
                     s.elem = s.elem || src(i).elem;

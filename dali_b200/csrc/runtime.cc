@@ -364,6 +364,13 @@ static int do_launch(uint64_t hash, int device, void* stream, const int64_t* spa
 
 }  // namespace dalib
 
+namespace dalib {
+cudaError_t gemm_simt(cudaStream_t stream, int dtype, int64_t m, int64_t n, int64_t k, const void* a, int64_t ars,
+                      int64_t acs, const void* b, int64_t brs, int64_t bcs, void* c, int64_t crs, int64_t ccs,
+                      double alpha, double beta);
+static thread_local std::string tl_gemm_kernel;
+}  // namespace dalib
+
 using namespace dalib;
 
 // =========================================================================== C ABI
@@ -556,6 +563,36 @@ size_t dalib200_last_variant(char* buffer, size_t capacity) {
         buffer[n] = '\0';
     }
     return tl_variant.size();
+}
+
+int dalib200_gemm(int device, void* stream, int dtype, int64_t m, int64_t n, int64_t k, const void* a, int64_t ars,
+                  int64_t acs, const void* b, int64_t brs, int64_t bcs, void* c, int64_t crs, int64_t ccs, double alpha,
+                  double beta) {
+    {
+        State& s = S();
+        std::lock_guard<std::mutex> g(s.mu);
+        int rc = check_device(device);
+        if (rc != DALIB200_OK) return rc;
+        CUDA_OK(cudaSetDevice(s.devices[device].ordinal));
+    }
+    if (dtype != DALIB200_F32 && dtype != DALIB200_F64 && dtype != DALIB200_I32) {
+        set_error("dalib200_gemm: dtype must be f32, f64 or i32");
+        return DALIB200_ERR_INVALID;
+    }
+    if (m < 0 || n < 0 || k < 0 || !a || !b || !c) { set_error("dalib200_gemm: bad argument"); return DALIB200_ERR_INVALID; }
+    if (m == 0 || n == 0) return DALIB200_OK;
+    tl_gemm_kernel = "simt";
+    CUDA_OK(gemm_simt((cudaStream_t)stream, dtype, m, n, k, a, ars, acs, b, brs, bcs, c, crs, ccs, alpha, beta));
+    return DALIB200_OK;
+}
+
+size_t dalib200_last_gemm_kernel(char* buffer, size_t capacity) {
+    if (buffer && capacity) {
+        size_t n = tl_gemm_kernel.size() < capacity - 1 ? tl_gemm_kernel.size() : capacity - 1;
+        std::memcpy(buffer, tl_gemm_kernel.data(), n);
+        buffer[n] = '\0';
+    }
+    return tl_gemm_kernel.size();
 }
 
 int dalib200_alloc(int device, size_t bytes, void** out) {

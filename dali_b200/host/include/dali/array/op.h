@@ -1,0 +1,126 @@
+// op:: free functions of the lazy front end (reference: dali/array/op.h umbrella,
+// op/unary.h:7-31, op/binary.h:6-32, op/reducers.h:8-47, op/elementwise_operation.h,
+// op/gather.h, op/gather_from_rows.h, op/softmax.h, op/dot.h, op/arange.h).
+#ifndef DALI_ARRAY_OP_H
+#define DALI_ARRAY_OP_H
+
+#include <string>
+#include <tuple>
+#include <vector>
+
+#include "dali/array/array.h"
+
+namespace op {
+// ---- elementwise (functor names as in dali/array/functor.h)
+Array elementwise(Array a, const std::string& functor_name);
+Array elementwise(Array a, Array b, const std::string& functor_name);
+Array astype(Array x, DType dtype);          // rounds when converting to int32
+Array unsafe_cast(Array x, DType dtype);     // static_cast
+Array round(Array x);
+Array ceil(Array x);
+std::tuple<Array, Array> ensure_arguments_compatible(Array a, Array b, const std::string& functor_name, bool update_shape);
+
+Array identity(Array x);
+Array identity(int x);
+Array identity(float x);
+Array identity(double x);
+Array sqrt(Array x);
+Array square(Array x);
+Array abs(Array x);
+Array sigmoid(Array x);
+Array dsigmoid(Array x);
+Array tanh(Array x);
+Array dtanh(Array x);
+Array relu(Array x);
+Array relu_backward(Array x);
+Array eltinv(Array x);
+Array exp(Array x);
+Array log(Array x);
+Array log_or_zero(Array x);
+Array sign(Array x);
+Array softplus(Array x);
+Array softplus_backward(Array x);
+Array cube(Array x);
+Array rsqrt(Array x);
+Array isnan(Array x);
+Array isinf(Array x);
+Array inverse_tanh(Array x);
+
+Array all_equals(Array left, Array right);
+Array all_close(Array left, Array right, Array atolerance);
+Array close(Array left, Array right, Array atolerance);
+Array add(Array left, Array right);
+Array add(const std::vector<Array>& arrays, bool single_op = false);
+Array subtract(Array left, Array right);
+Array eltmul(Array left, Array right);
+Array eltdiv(Array left, Array right);
+Array equals(Array left, Array right);
+Array pow(Array left, Array right);
+Array steep_sigmoid(Array x, Array aggressiveness);
+Array steep_sigmoid_backward(Array x, Array aggressiveness);
+Array clipped_relu(Array x, Array clipval);
+Array clipped_relu_backward(Array x, Array clipval);
+Array prelu(Array x, Array weights);
+Array prelu_backward_weights(Array a, Array grad);
+Array prelu_backward_inputs(Array a, Array weights);
+Array lessthanequal(Array a, Array b);
+Array greaterthanequal(Array a, Array b);
+Array maximum(Array a, Array b);
+Array minimum(Array a, Array b);
+Array clip(Array a, Array b);
+Array binary_cross_entropy(Array a, Array b);
+Array binary_cross_entropy_grad(Array a, Array b);
+
+// ---- reducers
+Array sum(const Array& x);
+Array sum(const Array& x, const std::vector<int>& axes, bool keepdims = false);
+Array prod(const Array& x);
+Array prod(const Array& x, const std::vector<int>& axes, bool keepdims = false);
+Array max(const Array& x);
+Array max(const Array& x, const std::vector<int>& axes, bool keepdims = false);
+Array min(const Array& x);
+Array min(const Array& x, const std::vector<int>& axes, bool keepdims = false);
+Array mean(const Array& x);
+Array mean(const Array& x, const std::vector<int>& axes, bool keepdims = false);
+Array L2_norm(const Array& x);
+Array L2_norm(const Array& x, const std::vector<int>& axes, bool keepdims = false);
+Array argmax(const Array& x);
+Array argmax(const Array& x, const int& axis);
+Array argmin(const Array& x);
+Array argmin(const Array& x, const int& axis);
+Array any_isnan(const Array& array);
+Array any_isinf(const Array& array);
+Array any_isnan(const Array& array, const std::vector<int>& axes, bool keepdims = false);
+Array any_isinf(const Array& array, const std::vector<int>& axes, bool keepdims = false);
+Array all_reduce(const Array& a, const std::string& reducer_name);
+Array axis_reduce(const Array& a, const std::string& reducer_name, const std::vector<int>& axes, bool keepdims = false);
+Array argument_all_reduce(const Array& a, const std::string& reducer_name);
+Array argument_axis_reduce(const Array& a, const std::string& reducer_name, const int& axis);
+
+// ---- index ops
+Array gather(const Array& source, const Array& indices);
+Array gather_from_rows(const Array& source, const Array& indices);
+
+// ---- compositions
+Array softmax(const Array& logits, int axis = -1);
+Array softmax_temperature(const Array& logits, const Array& temperature, int axis = -1);
+
+// ---- dot
+Array matmul(Array a, Array b);
+Array matrix_vector_dot(const Array& a, const Array& b);
+Array inner(const Array& a, const Array& b);
+Array dot(const Array& a, const Array& b);
+
+// ---- construction helpers the reference's tests lean on
+Array arange(int start, int stop, int step);
+Array arange(int start, int stop);
+Array arange(int stop);
+Array fill(const Array& x, double value);      // same-shaped array holding `value`
+
+// ---- assignment
+Array assign(const Array& left, OPERATOR_T operator_t, const Array& right);
+Array autoreduce_assign(const Array& left, const Array& right);
+Array to_assignment(const Array& node);
+}  // namespace op
+
+#endif

@@ -146,6 +146,25 @@ int dalib200_launch_host(uint64_t hash, int device,
  * for tests and profiles. */
 size_t dalib200_last_variant(char* buffer, size_t capacity);
 
+/* ---- GEMM -------------------------------------------------------------------
+ * C[m,n] = alpha * A[m,k] . B[k,n] + beta * C, every operand addressed by
+ * element strides (row stride, column stride), so contiguous, transposed and
+ * strided views all pass as they are.  dtype: DALIB200_F32 / F64 / I32 (I32
+ * accumulates in int32 like the reference's ReferenceGemm<int>).  Replaces
+ * CublasGemmImpl::run (dali/array/gemm/cublas_gemm.cu:110-186), whose beta is
+ * hard-wired to 0, and CpuGemmImpl::run (dali/array/gemm/cpu_gemm.cpp:22-84).
+ * Asynchronous on `stream`. */
+int dalib200_gemm(int device, void* stream, int dtype,
+                  int64_t m, int64_t n, int64_t k,
+                  const void* a, int64_t a_row_stride, int64_t a_col_stride,
+                  const void* b, int64_t b_row_stride, int64_t b_col_stride,
+                  void* c, int64_t c_row_stride, int64_t c_col_stride,
+                  double alpha, double beta);
+
+/* Name of the GEMM kernel the last dalib200_gemm* call on this thread chose
+ * ("simt", "tcgen05.bf16", "tcgen05.tf32x3", ...); for tests and profiles. */
+size_t dalib200_last_gemm_kernel(char* buffer, size_t capacity);
+
 /* ---- device memory ---------------------------------------------------------
  * Replaces memory::bank::allocate / deposit / clear
  * (dali/array/memory/memory_bank.cpp:41-81) and memory::copy / clear

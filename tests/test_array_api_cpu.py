@@ -1,0 +1,165 @@
+"""Host logic of the lazy Array / op:: front end, without a GPU: shapes and
+view algebra, error behaviour (the reference's tests expect std::runtime_error,
+which arrives here as DaliB200Error), and -- in dry-run mode, where kernels are
+lowered and NVRTC-compiled but nothing is launched -- what fuses into what."""
+import numpy as np
+import pytest
+
+import dali_b200
+from dali_b200 import DaliB200Error
+from dali_b200.array import (Array, DTYPE_DOUBLE, DTYPE_FLOAT, DTYPE_INT32, last_ir, last_variant, lazy_stats, op,
+                             set_dry_run)
+
+
+@pytest.fixture(autouse=True, scope="module")
+def dry(tmp_path_factory):
+    dali_b200.load_library().cache_set_dir(str(tmp_path_factory.mktemp("dali_cache")))
+    set_dry_run(True)
+    yield
+    set_dry_run(False)
+
+
+def launched(arr):
+    before = lazy_stats()
+    arr.eval()
+    after = lazy_stats()
+    return {k: after[k] - before[k] for k in after}
+
+
+def test_shapes_and_views():
+    a = Array(np.zeros((3, 4, 5), np.float32))
+    assert a.shape == (3, 4, 5) and a.ndim == 3 and a.dtype == DTYPE_FLOAT
+    assert a[1].shape == (4, 5)
+    assert a[:, 1:3].shape == (3, 2, 5)
+    assert a[:, ::2, 4].shape == (3, 2)
+    assert a[None].shape == (1, 3, 4, 5)
+    assert a.T.shape == (5, 4, 3)
+    assert a.transpose([1, 0, 2]).shape == (4, 3, 5)
+    assert a.reshape([12, 5]).shape == (12, 5)
+    assert a.reshape([-1]).shape == (60,)
+    assert a.expand_dims(1).squeeze(1).shape == (3, 4, 5)
+    assert a[:, 0:1].broadcast_to_shape([3, 7, 5]).shape == (3, 7, 5)
+    # views of lazy nodes keep being lazy
+    e = op.exp(a)
+    assert e[1].shape == (4, 5) and not e.is_buffer()
+    assert op.sum(a, [1], True).shape == (3, 1, 5)
+    assert op.sum(a, [0, 2]).shape == (4,)
+    assert op.argmax(a, 1).shape == (3, 5) and op.argmax(a, 1).dtype == DTYPE_INT32
+    assert op.sum(a).shape == () and op.argmax(a).dtype == DTYPE_INT32
+
+
+def test_type_promotion():
+    f = Array(np.zeros((2, 2), np.float32))
+    d = Array(np.zeros((2, 2), np.float64))
+    i = Array(np.zeros((2, 2), np.int32))
+    assert (f + d).dtype == DTYPE_DOUBLE and (f + i).dtype == DTYPE_FLOAT and (d + i).dtype == DTYPE_DOUBLE
+    assert (i + i).dtype == DTYPE_INT32 and (i * 2).dtype == DTYPE_INT32 and (i * 2.0).dtype == DTYPE_DOUBLE
+    assert op.mean(i).dtype == DTYPE_DOUBLE          # reducers.cpp: mean of ints is a double
+    assert f.astype(DTYPE_INT32).dtype == DTYPE_INT32
+
+
+def test_errors_like_the_reference():
+    a = Array(np.zeros((3, 4), np.float32))
+    b = Array(np.zeros((3, 5), np.float32))
+    v = Array(np.zeros((4,), np.float32))
+    with pytest.raises(DaliB200Error):      # incompatible shapes
+        (a + b).eval()
+    with pytest.raises(DaliB200Error):      # rank mismatch (tests.cpp:613)
+        a + v
+    with pytest.raises(DaliB200Error):      # reduction axis out of range
+        op.sum(a, [2])
+    with pytest.raises(DaliB200Error):      # duplicate axes
+        op.sum(a, [0, 0])
+    with pytest.raises(DaliB200Error):      # slice out of range (python slices clamp, Slice(2, 9) does not)
+        Array._new(dali_b200.load_library().c.dali_array_slice, a._h, 1, 2, 9, 1)
+    with pytest.raises(DaliB200Error):      # index out of range
+        a[3]
+    with pytest.raises(DaliB200Error):      # reshape changes element count (tests.cpp:438-440)
+        a.reshape([5, 5])
+    with pytest.raises(DaliB200Error):      # gather needs int32 indices
+        op.gather(a, Array(np.zeros((2,), np.float32)))
+    with pytest.raises(DaliB200Error):      # dot shapes (dot_tests.cpp:213-216)
+        op.dot(a, b)
+    with pytest.raises(DaliB200Error):      # unknown functor name through the binding
+        op._unary("nosuchop", a)
+
+
+def test_softmax_is_one_kernel_without_temporaries():
+    a = Array(np.zeros((4096, 1024), np.float32))
+    exped = op.exp(a - op.max(a, [-1], True))
+    s = exped / op.sum(exped, [-1], True)
+    assert "View(max(Buffer))" in s.expression_name()
+    assert launched(s) == {"kernels": 1, "gemms": 0, "temporaries": 0}
+    ir = last_ir()
+    assert ir.count(" ld ") == 1 and ir.count("red max") == 1 and ir.count("red sum") == 1 and ir.count("op exp") == 1
+    assert last_variant().startswith("row.") and ".v4." in last_variant()
+    assert s.is_buffer()                       # evaluated once, remembered
+    assert launched(s) == {"kernels": 0, "gemms": 0, "temporaries": 0}
+    # the library composition lowers to the very same program
+    s2 = op.softmax(Array(np.zeros((4096, 1024), np.float32)))
+    s2.eval()
+    assert last_ir() == ir
+
+
+def test_reduction_skeletons_from_the_front_end():
+    x = Array(np.zeros((2048, 2048), np.float32))
+    for fn, want in ((lambda: op.sum(x, [-1]), "row."), (lambda: op.sum(x, [0]), "col."), (lambda: op.sum(x), "all."),
+                     (lambda: op.max(x, [0], True), "col."), (lambda: op.argmax(x, 0), "col."),
+                     (lambda: op.argmax(x, -1), "row."), (lambda: op.argmin(x), "all."),
+                     (lambda: op.mean(x, [0]), "col."), (lambda: op.L2_norm(x, [-1]), "row.")):
+        assert launched(fn()) == {"kernels": 1, "gemms": 0, "temporaries": 0}
+        assert last_variant().startswith(want), (want, last_variant())
+
+
+def test_chain_fuses_into_the_all_reduce():
+    v = Array(np.zeros((1 << 20,), np.float32))
+    s = op.sum(op.sigmoid(v * np.float32(0.5) + np.float32(0.1)) * op.exp(-v * v))
+    assert launched(s) == {"kernels": 1, "gemms": 0, "temporaries": 0}
+    ir = last_ir()
+    assert "scalar 0 f32" in ir and "scalar 1 f32" in ir and " ld " in ir and ir.count(" ld ") == 1
+    assert last_variant().startswith("all.")
+    # other scalar values reuse the same program (values are run-time arguments)
+    s2 = op.sum(op.sigmoid(v * np.float32(0.25) + np.float32(0.7)) * op.exp(-v * v))
+    s2.eval()
+    assert last_ir() == ir
+
+
+def test_unfusable_subtrees_become_temporaries():
+    x = Array(np.zeros((64, 64), np.float32))
+    assert launched(x - op.mean(x)) == {"kernels": 2, "gemms": 0, "temporaries": 1}      # all-reduce inside a map
+    assert launched(x / op.sum(x, [0], True)) == {"kernels": 2, "gemms": 0, "temporaries": 1}   # reduce over a leading dim
+    y = op.sum(x, [-1], True) * op.max(x, [-1], True) + x                               # two row reductions: one kernel
+    assert launched(y) == {"kernels": 1, "gemms": 0, "temporaries": 0}
+    w = Array(np.zeros((64, 32), np.float32))
+    assert launched(op.tanh(op.dot(x, w) + Array(np.zeros((32,), np.float32))[None])) == {"kernels": 1, "gemms": 1, "temporaries": 1}
+
+
+def test_lstm_gating_on_slices_is_one_map_kernel():
+    H = 128
+    g = Array(np.zeros((16, 4 * H), np.float32))
+    c = Array(np.zeros((16, H), np.float32))
+    i, f, o = (op.sigmoid(g[:, k * H:(k + 1) * H]) for k in range(3))
+    gg = op.tanh(g[:, 3 * H:4 * H])
+    cn = f * c + i * gg
+    hn = o * op.tanh(cn)
+    assert launched(hn) == {"kernels": 1, "gemms": 0, "temporaries": 0}
+    assert last_variant().startswith("map.o1.i1.v4.")
+    assert last_ir().count(" ld ") == 5       # four gate slices + c, each read once
+
+
+def test_inplace_and_scatter_lowering():
+    a = Array(np.zeros((8, 8), np.float32))
+    b = Array(np.zeros((8, 8), np.float32))
+    a += b * 2.0
+    assert launched(a) == {"kernels": 1, "gemms": 0, "temporaries": 0}
+    assert "st 1 add" in last_ir() or "st 0 add" in last_ir()
+    dest = Array.zeros((3,), DTYPE_INT32)
+    idx = Array(np.array([0, 0, 1, 1, 1, 2], np.int32))
+    gathered = dest[idx]
+    gathered += 1
+    assert launched(gathered) == {"kernels": 1, "gemms": 0, "temporaries": 0}
+    assert "stx" in last_ir() and " add " in last_ir()
+    lse = Array.zeros((2, 1), DTYPE_INT32)
+    lse <<= Array.ones((2, 5), DTYPE_INT32)
+    lse.eval()
+    assert "red sum" in last_ir()
