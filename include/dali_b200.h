@@ -165,6 +165,29 @@ int dalib200_gemm(int device, void* stream, int dtype,
  * ("simt", "tcgen05.bf16", "tcgen05.tf32x3", ...); for tests and profiles. */
 size_t dalib200_last_gemm_kernel(char* buffer, size_t capacity);
 
+/* ---- allocation-free entry point ----------------------------------------------
+ * No counterpart in the reference (it allocates freely through memory::bank).
+ *
+ * *out = sum of the n fp32 elements at x (device pointers), asynchronous on
+ * `stream` -- the all-axis reduction of dalib200_launch, for callers that may
+ * not allocate device memory at call time: a thread inside a CUDA-graph stream
+ * capture, a latency-critical host thread that must stay away from allocator
+ * locks, an embedding with a memory budget fixed at load time.  The cross-CTA
+ * exchange space lives in a fixed 8.25 KiB array inside the library image
+ * (every GPU that loads the library holds it until exit); the call performs no
+ * cudaMalloc / cudaFree and calls no allocating library routine.
+ *   - n may be at most DALIB200_NOALLOC_MAX_ELEMENTS; more is refused with
+ *     DALIB200_ERR_TOO_LARGE (use dalib200_launch, whose scratch grows).
+ *   - The first call on a device looks up the array's device address
+ *     (cudaGetSymbolAddress) with that device current; make that first call
+ *     before starting any stream capture.
+ *   - All calls share the one array: two calls whose kernels can overlap on the
+ *     GPU (different streams, no dependency) race on it.  Issue them on one
+ *     stream or order them with events.
+ * Needs dalib200_init to have bound `device`. */
+#define DALIB200_NOALLOC_MAX_ELEMENTS ((int64_t)1 << 31)
+int dalib200_sum_f32_noalloc(int device, void* stream, const float* x, int64_t n, float* out);
+
 /* ---- device memory ---------------------------------------------------------
  * Replaces memory::bank::allocate / deposit / clear
  * (dali/array/memory/memory_bank.cpp:41-81) and memory::copy / clear
