@@ -31,6 +31,17 @@ def _embed_prelude():
             f.write(text)
 
 
+def _embed(src_name, out_name, tag):
+    src = open(os.path.join(CSRC, src_name)).read()
+    close = ")" + tag + '"'
+    assert close not in src
+    out = os.path.join(CSRC, out_name)
+    text = 'R"' + tag + "(" + src + close + "\n"
+    if not os.path.exists(out) or open(out).read() != text:
+        with open(out, "w") as f:
+            f.write(text)
+
+
 def _newer(target, sources):
     if not os.path.exists(target):
         return True
@@ -54,6 +65,7 @@ def build(force=False, verbose=False):
     objdir = os.path.join(LIBDIR, "obj")
     os.makedirs(objdir, exist_ok=True)
     _embed_prelude()
+    _embed("gemm_sm100.cuh", "gemm_embed.inc", "DALIGEMM")
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh", ".inc"))]
     headers += [os.path.join(HERE, "..", "include", f) for f in os.listdir(os.path.join(HERE, "..", "include"))]
     for d in (os.path.join(CSRC, "host"), os.path.join(HERE, "host", "include", "dali", "array")):

@@ -60,6 +60,19 @@ class Library:
                                          ctypes.c_void_p]
         c.dalib200_memset.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t, ctypes.c_void_p]
         c.dalib200_sync.argtypes = [ctypes.c_int, ctypes.c_void_p]
+        c.dalib200_gemm.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int] + [ctypes.c_int64] * 3 + \
+            [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64] * 3 + [ctypes.c_double, ctypes.c_double]
+        c.dalib200_gemm_fused.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_int64,
+                                          ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64,
+                                          ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint64,
+                                          ctypes.POINTER(ctypes.c_void_p), c_i64p, ctypes.POINTER(c_i64p), ctypes.c_int,
+                                          ctypes.POINTER(ctypes.c_void_p), ctypes.c_int]
+        c.dalib200_gemm_split_tf32.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                               ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_void_p,
+                                               ctypes.c_void_p]
+        c.dalib200_gemm_error_flag.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
+        c.dalib200_last_gemm_kernel.restype = ctypes.c_size_t
+        c.dalib200_last_gemm_kernel.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
         c.dalib200_cache_set_dir.argtypes = [ctypes.c_char_p]
         c.dalib200_cache_stats.argtypes = [ctypes.POINTER(ctypes.c_uint64)]
         self._next_hash = 0x0da11b200
@@ -173,6 +186,43 @@ class Library:
         sc, keep2 = self._scalars_arg(scalars)
         self.check(self.c.dalib200_launch_host(ctypes.c_uint64(hash_), device, _i64_array(space), len(space), ptrs,
                                                ext, offs, st, n, sc, len(scalars or [])))
+
+    # -- GEMM -----------------------------------------------------------------
+    @staticmethod
+    def _ptr(x):
+        return ctypes.c_void_p(x.data_ptr() if hasattr(x, "data_ptr") else int(x))
+
+    def gemm(self, dtype, m, n, k, a, a_strides, b, b_strides, c, c_strides, alpha=1.0, beta=0.0, device=0, stream=None):
+        self.check(self.c.dalib200_gemm(device, ctypes.c_void_p(stream or 0), dtype, m, n, k, self._ptr(a), a_strides[0],
+                                        a_strides[1], self._ptr(b), b_strides[0], b_strides[1], self._ptr(c), c_strides[0],
+                                        c_strides[1], alpha, beta))
+
+    def gemm_fused(self, ab_dtype, m, n, k, a, lda, b, ldb, epilogue_hash, arrays, strides=None, offsets=None, scalars=None,
+                   a_lo=None, b_lo=None, device=0, stream=None):
+        """acc = A[m,k] . B[k,n] on the tensor cores, then the registered epilogue program over [m,n]."""
+        na = len(arrays)
+        ptrs = (ctypes.c_void_p * na)(*[(x.data_ptr() if hasattr(x, "data_ptr") else int(x)) for x in arrays])
+        offs = _i64_array(offsets if offsets else [0] * na)
+        st, keep = self._strides_arg(strides, na)
+        sc, keep2 = self._scalars_arg(scalars)
+        self.check(self.c.dalib200_gemm_fused(device, ctypes.c_void_p(stream or 0), ab_dtype, m, n, k, self._ptr(a), lda,
+                                              self._ptr(b), ldb, self._ptr(a_lo) if a_lo is not None else None,
+                                              self._ptr(b_lo) if b_lo is not None else None, ctypes.c_uint64(epilogue_hash),
+                                              ptrs, offs, st, na, sc, len(scalars or [])))
+
+    def gemm_split_tf32(self, x, rows, cols, ld, hi, lo, transpose=False, device=0, stream=None):
+        self.check(self.c.dalib200_gemm_split_tf32(device, ctypes.c_void_p(stream or 0), self._ptr(x), rows, cols, ld,
+                                                   int(transpose), self._ptr(hi), self._ptr(lo)))
+
+    def gemm_error_flag(self, device=0):
+        f = ctypes.c_int(0)
+        self.check(self.c.dalib200_gemm_error_flag(device, ctypes.byref(f)))
+        return f.value
+
+    def last_gemm_kernel(self):
+        buf = ctypes.create_string_buffer(512)
+        self.c.dalib200_last_gemm_kernel(buf, len(buf))
+        return buf.value.decode()
 
     # -- memory ---------------------------------------------------------------
     def alloc(self, nbytes, device=0):

@@ -1,0 +1,424 @@
+// Host side of the tcgen05 GEMM: epilogue splicing, tile choice, TMA tensor
+// maps, 3xTF32 operand split, launch.  Kernel: gemm_sm100.cuh.
+//
+// Replaces CublasGemmImpl::run (dali/array/gemm/cublas_gemm.cu:110-186) for
+// the large aligned products, together with the elementwise kernel that the
+// reference launches afterwards on the product (dali/array/jit/jit.cpp:1080-
+// 1142 keeps MatMul out of every fused kernel, dali/array/op/dot.h:7).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstring>
+#include <sstream>
+
+#include "../../include/dali_b200.h"
+#include "runtime.h"
+
+namespace dalib {
+
+static const char* kGemmSkeleton =
+#include "gemm_embed.inc"
+    ;
+
+cudaError_t split_tf32(cudaStream_t stream, const float* x, long long rows, long long cols, long long ld, bool transpose,
+                       float* hi, float* lo);
+
+namespace {
+
+struct GemmVariant {
+    int esize;      // 2 bf16, 4 tf32
+    int split;      // 3xTF32
+    int bm, bn, bk, stages;
+    bool b_kmajor() const { return split != 0; }   // the fp32 path transposes B while splitting it
+    unsigned idesc() const {
+        unsigned fmt = esize == 2 ? 1u : 2u;       // kind::f16: 1 = bf16; kind::tf32: 2 = tf32
+        unsigned d = 0;
+        d |= 1u << 4;                              // accumulate in fp32
+        d |= fmt << 7;                             // A format
+        d |= fmt << 10;                            // B format
+        d |= 0u << 15;                             // A is K-major
+        d |= (b_kmajor() ? 0u : 1u) << 16;         // B: K-major ([N,K]) or MN-major ([K,N])
+        d |= (unsigned)(bn >> 3) << 17;
+        d |= (unsigned)(bm >> 4) << 24;
+        return d;
+    }
+    size_t stage_bytes() const { return (size_t)(split ? 2 : 1) * ((size_t)bm * bk * esize + (size_t)bn * bk * esize); }
+    size_t smem_bytes() const { return stages * stage_bytes() + 1024; }
+    std::string key() const {
+        std::ostringstream o;
+        o << "gemm.e" << esize << ".s" << split << ".m" << bm << ".n" << bn << ".k" << bk << ".st" << stages;
+        return o.str();
+    }
+};
+
+const char* red_c(DType t) { return dtype_c_name(t); }
+
+// EPILOGUE_CHUNK(row, col0, acc, nvalid): thread-local 32-wide slab of one output row
+bool epilogue_macro(const Program& p, std::string* out, std::string* err) {
+    if (!p.has_acc || p.nreduce != 0 || p.rank != 2) { *err = "epilogue program must be 'space 2 0' and read 'acc'"; return false; }
+    if (p.has_indirect || p.n_reductions) { *err = "epilogue program may not gather or reduce"; return false; }
+    const int nargs = (int)p.args.size();
+    std::ostringstream o;
+    auto W = [&](int w) { return "p.w[" + std::to_string(w) + "]"; };
+    auto argT = [&](int a) -> std::string { return p.args[a].dtype == BF16 ? "unsigned short" : dtype_c_name(p.args[a].dtype); };
+    o << "#define EPILOGUE_CHUNK(row, col0, acc, nvalid) { \\\n";
+    for (int a = 0; a < nargs; ++a) {
+        bool ro = !p.args[a].written;
+        o << "  " << (ro ? "const " : "") << argT(a) << "* const a" << a << " = reinterpret_cast<" << (ro ? "const " : "")
+          << argT(a) << "*>(" << W(3 * a) << ") + (row) * " << W(3 * a + 1) << "; \\\n";
+    }
+    // loads
+    std::vector<bool> loaded(nargs, false);
+    for (const Stmt& s : p.stmts) {
+        int a = -1;
+        if (s.kind == S_LD) a = s.arg;
+        if (s.kind == S_ST && s.aop != A_ASSIGN) a = s.arg;
+        if (a < 0 || loaded[a]) continue;
+        loaded[a] = true;
+        o << "  float in" << a << "[32]; gemm_io::load_chunk(a" << a << ", (col0), " << W(3 * a + 2) << ", in" << a << ", (nvalid)); \\\n";
+    }
+    for (const Stmt& s : p.stmts)
+        if (s.kind == S_ST) o << "  float out" << s.arg << "[32]; \\\n";
+    for (const Stmt& s : p.stmts) {
+        if (s.kind == S_SC)
+            o << "  const " << red_c(s.dtype) << " v" << s.id << " = *reinterpret_cast<const " << red_c(s.dtype) << "*>(&"
+              << W(3 * nargs + s.arg) << "); \\\n";
+        if (s.kind == S_CONST) {
+            std::string lit = s.literal;
+            if (s.dtype != I32 && lit.find_first_of(".eEn") == std::string::npos) lit += ".0";
+            o << "  const " << red_c(s.dtype) << " v" << s.id << " = (" << red_c(s.dtype) << ")(" << lit << "); \\\n";
+        }
+    }
+    o << "  _Pragma(\"unroll\") for (int j = 0; j < 32; ++j) { \\\n";
+    for (const Stmt& s : p.stmts) {
+        const std::string T = red_c(s.dtype);
+        switch (s.kind) {
+            case S_ACC: o << "    const float v" << s.id << " = acc[j]; \\\n"; break;
+            case S_LD: o << "    const " << T << " v" << s.id << " = (" << T << ")in" << s.arg << "[j]; \\\n"; break;
+            case S_CAST: o << "    const " << T << " v" << s.id << " = (" << T << ")v" << s.in[0] << "; \\\n"; break;
+            case S_OP: {
+                o << "    const " << T << " v" << s.id << " = ";
+                if (s.name == "round" || s.name == "ceiling") o << "f_" << s.name << "<" << T << ">(v" << s.in[0] << ")";
+                else {
+                    o << "f_" << s.name << "(v" << s.in[0];
+                    if (s.in.size() > 1) o << ", v" << s.in[1];
+                    o << ")";
+                }
+                o << "; \\\n";
+                break;
+            }
+            case S_ST: {
+                std::string v = "(float)v" + std::to_string(s.in[0]);
+                std::string old = "in" + std::to_string(s.arg) + "[j]";
+                switch (s.aop) {
+                    case A_ASSIGN: break;
+                    case A_ADD: v = old + " + " + v; break;
+                    case A_SUB: v = old + " - " + v; break;
+                    case A_MUL: v = old + " * " + v; break;
+                    case A_DIV: v = old + " / " + v; break;
+                }
+                o << "    out" << s.arg << "[j] = " << v << "; \\\n";
+                break;
+            }
+            default: break;
+        }
+    }
+    o << "  } \\\n";
+    for (const Stmt& s : p.stmts)
+        if (s.kind == S_ST)
+            o << "  gemm_io::store_chunk(a" << s.arg << ", (col0), " << W(3 * s.arg + 2) << ", out" << s.arg << ", (nvalid)); \\\n";
+    o << "}\n";
+    *out = o.str();
+    return true;
+}
+
+// chunk I/O helpers used by the epilogue macro
+const char* kGemmIo = R"IO(
+namespace gemm_io {
+DEV bool aligned16(const void* p) { return (reinterpret_cast<unsigned long long>(p) & 15ull) == 0; }
+// 32 consecutive columns of one row, element stride cs, as fp32
+DEV void load_chunk(const float* p, long long col0, long long cs, float* dst, int nvalid) {
+    if (cs == 1 && nvalid == 32 && aligned16(p + col0)) {
+        const float4* q = reinterpret_cast<const float4*>(p + col0);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { float4 t = q[i]; dst[4 * i] = t.x; dst[4 * i + 1] = t.y; dst[4 * i + 2] = t.z; dst[4 * i + 3] = t.w; }
+    } else if (cs == 0) {
+        const float t = p[0];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) dst[i] = t;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) dst[i] = i < nvalid ? p[(col0 + i) * cs] : 0.0f;
+    }
+}
+DEV void load_chunk(const unsigned short* p, long long col0, long long cs, float* dst, int nvalid) {
+    if (cs == 1 && nvalid == 32 && aligned16(p + col0)) {
+        const uint4* q = reinterpret_cast<const uint4*>(p + col0);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint4 t = q[i];
+            unsigned w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { dst[8 * i + 2 * k] = __uint_as_float(w[k] << 16); dst[8 * i + 2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u); }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) dst[i] = i < nvalid ? gemm::bf16_to_f32(p[cs == 0 ? 0 : (col0 + i) * cs]) : 0.0f;
+    }
+}
+template <typename T> DEV void load_chunk(const T* p, long long col0, long long cs, float* dst, int nvalid) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) dst[i] = i < nvalid ? (float)p[cs == 0 ? 0 : (col0 + i) * cs] : 0.0f;
+}
+DEV void store_chunk(float* p, long long col0, long long cs, const float* src, int nvalid) {
+    if (cs == 1 && nvalid == 32 && aligned16(p + col0)) {
+        float4* q = reinterpret_cast<float4*>(p + col0);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[i] = make_float4(src[4 * i], src[4 * i + 1], src[4 * i + 2], src[4 * i + 3]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) if (i < nvalid) p[(col0 + i) * cs] = src[i];
+    }
+}
+DEV void store_chunk(unsigned short* p, long long col0, long long cs, const float* src, int nvalid) {
+    if (cs == 1 && nvalid == 32 && aligned16(p + col0)) {
+        uint4* q = reinterpret_cast<uint4*>(p + col0);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            q[i] = make_uint4(gemm::pack_bf16x2(src[8 * i], src[8 * i + 1]), gemm::pack_bf16x2(src[8 * i + 2], src[8 * i + 3]),
+                              gemm::pack_bf16x2(src[8 * i + 4], src[8 * i + 5]), gemm::pack_bf16x2(src[8 * i + 6], src[8 * i + 7]));
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (i < nvalid) p[(col0 + i) * cs] = (unsigned short)(gemm::pack_bf16x2(src[i], 0.0f) & 0xffffu);
+    }
+}
+template <typename T> DEV void store_chunk(T* p, long long col0, long long cs, const float* src, int nvalid) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) if (i < nvalid) p[(col0 + i) * cs] = (T)src[i];
+}
+}  // namespace gemm_io
+)IO";
+
+struct GemmSourceCtx { const Program* p; GemmVariant v; };
+
+bool gemm_source(void* ctx, std::string* src, std::string* err) {
+    GemmSourceCtx* c = static_cast<GemmSourceCtx*>(ctx);
+    std::string macro;
+    if (!epilogue_macro(*c->p, &macro, err)) return false;
+    std::ostringstream o;
+    o << device_prelude() << "\n";
+    o << "#define GEMM_BM " << c->v.bm << "\n#define GEMM_BN " << c->v.bn << "\n#define GEMM_BK " << c->v.bk << "\n";
+    o << "#define GEMM_STAGES " << c->v.stages << "\n#define GEMM_ESIZE " << c->v.esize << "\n#define GEMM_SPLIT " << c->v.split << "\n";
+    o << "#define GEMM_IDESC " << c->v.idesc() << "u\n";
+    o << "#define GEMM_B_KMAJOR " << (c->v.b_kmajor() ? 1 : 0) << "\n";
+    int words = 3 * (int)c->p->args.size() + (int)c->p->scalars.size();
+    o << "#define GEMM_EPI_WORDS " << (words < 1 ? 1 : words) << "\n";
+    // the io helpers need gemm:: conversions, which the skeleton defines: split the skeleton at its kernel
+    std::string skel(kGemmSkeleton);
+    size_t cut = skel.find("extern \"C\" __global__");
+    o << skel.substr(0, cut) << kGemmIo << macro << skel.substr(cut);
+    *src = o.str();
+    return true;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+bool make_map(CUtensorMap* map, bool bf16, const void* base, uint64_t inner, uint64_t outer, uint64_t ld_elems, uint32_t box_inner,
+              uint32_t box_outer, std::string* err) {
+    static EncodeTiledFn encode = reinterpret_cast<EncodeTiledFn>(driver_entry("cuTensorMapEncodeTiled"));
+    if (!encode) { *err = "cuTensorMapEncodeTiled unavailable"; return false; }
+    const uint64_t esize = bf16 ? 2 : 4;
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {ld_elems * esize};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base),
+                        dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { *err = "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r); return false; }
+    return true;
+}
+
+GemmVariant choose_variant(bool bf16, int64_t m, int64_t n) {
+    GemmVariant v;
+    v.esize = bf16 ? 2 : 4;
+    v.split = bf16 ? 0 : 1;
+    v.bm = 128;
+    v.bk = 128 / v.esize;
+    const int64_t mt = (m + 127) / 128;
+    auto tiles = [&](int bn) { return mt * ((n + bn - 1) / bn); };
+    const int max_bn = bf16 ? 256 : 128;
+    v.bn = 64;
+    for (int bn = max_bn; bn >= 64; bn >>= 1)
+        if (n >= bn && tiles(bn) >= 120) { v.bn = bn; break; }
+    if (n < 64) v.bn = 64;
+    const size_t budget = 200 * 1024;
+    v.stages = (int)(budget / v.stage_bytes());
+    if (v.stages > 8) v.stages = 8;
+    if (v.stages < 2) v.stages = 2;
+    return v;
+}
+
+struct GemmP {
+    long long M, N, K;
+    int* err;
+    long long w[64];
+};
+
+thread_local std::string tl_gemm_variant;
+
+}  // namespace
+
+const std::string& last_gemm_variant() { return tl_gemm_variant; }
+
+// a, b: device pointers; lda / ldb in elements.  For fp32 the caller passes the
+// already split operands (hi / lo); see dalib200_gemm_fused.
+int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n, int64_t k, const void* a, const void* a_lo,
+                      int64_t lda, const void* b, const void* b_lo, int64_t ldb, uint64_t epilogue_hash, void* const* array_data,
+                      const int64_t* offsets, const int64_t* const* strides, int n_arrays, const void* const* scalars, int n_scalars,
+                      bool compile_only) {
+    Program prog;
+    if (!find_program(epilogue_hash, &prog)) { set_error("unknown epilogue hash"); return DALIB200_ERR_NOT_FOUND; }
+    if (n_arrays != (int)prog.args.size() || n_scalars != (int)prog.scalars.size()) {
+        set_error("gemm_fused: wrong number of epilogue arrays / scalars");
+        return DALIB200_ERR_INVALID;
+    }
+    if (3 * n_arrays + n_scalars > 64) { set_error("gemm_fused: too many epilogue operands"); return DALIB200_ERR_TOO_LARGE; }
+    GemmSourceCtx ctx{&prog, choose_variant(bf16, m, n)};
+    const GemmVariant& v = ctx.v;
+    std::ostringstream key;
+    key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + "|sm_100a|gemm-2|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" +
+                                                     std::to_string(fnv1a(device_prelude())));
+    tl_gemm_variant = std::string(bf16 ? "tcgen05.bf16 " : "tcgen05.tf32x3 ") + v.key();
+    void* fn = nullptr;
+    int rc = acquire_kernel(compile_only ? -1 : device, key.str(), "dali_gemm_kernel", gemm_source, &ctx, &fn, nullptr);
+    if (rc != DALIB200_OK || compile_only) return rc;
+
+    std::string err;
+    CUtensorMap tmA, tmB, tmAlo, tmBlo;
+    const uint32_t sw = 128 / v.esize;
+    if (!make_map(&tmA, bf16, a, (uint64_t)k, (uint64_t)m, (uint64_t)lda, (uint32_t)v.bk, (uint32_t)v.bm, &err) ||
+        !(v.b_kmajor() ? make_map(&tmB, bf16, b, (uint64_t)k, (uint64_t)n, (uint64_t)ldb, (uint32_t)v.bk, (uint32_t)v.bn, &err)
+                       : make_map(&tmB, bf16, b, (uint64_t)n, (uint64_t)k, (uint64_t)ldb, sw, (uint32_t)v.bk, &err)) ||
+        !make_map(&tmAlo, bf16, a_lo ? a_lo : a, (uint64_t)k, (uint64_t)m, (uint64_t)lda, (uint32_t)v.bk, (uint32_t)v.bm, &err) ||
+        !(v.b_kmajor() ? make_map(&tmBlo, bf16, b_lo ? b_lo : b, (uint64_t)k, (uint64_t)n, (uint64_t)ldb, (uint32_t)v.bk, (uint32_t)v.bn, &err)
+                       : make_map(&tmBlo, bf16, b_lo ? b_lo : b, (uint64_t)n, (uint64_t)k, (uint64_t)ldb, sw, (uint32_t)v.bk, &err))) {
+        set_error("gemm_fused: " + err);
+        return DALIB200_ERR_CUDA;
+    }
+    GemmP p;
+    std::memset(&p, 0, sizeof p);
+    p.M = m; p.N = n; p.K = k;
+    p.err = gemm_error_word(device);
+    if (!p.err) { set_error("gemm_fused: cannot allocate the error word"); return DALIB200_ERR_CUDA; }
+    for (int i = 0; i < n_arrays; ++i) {
+        const int es = dtype_size(prog.args[i].dtype);
+        p.w[3 * i] = (long long)(uintptr_t)((char*)array_data[i] + (offsets ? offsets[i] : 0) * es);
+        p.w[3 * i + 1] = strides && strides[i] ? strides[i][0] : n;
+        p.w[3 * i + 2] = strides && strides[i] ? strides[i][1] : 1;
+    }
+    for (int j = 0; j < n_scalars; ++j) {
+        long long w = 0;
+        std::memcpy(&w, scalars[j], dtype_size(prog.scalars[j]));
+        p.w[3 * n_arrays + j] = w;
+    }
+    // the kernel's GemmP has exactly GEMM_EPI_WORDS words; ours is a superset with the same prefix
+    void* params[] = {&tmA, &tmB, &tmAlo, &tmBlo, &p};
+    const unsigned gx = (unsigned)((n + v.bn - 1) / v.bn), gy = (unsigned)((m + v.bm - 1) / v.bm);
+    return launch_function(device, fn, gx, gy, 192, (unsigned)v.smem_bytes(), stream, params);
+}
+
+}  // namespace dalib
+
+using namespace dalib;
+
+extern "C" {
+
+int dalib200_gemm_fused(int device, void* stream, int ab_dtype, int64_t m, int64_t n, int64_t k, const void* a, int64_t lda,
+                        const void* b, int64_t ldb, const void* a_lo, const void* b_lo, uint64_t epilogue_hash,
+                        void* const* array_data, const int64_t* offsets, const int64_t* const* strides, int n_arrays,
+                        const void* const* scalars, int n_scalars) {
+    if (ab_dtype != DALIB200_BF16 && ab_dtype != DALIB200_F32) {
+        set_error("dalib200_gemm_fused: operands must be bf16 or f32");
+        return DALIB200_ERR_INVALID;
+    }
+    if (m < 0 || n < 0 || k < 0 || !a || !b) { set_error("dalib200_gemm_fused: bad argument"); return DALIB200_ERR_INVALID; }
+    if (m == 0 || n == 0) return DALIB200_OK;
+    const bool bf16 = ab_dtype == DALIB200_BF16;
+    const int es = bf16 ? 2 : 4;
+    // what TMA needs: 16-byte aligned bases and row pitches
+    const bool presplit = !bf16 && a_lo && b_lo;       // then b / b_lo are the TRANSPOSED parts, [n,k] with pitch ldb
+    if (((uintptr_t)a & 15) || ((uintptr_t)b & 15) || (lda * es) % 16 || (ldb * es) % 16 || lda < k || ldb < (presplit ? k : n) ||
+        (a_lo && ((uintptr_t)a_lo & 15)) || (b_lo && ((uintptr_t)b_lo & 15)) || m > 2147483647LL || n > 2147483647LL ||
+        k > 2147483647LL) {
+        set_error("dalib200_gemm_fused: operands must be row-major with 16-byte aligned base and row pitch");
+        return DALIB200_ERR_UNSUPPORTED;
+    }
+    const bool compile_only = device < 0;
+    if (!bf16 && ((a_lo != nullptr) != (b_lo != nullptr))) {
+        set_error("dalib200_gemm_fused: pass both split operands or neither");
+        return DALIB200_ERR_INVALID;
+    }
+    if (bf16 || compile_only || presplit)
+        return gemm_fused_launch(device, stream, bf16, m, n, k, a, a_lo, lda, b, b_lo, ldb, epilogue_hash, array_data, offsets,
+                                 strides, n_arrays, scalars, n_scalars, compile_only);
+    // fp32 without pre-split operands: split here into pool temporaries (recycled in stream order)
+    if (k % 4 || n % 4) { set_error("dalib200_gemm_fused: fp32 operands need k and n to be multiples of 4"); return DALIB200_ERR_UNSUPPORTED; }
+    if (a_lo || b_lo) { set_error("dalib200_gemm_fused: pass both split operands or neither"); return DALIB200_ERR_INVALID; }
+    int ord = device_ordinal(device);
+    if (ord < 0) { set_error("device index out of range"); return DALIB200_ERR_INVALID; }
+    cudaSetDevice(ord);
+    void *ahi = nullptr, *alo = nullptr, *bhi = nullptr, *blo = nullptr;
+    const size_t abytes = (size_t)m * k * 4, bbytes = (size_t)k * n * 4;
+    int rc = dalib200_alloc(device, abytes, &ahi);
+    if (rc == DALIB200_OK) rc = dalib200_alloc(device, abytes, &alo);
+    if (rc == DALIB200_OK) rc = dalib200_alloc(device, bbytes, &bhi);
+    if (rc == DALIB200_OK) rc = dalib200_alloc(device, bbytes, &blo);
+    if (rc == DALIB200_OK && (split_tf32((cudaStream_t)stream, (const float*)a, m, k, lda, false, (float*)ahi, (float*)alo) != cudaSuccess ||
+                              split_tf32((cudaStream_t)stream, (const float*)b, k, n, ldb, true, (float*)bhi, (float*)blo) != cudaSuccess)) {
+        set_error("split_tf32 launch failed");
+        rc = DALIB200_ERR_CUDA;
+    }
+    if (rc == DALIB200_OK)
+        rc = gemm_fused_launch(device, stream, false, m, n, k, ahi, alo, k, bhi, blo, k, epilogue_hash, array_data, offsets,
+                               strides, n_arrays, scalars, n_scalars, false);
+    if (ahi) dalib200_free(device, ahi, abytes);
+    if (alo) dalib200_free(device, alo, abytes);
+    if (bhi) dalib200_free(device, bhi, bbytes);
+    if (blo) dalib200_free(device, blo, bbytes);
+    return rc;
+}
+
+int dalib200_gemm_split_tf32(int device, void* stream, const float* x, int64_t rows, int64_t cols, int64_t ld, int transpose,
+                             float* hi, float* lo) {
+    int ord = device_ordinal(device);
+    if (ord < 0) { set_error("device index out of range"); return dalib200_device_count() ? DALIB200_ERR_INVALID : DALIB200_ERR_NO_DEVICE; }
+    if (!x || !hi || !lo || cols % 4 || ld % 4 || ((uintptr_t)x & 15) || ((uintptr_t)hi & 15) || ((uintptr_t)lo & 15)) {
+        set_error("dalib200_gemm_split_tf32: needs 16-byte aligned pointers and cols, ld multiples of 4");
+        return DALIB200_ERR_INVALID;
+    }
+    cudaSetDevice(ord);
+    if (transpose && rows % 4) { set_error("dalib200_gemm_split_tf32: transposed output needs rows % 4 == 0"); return DALIB200_ERR_INVALID; }
+    if (split_tf32((cudaStream_t)stream, x, rows, cols, ld, transpose != 0, hi, lo) != cudaSuccess) {
+        set_error("split_tf32 launch failed");
+        return DALIB200_ERR_CUDA;
+    }
+    return DALIB200_OK;
+}
+
+int dalib200_gemm_error_flag(int device, int* flag) {
+    int ord = device_ordinal(device);
+    if (ord < 0) { set_error("device index out of range"); return DALIB200_ERR_INVALID; }
+    int* w = gemm_error_word(device);
+    if (!w) { set_error("no error word"); return DALIB200_ERR_CUDA; }
+    cudaSetDevice(ord);
+    cudaError_t e = cudaMemcpy(flag, w, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) { set_error(std::string("cudaMemcpy: ") + cudaGetErrorString(e)); return DALIB200_ERR_CUDA; }
+    if (*flag) cudaMemset(w, 0, sizeof(int));
+    return DALIB200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,291 @@
+// tcgen05 / TMEM GEMM skeleton for sm_100a with a spliced elementwise epilogue.
+// Compiled at run time by NVRTC behind dalib200_gemm_fused; the host side
+// (gemm_sm100.cc) prepends the device prelude, a block of #defines
+//   GEMM_BM GEMM_BN GEMM_BK GEMM_STAGES   tile and pipeline depth
+//   GEMM_ESIZE        operand element bytes: 2 (bf16, kind::f16) or 4 (tf32)
+//   GEMM_SPLIT        1: 3xTF32 (operands come with their low parts), else 0
+//   GEMM_B_KMAJOR     1: B is given transposed, [N,K] row-major (K-major, like A);
+//                     0: B is [K,N] row-major (MN-major).  bf16 takes B as it lies in
+//                     memory; the fp32 path gets B transposed for free by the pass that
+//                     splits it into high and low parts
+//   GEMM_IDESC        tcgen05 instruction descriptor
+// and a macro EPILOGUE_CHUNK(row, col0, acc, nvalid) generated from the
+// expression that consumes the product.
+//
+// Replaces cublasSgemm + a separate elementwise kernel that re-reads C
+// (dali/array/gemm/cublas_gemm.cu:157-178 followed by the JIT kernel of the
+// surrounding expression): one kernel, the accumulator goes from tensor memory
+// through the epilogue straight to its destination.
+//
+// Layout of the work:
+//   one CTA per GEMM_BM x GEMM_BN output tile, 192 threads:
+//     warps 0-3  epilogue: warp w owns TMEM lanes 32w..32w+31 (= tile rows)
+//     warp 4     TMA producer (one elected lane)
+//     warp 5     allocates TMEM, issues tcgen05.mma (one elected lane)
+//   A is K-major (row-major [M,K]), B is MN-major (row-major [K,N]); both are
+//   staged by TMA with 128-byte swizzle into a GEMM_STAGES-deep ring guarded
+//   by full / empty mbarriers; tcgen05.commit releases a stage when the MMAs
+//   that read it have finished.  No cluster, no multicast.
+//
+// Every wait is bounded (about a second of polling): on expiry the waiting
+// thread records a code in *p.err, raises a CTA-wide abort flag and all roles
+// drain; TMEM is always released before the CTA exits.
+
+struct alignas(64) TensorMap { unsigned long long opaque[16]; };
+
+struct GemmP {
+    long long M, N, K;
+    int* err;                 // device int, 0 = fine
+    long long w[GEMM_EPI_WORDS];
+};
+
+#define GEMM_THREADS 192
+#define GEMM_SWIZZLE_ELEMS (128 / GEMM_ESIZE)               /* elements per 128-byte swizzle row */
+#define GEMM_UMMA_K (32 / GEMM_ESIZE)                        /* K per tcgen05.mma: 32 bytes */
+#define GEMM_A_TILE_BYTES (GEMM_BM * GEMM_BK * GEMM_ESIZE)
+#define GEMM_B_ATOMS (GEMM_BN / GEMM_SWIZZLE_ELEMS)          /* 128-byte wide column panels of the B tile */
+#define GEMM_B_ATOM_BYTES (GEMM_BK * 128)
+#define GEMM_B_TILE_BYTES (GEMM_B_ATOMS * GEMM_B_ATOM_BYTES)
+#define GEMM_OPERAND_SETS (GEMM_SPLIT ? 2 : 1)
+#define GEMM_STAGE_BYTES (GEMM_OPERAND_SETS * (GEMM_A_TILE_BYTES + GEMM_B_TILE_BYTES))
+#define GEMM_TMEM_COLS (GEMM_BN < 32 ? 32 : GEMM_BN)
+
+namespace gemm {
+
+DEV unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+DEV void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+DEV void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+DEV bool mbar_test(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait: false after ~1 s (or as soon as another role aborted)
+DEV bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* abort_flag) {
+    if (mbar_test(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_test(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > 2000000000LL) return false;
+    }
+}
+
+DEV void tma_load_2d(void* dst, const TensorMap* map, unsigned long long* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+DEV void tmem_alloc(unsigned* slot, unsigned cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+DEV void tmem_dealloc(unsigned taddr, unsigned cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+DEV void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+DEV void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+DEV void umma(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc, unsigned idesc, unsigned accumulate) {
+#if GEMM_ESIZE == 2
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+#else
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+#endif
+}
+// arrives on `bar` when every tcgen05.mma issued so far by this thread has completed
+DEV void umma_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// shared-memory matrix descriptor: 128-byte swizzle, 1024-byte groups of 8 rows
+//   K-major operand (A):  rows = M, a row holds GEMM_BK elements (128 bytes); SBO = 1024 between 8-row groups
+//   MN-major operand (B): rows = K, a row holds 128 bytes of N; SBO = 1024 between 8-row K groups,
+//                         LBO = bytes between 128-byte-wide N panels
+DEV unsigned long long smem_desc(unsigned addr, unsigned lbo_bytes, unsigned sbo_bytes) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr & 0x3FFFF) >> 4);
+    d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (unsigned long long)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= 1ull << 46;          // descriptor version of this architecture
+    d |= 2ull << 61;          // SWIZZLE_128B
+    return d;
+}
+
+DEV void tmem_ld32(unsigned taddr, float* v) {
+    unsigned r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// two fp32 -> packed bf16x2, round to nearest even (lo in the low half)
+DEV unsigned pack_bf16x2(float lo, float hi) {
+    unsigned r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+DEV float bf16_to_f32(unsigned short b) { return __uint_as_float(((unsigned)b) << 16); }
+
+}  // namespace gemm
+
+extern "C" __global__ void __launch_bounds__(GEMM_THREADS, 1)
+dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ TensorMap tmB,
+                 const __grid_constant__ TensorMap tmAlo, const __grid_constant__ TensorMap tmBlo,
+                 const __grid_constant__ GemmP p) {
+    using namespace gemm;
+    extern __shared__ unsigned char smem_raw[];
+    // tiles need 1024-byte alignment for the 128-byte swizzle pattern
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<unsigned long long>(smem_raw) + 1023) & ~1023ull);
+    __shared__ __align__(8) unsigned long long full_bar[GEMM_STAGES];
+    __shared__ __align__(8) unsigned long long empty_bar[GEMM_STAGES];
+    __shared__ __align__(8) unsigned long long accum_bar;
+    __shared__ unsigned tmem_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long m0 = (long long)blockIdx.y * GEMM_BM, n0 = (long long)blockIdx.x * GEMM_BN;
+    const int num_kb = (int)((p.K + GEMM_BK - 1) / GEMM_BK);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < GEMM_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(&accum_bar, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) tmem_alloc(&tmem_slot, GEMM_TMEM_COLS);
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const unsigned tmem_base = tmem_slot;
+
+    if (warp == 4 && lane == 0) {
+        // ------------------------------------------------------------ TMA producer
+        for (int kb = 0; kb < num_kb; ++kb) {
+            const int s = kb % GEMM_STAGES;
+            const unsigned parity = (unsigned)((kb / GEMM_STAGES) & 1);
+            if (!mbar_wait(&empty_bar[s], parity ^ 1u, &abort_flag)) { atomicExch(p.err, 1); abort_flag = 1; break; }
+            unsigned char* st = tiles + (size_t)s * GEMM_STAGE_BYTES;
+            mbar_expect_tx(&full_bar[s], GEMM_STAGE_BYTES);
+            tma_load_2d(st, &tmA, &full_bar[s], kb * GEMM_BK, (int)m0);
+            unsigned char* bt = st + GEMM_A_TILE_BYTES;
+#if GEMM_B_KMAJOR
+            tma_load_2d(bt, &tmB, &full_bar[s], kb * GEMM_BK, (int)n0);
+#else
+#pragma unroll
+            for (int j = 0; j < GEMM_B_ATOMS; ++j)
+                tma_load_2d(bt + j * GEMM_B_ATOM_BYTES, &tmB, &full_bar[s], (int)n0 + j * GEMM_SWIZZLE_ELEMS, kb * GEMM_BK);
+#endif
+#if GEMM_SPLIT
+            unsigned char* alo = bt + GEMM_B_TILE_BYTES;
+            tma_load_2d(alo, &tmAlo, &full_bar[s], kb * GEMM_BK, (int)m0);
+            unsigned char* blo = alo + GEMM_A_TILE_BYTES;
+#if GEMM_B_KMAJOR
+            tma_load_2d(blo, &tmBlo, &full_bar[s], kb * GEMM_BK, (int)n0);
+#else
+#pragma unroll
+            for (int j = 0; j < GEMM_B_ATOMS; ++j)
+                tma_load_2d(blo + j * GEMM_B_ATOM_BYTES, &tmBlo, &full_bar[s], (int)n0 + j * GEMM_SWIZZLE_ELEMS, kb * GEMM_BK);
+#endif
+#endif
+        }
+    } else if (warp == 5 && lane == 0) {
+        // ------------------------------------------------------------ MMA issuer
+        bool ok = true;
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+            const int s = kb % GEMM_STAGES;
+            const unsigned parity = (unsigned)((kb / GEMM_STAGES) & 1);
+            if (!mbar_wait(&full_bar[s], parity, &abort_flag)) { atomicExch(p.err, 2); abort_flag = 1; ok = false; break; }
+            fence_after_sync();
+            const unsigned a_addr = smem_u32(tiles + (size_t)s * GEMM_STAGE_BYTES);
+            const unsigned b_addr = a_addr + GEMM_A_TILE_BYTES;
+#pragma unroll
+            for (int k = 0; k < GEMM_BK / GEMM_UMMA_K; ++k) {
+                // A: 32 bytes further along its 128-byte rows; B: GEMM_UMMA_K rows (128 bytes each) further down
+                const unsigned long long ad = smem_desc(a_addr + k * 32, 0, 1024);
+#if GEMM_B_KMAJOR
+                const unsigned long long bd = smem_desc(b_addr + k * 32, 0, 1024);
+#else
+                const unsigned long long bd = smem_desc(b_addr + k * GEMM_UMMA_K * 128, GEMM_B_ATOM_BYTES, 1024);
+#endif
+                umma(tmem_base, ad, bd, GEMM_IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+#if GEMM_SPLIT
+                const unsigned alo_addr = b_addr + GEMM_B_TILE_BYTES;
+                const unsigned blo_addr = alo_addr + GEMM_A_TILE_BYTES;
+                const unsigned long long ald = smem_desc(alo_addr + k * 32, 0, 1024);
+#if GEMM_B_KMAJOR
+                const unsigned long long bld = smem_desc(blo_addr + k * 32, 0, 1024);
+#else
+                const unsigned long long bld = smem_desc(blo_addr + k * GEMM_UMMA_K * 128, GEMM_B_ATOM_BYTES, 1024);
+#endif
+                umma(tmem_base, ald, bd, GEMM_IDESC, 1u);    // a_lo * b_hi
+                umma(tmem_base, ad, bld, GEMM_IDESC, 1u);    // a_hi * b_lo
+#endif
+            }
+            umma_commit(&empty_bar[s]);       // the stage is free once these MMAs have read it
+        }
+        if (ok) umma_commit(&accum_bar);      // the accumulator is complete
+    } else if (warp < 4) {
+        // ------------------------------------------------------------ epilogue
+        bool ok = true;
+        if (num_kb > 0) ok = mbar_wait(&accum_bar, 0, &abort_flag);
+        if (!ok) { if (lane == 0) atomicExch(p.err, 3); abort_flag = 1; }
+        if (ok) {
+            fence_after_sync();
+            const long long row = m0 + warp * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < GEMM_BN; c += 32) {
+                float acc[32];
+                if (num_kb > 0) {
+                    tmem_ld32(tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)c, acc);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[i] = 0.0f;
+                }
+                const long long col0 = n0 + c;
+                if (row < p.M && col0 < p.N) {
+                    const int nvalid = (p.N - col0) < 32 ? (int)(p.N - col0) : 32;
+                    EPILOGUE_CHUNK(row, col0, acc, nvalid)
+                }
+            }
+        }
+    }
+    // ---------------------------------------------------------------- teardown
+    fence_before_sync();
+    __syncthreads();
+    if (abort_flag) {
+        // let copies that were already issued land before the shared memory goes away
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) { }
+        __syncthreads();
+    }
+    if (warp == 5) {
+        fence_after_sync();
+        tmem_dealloc(tmem_base, GEMM_TMEM_COLS);
+    }
+}

@@ -46,6 +46,11 @@ bool parse_dtype(const std::string& s, DType* out) {
     return false;   // bf16 is a GEMM operand type only, never an IR value type
 }
 
+bool parse_arg_dtype(const std::string& s, DType* out) {
+    if (s == "bf16") { *out = BF16; return true; }
+    return parse_dtype(s, out);
+}
+
 bool parse_value_ref(const std::string& s, int* out) {
     if (s.size() < 2 || s[0] != 'v') return false;
     for (size_t i = 1; i < s.size(); ++i) if (s[i] < '0' || s[i] > '9') return false;
@@ -139,12 +144,13 @@ bool parse_program(const std::string& text, Program* out, std::string* err) {
         if (t[0] == "arg") {
             int idx;
             ArgDecl a;
-            if (t.size() != 4 || !parse_int(t[1], &idx) || !parse_dtype(t[2], &a.dtype) ||
+            if (t.size() != 4 || !parse_int(t[1], &idx) || !parse_arg_dtype(t[2], &a.dtype) ||
                 (t[3] != "E" && t[3] != "R"))
                 return fail("expected 'arg <i> <dtype> <E|R>'");
             if (idx != (int)p.args.size()) return fail("args must be declared densely in order");
             if (!p.stmts.empty()) return fail("args must precede statements");
             a.elem_level = t[3] == "E";
+            if (a.dtype == BF16) p.has_bf16 = true;
             p.args.push_back(a);
             continue;
         }
@@ -180,7 +186,7 @@ bool parse_program(const std::string& text, Program* out, std::string* err) {
             s.in.push_back(v);
             s.kind = x ? S_STX : S_ST;
             s.dtype = p.args[s.arg].dtype;
-            if (p.stmts[p.value_stmt[v]].dtype != s.dtype)
+            if (p.stmts[p.value_stmt[v]].dtype != (s.dtype == BF16 ? F32 : s.dtype))
                 return fail("stored value type differs from the arg's type (insert a cast)");
             p.args[s.arg].written = true;
             if (s.aop != A_ASSIGN) p.args[s.arg].read = true;
@@ -199,7 +205,8 @@ bool parse_program(const std::string& text, Program* out, std::string* err) {
             if ((int)t.size() != (x ? 5 : 4)) return fail("malformed load");
             if (!parse_int(t[3], &s.arg) || s.arg < 0 || s.arg >= (int)p.args.size())
                 return fail("load from unknown arg");
-            if (p.args[s.arg].dtype != s.dtype) return fail("load type differs from the arg's type");
+            if ((p.args[s.arg].dtype == BF16 ? F32 : p.args[s.arg].dtype) != s.dtype)
+                return fail("load type differs from the arg's type");
             p.args[s.arg].read = true;
             if (x) {
                 int vi;
@@ -210,6 +217,11 @@ bool parse_program(const std::string& text, Program* out, std::string* err) {
                 p.has_indirect = true;
             }
             s.kind = x ? S_LDX : S_LD;
+        } else if (k == "acc") {
+            if (t.size() != 3 || s.dtype != F32) return fail("expected 'v<k> f32 acc'");
+            if (p.nreduce != 0 || p.rank != 2) return fail("'acc' needs 'space 2 0'");
+            s.kind = S_ACC;
+            p.has_acc = true;
         } else if (k == "sc") {
             if (t.size() != 4 || !parse_int(t[3], &s.arg) || s.arg < 0 || s.arg >= (int)p.scalars.size())
                 return fail("unknown scalar");
@@ -284,6 +296,10 @@ bool parse_program(const std::string& text, Program* out, std::string* err) {
             case S_LDX:
                 s.elem = (p.nreduce == 0 ? true : p.args[s.arg].elem_level) || src(0).elem;
                 s.stage = src(0).stage;
+                break;
+            case S_ACC:
+                s.elem = true;
+                s.stage = 0;
                 break;
             case S_SC:
             case S_CONST:

@@ -8,13 +8,17 @@
 //   dali-ir 1
 //   space <rank> <nreduce>      iteration space; reductions fold the innermost
 //                               <nreduce> dims (0 = pure elementwise map)
-//   arg <i> <f32|f64|i32> <E|R> i-th buffer.  E: indexed by the whole space,
+//   arg <i> <f32|f64|i32|bf16> <E|R>  (bf16: storage type of GEMM epilogue operands; loads
+//                               yield f32, stores take f32)
+//                               i-th buffer.  E: indexed by the whole space,
 //                               R: indexed by the outer (non-reduced) dims only
 //   scalar <j> <dtype>          j-th run-time scalar (value read at launch)
 //   v<k> <dtype> ld <arg>                   load at the current index
 //   v<k> <dtype> ldx <arg> v<i>             indirect load: adds v<i> * lead-stride
 //   v<k> <dtype> sc <j>                     scalar argument
 //   v<k> <dtype> const <literal>
+//   v<k> f32     acc                        the GEMM accumulator at (row, col); only in
+//                                           epilogue programs run by dalib200_gemm_fused
 //   v<k> <dtype> op <functor> v<a> [v<b>]   functor names as dali/array/functor.h
 //   v<k> <dtype> cast v<a>                  static_cast (functor::cast)
 //   v<k> <dtype> red <sum|prod|max|min> v<a>
@@ -41,7 +45,7 @@ const char* dtype_ir_name(DType t);
 const char* dtype_c_name(DType t);
 int dtype_size(DType t);
 
-enum StmtKind { S_LD, S_LDX, S_SC, S_CONST, S_OP, S_CAST, S_RED, S_ARGRED, S_ST, S_STX };
+enum StmtKind { S_LD, S_LDX, S_SC, S_CONST, S_OP, S_CAST, S_RED, S_ARGRED, S_ST, S_STX, S_ACC };
 enum AssignOp { A_ASSIGN, A_ADD, A_SUB, A_MUL, A_DIV };
 
 struct ArgDecl {
@@ -76,6 +80,8 @@ struct Program {
     int max_stage = 0;             // deepest reduction nesting
     int n_reductions = 0;
     bool has_indirect = false;
+    bool has_acc = false;          // reads the GEMM accumulator: an epilogue program
+    bool has_bf16 = false;
     std::string text;              // canonical source text (for collision checks)
 };
 

@@ -77,6 +77,8 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
                  const int64_t* const* strides, int n_arrays,
                  const void* const* scalars, int n_scalars,
                  LaunchPlan* plan, std::string* err) {
+    if (p.has_acc) { *err = "launch: this program reads a GEMM accumulator; run it through dalib200_gemm_fused"; return false; }
+    if (p.has_bf16) { *err = "launch: bf16 operands exist only in GEMM epilogue programs"; return false; }
     if (rank != p.rank) { *err = "launch: space rank differs from the program's"; return false; }
     if (n_arrays != (int)p.args.size()) { *err = "launch: wrong number of arrays"; return false; }
     if (n_scalars != (int)p.scalars.size()) { *err = "launch: wrong number of scalars"; return false; }

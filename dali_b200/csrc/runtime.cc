@@ -181,8 +181,8 @@ static std::string kernel_key(uint64_t hash, const Variant& v) {
     return k.str();
 }
 
-// Returns the cubin for (hash, variant): memory -> disk -> NVRTC.
-static bool get_image(uint64_t hash, const Program& p, const Variant& v, const std::string& key,
+// Returns the cubin for `key`: memory -> disk -> NVRTC (source from `make_source`).
+static bool get_image(const std::string& key, const std::string& what, SourceFn make_source, void* ctx,
                       const KernelImage** out) {
     State& s = S();
     bool force = always_recompile_locked() && !s.recompiled_once[key];
@@ -204,9 +204,8 @@ static bool get_image(uint64_t hash, const Program& p, const Variant& v, const s
             img.cubin.clear();   // truncated / corrupt file: fall through and rebuild it
         }
     }
-    std::string body, err;
-    if (!generate_kernel(p, v, &body, &err)) { set_error("codegen: " + err); return false; }
-    std::string src = std::string(kPrelude) + "\n" + body;
+    std::string src, err;
+    if (!make_source(ctx, &src, &err)) { set_error("codegen: " + err); return false; }
     std::string log;
     make_dirs(dir);
     { std::ofstream f(base + ".cu"); f << src; }
@@ -214,7 +213,7 @@ static bool get_image(uint64_t hash, const Program& p, const Variant& v, const s
     { std::ofstream f(base + ".log"); f << log; }
     ++s.n_compiles;
     if (!ok) {
-        set_error("NVRTC failed for kernel " + key + " (" + v.key() + "), source " + base + ".cu:\n" + log);
+        set_error("NVRTC failed for kernel " + key + " (" + what + "), source " + base + ".cu:\n" + log);
         return false;
     }
     {
@@ -227,7 +226,15 @@ static bool get_image(uint64_t hash, const Program& p, const Variant& v, const s
     s.recompiled_once[key] = true;
     s.images[key] = img;
     *out = &s.images[key];
-    (void)hash;
+    return true;
+}
+
+struct ExprSourceCtx { const Program* p; const Variant* v; };
+static bool expr_source(void* ctx, std::string* src, std::string* err) {
+    ExprSourceCtx* c = static_cast<ExprSourceCtx*>(ctx);
+    std::string body;
+    if (!generate_kernel(*c->p, *c->v, &body, err)) return false;
+    *src = std::string(kPrelude) + "\n" + body;
     return true;
 }
 
@@ -295,7 +302,8 @@ static int get_scratch_locked(int device, void* stream, size_t bytes, size_t cou
     return DALIB200_OK;
 }
 
-static int get_function_locked(int device, const std::string& key, const KernelImage& img, CUfunction* fn) {
+static int get_function_locked(int device, const std::string& key, const KernelImage& img, CUfunction* fn,
+                               const char* entry = "dali_kernel") {
     DeviceState& d = S().devices[device];
     auto it = d.functions.find(key);
     if (it != d.functions.end()) { *fn = it->second; return DALIB200_OK; }
@@ -303,7 +311,7 @@ static int get_function_locked(int device, const std::string& key, const KernelI
     CUmodule mod;
     CUresult r = g_drv.ModuleLoadData(&mod, img.cubin.data());
     if (r != CUDA_SUCCESS) { set_error("cuModuleLoadData(" + key + "): " + cu_err(r)); return DALIB200_ERR_CUDA; }
-    r = g_drv.ModuleGetFunction(fn, mod, "dali_kernel");
+    r = g_drv.ModuleGetFunction(fn, mod, entry);
     if (r != CUDA_SUCCESS) { set_error("cuModuleGetFunction: " + cu_err(r)); return DALIB200_ERR_CUDA; }
     d.modules.push_back(mod);
     d.functions[key] = *fn;
@@ -336,7 +344,8 @@ static int do_launch(uint64_t hash, int device, void* stream, const int64_t* spa
     tl_variant = plan.describe();
     const std::string key = kernel_key(hash, plan.variant);
     const KernelImage* img = nullptr;
-    if (!get_image(hash, p, plan.variant, key, &img)) return DALIB200_ERR_COMPILE;
+    ExprSourceCtx ctx{&p, &plan.variant};
+    if (!get_image(key, plan.variant.key(), expr_source, &ctx, &img)) return DALIB200_ERR_COMPILE;
     if (cubin_size) *cubin_size = img->cubin.size();
     if (compile_only) return DALIB200_OK;
 
@@ -362,6 +371,86 @@ static int do_launch(uint64_t hash, int device, void* stream, const int64_t* spa
     return DALIB200_OK;
 }
 
+bool find_program(uint64_t hash, Program* out) {
+    State& s = S();
+    std::lock_guard<std::mutex> g(s.mu);
+    auto it = s.programs.find(hash);
+    if (it == s.programs.end()) return false;
+    *out = it->second;
+    return true;
+}
+
+const char* device_prelude() { return kPrelude; }
+
+int acquire_kernel(int device, const std::string& key, const char* entry_name, SourceFn make_source, void* ctx,
+                   void** function, size_t* cubin_size) {
+    State& s = S();
+    std::lock_guard<std::mutex> g(s.mu);
+    const KernelImage* img = nullptr;
+    if (!get_image(key, entry_name, make_source, ctx, &img)) return DALIB200_ERR_COMPILE;
+    if (cubin_size) *cubin_size = img->cubin.size();
+    if (device < 0) return DALIB200_OK;
+    int rc = check_device(device);
+    if (rc != DALIB200_OK) return rc;
+    CUfunction fn;
+    rc = get_function_locked(device, key, *img, &fn, entry_name);
+    if (rc != DALIB200_OK) return rc;
+    *function = (void*)fn;
+    return DALIB200_OK;
+}
+
+void* driver_entry(const char* name) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint(name, &fn, cudaEnableDefault, &q) != cudaSuccess) return nullptr;
+    return fn;
+}
+
+int device_ordinal(int device) {
+    State& s = S();
+    std::lock_guard<std::mutex> g(s.mu);
+    if (device < 0 || device >= (int)s.devices.size()) return -1;
+    return s.devices[device].ordinal;
+}
+
+void count_launch() {
+    State& s = S();
+    std::lock_guard<std::mutex> g(s.mu);
+    ++s.n_launches;
+}
+
+int launch_function(int device, void* function, unsigned gx, unsigned gy, unsigned threads, unsigned smem_bytes,
+                    void* stream, void** params) {
+    int ord = device_ordinal(device);
+    if (ord < 0) { set_error("device index out of range"); return DALIB200_ERR_INVALID; }
+    CUDA_OK(cudaSetDevice(ord));
+    static CUresult (*set_attr)(CUfunction, CUfunction_attribute, int) = nullptr;
+    if (!set_attr) set_attr = reinterpret_cast<CUresult (*)(CUfunction, CUfunction_attribute, int)>(driver_entry("cuFuncSetAttribute"));
+    if (smem_bytes > 48 * 1024) {
+        if (!set_attr) { set_error("cuFuncSetAttribute unavailable"); return DALIB200_ERR_CUDA; }
+        CUresult r = set_attr((CUfunction)function, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)smem_bytes);
+        if (r != CUDA_SUCCESS) { set_error("cuFuncSetAttribute(max dynamic smem): " + cu_err(r)); return DALIB200_ERR_CUDA; }
+    }
+    CUresult r = g_drv.LaunchKernel((CUfunction)function, gx, gy, 1, threads, 1, 1, smem_bytes, (CUstream)stream, params, nullptr);
+    if (r != CUDA_SUCCESS) { set_error("cuLaunchKernel: " + cu_err(r)); return DALIB200_ERR_CUDA; }
+    count_launch();
+    return DALIB200_OK;
+}
+
+int* gemm_error_word(int device) {
+    State& s = S();
+    std::lock_guard<std::mutex> g(s.mu);
+    static int* words[64] = {nullptr};
+    if (device < 0 || device >= (int)s.devices.size() || device >= 64) return nullptr;
+    if (!words[device]) {
+        cudaSetDevice(s.devices[device].ordinal);
+        if (cudaMalloc((void**)&words[device], 256) != cudaSuccess) return nullptr;
+        cudaMemset(words[device], 0, 256);
+        cudaDeviceSynchronize();
+    }
+    return words[device];
+}
+
 }  // namespace dalib
 
 namespace dalib {
@@ -369,6 +458,7 @@ cudaError_t gemm_simt(cudaStream_t stream, int dtype, int64_t m, int64_t n, int6
                       int64_t acs, const void* b, int64_t brs, int64_t bcs, void* c, int64_t crs, int64_t ccs,
                       double alpha, double beta);
 static thread_local std::string tl_gemm_kernel;
+const std::string& last_gemm_variant();
 }  // namespace dalib
 
 using namespace dalib;
@@ -587,6 +677,7 @@ int dalib200_gemm(int device, void* stream, int dtype, int64_t m, int64_t n, int
 }
 
 size_t dalib200_last_gemm_kernel(char* buffer, size_t capacity) {
+    if (!last_gemm_variant().empty() && tl_gemm_kernel != "simt") tl_gemm_kernel = last_gemm_variant();
     if (buffer && capacity) {
         size_t n = tl_gemm_kernel.size() < capacity - 1 ? tl_gemm_kernel.size() : capacity - 1;
         std::memcpy(buffer, tl_gemm_kernel.data(), n);

@@ -43,5 +43,26 @@ bool nvrtc_compile(const std::string& source, const std::string& name,
 
 uint64_t fnv1a(const std::string& s, uint64_t seed = 1469598103934665603ull);
 
+// ---- services of runtime.cc for the other translation units ------------------------
+// Copy of the program registered under `hash` (false if unknown).
+bool find_program(uint64_t hash, Program* out);
+// The device prelude text (functors, reducers) that precedes every generated kernel.
+const char* device_prelude();
+// Compiles (memory -> disk -> NVRTC) the kernel identified by `key`; `make_source` is
+// only called on a miss.  With device >= 0 also loads it there and returns the function
+// handle (a CUfunction) in *function.  Returns a dalib200_status.
+typedef bool (*SourceFn)(void* ctx, std::string* source, std::string* err);
+int acquire_kernel(int device, const std::string& key, const char* entry_name, SourceFn make_source, void* ctx,
+                   void** function, size_t* cubin_size);
+// cuLaunchKernel / cuFuncSetAttribute(max dynamic shared memory) on the bound device.
+int launch_function(int device, void* function, unsigned gx, unsigned gy, unsigned threads, unsigned smem_bytes,
+                    void* stream, void** params);
+// Driver entry point by name (nullptr if unavailable).
+void* driver_entry(const char* name);
+int device_ordinal(int device);            // CUDA ordinal of bound device, -1 if not bound
+void count_launch();
+// One int per device that tensor-core kernels raise when a bounded wait expires.
+int* gemm_error_word(int device);
+
 }  // namespace dalib
 #endif

@@ -26,13 +26,18 @@ class IRBuilder:
         return k
 
     def ld(self, arg):
-        return self._val(self.args[arg][0], "ld %d" % arg)
+        dt = self.args[arg][0]
+        return self._val("f32" if dt == "bf16" else dt, "ld %d" % arg)
 
     def ldx(self, arg, index):
         return self._val(self.args[arg][0], "ldx %d v%d" % (arg, index))
 
     def sc(self, j):
         return self._val(self.scalars[j], "sc %d" % j)
+
+    def acc(self):
+        """The GEMM accumulator at (row, col) -- epilogue programs only."""
+        return self._val("f32", "acc")
 
     def const(self, dtype, literal):
         return self._val(dtype, "const %s" % literal)
@@ -108,4 +113,20 @@ def lstm_gating_ir():
     cnew = b.op("add", b.op("eltmul", f, b.ld(c)), b.op("eltmul", i, g))
     b.st(cn, cnew)
     b.st(hn, b.op("eltmul", o, b.op("tanh", cnew)))
+    return b.text()
+
+
+def gemm_bias_tanh_ir(out_dtype="bf16"):
+    """tanh(acc + bias[col]) as a GEMM epilogue: args (out [m,n], bias broadcast over rows)."""
+    b = IRBuilder(2, 0)
+    out, bias = b.arg(out_dtype), b.arg("f32")
+    b.st(out, b.op("tanh", b.op("add", b.acc(), b.ld(bias))))
+    return b.text()
+
+
+def gemm_store_ir(out_dtype="f32", op="assign"):
+    """Plain product: args (out [m,n])."""
+    b = IRBuilder(2, 0)
+    out = b.arg(out_dtype)
+    b.st(out, b.acc(), op)
     return b.text()

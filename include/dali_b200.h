@@ -161,6 +161,52 @@ int dalib200_gemm(int device, void* stream, int dtype,
                   void* c, int64_t c_row_stride, int64_t c_col_stride,
                   double alpha, double beta);
 
+/* Tensor-core GEMM (tcgen05.mma, accumulator in tensor memory, operand tiles
+ * staged by TMA) with the elementwise expression that consumes the product
+ * spliced in as its epilogue, so the product never goes to memory on its own:
+ *
+ *     acc[m,n] = A[m,k] . B[k,n]          fp32 accumulation
+ *     epilogue(acc, extra operands) -> destination(s)
+ *
+ * A and B are row-major with row pitches lda / ldb (elements), 16-byte aligned.
+ *   ab_dtype DALIB200_BF16: one bf16 pass.
+ *   ab_dtype DALIB200_F32 : three TF32 passes on operands split into a high
+ *     and a low part (fp32 parity with an fp32 GEMM).  With a_lo = b_lo = NULL the
+ *     parts are made in pool temporaries (recycled in stream order; k and n must
+ *     be multiples of 4).  To reuse them across calls (weights), pass the parts
+ *     made by dalib200_gemm_split_tf32: a / a_lo = parts of A, [m,k] with pitch lda;
+ *     b / b_lo = parts of B TRANSPOSED, [n,k] with pitch ldb.
+ * `epilogue_hash` names a program registered with dalib200_compile that is
+ * 'space 2 0' over [m, n] and reads the accumulator through `acc`; its arrays,
+ * offsets, strides ((row, col) element strides per array, NULL = contiguous
+ * [m,n]) and scalars are passed as for dalib200_launch.  bf16 epilogue arrays
+ * are declared 'arg i bf16 E'.  device < 0 only compiles.
+ * Replaces cublasSgemm plus the separate kernel the reference runs on the
+ * product (dali/array/gemm/cublas_gemm.cu:157-178, dali/array/op/dot.h:7).
+ * Returns DALIB200_ERR_UNSUPPORTED for layouts TMA cannot address (use
+ * dalib200_gemm and dalib200_launch then). */
+int dalib200_gemm_fused(int device, void* stream, int ab_dtype,
+                        int64_t m, int64_t n, int64_t k,
+                        const void* a, int64_t lda, const void* b, int64_t ldb,
+                        const void* a_lo, const void* b_lo,
+                        uint64_t epilogue_hash,
+                        void* const* array_data, const int64_t* offsets,
+                        const int64_t* const* strides, int n_arrays,
+                        const void* const* scalars, int n_scalars);
+
+/* hi = x with the 13 low mantissa bits cleared (what TF32 keeps), lo = x - hi,
+ * for a rows x cols fp32 matrix with row pitch ld; hi / lo are written tight:
+ * [rows, cols], or with transpose != 0 [cols, rows] (the form the B operand is
+ * consumed in).  16-byte aligned pointers, cols and ld multiples of 4 (rows too
+ * when transposing). */
+int dalib200_gemm_split_tf32(int device, void* stream, const float* x,
+                             int64_t rows, int64_t cols, int64_t ld, int transpose, float* hi, float* lo);
+
+/* Synchronises `device` and reads the word tensor-core kernels raise when one of
+ * their bounded waits expires (0 = none; 1 producer, 2 MMA issuer, 3 epilogue);
+ * a non-zero word is cleared by the read. */
+int dalib200_gemm_error_flag(int device, int* flag);
+
 /* Name of the GEMM kernel the last dalib200_gemm* call on this thread chose
  * ("simt", "tcgen05.bf16", "tcgen05.tf32x3", ...); for tests and profiles. */
 size_t dalib200_last_gemm_kernel(char* buffer, size_t capacity);
