@@ -293,6 +293,7 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
     key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + "|sm_100a|gemm-2|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" +
                                                      std::to_string(fnv1a(device_prelude())));
     tl_gemm_variant = std::string(bf16 ? "tcgen05.bf16 " : "tcgen05.tf32x3 ") + v.key();
+    note_gemm_kernel(tl_gemm_variant);
     void* fn = nullptr;
     int rc = acquire_kernel(compile_only ? -1 : device, key.str(), "dali_gemm_kernel", gemm_source, &ctx, &fn, nullptr);
     if (rc != DALIB200_OK || compile_only) return rc;

@@ -458,7 +458,7 @@ cudaError_t gemm_simt(cudaStream_t stream, int dtype, int64_t m, int64_t n, int6
                       int64_t acs, const void* b, int64_t brs, int64_t bcs, void* c, int64_t crs, int64_t ccs,
                       double alpha, double beta);
 static thread_local std::string tl_gemm_kernel;
-const std::string& last_gemm_variant();
+void note_gemm_kernel(const std::string& name) { tl_gemm_kernel = name; }
 }  // namespace dalib
 
 using namespace dalib;
@@ -677,7 +677,6 @@ int dalib200_gemm(int device, void* stream, int dtype, int64_t m, int64_t n, int
 }
 
 size_t dalib200_last_gemm_kernel(char* buffer, size_t capacity) {
-    if (!last_gemm_variant().empty() && tl_gemm_kernel != "simt") tl_gemm_kernel = last_gemm_variant();
     if (buffer && capacity) {
         size_t n = tl_gemm_kernel.size() < capacity - 1 ? tl_gemm_kernel.size() : capacity - 1;
         std::memcpy(buffer, tl_gemm_kernel.data(), n);

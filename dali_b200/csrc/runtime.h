@@ -63,6 +63,8 @@ int device_ordinal(int device);            // CUDA ordinal of bound device, -1 i
 void count_launch();
 // One int per device that tensor-core kernels raise when a bounded wait expires.
 int* gemm_error_word(int device);
+// Remembers, per thread, which GEMM kernel served the last call (dalib200_last_gemm_kernel).
+void note_gemm_kernel(const std::string& name);
 
 }  // namespace dalib
 #endif

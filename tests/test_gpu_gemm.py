@@ -1,0 +1,182 @@
+"""dalib200_gemm (CUDA-core kernel for any layout) and dalib200_gemm_fused
+(tcgen05 / TMEM kernel with the spliced epilogue) against the CPU oracle.
+
+Tolerances: fp32 products |gpu - fp64| <= 1e-5 * (|A| . |B|) elementwise (the
+3xTF32 split measures ~2e-6); bf16 inputs are exact in fp32 products, so the
+fp32-accumulated result is compared at 1e-5 * (|A| . |B|) too, and bf16 outputs
+at bf16 rounding (2^-8 relative); int32 bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+import dali_oracle as oracle
+from dali_b200.ir import IRBuilder, gemm_bias_tanh_ir, gemm_store_ir
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).cuda()
+
+
+def host(t):
+    torch.cuda.synchronize()
+    return t.float().cpu().numpy() if t.dtype == torch.bfloat16 else t.cpu().numpy()
+
+
+def to_bf16(x):
+    """fp32 -> nearest-even bf16, returned as fp32 values and as a torch bf16 tensor."""
+    t = torch.from_numpy(x).bfloat16()
+    return t.float().numpy(), t.cuda()
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64, np.int32])
+def test_simt_gemm_layouts_and_accumulate(lib, dtype):
+    rng = np.random.default_rng(0)
+    m, n, k = 37, 29, 53
+    if dtype == np.int32:
+        a, b = rng.integers(-9, 9, (m, k)).astype(dtype), rng.integers(-9, 9, (k, n)).astype(dtype)
+    else:
+        a, b = rng.standard_normal((m, k)).astype(dtype), rng.standard_normal((k, n)).astype(dtype)
+    code = {np.float32: 0, np.float64: 1, np.int32: 2}[dtype]
+    want = a.astype(np.float64) @ b.astype(np.float64)
+    tol = dict(rtol=0, atol=0) if dtype == np.int32 else dict(rtol=1e-5 if dtype == np.float32 else 1e-12, atol=1e-5 if dtype == np.float32 else 1e-12)
+    c = torch.zeros((m, n), dtype=torch.from_numpy(a).dtype, device="cuda")
+    lib.gemm(code, m, n, k, dev(a), (k, 1), dev(b), (n, 1), c, (n, 1))
+    np.testing.assert_allclose(host(c), want, **tol)
+    at, bt = np.ascontiguousarray(a.T), np.ascontiguousarray(b.T)          # transposed views
+    lib.gemm(code, m, n, k, dev(at), (1, m), dev(bt), (1, k), c, (n, 1))
+    np.testing.assert_allclose(host(c), want, **tol)
+    big = np.zeros((2 * m, 3 * k), dtype)                                   # strided view
+    big[::2, ::3] = a
+    lib.gemm(code, m, n, k, dev(big), (2 * 3 * k, 3), dev(b), (n, 1), c, (n, 1))
+    np.testing.assert_allclose(host(c), want, **tol)
+    lib.gemm(code, m, n, k, dev(a), (k, 1), dev(b), (n, 1), c, (n, 1), alpha=-1.0, beta=1.0)   # c -= a.b
+    np.testing.assert_allclose(host(c), np.zeros((m, n)), atol=1e-4)
+    ct = torch.zeros((n, m), dtype=c.dtype, device="cuda")                  # transposed destination
+    lib.gemm(code, m, n, k, dev(a), (k, 1), dev(b), (n, 1), ct, (1, m))
+    np.testing.assert_allclose(host(ct).T, want, **tol)
+    assert lib.last_gemm_kernel() == "simt"
+
+
+@pytest.mark.parametrize("shape", [(128, 64, 64), (128, 256, 512), (200, 328, 136), (256, 4096, 1024), (1024, 1024, 2048)])
+def test_tcgen05_fp32_product_matches_fp64_oracle(lib, shape):
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + k)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    b = (rng.standard_normal((k, n)) * 0.02).astype(np.float32)
+    out = torch.full((m, n), -7.0, device="cuda")
+    lib.gemm_fused(0, m, n, k, dev(a), k, dev(b), n, lib.compile(gemm_store_ir("f32")), [out])
+    got = host(out)
+    assert lib.gemm_error_flag() == 0
+    assert lib.last_gemm_kernel().startswith("tcgen05.tf32x3")
+    want = a.astype(np.float64) @ b.astype(np.float64)
+    bound = np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)
+    assert np.all(np.abs(got - want) <= 1e-5 * bound), float(np.max(np.abs(got - want) / bound))
+    if m * n * k <= 128 * 256 * 512:
+        np.testing.assert_allclose(got, oracle.gemm(a, b), rtol=1e-5, atol=1e-5 * float(bound.max()))
+
+
+def test_tcgen05_presplit_weights_and_accumulating_epilogue(lib):
+    """x.Wx then += h.Wh with weights split once (the LSTM pattern)."""
+    rng = np.random.default_rng(5)
+    B, H = 64, 256
+    x, h = (rng.standard_normal((B, H)).astype(np.float32) for _ in range(2))
+    Wx, Wh = ((rng.standard_normal((H, 4 * H)) * 0.02).astype(np.float32) for _ in range(2))
+    d = {k: dev(v) for k, v in dict(x=x, h=h, Wx=Wx, Wh=Wh).items()}
+    parts = {}
+    for name, rows, cols, tr in (("x", B, H, False), ("h", B, H, False), ("Wx", H, 4 * H, True), ("Wh", H, 4 * H, True)):
+        hi, lo = torch.empty(rows * cols, device="cuda"), torch.empty(rows * cols, device="cuda")
+        lib.gemm_split_tf32(d[name], rows, cols, cols, hi, lo, transpose=tr)
+        parts[name] = (hi, lo)
+    hi, lo = (host(t) for t in parts["Wx"])
+    np.testing.assert_array_equal((hi + lo).reshape(4 * H, H), Wx.T)                    # the split is exact
+    assert np.all((hi.view(np.uint32) & 0x1FFF) == 0)
+    gates = torch.zeros((B, 4 * H), device="cuda")
+    lib.gemm_fused(0, B, 4 * H, H, parts["x"][0], H, parts["Wx"][0], H, lib.compile(gemm_store_ir("f32")), [gates],
+                   a_lo=parts["x"][1], b_lo=parts["Wx"][1])
+    lib.gemm_fused(0, B, 4 * H, H, parts["h"][0], H, parts["Wh"][0], H, lib.compile(gemm_store_ir("f32", "add")), [gates],
+                   a_lo=parts["h"][1], b_lo=parts["Wh"][1])
+    got = host(gates)
+    assert lib.gemm_error_flag() == 0
+    want = x.astype(np.float64) @ Wx + h.astype(np.float64) @ Wh
+    bound = np.abs(x).astype(np.float64) @ np.abs(Wx) + np.abs(h).astype(np.float64) @ np.abs(Wh)
+    assert np.all(np.abs(got - want) <= 1e-5 * bound)
+
+
+@pytest.mark.parametrize("shape", [(128, 64, 64), (200, 328, 136), (512, 2048, 1024), (2048, 2048, 512)])
+def test_tcgen05_bf16_product_and_fused_bias_tanh(lib, shape):
+    m, n, k = shape
+    rng = np.random.default_rng(k)
+    a32, a16 = to_bf16((rng.standard_normal((m, k)) * 0.5).astype(np.float32))
+    b32, b16 = to_bf16((rng.standard_normal((k, n)) * 0.5).astype(np.float32))
+    bias = (rng.standard_normal(n) * 0.1).astype(np.float32)
+    want = a32.astype(np.float64) @ b32.astype(np.float64)
+    bound = np.abs(a32).astype(np.float64) @ np.abs(b32).astype(np.float64)
+    out = torch.full((m, n), -7.0, device="cuda")
+    lib.gemm_fused(3, m, n, k, a16, k, b16, n, lib.compile(gemm_store_ir("f32")), [out])
+    got = host(out)
+    assert lib.gemm_error_flag() == 0 and lib.last_gemm_kernel().startswith("tcgen05.bf16")
+    assert np.all(np.abs(got - want) <= 1e-5 * bound)
+    # config-4 epilogue: tanh(product + bias) stored as bf16; the reference's fp32 path on the same
+    # bf16-rounded inputs is the yardstick, at bf16 output rounding (1e-2 relative allowed, 2^-8 measured)
+    out16 = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    lib.gemm_fused(3, m, n, k, a16, k, b16, n, lib.compile(gemm_bias_tanh_ir("bf16")), [out16, dev(bias)],
+                   strides=[None, [0, 1]])
+    ref = oracle.bias_tanh(want.astype(np.float32), bias)
+    np.testing.assert_allclose(host(out16), ref, rtol=1e-2, atol=4e-3)
+    out32 = torch.zeros((m, n), device="cuda")
+    lib.gemm_fused(3, m, n, k, a16, k, b16, n, lib.compile(gemm_bias_tanh_ir("f32")), [out32, dev(bias)],
+                   strides=[None, [0, 1]])
+    np.testing.assert_allclose(host(out32), ref, rtol=2e-5, atol=2e-5)
+
+
+def test_epilogue_with_strided_destination_scalars_and_residual(lib):
+    """out[:, ::2] = relu(acc * s + residual): column-strided store, runtime scalar, second operand."""
+    rng = np.random.default_rng(11)
+    m, n, k = 256, 192, 128
+    a32, a16 = to_bf16(rng.standard_normal((m, k)).astype(np.float32))
+    b32, b16 = to_bf16(rng.standard_normal((k, n)).astype(np.float32))
+    res = rng.standard_normal((m, n)).astype(np.float32)
+    b = IRBuilder(2, 0)
+    o, r = b.arg("f32"), b.arg("f32")
+    s = b.scalar("f32")
+    b.st(o, b.op("relu", b.op("add", b.op("eltmul", b.acc(), b.sc(s)), b.ld(r))))
+    out = torch.full((m, 2 * n), -1.0, device="cuda")
+    lib.gemm_fused(3, m, n, k, a16, k, b16, n, lib.compile(b.text()), [out, dev(res)], strides=[[2 * n, 2], None],
+                   scalars=[np.float32(0.25)])
+    got = host(out)
+    assert lib.gemm_error_flag() == 0
+    want = np.maximum((a32.astype(np.float64) @ b32) * 0.25 + res, 0)
+    np.testing.assert_allclose(got[:, ::2], want, rtol=1e-5, atol=1e-4)
+    assert np.all(got[:, 1::2] == -1.0)
+
+
+def test_full_size_linearity_property(lib):
+    """Config-4 size: (A . B)[rows] for a few probe rows equals the fp64 product of those rows."""
+    n = 8192
+    g = torch.Generator(device="cuda").manual_seed(1237)
+    A = (torch.randn(n, n, device="cuda", generator=g) * 0.02).bfloat16()
+    B = (torch.randn(n, n, device="cuda", generator=g) * 0.02).bfloat16()
+    bias = torch.randn(n, device="cuda", generator=g) * 0.1
+    out = torch.zeros((n, n), dtype=torch.bfloat16, device="cuda")
+    lib.gemm_fused(3, n, n, n, A, n, B, n, lib.compile(gemm_bias_tanh_ir("bf16")), [out, bias], strides=[None, [0, 1]])
+    torch.cuda.synchronize()
+    assert lib.gemm_error_flag() == 0
+    rows = [0, 1, 127, 128, 4095, 8191]
+    a = A[rows].float().cpu().numpy().astype(np.float64)
+    want = np.tanh(a @ B.float().cpu().numpy().astype(np.float64) + bias.cpu().numpy())
+    np.testing.assert_allclose(out[rows].float().cpu().numpy(), want, rtol=1e-2, atol=4e-3)
+
+
+def test_unsupported_layouts_are_refused_not_faked(lib):
+    from dali_b200 import DaliB200Error
+    x = torch.zeros(64 * 64 + 1, device="cuda")
+    with pytest.raises(DaliB200Error) as e:     # base pointer 4 bytes off a 16-byte boundary
+        lib.gemm_fused(0, 64, 64, 64, x[1:], 64, x, 64, lib.compile(gemm_store_ir("f32")), [x])
+    assert e.value.status == -6
+    with pytest.raises(DaliB200Error):          # epilogue program without 'acc'
+        b = IRBuilder(2, 0)
+        o, i = b.arg("f32"), b.arg("f32")
+        b.st(o, b.ld(i))
+        lib.gemm_fused(0, 64, 64, 64, x, 64, x, 64, lib.compile(b.text()), [x, x])
