@@ -290,7 +290,7 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
     GemmSourceCtx ctx{&prog, choose_variant(bf16, m, n)};
     const GemmVariant& v = ctx.v;
     std::ostringstream key;
-    key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + "|sm_100a|gemm-2|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" +
+    key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + "|sm_100a|gemm-3|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" +
                                                      std::to_string(fnv1a(device_prelude())));
     tl_gemm_variant = std::string(bf16 ? "tcgen05.bf16 " : "tcgen05.tf32x3 ") + v.key();
     note_gemm_kernel(tl_gemm_variant);

@@ -48,7 +48,21 @@ struct GemmP {
 #define GEMM_B_TILE_BYTES (GEMM_B_ATOMS * GEMM_B_ATOM_BYTES)
 #define GEMM_OPERAND_SETS (GEMM_SPLIT ? 2 : 1)
 #define GEMM_STAGE_BYTES (GEMM_OPERAND_SETS * (GEMM_A_TILE_BYTES + GEMM_B_TILE_BYTES))
-#define GEMM_TMEM_COLS (GEMM_BN < 32 ? 32 : GEMM_BN)
+// Accumulators in tensor memory.  The tensor core adds into its fp32 accumulator with
+// truncation, a bias of about half an ulp of the accumulator per tcgen05.mma (measured:
+// 1.5e-5 absolute on O(1) sums after the 384 instructions of a K = 1024 3xTF32 product).
+// For fp32 parity the split path therefore keeps the small correction products
+// (a_lo.b_hi, a_hi.b_lo) in an accumulator of their own and deals the main products round
+// robin over GEMM_NACC accumulators, which the epilogue adds up in fp32 on the CUDA cores.
+#if GEMM_SPLIT
+#define GEMM_NACC 3
+#define GEMM_ACC_SETS (GEMM_NACC + 1)
+#else
+#define GEMM_NACC 1
+#define GEMM_ACC_SETS 1
+#endif
+#define GEMM_TMEM_NEED (GEMM_ACC_SETS * GEMM_BN)
+#define GEMM_TMEM_COLS (GEMM_TMEM_NEED <= 32 ? 32 : GEMM_TMEM_NEED <= 64 ? 64 : GEMM_TMEM_NEED <= 128 ? 128 : GEMM_TMEM_NEED <= 256 ? 256 : 512)
 
 namespace gemm {
 
@@ -233,7 +247,12 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
 #else
                 const unsigned long long bd = smem_desc(b_addr + k * GEMM_UMMA_K * 128, GEMM_B_ATOM_BYTES, 1024);
 #endif
+#if GEMM_SPLIT
+                // main products: accumulator kb % GEMM_NACC (its first use overwrites)
+                umma(tmem_base + (unsigned)((kb % GEMM_NACC) * GEMM_BN), ad, bd, GEMM_IDESC, (kb >= GEMM_NACC || k > 0) ? 1u : 0u);
+#else
                 umma(tmem_base, ad, bd, GEMM_IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+#endif
 #if GEMM_SPLIT
                 const unsigned alo_addr = b_addr + GEMM_B_TILE_BYTES;
                 const unsigned blo_addr = alo_addr + GEMM_A_TILE_BYTES;
@@ -243,8 +262,9 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
 #else
                 const unsigned long long bld = smem_desc(blo_addr + k * GEMM_UMMA_K * 128, GEMM_B_ATOM_BYTES, 1024);
 #endif
-                umma(tmem_base, ald, bd, GEMM_IDESC, 1u);    // a_lo * b_hi
-                umma(tmem_base, ad, bld, GEMM_IDESC, 1u);    // a_hi * b_lo
+                const unsigned corr = tmem_base + (unsigned)(GEMM_NACC * GEMM_BN);
+                umma(corr, ald, bd, GEMM_IDESC, (kb > 0 || k > 0) ? 1u : 0u);   // a_lo * b_hi
+                umma(corr, ad, bld, GEMM_IDESC, 1u);                            // a_hi * b_lo
 #endif
             }
             umma_commit(&empty_bar[s]);       // the stage is free once these MMAs have read it
@@ -262,7 +282,20 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
             for (int c = 0; c < GEMM_BN; c += 32) {
                 float acc[32];
                 if (num_kb > 0) {
-                    tmem_ld32(tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)c, acc);
+                    const unsigned lane_base = tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)c;
+                    tmem_ld32(lane_base, acc);
+#if GEMM_SPLIT
+                    const int used = num_kb < GEMM_NACC ? num_kb : GEMM_NACC;
+                    float part[32];
+                    for (int a = 1; a < used; ++a) {
+                        tmem_ld32(lane_base + (unsigned)(a * GEMM_BN), part);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) acc[i] += part[i];
+                    }
+                    tmem_ld32(lane_base + (unsigned)(GEMM_NACC * GEMM_BN), part);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[i] += part[i];
+#endif
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) acc[i] = 0.0f;

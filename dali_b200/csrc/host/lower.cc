@@ -104,6 +104,7 @@ struct Lowerer {
     std::map<std::pair<const Expression*, std::string>, int> memo;
     std::map<const Expression*, int> scalar_slot;
     std::vector<Array> keep_alive;
+    const Expression* acc_node = nullptr;    // the MatMul whose product is the GEMM accumulator (epilogue programs)
 
     Lowerer(const std::vector<int64_t>& space_, int nreduce_, memory::Device dev)
         : space(space_), rank((int)space_.size()), nreduce(nreduce_), n_outer(rank - nreduce_), device(dev) {}
@@ -150,6 +151,15 @@ struct Lowerer {
         }
         leaves.push_back(L);
         return (int)leaves.size() - 1;
+    }
+
+    static bool contains_matmul(const Array& a) {
+        if (a.is_stateless()) return false;
+        Expression* e = a.expression().get();
+        if (e->kind_ == N_MATMUL) return true;
+        if (e->kind_ != N_ELEMENTWISE) return false;
+        for (const Array& arg : e->arguments_) if (contains_matmul(arg)) return true;
+        return false;
     }
 
     Array materialize(const Array& a) {
@@ -232,6 +242,9 @@ struct Lowerer {
             case N_VIEW: {
                 View* v = static_cast<View*>(e.get());
                 const Array& arg = v->arguments_[0];
+                // a slice / broadcast of something that contains a product: evaluate that something
+                // once (GEMM with its elementwise surroundings as epilogue) and view the result
+                if (contains_matmul(arg)) materialize(arg);
                 IndexMap am(v->dims_.size());
                 for (size_t k = 0; k < v->dims_.size(); ++k) {
                     const ViewDim& d = v->dims_[k];
@@ -280,7 +293,10 @@ struct Lowerer {
                 break;
             }
             case N_MATMUL: {
-                id = visit(materialize(a), m);
+                bool identity = (int)m.size() == 2 && m[0].src == 0 && m[1].src == 1 && m[0].mult == 1 && m[1].mult == 1 &&
+                                m[0].off == 0 && m[1].off == 0;
+                if (e.get() == acc_node && identity) id = new_value(DTYPE_FLOAT, true, "acc");
+                else id = visit(materialize(a), m);
                 break;
             }
             default:
@@ -354,6 +370,56 @@ struct Lowerer {
     }
 };
 
+// last MatMul reachable from `a` through elementwise nodes only
+void find_matmul(const Array& a, const Expression** out) {
+    if (a.is_stateless()) return;
+    Expression* e = a.expression().get();
+    if (e->kind_ == N_MATMUL) { *out = e; return; }
+    if (e->kind_ != N_ELEMENTWISE) return;
+    for (const Array& arg : e->arguments_) find_matmul(arg, out);
+}
+
+// TF32 split parts of an fp32 matrix, kept next to the buffer until it is written again
+struct SplitParts {
+    int device = 0;
+    size_t bytes = 0;
+    int64_t offset = 0, rows = 0, cols = 0, ld = 0;
+    bool transposed = false;
+    void *hi = nullptr, *lo = nullptr;
+    ~SplitParts() {
+        if (hi) dalib200_free(device, hi, bytes);
+        if (lo) dalib200_free(device, lo, bytes);
+    }
+};
+
+// returns the (hi, lo) parts of a contiguous-row fp32 view; nullptr if the layout cannot be split in place
+std::shared_ptr<SplitParts> split_operand(BufferView* b, bool transpose, memory::Device device, int dev) {
+    std::vector<int> st = b->normalized_strides();
+    const int64_t rows = b->shape_[0], cols = b->shape_[1], ld = st[0];
+    if (st[1] != 1 && cols != 1) return nullptr;
+    if (cols % 4 || ld % 4 || (transpose && rows % 4) || (b->offset_ % 4)) return nullptr;
+    auto& slot = b->memory_->derived_data();
+    if (slot && b->memory_->derived_version() == b->memory_->version()) {
+        auto cached = std::static_pointer_cast<SplitParts>(slot);
+        if (cached->offset == b->offset_ && cached->rows == rows && cached->cols == cols && cached->ld == ld &&
+            cached->transposed == transpose && cached->device == dev)
+            return cached;
+    }
+    const float* x = (const float*)b->memory_->data(device, memory::AM_READONLY) + b->offset_;
+    if (((uintptr_t)x) & 15) return nullptr;
+    auto parts = std::make_shared<SplitParts>();
+    parts->device = dev;
+    parts->bytes = (size_t)rows * cols * 4;
+    parts->offset = b->offset_; parts->rows = rows; parts->cols = cols; parts->ld = ld; parts->transposed = transpose;
+    check(dalib200_alloc(dev, parts->bytes, &parts->hi), "dalib200_alloc");
+    check(dalib200_alloc(dev, parts->bytes, &parts->lo), "dalib200_alloc");
+    check(dalib200_gemm_split_tf32(dev, nullptr, x, rows, cols, ld, transpose ? 1 : 0, (float*)parts->hi, (float*)parts->lo),
+          "dalib200_gemm_split_tf32");
+    slot = parts;
+    b->memory_->derived_version() = b->memory_->version();
+    return parts;
+}
+
 // first reduction reachable from `a` through elementwise nodes and views
 struct FoundReduce { const Reduce* node = nullptr; bool through_view = false; };
 void find_reduce(const Array& a, bool through_view, FoundReduce* out) {
@@ -412,6 +478,82 @@ void run_matmul(const Array& dest, OPERATOR_T op, MatMul* mm) {
     ++tl_stats.gemms;
 }
 
+// dest (op)= tree(product, other operands): one tcgen05 GEMM whose epilogue is the tree.
+// false = this layout is not one the tensor-core path takes (the caller goes on with the
+// general path); other products in the tree have then already been evaluated, which is harmless.
+bool try_fused_gemm(const Array& dest, OPERATOR_T op, const Array& value, const Expression* mm) {
+    if (tl_dry_run) {
+        // count what would run: products other than the fused one first, then the fused GEMM
+    }
+    Array left = mm->arguments_[0], right = mm->arguments_[1];
+    if (!left.is_buffer()) left.eval(false);
+    if (!right.is_buffer()) right.eval(false);
+    BufferView* a = as<BufferView>(left);
+    BufferView* b = as<BufferView>(right);
+    if (!a || !b) return false;
+    const int64_t m = a->shape_[0], k = a->shape_[1], n = b->shape_[1];
+    if (m == 0 || n == 0 || k == 0) return false;
+    memory::Device device = dest.preferred_device();
+
+    Lowerer L({m, n}, 0, device);
+    L.acc_node = mm;
+    int v = L.visit(value, identity_map(2));
+    if (L.types[v] != DTYPE_FLOAT) return false;
+    BufferView* db = as<BufferView>(dest);
+    int leaf = L.leaf_for(db, identity_map(2), true, false, 0, 0, 0);
+    if (op != OPERATOR_T_EQL) L.leaves[leaf].read = true;
+    L.keep_alive.push_back(dest);
+    L.body.push_back("st " + std::to_string(leaf) + " " + ir_assign(op) + " v" + std::to_string(v));
+    const std::string text = L.ir_text();
+    const uint64_t hash = dalib::fnv1a(text);
+    if (!dalib200_is_loaded(hash)) check(dalib200_compile(hash, text.c_str(), text.size()), "dalib200_compile");
+    tl_stats.last_ir = text;
+    if (tl_dry_run) {
+        void* fake[16];
+        for (auto& p : fake) p = (void*)(uintptr_t)4096;
+        if (L.leaves.size() > 16 || k % 4 || n % 4) return false;
+        int rc = dalib200_gemm_fused(-1, nullptr, DALIB200_F32, m, n, k, fake[0], k, fake[0], n, nullptr, nullptr, hash, fake,
+                                     nullptr, nullptr, (int)L.leaves.size(), nullptr, 0);
+        if (rc == DALIB200_ERR_UNSUPPORTED) return false;
+        check(rc, "dalib200_gemm_fused (compile only)");
+        ++tl_stats.gemms;
+        tl_stats.last_variant = "tcgen05.tf32x3";
+        return true;
+    }
+    const int dev = device_index(device);
+    std::shared_ptr<SplitParts> pa = split_operand(a, false, device, dev);
+    std::shared_ptr<SplitParts> pb = split_operand(b, true, device, dev);
+    if (!pa || !pb) return false;
+    const int na = (int)L.leaves.size();
+    std::vector<void*> ptrs(na);
+    std::vector<int64_t> offsets(na);
+    std::vector<const int64_t*> strides(na);
+    for (int pass = 0; pass < 2; ++pass)
+        for (int i = 0; i < na; ++i) {
+            if ((pass == 1) != L.leaves[i].written) continue;
+            ptrs[i] = L.leaves[i].memory->data(device, L.leaves[i].written ? memory::AM_MUTABLE : memory::AM_READONLY);
+            offsets[i] = L.leaves[i].offset;
+            strides[i] = L.leaves[i].strides.data();
+        }
+    std::vector<double> sd(L.scalars.size());
+    std::vector<float> sf(L.scalars.size());
+    std::vector<int> si(L.scalars.size());
+    std::vector<const void*> sp(L.scalars.size());
+    for (size_t j = 0; j < L.scalars.size(); ++j) {
+        sd[j] = L.scalars[j].second; sf[j] = (float)sd[j]; si[j] = (int)sd[j];
+        sp[j] = L.scalars[j].first == DTYPE_DOUBLE ? (const void*)&sd[j] : (L.scalars[j].first == DTYPE_FLOAT ? (const void*)&sf[j] : (const void*)&si[j]);
+    }
+    int rc = dalib200_gemm_fused(dev, nullptr, DALIB200_F32, m, n, k, pa->hi, k, pb->hi, k, pa->lo, pb->lo, hash, ptrs.data(),
+                                 offsets.data(), strides.data(), na, sp.data(), (int)sp.size());
+    if (rc == DALIB200_ERR_UNSUPPORTED) return false;
+    check(rc, "dalib200_gemm_fused");
+    ++tl_stats.gemms;
+    char buf[256];
+    dalib200_last_gemm_kernel(buf, sizeof buf);
+    tl_stats.last_variant = buf;
+    return true;
+}
+
 }  // namespace
 
 void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) {
@@ -454,7 +596,14 @@ void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) 
         if (value.is_assignment()) value.eval(false);
     }
 
-    // ---- MatMul at the root goes to the GEMM entry point
+    // ---- an elementwise tree around a product: tensor-core GEMM with the tree as its epilogue
+    if (dest.is_buffer() && dest.ndim() == 2 && dest.dtype() == DTYPE_FLOAT && value.shape() == dest.shape()) {
+        const Expression* mm = nullptr;
+        find_matmul(value, &mm);
+        if (mm && mm->dtype_ == DTYPE_FLOAT && try_fused_gemm(dest, op, value, mm)) return;
+    }
+
+    // ---- MatMul at the root goes to the general GEMM entry point
     if (value.expression()->kind_ == N_MATMUL && dest.is_buffer()) {
         run_matmul(dest, op, static_cast<MatMul*>(value.expression().get()));
         return;

@@ -51,6 +51,9 @@ struct SynchronizedMemory::Impl {
     bool host_borrowed = false;
     bool dev_borrowed[kMaxGpus] = {false};
     bool clear_pending = false;
+    uint64_t version = 0;
+    std::shared_ptr<void> derived;
+    uint64_t derived_version = 0;
 };
 
 SynchronizedMemory::SynchronizedMemory(size_t total, int inner, Device preferred, bool clear_on_allocation)
@@ -81,7 +84,12 @@ bool SynchronizedMemory::is_any_fresh() const {
     return false;
 }
 
+uint64_t SynchronizedMemory::version() const { return impl_->version; }
+std::shared_ptr<void>& SynchronizedMemory::derived_data() { return impl_->derived; }
+uint64_t& SynchronizedMemory::derived_version() { return impl_->derived_version; }
+
 void SynchronizedMemory::clear() {
+    ++impl_->version;
     impl_->host_fresh = false;
     for (int g = 0; g < kMaxGpus; ++g) impl_->dev_fresh[g] = false;
     impl_->clear_pending = true;
@@ -133,6 +141,7 @@ void* SynchronizedMemory::data(const Device& device, AM mode) {
         fresh_here = true;
     }
     if (mode != AM_READONLY) {
+        ++m->version;
         m->host_fresh = false;
         for (int k = 0; k < kMaxGpus; ++k) m->dev_fresh[k] = false;
         fresh_here = true;
@@ -148,6 +157,7 @@ void SynchronizedMemory::to_device(const Device& d) { data(d, AM_READONLY); }
 void SynchronizedMemory::adopt_buffer(const Device& device, void* buffer) {
     Impl* m = impl_;
     DALI_ASSERT(!is_allocated(device), "adopt_buffer: this memory already owns a buffer on that device");
+    ++m->version;
     if (device.is_cpu()) { m->host = buffer; m->host_fresh = true; }
     else { m->dev[device.number()] = buffer; m->dev_fresh[device.number()] = true; }
 }

@@ -102,6 +102,11 @@ class SynchronizedMemory {
     // uses a caller buffer WITHOUT taking ownership: it is never freed here
     void borrow_buffer(const Device& device, void* buffer);
     void disown_buffer(const Device& device);
+    // Counts writable accesses; lets derived data (e.g. the TF32 split of a weight matrix)
+    // be kept next to the buffer and dropped when the buffer changes.
+    uint64_t version() const;
+    std::shared_ptr<void>& derived_data();
+    uint64_t& derived_version();
   private:
     struct Impl;
     Impl* impl_;

@@ -130,8 +130,30 @@ def test_unfusable_subtrees_become_temporaries():
     assert launched(x / op.sum(x, [0], True)) == {"kernels": 2, "gemms": 0, "temporaries": 1}   # reduce over a leading dim
     y = op.sum(x, [-1], True) * op.max(x, [-1], True) + x                               # two row reductions: one kernel
     assert launched(y) == {"kernels": 1, "gemms": 0, "temporaries": 0}
+    # an elementwise tree around a product is the epilogue of ONE tensor-core GEMM: no separate kernel
     w = Array(np.zeros((64, 32), np.float32))
-    assert launched(op.tanh(op.dot(x, w) + Array(np.zeros((32,), np.float32))[None])) == {"kernels": 1, "gemms": 1, "temporaries": 1}
+    assert launched(op.tanh(op.dot(x, w) + Array(np.zeros((32,), np.float32))[None])) == {"kernels": 0, "gemms": 1, "temporaries": 0}
+    assert "acc" in last_ir() and "op tanh" in last_ir() and last_variant().startswith("tcgen05")
+    # layouts TMA cannot address (k = 62) go to the CUDA-core GEMM plus one fused elementwise kernel
+    x62 = Array(np.zeros((64, 62), np.float32))
+    w62 = Array(np.zeros((62, 32), np.float32))
+    assert launched(op.tanh(op.dot(x62, w62) + 1.0)) == {"kernels": 1, "gemms": 1, "temporaries": 1}
+
+
+def test_lstm_cell_lowering():
+    """gates = dot(x,Wx) + dot(h,Wh) + b is evaluated once (GEMM, then GEMM with '+ first + b' as
+    epilogue) because it is used through four column slices; each output is then one map kernel."""
+    B, H = 32, 64
+    x, h, c = (Array(np.zeros((B, H), np.float32)) for _ in range(3))
+    Wx, Wh = (Array(np.zeros((H, 4 * H), np.float32)) for _ in range(2))
+    b = Array(np.zeros((4 * H,), np.float32))
+    gates = op.dot(x, Wx) + op.dot(h, Wh) + b[None, :]
+    i, f, o = (op.sigmoid(gates[:, k * H:(k + 1) * H]) for k in range(3))
+    g = op.tanh(gates[:, 3 * H:4 * H])
+    c_new = f * c + i * g
+    h_new = o * op.tanh(c_new)
+    assert launched(h_new) == {"kernels": 1, "gemms": 2, "temporaries": 2}
+    assert launched(c_new) == {"kernels": 1, "gemms": 0, "temporaries": 0}
 
 
 def test_lstm_gating_on_slices_is_one_map_kernel():

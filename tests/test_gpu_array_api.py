@@ -304,3 +304,49 @@ def test_memory_freshness_round_trip():
     b += 1                               # device copy updated, host copy must go stale
     np.testing.assert_array_equal(b.numpy(), a_np + 2)
     np.testing.assert_array_equal(a.numpy(), a_np)
+
+
+def test_config2_lstm_cell_full_size_goes_through_tensor_cores():
+    """B=256, H=1024 fp32: two tcgen05 3xTF32 GEMMs (the second with '+ first + b' as epilogue), then one
+    fused gating kernel per output.  Oracle: fp64-accumulated products + the float functors."""
+    rng = np.random.default_rng(1235)
+    B, H = 256, 1024
+    x, h, c = (rng.standard_normal((B, H)).astype(np.float32) for _ in range(3))
+    Wx, Wh = ((rng.standard_normal((H, 4 * H)) * 0.02).astype(np.float32) for _ in range(2))
+    b = (rng.standard_normal(4 * H) * 0.1).astype(np.float32)
+    X, Hh, C, WX, WH, Bv = (Array(v) for v in (x, h, c, Wx, Wh, b))
+
+    def cell():
+        gates = op.dot(X, WX) + op.dot(Hh, WH) + Bv[None, :]
+        i, f, o = (op.sigmoid(gates[:, k * H:(k + 1) * H]) for k in range(3))
+        g = op.tanh(gates[:, 3 * H:4 * H])
+        c_new = f * C + i * g
+        return c_new, o * op.tanh(c_new)
+
+    c_new, h_new = cell()
+    before = lazy_stats()
+    hn = h_new.numpy()
+    cn = c_new.numpy()
+    after = lazy_stats()
+    assert after["gemms"] - before["gemms"] == 2 and after["kernels"] - before["kernels"] == 2
+    gates64 = x.astype(np.float64) @ Wx + h.astype(np.float64) @ Wh + b
+    want_c, want_h = oracle.lstm_gating(gates64.astype(np.float32), c)
+    # K = 1024 products of O(1) magnitude: an fp32 GEMM itself (cuBLAS SGEMM, OpenBLAS) is 5e-6 away from
+    # the fp64 value, the 3xTF32 path measures the same; outputs are O(1), so 1e-5 relative = 1e-5 absolute
+    np.testing.assert_allclose(cn, want_c, rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(hn, want_h, rtol=1e-5, atol=1e-5)
+    # a second step reuses the split weights (same numbers)
+    c2, h2 = cell()
+    np.testing.assert_array_equal(h2.numpy(), hn)
+
+
+def test_dot_with_epilogue_at_mid_size_matches_oracle():
+    rng = np.random.default_rng(77)
+    A = (rng.standard_normal((512, 1024)) * 0.5).astype(np.float32)
+    Bm = (rng.standard_normal((1024, 768)) * 0.05).astype(np.float32)
+    bias = (rng.standard_normal(768) * 0.1).astype(np.float32)
+    r = op.tanh(op.dot(Array(A), Array(Bm)) + Array(bias)[None, :])
+    assert launched(r) == {"kernels": 0, "gemms": 1, "temporaries": 0}
+    assert last_variant().startswith("tcgen05.tf32x3")
+    want = np.tanh(A.astype(np.float64) @ Bm + bias)
+    np.testing.assert_allclose(r.numpy(), want, rtol=1e-5, atol=1e-5)
