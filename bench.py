@@ -5,11 +5,16 @@
 One "step" is one pass of a fused expression over one batch of synthetic
 input.  Prints ONE JSON line (rank 0).  Workloads (BASELINE.json configs):
 
-  chain    sum(sigmoid(x*w+b) * exp(-x*x)) over 2^31 fp32 elements, one fused
-           kernel; sharded over the GPUs with an all-reduce of the partial sums
-  softmax  exp(a - max(a,-1)) / sum(...) on fp32 [4096,1024]; rows shard
-  reduce   sum / max / argmax over axis -1, axis 0 and all axes of fp32 [8192,8192]
-  lstm     LSTM-cell gating on materialised gates (B=256, H=1024)
+  lstm     (default, BASELINE config 2) fused LSTM cell step, fp32 B=256 H=1024:
+           gates = dot(x,Wx)+dot(h,Wh)+b on the tensor cores (3xTF32, second GEMM
+           with "+ first + b" as epilogue), then the fused sigmoid/tanh gating
+  softmax  (config 1) exp(a - max(a,-1)) / sum(...) on fp32 [4096,1024]
+  reduce   (config 3) sum over axis 0 of fp32 [8192,8192] (the strided case)
+  gemm     (config 4) tanh(dot(A,B)+bias), bf16 8192^3, fp32 accumulate
+  chain    (config 5) sum(sigmoid(x*w+b) * exp(-x*x)) over 2^31 fp32 elements,
+           sharded over the GPUs with an all-reduce of the partial sums
+The default run also measures the other four briefly and reports them under
+"other_workloads".
 
 `value` is whole-job algorithmic GB/s with inputs resident in HBM; `e2e` is the
 same metric through dalib200_launch_host with pinned HOST buffers (copies
@@ -34,7 +39,11 @@ FALLBACK_HBM_GBS = 6650.0          # earlier measurement on this pool, used if M
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised
 # under profiles/ (bytes per ALGORITHMIC byte, so it scales with the launch size)
-DRAM_TRAFFIC_PER_ALGO_BYTE = {}
+DRAM_TRAFFIC_PER_ALGO_BYTE = {
+    "chain": 1.0004,     # profiles/chain_sum_all_kernel.md
+    "softmax": 0.50,     # profiles/softmax_row_kernel.md: the 16 MiB output is still in L2 when the kernel ends
+    "reduce": 1.0002,    # profiles/reduce_8192_row_col_all_kernels.md
+}
 
 
 def measured_peak():
@@ -145,6 +154,17 @@ class Workload:
     def e2e_step(self, i):
         raise NotImplementedError
 
+    def graph_fn(self):
+        """launch(i, stream) of one step's kernels when the step has no host-side part, else None."""
+        return None
+
+    def dominant(self):
+        """(kernel name, bound, algorithmic work per launch, launch(i, stream)) or None = the step itself."""
+        return None
+
+    def flops_per_step(self):
+        return 0
+
 
 class Chain(Workload):
     """BASELINE config 5: long elementwise chain + all-axis sum, strong-scaled over the ranks."""
@@ -174,10 +194,19 @@ class Chain(Workload):
     def bytes_per_step(self):
         return self.n * 4
 
+    launches_per_step = 1
+
+    def launch_step(self, i, stream):
+        self.lib.launch(self.h, (self.n,), [self.out, self.x], scalars=[self.w, self.b], device=self.device, stream=stream)
+
     def step(self, i):
-        self.lib.launch(self.h, (self.n,), [self.out, self.x], scalars=[self.w, self.b], stream=self.stream)
+        self.launch_step(i, self.stream)
         if self.world > 1:
-            self.torch.distributed.all_reduce(self.out)
+            from dali_b200.sharding import combine_partials
+            combine_partials(self.out, "sum")           # NCCL all-reduce of one fp32 per rank
+
+    def graph_fn(self):
+        return self.launch_step if self.world == 1 else None
 
     def e2e_setup(self):
         t = self.torch
@@ -250,9 +279,17 @@ class Softmax(Workload):
     def bytes_per_step(self):
         return self.ROWS * self.COLS * 8
 
-    def step(self, i):
+    launches_per_step = 1
+
+    def launch_step(self, i, stream):
         k = i % self.nbuf
-        self.lib.launch(self.h, (self.ROWS, self.COLS), [self.o[k], self.a[k]], stream=self.stream)
+        self.lib.launch(self.h, (self.ROWS, self.COLS), [self.o[k], self.a[k]], device=self.device, stream=stream)
+
+    def step(self, i):
+        self.launch_step(i, self.stream)
+
+    def graph_fn(self):
+        return self.launch_step
 
     def e2e_setup(self):
         t = self.torch
@@ -288,12 +325,344 @@ class Softmax(Workload):
                 "sample": "the full [4096,1024] batch"}
 
 
-WORKLOADS = {"chain": Chain, "softmax": Softmax}
+
+class GraphStepper:
+    """Replays the launches of `fn(i)` for i in range(n) as one CUDA graph (device time without
+    Python between the kernels)."""
+
+    def __init__(self, torch, fn, n):
+        self.torch = torch
+        self.stream = torch.cuda.Stream()
+        self.n = n
+        with torch.cuda.stream(self.stream):
+            for i in range(n):
+                fn(i, self.stream.cuda_stream)      # compile / load / warm pools outside the capture
+            torch.cuda.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=self.stream):
+                for i in range(n):
+                    fn(i, self.stream.cuda_stream)
+        torch.cuda.synchronize()
+
+    def replay(self):
+        with self.torch.cuda.stream(self.stream):     # a graph replays on the stream that is current
+            self.graph.replay()
+
+
+class Lstm(Workload):
+    """BASELINE config 2: fused LSTM cell step, fp32, B=256 H=1024 per GPU."""
+    name = "lstm"
+    B, H = 256, 1024
+
+    def __init__(self, *a):
+        super().__init__(*a)
+        import numpy as np
+        from dali_b200.ir import IRBuilder, gemm_store_ir
+        self.np = np
+        t, B, H = self.torch, self.B, self.H
+        t.manual_seed(1234 + 1 + self.rank)
+        self.nset = 6       # rotating activation sets; weights (2 x 16 MiB, split: 64 MiB) stay hot like in a real RNN
+        self.x = [t.randn(B, H, device="cuda") for _ in range(self.nset)]
+        self.h = [t.randn(B, H, device="cuda") for _ in range(self.nset)]
+        self.c = [t.randn(B, H, device="cuda") for _ in range(self.nset)]
+        self.Wx = t.randn(H, 4 * H, device="cuda") * 0.02
+        self.Wh = t.randn(H, 4 * H, device="cuda") * 0.02
+        self.b = t.zeros(4 * H, device="cuda")
+        self.gates = t.empty(B, 4 * H, device="cuda")
+        self.c_new = [t.empty(B, H, device="cuda") for _ in range(self.nset)]
+        self.h_new = [t.empty(B, H, device="cuda") for _ in range(self.nset)]
+        L = self.lib
+        # weights are split once and kept, as the front end keeps them next to the buffer
+        self.W = {}
+        for name, w in (("Wx", self.Wx), ("Wh", self.Wh)):
+            hi, lo = t.empty(4 * H * H, device="cuda"), t.empty(4 * H * H, device="cuda")
+            L.gemm_split_tf32(w, H, 4 * H, 4 * H, hi, lo, transpose=True, device=self.device)
+            self.W[name] = (hi, lo)
+        self.parts = [t.empty(B * H, device="cuda") for _ in range(4)]
+        self.h_store = L.compile(gemm_store_ir("f32"))
+        e = IRBuilder(2, 0)
+        o, first, bias = e.arg("f32"), e.arg("f32"), e.arg("f32")
+        e.st(o, e.op("add", e.op("add", e.acc(), e.ld(first)), e.ld(bias)))      # x.Wx + h.Wh + b
+        self.h_epi = L.compile(e.text())
+        g = IRBuilder(2, 0)                                                         # the gating kernel the front end emits
+        out = g.arg("f32")
+        gi, gf, go, gg, c = (g.arg("f32") for _ in range(5))
+        i, f, o_ = (g.op("sigmoid", g.ld(a_)) for a_ in (gi, gf, go))
+        cn = g.op("add", g.op("eltmul", f, g.ld(c)), g.op("eltmul", i, g.op("tanh", g.ld(gg))))
+        gh = IRBuilder(2, 0)
+        self.ir_c = None
+        # h_new = o * tanh(c_new) recomputes c_new inside its own kernel, exactly as Array::eval lowers it
+        outh = gh.arg("f32")
+        hi_, hf, ho, hg, hc = (gh.arg("f32") for _ in range(5))
+        i2, f2, o2 = (gh.op("sigmoid", gh.ld(a_)) for a_ in (hi_, hf, ho))
+        cn2 = gh.op("add", gh.op("eltmul", f2, gh.ld(hc)), gh.op("eltmul", i2, gh.op("tanh", gh.ld(hg))))
+        gh.st(outh, gh.op("eltmul", o2, gh.op("tanh", cn2)))
+        g.st(out, cn)
+        self.h_gate_c = L.compile(g.text())
+        self.h_gate_h = L.compile(gh.text())
+        self.scaling = "weak"
+        self.launches_per_step = 6
+
+    def describe(self):
+        return {"workload": "C2 LSTM cell step: gates = dot(x,Wx)+dot(h,Wh)+b, c' = sig(f)*c + sig(i)*tanh(g), "
+                            "h' = sig(o)*tanh(c'); fp32, B=256 H=1024 per GPU, x,h,c ~ N(0,1), W ~ N(0,0.02), b = 0",
+                "l2": "activations rotate over %d sets; the two weight matrices are reused every step (as in an RNN) "
+                      "and stay in L2" % self.nset,
+                "kernels_per_step": "2 TF32 splits (x, h), 2 tcgen05 3xTF32 GEMMs, 2 fused gating kernels",
+                "parallelism": "batch sharded: each of %d GPU(s) runs its own B=256 shard, weights replicated, no collective" % self.world}
+
+    def bytes_per_step(self):
+        B, H = self.B, self.H
+        return 4 * (3 * B * H + 2 * H * 4 * H + 4 * H + 2 * B * H)
+
+    def flops_per_step(self):
+        return 2 * 2 * self.B * self.H * 4 * self.H
+
+    def launch_step(self, i, stream):
+        L, B, H, k = self.lib, self.B, self.H, i % self.nset
+        d = self.device
+        L.gemm_split_tf32(self.x[k], B, H, H, self.parts[0], self.parts[1], device=d, stream=stream)
+        L.gemm_split_tf32(self.h[k], B, H, H, self.parts[2], self.parts[3], device=d, stream=stream)
+        L.gemm_fused(0, B, 4 * H, H, self.parts[0], H, self.W["Wx"][0], H, self.h_store, [self.gates],
+                     a_lo=self.parts[1], b_lo=self.W["Wx"][1], device=d, stream=stream)
+        L.gemm_fused(0, B, 4 * H, H, self.parts[2], H, self.W["Wh"][0], H, self.h_epi, [self.gates, self.gates, self.b],
+                     strides=[None, None, [0, 1]], a_lo=self.parts[3], b_lo=self.W["Wh"][1], device=d, stream=stream)
+        gs = [4 * H, 1]
+        G = self.gates
+        for hsh, out in ((self.h_gate_h, self.h_new[k]), (self.h_gate_c, self.c_new[k])):
+            L.launch(hsh, (B, H), [out, G, G, G, G, self.c[k]], strides=[None, gs, gs, gs, gs, None],
+                     offsets=[0, 0, H, 2 * H, 3 * H, 0], device=d, stream=stream)
+
+    def step(self, i):
+        self.launch_step(i, self.stream)
+
+    def graph_fn(self):
+        return self.launch_step
+
+    def dominant(self):
+        """(name, launches per step, bound, algorithmic work per launch, launcher) of the dominant kernel."""
+        B, H = self.B, self.H
+
+        def one(i, stream):
+            self.lib.gemm_fused(0, B, 4 * H, H, self.parts[0], H, self.W["Wx"][0], H, self.h_store, [self.gates],
+                                a_lo=self.parts[1], b_lo=self.W["Wx"][1], device=self.device, stream=stream)
+        return ("tcgen05 3xTF32 GEMM [256,1024]x[1024,4096]", "tensor", 2.0 * B * H * 4 * H, one)
+
+    def e2e_setup(self):
+        np = self.np
+        self.host = {k: getattr(self, k)[0].cpu().numpy() for k in ("x", "h", "c")}
+        from dali_b200.array import Array, set_default_device
+        set_default_device(self.device)
+        self.fe = {"Wx": Array(self.Wx.cpu().numpy()), "Wh": Array(self.Wh.cpu().numpy()), "b": Array(self.b.cpu().numpy())}
+        self.h2d, self.d2h = 3 * self.B * self.H * 4, 2 * self.B * self.H * 4
+
+    def e2e_step(self, i):
+        # the call a user makes: host arrays in, lazy expression, eval, results back on the host
+        from dali_b200.array import Array, op
+        H = self.H
+        x, h, c = (Array(self.host[k]) for k in ("x", "h", "c"))
+        gates = op.dot(x, self.fe["Wx"]) + op.dot(h, self.fe["Wh"]) + self.fe["b"][None, :]
+        i_, f, o = (op.sigmoid(gates[:, k * H:(k + 1) * H]) for k in range(3))
+        g = op.tanh(gates[:, 3 * H:4 * H])
+        c_new = f * c + i_ * g
+        h_new = o * op.tanh(c_new)
+        self.last = (h_new.numpy(), c_new.numpy())
+
+    def verify(self):
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import dali_oracle as oracle
+        np = self.np
+        self.step(0)
+        self.torch.cuda.synchronize()
+        assert self.lib.gemm_error_flag(self.device) == 0
+        x, h, c, Wx, Wh = (v.cpu().numpy().astype(np.float64) for v in (self.x[0], self.h[0], self.c[0], self.Wx, self.Wh))
+        gates = (x @ Wx + h @ Wh).astype(np.float32)
+        want_c, want_h = oracle.lstm_gating(gates, self.c[0].cpu().numpy())
+        assert np.allclose(self.c_new[0].cpu().numpy(), want_c, rtol=1e-5, atol=1e-5)
+        assert np.allclose(self.h_new[0].cpu().numpy(), want_h, rtol=1e-5, atol=1e-5)
+
+    def cpu_baseline(self, tmpdir, reps):
+        np = self.np
+        for k in ("x", "h", "c"):
+            np.save(os.path.join(tmpdir, k + ".npy"), getattr(self, k)[0].cpu().numpy())
+        np.save(os.path.join(tmpdir, "Wx.npy"), self.Wx.cpu().numpy())
+        np.save(os.path.join(tmpdir, "Wh.npy"), self.Wh.cpu().numpy())
+        np.save(os.path.join(tmpdir, "b.npy"), self.b.cpu().numpy().reshape(1, -1))
+        times = run_ref_driver("lstm", ["x.npy", "h.npy", "c.npy", "Wx.npy", "Wh.npy", "b.npy", "c_out.npy", "h_out.npy"], reps, tmpdir)
+        if not times:
+            return None
+        return {"ms": times, "bytes": self.bytes_per_step(), "cores": os.cpu_count() or 1, "kind": "reference",
+                "sample": "the full B=256 H=1024 cell step (reference: 8 OpenBLAS sgemm on all host cores + 5 single-threaded JIT kernels)"}
+
+
+class Gemm(Workload):
+    """BASELINE config 4: tanh(dot(A,B)+bias), bf16 8192^3, fp32 accumulate, bf16 out."""
+    name = "gemm"
+    N = 8192
+
+    def __init__(self, *a, n=None):
+        super().__init__(*a)
+        import numpy as np
+        from dali_b200.ir import gemm_bias_tanh_ir
+        self.np = np
+        t = self.torch
+        n = self.n = n or self.N
+        t.manual_seed(1234 + 3 + self.rank)
+        self.A = (t.randn(n, n, device="cuda") * 0.02).bfloat16()
+        self.Bm = (t.randn(n, n, device="cuda") * 0.02).bfloat16()
+        self.bias = t.randn(n, device="cuda") * 0.1
+        self.out = t.empty(n, n, device="cuda", dtype=t.bfloat16)
+        self.h = self.lib.compile(gemm_bias_tanh_ir("bf16"))
+        self.scaling = "weak"
+        self.launches_per_step = 1
+
+    def describe(self):
+        return {"workload": "C4 tanh(dot(A,B)+bias), bf16 A,B [%d,%d] ~ N(0,0.02), bias ~ N(0,0.1), fp32 accumulate, bf16 out" % (self.n, self.n),
+                "l2": "operands + output = %d MiB per launch, larger than L2" % (3 * self.n * self.n * 2 >> 20),
+                "parallelism": "rows of A sharded: each of %d GPU(s) runs its own [%d,%d] block, B and bias replicated, no collective" % (self.world, self.n, self.n)}
+
+    def bytes_per_step(self):
+        return 3 * self.n * self.n * 2
+
+    def flops_per_step(self):
+        return 2 * self.n ** 3
+
+    def launch_step(self, i, stream):
+        n = self.n
+        self.lib.gemm_fused(3, n, n, n, self.A, n, self.Bm, n, self.h, [self.out, self.bias], strides=[None, [0, 1]],
+                            device=self.device, stream=stream)
+
+    def step(self, i):
+        self.launch_step(i, self.stream)
+
+    def graph_fn(self):
+        return self.launch_step
+
+    def dominant(self):
+        return ("tcgen05 bf16 GEMM + bias/tanh epilogue", "tensor", float(self.flops_per_step()), self.launch_step)
+
+    def e2e_setup(self):
+        t = self.torch
+        n = self.n
+        self.hA = t.empty(n, n, dtype=t.bfloat16, pin_memory=True); self.hA.copy_(self.A)
+        self.hB = t.empty(n, n, dtype=t.bfloat16, pin_memory=True); self.hB.copy_(self.Bm)
+        self.hbias = t.empty(n, pin_memory=True); self.hbias.copy_(self.bias)
+        self.hout = t.empty(n, n, dtype=t.bfloat16, pin_memory=True)
+        self.h2d, self.d2h = 2 * n * n * 2 + n * 4, n * n * 2
+
+    def e2e_step(self, i):
+        # bf16 is not a dtype of the reference's Array: the user-facing call for it is the C ABI with
+        # caller-managed copies (pinned host -> device, fused GEMM, device -> pinned host)
+        t = self.torch
+        self.A.copy_(self.hA, non_blocking=True)
+        self.Bm.copy_(self.hB, non_blocking=True)
+        self.bias.copy_(self.hbias, non_blocking=True)
+        self.launch_step(i, self.stream)
+        self.hout.copy_(self.out, non_blocking=True)
+        t.cuda.synchronize()
+
+    def verify(self):
+        np, n = self.np, self.n
+        self.step(0)
+        self.torch.cuda.synchronize()
+        assert self.lib.gemm_error_flag(self.device) == 0
+        rows = [0, 129, n - 1]
+        a = self.A[rows].float().cpu().numpy().astype(np.float64)
+        want = np.tanh(a @ self.Bm.float().cpu().numpy().astype(np.float64) + self.bias.cpu().numpy())
+        assert np.allclose(self.out[rows].float().cpu().numpy(), want, rtol=1e-2, atol=4e-3)
+
+    def cpu_baseline(self, tmpdir, reps):
+        np = self.np
+        m = 2048        # the reference has no bf16: fp32 sgemm + its fused add/tanh kernel on bf16-rounded inputs
+        np.save(os.path.join(tmpdir, "A.npy"), self.A[:m, :m].float().cpu().numpy())
+        np.save(os.path.join(tmpdir, "B.npy"), self.Bm[:m, :m].float().cpu().numpy())
+        np.save(os.path.join(tmpdir, "bias.npy"), self.bias[:m].cpu().numpy())
+        times = run_ref_driver("gemm_tanh", ["A.npy", "B.npy", "bias.npy", "out.npy"], min(reps, 3), tmpdir)
+        if not times:
+            return None
+        return {"ms": times, "bytes": 3 * m * m * 2, "flops": 2.0 * m ** 3, "cores": os.cpu_count() or 1, "kind": "reference",
+                "sample": "2048^3 fp32 (1/64 of the flops): OpenBLAS sgemm on all host cores + the reference's single-threaded tanh kernel"}
+
+
+class ReduceAxis0(Workload):
+    """BASELINE config 3 (the strided case): sum over axis 0 of fp32 [8192,8192]."""
+    name = "reduce"
+    N = 8192
+
+    def __init__(self, *a):
+        super().__init__(*a)
+        import numpy as np
+        from dali_b200.ir import reduce_ir
+        self.np = np
+        t = self.torch
+        t.manual_seed(1234 + 2 + self.rank)
+        self.x = [t.rand(self.N, self.N, device="cuda") * 2 - 1 for _ in range(2)]    # 2 x 256 MiB > L2
+        self.out = t.empty(self.N, device="cuda")
+        self.h = self.lib.compile(reduce_ir("sum", "f32", 2, 1))
+        self.scaling = "weak"
+        self.launches_per_step = 1
+
+    def describe(self):
+        return {"workload": "C3 op::sum over axis 0 of fp32 [8192,8192] ~ U(-1,1) per GPU",
+                "l2": "two 256 MiB inputs alternate (512 MiB > L2)",
+                "parallelism": "rows sharded over %d GPU(s); the [8192] partial sums meet in an all-reduce" % self.world}
+
+    def bytes_per_step(self):
+        return self.N * self.N * 4
+
+    def launch_step(self, i, stream):
+        N = self.N
+        self.lib.launch(self.h, (N, N), [self.out, self.x[i % 2]], strides=[None, [1, N]], device=self.device, stream=stream)
+
+    def step(self, i):
+        self.launch_step(i, self.stream)
+        if self.world > 1:
+            from dali_b200.sharding import combine_partials
+            combine_partials(self.out, "sum")           # NCCL all-reduce of the [8192] partial sums
+
+    def graph_fn(self):
+        return self.launch_step if self.world == 1 else None
+
+    def e2e_setup(self):
+        t = self.torch
+        self.hx = t.empty(self.N, self.N, pin_memory=True); self.hx.copy_(self.x[0])
+        self.hout = self.np.zeros(self.N, self.np.float32)
+        self.h2d, self.d2h = self.N * self.N * 4, self.N * 4
+
+    def e2e_step(self, i):
+        import ctypes
+        N = self.N
+        ptrs = (ctypes.c_void_p * 2)(self.hout.ctypes.data, self.hx.data_ptr())
+        ext = (ctypes.c_int64 * 2)(N, N * N)
+        offs = (ctypes.c_int64 * 2)(0, 0)
+        space = (ctypes.c_int64 * 2)(N, N)
+        st1 = (ctypes.c_int64 * 2)(1, N)
+        st = (ctypes.POINTER(ctypes.c_int64) * 2)(None, ctypes.cast(st1, ctypes.POINTER(ctypes.c_int64)))
+        self.lib.check(self.lib.c.dalib200_launch_host(ctypes.c_uint64(self.h), self.device, space, 2, ptrs, ext, offs, st, 2, None, 0))
+
+    def verify(self):
+        self.launch_step(0, self.stream)
+        self.torch.cuda.synchronize()
+        want = self.x[0].sum(0, dtype=self.torch.float64)
+        bound = 1e-5 * self.x[0].abs().sum(0, dtype=self.torch.float64)
+        assert bool(((self.out.double() - want).abs() <= bound).all())
+
+    def cpu_baseline(self, tmpdir, reps):
+        m = 2048
+        self.np.save(os.path.join(tmpdir, "x.npy"), self.x[0][:m, :m].contiguous().cpu().numpy())
+        times = run_ref_driver("reduce", ["sum", "0", "x.npy", "out.npy"], reps, tmpdir)
+        if not times:
+            return None
+        return {"ms": times, "bytes": m * m * 4, "cores": 1, "kind": "reference", "sample": "a [2048,2048] corner (1/16 of the bytes)"}
+
+
+WORKLOADS = {"lstm": Lstm, "softmax": Softmax, "reduce": ReduceAxis0, "gemm": Gemm, "chain": Chain}
 
 
 # ----------------------------------------------------------------------------- main
 def reference_arm(args):
-    """--impl reference: the reference's own CPU implementation on this box's host cores."""
+    """--impl reference: the reference's own CPU implementation (oracle/_ref) on this box's host cores,
+    same metric and config, a bounded sample per step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -303,32 +672,160 @@ def reference_arm(args):
     if not os.path.exists(drv):
         print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/ref_driver was not built (no reference checkout at build time)"}))
         return
-    peak, _ = measured_peak()
+    cores = os.cpu_count() or 1
     with tempfile.TemporaryDirectory() as tmp:
-        rng = np.random.default_rng(1234 + 4)
-        if args.workload == "softmax":
-            np.save(os.path.join(tmp, "a.npy"), rng.standard_normal((4096, 1024)).astype(np.float32))
-            case, cargs, nbytes = "softmax_naive", ["a.npy", "out.npy"], 4096 * 1024 * 8
+        def save(name, arr):
+            np.save(os.path.join(tmp, name), arr)
+        w = args.workload
+        if w == "lstm":
+            rng = np.random.default_rng(1234 + 1)
+            B, H = 256, 1024
+            for k in ("x", "h", "c"):
+                save(k + ".npy", rng.standard_normal((B, H)).astype(np.float32))
+            for k in ("Wx", "Wh"):
+                save(k + ".npy", (rng.standard_normal((H, 4 * H)) * 0.02).astype(np.float32))
+            save("b.npy", np.zeros((1, 4 * H), np.float32))
+            case, cargs = "lstm", ["x.npy", "h.npy", "c.npy", "Wx.npy", "Wh.npy", "b.npy", "c_out.npy", "h_out.npy"]
+            nbytes = 4 * (3 * B * H + 2 * H * 4 * H + 4 * H + 2 * B * H)
+            flops = 2 * 2 * B * H * 4 * H
+            wl = ("C2 LSTM cell step: gates = dot(x,Wx)+dot(h,Wh)+b, c' = sig(f)*c + sig(i)*tanh(g), h' = sig(o)*tanh(c'); "
+                  "fp32, B=256 H=1024 per GPU, x,h,c ~ N(0,1), W ~ N(0,0.02), b = 0")
+            sample, ncores, scaling, dtype = "the full cell step (8 OpenBLAS sgemm on all host cores + 5 single-threaded JIT kernels)", cores, "weak", "f32"
+        elif w == "softmax":
+            rng = np.random.default_rng(1234)
+            save("a.npy", rng.standard_normal((4096, 1024)).astype(np.float32))
+            case, cargs, nbytes, flops = "softmax_naive", ["a.npy", "out.npy"], 4096 * 1024 * 8, 0
             wl = "C1 exp(a-max(a,{-1},true))/sum(exped,{-1},true), fp32 [4096,1024] ~ N(0,1) per GPU"
-            sample = "the full [4096,1024] batch per step"
+            sample, ncores, scaling, dtype = "the full [4096,1024] batch per step", 1, "weak", "f32"
+        elif w == "reduce":
+            rng = np.random.default_rng(1236)
+            m = 2048
+            save("x.npy", (rng.random((m, m)) * 2 - 1).astype(np.float32))
+            case, cargs, nbytes, flops = "reduce", ["sum", "0", "x.npy", "out.npy"], m * m * 4, 0
+            wl = "C3 op::sum over axis 0 of fp32 [8192,8192] ~ U(-1,1) per GPU"
+            sample, ncores, scaling, dtype = "a [2048,2048] array per step (1/16 of the bytes)", 1, "weak", "f32"
+        elif w == "gemm":
+            rng = np.random.default_rng(1237)
+            m = 2048
+            save("A.npy", (rng.standard_normal((m, m)) * 0.02).astype(np.float32))
+            save("B.npy", (rng.standard_normal((m, m)) * 0.02).astype(np.float32))
+            save("bias.npy", (rng.standard_normal(m) * 0.1).astype(np.float32))
+            case, cargs, nbytes, flops = "gemm_tanh", ["A.npy", "B.npy", "bias.npy", "out.npy"], 3 * m * m * 2, 2.0 * m ** 3
+            wl = "C4 tanh(dot(A,B)+bias), bf16 A,B [8192,8192] ~ N(0,0.02), bias ~ N(0,0.1), fp32 accumulate, bf16 out"
+            sample, ncores, scaling, dtype = "2048^3 in fp32 per step (the reference has no bf16; 1/64 of the flops)", cores, "weak", "f32"
         else:
+            rng = np.random.default_rng(1234 + 4)
             m = 1 << 24
-            np.save(os.path.join(tmp, "x.npy"), rng.standard_normal(m).astype(np.float32))
-            case, cargs, nbytes = "chain", ["x.npy", "0.5", "0.1", "out.npy"], m * 4
+            save("x.npy", rng.standard_normal(m).astype(np.float32))
+            case, cargs, nbytes, flops = "chain", ["x.npy", "0.5", "0.1", "out.npy"], m * 4, 0
             wl = "C5 sum(sigmoid(x*w+b)*exp(-x*x)), fp32 x ~ N(0,1), 2^31 elements total, w=0.5 b=0.1"
-            sample = "2^24 elements per step (1/128 of the workload; the reference's int sizes cap a chunk at 2^28)"
+            sample, ncores, scaling, dtype = "2^24 elements per step (1/128 of the workload; the reference's int sizes cap a chunk at 2^28)", 1, "strong", "f32"
         times = run_ref_driver(case, cargs, args.warmup + args.steps, tmp)
     timed = times[args.warmup:]
     ms = sum(timed) / len(timed)
     gbs = nbytes / (ms * 1e-3) / 1e9
     line = {"metric": "fused_expr_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if args.workload == "chain" else "weak",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "reference",
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": scaling,
+            "vs_baseline": None, "dtype": dtype, "data": "synthetic", "impl": "reference",
             "config": {"workload": wl},
-            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": 1, "kind": "reference", "sample": sample},
+            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": ncores, "kind": "reference", "sample": sample},
             "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
+    if flops:
+        line["gemm_tflops"] = flops / (ms * 1e-3) / 1e12
     print(json.dumps(line))
+
+
+def measure(wl, torch, world, steps, warmup, lib, sample_clocks=True, local=0):
+    """Times exactly `steps` steps (device time, max over ranks).  Returns a dict."""
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(warmup):
+        wl.step(i)
+    barrier()
+    fn = wl.graph_fn()
+    stepper = GraphStepper(torch, lambda i, st: fn(warmup + i, st), steps) if fn else None
+    if stepper:
+        for _ in range(2):
+            stepper.replay()
+    barrier()
+    sampler = ClockSampler(local) if sample_clocks else None
+    if sampler:
+        sampler.start()
+    launches0 = lib.cache_stats()["launches"]
+    block_ms = []
+    t_end = time.time() + (1.5 if sample_clocks else 0.0)
+    while True:
+        if stepper:
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record(stepper.stream)
+            stepper.replay()
+            ev1.record(stepper.stream)
+        else:
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            for i in range(steps):
+                wl.step(warmup + i)
+            ev1.record()
+        barrier()
+        block_ms.append(ev0.elapsed_time(ev1))
+        if time.time() > t_end or len(block_ms) >= 200:
+            break
+    clocks = sampler.stop() if sampler else None
+    # the reported figure is the FIRST timed block of exactly `steps` steps; later blocks only keep
+    # the GPU busy while nvidia-smi samples the clocks
+    t = torch.tensor([block_ms[0]], dtype=torch.float64, device="cuda")
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    ms_step = float(t.item()) / steps
+    res = {"ms_per_step": ms_step, "clocks": clocks, "graph": bool(stepper),
+           "gpu_launches": steps * getattr(wl, "launches_per_step", 1),
+           "median_block_ms_per_step": sorted(block_ms)[len(block_ms) // 2] / steps}
+    # dominant kernel alone, replayed back to back
+    dom = wl.dominant()
+    if dom:
+        name, bound, work, launch = dom
+        reps = 20
+        ds = GraphStepper(torch, launch, reps)
+        ds.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(ds.stream)
+        ds.replay()
+        e1.record(ds.stream)
+        torch.cuda.synchronize()
+        res["dominant"] = {"kernel": name, "bound": bound, "work": work, "ms": e0.elapsed_time(e1) / reps}
+    return res
+
+
+def roofline_of(wl, m, lib):
+    peak_hbm, kind = measured_peak()
+    dom = m.get("dominant")
+    if dom and dom["bound"] == "tensor":
+        path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        peak = 1590.0
+        src = "fallback 1.59 PFLOP/s"
+        if os.path.exists(path):
+            with open(path) as f:
+                peak = float(json.load(f)["bf16_tflops"])
+            src = "measured (MEASURED_PEAKS.json bf16_tflops, burst: kernel timed alone)"
+        achieved = dom["work"] / (dom["ms"] * 1e-3) / 1e12
+        return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "traffic": None, "peak_source": src, "kernel": dom["kernel"] + " [" + lib.last_gemm_kernel() + "]",
+                "kernel_ms": dom["ms"],
+                "note": "algorithmic flops 2*M*N*K per launch; an fp32 product issues three TF32 passes, whose dense rate is half the bf16 rate"
+                        if "TF32" in dom["kernel"] else "algorithmic flops 2*M*N*K per launch"}
+    ms = dom["ms"] if dom else m["ms_per_step"]
+    work = dom["work"] if dom else wl.bytes_per_step()
+    achieved = work / (ms * 1e-3) / 1e9
+    ratio = DRAM_TRAFFIC_PER_ALGO_BYTE.get(wl.name)
+    return {"bound": "hbm", "achieved": achieved, "peak": peak_hbm, "unit": "GB/s", "frac": achieved / peak_hbm,
+            "traffic": ratio * work if ratio else None,
+            "peak_source": (kind + " (MEASURED_PEAKS.json hbm_gbs)") if kind == "measured" else "fallback 6.65 TB/s",
+            "kernel": lib.last_variant(), "kernel_ms": ms}
 
 
 def main():
@@ -337,14 +834,16 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="chain", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="lstm", choices=sorted(WORKLOADS))
     ap.add_argument("--elements", type=int, default=0, help="chain: total elements (profiling on a small case)")
+    ap.add_argument("--gemm-n", type=int, default=0, help="gemm: matrix size (profiling on a small case)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-others", action="store_true")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         return reference_arm(args)
+    args.warmup = max(args.warmup, 3)
 
     import torch
     import dali_b200
@@ -358,61 +857,28 @@ def main():
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local))
     lib = dali_b200.load_library()
     lib.init(0)
-    # the library indexes the devices it bound; with one process per GPU that is `local`
-    dev_index = local
-    cls = WORKLOADS[args.workload]
-    kw = {"total": args.elements} if (args.workload == "chain" and args.elements) else {}
-    wl = cls(lib, torch, rank, world, dev_index, **kw)
-    if dev_index != 0:
-        # route every launch of this process to its own device
-        orig_launch = lib.launch
-        lib.launch = lambda *a, **k: orig_launch(*a, device=dev_index, **k)
+    dev_index = local      # the library indexes the devices it bound; one process per GPU uses its own
+
+    def build(name):
+        kw = {}
+        if name == "chain" and args.elements:
+            kw["total"] = args.elements
+        if name == "gemm" and args.gemm_n:
+            kw["n"] = args.gemm_n
+        return WORKLOADS[name](lib, torch, rank, world, dev_index, **kw)
+
+    wl = build(args.workload)
     wl.verify()
+    m = measure(wl, torch, world, args.steps, args.warmup, lib, True, local)
+    ms_step = m["ms_per_step"]
+    job_bytes = wl.bytes_per_step() * world
+    value = job_bytes / (ms_step * 1e-3) / 1e9
+    roofline = roofline_of(wl, m, lib)
 
     def barrier():
         if world > 1:
             torch.distributed.barrier()
         torch.cuda.synchronize()
-
-    for i in range(args.warmup):
-        wl.step(i)
-    barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
-    launches0 = lib.cache_stats()["launches"]
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    # long enough for nvidia-smi to sample clocks under load: repeat the K steps, time each block
-    block_ms = []
-    t_end = time.time() + 1.5
-    while True:
-        ev0.record()
-        for i in range(args.steps):
-            wl.step(args.warmup + i)
-        ev1.record()
-        barrier()
-        block_ms.append(ev0.elapsed_time(ev1))
-        if time.time() > t_end or len(block_ms) >= 50:
-            break
-    launches = (lib.cache_stats()["launches"] - launches0) // len(block_ms)
-    clocks = sampler.stop()
-    # the reported figure is the FIRST timed block of exactly K steps; the later blocks only
-    # keep the GPU busy while clocks are sampled
-    ms_total = block_ms[0]
-    t = torch.tensor([ms_total], dtype=torch.float64, device="cuda")
-    if world > 1:
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-    ms_total = float(t.item())
-    ms_step = ms_total / args.steps
-    job_bytes = wl.bytes_per_step() * world
-    value = job_bytes / (ms_step * 1e-3) / 1e9
-
-    peak, peak_kind = measured_peak()
-    achieved = wl.bytes_per_step() / (ms_step * 1e-3) / 1e9     # one launch per step on each GPU
-    traffic_ratio = DRAM_TRAFFIC_PER_ALGO_BYTE.get(args.workload)
-    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": traffic_ratio * wl.bytes_per_step() if traffic_ratio else None,
-                "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6.65 TB/s",
-                "kernel": lib.last_variant()}
 
     e2e = None
     if not args.no_e2e:
@@ -430,8 +896,10 @@ def main():
         if world > 1:
             torch.distributed.all_reduce(te, op=torch.distributed.ReduceOp.MAX)
         e2e = {"value": job_bytes / float(te.item()) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": wl.h2d,
-               "d2h_bytes_per_step": wl.d2h, "steps": n_e2e,
-               "api": "dalib200_launch_host (pinned host buffers; alloc from pool + H2D + kernel + D2H + sync per step)"}
+               "d2h_bytes_per_step": wl.d2h, "steps": n_e2e, "ms_per_step": float(te.item()) * 1e3,
+               "api": "host arrays -> lazy Array/op:: expression -> eval -> host arrays (C++ front end through its C binding)"
+                      if args.workload == "lstm" else
+                      "dalib200_launch_host / C ABI with pinned host buffers (alloc from pool + H2D + kernel + D2H + sync per step)"}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -442,14 +910,39 @@ def main():
             best = sorted(r["ms"])[len(r["ms"]) // 2]
             cpu = {"value": r["bytes"] / (best * 1e-3) / 1e9, "unit": "GB/s", "cores": r["cores"], "kind": r["kind"],
                    "sample": r["sample"], "ms": best}
+            if r.get("flops"):
+                cpu["tflops"] = r["flops"] / (best * 1e-3) / 1e12
+
+    others = None
+    if args.workload == "lstm" and not args.no_others and world == 1:
+        others = {}
+        for name in ("softmax", "reduce", "gemm", "chain"):
+            del wl
+            torch.cuda.empty_cache()
+            wl = build(name)
+            wl.verify()
+            mo = measure(wl, torch, world, 10, 3, lib, False, local)
+            ro = roofline_of(wl, mo, lib)
+            entry = {"workload": wl.describe()["workload"], "ms_per_step": mo["ms_per_step"],
+                     "gbs": wl.bytes_per_step() / (mo["ms_per_step"] * 1e-3) / 1e9,
+                     "roofline": {k: ro[k] for k in ("bound", "achieved", "peak", "unit", "frac", "kernel")}}
+            if wl.flops_per_step():
+                entry["tflops"] = wl.flops_per_step() / (mo["ms_per_step"] * 1e-3) / 1e12
+            others[name] = entry
+        wl = build("lstm")
 
     if rank == 0:
         cfg = wl.describe()
         line = {"metric": "fused_expr_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": wl.scaling,
-                "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg, "clocks": clocks,
-                "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
-                "pct_of_measured_hbm_peak": 100.0 * achieved / peak, "pct_of_nominal_8TBs": 100.0 * achieved / 8000.0}
+                "vs_baseline": None, "dtype": "bf16" if args.workload == "gemm" else "f32", "data": "synthetic",
+                "config": cfg, "clocks": m["clocks"], "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+                "gpu_launches": int(m["gpu_launches"]), "timed_with": "CUDA graph replay of the step's launches" if m["graph"] else "eager launches",
+                "pct_of_nominal_8TBs": 100.0 * value / world / 8000.0}
+        if wl.flops_per_step():
+            line["gemm_tflops"] = wl.flops_per_step() * world / (ms_step * 1e-3) / 1e12
+        if others:
+            line["other_workloads"] = others
         print(json.dumps(line))
     if world > 1:
         torch.distributed.destroy_process_group()

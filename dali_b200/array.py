@@ -336,6 +336,11 @@ def set_dry_run(on):
     _c().c.dali_lazy_set_dry_run(int(bool(on)))
 
 
+def set_default_device(gpu):
+    """memory::default_preferred_device = Device::gpu(gpu) (one process per GPU sets its own)."""
+    _check(_c().c.dali_set_default_device(int(gpu)))
+
+
 def last_ir():
     buf = ctypes.create_string_buffer(1 << 16)
     _c().c.dali_lazy_last_ir(buf, len(buf))

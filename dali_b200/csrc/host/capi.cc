@@ -254,6 +254,13 @@ int dali_array_assign(dali_array_t dest, int op_code, dali_array_t value) {
     });
 }
 
+int dali_set_default_device(int gpu) {
+    return guard([&]() {
+        DALI_ASSERT(gpu >= 0, "dali_set_default_device: gpu index must be non-negative");
+        memory::default_preferred_device = memory::Device::gpu(gpu);
+    });
+}
+
 int dali_lazy_set_dry_run(int on) {
     lazy::set_dry_run(on != 0);
     return DALIB200_OK;

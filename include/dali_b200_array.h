@@ -77,6 +77,10 @@ int dali_op_dot(dali_array_t a, dali_array_t b, dali_array_t* out);
 /* ---- assignment (array.h:201-205, 233-241): op 0 '=', 1 '+=', 2 '-=', 3 '*=', 4 '/=', 5 '<<=' */
 int dali_array_assign(dali_array_t dest, int op, dali_array_t value);
 
+/* memory::default_preferred_device = Device::gpu(gpu) (dali/runtime_config.cpp:12-18): where
+ * newly created Arrays compute.  One process per GPU sets its own index. */
+int dali_set_default_device(int gpu);
+
 /* ---- introspection of the lowering, for tests (kernels, gemms, temporaries launched by
  * this thread so far) and the IR / kernel variant of the last fused kernel ----------- */
 int dali_lazy_stats(int64_t counts[3]);
