@@ -235,7 +235,7 @@ class Chain(Workload):
         m = min(self.n, 1 << 22)
         xs = self.x[:m].contiguous()
         o = self.torch.zeros(1, dtype=self.torch.float32, device="cuda")
-        self.lib.launch(self.h, (m,), [o, xs], scalars=[self.w, self.b], stream=self.stream)
+        self.lib.launch(self.h, (m,), [o, xs], scalars=[self.w, self.b], device=self.device, stream=self.stream)
         self.torch.cuda.synchronize()
         s32, s64, sabs = oracle.chain_sum(xs.cpu().numpy(), 0.5, 0.1)
         assert abs(float(o.item()) - s64) <= 1e-5 * sabs, (float(o.item()), s64)
@@ -757,23 +757,33 @@ def measure(wl, torch, world, steps, warmup, lib, sample_clocks=True, local=0):
         sampler.start()
     launches0 = lib.cache_stats()["launches"]
     block_ms = []
-    t_end = time.time() + (1.5 if sample_clocks else 0.0)
-    while True:
+
+    def one_block():
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         if stepper:
-            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             ev0.record(stepper.stream)
             stepper.replay()
             ev1.record(stepper.stream)
         else:
-            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             ev0.record()
             for i in range(steps):
                 wl.step(warmup + i)
             ev1.record()
         barrier()
         block_ms.append(ev0.elapsed_time(ev1))
-        if time.time() > t_end or len(block_ms) >= 200:
-            break
+
+    one_block()        # the reported block: exactly `steps` steps
+    # more blocks only to keep the GPU busy ~1.5 s while nvidia-smi samples the clocks; every rank must run
+    # the same number of them (each ends in a barrier), so the count is agreed on, not timed per rank
+    extra = 0
+    if sample_clocks:
+        extra = int(min(200, max(0, 1500.0 / max(block_ms[0], 1e-3))))
+        if world > 1:
+            cnt = torch.tensor([extra], dtype=torch.int64, device="cuda")
+            torch.distributed.all_reduce(cnt, op=torch.distributed.ReduceOp.MAX)
+            extra = int(cnt.item())
+    for _ in range(extra):
+        one_block()
     clocks = sampler.stop() if sampler else None
     # the reported figure is the FIRST timed block of exactly `steps` steps; later blocks only keep
     # the GPU busy while nvidia-smi samples the clocks

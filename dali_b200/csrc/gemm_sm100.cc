@@ -342,6 +342,7 @@ int dalib200_gemm_fused(int device, void* stream, int ab_dtype, int64_t m, int64
                         const void* b, int64_t ldb, const void* a_lo, const void* b_lo, uint64_t epilogue_hash,
                         void* const* array_data, const int64_t* offsets, const int64_t* const* strides, int n_arrays,
                         const void* const* scalars, int n_scalars) {
+    DeviceRestore restore_device;
     if (ab_dtype != DALIB200_BF16 && ab_dtype != DALIB200_F32) {
         set_error("dalib200_gemm_fused: operands must be bf16 or f32");
         return DALIB200_ERR_INVALID;
@@ -395,6 +396,7 @@ int dalib200_gemm_fused(int device, void* stream, int ab_dtype, int64_t m, int64
 
 int dalib200_gemm_split_tf32(int device, void* stream, const float* x, int64_t rows, int64_t cols, int64_t ld, int transpose,
                              float* hi, float* lo) {
+    DeviceRestore restore_device;
     int ord = device_ordinal(device);
     if (ord < 0) { set_error("device index out of range"); return dalib200_device_count() ? DALIB200_ERR_INVALID : DALIB200_ERR_NO_DEVICE; }
     if (!x || !hi || !lo || cols % 4 || ld % 4 || ((uintptr_t)x & 15) || ((uintptr_t)hi & 15) || ((uintptr_t)lo & 15)) {
@@ -411,6 +413,7 @@ int dalib200_gemm_split_tf32(int device, void* stream, const float* x, int64_t r
 }
 
 int dalib200_gemm_error_flag(int device, int* flag) {
+    DeviceRestore restore_device;
     int ord = device_ordinal(device);
     if (ord < 0) { set_error("device index out of range"); return DALIB200_ERR_INVALID; }
     int* w = gemm_error_word(device);

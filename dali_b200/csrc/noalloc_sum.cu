@@ -94,6 +94,7 @@ unsigned char* g_scratch_addr[kMaxDevices] = {nullptr};
 }  // namespace
 
 extern "C" int dalib200_sum_f32_noalloc(int device, void* stream, const float* x, int64_t n, float* out) {
+    dalib::DeviceRestore restore_device;
     if (device < 0 || device >= kMaxDevices || device >= dalib200_device_count()) {
         dalib::set_error("dalib200_sum_f32_noalloc: device index out of range (call dalib200_init first)");
         return dalib200_device_count() == 0 ? DALIB200_ERR_NO_DEVICE : DALIB200_ERR_INVALID;

@@ -35,6 +35,14 @@ static thread_local std::string tl_variant;
 void set_error(const std::string& msg) { tl_error = msg; }
 const std::string& get_error() { return tl_error; }
 
+DeviceRestore::DeviceRestore() : prev(-1) {
+    if (cudaGetDevice(&prev) != cudaSuccess) { prev = -1; cudaGetLastError(); }
+}
+DeviceRestore::~DeviceRestore() {
+    int cur = -1;
+    if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+}
+
 uint64_t fnv1a(const std::string& s, uint64_t h) {
     for (unsigned char c : s) { h ^= c; h *= 1099511628211ull; }
     return h;
@@ -542,6 +550,7 @@ int dalib200_is_loaded(uint64_t hash) {
 
 int dalib200_precompile(uint64_t hash, const int64_t* space, int space_rank, void* const* array_data,
                         const int64_t* offsets, const int64_t* const* strides, int n_arrays, size_t* cubin_size) {
+    DeviceRestore restore_device;
     return do_launch(hash, 0, nullptr, space, space_rank, array_data, offsets, strides, n_arrays, nullptr, 0, true,
                      cubin_size);
 }
@@ -568,6 +577,7 @@ size_t dalib200_cache_get_dir(char* buffer, size_t capacity) {
 }
 
 int dalib200_cache_clear(int remove_files) {
+    DeviceRestore restore_device;
     State& s = S();
     std::lock_guard<std::mutex> g(s.mu);
     if (remove_files) {
@@ -601,6 +611,7 @@ int dalib200_cache_stats(uint64_t stats[5]) {
 int dalib200_launch(uint64_t hash, int device, void* stream, const int64_t* space, int space_rank,
                     void* const* array_data, const int64_t* offsets, const int64_t* const* strides, int n_arrays,
                     const void* const* scalars, int n_scalars) {
+    DeviceRestore restore_device;
     {
         State& s = S();
         std::lock_guard<std::mutex> g(s.mu);
@@ -614,6 +625,7 @@ int dalib200_launch(uint64_t hash, int device, void* stream, const int64_t* spac
 int dalib200_launch_host(uint64_t hash, int device, const int64_t* space, int space_rank, void* const* host_data,
                          const int64_t* extents, const int64_t* offsets, const int64_t* const* strides, int n_arrays,
                          const void* const* scalars, int n_scalars) {
+    DeviceRestore restore_device;
     State& s = S();
     std::vector<DType> dts;
     std::vector<bool> rd, wr;
@@ -658,6 +670,7 @@ size_t dalib200_last_variant(char* buffer, size_t capacity) {
 int dalib200_gemm(int device, void* stream, int dtype, int64_t m, int64_t n, int64_t k, const void* a, int64_t ars,
                   int64_t acs, const void* b, int64_t brs, int64_t bcs, void* c, int64_t crs, int64_t ccs, double alpha,
                   double beta) {
+    DeviceRestore restore_device;
     {
         State& s = S();
         std::lock_guard<std::mutex> g(s.mu);
@@ -686,6 +699,7 @@ size_t dalib200_last_gemm_kernel(char* buffer, size_t capacity) {
 }
 
 int dalib200_alloc(int device, size_t bytes, void** out) {
+    DeviceRestore restore_device;
     State& s = S();
     std::lock_guard<std::mutex> g(s.mu);
     int rc = check_device(device);
@@ -705,6 +719,7 @@ int dalib200_free(int device, void* ptr, size_t bytes) {
 }
 
 int dalib200_pool_clear(int device) {
+    DeviceRestore restore_device;
     State& s = S();
     std::lock_guard<std::mutex> g(s.mu);
     int rc = check_device(device);
@@ -719,6 +734,7 @@ int dalib200_pool_clear(int device) {
 }
 
 static int copy_common(int device, void* dst, const void* src, size_t bytes, void* stream, cudaMemcpyKind kind) {
+    DeviceRestore restore_device;
     {
         State& s = S();
         std::lock_guard<std::mutex> g(s.mu);
@@ -742,6 +758,7 @@ int dalib200_memcpy_d2d(int device, void* dst, const void* src, size_t bytes, vo
 }
 
 int dalib200_memset(int device, void* dst, int byte, size_t bytes, void* stream) {
+    DeviceRestore restore_device;
     {
         State& s = S();
         std::lock_guard<std::mutex> g(s.mu);
@@ -755,6 +772,7 @@ int dalib200_memset(int device, void* dst, int byte, size_t bytes, void* stream)
 }
 
 int dalib200_sync(int device, void* stream) {
+    DeviceRestore restore_device;
     {
         State& s = S();
         std::lock_guard<std::mutex> g(s.mu);

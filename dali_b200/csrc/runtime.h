@@ -43,6 +43,15 @@ bool nvrtc_compile(const std::string& source, const std::string& name,
 
 uint64_t fnv1a(const std::string& s, uint64_t seed = 1469598103934665603ull);
 
+// Entry points select the device they work on with cudaSetDevice; this puts the caller's
+// current device back when the entry point returns (a caller with several GPUs in one
+// process, or torch with its own notion of the current device, must not see it move).
+struct DeviceRestore {
+    int prev;
+    DeviceRestore();
+    ~DeviceRestore();
+};
+
 // ---- services of runtime.cc for the other translation units ------------------------
 // Copy of the program registered under `hash` (false if unknown).
 bool find_program(uint64_t hash, Program* out);
