@@ -864,7 +864,10 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
     torch.cuda.set_device(local)
     if world > 1:
-        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local))
+        import datetime
+        # a rank that falls out of step ends the run in two minutes, not ten
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local),
+                                             timeout=datetime.timedelta(seconds=120))
     lib = dali_b200.load_library()
     lib.init(0)
     dev_index = local      # the library indexes the devices it bound; one process per GPU uses its own
