@@ -269,11 +269,13 @@ class Softmax(Workload):
         self.o = [t.empty(self.ROWS, self.COLS, dtype=t.float32, device="cuda") for _ in range(self.nbuf)]
         self.h = self.lib.compile(softmax_ir())
         self.scaling = "weak"
+        self.lanes = int(os.environ.get("DALI_BENCH_SOFTMAX_LANES", "3"))   # independent batches on three streams
 
     def describe(self):
         return {"workload": "C1 exp(a-max(a,{-1},true))/sum(exped,{-1},true), fp32 [4096,1024] ~ N(0,1) per GPU",
                 "l2": "rotating over %d input/output buffer pairs (%d MiB) so every launch misses L2" %
                       (self.nbuf, self.nbuf * 32),
+                "concurrency": "%d streams: consecutive batches are independent and may overlap" % self.lanes,
                 "parallelism": "rows sharded: each of %d GPU(s) runs its own [4096,1024] batch, no collective" % self.world}
 
     def bytes_per_step(self):
@@ -327,21 +329,28 @@ class Softmax(Workload):
 
 
 class GraphStepper:
-    """Replays the launches of `fn(i)` for i in range(n) as one CUDA graph (device time without
-    Python between the kernels)."""
+    """Replays the launches of `fn(i, stream)` for i in range(n) as one CUDA graph (device time without
+    Python between the kernels).  With lanes > 1 step i goes to lane i % lanes: independent steps (separate
+    batches) form parallel chains in the graph, so one batch's tail overlaps the next one's ramp-up."""
 
-    def __init__(self, torch, fn, n):
+    def __init__(self, torch, fn, n, lanes=1):
         self.torch = torch
         self.stream = torch.cuda.Stream()
+        self.side = [torch.cuda.Stream() for _ in range(lanes - 1)]
         self.n = n
+        lanes_streams = [self.stream] + self.side
         with torch.cuda.stream(self.stream):
             for i in range(n):
-                fn(i, self.stream.cuda_stream)      # compile / load / warm pools outside the capture
+                fn(i, lanes_streams[i % lanes].cuda_stream)      # compile / load / warm pools outside the capture
             torch.cuda.synchronize()
             self.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph, stream=self.stream):
+                for s_ in self.side:
+                    s_.wait_stream(self.stream)                   # fork
                 for i in range(n):
-                    fn(i, self.stream.cuda_stream)
+                    fn(i, lanes_streams[i % lanes].cuda_stream)
+                for s_ in self.side:
+                    self.stream.wait_stream(s_)                   # join
         torch.cuda.synchronize()
 
     def replay(self):
@@ -357,7 +366,7 @@ class Lstm(Workload):
     def __init__(self, *a):
         super().__init__(*a)
         import numpy as np
-        from dali_b200.ir import IRBuilder, gemm_store_ir
+        from dali_b200.ir import IRBuilder
         self.np = np
         t, B, H = self.torch, self.B, self.H
         t.manual_seed(1234 + 1 + self.rank)
@@ -379,10 +388,9 @@ class Lstm(Workload):
             L.gemm_split_tf32(w, H, 4 * H, 4 * H, hi, lo, transpose=True, device=self.device)
             self.W[name] = (hi, lo)
         self.parts = [t.empty(B * H, device="cuda") for _ in range(4)]
-        self.h_store = L.compile(gemm_store_ir("f32"))
         e = IRBuilder(2, 0)
-        o, first, bias = e.arg("f32"), e.arg("f32"), e.arg("f32")
-        e.st(o, e.op("add", e.op("add", e.acc(), e.ld(first)), e.ld(bias)))      # x.Wx + h.Wh + b
+        o, bias = e.arg("f32"), e.arg("f32")
+        e.st(o, e.op("add", e.acc(), e.ld(bias)))      # acc = x.Wx + h.Wh (one accumulator), + b
         self.h_epi = L.compile(e.text())
         g = IRBuilder(2, 0)                                                         # the gating kernel the front end emits
         out = g.arg("f32")
@@ -401,14 +409,14 @@ class Lstm(Workload):
         self.h_gate_c = L.compile(g.text())
         self.h_gate_h = L.compile(gh.text())
         self.scaling = "weak"
-        self.launches_per_step = 6
+        self.launches_per_step = 5
 
     def describe(self):
         return {"workload": "C2 LSTM cell step: gates = dot(x,Wx)+dot(h,Wh)+b, c' = sig(f)*c + sig(i)*tanh(g), "
                             "h' = sig(o)*tanh(c'); fp32, B=256 H=1024 per GPU, x,h,c ~ N(0,1), W ~ N(0,0.02), b = 0",
                 "l2": "activations rotate over %d sets; the two weight matrices are reused every step (as in an RNN) "
                       "and stay in L2" % self.nset,
-                "kernels_per_step": "2 TF32 splits (x, h), 2 tcgen05 3xTF32 GEMMs, 2 fused gating kernels",
+                "kernels_per_step": "2 TF32 splits (x, h), 1 tcgen05 3xTF32 GEMM accumulating x.Wx + h.Wh with '+ b' as epilogue, 2 fused gating kernels",
                 "parallelism": "batch sharded: each of %d GPU(s) runs its own B=256 shard, weights replicated, no collective" % self.world}
 
     def bytes_per_step(self):
@@ -423,15 +431,18 @@ class Lstm(Workload):
         d = self.device
         L.gemm_split_tf32(self.x[k], B, H, H, self.parts[0], self.parts[1], device=d, stream=stream)
         L.gemm_split_tf32(self.h[k], B, H, H, self.parts[2], self.parts[3], device=d, stream=stream)
-        L.gemm_fused(0, B, 4 * H, H, self.parts[0], H, self.W["Wx"][0], H, self.h_store, [self.gates],
-                     a_lo=self.parts[1], b_lo=self.W["Wx"][1], device=d, stream=stream)
-        L.gemm_fused(0, B, 4 * H, H, self.parts[2], H, self.W["Wh"][0], H, self.h_epi, [self.gates, self.gates, self.b],
-                     strides=[None, None, [0, 1]], a_lo=self.parts[3], b_lo=self.W["Wh"][1], device=d, stream=stream)
+        self.launch_gemm(stream)
         gs = [4 * H, 1]
         G = self.gates
         for hsh, out in ((self.h_gate_h, self.h_new[k]), (self.h_gate_c, self.c_new[k])):
             L.launch(hsh, (B, H), [out, G, G, G, G, self.c[k]], strides=[None, gs, gs, gs, gs, None],
                      offsets=[0, 0, H, 2 * H, 3 * H, 0], device=d, stream=stream)
+
+    def launch_gemm(self, stream):
+        B, H, P, W = self.B, self.H, self.parts, self.W
+        self.lib.gemm_fused_sum(0, B, 4 * H, [(H, P[0], H, W["Wx"][0], H, P[1], W["Wx"][1]),
+                                              (H, P[2], H, W["Wh"][0], H, P[3], W["Wh"][1])],
+                                self.h_epi, [self.gates, self.b], strides=[None, [0, 1]], device=self.device, stream=stream)
 
     def step(self, i):
         self.launch_step(i, self.stream)
@@ -440,13 +451,10 @@ class Lstm(Workload):
         return self.launch_step
 
     def dominant(self):
-        """(name, launches per step, bound, algorithmic work per launch, launcher) of the dominant kernel."""
+        """(name, bound, algorithmic work per launch, launcher) of the dominant kernel."""
         B, H = self.B, self.H
-
-        def one(i, stream):
-            self.lib.gemm_fused(0, B, 4 * H, H, self.parts[0], H, self.W["Wx"][0], H, self.h_store, [self.gates],
-                                a_lo=self.parts[1], b_lo=self.W["Wx"][1], device=self.device, stream=stream)
-        return ("tcgen05 3xTF32 GEMM [256,1024]x[1024,4096]", "tensor", 2.0 * B * H * 4 * H, one)
+        return ("tcgen05 3xTF32 GEMM [256,1024]x[1024,4096] + [256,1024]x[1024,4096], one accumulator", "tensor",
+                2.0 * 2 * B * H * 4 * H, lambda i, stream: self.launch_gemm(stream))
 
     def e2e_setup(self):
         np = self.np
@@ -747,7 +755,7 @@ def measure(wl, torch, world, steps, warmup, lib, sample_clocks=True, local=0):
         wl.step(i)
     barrier()
     fn = wl.graph_fn()
-    stepper = GraphStepper(torch, lambda i, st: fn(warmup + i, st), steps) if fn else None
+    stepper = GraphStepper(torch, lambda i, st: fn(warmup + i, st), steps, getattr(wl, "lanes", 1)) if fn else None
     if stepper:
         for _ in range(2):
             stepper.replay()

@@ -67,6 +67,10 @@ class Library:
                                           ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint64,
                                           ctypes.POINTER(ctypes.c_void_p), c_i64p, ctypes.POINTER(c_i64p), ctypes.c_int,
                                           ctypes.POINTER(ctypes.c_void_p), ctypes.c_int]
+        vpp = ctypes.POINTER(ctypes.c_void_p)
+        c.dalib200_gemm_fused_sum.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int64,
+                                              ctypes.c_int64, c_i64p, vpp, c_i64p, vpp, c_i64p, vpp, vpp, ctypes.c_uint64,
+                                              vpp, c_i64p, ctypes.POINTER(c_i64p), ctypes.c_int, vpp, ctypes.c_int]
         c.dalib200_gemm_split_tf32.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
                                                ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_void_p,
                                                ctypes.c_void_p]
@@ -209,6 +213,25 @@ class Library:
                                               self._ptr(b), ldb, self._ptr(a_lo) if a_lo is not None else None,
                                               self._ptr(b_lo) if b_lo is not None else None, ctypes.c_uint64(epilogue_hash),
                                               ptrs, offs, st, na, sc, len(scalars or [])))
+
+    def gemm_fused_sum(self, ab_dtype, m, n, pairs, epilogue_hash, arrays, strides=None, offsets=None, scalars=None,
+                       device=0, stream=None):
+        """acc = sum over pairs of A_p[m,k_p] . B_p[k_p,n] in one launch, then the epilogue program.  Each pair is
+        (k, a, lda, b, ldb) or, with the TF32 split parts of fp32 operands, (k, a_hi, lda, b_hi, ldb, a_lo, b_lo)."""
+        na, npairs = len(arrays), len(pairs)
+        ptrs = (ctypes.c_void_p * na)(*[(x.data_ptr() if hasattr(x, "data_ptr") else int(x)) for x in arrays])
+        offs = _i64_array(offsets if offsets else [0] * na)
+        st, keep = self._strides_arg(strides, na)
+        sc, keep2 = self._scalars_arg(scalars)
+
+        def col(j):
+            return (ctypes.c_void_p * npairs)(*[self._ptr(p[j]).value for p in pairs])
+        with_lo = all(len(p) == 7 for p in pairs)
+        self.check(self.c.dalib200_gemm_fused_sum(device, ctypes.c_void_p(stream or 0), ab_dtype, npairs, m, n,
+                                                  _i64_array([p[0] for p in pairs]), col(1), _i64_array([p[2] for p in pairs]),
+                                                  col(3), _i64_array([p[4] for p in pairs]), col(5) if with_lo else None,
+                                                  col(6) if with_lo else None, ctypes.c_uint64(epilogue_hash), ptrs, offs, st,
+                                                  na, sc, len(scalars or [])))
 
     def gemm_split_tf32(self, x, rows, cols, ld, hi, lo, transpose=False, device=0, stream=None):
         self.check(self.c.dalib200_gemm_split_tf32(device, ctypes.c_void_p(stream or 0), self._ptr(x), rows, cols, ld,

@@ -263,7 +263,7 @@ GemmVariant choose_variant(bool bf16, int64_t m, int64_t n) {
 }
 
 struct GemmP {
-    long long M, N, K;
+    long long M, N, K, K2;
     int* err;
     long long w[64];
 };
@@ -274,12 +274,17 @@ thread_local std::string tl_gemm_variant;
 
 const std::string& last_gemm_variant() { return tl_gemm_variant; }
 
-// a, b: device pointers; lda / ldb in elements.  For fp32 the caller passes the
-// already split operands (hi / lo); see dalib200_gemm_fused.
-int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n, int64_t k, const void* a, const void* a_lo,
-                      int64_t lda, const void* b, const void* b_lo, int64_t ldb, uint64_t epilogue_hash, void* const* array_data,
-                      const int64_t* offsets, const int64_t* const* strides, int n_arrays, const void* const* scalars, int n_scalars,
-                      bool compile_only) {
+// One operand pair of acc = sum_p A_p . B_p.  a / b: device pointers; lda / ldb in elements.  For
+// fp32 these are the already split operands (hi parts in a / b, lo parts in a_lo / b_lo, B transposed).
+struct GemmPair {
+    int64_t k;
+    const void *a, *a_lo, *b, *b_lo;
+    int64_t lda, ldb;
+};
+
+int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n, const GemmPair* pairs, int n_pairs,
+                      uint64_t epilogue_hash, void* const* array_data, const int64_t* offsets, const int64_t* const* strides,
+                      int n_arrays, const void* const* scalars, int n_scalars, bool compile_only) {
     Program prog;
     if (!find_program(epilogue_hash, &prog)) { set_error("unknown epilogue hash"); return DALIB200_ERR_NOT_FOUND; }
     if (n_arrays != (int)prog.args.size() || n_scalars != (int)prog.scalars.size()) {
@@ -290,29 +295,33 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
     GemmSourceCtx ctx{&prog, choose_variant(bf16, m, n)};
     const GemmVariant& v = ctx.v;
     std::ostringstream key;
-    key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + "|sm_100a|gemm-3|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" +
+    key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + "|sm_100a|gemm-4|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" +
                                                      std::to_string(fnv1a(device_prelude())));
-    tl_gemm_variant = std::string(bf16 ? "tcgen05.bf16 " : "tcgen05.tf32x3 ") + v.key();
+    tl_gemm_variant = std::string(bf16 ? "tcgen05.bf16 " : "tcgen05.tf32x3 ") + v.key() + (n_pairs > 1 ? " x2" : "");
     note_gemm_kernel(tl_gemm_variant);
     void* fn = nullptr;
     int rc = acquire_kernel(compile_only ? -1 : device, key.str(), "dali_gemm_kernel", gemm_source, &ctx, &fn, nullptr);
     if (rc != DALIB200_OK || compile_only) return rc;
 
     std::string err;
-    CUtensorMap tmA, tmB, tmAlo, tmBlo;
+    CUtensorMap tm[8];
     const uint32_t sw = 128 / v.esize;
-    if (!make_map(&tmA, bf16, a, (uint64_t)k, (uint64_t)m, (uint64_t)lda, (uint32_t)v.bk, (uint32_t)v.bm, &err) ||
-        !(v.b_kmajor() ? make_map(&tmB, bf16, b, (uint64_t)k, (uint64_t)n, (uint64_t)ldb, (uint32_t)v.bk, (uint32_t)v.bn, &err)
-                       : make_map(&tmB, bf16, b, (uint64_t)n, (uint64_t)k, (uint64_t)ldb, sw, (uint32_t)v.bk, &err)) ||
-        !make_map(&tmAlo, bf16, a_lo ? a_lo : a, (uint64_t)k, (uint64_t)m, (uint64_t)lda, (uint32_t)v.bk, (uint32_t)v.bm, &err) ||
-        !(v.b_kmajor() ? make_map(&tmBlo, bf16, b_lo ? b_lo : b, (uint64_t)k, (uint64_t)n, (uint64_t)ldb, (uint32_t)v.bk, (uint32_t)v.bn, &err)
-                       : make_map(&tmBlo, bf16, b_lo ? b_lo : b, (uint64_t)n, (uint64_t)k, (uint64_t)ldb, sw, (uint32_t)v.bk, &err))) {
-        set_error("gemm_fused: " + err);
-        return DALIB200_ERR_CUDA;
+    for (int pi = 0; pi < 2; ++pi) {
+        const GemmPair& g = pairs[pi < n_pairs ? pi : 0];     // an unused second set just repeats the first
+        const uint64_t k = (uint64_t)g.k;
+        bool ok = make_map(&tm[4 * pi + 0], bf16, g.a, k, (uint64_t)m, (uint64_t)g.lda, (uint32_t)v.bk, (uint32_t)v.bm, &err) &&
+                  make_map(&tm[4 * pi + 2], bf16, g.a_lo ? g.a_lo : g.a, k, (uint64_t)m, (uint64_t)g.lda, (uint32_t)v.bk, (uint32_t)v.bm, &err);
+        if (ok && v.b_kmajor())
+            ok = make_map(&tm[4 * pi + 1], bf16, g.b, k, (uint64_t)n, (uint64_t)g.ldb, (uint32_t)v.bk, (uint32_t)v.bn, &err) &&
+                 make_map(&tm[4 * pi + 3], bf16, g.b_lo ? g.b_lo : g.b, k, (uint64_t)n, (uint64_t)g.ldb, (uint32_t)v.bk, (uint32_t)v.bn, &err);
+        else if (ok)
+            ok = make_map(&tm[4 * pi + 1], bf16, g.b, (uint64_t)n, k, (uint64_t)g.ldb, sw, (uint32_t)v.bk, &err) &&
+                 make_map(&tm[4 * pi + 3], bf16, g.b_lo ? g.b_lo : g.b, (uint64_t)n, k, (uint64_t)g.ldb, sw, (uint32_t)v.bk, &err);
+        if (!ok) { set_error("gemm_fused: " + err); return DALIB200_ERR_CUDA; }
     }
     GemmP p;
     std::memset(&p, 0, sizeof p);
-    p.M = m; p.N = n; p.K = k;
+    p.M = m; p.N = n; p.K = pairs[0].k; p.K2 = n_pairs > 1 ? pairs[1].k : 0;
     p.err = gemm_error_word(device);
     if (!p.err) { set_error("gemm_fused: cannot allocate the error word"); return DALIB200_ERR_CUDA; }
     for (int i = 0; i < n_arrays; ++i) {
@@ -327,7 +336,7 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
         p.w[3 * n_arrays + j] = w;
     }
     // the kernel's GemmP has exactly GEMM_EPI_WORDS words; ours is a superset with the same prefix
-    void* params[] = {&tmA, &tmB, &tmAlo, &tmBlo, &p};
+    void* params[] = {&tm[0], &tm[1], &tm[2], &tm[3], &tm[4], &tm[5], &tm[6], &tm[7], &p};
     const unsigned gx = (unsigned)((n + v.bn - 1) / v.bn), gy = (unsigned)((m + v.bm - 1) / v.bm);
     return launch_function(device, fn, gx, gy, 192, (unsigned)v.smem_bytes(), stream, params);
 }
@@ -338,60 +347,85 @@ using namespace dalib;
 
 extern "C" {
 
-int dalib200_gemm_fused(int device, void* stream, int ab_dtype, int64_t m, int64_t n, int64_t k, const void* a, int64_t lda,
-                        const void* b, int64_t ldb, const void* a_lo, const void* b_lo, uint64_t epilogue_hash,
-                        void* const* array_data, const int64_t* offsets, const int64_t* const* strides, int n_arrays,
-                        const void* const* scalars, int n_scalars) {
+int dalib200_gemm_fused_sum(int device, void* stream, int ab_dtype, int n_pairs, int64_t m, int64_t n, const int64_t* k,
+                            const void* const* a, const int64_t* lda, const void* const* b, const int64_t* ldb,
+                            const void* const* a_lo, const void* const* b_lo, uint64_t epilogue_hash,
+                            void* const* array_data, const int64_t* offsets, const int64_t* const* strides, int n_arrays,
+                            const void* const* scalars, int n_scalars) {
     DeviceRestore restore_device;
     if (ab_dtype != DALIB200_BF16 && ab_dtype != DALIB200_F32) {
         set_error("dalib200_gemm_fused: operands must be bf16 or f32");
         return DALIB200_ERR_INVALID;
     }
-    if (m < 0 || n < 0 || k < 0 || !a || !b) { set_error("dalib200_gemm_fused: bad argument"); return DALIB200_ERR_INVALID; }
+    if (n_pairs < 1 || n_pairs > 2 || m < 0 || n < 0 || !k || !a || !b || !lda || !ldb) {
+        set_error("dalib200_gemm_fused: bad argument (one or two operand pairs)");
+        return DALIB200_ERR_INVALID;
+    }
     if (m == 0 || n == 0) return DALIB200_OK;
     const bool bf16 = ab_dtype == DALIB200_BF16;
     const int es = bf16 ? 2 : 4;
-    // what TMA needs: 16-byte aligned bases and row pitches
-    const bool presplit = !bf16 && a_lo && b_lo;       // then b / b_lo are the TRANSPOSED parts, [n,k] with pitch ldb
-    if (((uintptr_t)a & 15) || ((uintptr_t)b & 15) || (lda * es) % 16 || (ldb * es) % 16 || lda < k || ldb < (presplit ? k : n) ||
-        (a_lo && ((uintptr_t)a_lo & 15)) || (b_lo && ((uintptr_t)b_lo & 15)) || m > 2147483647LL || n > 2147483647LL ||
-        k > 2147483647LL) {
-        set_error("dalib200_gemm_fused: operands must be row-major with 16-byte aligned base and row pitch");
-        return DALIB200_ERR_UNSUPPORTED;
-    }
     const bool compile_only = device < 0;
-    if (!bf16 && ((a_lo != nullptr) != (b_lo != nullptr))) {
-        set_error("dalib200_gemm_fused: pass both split operands or neither");
-        return DALIB200_ERR_INVALID;
+    bool presplit = !bf16 && a_lo && b_lo && a_lo[0] && b_lo[0];
+    GemmPair pairs[2];
+    for (int p = 0; p < n_pairs; ++p) {
+        const bool lo_a = a_lo && a_lo[p], lo_b = b_lo && b_lo[p];
+        if (!bf16 && (lo_a != lo_b || (lo_a && lo_b) != presplit)) {
+            set_error("dalib200_gemm_fused: pass the split parts of every operand or of none");
+            return DALIB200_ERR_INVALID;
+        }
+        if (!a[p] || !b[p] || k[p] < 0) { set_error("dalib200_gemm_fused: bad operand pair"); return DALIB200_ERR_INVALID; }
+        // what TMA needs: 16-byte aligned bases and row pitches
+        if (((uintptr_t)a[p] & 15) || ((uintptr_t)b[p] & 15) || (lda[p] * es) % 16 || (ldb[p] * es) % 16 || lda[p] < k[p] ||
+            ldb[p] < (presplit ? k[p] : n) || (lo_a && ((uintptr_t)a_lo[p] & 15)) || (lo_b && ((uintptr_t)b_lo[p] & 15)) ||
+            m > 2147483647LL || n > 2147483647LL || k[p] > 2147483647LL) {
+            set_error("dalib200_gemm_fused: operands must be row-major with 16-byte aligned base and row pitch");
+            return DALIB200_ERR_UNSUPPORTED;
+        }
+        pairs[p] = GemmPair{k[p], a[p], lo_a ? a_lo[p] : nullptr, b[p], lo_b ? b_lo[p] : nullptr, lda[p], ldb[p]};
     }
     if (bf16 || compile_only || presplit)
-        return gemm_fused_launch(device, stream, bf16, m, n, k, a, a_lo, lda, b, b_lo, ldb, epilogue_hash, array_data, offsets,
-                                 strides, n_arrays, scalars, n_scalars, compile_only);
+        return gemm_fused_launch(device, stream, bf16, m, n, pairs, n_pairs, epilogue_hash, array_data, offsets, strides,
+                                 n_arrays, scalars, n_scalars, compile_only);
     // fp32 without pre-split operands: split here into pool temporaries (recycled in stream order)
-    if (k % 4 || n % 4) { set_error("dalib200_gemm_fused: fp32 operands need k and n to be multiples of 4"); return DALIB200_ERR_UNSUPPORTED; }
-    if (a_lo || b_lo) { set_error("dalib200_gemm_fused: pass both split operands or neither"); return DALIB200_ERR_INVALID; }
     int ord = device_ordinal(device);
     if (ord < 0) { set_error("device index out of range"); return DALIB200_ERR_INVALID; }
     cudaSetDevice(ord);
-    void *ahi = nullptr, *alo = nullptr, *bhi = nullptr, *blo = nullptr;
-    const size_t abytes = (size_t)m * k * 4, bbytes = (size_t)k * n * 4;
-    int rc = dalib200_alloc(device, abytes, &ahi);
-    if (rc == DALIB200_OK) rc = dalib200_alloc(device, abytes, &alo);
-    if (rc == DALIB200_OK) rc = dalib200_alloc(device, bbytes, &bhi);
-    if (rc == DALIB200_OK) rc = dalib200_alloc(device, bbytes, &blo);
-    if (rc == DALIB200_OK && (split_tf32((cudaStream_t)stream, (const float*)a, m, k, lda, false, (float*)ahi, (float*)alo) != cudaSuccess ||
-                              split_tf32((cudaStream_t)stream, (const float*)b, k, n, ldb, true, (float*)bhi, (float*)blo) != cudaSuccess)) {
-        set_error("split_tf32 launch failed");
-        rc = DALIB200_ERR_CUDA;
+    void* tmp[8] = {nullptr};
+    size_t bytes[8] = {0};
+    int rc = DALIB200_OK;
+    for (int p = 0; p < n_pairs && rc == DALIB200_OK; ++p) {
+        if (k[p] % 4 || n % 4) { set_error("dalib200_gemm_fused: fp32 operands need k and n to be multiples of 4"); rc = DALIB200_ERR_UNSUPPORTED; break; }
+        bytes[4 * p] = bytes[4 * p + 1] = (size_t)m * k[p] * 4;
+        bytes[4 * p + 2] = bytes[4 * p + 3] = (size_t)k[p] * n * 4;
+        for (int j = 0; j < 4 && rc == DALIB200_OK; ++j) rc = dalib200_alloc(device, bytes[4 * p + j], &tmp[4 * p + j]);
+        if (rc != DALIB200_OK) break;
+        if (split_tf32((cudaStream_t)stream, (const float*)a[p], m, k[p], lda[p], false, (float*)tmp[4 * p], (float*)tmp[4 * p + 1]) != cudaSuccess ||
+            split_tf32((cudaStream_t)stream, (const float*)b[p], k[p], n, ldb[p], true, (float*)tmp[4 * p + 2], (float*)tmp[4 * p + 3]) != cudaSuccess) {
+            set_error("split_tf32 launch failed");
+            rc = DALIB200_ERR_CUDA;
+        }
+        pairs[p] = GemmPair{k[p], tmp[4 * p], tmp[4 * p + 1], tmp[4 * p + 2], tmp[4 * p + 3], k[p], k[p]};
     }
     if (rc == DALIB200_OK)
-        rc = gemm_fused_launch(device, stream, false, m, n, k, ahi, alo, k, bhi, blo, k, epilogue_hash, array_data, offsets,
-                               strides, n_arrays, scalars, n_scalars, false);
-    if (ahi) dalib200_free(device, ahi, abytes);
-    if (alo) dalib200_free(device, alo, abytes);
-    if (bhi) dalib200_free(device, bhi, bbytes);
-    if (blo) dalib200_free(device, blo, bbytes);
+        rc = gemm_fused_launch(device, stream, false, m, n, pairs, n_pairs, epilogue_hash, array_data, offsets, strides, n_arrays,
+                               scalars, n_scalars, false);
+    for (int j = 0; j < 8; ++j)
+        if (tmp[j]) dalib200_free(device, tmp[j], bytes[j]);
     return rc;
+}
+
+int dalib200_gemm_fused(int device, void* stream, int ab_dtype, int64_t m, int64_t n, int64_t k, const void* a, int64_t lda,
+                        const void* b, int64_t ldb, const void* a_lo, const void* b_lo, uint64_t epilogue_hash,
+                        void* const* array_data, const int64_t* offsets, const int64_t* const* strides, int n_arrays,
+                        const void* const* scalars, int n_scalars) {
+    if (ab_dtype == DALIB200_F32 && ((a_lo != nullptr) != (b_lo != nullptr))) {
+        set_error("dalib200_gemm_fused: pass both split operands or neither");
+        return DALIB200_ERR_INVALID;
+    }
+    if (!a || !b) { set_error("dalib200_gemm_fused: bad argument"); return DALIB200_ERR_INVALID; }
+    return dalib200_gemm_fused_sum(device, stream, ab_dtype, 1, m, n, &k, &a, &lda, &b, &ldb, a_lo ? &a_lo : nullptr,
+                                   b_lo ? &b_lo : nullptr, epilogue_hash, array_data, offsets, strides, n_arrays, scalars,
+                                   n_scalars);
 }
 
 int dalib200_gemm_split_tf32(int device, void* stream, const float* x, int64_t rows, int64_t cols, int64_t ld, int transpose,

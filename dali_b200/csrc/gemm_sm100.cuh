@@ -34,7 +34,8 @@
 struct alignas(64) TensorMap { unsigned long long opaque[16]; };
 
 struct GemmP {
-    long long M, N, K;
+    long long M, N, K;        // K: reduction length of the first (or only) operand pair
+    long long K2;             // of the second pair (0 = none): acc = A.B + A2.B2 in one accumulator
     int* err;                 // device int, 0 = fine
     long long w[GEMM_EPI_WORDS];
 };
@@ -171,6 +172,8 @@ DEV float bf16_to_f32(unsigned short b) { return __uint_as_float(((unsigned)b) <
 extern "C" __global__ void __launch_bounds__(GEMM_THREADS, 1)
 dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ TensorMap tmB,
                  const __grid_constant__ TensorMap tmAlo, const __grid_constant__ TensorMap tmBlo,
+                 const __grid_constant__ TensorMap tmA2, const __grid_constant__ TensorMap tmB2,
+                 const __grid_constant__ TensorMap tmA2lo, const __grid_constant__ TensorMap tmB2lo,
                  const __grid_constant__ GemmP p) {
     using namespace gemm;
     extern __shared__ unsigned char smem_raw[];
@@ -184,7 +187,8 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long m0 = (long long)blockIdx.y * GEMM_BM, n0 = (long long)blockIdx.x * GEMM_BN;
-    const int num_kb = (int)((p.K + GEMM_BK - 1) / GEMM_BK);
+    const int num_kb1 = (int)((p.K + GEMM_BK - 1) / GEMM_BK);
+    const int num_kb = num_kb1 + (int)((p.K2 + GEMM_BK - 1) / GEMM_BK);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < GEMM_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -206,25 +210,32 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
             if (!mbar_wait(&empty_bar[s], parity ^ 1u, &abort_flag)) { atomicExch(p.err, 1); abort_flag = 1; break; }
             unsigned char* st = tiles + (size_t)s * GEMM_STAGE_BYTES;
             mbar_expect_tx(&full_bar[s], GEMM_STAGE_BYTES);
-            tma_load_2d(st, &tmA, &full_bar[s], kb * GEMM_BK, (int)m0);
+            // K blocks of the second operand pair follow those of the first
+            const bool second = kb >= num_kb1;
+            const int kx = (second ? kb - num_kb1 : kb) * GEMM_BK;
+            const TensorMap* mA = second ? &tmA2 : &tmA;
+            const TensorMap* mB = second ? &tmB2 : &tmB;
+            tma_load_2d(st, mA, &full_bar[s], kx, (int)m0);
             unsigned char* bt = st + GEMM_A_TILE_BYTES;
 #if GEMM_B_KMAJOR
-            tma_load_2d(bt, &tmB, &full_bar[s], kb * GEMM_BK, (int)n0);
+            tma_load_2d(bt, mB, &full_bar[s], kx, (int)n0);
 #else
 #pragma unroll
             for (int j = 0; j < GEMM_B_ATOMS; ++j)
-                tma_load_2d(bt + j * GEMM_B_ATOM_BYTES, &tmB, &full_bar[s], (int)n0 + j * GEMM_SWIZZLE_ELEMS, kb * GEMM_BK);
+                tma_load_2d(bt + j * GEMM_B_ATOM_BYTES, mB, &full_bar[s], (int)n0 + j * GEMM_SWIZZLE_ELEMS, kx);
 #endif
 #if GEMM_SPLIT
+            const TensorMap* mAlo = second ? &tmA2lo : &tmAlo;
+            const TensorMap* mBlo = second ? &tmB2lo : &tmBlo;
             unsigned char* alo = bt + GEMM_B_TILE_BYTES;
-            tma_load_2d(alo, &tmAlo, &full_bar[s], kb * GEMM_BK, (int)m0);
+            tma_load_2d(alo, mAlo, &full_bar[s], kx, (int)m0);
             unsigned char* blo = alo + GEMM_A_TILE_BYTES;
 #if GEMM_B_KMAJOR
-            tma_load_2d(blo, &tmBlo, &full_bar[s], kb * GEMM_BK, (int)n0);
+            tma_load_2d(blo, mBlo, &full_bar[s], kx, (int)n0);
 #else
 #pragma unroll
             for (int j = 0; j < GEMM_B_ATOMS; ++j)
-                tma_load_2d(blo + j * GEMM_B_ATOM_BYTES, &tmBlo, &full_bar[s], (int)n0 + j * GEMM_SWIZZLE_ELEMS, kb * GEMM_BK);
+                tma_load_2d(blo + j * GEMM_B_ATOM_BYTES, mBlo, &full_bar[s], (int)n0 + j * GEMM_SWIZZLE_ELEMS, kx);
 #endif
 #endif
         }

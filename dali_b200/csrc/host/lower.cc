@@ -104,7 +104,8 @@ struct Lowerer {
     std::map<std::pair<const Expression*, std::string>, int> memo;
     std::map<const Expression*, int> scalar_slot;
     std::vector<Array> keep_alive;
-    const Expression* acc_node = nullptr;    // the MatMul whose product is the GEMM accumulator (epilogue programs)
+    // the node whose value is the GEMM accumulator (epilogue programs): a MatMul, or the sum of two of them
+    const Expression* acc_node = nullptr;
 
     Lowerer(const std::vector<int64_t>& space_, int nreduce_, memory::Device dev)
         : space(space_), rank((int)space_.size()), nreduce(nreduce_), n_outer(rank - nreduce_), device(dev) {}
@@ -218,6 +219,7 @@ struct Lowerer {
             }
             case N_ELEMENTWISE: {
                 Elementwise* w = static_cast<Elementwise*>(e.get());
+                if (e.get() == acc_node && is_identity(m)) { id = new_value(DTYPE_FLOAT, true, "acc"); break; }
                 std::vector<int> in;
                 bool is_elem = false;
                 for (const Array& arg : w->arguments_) {
@@ -293,9 +295,7 @@ struct Lowerer {
                 break;
             }
             case N_MATMUL: {
-                bool identity = (int)m.size() == 2 && m[0].src == 0 && m[1].src == 1 && m[0].mult == 1 && m[1].mult == 1 &&
-                                m[0].off == 0 && m[1].off == 0;
-                if (e.get() == acc_node && identity) id = new_value(DTYPE_FLOAT, true, "acc");
+                if (e.get() == acc_node && is_identity(m)) id = new_value(DTYPE_FLOAT, true, "acc");
                 else id = visit(materialize(a), m);
                 break;
             }
@@ -304,6 +304,11 @@ struct Lowerer {
         }
         memo[key] = id;
         return id;
+    }
+
+    static bool is_identity(const IndexMap& m) {
+        return (int)m.size() == 2 && m[0].src == 0 && m[1].src == 1 && m[0].mult == 1 && m[1].mult == 1 && m[0].off == 0 &&
+               m[1].off == 0;
     }
 
     std::string ir_text() const {
@@ -377,6 +382,23 @@ void find_matmul(const Array& a, const Expression** out) {
     if (e->kind_ == N_MATMUL) { *out = e; return; }
     if (e->kind_ != N_ELEMENTWISE) return;
     for (const Array& arg : e->arguments_) find_matmul(arg, out);
+}
+
+// add(MatMul, MatMul) of fp32 products reachable the same way: both accumulate in one GEMM launch
+void find_matmul_sum(const Array& a, const Expression** out) {
+    if (*out || a.is_stateless()) return;
+    Expression* e = a.expression().get();
+    if (e->kind_ != N_ELEMENTWISE) return;
+    Elementwise* w = static_cast<Elementwise*>(e);
+    if (w->functor_ == "add" && w->arguments_.size() == 2 && w->dtype_ == DTYPE_FLOAT) {
+        const Array &l = w->arguments_[0], &r = w->arguments_[1];
+        if (!l.is_stateless() && !r.is_stateless() && l.expression()->kind_ == N_MATMUL && r.expression()->kind_ == N_MATMUL &&
+            l.dtype() == DTYPE_FLOAT && r.dtype() == DTYPE_FLOAT && l.shape() == r.shape() && l.shape() == w->shape_) {
+            *out = e;
+            return;
+        }
+    }
+    for (const Array& arg : e->arguments_) find_matmul_sum(arg, out);
 }
 
 // TF32 split parts of an fp32 matrix, kept next to the buffer until it is written again
@@ -478,25 +500,34 @@ void run_matmul(const Array& dest, OPERATOR_T op, MatMul* mm) {
     ++tl_stats.gemms;
 }
 
-// dest (op)= tree(product, other operands): one tcgen05 GEMM whose epilogue is the tree.
-// false = this layout is not one the tensor-core path takes (the caller goes on with the
-// general path); other products in the tree have then already been evaluated, which is harmless.
-bool try_fused_gemm(const Array& dest, OPERATOR_T op, const Array& value, const Expression* mm) {
-    if (tl_dry_run) {
-        // count what would run: products other than the fused one first, then the fused GEMM
+// dest (op)= tree(acc, other operands) with acc a product or the sum of two products: one
+// tcgen05 GEMM whose epilogue is the tree.  false = this layout is not one the tensor-core path
+// takes (the caller goes on with the general path); operands of the products have then already
+// been evaluated, which is harmless.
+bool try_fused_gemm(const Array& dest, OPERATOR_T op, const Array& value, const Expression* acc) {
+    std::vector<const Expression*> products;
+    if (acc->kind_ == N_MATMUL) products.push_back(acc);
+    else for (const Array& arg : acc->arguments_) products.push_back(arg.expression().get());
+    const int np = (int)products.size();
+    BufferView *a[2] = {nullptr, nullptr}, *b[2] = {nullptr, nullptr};
+    std::vector<Array> operands;
+    int64_t m = 0, n = 0, k[2] = {0, 0};
+    for (int p = 0; p < np; ++p) {
+        Array left = products[p]->arguments_[0], right = products[p]->arguments_[1];
+        if (!left.is_buffer()) left.eval(false);
+        if (!right.is_buffer()) right.eval(false);
+        a[p] = as<BufferView>(left);
+        b[p] = as<BufferView>(right);
+        if (!a[p] || !b[p]) return false;
+        operands.push_back(left);
+        operands.push_back(right);
+        m = a[p]->shape_[0]; k[p] = a[p]->shape_[1]; n = b[p]->shape_[1];
+        if (m == 0 || n == 0 || k[p] == 0) return false;
     }
-    Array left = mm->arguments_[0], right = mm->arguments_[1];
-    if (!left.is_buffer()) left.eval(false);
-    if (!right.is_buffer()) right.eval(false);
-    BufferView* a = as<BufferView>(left);
-    BufferView* b = as<BufferView>(right);
-    if (!a || !b) return false;
-    const int64_t m = a->shape_[0], k = a->shape_[1], n = b->shape_[1];
-    if (m == 0 || n == 0 || k == 0) return false;
     memory::Device device = dest.preferred_device();
 
     Lowerer L({m, n}, 0, device);
-    L.acc_node = mm;
+    L.acc_node = acc;
     int v = L.visit(value, identity_map(2));
     if (L.types[v] != DTYPE_FLOAT) return false;
     BufferView* db = as<BufferView>(dest);
@@ -508,22 +539,35 @@ bool try_fused_gemm(const Array& dest, OPERATOR_T op, const Array& value, const 
     const uint64_t hash = dalib::fnv1a(text);
     if (!dalib200_is_loaded(hash)) check(dalib200_compile(hash, text.c_str(), text.size()), "dalib200_compile");
     tl_stats.last_ir = text;
+    const void *pa_hi[2], *pa_lo[2], *pb_hi[2], *pb_lo[2];
+    int64_t ld[2];
     if (tl_dry_run) {
         void* fake[16];
         for (auto& p : fake) p = (void*)(uintptr_t)4096;
-        if (L.leaves.size() > 16 || k % 4 || n % 4) return false;
-        int rc = dalib200_gemm_fused(-1, nullptr, DALIB200_F32, m, n, k, fake[0], k, fake[0], n, nullptr, nullptr, hash, fake,
-                                     nullptr, nullptr, (int)L.leaves.size(), nullptr, 0);
+        if (L.leaves.size() > 16 || n % 4) return false;
+        for (int p = 0; p < np; ++p) {
+            if (k[p] % 4) return false;
+            pa_hi[p] = pa_lo[p] = pb_hi[p] = pb_lo[p] = fake[0];
+            ld[p] = k[p];
+        }
+        int rc = dalib200_gemm_fused_sum(-1, nullptr, DALIB200_F32, np, m, n, k, pa_hi, ld, pb_hi, ld, pa_lo, pb_lo, hash, fake,
+                                         nullptr, nullptr, (int)L.leaves.size(), nullptr, 0);
         if (rc == DALIB200_ERR_UNSUPPORTED) return false;
-        check(rc, "dalib200_gemm_fused (compile only)");
-        ++tl_stats.gemms;
-        tl_stats.last_variant = "tcgen05.tf32x3";
+        check(rc, "dalib200_gemm_fused_sum (compile only)");
+        ++tl_stats.gemms;   // one launch, whatever the number of products
+        tl_stats.last_variant = np > 1 ? "tcgen05.tf32x3 x2" : "tcgen05.tf32x3";
         return true;
     }
     const int dev = device_index(device);
-    std::shared_ptr<SplitParts> pa = split_operand(a, false, device, dev);
-    std::shared_ptr<SplitParts> pb = split_operand(b, true, device, dev);
-    if (!pa || !pb) return false;
+    std::shared_ptr<SplitParts> parts[4];
+    for (int p = 0; p < np; ++p) {
+        parts[2 * p] = split_operand(a[p], false, device, dev);
+        parts[2 * p + 1] = split_operand(b[p], true, device, dev);
+        if (!parts[2 * p] || !parts[2 * p + 1]) return false;
+        pa_hi[p] = parts[2 * p]->hi; pa_lo[p] = parts[2 * p]->lo;
+        pb_hi[p] = parts[2 * p + 1]->hi; pb_lo[p] = parts[2 * p + 1]->lo;
+        ld[p] = k[p];
+    }
     const int na = (int)L.leaves.size();
     std::vector<void*> ptrs(na);
     std::vector<int64_t> offsets(na);
@@ -543,11 +587,11 @@ bool try_fused_gemm(const Array& dest, OPERATOR_T op, const Array& value, const 
         sd[j] = L.scalars[j].second; sf[j] = (float)sd[j]; si[j] = (int)sd[j];
         sp[j] = L.scalars[j].first == DTYPE_DOUBLE ? (const void*)&sd[j] : (L.scalars[j].first == DTYPE_FLOAT ? (const void*)&sf[j] : (const void*)&si[j]);
     }
-    int rc = dalib200_gemm_fused(dev, nullptr, DALIB200_F32, m, n, k, pa->hi, k, pb->hi, k, pa->lo, pb->lo, hash, ptrs.data(),
-                                 offsets.data(), strides.data(), na, sp.data(), (int)sp.size());
+    int rc = dalib200_gemm_fused_sum(dev, nullptr, DALIB200_F32, np, m, n, k, pa_hi, ld, pb_hi, ld, pa_lo, pb_lo, hash,
+                                     ptrs.data(), offsets.data(), strides.data(), na, sp.data(), (int)sp.size());
     if (rc == DALIB200_ERR_UNSUPPORTED) return false;
-    check(rc, "dalib200_gemm_fused");
-    ++tl_stats.gemms;
+    check(rc, "dalib200_gemm_fused_sum");
+    ++tl_stats.gemms;   // one launch, whatever the number of products
     char buf[256];
     dalib200_last_gemm_kernel(buf, sizeof buf);
     tl_stats.last_variant = buf;
@@ -598,9 +642,10 @@ void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) 
 
     // ---- an elementwise tree around a product: tensor-core GEMM with the tree as its epilogue
     if (dest.is_buffer() && dest.ndim() == 2 && dest.dtype() == DTYPE_FLOAT && value.shape() == dest.shape()) {
-        const Expression* mm = nullptr;
-        find_matmul(value, &mm);
-        if (mm && mm->dtype_ == DTYPE_FLOAT && try_fused_gemm(dest, op, value, mm)) return;
+        const Expression* acc = nullptr;
+        find_matmul_sum(value, &acc);
+        if (!acc) find_matmul(value, &acc);
+        if (acc && acc->dtype_ == DTYPE_FLOAT && try_fused_gemm(dest, op, value, acc)) return;
     }
 
     // ---- MatMul at the root goes to the general GEMM entry point

@@ -194,6 +194,23 @@ int dalib200_gemm_fused(int device, void* stream, int ab_dtype,
                         const int64_t* const* strides, int n_arrays,
                         const void* const* scalars, int n_scalars);
 
+/* The same with the accumulator summed over n_pairs (1 or 2) operand pairs,
+ *     acc[m,n] = A_0[m,k_0] . B_0[k_0,n] + A_1[m,k_1] . B_1[k_1,n],
+ * in ONE launch and one accumulator: dot(x,Wx) + dot(h,Wh) of a recurrent cell
+ * without concatenating anything in memory (the K blocks of the second pair
+ * simply follow those of the first in the kernel's pipeline).  Arrays of
+ * n_pairs entries; a_lo / b_lo may be NULL (fp32 operands are then split in
+ * pool temporaries) and otherwise follow dalib200_gemm_fused. */
+int dalib200_gemm_fused_sum(int device, void* stream, int ab_dtype, int n_pairs,
+                            int64_t m, int64_t n, const int64_t* k,
+                            const void* const* a, const int64_t* lda,
+                            const void* const* b, const int64_t* ldb,
+                            const void* const* a_lo, const void* const* b_lo,
+                            uint64_t epilogue_hash,
+                            void* const* array_data, const int64_t* offsets,
+                            const int64_t* const* strides, int n_arrays,
+                            const void* const* scalars, int n_scalars);
+
 /* hi = x with the 13 low mantissa bits cleared (what TF32 keeps), lo = x - hi,
  * for a rows x cols fp32 matrix with row pitch ld; hi / lo are written tight:
  * [rows, cols], or with transpose != 0 [cols, rows] (the form the B operand is

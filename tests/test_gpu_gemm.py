@@ -104,6 +104,51 @@ def test_tcgen05_presplit_weights_and_accumulating_epilogue(lib):
     assert np.all(np.abs(got - want) <= 1e-5 * bound)
 
 
+@pytest.mark.parametrize("shape", [(64, 1024, 256, 256), (200, 328, 136, 72), (256, 4096, 1024, 1024), (128, 128, 32, 480)])
+def test_two_products_in_one_accumulator(lib, shape):
+    """acc = x.Wx + h.Wh in one launch (different K per pair allowed), '+ b' as epilogue; against fp64 and
+    against the two-launch form of the same sum."""
+    m, n, k1, k2 = shape
+    rng = np.random.default_rng(sum(shape))
+    x, h = rng.standard_normal((m, k1)).astype(np.float32), rng.standard_normal((m, k2)).astype(np.float32)
+    Wx, Wh = (rng.standard_normal((k1, n)) * 0.02).astype(np.float32), (rng.standard_normal((k2, n)) * 0.02).astype(np.float32)
+    b = rng.standard_normal(n).astype(np.float32)
+    e = IRBuilder(2, 0)
+    o, bias = e.arg("f32"), e.arg("f32")
+    e.st(o, e.op("add", e.acc(), e.ld(bias)))
+    out = torch.full((m, n), -7.0, device="cuda")
+    d = [dev(v) for v in (x, Wx, h, Wh)]
+    lib.gemm_fused_sum(0, m, n, [(k1, d[0], k1, d[1], n), (k2, d[2], k2, d[3], n)], lib.compile(e.text()), [out, dev(b)],
+                       strides=[None, [0, 1]])
+    got = host(out)
+    assert lib.gemm_error_flag() == 0
+    assert lib.last_gemm_kernel().startswith("tcgen05.tf32x3") and lib.last_gemm_kernel().endswith("x2")
+    want = x.astype(np.float64) @ Wx + h.astype(np.float64) @ Wh + b
+    bound = np.abs(x).astype(np.float64) @ np.abs(Wx) + np.abs(h).astype(np.float64) @ np.abs(Wh) + np.abs(b)
+    assert np.all(np.abs(got - want) <= 1e-5 * bound), float(np.max(np.abs(got - want) / bound))
+    two = torch.zeros((m, n), device="cuda")
+    lib.gemm_fused(0, m, n, k1, d[0], k1, d[1], n, lib.compile(gemm_store_ir("f32")), [two])
+    e2 = IRBuilder(2, 0)
+    o2, first, bias2 = e2.arg("f32"), e2.arg("f32"), e2.arg("f32")
+    e2.st(o2, e2.op("add", e2.op("add", e2.acc(), e2.ld(first)), e2.ld(bias2)))
+    lib.gemm_fused(0, m, n, k2, d[2], k2, d[3], n, lib.compile(e2.text()), [two, two, dev(b)], strides=[None, None, [0, 1]])
+    np.testing.assert_allclose(got, host(two), rtol=1e-5, atol=1e-5 * float(bound.max()))
+
+
+def test_two_bf16_products_in_one_accumulator(lib):
+    m, n, k1, k2 = 256, 512, 192, 320
+    rng = np.random.default_rng(77)
+    (x, xd), (h, hd) = to_bf16(rng.standard_normal((m, k1)).astype(np.float32)), to_bf16(rng.standard_normal((m, k2)).astype(np.float32))
+    (Wx, Wxd), (Wh, Whd) = (to_bf16((rng.standard_normal((k, n)) * 0.05).astype(np.float32)) for k in (k1, k2))
+    out = torch.zeros((m, n), device="cuda")
+    lib.gemm_fused_sum(3, m, n, [(k1, xd, k1, Wxd, n), (k2, hd, k2, Whd, n)], lib.compile(gemm_store_ir("f32")), [out])
+    got = host(out)
+    assert lib.gemm_error_flag() == 0
+    want = x.astype(np.float64) @ Wx + h.astype(np.float64) @ Wh
+    bound = np.abs(x).astype(np.float64) @ np.abs(Wx) + np.abs(h).astype(np.float64) @ np.abs(Wh)
+    assert np.all(np.abs(got - want) <= 1e-5 * bound)
+
+
 @pytest.mark.parametrize("shape", [(128, 64, 64), (200, 328, 136), (512, 2048, 1024), (2048, 2048, 512)])
 def test_tcgen05_bf16_product_and_fused_bias_tanh(lib, shape):
     m, n, k = shape
