@@ -458,23 +458,30 @@ class Lstm(Workload):
 
     def e2e_setup(self):
         np = self.np
-        self.host = {k: getattr(self, k)[0].cpu().numpy() for k in ("x", "h", "c")}
+        t = self.torch
+        self.pinned = {}
+        for k in ("x", "h", "c"):
+            self.pinned[k] = t.empty(self.B, self.H, pin_memory=True)
+            self.pinned[k].copy_(getattr(self, k)[0])
+        for k in ("h_out", "c_out"):
+            self.pinned[k] = t.empty(self.B, self.H, pin_memory=True)
+        self.host = {k: v.numpy() for k, v in self.pinned.items()}       # numpy views of the page-locked buffers
         from dali_b200.array import Array, set_default_device
         set_default_device(self.device)
         self.fe = {"Wx": Array(self.Wx.cpu().numpy()), "Wh": Array(self.Wh.cpu().numpy()), "b": Array(self.b.cpu().numpy())}
         self.h2d, self.d2h = 3 * self.B * self.H * 4, 2 * self.B * self.H * 4
 
     def e2e_step(self, i):
-        # the call a user makes: host arrays in, lazy expression, eval, results back on the host
+        # the call a user makes: (page-locked) host arrays in, lazy expression, eval, results back on the host
         from dali_b200.array import Array, op
         H = self.H
-        x, h, c = (Array(self.host[k]) for k in ("x", "h", "c"))
+        x, h, c = (Array.borrow(self.host[k]) for k in ("x", "h", "c"))
         gates = op.dot(x, self.fe["Wx"]) + op.dot(h, self.fe["Wh"]) + self.fe["b"][None, :]
         i_, f, o = (op.sigmoid(gates[:, k * H:(k + 1) * H]) for k in range(3))
         g = op.tanh(gates[:, 3 * H:4 * H])
         c_new = f * c + i_ * g
         h_new = o * op.tanh(c_new)
-        self.last = (h_new.numpy(), c_new.numpy())
+        self.last = (h_new.numpy(out=self.host["h_out"]), c_new.numpy(out=self.host["c_out"]))
 
     def verify(self):
         sys.path.insert(0, os.path.join(ROOT, "oracle"))

@@ -100,6 +100,17 @@ class Array:
         return out
 
     @staticmethod
+    def borrow(array):
+        """Wraps a C-contiguous numpy array WITHOUT copying it (page-locked memory then reaches the GPU by DMA);
+        the caller keeps it alive and unchanged until the expressions reading it have been evaluated."""
+        if not (isinstance(array, np.ndarray) and array.flags.c_contiguous and array.dtype in _NP2D):
+            raise TypeError("Array.borrow needs a C-contiguous float32 / float64 / int32 numpy array")
+        out = Array._new(_c().c.dali_array_borrow_host, ctypes.c_void_p(array.ctypes.data), _shape_arg(array.shape),
+                         array.ndim, _NP2D[array.dtype])
+        out._keep = array
+        return out
+
+    @staticmethod
     def from_device(ptr, shape, dtype=DTYPE_FLOAT, gpu=0):
         """Wraps device memory owned by the caller (e.g. a torch CUDA tensor's data_ptr())."""
         return Array._new(_c().c.dali_array_from_device, ctypes.c_void_p(int(ptr)), _shape_arg(shape), len(shape),
@@ -134,8 +145,12 @@ class Array:
         _check(_c().c.dali_array_eval(self._h, int(wait)))
         return self
 
-    def numpy(self):
-        out = np.empty(self.shape, _D2NP[self.dtype])
+    def numpy(self, out=None):
+        """Evaluates and returns the value as a numpy array (written into `out` when given)."""
+        if out is None:
+            out = np.empty(self.shape, _D2NP[self.dtype])
+        elif not (out.flags.c_contiguous and out.shape == self.shape and out.dtype == _D2NP[self.dtype]):
+            raise TypeError("numpy(out=...): out must be C-contiguous with the Array's shape and dtype")
         _check(_c().c.dali_array_to_host(self._h, ctypes.c_void_p(out.ctypes.data), out.nbytes))
         return out
 

@@ -68,6 +68,18 @@ int dali_array_from_host(const void* data, const int64_t* shape, int ndim, int d
     });
 }
 
+int dali_array_borrow_host(void* data, const int64_t* shape, int ndim, int dtype, dali_array_t* out) {
+    return guard([&]() {
+        DType dt = to_dtype(dtype);
+        std::vector<int> s = to_shape(shape, ndim);
+        int64_t n = 1;
+        for (int d : s) n *= d;
+        auto mem = std::make_shared<memory::SynchronizedMemory>((size_t)n * size_of_dtype(dt), s.empty() ? 1 : s.back());
+        mem->borrow_buffer(memory::Device::cpu(), data);
+        *out = wrap(Array(s, mem, 0, std::vector<int>(), dt));
+    });
+}
+
 int dali_array_from_device(void* device_ptr, const int64_t* shape, int ndim, int dtype, int gpu, dali_array_t* out) {
     return guard([&]() {
         DType dt = to_dtype(dtype);
@@ -119,7 +131,19 @@ int dali_array_to_host(dali_array_t a, void* out, size_t capacity) {
         size_t bytes = (size_t)c.numel() * size_of_dtype(c.dtype());
         DALI_ASSERT(capacity >= bytes, "dali_array_to_host: output buffer too small");
         BufferView* b = as<BufferView>(c);
-        const char* base = (const char*)b->memory_->readonly_data(memory::Device::cpu()) + b->offset_ * size_of_dtype(b->dtype_);
+        const size_t skip = (size_t)b->offset_ * size_of_dtype(b->dtype_);
+        if (!b->memory_->is_fresh(memory::Device::cpu())) {
+            // the value lives on a GPU only: copy straight into the caller's buffer (DMA when it is
+            // page-locked) instead of through a host copy of the whole allocation
+            const int g = b->memory_->fresh_gpu();
+            if (g >= 0) {
+                const char* src = (const char*)b->memory_->readonly_data(memory::Device::gpu(g)) + skip;
+                lazy::check(dalib200_memcpy_d2h(g, out, src, bytes, nullptr), "dalib200_memcpy_d2h");
+                lazy::check(dalib200_sync(g, nullptr), "dalib200_sync");
+                return;
+            }
+        }
+        const char* base = (const char*)b->memory_->readonly_data(memory::Device::cpu()) + skip;
         std::memcpy(out, base, bytes);
     });
 }

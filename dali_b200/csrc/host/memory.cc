@@ -73,6 +73,11 @@ bool SynchronizedMemory::is_fresh(const Device& d) const {
     if (d.is_gpu() && d.number() >= 0 && d.number() < kMaxGpus) return impl_->dev_fresh[d.number()];
     return false;
 }
+int SynchronizedMemory::fresh_gpu() const {
+    for (int g = 0; g < kMaxGpus; ++g)
+        if (impl_->dev_fresh[g]) return g;
+    return -1;
+}
 bool SynchronizedMemory::is_allocated(const Device& d) const {
     if (d.is_cpu()) return impl_->host != nullptr;
     if (d.is_gpu() && d.number() >= 0 && d.number() < kMaxGpus) return impl_->dev[d.number()] != nullptr;

@@ -95,6 +95,7 @@ class SynchronizedMemory {
     bool is_fresh(const Device& device) const;
     bool is_allocated(const Device& device) const;
     bool is_any_fresh() const;
+    int fresh_gpu() const;                               // a GPU that holds a fresh copy, -1 if none does
     void clear();                                        // zero everything, lazily
     void to_device(const Device& device);
     // takes ownership of a caller buffer (host: freed with free(); device: returned to the pool)

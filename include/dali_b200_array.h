@@ -28,6 +28,11 @@ typedef struct dali_array_s* dali_array_t;
 /* ---- construction (Array::Array, Array::adopt_buffer, array.h:43-73) ------------- */
 /* copies `data` (C-contiguous, `shape`) into a new host-fresh Array; dtype as dalib200_dtype */
 int dali_array_from_host(const void* data, const int64_t* shape, int ndim, int dtype, dali_array_t* out);
+/* wraps HOST memory the caller keeps owning (no copy, never freed here; what the reference's
+ * Array::adopt_buffer is used for when a harness hands in prepared inputs, array.cpp:203-222).
+ * The memory must stay alive and unchanged until every expression that reads it has been
+ * evaluated; page-locked memory reaches the GPU by DMA without a staging copy. */
+int dali_array_borrow_host(void* data, const int64_t* shape, int ndim, int dtype, dali_array_t* out);
 /* wraps DEVICE memory the caller keeps owning (no copy, never freed here) */
 int dali_array_from_device(void* device_ptr, const int64_t* shape, int ndim, int dtype, int gpu, dali_array_t* out);
 int dali_array_empty(const int64_t* shape, int ndim, int dtype, dali_array_t* out);

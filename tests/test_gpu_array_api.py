@@ -350,3 +350,30 @@ def test_dot_with_epilogue_at_mid_size_matches_oracle():
     assert last_variant().startswith("tcgen05.tf32x3")
     want = np.tanh(A.astype(np.float64) @ Bm + bias)
     np.testing.assert_allclose(r.numpy(), want, rtol=1e-5, atol=1e-5)
+
+
+def test_borrowed_host_arrays_and_reading_into_a_caller_buffer():
+    """Array.borrow wraps caller memory (page-locked or not) without a copy; numpy(out=) reads the device
+    value straight into the caller's buffer.  Same numbers as the copying constructors."""
+    import torch
+    rng = np.random.default_rng(9)
+    a_np = rng.standard_normal((300, 70)).astype(np.float32)
+    pinned = torch.empty(300, 70, pin_memory=True)
+    pinned.copy_(torch.from_numpy(a_np))
+    two, one = Array(2.0, DTYPE_FLOAT), Array(1.0, DTYPE_FLOAT)
+    want = (Array(a_np) * two + one).numpy()
+    for src in (a_np, pinned.numpy()):
+        got = np.full((300, 70), -1.0, np.float32)
+        ret = (Array.borrow(src) * two + one).numpy(out=got)
+        assert ret is got
+        np.testing.assert_array_equal(got, want)
+    out_pinned = torch.empty(70, 300, pin_memory=True)
+    op.identity(Array.borrow(a_np).transpose()).numpy(out=out_pinned.numpy())      # a strided view is made contiguous first
+    np.testing.assert_array_equal(out_pinned.numpy(), a_np.T)
+    sl = (Array.borrow(a_np) + Array(0.0, DTYPE_FLOAT))[10:20]                                          # offset into a device-only buffer
+    np.testing.assert_array_equal(sl.numpy(), a_np[10:20])
+    np.testing.assert_array_equal(a_np, pinned.numpy())                             # borrowed memory is never written
+    with pytest.raises(TypeError):
+        Array.borrow(a_np.T)
+    with pytest.raises(TypeError):
+        Array(a_np).numpy(out=np.empty((3, 3), np.float32))
