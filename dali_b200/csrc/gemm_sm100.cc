@@ -8,6 +8,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <sstream>
 
@@ -29,6 +30,7 @@ struct GemmVariant {
     int esize;      // 2 bf16, 4 tf32
     int split;      // 3xTF32
     int bm, bn, bk, stages;
+    int pair = 0;   // two CTAs (cta_group::2) share a 2*bm x bn tile, each staging half of the B tile
     bool b_kmajor() const { return split != 0; }   // the fp32 path transposes B while splitting it
     unsigned idesc() const {
         unsigned fmt = esize == 2 ? 1u : 2u;       // kind::f16: 1 = bf16; kind::tf32: 2 = tf32
@@ -39,14 +41,17 @@ struct GemmVariant {
         d |= 0u << 15;                             // A is K-major
         d |= (b_kmajor() ? 0u : 1u) << 16;         // B: K-major ([N,K]) or MN-major ([K,N])
         d |= (unsigned)(bn >> 3) << 17;
-        d |= (unsigned)(bm >> 4) << 24;
+        d |= (unsigned)(((pair ? 2 : 1) * bm) >> 4) << 24;
         return d;
     }
-    size_t stage_bytes() const { return (size_t)(split ? 2 : 1) * ((size_t)bm * bk * esize + (size_t)bn * bk * esize); }
+    size_t stage_bytes() const {
+        return (size_t)(split ? 2 : 1) * ((size_t)bm * bk * esize + (size_t)(bn / (pair ? 2 : 1)) * bk * esize);
+    }
     size_t smem_bytes() const { return stages * stage_bytes() + 1024; }
     std::string key() const {
         std::ostringstream o;
         o << "gemm.e" << esize << ".s" << split << ".m" << bm << ".n" << bn << ".k" << bk << ".st" << stages;
+        if (pair) o << ".pair";
         return o.str();
     }
 };
@@ -211,7 +216,7 @@ bool gemm_source(void* ctx, std::string* src, std::string* err) {
     o << "#define GEMM_BM " << c->v.bm << "\n#define GEMM_BN " << c->v.bn << "\n#define GEMM_BK " << c->v.bk << "\n";
     o << "#define GEMM_STAGES " << c->v.stages << "\n#define GEMM_ESIZE " << c->v.esize << "\n#define GEMM_SPLIT " << c->v.split << "\n";
     o << "#define GEMM_IDESC " << c->v.idesc() << "u\n";
-    o << "#define GEMM_B_KMAJOR " << (c->v.b_kmajor() ? 1 : 0) << "\n";
+    o << "#define GEMM_B_KMAJOR " << (c->v.b_kmajor() ? 1 : 0) << "\n#define GEMM_PAIR " << c->v.pair << "\n";
     int words = 3 * (int)c->p->args.size() + (int)c->p->scalars.size();
     o << "#define GEMM_EPI_WORDS " << (words < 1 ? 1 : words) << "\n";
     // the io helpers need gemm:: conversions, which the skeleton defines: split the skeleton at its kernel
@@ -255,6 +260,14 @@ GemmVariant choose_variant(bool bf16, int64_t m, int64_t n) {
     for (int bn = max_bn; bn >= 64; bn >>= 1)
         if (n >= bn && tiles(bn) >= 120) { v.bn = bn; break; }
     if (n < 64) v.bn = 64;
+    // bf16 with enough 256 x 256 tiles to fill the SM pairs: CTA-pair MMA
+    const char* pair_env = std::getenv("DALI_B200_GEMM_PAIR");
+    const bool want_pair = pair_env && pair_env[0] ? pair_env[0] == '1'      // 1 / 0 force it on / off (tests)
+                                                   : (m >= 256 && n >= 256 && ((m + 255) / 256) * ((n + 255) / 256) >= 64);
+    if (bf16 && want_pair) {
+        v.pair = 1;
+        v.bn = 256;
+    }
     const size_t budget = 200 * 1024;
     v.stages = (int)(budget / v.stage_bytes());
     if (v.stages > 8) v.stages = 8;
@@ -295,7 +308,7 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
     GemmSourceCtx ctx{&prog, choose_variant(bf16, m, n)};
     const GemmVariant& v = ctx.v;
     std::ostringstream key;
-    key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + "|sm_100a|gemm-4|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" +
+    key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + "|sm_100a|gemm-6|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" +
                                                      std::to_string(fnv1a(device_prelude())));
     tl_gemm_variant = std::string(bf16 ? "tcgen05.bf16 " : "tcgen05.tf32x3 ") + v.key() + (n_pairs > 1 ? " x2" : "");
     note_gemm_kernel(tl_gemm_variant);
@@ -337,7 +350,11 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
     }
     // the kernel's GemmP has exactly GEMM_EPI_WORDS words; ours is a superset with the same prefix
     void* params[] = {&tm[0], &tm[1], &tm[2], &tm[3], &tm[4], &tm[5], &tm[6], &tm[7], &p};
-    const unsigned gx = (unsigned)((n + v.bn - 1) / v.bn), gy = (unsigned)((m + v.bm - 1) / v.bm);
+    unsigned gx = (unsigned)((n + v.bn - 1) / v.bn), gy = (unsigned)((m + v.bm - 1) / v.bm);
+    if (v.pair) {      // x: 128-row slabs, two per cluster; y: column tiles
+        gx = 2u * (unsigned)((m + 2 * v.bm - 1) / (2 * v.bm));
+        gy = (unsigned)((n + v.bn - 1) / v.bn);
+    }
     return launch_function(device, fn, gx, gy, 192, (unsigned)v.smem_bytes(), stream, params);
 }
 

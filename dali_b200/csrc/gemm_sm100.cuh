@@ -8,6 +8,12 @@
 //                     0: B is [K,N] row-major (MN-major).  bf16 takes B as it lies in
 //                     memory; the fp32 path gets B transposed for free by the pass that
 //                     splits it into high and low parts
+//   GEMM_PAIR         1: two CTAs on neighbouring SMs (a cluster of 2, tcgen05 cta_group::2) share one
+//                     256 x GEMM_BN tile: each loads its own 128 rows of A and HALF of the B tile,
+//                     the leader CTA issues one MMA that runs on both tensor cores and reads both
+//                     halves of B, each CTA ends up with its 128 rows of the accumulator in its own
+//                     tensor memory.  Halves the shared-memory traffic per flop, which is what
+//                     bounds the single-CTA 128 x 256 bf16 tile
 //   GEMM_IDESC        tcgen05 instruction descriptor
 // and a macro EPILOGUE_CHUNK(row, col0, acc, nvalid) generated from the
 // expression that consumes the product.
@@ -41,10 +47,21 @@ struct GemmP {
 };
 
 #define GEMM_THREADS 192
+#define GEMM_RASTER 8u
+#ifndef GEMM_PAIR
+#define GEMM_PAIR 0
+#endif
+#if GEMM_PAIR
+#define GEMM_CG "2"
+#define GEMM_BN_LOCAL (GEMM_BN / 2)                          /* columns of B this CTA stages */
+#else
+#define GEMM_CG "1"
+#define GEMM_BN_LOCAL GEMM_BN
+#endif
 #define GEMM_SWIZZLE_ELEMS (128 / GEMM_ESIZE)               /* elements per 128-byte swizzle row */
 #define GEMM_UMMA_K (32 / GEMM_ESIZE)                        /* K per tcgen05.mma: 32 bytes */
 #define GEMM_A_TILE_BYTES (GEMM_BM * GEMM_BK * GEMM_ESIZE)
-#define GEMM_B_ATOMS (GEMM_BN / GEMM_SWIZZLE_ELEMS)          /* 128-byte wide column panels of the B tile */
+#define GEMM_B_ATOMS (GEMM_BN_LOCAL / GEMM_SWIZZLE_ELEMS)          /* 128-byte wide column panels of the B tile */
 #define GEMM_B_ATOM_BYTES (GEMM_BK * 128)
 #define GEMM_B_TILE_BYTES (GEMM_B_ATOMS * GEMM_B_ATOM_BYTES)
 #define GEMM_OPERAND_SETS (GEMM_SPLIT ? 2 : 1)
@@ -100,13 +117,37 @@ DEV void tma_load_2d(void* dst, const TensorMap* map, unsigned long long* bar, i
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
+#if GEMM_PAIR
+// the copy lands in THIS CTA's shared memory and reports its bytes to the barrier at shared::cluster
+// address bar_cluster (the leader CTA's), as a CTA-pair MMA expects
+DEV void tma_load_2d_pair(void* dst, const TensorMap* map, unsigned bar_cluster, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster), "r"(x), "r"(y) : "memory");
+}
+DEV unsigned cluster_ctarank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same variable in CTA `rank` of this cluster
+DEV unsigned map_to_cta(const void* p, unsigned rank) {
+    unsigned r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
+    return r;
+}
+DEV void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+#endif
 
 DEV void tmem_alloc(unsigned* slot, unsigned cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    asm volatile("tcgen05.alloc.cta_group::" GEMM_CG ".sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::" GEMM_CG ".sync.aligned;" ::: "memory");
 }
 DEV void tmem_dealloc(unsigned taddr, unsigned cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::" GEMM_CG ".sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
 DEV void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 DEV void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -115,18 +156,24 @@ DEV void umma(unsigned tmem_d, unsigned long long adesc, unsigned long long bdes
 #if GEMM_ESIZE == 2
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        "tcgen05.mma.cta_group::" GEMM_CG ".kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 #else
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        "tcgen05.mma.cta_group::" GEMM_CG ".kind::tf32 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 #endif
 }
 // arrives on `bar` when every tcgen05.mma issued so far by this thread has completed
 DEV void umma_commit(unsigned long long* bar) {
+#if GEMM_PAIR
+    // the same barrier in both CTAs of the pair
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"((unsigned short)3) : "memory");
+#else
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+#endif
 }
 
 // shared-memory matrix descriptor: 128-byte swizzle, 1024-byte groups of 8 rows
@@ -170,6 +217,9 @@ DEV float bf16_to_f32(unsigned short b) { return __uint_as_float(((unsigned)b) <
 }  // namespace gemm
 
 extern "C" __global__ void __launch_bounds__(GEMM_THREADS, 1)
+#if GEMM_PAIR
+__cluster_dims__(2, 1, 1)
+#endif
 dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ TensorMap tmB,
                  const __grid_constant__ TensorMap tmAlo, const __grid_constant__ TensorMap tmBlo,
                  const __grid_constant__ TensorMap tmA2, const __grid_constant__ TensorMap tmB2,
@@ -186,7 +236,27 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long m0 = (long long)blockIdx.y * GEMM_BM, n0 = (long long)blockIdx.x * GEMM_BN;
+    // Tiles are handed out in launch order; walking them in bands of GEMM_RASTER column tiles keeps
+    // the operands of the tiles in flight (about one band row per 8 SMs) inside L2.
+#if GEMM_PAIR
+    // blockIdx.x counts 128-row slabs (the two CTAs of a pair are neighbours in x), blockIdx.y column tiles
+    const unsigned cta_rank = cluster_ctarank();
+    const bool leader = cta_rank == 0;
+    const unsigned tiles_m = gridDim.x >> 1, tiles_n = gridDim.y;
+    const unsigned lin = blockIdx.y * tiles_m + (blockIdx.x >> 1);
+#else
+    const unsigned cta_rank = 0;
+    const bool leader = true;
+    const unsigned tiles_m = gridDim.y, tiles_n = gridDim.x;
+    const unsigned lin = blockIdx.y * gridDim.x + blockIdx.x;
+#endif
+    const unsigned band = lin / (GEMM_RASTER * tiles_m);
+    const unsigned band_n0 = band * GEMM_RASTER;
+    const unsigned band_w = tiles_n - band_n0 < GEMM_RASTER ? tiles_n - band_n0 : GEMM_RASTER;
+    const unsigned in_band = lin - band * GEMM_RASTER * tiles_m;
+    const unsigned tile_m = in_band / band_w, tile_n = band_n0 + in_band % band_w;
+    const long long m0 = ((long long)tile_m * (GEMM_PAIR ? 2 : 1) + cta_rank) * GEMM_BM, n0 = (long long)tile_n * GEMM_BN;
+    const long long n_load = n0 + (long long)cta_rank * GEMM_BN_LOCAL;      // the part of the B tile this CTA stages
     const int num_kb1 = (int)((p.K + GEMM_BK - 1) / GEMM_BK);
     const int num_kb = num_kb1 + (int)((p.K2 + GEMM_BK - 1) / GEMM_BK);
 
@@ -199,6 +269,9 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
     if (warp == 5) tmem_alloc(&tmem_slot, GEMM_TMEM_COLS);
     fence_before_sync();
     __syncthreads();
+#if GEMM_PAIR
+    cluster_sync();      // the peer's barriers exist before anything is sent to them
+#endif
     fence_after_sync();
     const unsigned tmem_base = tmem_slot;
 
@@ -209,20 +282,29 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
             const unsigned parity = (unsigned)((kb / GEMM_STAGES) & 1);
             if (!mbar_wait(&empty_bar[s], parity ^ 1u, &abort_flag)) { atomicExch(p.err, 1); abort_flag = 1; break; }
             unsigned char* st = tiles + (size_t)s * GEMM_STAGE_BYTES;
-            mbar_expect_tx(&full_bar[s], GEMM_STAGE_BYTES);
             // K blocks of the second operand pair follow those of the first
             const bool second = kb >= num_kb1;
             const int kx = (second ? kb - num_kb1 : kb) * GEMM_BK;
             const TensorMap* mA = second ? &tmA2 : &tmA;
             const TensorMap* mB = second ? &tmB2 : &tmB;
-            tma_load_2d(st, mA, &full_bar[s], kx, (int)m0);
             unsigned char* bt = st + GEMM_A_TILE_BYTES;
+#if GEMM_PAIR
+            // both CTAs' copies report to the leader's barrier, which the leader arms for both
+            if (leader) mbar_expect_tx(&full_bar[s], 2 * GEMM_STAGE_BYTES);
+            const unsigned bar = map_to_cta(&full_bar[s], 0);
+            tma_load_2d_pair(st, mA, bar, kx, (int)m0);
+#pragma unroll
+            for (int j = 0; j < GEMM_B_ATOMS; ++j)
+                tma_load_2d_pair(bt + j * GEMM_B_ATOM_BYTES, mB, bar, (int)n_load + j * GEMM_SWIZZLE_ELEMS, kx);
+#else
+            mbar_expect_tx(&full_bar[s], GEMM_STAGE_BYTES);
+            tma_load_2d(st, mA, &full_bar[s], kx, (int)m0);
 #if GEMM_B_KMAJOR
             tma_load_2d(bt, mB, &full_bar[s], kx, (int)n0);
 #else
 #pragma unroll
             for (int j = 0; j < GEMM_B_ATOMS; ++j)
-                tma_load_2d(bt + j * GEMM_B_ATOM_BYTES, mB, &full_bar[s], (int)n0 + j * GEMM_SWIZZLE_ELEMS, kx);
+                tma_load_2d(bt + j * GEMM_B_ATOM_BYTES, mB, &full_bar[s], (int)n_load + j * GEMM_SWIZZLE_ELEMS, kx);
 #endif
 #if GEMM_SPLIT
             const TensorMap* mAlo = second ? &tmA2lo : &tmAlo;
@@ -238,9 +320,10 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
                 tma_load_2d(blo + j * GEMM_B_ATOM_BYTES, mBlo, &full_bar[s], (int)n0 + j * GEMM_SWIZZLE_ELEMS, kx);
 #endif
 #endif
+#endif      // GEMM_PAIR
         }
-    } else if (warp == 5 && lane == 0) {
-        // ------------------------------------------------------------ MMA issuer
+    } else if (warp == 5 && lane == 0 && leader) {
+        // ------------------------------------------------------------ MMA issuer (of a pair: the leader CTA)
         bool ok = true;
         for (int kb = 0; kb < num_kb && ok; ++kb) {
             const int s = kb % GEMM_STAGES;
@@ -328,6 +411,11 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
         while (clock64() - t0 < 2000000LL) { }
         __syncthreads();
     }
+#if GEMM_PAIR
+    // neither CTA may free tensor memory or leave (the leader's MMAs read the peer's shared memory,
+    // the peer's copies report to the leader's barriers) before both are done
+    cluster_sync();
+#endif
     if (warp == 5) {
         fence_after_sync();
         tmem_dealloc(tmem_base, GEMM_TMEM_COLS);

@@ -176,6 +176,29 @@ def test_tcgen05_bf16_product_and_fused_bias_tanh(lib, shape):
     np.testing.assert_allclose(host(out32), ref, rtol=2e-5, atol=2e-5)
 
 
+@pytest.mark.parametrize("shape", [(256, 256, 64), (200, 328, 136), (1024, 768, 1024), (2048, 2048, 512)])
+def test_cta_pair_bf16_product(lib, shape, monkeypatch):
+    """Two CTAs per 256 x 256 tile (tcgen05 cta_group::2), forced on for shapes the heuristic would leave to the
+    single-CTA kernel, ragged edges included; same bound as the single-CTA path, and bit-identical to it where
+    the accumulation order is the same (one K sweep per output)."""
+    m, n, k = shape
+    rng = np.random.default_rng(m * 3 + n * 5 + k)
+    a, ad = to_bf16(rng.standard_normal((m, k)).astype(np.float32))
+    b, bd = to_bf16((rng.standard_normal((k, n)) * 0.05).astype(np.float32))
+    out = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("DALI_B200_GEMM_PAIR", mode)
+        o = torch.full((m, n), -7.0, device="cuda")
+        lib.gemm_fused(3, m, n, k, ad, k, bd, n, lib.compile(gemm_store_ir("f32")), [o])
+        out[mode] = host(o)
+        assert lib.gemm_error_flag() == 0
+        assert lib.last_gemm_kernel().endswith(".pair") == (mode == "1")
+    want = a.astype(np.float64) @ b.astype(np.float64)
+    bound = np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)
+    assert np.all(np.abs(out["1"] - want) <= 1e-5 * bound)
+    np.testing.assert_array_equal(out["1"], out["0"])
+
+
 def test_epilogue_with_strided_destination_scalars_and_residual(lib):
     """out[:, ::2] = relu(acc * s + residual): column-strided store, runtime scalar, second operand."""
     rng = np.random.default_rng(11)
