@@ -277,6 +277,7 @@ GemmVariant choose_variant(bool bf16, int64_t m, int64_t n) {
 
 struct GemmP {
     long long M, N, K, K2;
+    unsigned tiles_m, tiles_n;
     int* err;
     long long w[64];
 };
@@ -308,7 +309,7 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
     GemmSourceCtx ctx{&prog, choose_variant(bf16, m, n)};
     const GemmVariant& v = ctx.v;
     std::ostringstream key;
-    key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + "|sm_100a|gemm-6|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" +
+    key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + "|sm_100a|gemm-7|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" +
                                                      std::to_string(fnv1a(device_prelude())));
     tl_gemm_variant = std::string(bf16 ? "tcgen05.bf16 " : "tcgen05.tf32x3 ") + v.key() + (n_pairs > 1 ? " x2" : "");
     note_gemm_kernel(tl_gemm_variant);
@@ -350,11 +351,17 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
     }
     // the kernel's GemmP has exactly GEMM_EPI_WORDS words; ours is a superset with the same prefix
     void* params[] = {&tm[0], &tm[1], &tm[2], &tm[3], &tm[4], &tm[5], &tm[6], &tm[7], &p};
-    unsigned gx = (unsigned)((n + v.bn - 1) / v.bn), gy = (unsigned)((m + v.bm - 1) / v.bm);
-    if (v.pair) {      // x: 128-row slabs, two per cluster; y: column tiles
-        gx = 2u * (unsigned)((m + 2 * v.bm - 1) / (2 * v.bm));
-        gy = (unsigned)((n + v.bn - 1) / v.bn);
-    }
+    // persistent CTAs (CTA pairs), at most one per SM (SM pair); they take the tiles round robin
+    const int64_t rows_per_tile = (int64_t)v.bm * (v.pair ? 2 : 1);
+    p.tiles_m = (unsigned)((m + rows_per_tile - 1) / rows_per_tile);
+    p.tiles_n = (unsigned)((n + v.bn - 1) / v.bn);
+    const uint64_t total_tiles = (uint64_t)p.tiles_m * p.tiles_n;
+    if (total_tiles > 0x7fffffffull) { set_error("gemm_fused: too many output tiles"); return DALIB200_ERR_TOO_LARGE; }
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device_ordinal(device)) != cudaSuccess || sms < 2) sms = 148;
+    uint64_t workers = (uint64_t)(v.pair ? sms / 2 : sms);
+    if (workers > total_tiles) workers = total_tiles;
+    const unsigned gx = (unsigned)(workers * (v.pair ? 2 : 1)), gy = 1;
     return launch_function(device, fn, gx, gy, 192, (unsigned)v.smem_bytes(), stream, params);
 }
 

@@ -24,14 +24,16 @@
 // through the epilogue straight to its destination.
 //
 // Layout of the work:
-//   one CTA per GEMM_BM x GEMM_BN output tile, 192 threads:
+//   persistent CTAs (one per SM, or one pair per two SMs) take output tiles round robin; 192 threads:
 //     warps 0-3  epilogue: warp w owns TMEM lanes 32w..32w+31 (= tile rows)
 //     warp 4     TMA producer (one elected lane)
 //     warp 5     allocates TMEM, issues tcgen05.mma (one elected lane)
 //   A is K-major (row-major [M,K]), B is MN-major (row-major [K,N]); both are
 //   staged by TMA with 128-byte swizzle into a GEMM_STAGES-deep ring guarded
 //   by full / empty mbarriers; tcgen05.commit releases a stage when the MMAs
-//   that read it have finished.  No cluster, no multicast.
+//   that read it have finished.  Tensor memory holds the accumulators of two
+//   tiles when they fit, so the epilogue of a tile runs while the tensor core
+//   works on the next one.  No multicast loads.
 //
 // Every wait is bounded (about a second of polling): on expiry the waiting
 // thread records a code in *p.err, raises a CTA-wide abort flag and all roles
@@ -42,6 +44,7 @@ struct alignas(64) TensorMap { unsigned long long opaque[16]; };
 struct GemmP {
     long long M, N, K;        // K: reduction length of the first (or only) operand pair
     long long K2;             // of the second pair (0 = none): acc = A.B + A2.B2 in one accumulator
+    unsigned tiles_m, tiles_n;   // output tiles (of a CTA pair: 2*GEMM_BM rows) in each direction
     int* err;                 // device int, 0 = fine
     long long w[GEMM_EPI_WORDS];
 };
@@ -79,7 +82,9 @@ struct GemmP {
 #define GEMM_NACC 1
 #define GEMM_ACC_SETS 1
 #endif
-#define GEMM_TMEM_NEED (GEMM_ACC_SETS * GEMM_BN)
+#define GEMM_ACC_COLS (GEMM_ACC_SETS * GEMM_BN)                 /* tensor-memory columns of one tile's accumulators */
+#define GEMM_ACC_STAGES (2 * GEMM_ACC_COLS <= 512 ? 2 : 1)      /* two tiles' worth when they fit: the epilogue of one tile overlaps the next main loop */
+#define GEMM_TMEM_NEED (GEMM_ACC_STAGES * GEMM_ACC_COLS)
 #define GEMM_TMEM_COLS (GEMM_TMEM_NEED <= 32 ? 32 : GEMM_TMEM_NEED <= 64 ? 64 : GEMM_TMEM_NEED <= 128 ? 128 : GEMM_TMEM_NEED <= 256 ? 256 : 512)
 
 namespace gemm {
@@ -141,6 +146,15 @@ DEV void cluster_sync() {
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 #endif
+
+// one arrival on `bar` of the leader CTA (of this CTA when there is no pair)
+DEV void arrive_at_leader(unsigned long long* bar) {
+#if GEMM_PAIR
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(map_to_cta(bar, 0)) : "memory");
+#else
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+#endif
+}
 
 DEV void tmem_alloc(unsigned* slot, unsigned cols) {
     asm volatile("tcgen05.alloc.cta_group::" GEMM_CG ".sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
@@ -231,38 +245,39 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<unsigned long long>(smem_raw) + 1023) & ~1023ull);
     __shared__ __align__(8) unsigned long long full_bar[GEMM_STAGES];
     __shared__ __align__(8) unsigned long long empty_bar[GEMM_STAGES];
-    __shared__ __align__(8) unsigned long long accum_bar;
+    __shared__ __align__(8) unsigned long long acc_full[GEMM_ACC_STAGES];     // MMA -> epilogue: the tile's accumulators are complete
+    __shared__ __align__(8) unsigned long long acc_empty[GEMM_ACC_STAGES];    // epilogue -> MMA: they have been read
     __shared__ unsigned tmem_slot;
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // Tiles are handed out in launch order; walking them in bands of GEMM_RASTER column tiles keeps
-    // the operands of the tiles in flight (about one band row per 8 SMs) inside L2.
 #if GEMM_PAIR
-    // blockIdx.x counts 128-row slabs (the two CTAs of a pair are neighbours in x), blockIdx.y column tiles
-    const unsigned cta_rank = cluster_ctarank();
-    const bool leader = cta_rank == 0;
-    const unsigned tiles_m = gridDim.x >> 1, tiles_n = gridDim.y;
-    const unsigned lin = blockIdx.y * tiles_m + (blockIdx.x >> 1);
+    const unsigned cta_rank = cluster_ctarank();     // the two CTAs of a pair are neighbours in x
+    const unsigned worker = blockIdx.x >> 1, n_workers = gridDim.x >> 1;
 #else
     const unsigned cta_rank = 0;
-    const bool leader = true;
-    const unsigned tiles_m = gridDim.y, tiles_n = gridDim.x;
-    const unsigned lin = blockIdx.y * gridDim.x + blockIdx.x;
+    const unsigned worker = blockIdx.x, n_workers = gridDim.x;
 #endif
-    const unsigned band = lin / (GEMM_RASTER * tiles_m);
-    const unsigned band_n0 = band * GEMM_RASTER;
-    const unsigned band_w = tiles_n - band_n0 < GEMM_RASTER ? tiles_n - band_n0 : GEMM_RASTER;
-    const unsigned in_band = lin - band * GEMM_RASTER * tiles_m;
-    const unsigned tile_m = in_band / band_w, tile_n = band_n0 + in_band % band_w;
-    const long long m0 = ((long long)tile_m * (GEMM_PAIR ? 2 : 1) + cta_rank) * GEMM_BM, n0 = (long long)tile_n * GEMM_BN;
-    const long long n_load = n0 + (long long)cta_rank * GEMM_BN_LOCAL;      // the part of the B tile this CTA stages
+    const bool leader = cta_rank == 0;
+    const unsigned total_tiles = p.tiles_m * p.tiles_n;
     const int num_kb1 = (int)((p.K + GEMM_BK - 1) / GEMM_BK);
     const int num_kb = num_kb1 + (int)((p.K2 + GEMM_BK - 1) / GEMM_BK);
 
+    // Tiles are numbered in bands of GEMM_RASTER column tiles, rows fastest inside a band, so that the
+    // operands of the tiles in flight at any time (consecutive numbers) stay inside L2.
+    auto tile_origin = [&](unsigned lin, long long* m0, long long* n0) {
+        const unsigned band = lin / (GEMM_RASTER * p.tiles_m);
+        const unsigned band_n0 = band * GEMM_RASTER;
+        const unsigned band_w = p.tiles_n - band_n0 < GEMM_RASTER ? p.tiles_n - band_n0 : GEMM_RASTER;
+        const unsigned in_band = lin - band * GEMM_RASTER * p.tiles_m;
+        *m0 = ((long long)(in_band / band_w) * (GEMM_PAIR ? 2 : 1) + cta_rank) * GEMM_BM;     // this CTA's rows
+        *n0 = (long long)(band_n0 + in_band % band_w) * GEMM_BN;
+    };
+
     if (threadIdx.x == 0) {
         for (int s = 0; s < GEMM_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        mbar_init(&accum_bar, 1);
+        // every epilogue warp (of both CTAs of a pair) reports to the leader's barrier
+        for (int s = 0; s < GEMM_ACC_STAGES; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4 * (GEMM_PAIR ? 2 : 1)); }
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -277,106 +292,127 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
 
     if (warp == 4 && lane == 0) {
         // ------------------------------------------------------------ TMA producer
-        for (int kb = 0; kb < num_kb; ++kb) {
-            const int s = kb % GEMM_STAGES;
-            const unsigned parity = (unsigned)((kb / GEMM_STAGES) & 1);
-            if (!mbar_wait(&empty_bar[s], parity ^ 1u, &abort_flag)) { atomicExch(p.err, 1); abort_flag = 1; break; }
-            unsigned char* st = tiles + (size_t)s * GEMM_STAGE_BYTES;
-            // K blocks of the second operand pair follow those of the first
-            const bool second = kb >= num_kb1;
-            const int kx = (second ? kb - num_kb1 : kb) * GEMM_BK;
-            const TensorMap* mA = second ? &tmA2 : &tmA;
-            const TensorMap* mB = second ? &tmB2 : &tmB;
-            unsigned char* bt = st + GEMM_A_TILE_BYTES;
+        unsigned it = 0;      // K blocks issued so far, over all tiles: position in the stage ring
+        bool ok = true;
+        for (unsigned t = worker; t < total_tiles && ok; t += n_workers) {
+            long long m0, n0;
+            tile_origin(t, &m0, &n0);
+            const long long n_load = n0 + (long long)cta_rank * GEMM_BN_LOCAL;      // the part of the B tile this CTA stages
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const unsigned s = it % GEMM_STAGES;
+                const unsigned parity = (it / GEMM_STAGES) & 1u;
+                if (!mbar_wait(&empty_bar[s], parity ^ 1u, &abort_flag)) { atomicExch(p.err, 1); abort_flag = 1; ok = false; break; }
+                unsigned char* st = tiles + (size_t)s * GEMM_STAGE_BYTES;
+                // K blocks of the second operand pair follow those of the first
+                const bool second = kb >= num_kb1;
+                const int kx = (second ? kb - num_kb1 : kb) * GEMM_BK;
+                const TensorMap* mA = second ? &tmA2 : &tmA;
+                const TensorMap* mB = second ? &tmB2 : &tmB;
+                unsigned char* bt = st + GEMM_A_TILE_BYTES;
 #if GEMM_PAIR
-            // both CTAs' copies report to the leader's barrier, which the leader arms for both
-            if (leader) mbar_expect_tx(&full_bar[s], 2 * GEMM_STAGE_BYTES);
-            const unsigned bar = map_to_cta(&full_bar[s], 0);
-            tma_load_2d_pair(st, mA, bar, kx, (int)m0);
+                // both CTAs' copies report to the leader's barrier, which the leader arms for both
+                if (leader) mbar_expect_tx(&full_bar[s], 2 * GEMM_STAGE_BYTES);
+                const unsigned bar = map_to_cta(&full_bar[s], 0);
+                tma_load_2d_pair(st, mA, bar, kx, (int)m0);
 #pragma unroll
-            for (int j = 0; j < GEMM_B_ATOMS; ++j)
-                tma_load_2d_pair(bt + j * GEMM_B_ATOM_BYTES, mB, bar, (int)n_load + j * GEMM_SWIZZLE_ELEMS, kx);
+                for (int j = 0; j < GEMM_B_ATOMS; ++j)
+                    tma_load_2d_pair(bt + j * GEMM_B_ATOM_BYTES, mB, bar, (int)n_load + j * GEMM_SWIZZLE_ELEMS, kx);
 #else
-            mbar_expect_tx(&full_bar[s], GEMM_STAGE_BYTES);
-            tma_load_2d(st, mA, &full_bar[s], kx, (int)m0);
+                mbar_expect_tx(&full_bar[s], GEMM_STAGE_BYTES);
+                tma_load_2d(st, mA, &full_bar[s], kx, (int)m0);
 #if GEMM_B_KMAJOR
-            tma_load_2d(bt, mB, &full_bar[s], kx, (int)n0);
+                tma_load_2d(bt, mB, &full_bar[s], kx, (int)n0);
 #else
 #pragma unroll
-            for (int j = 0; j < GEMM_B_ATOMS; ++j)
-                tma_load_2d(bt + j * GEMM_B_ATOM_BYTES, mB, &full_bar[s], (int)n_load + j * GEMM_SWIZZLE_ELEMS, kx);
+                for (int j = 0; j < GEMM_B_ATOMS; ++j)
+                    tma_load_2d(bt + j * GEMM_B_ATOM_BYTES, mB, &full_bar[s], (int)n_load + j * GEMM_SWIZZLE_ELEMS, kx);
 #endif
 #if GEMM_SPLIT
-            const TensorMap* mAlo = second ? &tmA2lo : &tmAlo;
-            const TensorMap* mBlo = second ? &tmB2lo : &tmBlo;
-            unsigned char* alo = bt + GEMM_B_TILE_BYTES;
-            tma_load_2d(alo, mAlo, &full_bar[s], kx, (int)m0);
-            unsigned char* blo = alo + GEMM_A_TILE_BYTES;
+                const TensorMap* mAlo = second ? &tmA2lo : &tmAlo;
+                const TensorMap* mBlo = second ? &tmB2lo : &tmBlo;
+                unsigned char* alo = bt + GEMM_B_TILE_BYTES;
+                tma_load_2d(alo, mAlo, &full_bar[s], kx, (int)m0);
+                unsigned char* blo = alo + GEMM_A_TILE_BYTES;
 #if GEMM_B_KMAJOR
-            tma_load_2d(blo, mBlo, &full_bar[s], kx, (int)n0);
+                tma_load_2d(blo, mBlo, &full_bar[s], kx, (int)n0);
 #else
 #pragma unroll
-            for (int j = 0; j < GEMM_B_ATOMS; ++j)
-                tma_load_2d(blo + j * GEMM_B_ATOM_BYTES, mBlo, &full_bar[s], (int)n0 + j * GEMM_SWIZZLE_ELEMS, kx);
+                for (int j = 0; j < GEMM_B_ATOMS; ++j)
+                    tma_load_2d(blo + j * GEMM_B_ATOM_BYTES, mBlo, &full_bar[s], (int)n0 + j * GEMM_SWIZZLE_ELEMS, kx);
 #endif
 #endif
 #endif      // GEMM_PAIR
+            }
         }
     } else if (warp == 5 && lane == 0 && leader) {
         // ------------------------------------------------------------ MMA issuer (of a pair: the leader CTA)
+        unsigned it = 0, done = 0;     // K blocks consumed; tiles finished
         bool ok = true;
-        for (int kb = 0; kb < num_kb && ok; ++kb) {
-            const int s = kb % GEMM_STAGES;
-            const unsigned parity = (unsigned)((kb / GEMM_STAGES) & 1);
-            if (!mbar_wait(&full_bar[s], parity, &abort_flag)) { atomicExch(p.err, 2); abort_flag = 1; ok = false; break; }
+        for (unsigned t = worker; t < total_tiles && ok && num_kb > 0; t += n_workers, ++done) {
+            const unsigned as = done % GEMM_ACC_STAGES;
+            // the epilogue must have read what this accumulator stage held two tiles ago
+            if (!mbar_wait(&acc_empty[as], ((done / GEMM_ACC_STAGES) & 1u) ^ 1u, &abort_flag)) { atomicExch(p.err, 5); abort_flag = 1; ok = false; break; }
             fence_after_sync();
-            const unsigned a_addr = smem_u32(tiles + (size_t)s * GEMM_STAGE_BYTES);
-            const unsigned b_addr = a_addr + GEMM_A_TILE_BYTES;
+            const unsigned acc0 = tmem_base + as * GEMM_ACC_COLS;
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const unsigned s = it % GEMM_STAGES;
+                const unsigned parity = (it / GEMM_STAGES) & 1u;
+                if (!mbar_wait(&full_bar[s], parity, &abort_flag)) { atomicExch(p.err, 2); abort_flag = 1; ok = false; break; }
+                fence_after_sync();
+                const unsigned a_addr = smem_u32(tiles + (size_t)s * GEMM_STAGE_BYTES);
+                const unsigned b_addr = a_addr + GEMM_A_TILE_BYTES;
 #pragma unroll
-            for (int k = 0; k < GEMM_BK / GEMM_UMMA_K; ++k) {
-                // A: 32 bytes further along its 128-byte rows; B: GEMM_UMMA_K rows (128 bytes each) further down
-                const unsigned long long ad = smem_desc(a_addr + k * 32, 0, 1024);
+                for (int k = 0; k < GEMM_BK / GEMM_UMMA_K; ++k) {
+                    // A: 32 bytes further along its 128-byte rows; B: GEMM_UMMA_K rows (128 bytes each) further down
+                    const unsigned long long ad = smem_desc(a_addr + k * 32, 0, 1024);
 #if GEMM_B_KMAJOR
-                const unsigned long long bd = smem_desc(b_addr + k * 32, 0, 1024);
+                    const unsigned long long bd = smem_desc(b_addr + k * 32, 0, 1024);
 #else
-                const unsigned long long bd = smem_desc(b_addr + k * GEMM_UMMA_K * 128, GEMM_B_ATOM_BYTES, 1024);
+                    const unsigned long long bd = smem_desc(b_addr + k * GEMM_UMMA_K * 128, GEMM_B_ATOM_BYTES, 1024);
 #endif
 #if GEMM_SPLIT
-                // main products: accumulator kb % GEMM_NACC (its first use overwrites)
-                umma(tmem_base + (unsigned)((kb % GEMM_NACC) * GEMM_BN), ad, bd, GEMM_IDESC, (kb >= GEMM_NACC || k > 0) ? 1u : 0u);
-#else
-                umma(tmem_base, ad, bd, GEMM_IDESC, (kb > 0 || k > 0) ? 1u : 0u);
-#endif
-#if GEMM_SPLIT
-                const unsigned alo_addr = b_addr + GEMM_B_TILE_BYTES;
-                const unsigned blo_addr = alo_addr + GEMM_A_TILE_BYTES;
-                const unsigned long long ald = smem_desc(alo_addr + k * 32, 0, 1024);
+                    // main products: accumulator kb % GEMM_NACC (its first use overwrites)
+                    umma(acc0 + (unsigned)((kb % GEMM_NACC) * GEMM_BN), ad, bd, GEMM_IDESC, (kb >= GEMM_NACC || k > 0) ? 1u : 0u);
+                    const unsigned alo_addr = b_addr + GEMM_B_TILE_BYTES;
+                    const unsigned blo_addr = alo_addr + GEMM_A_TILE_BYTES;
+                    const unsigned long long ald = smem_desc(alo_addr + k * 32, 0, 1024);
 #if GEMM_B_KMAJOR
-                const unsigned long long bld = smem_desc(blo_addr + k * 32, 0, 1024);
+                    const unsigned long long bld = smem_desc(blo_addr + k * 32, 0, 1024);
 #else
-                const unsigned long long bld = smem_desc(blo_addr + k * GEMM_UMMA_K * 128, GEMM_B_ATOM_BYTES, 1024);
+                    const unsigned long long bld = smem_desc(blo_addr + k * GEMM_UMMA_K * 128, GEMM_B_ATOM_BYTES, 1024);
 #endif
-                const unsigned corr = tmem_base + (unsigned)(GEMM_NACC * GEMM_BN);
-                umma(corr, ald, bd, GEMM_IDESC, (kb > 0 || k > 0) ? 1u : 0u);   // a_lo * b_hi
-                umma(corr, ad, bld, GEMM_IDESC, 1u);                            // a_hi * b_lo
+                    const unsigned corr = acc0 + (unsigned)(GEMM_NACC * GEMM_BN);
+                    umma(corr, ald, bd, GEMM_IDESC, (kb > 0 || k > 0) ? 1u : 0u);   // a_lo * b_hi
+                    umma(corr, ad, bld, GEMM_IDESC, 1u);                            // a_hi * b_lo
+#else
+                    umma(acc0, ad, bd, GEMM_IDESC, (kb > 0 || k > 0) ? 1u : 0u);
 #endif
+                }
+                umma_commit(&empty_bar[s]);       // the stage is free once these MMAs have read it
             }
-            umma_commit(&empty_bar[s]);       // the stage is free once these MMAs have read it
+            if (ok) umma_commit(&acc_full[as]);   // the tile's accumulators are complete
         }
-        if (ok) umma_commit(&accum_bar);      // the accumulator is complete
     } else if (warp < 4) {
         // ------------------------------------------------------------ epilogue
+        unsigned done = 0;
         bool ok = true;
-        if (num_kb > 0) ok = mbar_wait(&accum_bar, 0, &abort_flag);
-        if (!ok) { if (lane == 0) atomicExch(p.err, 3); abort_flag = 1; }
-        if (ok) {
+        for (unsigned t = worker; t < total_tiles && ok; t += n_workers, ++done) {
+            long long m0, n0;
+            tile_origin(t, &m0, &n0);
+            const unsigned as = done % GEMM_ACC_STAGES;
+            if (num_kb > 0 && !mbar_wait(&acc_full[as], (done / GEMM_ACC_STAGES) & 1u, &abort_flag)) {
+                if (lane == 0) atomicExch(p.err, 3);
+                abort_flag = 1;
+                ok = false;
+                break;
+            }
             fence_after_sync();
             const long long row = m0 + warp * 32 + lane;
 #pragma unroll 1
             for (int c = 0; c < GEMM_BN; c += 32) {
                 float acc[32];
                 if (num_kb > 0) {
-                    const unsigned lane_base = tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)c;
+                    const unsigned lane_base = tmem_base + as * GEMM_ACC_COLS + ((unsigned)(warp * 32) << 16) + (unsigned)c;
                     tmem_ld32(lane_base, acc);
 #if GEMM_SPLIT
                     const int used = num_kb < GEMM_NACC ? num_kb : GEMM_NACC;
@@ -400,6 +436,12 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
                     EPILOGUE_CHUNK(row, col0, acc, nvalid)
                 }
             }
+            if (num_kb > 0) {
+                // this warp has read its part of the accumulator stage: hand it back to the MMA issuer
+                fence_before_sync();
+                __syncwarp();
+                if (lane == 0) arrive_at_leader(&acc_empty[as]);
+            }
         }
     }
     // ---------------------------------------------------------------- teardown
@@ -413,7 +455,7 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
     }
 #if GEMM_PAIR
     // neither CTA may free tensor memory or leave (the leader's MMAs read the peer's shared memory,
-    // the peer's copies report to the leader's barriers) before both are done
+    // the peer's copies and epilogue report to the leader's barriers) before both are done
     cluster_sync();
 #endif
     if (warp == 5) {
