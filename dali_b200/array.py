@@ -314,9 +314,38 @@ class _Op:
         return Array._new(_c().c.dali_op_dot, a._h, b._h)
 
     def arange(self, start, stop=None, step=1):
+        """Lazy: ints give an int32 index expression, anything else op::arange(Array, Array, Array)."""
         if stop is None:
             start, stop = 0, start
-        return Array._new(_c().c.dali_array_arange, int(start), int(stop), int(step))
+        if all(isinstance(v, (int, np.integer)) for v in (start, stop, step)):
+            return Array._new(_c().c.dali_array_arange, int(start), int(stop), int(step))
+        a, b, c = _wrap(start), _wrap(stop), _wrap(step)
+        return Array._new(_c().c.dali_op_arange, a._h, b._h, c._h)
+
+    def diag(self, d, rows=None, cols=None):
+        d = _wrap(d)
+        if rows is None:
+            rows = d.shape[0]
+        return Array._new(_c().c.dali_op_diag, d._h, int(rows), int(rows if cols is None else cols))
+
+    def eye(self, rows, cols=None):
+        return self.diag(Array(1.0, DTYPE_FLOAT), rows, cols)
+
+    def one_hot(self, indices, depth, on_value, off_value):
+        on, off = _wrap(on_value), _wrap(off_value)
+        return Array._new(_c().c.dali_op_one_hot, indices._h, int(depth), on._h, off._h)
+
+    def outer(self, a, b):
+        return Array._new(_c().c.dali_op_outer, a._h, b._h)
+
+    def axis_scan(self, a, reducer, inclusive=True):
+        return Array._new(_c().c.dali_op_scan, a._h, reducer.encode(), int(bool(inclusive)))
+
+    def cumsum(self, a, inclusive=True):
+        return self.axis_scan(a, "sum", inclusive)
+
+    def cumprod(self, a, inclusive=True):
+        return self.axis_scan(a, "prod", inclusive)
 
     def astype(self, a, dtype):
         return a.astype(dtype)

@@ -74,6 +74,8 @@ class Library:
         c.dalib200_gemm_split_tf32.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
                                                ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_void_p,
                                                ctypes.c_void_p]
+        c.dalib200_scan.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int64,
+                                    ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64]
         c.dalib200_gemm_error_flag.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
         c.dalib200_last_gemm_kernel.restype = ctypes.c_size_t
         c.dalib200_last_gemm_kernel.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
@@ -236,6 +238,12 @@ class Library:
     def gemm_split_tf32(self, x, rows, cols, ld, hi, lo, transpose=False, device=0, stream=None):
         self.check(self.c.dalib200_gemm_split_tf32(device, ctypes.c_void_p(stream or 0), self._ptr(x), rows, cols, ld,
                                                    int(transpose), self._ptr(hi), self._ptr(lo)))
+
+    def scan(self, dtype, op, inclusive, rows, cols, x, out, in_row_stride=None, out_row_stride=None, device=0, stream=None):
+        """Running reduction (op 0 sum, 1 prod, 2 max, 3 min) along the rows of a [rows, cols] matrix."""
+        self.check(self.c.dalib200_scan(device, ctypes.c_void_p(stream or 0), dtype, op, int(bool(inclusive)), rows, cols,
+                                        self._ptr(x), cols if in_row_stride is None else in_row_stride, self._ptr(out),
+                                        (cols + (0 if inclusive else 1)) if out_row_stride is None else out_row_stride))
 
     def gemm_error_flag(self, device=0):
         f = ctypes.c_int(0)

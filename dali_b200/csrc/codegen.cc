@@ -133,6 +133,10 @@ struct Gen {
         o << "  const int tid = threadIdx.x;\n";
         for (size_t a = 0; a < p.args.size(); ++a) {
             bool ro = !p.args[a].written;
+            if (p.args[a].iota) {
+                o << "  const IotaPtr a" << a << "{" << W(L.arg_ptr((int)a)) << "};   // base value instead of a pointer\n";
+                continue;
+            }
             o << "  " << (ro ? "const " : "") << argT((int)a) << "* const a" << a << " = reinterpret_cast<"
               << (ro ? "const " : "") << argT((int)a) << "*>(" << W(L.arg_ptr((int)a)) << ");\n";
         }

@@ -61,7 +61,7 @@ const char* red_c(DType t) { return dtype_c_name(t); }
 // EPILOGUE_CHUNK(row, col0, acc, nvalid): thread-local 32-wide slab of one output row
 bool epilogue_macro(const Program& p, std::string* out, std::string* err) {
     if (!p.has_acc || p.nreduce != 0 || p.rank != 2) { *err = "epilogue program must be 'space 2 0' and read 'acc'"; return false; }
-    if (p.has_indirect || p.n_reductions) { *err = "epilogue program may not gather or reduce"; return false; }
+    if (p.has_indirect || p.n_reductions || p.has_iota) { *err = "epilogue program may not gather, reduce or use iota args"; return false; }
     const int nargs = (int)p.args.size();
     std::ostringstream o;
     auto W = [&](int w) { return "p.w[" + std::to_string(w) + "]"; };

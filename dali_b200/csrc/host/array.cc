@@ -117,6 +117,28 @@ Reduce::Reduce(const std::string& reducer, const Array& a, int nreduce, bool arg
     : Expression(N_REDUCE, std::vector<int>(a.shape().begin(), a.shape().end() - nreduce), dtype, {a}),
       reducer_(reducer), nreduce_(nreduce), arg_(arg) {}
 
+static std::vector<int> scan_shape(const Array& a, bool inclusive) {
+    std::vector<int> s = a.shape();
+    if (!inclusive) s.back() += 1;
+    return s;
+}
+Scan::Scan(const Array& a, const std::string& reducer, bool inclusive)
+    : Expression(N_SCAN, scan_shape(a, inclusive), a.dtype(), {a}), reducer_(reducer), inclusive_(inclusive) {}
+
+bool Iota::linear(int64_t* step) const {
+    // walk from the innermost dim: stride[k] must equal step * (product of the extents after k)
+    int64_t s = 0, expect = 0;
+    bool have = false;
+    for (int k = ndim() - 1; k >= 0; --k) {
+        if (shape_[k] == 1) continue;
+        if (!have) { s = strides_[k]; expect = s * shape_[k]; have = true; continue; }
+        if (strides_[k] != expect) return false;
+        expect *= shape_[k];
+    }
+    *step = have ? s : 0;
+    return true;
+}
+
 static std::vector<int> gather_shape(const Array& source, const Array& indices) {
     std::vector<int> s = indices.shape();
     s.insert(s.end(), source.shape().begin() + 1, source.shape().end());
@@ -297,7 +319,7 @@ static memory::Device device_of(const expression_ptr& e) {
     if (e->kind_ == N_BUFFER) return static_cast<BufferView*>(e.get())->memory_->preferred_device;
     for (const Array& a : e->arguments_) {
         if (a.is_stateless()) continue;
-        if (a.expression()->kind_ == N_SCALAR) continue;
+        if (a.expression()->kind_ == N_SCALAR || a.expression()->kind_ == N_IOTA) continue;
         return device_of(a.expression());
     }
     return memory::default_preferred_device;
@@ -513,6 +535,15 @@ Array Array::reshape(const std::vector<int>& new_shape_) const {
     }
     DALI_ASSERT(known == numel(), "New shape (" + shape_str(ns) + ") must have the same number of elements as previous shape (" + shape_str(shape()) + ")");
     if (ns == shape()) return *this;
+    if (Iota* io = as<Iota>(*this)) {
+        int64_t step;
+        if (io->linear(&step)) {      // offset + step * linear index, whatever the shape
+            std::vector<int64_t> st(ns.size(), 0);
+            int64_t acc = step;
+            for (int d = (int)ns.size() - 1; d >= 0; --d) { st[d] = acc; acc *= ns[d]; }
+            return Array(std::make_shared<Iota>(ns, io->offset_, st));
+        }
+    }
     Array src = *this;
     if (!src.is_buffer()) src.eval(false);
     if (!src.contiguous_memory()) src = src.ascontiguousarray();

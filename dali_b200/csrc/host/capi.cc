@@ -257,6 +257,21 @@ int dali_op_gather(dali_array_t source, dali_array_t indices, dali_array_t* out)
 int dali_op_gather_from_rows(dali_array_t source, dali_array_t indices, dali_array_t* out) {
     return guard([&]() { *out = wrap(op::gather_from_rows(source->a, indices->a)); });
 }
+int dali_op_diag(dali_array_t diag, int rows, int cols, dali_array_t* out) {
+    return guard([&]() { *out = wrap(op::diag(diag->a, rows, cols)); });
+}
+int dali_op_one_hot(dali_array_t indices, int depth, dali_array_t on_value, dali_array_t off_value, dali_array_t* out) {
+    return guard([&]() { *out = wrap(op::one_hot(indices->a, depth, on_value->a, off_value->a)); });
+}
+int dali_op_outer(dali_array_t a, dali_array_t b, dali_array_t* out) {
+    return guard([&]() { *out = wrap(op::outer(a->a, b->a)); });
+}
+int dali_op_scan(dali_array_t a, const char* reducer, int inclusive, dali_array_t* out) {
+    return guard([&]() { *out = wrap(op::axis_scan(a->a, reducer, inclusive != 0)); });
+}
+int dali_op_arange(dali_array_t start, dali_array_t stop, dali_array_t step, dali_array_t* out) {
+    return guard([&]() { *out = wrap(op::arange(start->a, stop->a, step->a)); });
+}
 int dali_op_softmax(dali_array_t logits, int axis, dali_array_t* out) {
     return guard([&]() { *out = wrap(op::softmax(logits->a, axis)); });
 }

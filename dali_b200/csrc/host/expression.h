@@ -21,7 +21,7 @@
 
 #include "dali/array/array.h"
 
-enum NodeKind { N_BUFFER, N_SCALAR, N_ELEMENTWISE, N_REDUCE, N_VIEW, N_GATHER, N_GATHER_ROWS, N_MATMUL, N_ASSIGN };
+enum NodeKind { N_BUFFER, N_SCALAR, N_ELEMENTWISE, N_REDUCE, N_VIEW, N_GATHER, N_GATHER_ROWS, N_MATMUL, N_ASSIGN, N_IOTA, N_SCAN };
 
 class Expression {
   public:
@@ -63,6 +63,29 @@ struct ScalarValue : public Expression {
     double value_;
     ScalarValue(double value, DType dtype) : Expression(N_SCALAR, {}, dtype, {}), value_(value) {}
     std::string name() const override { return "Scalar"; }
+};
+
+// value[i_0 .. i_{n-1}] = offset + sum_k i_k * strides[k], int32, no memory behind it.  One node
+// stands for the reference's Arange (dali/array/op/arange.cpp:12-52) and for the index
+// `query[k]` that its OneHot and Diag kernels compare against (one_hot.cpp:41-46,
+// eye.cpp:33-38); being affine, it slices, transposes, broadcasts and reshapes for free.
+struct Iota : public Expression {
+    int64_t offset_;
+    std::vector<int64_t> strides_;
+    Iota(const std::vector<int>& shape, int64_t offset, const std::vector<int64_t>& strides)
+        : Expression(N_IOTA, shape, DTYPE_INT32, {}), offset_(offset), strides_(strides) {}
+    std::string name() const override { return "Iota"; }
+    // offset + s * (row-major linear index)?  Then any reshape is again an Iota.
+    bool linear(int64_t* step) const;
+};
+
+// Running reduction along the last dim (dali/array/op/scan.cpp:19-180): inclusive keeps the
+// shape; exclusive starts with the reducer's neutral element and is one longer.
+struct Scan : public Expression {
+    std::string reducer_;   // sum | prod | max | min
+    bool inclusive_;
+    Scan(const Array& a, const std::string& reducer, bool inclusive);
+    std::string name() const override { return std::string(inclusive_ ? "inclusive_" : "exclusive_") + "scan_" + reducer_; }
 };
 
 // functor(arg0[, arg1]); rank-0 arguments broadcast implicitly.

@@ -90,6 +90,7 @@ struct Leaf {
     int64_t offset;                   // elements
     std::vector<int64_t> strides;     // `rank` space strides (+ 1 lead stride when indirect)
     bool elem_level, written, read, indirect;
+    bool iota = false;                // no memory: the value is offset + sum(index * stride)
 };
 
 struct Lowerer {
@@ -294,6 +295,33 @@ struct Lowerer {
                 id = new_value(sb->dtype_, is_elem, "ldx " + std::to_string(leaf) + " v" + std::to_string(vi));
                 break;
             }
+            case N_IOTA: {
+                Iota* io = static_cast<Iota*>(e.get());
+                Leaf L;
+                L.dtype = DTYPE_INT32;
+                L.offset = io->offset_;
+                L.strides.assign(rank, 0);
+                L.indirect = L.written = false;
+                L.read = true;
+                L.iota = true;
+                for (int k = 0; k < io->ndim(); ++k) {
+                    L.offset += m[k].off * io->strides_[k];
+                    if (m[k].src >= 0) L.strides[m[k].src] += m[k].mult * io->strides_[k];
+                }
+                for (int d = 0; d < rank; ++d) if (space[d] == 1) L.strides[d] = 0;
+                L.elem_level = nreduce == 0;
+                for (int d = n_outer; d < rank; ++d) if (L.strides[d] != 0) L.elem_level = true;
+                int leaf = -1;
+                for (size_t i = 0; i < leaves.size() && leaf < 0; ++i)
+                    if (leaves[i].iota && leaves[i].offset == L.offset && leaves[i].strides == L.strides) leaf = (int)i;
+                if (leaf < 0) { leaves.push_back(L); leaf = (int)leaves.size() - 1; }
+                id = new_value(DTYPE_INT32, leaves[leaf].elem_level, "ld " + std::to_string(leaf));
+                break;
+            }
+            case N_SCAN:
+                // never fused with what consumes it (dali/array/op/scan.cpp:37-39: chainable() is false)
+                id = visit(materialize(a), m);
+                break;
             case N_MATMUL: {
                 if (e.get() == acc_node && is_identity(m)) id = new_value(DTYPE_FLOAT, true, "acc");
                 else id = visit(materialize(a), m);
@@ -315,7 +343,8 @@ struct Lowerer {
         std::ostringstream o;
         o << "dali-ir 1\nspace " << rank << " " << nreduce << "\n";
         for (size_t i = 0; i < leaves.size(); ++i)
-            o << "arg " << i << " " << ir_dtype(leaves[i].dtype) << " " << (leaves[i].elem_level || nreduce == 0 ? "E" : "R") << "\n";
+            o << "arg " << i << " " << ir_dtype(leaves[i].dtype) << " " << (leaves[i].elem_level || nreduce == 0 ? "E" : "R")
+              << (leaves[i].iota ? " iota" : "") << "\n";
         for (size_t j = 0; j < scalars.size(); ++j) o << "scalar " << j << " " << ir_dtype(scalars[j].first) << "\n";
         for (const std::string& line : body) o << line << "\n";
         o << "end\n";
@@ -349,7 +378,8 @@ struct Lowerer {
         for (int pass = 0; pass < 2; ++pass)
             for (int i = 0; i < n; ++i) {
                 if ((pass == 1) != leaves[i].written) continue;
-                ptrs[i] = leaves[i].memory->data(device, leaves[i].written ? memory::AM_MUTABLE : memory::AM_READONLY);
+                ptrs[i] = leaves[i].iota ? nullptr
+                                         : leaves[i].memory->data(device, leaves[i].written ? memory::AM_MUTABLE : memory::AM_READONLY);
                 offsets[i] = leaves[i].offset;
                 strides[i] = leaves[i].strides.data();
             }
@@ -500,6 +530,36 @@ void run_matmul(const Array& dest, OPERATOR_T op, MatMul* mm) {
     ++tl_stats.gemms;
 }
 
+// dest (op)= running reduction of the rows of the argument (reference: AxisScan, dali/array/op/scan.cpp:19-180).
+void run_scan(const Array& dest, OPERATOR_T op, Scan* sc) {
+    if (op != OPERATOR_T_EQL || !as<BufferView>(dest)->contiguous()) {
+        Array tmp(dest.shape(), dest.dtype(), dest.preferred_device());
+        run_scan(tmp, OPERATOR_T_EQL, sc);
+        run_assignment(dest, op, tmp);
+        return;
+    }
+    Array in = sc->arguments_[0];
+    if (!in.is_buffer()) in.eval(false);
+    if (!as<BufferView>(in)->contiguous()) in = in.ascontiguousarray();
+    BufferView* a = as<BufferView>(in);
+    BufferView* d = as<BufferView>(dest);
+    const int64_t cols = a->shape_.back();
+    const int64_t rows = cols ? a->numel() / cols : 0;
+    const int64_t out_cols = cols + (sc->inclusive_ ? 0 : 1);
+    if (tl_dry_run) { ++tl_stats.kernels; tl_stats.last_variant = "scan." + sc->name(); return; }
+    memory::Device device = dest.preferred_device();
+    const int dev = device_index(device);
+    const int item = size_of_dtype(dest.dtype());
+    const char* pin = (const char*)a->memory_->data(device, memory::AM_READONLY) + a->offset_ * item;
+    char* pout = (char*)d->memory_->data(device, memory::AM_MUTABLE) + d->offset_ * item;
+    const int opcode = sc->reducer_ == "sum" ? DALIB200_SCAN_SUM : sc->reducer_ == "prod" ? DALIB200_SCAN_PROD
+                       : sc->reducer_ == "max" ? DALIB200_SCAN_MAX : DALIB200_SCAN_MIN;
+    check(dalib200_scan(dev, nullptr, (int)dest.dtype(), opcode, sc->inclusive_ ? 1 : 0, rows, cols, pin, cols, pout, out_cols),
+          "dalib200_scan");
+    ++tl_stats.kernels;
+    tl_stats.last_variant = "scan." + sc->name();
+}
+
 // dest (op)= tree(acc, other operands) with acc a product or the sum of two products: one
 // tcgen05 GEMM whose epilogue is the tree.  false = this layout is not one the tensor-core path
 // takes (the caller goes on with the general path); operands of the products have then already
@@ -530,6 +590,8 @@ bool try_fused_gemm(const Array& dest, OPERATOR_T op, const Array& value, const 
     L.acc_node = acc;
     int v = L.visit(value, identity_map(2));
     if (L.types[v] != DTYPE_FLOAT) return false;
+    for (const Leaf& leaf : L.leaves)
+        if (leaf.iota) return false;      // epilogue programs read memory operands only
     BufferView* db = as<BufferView>(dest);
     int leaf = L.leaf_for(db, identity_map(2), true, false, 0, 0, 0);
     if (op != OPERATOR_T_EQL) L.leaves[leaf].read = true;
@@ -646,6 +708,12 @@ void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) 
         find_matmul_sum(value, &acc);
         if (!acc) find_matmul(value, &acc);
         if (acc && acc->dtype_ == DTYPE_FLOAT && try_fused_gemm(dest, op, value, acc)) return;
+    }
+
+    // ---- a running reduction at the root has its own kernel
+    if (value.expression()->kind_ == N_SCAN && dest.is_buffer()) {
+        run_scan(dest, op, static_cast<Scan*>(value.expression().get()));
+        return;
     }
 
     // ---- MatMul at the root goes to the general GEMM entry point

@@ -2,6 +2,7 @@
 // dali/array/op/{unary,binary,reducers,reducer_operation,elementwise_operation,
 // gather,gather_from_rows,softmax,dot,arange}.cpp).
 #include <algorithm>
+#include <cmath>
 #include <map>
 #include <sstream>
 
@@ -335,17 +336,103 @@ Array dot(const Array& a, const Array& b) {
     throw std::runtime_error("dot of arrays with rank above 2 (tensordot) is not part of this back end");
 }
 
-// ---------------------------------------------------------------- arange
+// ---------------------------------------------------------------- arange, eye, one_hot, outer, scan
 Array arange(int start, int stop, int step) {
     DALI_ASSERT(step != 0, "arange's step cannot be zero.");
-    int n = step > 0 ? (stop - start + step - 1) / step : (start - stop - step - 1) / (-step);
-    DALI_ASSERT(n > 0, "arange's start, stop and step values lead to an empty array.");
-    int* buf = (int*)std::malloc(sizeof(int) * (size_t)n);
-    for (int i = 0; i < n; ++i) buf[i] = start + i * step;
-    return Array::adopt_buffer(buf, {n}, DTYPE_INT32);
+    // size = (int)ceil((stop - start) / step) in the operands' type (dali/array/op/arange.cpp:63):
+    // with three ints the division truncates, so arange(0, 10, 3) has 3 elements
+    const int n = (stop - start) / step;
+    DALI_ASSERT(n > 0, "arange's size must be strictly positive (got start = " + std::to_string(start) + ", stop = " +
+                           std::to_string(stop) + ", step = " + std::to_string(step) + ").");
+    return Array(std::make_shared<Iota>(std::vector<int>({n}), (int64_t)start, std::vector<int64_t>({(int64_t)step})));
 }
 Array arange(int start, int stop) { return arange(start, stop, 1); }
 Array arange(int stop) { return arange(0, stop, 1); }
+Array arange(const Array& start, const Array& stop, const Array& step) {
+    DALI_ASSERT(start.ndim() == 0, "arange's start argument must be a scalar but got start.shape = " + shape_str(start.shape()) + ".");
+    DALI_ASSERT(stop.ndim() == 0, "arange's stop argument must be a scalar but got stop.shape = " + shape_str(stop.shape()) + ".");
+    DALI_ASSERT(step.ndim() == 0, "arange's step argument must be a scalar but got step.shape = " + shape_str(step.shape()) + ".");
+    const double a = (double)start, b = (double)stop, st = (double)step;
+    const bool ints = start.dtype() == DTYPE_INT32 && stop.dtype() == DTYPE_INT32 && step.dtype() == DTYPE_INT32;
+    DALI_ASSERT(st != 0, "arange's step cannot be zero.");
+    // the quotient is formed in the operands' common type: integer operands truncate (arange.cpp:63)
+    const int size = ints ? ((int)b - (int)a) / (int)st : (int)std::ceil((b - a) / st);
+    DALI_ASSERT(size > 0, "arange's size must be strictly positive (got start = " + std::to_string(a) + ", stop = " +
+                              std::to_string(b) + ", step = " + std::to_string(st) + ").");
+    if (ints)
+        return Array(std::make_shared<Iota>(std::vector<int>({size}), (int64_t)a, std::vector<int64_t>({(int64_t)st})));
+    // start + index * step in start's type (dali/array/op/arange.cpp:41)
+    Array idx(std::make_shared<Iota>(std::vector<int>({size}), 0, std::vector<int64_t>({1})));
+    return unsafe_cast(start + unsafe_cast(idx, start.dtype()) * unsafe_cast(step, start.dtype()), start.dtype());
+}
+
+Array eye(int size) { return eye(size, size); }
+Array eye(int rows, int cols) {
+    DALI_ASSERT(rows > 0 && cols > 0, "eye's rows and cols must > 0 (got rows = " + std::to_string(rows) + ", cols = " + std::to_string(cols) + ").");
+    return diag(Array(1.0f), rows, cols);
+}
+Array diag(const Array& d) {
+    DALI_ASSERT(d.ndim() == 1, "diag with no size needs a vector");
+    return diag(d, d.shape()[0], d.shape()[0]);
+}
+Array diag(const Array& d, int rows) { return diag(d, rows, rows); }
+Array diag(const Array& d, int rows, int cols) {
+    DALI_ASSERT(rows > 0 && cols > 0, "diag's rows and cols must > 0 (got rows = " + std::to_string(rows) + ", cols = " + std::to_string(cols) + ").");
+    DALI_ASSERT(d.ndim() <= 1, "diag's argument must be a scalar or a vector (got array.shape = " + shape_str(d.shape()) + ").");
+    const int m = std::min(rows, cols);
+    if (d.ndim() == 1)
+        DALI_ASSERT(d.shape()[0] >= m, "diag's argument is smaller than the maximal diagonal item (array.shape = " +
+                                           shape_str(d.shape()) + ", rows = " + std::to_string(rows) + ", cols = " + std::to_string(cols) + ").");
+    const std::vector<int> shape({rows, cols});
+    Array i(std::make_shared<Iota>(shape, 0, std::vector<int64_t>({1, 0})));
+    Array j(std::make_shared<Iota>(shape, 0, std::vector<int64_t>({0, 1})));
+    Array on_diag = unsafe_cast(elementwise(i, j, "equals"), d.dtype());
+    Array values = d;
+    if (d.ndim() == 1) {
+        // only entries below min(rows, cols) are ever selected: view whichever side is long enough
+        if (d.shape()[0] >= cols) values = d.pluck_axis(0, Slice(0, cols)).expand_dims(0).broadcast_to_shape(shape);
+        else values = d.pluck_axis(0, Slice(0, rows)).expand_dims(1).broadcast_to_shape(shape);
+    }
+    return elementwise(on_diag, values, "where_nonzero");
+}
+
+Array one_hot(const Array& indices, int depth, const Array& on_value, const Array& off_value) {
+    DALI_ASSERT(indices.dtype() == DTYPE_INT32, "indices must be integers (got " + dtype_to_name(indices.dtype()) + ").");
+    DALI_ASSERT(on_value.ndim() == 0, "on_value must be a scalar (got on_value.ndim=" + std::to_string(on_value.ndim()) + ").");
+    DALI_ASSERT(off_value.ndim() == 0, "off_value must be a scalar (got off_value.ndim=" + std::to_string(off_value.ndim()) + ").");
+    DALI_ASSERT(depth > 0, "depth must be strictly positive (got depth=" + std::to_string(depth) + ").");
+    std::vector<int> shape = indices.shape();
+    shape.push_back(depth);
+    std::vector<int64_t> st(shape.size(), 0);
+    st.back() = 1;
+    Array position(std::make_shared<Iota>(shape, 0, st));
+    Array idx = indices.expand_dims(indices.ndim()).broadcast_to_shape(shape);
+    const DType t = on_value.dtype();
+    // on * is_on + (1 - is_on) * off, as the reference's kernel writes it (one_hot.cpp:45-46)
+    Array is_on = unsafe_cast(elementwise(idx, position, "equals"), t);
+    Array off = unsafe_cast(off_value, t);
+    return on_value * is_on + (unsafe_cast(Array(1.0), t) - is_on) * off;
+}
+
+Array outer(const Array& a_, const Array& b_) {
+    Array a = a_.ravel(), b = b_.ravel();
+    std::tie(a, b) = ensure_arguments_compatible(a, b, "outer", /*update_shape=*/false);
+    const std::vector<int> shape({a.shape()[0], b.shape()[0]});
+    return elementwise(a.expand_dims(1).broadcast_to_shape(shape), b.expand_dims(0).broadcast_to_shape(shape), "eltmul");
+}
+
+Array axis_scan(const Array& a, const std::string& reducer_name, bool inclusive) {
+    std::string r = reducer_name;
+    if (r.compare(0, 10, "reducers::") == 0) r = r.substr(10);
+    if (r == "maximum") r = "max";
+    if (r == "minimum") r = "min";
+    if (r == "product") r = "prod";
+    DALI_ASSERT(r == "sum" || r == "prod" || r == "max" || r == "min", "axis_scan: unknown reducer " + reducer_name);
+    Array x = a.ndim() == 0 ? a.expand_dims(0) : a;
+    return Array(std::make_shared<Scan>(x, r, inclusive));
+}
+Array cumsum(const Array& a, bool inclusive) { return axis_scan(a, "reducers::sum", inclusive); }
+Array cumprod(const Array& a, bool inclusive) { return axis_scan(a, "reducers::product", inclusive); }
 
 // ---------------------------------------------------------------- assignment
 Array assign(const Array& left, OPERATOR_T op, const Array& right) {

@@ -91,7 +91,9 @@ int functor_arity(const std::string& n) {
         "max_scalar", "min_scalar", "steep_sigmoid", "steep_sigmoid_backward", "clipped_relu",
         "clipped_relu_backward", "clip", "lessthanequal", "greaterthanequal",
         "binary_cross_entropy", "binary_cross_entropy_grad", "prelu", "prelu_backward_weights",
-        "prelu_backward_inputs", nullptr};
+        "prelu_backward_inputs",
+        "where_nonzero",   // not a reference functor: a != 0 ? b : 0, the select of its Diag kernel (op/eye.cpp:37)
+        nullptr};
     for (int i = 0; unary[i]; ++i) if (n == unary[i]) return 1;
     for (int i = 0; binary[i]; ++i) if (n == binary[i]) return 2;
     return 0;
@@ -144,9 +146,14 @@ bool parse_program(const std::string& text, Program* out, std::string* err) {
         if (t[0] == "arg") {
             int idx;
             ArgDecl a;
-            if (t.size() != 4 || !parse_int(t[1], &idx) || !parse_arg_dtype(t[2], &a.dtype) ||
-                (t[3] != "E" && t[3] != "R"))
-                return fail("expected 'arg <i> <dtype> <E|R>'");
+            if ((t.size() != 4 && t.size() != 5) || !parse_int(t[1], &idx) || !parse_arg_dtype(t[2], &a.dtype) ||
+                (t[3] != "E" && t[3] != "R") || (t.size() == 5 && t[4] != "iota"))
+                return fail("expected 'arg <i> <dtype> <E|R> [iota]'");
+            if (t.size() == 5) {
+                if (a.dtype != I32) return fail("an iota arg is int32");
+                a.iota = true;
+                p.has_iota = true;
+            }
             if (idx != (int)p.args.size()) return fail("args must be declared densely in order");
             if (!p.stmts.empty()) return fail("args must precede statements");
             a.elem_level = t[3] == "E";
@@ -188,6 +195,7 @@ bool parse_program(const std::string& text, Program* out, std::string* err) {
             s.dtype = p.args[s.arg].dtype;
             if (p.stmts[p.value_stmt[v]].dtype != (s.dtype == BF16 ? F32 : s.dtype))
                 return fail("stored value type differs from the arg's type (insert a cast)");
+            if (p.args[s.arg].iota) return fail("an iota arg cannot be stored to");
             p.args[s.arg].written = true;
             if (s.aop != A_ASSIGN) p.args[s.arg].read = true;
             if (x) p.args[s.arg].indirect = true;
@@ -213,6 +221,7 @@ bool parse_program(const std::string& text, Program* out, std::string* err) {
                 if (!parse_value_ref(t[4], &vi) || !value_ok(vi)) return fail("bad index value");
                 if (p.stmts[p.value_stmt[vi]].dtype != I32) return fail("gather index must be i32");
                 s.in.push_back(vi);
+                if (p.args[s.arg].iota) return fail("an iota arg cannot be gathered from");
                 p.args[s.arg].indirect = true;
                 p.has_indirect = true;
             }

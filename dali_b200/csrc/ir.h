@@ -54,6 +54,7 @@ struct ArgDecl {
     bool read = false;
     bool written = false;
     bool indirect = false;    // addressed through ldx / stx
+    bool iota = false;        // no memory behind it: the value IS the element offset (base + sum of index * stride), int32
 };
 
 struct Stmt {
@@ -80,6 +81,7 @@ struct Program {
     int max_stage = 0;             // deepest reduction nesting
     int n_reductions = 0;
     bool has_indirect = false;
+    bool has_iota = false;
     bool has_acc = false;          // reads the GEMM accumulator: an epilogue program
     bool has_bf16 = false;
     std::string text;              // canonical source text (for collision checks)

@@ -203,7 +203,7 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
     // ---------------------------------------------------------------- vector width
     auto aligned = [&](int a, int vec, bool along_outer) {
         const int bytes = dtype_size(p.args[a].dtype) * vec;
-        if (((uintptr_t)ptr[a]) % bytes != 0) return false;
+        if (!p.args[a].iota && ((uintptr_t)ptr[a]) % bytes != 0) return false;
         const std::vector<Dim>& other = along_outer ? inner : outer;
         for (const Dim& d : other)
             if (d.stride[a] % vec != 0) return false;
@@ -312,7 +312,8 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
     for (int k = 0; k < v.nout; ++k) out.words[L.w_oshape + k] = outer[k].extent;
     for (int k = 0; k < v.nin; ++k) out.words[L.w_ishape + k] = inner[k].extent;
     for (int a = 0; a < nargs; ++a) {
-        out.words[L.arg_ptr(a)] = (long long)(uintptr_t)ptr[a];
+        // an iota arg has no memory: its "pointer" word is the base value (the element offset)
+        out.words[L.arg_ptr(a)] = p.args[a].iota ? (long long)(offsets ? offsets[a] : 0) : (long long)(uintptr_t)ptr[a];
         // lead stride of an indirectly addressed arg travels as one extra stride
         // entry after the `rank` space strides
         long long xs = 0;

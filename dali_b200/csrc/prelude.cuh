@@ -27,6 +27,8 @@ template <typename T> DEV T f_eltmul(T a, T b) { return a * b; }
 template <typename T> DEV T f_eltdiv(T a, T b) { return a / b; }
 template <typename T> DEV T f_equals(T a, T b) { return a == b ? (T)1 : (T)0; }
 template <typename T> DEV T f_fill(T a, T b) { return b; }
+// the select of the reference's Diag kernel, "i == j ? diag[j] : 0" (dali/array/op/eye.cpp:33-38), as a functor
+template <typename T> DEV T f_where_nonzero(T a, T b) { return a != (T)0 ? b : (T)0; }
 template <typename T> DEV T f_div_grad(T a, T b) { return a / (b * b); }
 template <typename T> DEV T f_threshold(T a, T b) { return a < b ? (T)1 : (T)0; }
 template <typename T> DEV T f_max_scalar(T a, T b) { return a > b ? a : b; }
@@ -269,3 +271,19 @@ DEV void atomic_exch(double* p, double v) { atomicExch((unsigned long long*)p, (
 template <typename T, int N> struct alignas(sizeof(T) * N) Vec { T x[N]; };
 template <typename T, int N> DEV Vec<T, N> vload(const T* p) { return *reinterpret_cast<const Vec<T, N>*>(p); }
 template <typename T, int N> DEV void vstore(T* p, const Vec<T, N>& v) { *reinterpret_cast<Vec<T, N>*>(p) = v; }
+
+// An argument with no memory behind it whose "element" at offset i is base + i: with the
+// per-dim strides every argument has, base + sum(index_d * stride_d) is any affine function
+// of the iteration index (what the reference's arange / one_hot / diag kernels read from
+// `query`, dali/array/op/arange.cpp:41, one_hot.cpp:45, eye.cpp:37).
+struct IotaPtr {
+    i64 base;
+    DEV int operator[](i64 i) const { return (int)(base + i); }
+    DEV IotaPtr operator+(i64 i) const { return IotaPtr{base + i}; }
+};
+template <typename T, int N> DEV Vec<T, N> vload(IotaPtr p) {
+    Vec<T, N> v;
+#pragma unroll
+    for (int j = 0; j < N; ++j) v.x[j] = (T)(p.base + j);
+    return v;
+}

@@ -628,7 +628,7 @@ int dalib200_launch_host(uint64_t hash, int device, const int64_t* space, int sp
     DeviceRestore restore_device;
     State& s = S();
     std::vector<DType> dts;
-    std::vector<bool> rd, wr;
+    std::vector<bool> rd, wr, iota;
     {
         std::lock_guard<std::mutex> g(s.mu);
         int rc = check_device(device);
@@ -636,11 +636,14 @@ int dalib200_launch_host(uint64_t hash, int device, const int64_t* space, int sp
         auto pit = s.programs.find(hash);
         if (pit == s.programs.end()) { set_error("unknown kernel hash"); return DALIB200_ERR_NOT_FOUND; }
         if (n_arrays != (int)pit->second.args.size()) { set_error("launch: wrong number of arrays"); return DALIB200_ERR_INVALID; }
-        for (const ArgDecl& a : pit->second.args) { dts.push_back(a.dtype); rd.push_back(a.read); wr.push_back(a.written); }
+        for (const ArgDecl& a : pit->second.args) {
+            dts.push_back(a.dtype); rd.push_back(a.read); wr.push_back(a.written); iota.push_back(a.iota);
+        }
     }
     std::vector<void*> dev(n_arrays, nullptr);
     int rc = DALIB200_OK;
     for (int a = 0; a < n_arrays && rc == DALIB200_OK; ++a) {
+        if (iota[a]) continue;      // nothing behind it
         size_t bytes = (size_t)extents[a] * dtype_size(dts[a]);
         rc = dalib200_alloc(device, bytes, &dev[a]);
         // partially written views keep their untouched elements: upload written args too

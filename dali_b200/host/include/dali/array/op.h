@@ -112,9 +112,25 @@ Array inner(const Array& a, const Array& b);
 Array dot(const Array& a, const Array& b);
 
 // ---- construction helpers the reference's tests lean on
+// lazy: an affine index expression, no memory until something evaluates it (op/arange.h)
 Array arange(int start, int stop, int step);
 Array arange(int start, int stop);
 Array arange(int stop);
+Array arange(const Array& start, const Array& stop, const Array& step);   // scalars; dtype of `start`
+// op/eye.h: value[i, j] = i == j ? diag[j] : 0 (diag a scalar or a vector)
+Array eye(int size);
+Array eye(int rows, int cols);
+Array diag(const Array& diag);
+Array diag(const Array& diag, int rows);
+Array diag(const Array& diag, int rows, int cols);
+// op/one_hot.h: out[..., d] = indices[...] == d ? on_value : off_value, dtype of on_value
+Array one_hot(const Array& indices, int depth, const Array& on_value, const Array& off_value);
+// op/outer.h: out[i, j] = a.ravel()[i] * b.ravel()[j]
+Array outer(const Array& a, const Array& b);
+// op/scan.h: running reduction over the last dim; exclusive results are one element longer
+Array axis_scan(const Array& a, const std::string& reducer_name, bool inclusive);
+Array cumsum(const Array& a, bool inclusive = true);
+Array cumprod(const Array& a, bool inclusive = true);
 Array fill(const Array& x, double value);      // same-shaped array holding `value`
 
 // ---- assignment

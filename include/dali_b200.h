@@ -228,6 +228,19 @@ int dalib200_gemm_error_flag(int device, int* flag);
  * ("simt", "tcgen05.bf16", "tcgen05.tf32x3", ...); for tests and profiles. */
 size_t dalib200_last_gemm_kernel(char* buffer, size_t capacity);
 
+/* ---- running reductions ----------------------------------------------------
+ * Replaces the reference's AxisScan node (op::cumsum / op::cumprod / op::axis_scan,
+ * dali/array/op/scan.cpp:19-180, kernels :47-140): a running sum / product / max /
+ * min along every row of a row-major [rows, cols] matrix (unit inner stride, row
+ * pitches in elements).  inclusive != 0: out is [rows, cols].  inclusive == 0:
+ * out is [rows, cols + 1], out[r][0] is the reducer's neutral element (0, 1,
+ * lowest, max) and out[r][i + 1] the inclusive value at i (scan.cpp:9-15).
+ * dtype f32 / f64 / i32.  in and out must not overlap. */
+enum dalib200_scan_op { DALIB200_SCAN_SUM = 0, DALIB200_SCAN_PROD = 1, DALIB200_SCAN_MAX = 2, DALIB200_SCAN_MIN = 3 };
+int dalib200_scan(int device, void* stream, int dtype, int op, int inclusive,
+                  int64_t rows, int64_t cols, const void* in, int64_t in_row_stride,
+                  void* out, int64_t out_row_stride);
+
 /* ---- allocation-free entry point ----------------------------------------------
  * No counterpart in the reference (it allocates freely through memory::bank).
  *

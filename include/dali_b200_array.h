@@ -76,6 +76,12 @@ int dali_op_reduce(const char* name, dali_array_t a, const int* axes, int n_axes
 int dali_op_argreduce(const char* name, dali_array_t a, int axis, int all_axes, dali_array_t* out);
 int dali_op_gather(dali_array_t source, dali_array_t indices, dali_array_t* out);
 int dali_op_gather_from_rows(dali_array_t source, dali_array_t indices, dali_array_t* out);
+/* op/eye.h, op/one_hot.h, op/outer.h, op/scan.h, op/arange.h: all lazy; reducer = sum | prod | max | min */
+int dali_op_diag(dali_array_t diag, int rows, int cols, dali_array_t* out);
+int dali_op_one_hot(dali_array_t indices, int depth, dali_array_t on_value, dali_array_t off_value, dali_array_t* out);
+int dali_op_outer(dali_array_t a, dali_array_t b, dali_array_t* out);
+int dali_op_scan(dali_array_t a, const char* reducer, int inclusive, dali_array_t* out);
+int dali_op_arange(dali_array_t start, dali_array_t stop, dali_array_t step, dali_array_t* out);
 int dali_op_softmax(dali_array_t logits, int axis, dali_array_t* out);
 int dali_op_dot(dali_array_t a, dali_array_t b, dali_array_t* out);
 

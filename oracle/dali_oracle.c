@@ -320,3 +320,55 @@ void oracle_bias_tanh_f32(const float* x, const float* bias, int64_t rows, int64
     for (int64_t r = 0; r < rows; ++r)
         for (int64_t c = 0; c < cols; ++c) out[r * cols + c] = tanh_f32(x[r * cols + c] + bias[c]);
 }
+
+/* ---- running reductions: AxisScan, dali/array/op/scan.cpp:47-77 --------------------
+ * The CPU body walks each row left to right: so_far = init; for i: so_far = so_far (op) x[i];
+ * out = so_far.  Exclusive results start with the neutral element and are one longer.
+ * op: 0 sum, 1 prod, 2 max, 3 min; neutral elements as in jit/reducer_kernels.h:10-54. */
+#define SCAN_BODY(T, INIT_MAX, INIT_MIN)                                                          \
+    for (int64_t r = 0; r < rows; ++r) {                                                          \
+        const T* x = (const T*)in + r * cols;                                                     \
+        T* y = (T*)out + r * (cols + (inclusive ? 0 : 1));                                        \
+        volatile T so_far = op == 0 ? (T)0 : op == 1 ? (T)1 : op == 2 ? (T)(INIT_MAX) : (T)(INIT_MIN); \
+        if (!inclusive) *y++ = so_far;                                                            \
+        for (int64_t i = 0; i < cols; ++i) {                                                      \
+            const T v = x[i];                                                                     \
+            if (op == 0) so_far = so_far + v;                                                     \
+            else if (op == 1) so_far = so_far * v;                                                \
+            else if (op == 2) so_far = so_far > v ? so_far : v;                                   \
+            else so_far = so_far < v ? so_far : v;                                                \
+            y[i] = so_far;                                                                        \
+        }                                                                                         \
+    }
+int oracle_scan(int op, int dtype, int inclusive, int64_t rows, int64_t cols, const void* in, void* out) {
+    if (op < 0 || op > 3) return 1;
+    if (dtype == 0) { SCAN_BODY(float, -FLT_MAX, FLT_MAX) }
+    else if (dtype == 1) { SCAN_BODY(double, -DBL_MAX, DBL_MAX) }
+    else if (dtype == 2) { SCAN_BODY(int, INT_MIN, INT_MAX) }
+    else return 1;
+    return 0;
+}
+
+/* ---- one_hot: dali/array/op/one_hot.cpp:41-46 -----------------------------------------
+ * T is_on = indices[...] == d; return on * is_on + (1.0 - is_on) * off   (T = dtype of on_value) */
+int oracle_one_hot(const int* idx, int64_t n, int depth, int dtype, double on, double off, void* out) {
+    for (int64_t i = 0; i < n; ++i)
+        for (int d = 0; d < depth; ++d) {
+            if (dtype == 0) { float is_on = idx[i] == d; ((float*)out)[i * depth + d] = (float)((float)on * is_on + (1.0 - is_on) * (float)off); }
+            else if (dtype == 1) { double is_on = idx[i] == d; ((double*)out)[i * depth + d] = on * is_on + (1.0 - is_on) * off; }
+            else if (dtype == 2) { int is_on = idx[i] == d; ((int*)out)[i * depth + d] = (int)((int)on * is_on + (1.0 - is_on) * (int)off); }
+            else return 1;
+        }
+    return 0;
+}
+
+/* ---- diag / eye: dali/array/op/eye.cpp:33-38: query[1] == query[0] ? diag[query[1]] : 0 ----
+ * d_len == 0: scalar diag (d points at one element). */
+int oracle_diag(int dtype, const void* d, int64_t d_len, int64_t rows, int64_t cols, void* out) {
+    const int item = dtype == 1 ? 8 : 4;
+    if (dtype < 0 || dtype > 2) return 1;
+    memset(out, 0, (size_t)(rows * cols) * item);
+    for (int64_t i = 0; i < rows && i < cols; ++i)
+        memcpy((char*)out + (i * cols + i) * item, (const char*)d + (d_len ? i : 0) * item, item);
+    return 0;
+}

@@ -196,3 +196,59 @@ def bias_tanh(x, bias):
     out = np.empty_like(x)
     lib().oracle_bias_tanh_f32(_p(x), _p(bias), _i64(x.shape[0]), _i64(x.shape[1]), _p(out))
     return out
+
+
+_SCAN_OPS = {"sum": 0, "prod": 1, "max": 2, "min": 3}
+
+
+def scan(kind, x, inclusive=True):
+    """Running reduction over the last axis, in the reference's left-to-right order (op/scan.cpp:47-77)."""
+    x = np.ascontiguousarray(x)
+    cols = x.shape[-1]
+    rows = x.size // cols if cols else 0
+    out = np.empty(x.shape[:-1] + (cols + (0 if inclusive else 1),), x.dtype)
+    rc = lib().oracle_scan(_SCAN_OPS[kind], _DT[x.dtype], int(bool(inclusive)), _i64(rows), _i64(cols), _p(x), _p(out))
+    if rc != 0:
+        raise KeyError((kind, x.dtype))
+    return out
+
+
+def one_hot(indices, depth, on_value, off_value, dtype=np.float64):
+    """out[..., d] = on * (idx == d) + (1 - (idx == d)) * off in on_value's type (op/one_hot.cpp:41-46)."""
+    idx = np.ascontiguousarray(indices, dtype=np.int32)
+    out = np.empty(idx.shape + (depth,), dtype)
+    rc = lib().oracle_one_hot(_p(idx), _i64(idx.size), int(depth), _DT[np.dtype(dtype)], ctypes.c_double(on_value),
+                              ctypes.c_double(off_value), _p(out))
+    if rc != 0:
+        raise KeyError(dtype)
+    return out
+
+
+def diag(d, rows, cols):
+    """value[i, j] = i == j ? d[j] : 0 with d a scalar or a vector (op/eye.cpp:33-38)."""
+    scalar = np.ndim(d) == 0
+    d = np.ascontiguousarray(d)          # a scalar becomes shape (1,)
+    out = np.empty((rows, cols), d.dtype)
+    rc = lib().oracle_diag(_DT[d.dtype], _p(d), _i64(0 if scalar else d.shape[0]), _i64(rows), _i64(cols), _p(out))
+    if rc != 0:
+        raise KeyError(d.dtype)
+    return out
+
+
+def arange(start, stop, step, dtype=np.int32):
+    """start + i * step for i < size, in start's type (op/arange.cpp:41).  size = (int)ceil((stop - start) / step)
+    evaluated in the operands' common type (arange.cpp:63): for three ints the division TRUNCATES, so
+    arange(10, -5, -4) has 3 elements and arange(0, 10, 3) has 3, one fewer than numpy's."""
+    if all(isinstance(v, (int, np.integer)) for v in (start, stop, step)):
+        n = int((int(stop) - int(start)) / int(step))          # C integer division truncates toward zero
+    else:
+        n = int(np.ceil((float(stop) - float(start)) / float(step)))
+    t = np.dtype(dtype).type
+    return (t(start) + np.arange(n).astype(dtype) * t(step)).astype(dtype)
+
+
+def outer(a, b):
+    """left[i] * right[j] over the ravelled operands (op/outer.cpp:21, :43-47)."""
+    a, b = np.ravel(a), np.ravel(b)
+    t = np.result_type(a.dtype, b.dtype)
+    return a.astype(t)[:, None] * b.astype(t)[None, :]

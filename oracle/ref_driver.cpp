@@ -19,10 +19,19 @@
 //   chain   x w b out [reps]         sum(sigmoid(x*w+b)*exp(-x*x))
 //   gather  src idx out              gather_rows src idx out
 //   scatter_add dest idx out         (dest[idx] += 1, result = dest)
+//   arange  <i32|f32|f64> start stop step out     (numbers on the command line)
+//   diag_scalar <i32|f32|f64> value rows cols out  diag_vec d rows cols out
+//   one_hot idx depth on off out     (on / off: doubles on the command line, as the reference's test passes them)
+//   outer   a b out                  scan <sum|prod> <0|1 inclusive> in out
 // Every timed case prints "TIME_MS first=<ms> best=<ms> reps=<n>".
 #include "dali/array/array.h"
 #include "dali/array/op.h"
 #include "dali/array/op/softmax.h"
+#include "dali/array/op/arange.h"
+#include "dali/array/op/eye.h"
+#include "dali/array/op/one_hot.h"
+#include "dali/array/op/outer.h"
+#include "dali/array/op/scan.h"
 #include "dali/utils/random.h"
 #include "dali/utils/compiler.h"
 
@@ -228,6 +237,32 @@ int main(int argc, char** argv) {
         Array gathered = dest[idx];
         (gathered += 1).eval();
         save(a[2], dest);
+    } else if (c == "arange" && n >= 5) {
+        std::string t(a[0]);
+        auto num = [&](const char* v) {
+            return t == "i32" ? Array(std::atoi(v)) : t == "f32" ? Array((float)std::atof(v)) : Array(std::atof(v));
+        };
+        Array r = op::arange(num(a[1]), num(a[2]), num(a[3])); r.eval();
+        save(a[4], r);
+    } else if (c == "diag_scalar" && n >= 5) {
+        std::string t(a[0]);
+        Array d = t == "i32" ? Array(std::atoi(a[1])) : t == "f32" ? Array((float)std::atof(a[1])) : Array(std::atof(a[1]));
+        Array r = op::diag(d, std::atoi(a[2]), std::atoi(a[3])); r.eval();
+        save(a[4], r);
+    } else if (c == "diag_vec" && n >= 4) {
+        Array r = op::diag(load(a[0]), std::atoi(a[1]), std::atoi(a[2])); r.eval();
+        save(a[3], r);
+    } else if (c == "one_hot" && n >= 5) {
+        Array r = op::one_hot(load(a[0]), std::atoi(a[1]), std::atof(a[2]), std::atof(a[3])); r.eval();
+        save(a[4], r);
+    } else if (c == "outer" && n >= 3) {
+        Array r = op::outer(load(a[0]), load(a[1])); r.eval();
+        save(a[2], r);
+    } else if (c == "scan" && n >= 4) {
+        Array x = load(a[2]);
+        Array r = std::string(a[0]) == "sum" ? op::cumsum(x, std::atoi(a[1]) != 0) : op::cumprod(x, std::atoi(a[1]) != 0);
+        r.eval();
+        save(a[3], r);
     } else {
         return usage();
     }

@@ -168,6 +168,31 @@ def main():
     xc = rng.standard_normal((4099,)).astype(np.float32)
     g["chain/x"] = xc
     g["chain/sum"] = run("chain", [xc, "0.5", "0.1"])[0]
+    # ---- arange / diag / one_hot / outer / running reductions (appended: earlier draws are unchanged)
+    g["arange/i32_2_17_3"] = run("arange", ["i32", 2, 17, 3])[0]
+    g["arange/i32_24"] = run("arange", ["i32", 0, 24, 1])[0]
+    g["arange/i32_neg"] = run("arange", ["i32", 10, -5, -4])[0]
+    # (a float arange does not compile in the reference: op::ceil names a functor, "ceiling", that
+    # dali/array/functor.h does not define; and diag of a vector throws "cast a non-jit expression
+    # (Buffer) into a JITNode": only the scalar diagonal can be pinned against it)
+    g["diag/f64_5_4x5"] = run("diag_scalar", ["f64", 5.0, 4, 5])[0]
+    g["diag/f32_1_6x3"] = run("diag_scalar", ["f32", 1.0, 6, 3])[0]
+    g["diag/i32_7_3x3"] = run("diag_scalar", ["i32", 7, 3, 3])[0]
+    oh_idx = rng.integers(0, 7, (2, 3)).astype(np.int32)
+    g["one_hot/idx"] = oh_idx
+    g["one_hot/out"] = run("one_hot", [oh_idx, 7, 112.2, 42.0])[0]
+    oa = rng.standard_normal((5,)).astype(np.float32)
+    ob = rng.standard_normal((2, 4)).astype(np.float32)
+    g["outer/a"], g["outer/b"] = oa, ob
+    g["outer/out"] = run("outer", [oa, ob])[0]
+    si = rng.integers(-9, 10, (4, 23)).astype(np.int32)
+    sf = (rng.random((3, 41)) + 0.5).astype(np.float32)
+    g["scan/i32"], g["scan/f32"] = si, sf
+    for kind in ("sum", "prod"):
+        for inc in (1, 0):
+            g["scan/i32/%s/%d" % (kind, inc)] = run("scan", [kind, inc, si])[0]
+            g["scan/f32/%s/%d" % (kind, inc)] = run("scan", [kind, inc, sf])[0]
+    g["scan/1d/sum/0"] = run("scan", ["sum", 0, np.arange(20, dtype=np.int32)])[0]
     np.savez_compressed(OUT, **g)
     print("wrote %s: %d arrays, %d bytes" % (OUT, len(g), os.path.getsize(OUT)))
 

@@ -185,3 +185,38 @@ def test_inplace_and_scatter_lowering():
     lse <<= Array.ones((2, 5), DTYPE_INT32)
     lse.eval()
     assert "red sum" in last_ir()
+
+
+def test_index_ops_are_lazy_and_fuse_into_one_kernel():
+    """arange / eye / one_hot / outer are affine index expressions or views: no memory, no kernel of their own."""
+    x = Array(np.zeros((3, 2), np.float32))
+    r = x + op.arange(6).reshape((3, 2)).astype(DTYPE_FLOAT)
+    assert launched(r) == {"kernels": 1, "gemms": 0, "temporaries": 0}
+    assert " iota" in last_ir() and last_ir().count("arg ") == 3
+    idx = Array(np.zeros((2, 3), np.int32))
+    oh = op.one_hot(idx, 7, 112.2, 42.0)
+    assert oh.shape == (2, 3, 7) and oh.dtype == DTYPE_DOUBLE
+    assert launched(oh) == {"kernels": 1, "gemms": 0, "temporaries": 0}
+    e = op.eye(4, 5)
+    assert e.shape == (4, 5) and launched(e) == {"kernels": 1, "gemms": 0, "temporaries": 0}
+    assert last_ir().count(" iota") == 2 and "where_nonzero" in last_ir()
+    a, b = Array(np.zeros(3, np.float32)), Array(np.zeros(4, np.float32))
+    o = op.outer(op.tanh(a - 3.0), op.tanh(b - 2.0))          # tests.cpp:968-974: chainable
+    assert o.shape == (3, 4) and launched(o) == {"kernels": 1, "gemms": 0, "temporaries": 0}
+    s = op.arange(24).reshape((2, 3, 4))[:, 1, ::2]            # slicing an arange stays an index expression
+    assert s.shape == (2, 2) and launched(s) == {"kernels": 1, "gemms": 0, "temporaries": 0}
+    with pytest.raises(RuntimeError):
+        op.one_hot(Array(np.zeros(3, np.float32)), 4, 1.0, 0.0)
+    with pytest.raises(RuntimeError):
+        op.diag(Array(np.zeros(2, np.float32)), 3, 4)
+
+
+def test_running_reduction_lowering():
+    x = Array(np.zeros((4, 10), np.float32))
+    c = op.cumsum(op.tanh(x))
+    assert c.shape == (4, 10)
+    assert launched(c) == {"kernels": 2, "gemms": 0, "temporaries": 0}      # fused producer, then the scan kernel
+    assert last_variant() == "scan.inclusive_scan_sum"
+    assert op.cumprod(x, inclusive=False).shape == (4, 11)
+    y = op.cumsum(x) * 2.0                                                   # never fused with its consumer (scan.cpp:37-39)
+    assert launched(y) == {"kernels": 2, "gemms": 0, "temporaries": 1}

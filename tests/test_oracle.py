@@ -156,3 +156,45 @@ def test_known_answers_gather_and_dot():
     b = np.arange(12, dtype=np.int32).reshape(3, 4)
     np.testing.assert_array_equal(oracle.gemm(a, b), a @ b)                    # dot_tests.cpp:37-67
     np.testing.assert_array_equal(oracle.gemm(a.astype(np.float32), b.astype(np.float32)), (a @ b).astype(np.float32))
+
+
+def test_arange_diag_one_hot_outer_pinned_by_the_reference(golden):
+    """The restated index ops against what the reference's own kernels wrote, bit for bit."""
+    np.testing.assert_array_equal(oracle.arange(2, 17, 3), golden["arange/i32_2_17_3"])
+    np.testing.assert_array_equal(oracle.arange(0, 24, 1), golden["arange/i32_24"])
+    np.testing.assert_array_equal(oracle.arange(10, -5, -4), golden["arange/i32_neg"])
+    for key, d, (r, c) in (("diag/f64_5_4x5", np.float64(5.0), (4, 5)), ("diag/f32_1_6x3", np.float32(1.0), (6, 3)),
+                           ("diag/i32_7_3x3", np.int32(7), (3, 3))):
+        want = golden[key]
+        got = oracle.diag(d, r, c)
+        assert got.dtype == want.dtype
+        np.testing.assert_array_equal(got, want)
+    # vector diagonal: the reference throws on it; known answer from its kernel text (eye.cpp:37)
+    np.testing.assert_array_equal(oracle.diag(np.arange(1, 6, dtype=np.float32), 3, 5),
+                                  np.eye(3, 5, dtype=np.float32) * np.arange(1, 6, dtype=np.float32))
+    want = golden["one_hot/out"]
+    got = oracle.one_hot(golden["one_hot/idx"], 7, 112.2, 42.0, np.float64)
+    assert got.dtype == want.dtype
+    np.testing.assert_array_equal(got, want)                                   # tests.cpp:1000-1012
+    np.testing.assert_array_equal(oracle.outer(golden["outer/a"], golden["outer/b"]), golden["outer/out"])
+
+
+def test_running_reductions_pinned_by_the_reference(golden):
+    for dt in ("i32", "f32"):
+        x = golden["scan/" + dt]
+        for kind in ("sum", "prod"):
+            for inc in (1, 0):
+                want = golden["scan/%s/%s/%d" % (dt, kind, inc)]
+                got = oracle.scan(kind, x, bool(inc))
+                assert got.shape == want.shape and got.dtype == want.dtype
+                np.testing.assert_array_equal(got, want)
+    np.testing.assert_array_equal(oracle.scan("sum", np.arange(20, dtype=np.int32), False), golden["scan/1d/sum/0"])
+    # known answers of tests.cpp:1737-1771: cumsum of arange(0, 20), cumprod of arange(1, 21) (int32 wraps like the reference's)
+    a = np.arange(20, dtype=np.int32)
+    np.testing.assert_array_equal(oracle.scan("sum", a), np.cumsum(a, dtype=np.int32))
+    np.testing.assert_array_equal(oracle.scan("sum", a.reshape(2, 10), False)[:, 1:], np.cumsum(a.reshape(2, 10), axis=1, dtype=np.int32))
+    p = np.arange(1, 13, dtype=np.int32)
+    np.testing.assert_array_equal(oracle.scan("prod", p), np.cumprod(p, dtype=np.int32))
+    f = np.array([[3.0, -1.0, 7.0, 2.0]], np.float32)
+    np.testing.assert_array_equal(oracle.scan("max", f), [[3, 3, 7, 7]])
+    np.testing.assert_array_equal(oracle.scan("min", f, False), [[np.finfo(np.float32).max, 3, -1, -1, -1]])
