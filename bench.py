@@ -362,6 +362,7 @@ class Lstm(Workload):
     """BASELINE config 2: fused LSTM cell step, fp32, B=256 H=1024 per GPU."""
     name = "lstm"
     B, H = 256, 1024
+    e2e_api = "page-locked host arrays -> lazy Array/op:: expression -> eval -> host arrays (C++ front end through its C binding)"
 
     def __init__(self, *a):
         super().__init__(*a)
@@ -513,6 +514,7 @@ class Lstm(Workload):
 class Gemm(Workload):
     """BASELINE config 4: tanh(dot(A,B)+bias), bf16 8192^3, fp32 accumulate, bf16 out."""
     name = "gemm"
+    e2e_api = "C ABI with caller-managed copies (page-locked host -> device, dalib200_gemm_fused, device -> page-locked host, sync)"
     N = 8192
 
     def __init__(self, *a, n=None):
@@ -671,7 +673,79 @@ class ReduceAxis0(Workload):
         return {"ms": times, "bytes": m * m * 4, "cores": 1, "kind": "reference", "sample": "a [2048,2048] corner (1/16 of the bytes)"}
 
 
-WORKLOADS = {"lstm": Lstm, "softmax": Softmax, "reduce": ReduceAxis0, "gemm": Gemm, "chain": Chain}
+class Cumsum(Workload):
+    """Running sum along the rows of fp32 [8192,8192] (op::cumsum; not one of the BASELINE configs: the first of
+    the operators either side of the path, measured to the same bar)."""
+    name = "scan"
+    N = 8192
+    kernel_name = "scan_rows_kernel<float, sum, 256 threads per row, 128-bit> (dalib200_scan)"
+    e2e_api = "C ABI with caller-managed copies (page-locked host -> device, dalib200_scan, device -> page-locked host, sync)"
+
+    def __init__(self, *a):
+        super().__init__(*a)
+        import numpy as np
+        self.np = np
+        t = self.torch
+        t.manual_seed(1234 + 6 + self.rank)
+        self.x = [t.rand(self.N, self.N, device="cuda") * 2 - 1 for _ in range(2)]    # 2 x 256 MiB > L2
+        self.out = t.empty(self.N, self.N, device="cuda")
+        self.scaling = "weak"
+        self.launches_per_step = 1
+
+    def describe(self):
+        return {"workload": "op::cumsum over the last axis of fp32 [8192,8192] ~ U(-1,1) per GPU (inclusive)",
+                "l2": "two 256 MiB inputs alternate, 256 MiB output (768 MiB > L2)",
+                "parallelism": "rows sharded: each of %d GPU(s) scans its own rows, no collective" % self.world}
+
+    def bytes_per_step(self):
+        return 2 * self.N * self.N * 4
+
+    def launch_step(self, i, stream):
+        self.lib.scan(0, 0, 1, self.N, self.N, self.x[i % 2], self.out, device=self.device, stream=stream)
+
+    def step(self, i):
+        self.launch_step(i, self.stream)
+
+    def graph_fn(self):
+        return self.launch_step
+
+    def e2e_setup(self):
+        t = self.torch
+        self.hx = t.empty(self.N, self.N, pin_memory=True); self.hx.copy_(self.x[0])
+        self.hout = t.empty(self.N, self.N, pin_memory=True)
+        self.h2d = self.d2h = self.N * self.N * 4
+
+    def e2e_step(self, i):
+        # the C ABI with caller-managed copies (page-locked host -> device, scan, device -> page-locked host)
+        self.x[0].copy_(self.hx, non_blocking=True)
+        self.launch_step(0, self.stream)
+        self.hout.copy_(self.out, non_blocking=True)
+        self.torch.cuda.synchronize()
+
+    def verify(self):
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import dali_oracle as oracle
+        self.launch_step(0, self.stream)
+        self.torch.cuda.synchronize()
+        rows = [0, 4097, self.N - 1]
+        x = self.x[0][rows].cpu().numpy()
+        want = self.np.cumsum(x.astype(self.np.float64), axis=1)
+        bound = 1e-5 * self.np.cumsum(self.np.abs(x).astype(self.np.float64), axis=1)
+        got = self.out[rows].cpu().numpy()
+        assert self.np.all(self.np.abs(got - want) <= bound)
+        assert self.np.all(self.np.abs(oracle.scan("sum", x, True) - want) <= bound)
+
+    def cpu_baseline(self, tmpdir, reps):
+        # the reference's CPU scan takes time quadratic in the row length (18 s for [2048,2048]): a few full-length rows
+        m = 4
+        self.np.save(os.path.join(tmpdir, "x.npy"), self.x[0][:m].contiguous().cpu().numpy())
+        times = run_ref_driver("scan", ["sum", "1", "x.npy", "out.npy"], min(reps, 3), tmpdir)
+        if not times:
+            return None
+        return {"ms": times, "bytes": 2 * m * self.N * 4, "cores": 1, "kind": "reference", "sample": "4 of the 8192 rows (full length 8192)"}
+
+
+WORKLOADS = {"lstm": Lstm, "softmax": Softmax, "reduce": ReduceAxis0, "gemm": Gemm, "chain": Chain, "scan": Cumsum}
 
 
 # ----------------------------------------------------------------------------- main
@@ -728,6 +802,13 @@ def reference_arm(args):
             case, cargs, nbytes, flops = "gemm_tanh", ["A.npy", "B.npy", "bias.npy", "out.npy"], 3 * m * m * 2, 2.0 * m ** 3
             wl = "C4 tanh(dot(A,B)+bias), bf16 A,B [8192,8192] ~ N(0,0.02), bias ~ N(0,0.1), fp32 accumulate, bf16 out"
             sample, ncores, scaling, dtype = "2048^3 in fp32 per step (the reference has no bf16; 1/64 of the flops)", cores, "weak", "f32"
+        elif w == "scan":
+            rng = np.random.default_rng(1240)
+            m = 4
+            save("x.npy", (rng.random((m, 8192)) * 2 - 1).astype(np.float32))
+            case, cargs, nbytes, flops = "scan", ["sum", "1", "x.npy", "out.npy"], 2 * m * 8192 * 4, 0
+            wl = "op::cumsum over the last axis of fp32 [8192,8192] ~ U(-1,1) per GPU (inclusive)"
+            sample, ncores, scaling, dtype = "4 of the 8192 rows per step (the reference's CPU scan is quadratic in the row length)", 1, "weak", "f32"
         else:
             rng = np.random.default_rng(1234 + 4)
             m = 1 << 24
@@ -850,7 +931,7 @@ def roofline_of(wl, m, lib):
     return {"bound": "hbm", "achieved": achieved, "peak": peak_hbm, "unit": "GB/s", "frac": achieved / peak_hbm,
             "traffic": ratio * work if ratio else None,
             "peak_source": (kind + " (MEASURED_PEAKS.json hbm_gbs)") if kind == "measured" else "fallback 6.65 TB/s",
-            "kernel": lib.last_variant(), "kernel_ms": ms}
+            "kernel": getattr(wl, "kernel_name", None) or lib.last_variant(), "kernel_ms": ms}
 
 
 def main():
@@ -925,9 +1006,8 @@ def main():
             torch.distributed.all_reduce(te, op=torch.distributed.ReduceOp.MAX)
         e2e = {"value": job_bytes / float(te.item()) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": wl.h2d,
                "d2h_bytes_per_step": wl.d2h, "steps": n_e2e, "ms_per_step": float(te.item()) * 1e3,
-               "api": "host arrays -> lazy Array/op:: expression -> eval -> host arrays (C++ front end through its C binding)"
-                      if args.workload == "lstm" else
-                      "dalib200_launch_host / C ABI with pinned host buffers (alloc from pool + H2D + kernel + D2H + sync per step)"}
+               "api": getattr(wl, "e2e_api", "dalib200_launch_host / C ABI with pinned host buffers (alloc from pool + H2D + "
+                                              "kernel + D2H + sync per step)")}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -944,7 +1024,7 @@ def main():
     others = None
     if args.workload == "lstm" and not args.no_others and world == 1:
         others = {}
-        for name in ("softmax", "reduce", "gemm", "chain"):
+        for name in ("softmax", "reduce", "gemm", "chain", "scan"):
             del wl
             torch.cuda.empty_cache()
             wl = build(name)

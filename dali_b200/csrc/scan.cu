@@ -5,10 +5,11 @@
 // its CPU body walks a row left to right, its GPU body gives one block per row
 // and a Hillis-Steele pass over shared memory.  Here a row is owned by a group of
 // G threads (a warp for short rows, a 256-thread CTA for long ones) that walks
-// it in tiles of 4 G elements: every thread scans its 4 consecutive elements in
-// registers, thread totals are scanned with warp shuffles (and across the warps
-// of a CTA through 8 words of shared memory), and the running total of the tiles
-// before is carried in a register.  One read and one write of the matrix, both
+// it in tiles of 8 G elements: every thread scans its 8 consecutive elements
+// (128-bit loads and stores when rows are 16-byte aligned) in registers, thread
+// totals are scanned with warp shuffles (and across the warps of a CTA through 8
+// words of shared memory), and the running total of the tiles before is carried
+// in a register.  One read and one write of the matrix, both
 // coalesced; HBM bound: 2 * sizeof(T) bytes per element.
 //
 // inclusive: out[r][i] = x[r][0] (+) ... (+) x[r][i], out is [rows, cols]
@@ -51,13 +52,16 @@ template <> __device__ double shfl_idx<double>(double v, int l) {
     return __longlong_as_double(((long long)hi << 32) | (unsigned int)lo);
 }
 
-constexpr int kItems = 4;       // consecutive elements per thread and tile
+constexpr int kItems = 8;       // consecutive elements per thread and tile
 constexpr int kThreads = 256;   // threads per CTA
 
 // G threads per row (32 or kThreads); a CTA holds kThreads / G rows
-template <typename T, typename Op, int G>
+// VEC: rows start 16-byte aligned and row pitches keep that alignment (inclusive scans only: the
+// exclusive output is shifted by one element)
+template <typename T, typename Op, int G, bool VEC>
 __global__ void __launch_bounds__(kThreads) scan_rows_kernel(const T* __restrict__ in, long long in_ld, T* __restrict__ out,
                                                              long long out_ld, long long rows, long long cols, int exclusive) {
+    constexpr int kChunks = kItems * (int)sizeof(T) / 16;     // 128-bit pieces of a thread's elements
     __shared__ T warp_total[kThreads / 32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = threadIdx.x % G;                       // position in the row's group
@@ -71,9 +75,15 @@ __global__ void __launch_bounds__(kThreads) scan_rows_kernel(const T* __restrict
         if (live && exclusive && g == 0) y[-1] = carry;
         for (long long base = 0; base < cols; base += (long long)G * kItems) {
             const long long i0 = base + (long long)g * kItems;
-            T v[kItems];
+            alignas(16) T v[kItems];
+            const bool whole = live && i0 + kItems <= cols;
+            if (VEC && whole) {
 #pragma unroll
-            for (int k = 0; k < kItems; ++k) v[k] = (live && i0 + k < cols) ? x[i0 + k] : Op::template init<T>();
+                for (int q = 0; q < kChunks; ++q) reinterpret_cast<uint4*>(v)[q] = reinterpret_cast<const uint4*>(x + i0)[q];
+            } else {
+#pragma unroll
+                for (int k = 0; k < kItems; ++k) v[k] = (live && i0 + k < cols) ? x[i0 + k] : Op::template init<T>();
+            }
 #pragma unroll
             for (int k = 1; k < kItems; ++k) v[k] = Op::apply(v[k - 1], v[k]);
             // inclusive scan of the thread totals inside the warp
@@ -103,8 +113,15 @@ __global__ void __launch_bounds__(kThreads) scan_rows_kernel(const T* __restrict
             }
             const T offset = Op::apply(carry, before);
 #pragma unroll
-            for (int k = 0; k < kItems; ++k)
-                if (live && i0 + k < cols) y[i0 + k] = Op::apply(offset, v[k]);
+            for (int k = 0; k < kItems; ++k) v[k] = Op::apply(offset, v[k]);
+            if (VEC && whole) {
+#pragma unroll
+                for (int q = 0; q < kChunks; ++q) reinterpret_cast<uint4*>(y + i0)[q] = reinterpret_cast<const uint4*>(v)[q];
+            } else {
+#pragma unroll
+                for (int k = 0; k < kItems; ++k)
+                    if (live && i0 + k < cols) y[i0 + k] = v[k];
+            }
             carry = Op::apply(carry, tile_total);
         }
     }
@@ -114,14 +131,19 @@ template <typename T, typename Op>
 cudaError_t launch_scan(cudaStream_t stream, const T* in, long long in_ld, T* out, long long out_ld, long long rows, long long cols,
                         bool exclusive) {
     if (rows <= 0) return cudaSuccess;
-    if (cols <= 32 * kItems * 8) {
+    const long long per16 = 16 / (long long)sizeof(T);
+    const bool vec = !exclusive && ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0) && in_ld % per16 == 0 && out_ld % per16 == 0;
+    const int ex = exclusive ? 1 : 0;
+    if (cols <= 32 * kItems * 4) {
         const long long per = kThreads / 32;
         long long ctas = (rows + per - 1) / per;
         if (ctas > 148 * 16) ctas = 148 * 16;
-        scan_rows_kernel<T, Op, 32><<<(unsigned)ctas, kThreads, 0, stream>>>(in, in_ld, out, out_ld, rows, cols, exclusive ? 1 : 0);
+        if (vec) scan_rows_kernel<T, Op, 32, true><<<(unsigned)ctas, kThreads, 0, stream>>>(in, in_ld, out, out_ld, rows, cols, ex);
+        else scan_rows_kernel<T, Op, 32, false><<<(unsigned)ctas, kThreads, 0, stream>>>(in, in_ld, out, out_ld, rows, cols, ex);
     } else {
         long long ctas = rows > 148 * 16 ? 148 * 16 : rows;
-        scan_rows_kernel<T, Op, kThreads><<<(unsigned)ctas, kThreads, 0, stream>>>(in, in_ld, out, out_ld, rows, cols, exclusive ? 1 : 0);
+        if (vec) scan_rows_kernel<T, Op, kThreads, true><<<(unsigned)ctas, kThreads, 0, stream>>>(in, in_ld, out, out_ld, rows, cols, ex);
+        else scan_rows_kernel<T, Op, kThreads, false><<<(unsigned)ctas, kThreads, 0, stream>>>(in, in_ld, out, out_ld, rows, cols, ex);
     }
     return cudaGetLastError();
 }

@@ -22,7 +22,7 @@
 //   arange  <i32|f32|f64> start stop step out     (numbers on the command line)
 //   diag_scalar <i32|f32|f64> value rows cols out  diag_vec d rows cols out
 //   one_hot idx depth on off out     (on / off: doubles on the command line, as the reference's test passes them)
-//   outer   a b out                  scan <sum|prod> <0|1 inclusive> in out
+//   outer   a b out                  scan <sum|prod> <0|1 inclusive> in out [reps]
 // Every timed case prints "TIME_MS first=<ms> best=<ms> reps=<n>".
 #include "dali/array/array.h"
 #include "dali/array/op.h"
@@ -260,8 +260,13 @@ int main(int argc, char** argv) {
         save(a[2], r);
     } else if (c == "scan" && n >= 4) {
         Array x = load(a[2]);
-        Array r = std::string(a[0]) == "sum" ? op::cumsum(x, std::atoi(a[1]) != 0) : op::cumprod(x, std::atoi(a[1]) != 0);
-        r.eval();
+        const bool inclusive = std::atoi(a[1]) != 0, sum = std::string(a[0]) == "sum";
+        Array r;
+        timed(reps_at(4), [&]() {
+            Array s = sum ? op::cumsum(x, inclusive) : op::cumprod(x, inclusive);
+            s.eval();
+            r = s;
+        });
         save(a[3], r);
     } else {
         return usage();
