@@ -338,6 +338,22 @@ class _Op:
     def outer(self, a, b):
         return Array._new(_c().c.dali_op_outer, a._h, b._h)
 
+    def _random(self, kind, a, b, shape):
+        a, b = _wrap(a), _wrap(b)
+        return Array._new(_c().c.dali_op_random, kind.encode(), a._h, b._h, _shape_arg(shape), len(shape))
+
+    def uniform(self, low, high, shape):
+        return self._random("uniform", low, high, shape)
+
+    def normal(self, loc, scale, shape):
+        return self._random("normal", loc, scale, shape)
+
+    def bernoulli(self, prob, shape):
+        return self._random("bernoulli", prob, prob, shape)
+
+    def bernoulli_normalized(self, prob, shape):
+        return self._random("bernoulli_normalized", prob, prob, shape)
+
     def axis_scan(self, a, reducer, inclusive=True):
         return Array._new(_c().c.dali_op_scan, a._h, reducer.encode(), int(bool(inclusive)))
 
@@ -378,6 +394,11 @@ def lazy_stats():
 def set_dry_run(on):
     """Lower and compile only (no device work, results undefined): inspect fusion without a GPU."""
     _c().c.dali_lazy_set_dry_run(int(bool(on)))
+
+
+def set_seed(seed):
+    """utils::random::set_seed: the seeds of the random operators built from now on."""
+    _check(_c().c.dali_random_set_seed(int(seed)))
 
 
 def set_default_device(gpu):

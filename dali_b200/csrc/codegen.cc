@@ -102,6 +102,8 @@ struct Gen {
             case S_OP: {
                 if (s.name == "round" || s.name == "ceiling")
                     return "f_" + s.name + "<" + ct(s.dtype) + ">(" + vn(s.in[0]) + ")";
+                if (s.name == "rng_uniform" || s.name == "rng_normal")
+                    return "f_" + s.name + "<" + ct(s.dtype) + ">(" + vn(s.in[0]) + ", " + vn(s.in[1]) + ")";
                 if (s.name == "eltdiv" && s.in.size() == 2 && need_inv.count(s.in[1]) && s.elem && s.dtype == F32)
                     return vn(s.in[0]) + " * rinv" + std::to_string(s.in[1]);
                 std::string e = "f_" + s.name + "(" + vn(s.in[0]);

@@ -104,6 +104,8 @@ bool epilogue_macro(const Program& p, std::string* out, std::string* err) {
             case S_OP: {
                 o << "    const " << T << " v" << s.id << " = ";
                 if (s.name == "round" || s.name == "ceiling") o << "f_" << s.name << "<" << T << ">(v" << s.in[0] << ")";
+                else if (s.name == "rng_uniform" || s.name == "rng_normal")
+                    o << "f_" << s.name << "<" << T << ">(v" << s.in[0] << ", v" << s.in[1] << ")";
                 else {
                     o << "f_" << s.name << "(v" << s.in[0];
                     if (s.in.size() > 1) o << ", v" << s.in[1];

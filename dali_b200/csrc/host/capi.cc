@@ -9,6 +9,7 @@
 #include "../runtime.h"
 #include "dali/array/op.h"
 #include "expression.h"
+#include "dali/utils/random.h"
 
 struct dali_array_s { Array a; };
 
@@ -271,6 +272,20 @@ int dali_op_scan(dali_array_t a, const char* reducer, int inclusive, dali_array_
 }
 int dali_op_arange(dali_array_t start, dali_array_t stop, dali_array_t step, dali_array_t* out) {
     return guard([&]() { *out = wrap(op::arange(start->a, stop->a, step->a)); });
+}
+int dali_op_random(const char* kind, dali_array_t a, dali_array_t b, const int64_t* shape, int ndim, dali_array_t* out) {
+    return guard([&]() {
+        const std::string k(kind);
+        std::vector<int> s = to_shape(shape, ndim);
+        if (k == "uniform") *out = wrap(op::uniform(a->a, b->a, s));
+        else if (k == "normal") *out = wrap(op::normal(a->a, b->a, s));
+        else if (k == "bernoulli") *out = wrap(op::bernoulli(a->a, s));
+        else if (k == "bernoulli_normalized") *out = wrap(op::bernoulli_normalized(a->a, s));
+        else throw std::runtime_error("dali_op_random: unknown kind " + k);
+    });
+}
+int dali_random_set_seed(int seed) {
+    return guard([&]() { utils::random::set_seed(seed); });
 }
 int dali_op_softmax(dali_array_t logits, int axis, dali_array_t* out) {
     return guard([&]() { *out = wrap(op::softmax(logits->a, axis)); });

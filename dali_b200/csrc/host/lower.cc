@@ -232,7 +232,8 @@ struct Lowerer {
                     id = new_value(w->dtype_, is_elem, "cast v" + std::to_string(in[0]));
                 } else {
                     // operands are promoted to the node's type, except for the converting functors
-                    bool converts = w->functor_ == "round" || w->functor_ == "ceiling";
+                    bool converts = w->functor_ == "round" || w->functor_ == "ceiling" || w->functor_ == "rng_uniform" ||
+                                    w->functor_ == "rng_normal";
                     std::string text = "op " + w->functor_;
                     for (int v : in) {
                         if (!converts && types[v] != w->dtype_) v = new_value(w->dtype_, elem[v], "cast v" + std::to_string(v));

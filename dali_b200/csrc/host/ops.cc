@@ -7,6 +7,7 @@
 #include <sstream>
 
 #include "dali/array/op.h"
+#include "dali/utils/random.h"
 #include "expression.h"
 
 static std::string shape_str(const std::vector<int>& s) {
@@ -16,6 +17,19 @@ static std::string shape_str(const std::vector<int>& s) {
     o << "]";
     return o.str();
 }
+
+namespace utils {
+namespace random {
+std::mt19937& generator() {
+    static std::mt19937 gen(std::random_device{}());
+    return gen;
+}
+void reseed() { generator().seed(std::random_device{}()); }
+void set_seed(int new_seed) { generator().seed((unsigned)new_seed); }
+}  // namespace random
+int randint(int lower, int upper) { return std::uniform_int_distribution<int>(lower, upper)(random::generator()); }
+double randdouble(double lower, double upper) { return std::uniform_real_distribution<double>(lower, upper)(random::generator()); }
+}  // namespace utils
 
 namespace op {
 
@@ -433,6 +447,54 @@ Array axis_scan(const Array& a, const std::string& reducer_name, bool inclusive)
 }
 Array cumsum(const Array& a, bool inclusive) { return axis_scan(a, "reducers::sum", inclusive); }
 Array cumprod(const Array& a, bool inclusive) { return axis_scan(a, "reducers::product", inclusive); }
+
+// ---------------------------------------------------------------- random numbers
+namespace {
+// value of element i = functor(i, seed): an Elementwise over (row-major index, seed drawn now)
+Array random_field(const char* functor, const std::vector<int>& shape, DType dtype) {
+    for (int d : shape) DALI_ASSERT(d >= 0, "random: negative dimension");
+    std::vector<int64_t> st(shape.size(), 0);
+    int64_t acc = 1;
+    for (int d = (int)shape.size() - 1; d >= 0; --d) { st[d] = acc; acc *= shape[d]; }
+    DALI_ASSERT(acc <= 2147483647LL, "random: more than 2^31 - 1 elements in one array");
+    Array index(std::make_shared<Iota>(shape, 0, st));
+    Array seed(std::make_shared<ScalarValue>((double)utils::randint(0, 2147483646), DTYPE_INT32));
+    return Array(std::make_shared<Elementwise>(functor, std::vector<Array>({index, seed}), shape, dtype));
+}
+#define DALI_ASSERT_SCALAR(NAME, ARG, ARRAY) \
+    DALI_ASSERT(ARRAY.ndim() == 0, std::string(NAME) + "'s " + ARG + " argument must be a scalar but got " + ARG + ".shape = " + shape_str(ARRAY.shape()) + ".")
+}  // namespace
+
+Array uniform(Array low, Array high, const std::vector<int>& shape) {
+    DALI_ASSERT_SCALAR("uniform", "low", low);
+    DALI_ASSERT_SCALAR("uniform", "high", high);
+    std::tie(low, high) = ensure_arguments_compatible(low, high, "uniform", false);
+    const DType t = low.dtype();
+    if (t == DTYPE_INT32) {
+        // inclusive range, as std::uniform_int_distribution (random.cu.cpp:67-74): low + floor(u * (high - low + 1))
+        Array u = random_field("rng_uniform", shape, DTYPE_DOUBLE);
+        Array span = unsafe_cast(high - low, DTYPE_DOUBLE) + Array(1.0);
+        return low + unsafe_cast(u * span, DTYPE_INT32);
+    }
+    return low + (high - low) * random_field("rng_uniform", shape, t);
+}
+Array normal(Array loc, Array scale, const std::vector<int>& shape) {
+    DALI_ASSERT_SCALAR("normal", "loc", loc);
+    DALI_ASSERT_SCALAR("normal", "scale", scale);
+    if (loc.dtype() == DTYPE_INT32) loc = unsafe_cast(loc, DTYPE_DOUBLE);
+    if (scale.dtype() == DTYPE_INT32) scale = unsafe_cast(scale, DTYPE_DOUBLE);
+    std::tie(loc, scale) = ensure_arguments_compatible(loc, scale, "normal", false);
+    return loc + scale * random_field("rng_normal", shape, loc.dtype());
+}
+Array bernoulli(Array prob, const std::vector<int>& shape) {
+    DALI_ASSERT_SCALAR("bernoulli", "prob", prob);
+    if (prob.dtype() == DTYPE_INT32) prob = unsafe_cast(prob, DTYPE_DOUBLE);
+    // uniform(0, 1) <= prob (random.cu.cpp:316-320)
+    return lessthanequal(random_field("rng_uniform", shape, prob.dtype()), prob);
+}
+Array bernoulli_normalized(Array prob, const std::vector<int>& shape) {
+    return bernoulli(prob, shape) * eltinv(prob.dtype() == DTYPE_INT32 ? unsafe_cast(prob, DTYPE_DOUBLE) : prob);
+}
 
 // ---------------------------------------------------------------- assignment
 Array assign(const Array& left, OPERATOR_T op, const Array& right) {

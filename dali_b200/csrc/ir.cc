@@ -92,6 +92,7 @@ int functor_arity(const std::string& n) {
         "clipped_relu_backward", "clip", "lessthanequal", "greaterthanequal",
         "binary_cross_entropy", "binary_cross_entropy_grad", "prelu", "prelu_backward_weights",
         "prelu_backward_inputs",
+        "rng_uniform", "rng_normal",   // (element index i32, seed i32) -> f32 / f64: Philox4x32-10, see the device prelude
         "where_nonzero",   // not a reference functor: a != 0 ? b : 0, the select of its Diag kernel (op/eye.cpp:37)
         nullptr};
     for (int i = 0; unary[i]; ++i) if (n == unary[i]) return 1;
@@ -253,9 +254,12 @@ bool parse_program(const std::string& text, Program* out, std::string* err) {
             for (int i = 0; i < ar; ++i) {
                 int v;
                 if (!parse_value_ref(t[4 + i], &v) || !value_ok(v)) return fail("bad operand");
-                bool converts = s.name == "round" || s.name == "ceiling";
+                const bool rng = s.name == "rng_uniform" || s.name == "rng_normal";
+                bool converts = s.name == "round" || s.name == "ceiling" || rng;
                 if (!converts && p.stmts[p.value_stmt[v]].dtype != s.dtype)
                     return fail("operand type differs from result type (insert a cast)");
+                if (rng && (p.stmts[p.value_stmt[v]].dtype != I32 || s.dtype == I32))
+                    return fail("rng functors take (i32 index, i32 seed) and yield f32 or f64");
                 s.in.push_back(v);
             }
             s.kind = S_OP;

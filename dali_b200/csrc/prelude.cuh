@@ -272,6 +272,52 @@ template <typename T, int N> struct alignas(sizeof(T) * N) Vec { T x[N]; };
 template <typename T, int N> DEV Vec<T, N> vload(const T* p) { return *reinterpret_cast<const Vec<T, N>*>(p); }
 template <typename T, int N> DEV void vstore(T* p, const Vec<T, N>& v) { *reinterpret_cast<Vec<T, N>*>(p) = v; }
 
+// Counter-based random numbers: Philox4x32-10 (Salmon et al., SC'11) with counter = (element
+// index, 0, 0, 0) and key = (seed, 0).  Replaces the thrust generators the reference seeds per
+// call on the GPU (dali/array/op/random.cu.cpp:153-232): being a pure function of (index,
+// seed) it fuses into whatever consumes the numbers (a dropout mask never touches memory) and
+// gives the same stream whatever the launch geometry.
+DEV void philox4x32_10(unsigned c0, unsigned k0, unsigned out[4]) {
+    unsigned c1 = 0, c2 = 0, c3 = 0, k1 = 0;
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const unsigned hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+        const unsigned hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+        const unsigned n0 = hi1 ^ c1 ^ k0, n2 = hi0 ^ c3 ^ k1;
+        c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+        k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+    }
+    out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+// u in [0, 1): 24 bits for float, 53 for double
+template <typename T> DEV T f_rng_uniform(int index, int seed);
+template <> DEV float f_rng_uniform<float>(int index, int seed) {
+    unsigned x[4];
+    philox4x32_10((unsigned)index, (unsigned)seed, x);
+    return (float)(x[0] >> 8) * (1.0f / 16777216.0f);
+}
+template <> DEV double f_rng_uniform<double>(int index, int seed) {
+    unsigned x[4];
+    philox4x32_10((unsigned)index, (unsigned)seed, x);
+    return ((double)(x[0] >> 5) * 67108864.0 + (double)(x[1] >> 6)) * (1.0 / 9007199254740992.0);
+}
+// standard normal by Box-Muller on two uniforms of one Philox block: sqrt(-2 ln u1) cos(2 pi u2), u1 in (0, 1]
+template <typename T> DEV T f_rng_normal(int index, int seed);
+template <> DEV float f_rng_normal<float>(int index, int seed) {
+    unsigned x[4];
+    philox4x32_10((unsigned)index, (unsigned)seed, x);
+    const float u1 = ((float)(x[0] >> 8) + 1.0f) * (1.0f / 16777216.0f);
+    const float u2 = (float)(x[1] >> 8) * (1.0f / 16777216.0f);
+    return sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
+}
+template <> DEV double f_rng_normal<double>(int index, int seed) {
+    unsigned x[4];
+    philox4x32_10((unsigned)index, (unsigned)seed, x);
+    const double u1 = ((double)(x[0] >> 5) * 67108864.0 + (double)(x[1] >> 6) + 1.0) * (1.0 / 9007199254740992.0);
+    const double u2 = ((double)(x[2] >> 5) * 67108864.0 + (double)(x[3] >> 6)) * (1.0 / 9007199254740992.0);
+    return sqrt(-2.0 * log(u1)) * cospi(2.0 * u2);
+}
+
 // An argument with no memory behind it whose "element" at offset i is base + i: with the
 // per-dim strides every argument has, base + sum(index_d * stride_d) is any affine function
 // of the iteration index (what the reference's arange / one_hot / diag kernels read from

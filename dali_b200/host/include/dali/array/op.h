@@ -133,6 +133,14 @@ Array cumsum(const Array& a, bool inclusive = true);
 Array cumprod(const Array& a, bool inclusive = true);
 Array fill(const Array& x, double value);      // same-shaped array holding `value`
 
+// ---- random numbers (op/random.h:7-10).  low / high / loc / scale / prob are scalars.  Lazy: the value of
+// element i is a pure function of (i, the seed drawn when the node was built), generated inside the
+// kernel that consumes it.  uniform: [low, high) for float / double, [low, high] for int32.
+Array uniform(Array low, Array high, const std::vector<int>& shape);
+Array normal(Array loc, Array scale, const std::vector<int>& shape);
+Array bernoulli(Array prob, const std::vector<int>& shape);
+Array bernoulli_normalized(Array prob, const std::vector<int>& shape);
+
 // ---- assignment
 Array assign(const Array& left, OPERATOR_T operator_t, const Array& right);
 Array autoreduce_assign(const Array& left, const Array& right);

@@ -11,8 +11,9 @@ class IRBuilder:
         self.args, self.scalars, self.body = [], [], []
         self.types = []
 
-    def arg(self, dtype="f32", level="E"):
-        self.args.append((dtype, level))
+    def arg(self, dtype="f32", level="E", iota=False):
+        """iota=True: no memory behind the arg; its element at offset i IS the int32 value (launch offset + i)."""
+        self.args.append((dtype, level + (" iota" if iota else "")))
         return len(self.args) - 1
 
     def scalar(self, dtype="f32"):

@@ -82,6 +82,10 @@ int dali_op_one_hot(dali_array_t indices, int depth, dali_array_t on_value, dali
 int dali_op_outer(dali_array_t a, dali_array_t b, dali_array_t* out);
 int dali_op_scan(dali_array_t a, const char* reducer, int inclusive, dali_array_t* out);
 int dali_op_arange(dali_array_t start, dali_array_t stop, dali_array_t step, dali_array_t* out);
+/* op/random.h: kind = uniform (a = low, b = high) | normal (a = loc, b = scale) | bernoulli | bernoulli_normalized
+ * (a = prob, b ignored); utils::random::set_seed (dali/utils/random.h:39) */
+int dali_op_random(const char* kind, dali_array_t a, dali_array_t b, const int64_t* shape, int ndim, dali_array_t* out);
+int dali_random_set_seed(int seed);
 int dali_op_softmax(dali_array_t logits, int axis, dali_array_t* out);
 int dali_op_dot(dali_array_t a, dali_array_t b, dali_array_t* out);
 

@@ -252,3 +252,50 @@ def outer(a, b):
     a, b = np.ravel(a), np.ravel(b)
     t = np.result_type(a.dtype, b.dtype)
     return a.astype(t)[:, None] * b.astype(t)[None, :]
+
+
+# ---- counter-based random numbers ------------------------------------------------------
+# The reference draws from std::mt19937 on the CPU and from thrust's generators on the GPU
+# (dali/array/op/random.cu.cpp:59-88, 153-232): its two streams differ from each other, so no
+# stream of its own can be pinned.  The B200 back end uses Philox4x32-10 (Salmon, Moraes, Dror,
+# Shaw: "Parallel random numbers: as easy as 1, 2, 3", SC'11) with counter = (element index, 0,
+# 0, 0) and key = (seed, 0); this is its plain restatement.
+_PHILOX_M0, _PHILOX_M1 = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57)
+_PHILOX_W0, _PHILOX_W1 = 0x9E3779B9, 0xBB67AE85
+
+
+def philox4x32_10(counter, key):
+    """counter: 4 arrays (or ints) of uint32 words, key: 2 words -> 4 uint32 arrays."""
+    c = [np.asarray(w, dtype=np.uint64) & np.uint64(0xFFFFFFFF) for w in counter]
+    k0, k1 = int(key[0]) & 0xFFFFFFFF, int(key[1]) & 0xFFFFFFFF
+    mask = np.uint64(0xFFFFFFFF)
+    for _ in range(10):
+        p0 = _PHILOX_M0 * c[0]
+        p1 = _PHILOX_M1 * c[2]
+        hi0, lo0 = p0 >> np.uint64(32), p0 & mask
+        hi1, lo1 = p1 >> np.uint64(32), p1 & mask
+        c = [hi1 ^ c[1] ^ np.uint64(k0), lo1, hi0 ^ c[3] ^ np.uint64(k1), lo0]
+        k0 = (k0 + _PHILOX_W0) & 0xFFFFFFFF
+        k1 = (k1 + _PHILOX_W1) & 0xFFFFFFFF
+    return [w.astype(np.uint32) for w in c]
+
+
+def rng_uniform(n, seed, dtype=np.float32):
+    """u[i] in [0, 1) for element index i < n."""
+    x = philox4x32_10((np.arange(n, dtype=np.uint64), 0, 0, 0), (seed, 0))
+    if np.dtype(dtype) == np.float32:
+        return ((x[0] >> np.uint32(8)).astype(np.float32) * np.float32(1.0 / 16777216.0)).astype(np.float32)
+    hi, lo = (x[0] >> np.uint32(5)).astype(np.float64), (x[1] >> np.uint32(6)).astype(np.float64)
+    return (hi * 67108864.0 + lo) * (1.0 / 9007199254740992.0)
+
+
+def rng_normal(n, seed, dtype=np.float32):
+    """Box-Muller on two uniforms of the same Philox block: sqrt(-2 ln u1) cos(2 pi u2), u1 in (0, 1]."""
+    x = philox4x32_10((np.arange(n, dtype=np.uint64), 0, 0, 0), (seed, 0))
+    if np.dtype(dtype) == np.float32:
+        u1 = ((x[0] >> np.uint32(8)).astype(np.float64) + 1.0) / 16777216.0
+        u2 = (x[1] >> np.uint32(8)).astype(np.float64) / 16777216.0
+    else:
+        u1 = ((x[0] >> np.uint32(5)).astype(np.float64) * 67108864.0 + (x[1] >> np.uint32(6)).astype(np.float64) + 1.0) / 9007199254740992.0
+        u2 = ((x[2] >> np.uint32(5)).astype(np.float64) * 67108864.0 + (x[3] >> np.uint32(6)).astype(np.float64)) / 9007199254740992.0
+    return (np.sqrt(-2.0 * np.log(u1)) * np.cos(2.0 * np.pi * u2)).astype(dtype)

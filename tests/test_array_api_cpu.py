@@ -220,3 +220,22 @@ def test_running_reduction_lowering():
     assert op.cumprod(x, inclusive=False).shape == (4, 11)
     y = op.cumsum(x) * 2.0                                                   # never fused with its consumer (scan.cpp:37-39)
     assert launched(y) == {"kernels": 2, "gemms": 0, "temporaries": 1}
+
+
+def test_random_operators_fuse_into_their_consumer():
+    """op::uniform / normal / bernoulli are functions of (element index, seed): a dropout mask is generated
+    inside the kernel that applies it."""
+    from dali_b200.array import set_seed
+    set_seed(5)
+    x = Array(np.zeros((64, 32), np.float32))
+    y = x * op.bernoulli_normalized(Array(0.5, DTYPE_FLOAT), (64, 32))
+    assert launched(y) == {"kernels": 1, "gemms": 0, "temporaries": 0}
+    ir = last_ir()
+    assert "rng_uniform" in ir and " iota" in ir and ir.count("arg ") == 3      # out, x, the index
+    n = op.normal(0.0, 2.0, (5, 7))
+    assert n.shape == (5, 7) and n.dtype == DTYPE_DOUBLE
+    assert launched(n) == {"kernels": 1, "gemms": 0, "temporaries": 0} and "rng_normal" in last_ir()
+    u = op.uniform(Array(0, DTYPE_INT32), Array(6, DTYPE_INT32), (2, 3))         # tests.cpp:1001: uniform(0, 6, {2, 3})
+    assert u.dtype == DTYPE_INT32 and launched(u)["kernels"] == 1
+    with pytest.raises(RuntimeError):
+        op.uniform(Array(np.zeros(2, np.float32)), 1.0, (3,))

@@ -198,3 +198,15 @@ def test_running_reductions_pinned_by_the_reference(golden):
     f = np.array([[3.0, -1.0, 7.0, 2.0]], np.float32)
     np.testing.assert_array_equal(oracle.scan("max", f), [[3, 3, 7, 7]])
     np.testing.assert_array_equal(oracle.scan("min", f, False), [[np.finfo(np.float32).max, 3, -1, -1, -1]])
+
+
+def test_known_answer_vectors_of_the_random_generator():
+    """Philox4x32-10 (Salmon et al., SC'11): the known-answer vectors published with the algorithm pin the
+    restatement that the GPU stream is compared with."""
+    h = lambda v: [int(w) for w in v]
+    assert h(oracle.philox4x32_10((0, 0, 0, 0), (0, 0))) == [0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8]
+    assert h(oracle.philox4x32_10((0xffffffff,) * 4, (0xffffffff,) * 2)) == [0x408f276d, 0x41c83b0e, 0xa20bc7c6, 0x6d5451fd]
+    pi_digits = oracle.philox4x32_10((0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344), (0xa4093822, 0x299f31d0))
+    assert h(pi_digits) == [0xd16cfe09, 0x94fdcceb, 0x5001e420, 0x24126ea1]
+    u = oracle.rng_uniform(1 << 16, 99)
+    assert u.dtype == np.float32 and u.min() >= 0.0 and u.max() < 1.0 and abs(u.mean() - 0.5) < 0.01
