@@ -111,6 +111,15 @@ class Array:
         return out
 
     @staticmethod
+    def load(path):
+        """Array::load: a .npy file (float32 / float64 / int32, C or Fortran order)."""
+        return Array._new(_c().c.dali_array_load, str(path).encode())
+
+    def save(self, path):
+        """Array::save: evaluates and writes a C-ordered .npy file."""
+        _check(_c().c.dali_array_save(str(path).encode(), self._h))
+
+    @staticmethod
     def from_device(ptr, shape, dtype=DTYPE_FLOAT, gpu=0):
         """Wraps device memory owned by the caller (e.g. a torch CUDA tensor's data_ptr())."""
         return Array._new(_c().c.dali_array_from_device, ctypes.c_void_p(int(ptr)), _shape_arg(shape), len(shape),

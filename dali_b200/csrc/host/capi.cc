@@ -81,6 +81,13 @@ int dali_array_borrow_host(void* data, const int64_t* shape, int ndim, int dtype
     });
 }
 
+int dali_array_load(const char* path, dali_array_t* out) {
+    return guard([&]() { *out = wrap(Array::load(std::string(path))); });
+}
+int dali_array_save(const char* path, dali_array_t a) {
+    return guard([&]() { Array::save(std::string(path), a->a); });
+}
+
 int dali_array_from_device(void* device_ptr, const int64_t* shape, int ndim, int dtype, int gpu, dali_array_t* out) {
     return guard([&]() {
         DType dt = to_dtype(dtype);

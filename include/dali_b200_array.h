@@ -33,6 +33,11 @@ int dali_array_from_host(const void* data, const int64_t* shape, int ndim, int d
  * The memory must stay alive and unchanged until every expression that reads it has been
  * evaluated; page-locked memory reaches the GPU by DMA without a staging copy. */
 int dali_array_borrow_host(void* data, const int64_t* shape, int ndim, int dtype, dali_array_t* out);
+/* NumPy .npy files, the reference's on-disk format (Array::load / Array::save, array.cpp:253-359): float32,
+ * float64 and int32, C or Fortran order on load (a Fortran-ordered file comes back as a transposed view),
+ * C order on save. */
+int dali_array_load(const char* path, dali_array_t* out);
+int dali_array_save(const char* path, dali_array_t a);
 /* wraps DEVICE memory the caller keeps owning (no copy, never freed here) */
 int dali_array_from_device(void* device_ptr, const int64_t* shape, int ndim, int dtype, int gpu, dali_array_t* out);
 int dali_array_empty(const int64_t* shape, int ndim, int dtype, dali_array_t* out);

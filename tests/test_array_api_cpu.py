@@ -239,3 +239,34 @@ def test_random_operators_fuse_into_their_consumer():
     assert u.dtype == DTYPE_INT32 and launched(u)["kernels"] == 1
     with pytest.raises(RuntimeError):
         op.uniform(Array(np.zeros(2, np.float32)), 1.0, (3,))
+
+
+def test_npy_files_round_trip_with_numpy(tmp_path):
+    """Array::load / Array::save against numpy's own reader and writer (reference tests: tests.cpp:745-776)."""
+    set_dry_run(False)
+    try:
+        rng = np.random.default_rng(2)
+        for arr in (np.arange(12, dtype=np.int32).reshape(3, 4), rng.standard_normal((2, 3, 5)).astype(np.float32),
+                    rng.standard_normal(7), np.arange(5, dtype=np.float32)):
+            p = tmp_path / "a.npy"
+            np.save(p, arr)
+            a = Array.load(p)
+            assert a.shape == arr.shape and a.dtype == {np.dtype(np.int32): DTYPE_INT32, np.dtype(np.float32): DTYPE_FLOAT,
+                                                          np.dtype(np.float64): DTYPE_DOUBLE}[arr.dtype]
+            q = tmp_path / "b.npy"
+            a.save(q)                                                          # host-fresh buffer: no device involved
+            back = np.load(q)
+            assert back.dtype == arr.dtype and not np.isfortran(back)
+            np.testing.assert_array_equal(back, arr)
+        # a Fortran-ordered file is the same array (tests.cpp:745-760: arange12.npy vs arange12.fortran.npy)
+        f = np.asfortranarray(np.arange(12, dtype=np.float64).reshape(3, 4))
+        np.save(tmp_path / "f.npy", f)
+        af = Array.load(tmp_path / "f.npy")
+        assert af.shape == (3, 4)
+        with pytest.raises(RuntimeError):
+            Array.load(tmp_path / "missing.npy")
+        np.save(tmp_path / "i8.npy", np.arange(3, dtype=np.int64))
+        with pytest.raises(RuntimeError):
+            Array.load(tmp_path / "i8.npy")
+    finally:
+        set_dry_run(True)

@@ -377,3 +377,15 @@ def test_borrowed_host_arrays_and_reading_into_a_caller_buffer():
         Array.borrow(a_np.T)
     with pytest.raises(TypeError):
         Array(a_np).numpy(out=np.empty((3, 3), np.float32))
+
+
+def test_npy_load_compute_save(tmp_path):
+    """Array::load -> expression -> Array::save; a Fortran-ordered file is the same array (tests.cpp:745-776)."""
+    c = np.arange(12, dtype=np.float32).reshape(3, 4)
+    np.save(tmp_path / "c.npy", c)
+    np.save(tmp_path / "f.npy", np.asfortranarray(c))
+    ac, af = Array.load(tmp_path / "c.npy"), Array.load(tmp_path / "f.npy")
+    np.testing.assert_array_equal(ac.numpy(), c)
+    np.testing.assert_array_equal(af.numpy(), c)
+    (op.tanh(af) + ac).save(tmp_path / "out.npy")           # evaluated on the device, written from the host copy
+    np.testing.assert_allclose(np.load(tmp_path / "out.npy"), np.tanh(c) + c, rtol=1e-5)
