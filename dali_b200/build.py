@@ -97,5 +97,16 @@ def build(force=False, verbose=False):
     return LIB
 
 
+def build_program(source, output):
+    """Compiles a C++ program written against the front end's headers (dali/array/array.h, op.h) and links it
+    with the library; the library is found next to the program at run time."""
+    lib = build()
+    inc = os.path.join(HERE, "host", "include")
+    if _newer(output, [source, lib]):
+        _run(["g++", "-std=c++14", "-O1", "-I" + inc, source, "-o", output, "-L" + LIBDIR, "-ldali_b200",
+              "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + LIBDIR])
+    return output
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

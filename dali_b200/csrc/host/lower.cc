@@ -102,7 +102,10 @@ struct Lowerer {
     std::vector<bool> elem;              // per value: varies over the reduced dims?
     std::vector<Leaf> leaves;
     std::vector<std::pair<DType, double>> scalars;
+    // keyed by node address: every node that has an entry is kept alive in `memo_nodes`, or a node created
+    // later (a temporary's buffer) could reuse the address of one that died during lowering and hit its entry
     std::map<std::pair<const Expression*, std::string>, int> memo;
+    std::vector<expression_ptr> memo_nodes;
     std::map<const Expression*, int> scalar_slot;
     std::vector<Array> keep_alive;
     // the node whose value is the GEMM accumulator (epilogue programs): a MatMul, or the sum of two of them
@@ -212,6 +215,7 @@ struct Lowerer {
                     slot = (int)scalars.size();
                     scalars.push_back(std::make_pair(s->dtype_, s->value_));
                     scalar_slot[s] = slot;
+                    keep_alive.push_back(a);      // the slot map is keyed by the node's address too
                 } else {
                     slot = sit->second;
                 }
@@ -332,6 +336,7 @@ struct Lowerer {
                 throw std::runtime_error("cannot lower expression node " + e->name());
         }
         memo[key] = id;
+        memo_nodes.push_back(e);
         return id;
     }
 

@@ -270,3 +270,19 @@ def test_npy_files_round_trip_with_numpy(tmp_path):
             Array.load(tmp_path / "i8.npy")
     finally:
         set_dry_run(True)
+
+
+def test_two_equal_subtrees_keep_their_own_temporaries():
+    """all_close(softmax(a), softmax(a)): four temporaries (two row maxima, two row sums) feed one all-axis kernel.
+    Nodes replaced by their evaluated buffers during lowering must not lend their addresses to later ones."""
+    a = Array(np.zeros((5, 10), np.float32))
+
+    def softmax():
+        e = op.exp(a - op.max(a, [-1], True))
+        return e / op.sum(e, [-1], True)
+
+    close = op.lessthanequal(op.abs(op.subtract(softmax(), softmax())), Array(1e-6, DTYPE_DOUBLE))
+    p = op.prod(close)
+    assert launched(p) == {"kernels": 5, "gemms": 0, "temporaries": 4}
+    ir = last_ir()
+    assert ir.count("arg ") == 6 and ir.count(" ld ") == 5          # a, 2 maxima, 2 sums read; one result written
