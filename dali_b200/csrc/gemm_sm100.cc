@@ -32,7 +32,9 @@ struct GemmVariant {
     int bm, bn, bk, stages;
     int pair = 0;   // two CTAs (cta_group::2) share a 2*bm x bn tile, each staging half of the B tile
     bool b_kmajor() const { return split != 0; }   // the fp32 path transposes B while splitting it
-    unsigned idesc() const {
+    bool ncat() const { return split != 0 && bn <= 64; }   // b_hi | b_lo read as one operand of 2 * bn columns
+    unsigned idesc(int n_cols = 0) const {
+        if (!n_cols) n_cols = bn;
         unsigned fmt = esize == 2 ? 1u : 2u;       // kind::f16: 1 = bf16; kind::tf32: 2 = tf32
         unsigned d = 0;
         d |= 1u << 4;                              // accumulate in fp32
@@ -40,7 +42,7 @@ struct GemmVariant {
         d |= fmt << 10;                            // B format
         d |= 0u << 15;                             // A is K-major
         d |= (b_kmajor() ? 0u : 1u) << 16;         // B: K-major ([N,K]) or MN-major ([K,N])
-        d |= (unsigned)(bn >> 3) << 17;
+        d |= (unsigned)(n_cols >> 3) << 17;
         d |= (unsigned)(((pair ? 2 : 1) * bm) >> 4) << 24;
         return d;
     }
@@ -52,6 +54,7 @@ struct GemmVariant {
         std::ostringstream o;
         o << "gemm.e" << esize << ".s" << split << ".m" << bm << ".n" << bn << ".k" << bk << ".st" << stages;
         if (pair) o << ".pair";
+        if (ncat()) o << ".ncat";
         return o.str();
     }
 };
@@ -218,6 +221,7 @@ bool gemm_source(void* ctx, std::string* src, std::string* err) {
     o << "#define GEMM_BM " << c->v.bm << "\n#define GEMM_BN " << c->v.bn << "\n#define GEMM_BK " << c->v.bk << "\n";
     o << "#define GEMM_STAGES " << c->v.stages << "\n#define GEMM_ESIZE " << c->v.esize << "\n#define GEMM_SPLIT " << c->v.split << "\n";
     o << "#define GEMM_IDESC " << c->v.idesc() << "u\n";
+    o << "#define GEMM_NCAT " << (c->v.ncat() ? 1 : 0) << "\n#define GEMM_IDESC_WIDE " << c->v.idesc(2 * c->v.bn) << "u\n";
     o << "#define GEMM_B_KMAJOR " << (c->v.b_kmajor() ? 1 : 0) << "\n#define GEMM_PAIR " << c->v.pair << "\n";
     int words = 3 * (int)c->p->args.size() + (int)c->p->scalars.size();
     o << "#define GEMM_EPI_WORDS " << (words < 1 ? 1 : words) << "\n";
@@ -311,7 +315,7 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
     GemmSourceCtx ctx{&prog, choose_variant(bf16, m, n)};
     const GemmVariant& v = ctx.v;
     std::ostringstream key;
-    key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + "|sm_100a|gemm-7|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" +
+    key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + "|sm_100a|gemm-8|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" +
                                                      std::to_string(fnv1a(device_prelude())));
     tl_gemm_variant = std::string(bf16 ? "tcgen05.bf16 " : "tcgen05.tf32x3 ") + v.key() + (n_pairs > 1 ? " x2" : "");
     note_gemm_kernel(tl_gemm_variant);

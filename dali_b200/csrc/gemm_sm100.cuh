@@ -14,6 +14,11 @@
 //                     halves of B, each CTA ends up with its 128 rows of the accumulator in its own
 //                     tensor memory.  Halves the shared-memory traffic per flop, which is what
 //                     bounds the single-CTA 128 x 256 bf16 tile
+//   GEMM_NCAT         1 (with GEMM_SPLIT, GEMM_B_KMAJOR, GEMM_BN <= 128): the B hi and lo tiles lie one after
+//                     the other in a stage and are read as ONE operand of 2*GEMM_BN columns, so a K step
+//                     issues a_hi.[b_hi | b_lo] (GEMM_IDESC_WIDE) and a_lo.b_hi: two instructions and one
+//                     read of a_hi instead of three and two.  Each round-robin accumulator then has its own
+//                     correction accumulator in the columns next to it.
 //   GEMM_IDESC        tcgen05 instruction descriptor
 // and a macro EPILOGUE_CHUNK(row, col0, acc, nvalid) generated from the
 // expression that consumes the product.
@@ -75,7 +80,13 @@ struct GemmP {
 // For fp32 parity the split path therefore keeps the small correction products
 // (a_lo.b_hi, a_hi.b_lo) in an accumulator of their own and deals the main products round
 // robin over GEMM_NACC accumulators, which the epilogue adds up in fp32 on the CUDA cores.
-#if GEMM_SPLIT
+#ifndef GEMM_NCAT
+#define GEMM_NCAT 0
+#endif
+#if GEMM_SPLIT && GEMM_NCAT
+#define GEMM_NACC 3
+#define GEMM_ACC_SETS (2 * GEMM_NACC)        /* (main, correction) pairs side by side */
+#elif GEMM_SPLIT
 #define GEMM_NACC 3
 #define GEMM_ACC_SETS (GEMM_NACC + 1)
 #else
@@ -330,9 +341,14 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
 #if GEMM_SPLIT
                 const TensorMap* mAlo = second ? &tmA2lo : &tmAlo;
                 const TensorMap* mBlo = second ? &tmB2lo : &tmBlo;
-                unsigned char* alo = bt + GEMM_B_TILE_BYTES;
-                tma_load_2d(alo, mAlo, &full_bar[s], kx, (int)m0);
+#if GEMM_NCAT
+                unsigned char* blo = bt + GEMM_B_TILE_BYTES;            // stage = a_hi, b_hi, b_lo, a_lo
+                unsigned char* alo = blo + GEMM_B_TILE_BYTES;
+#else
+                unsigned char* alo = bt + GEMM_B_TILE_BYTES;            // stage = a_hi, b_hi, a_lo, b_lo
                 unsigned char* blo = alo + GEMM_A_TILE_BYTES;
+#endif
+                tma_load_2d(alo, mAlo, &full_bar[s], kx, (int)m0);
 #if GEMM_B_KMAJOR
                 tma_load_2d(blo, mBlo, &full_bar[s], kx, (int)n0);
 #else
@@ -370,7 +386,15 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
 #else
                     const unsigned long long bd = smem_desc(b_addr + k * GEMM_UMMA_K * 128, GEMM_B_ATOM_BYTES, 1024);
 #endif
-#if GEMM_SPLIT
+#if GEMM_SPLIT && GEMM_NCAT
+                    // [main | correction] pair kb % GEMM_NACC: a_hi.[b_hi | b_lo] writes both halves (the first
+                    // use overwrites), a_lo.b_hi adds into the correction half
+                    const unsigned pair0 = acc0 + (unsigned)((kb % GEMM_NACC) * 2 * GEMM_BN);
+                    umma(pair0, ad, bd, GEMM_IDESC_WIDE, (kb >= GEMM_NACC || k > 0) ? 1u : 0u);
+                    const unsigned alo_addr = b_addr + 2 * GEMM_B_TILE_BYTES;
+                    const unsigned long long ald = smem_desc(alo_addr + k * 32, 0, 1024);
+                    umma(pair0 + GEMM_BN, ald, bd, GEMM_IDESC, 1u);
+#elif GEMM_SPLIT
                     // main products: accumulator kb % GEMM_NACC (its first use overwrites)
                     umma(acc0 + (unsigned)((kb % GEMM_NACC) * GEMM_BN), ad, bd, GEMM_IDESC, (kb >= GEMM_NACC || k > 0) ? 1u : 0u);
                     const unsigned alo_addr = b_addr + GEMM_B_TILE_BYTES;
@@ -414,7 +438,15 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
                 if (num_kb > 0) {
                     const unsigned lane_base = tmem_base + as * GEMM_ACC_COLS + ((unsigned)(warp * 32) << 16) + (unsigned)c;
                     tmem_ld32(lane_base, acc);
-#if GEMM_SPLIT
+#if GEMM_SPLIT && GEMM_NCAT
+                    const int used = num_kb < GEMM_NACC ? num_kb : GEMM_NACC;
+                    float part[32];
+                    for (int a = 1; a < 2 * used; ++a) {          // main_0 (+) corr_0 (+) main_1 (+) corr_1 ...
+                        tmem_ld32(lane_base + (unsigned)(a * GEMM_BN), part);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) acc[i] += part[i];
+                    }
+#elif GEMM_SPLIT
                     const int used = num_kb < GEMM_NACC ? num_kb : GEMM_NACC;
                     float part[32];
                     for (int a = 1; a < used; ++a) {
