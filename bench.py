@@ -393,31 +393,28 @@ class Lstm(Workload):
         o, bias = e.arg("f32"), e.arg("f32")
         e.st(o, e.op("add", e.acc(), e.ld(bias)))      # acc = x.Wx + h.Wh (one accumulator), + b
         self.h_epi = L.compile(e.text())
-        g = IRBuilder(2, 0)                                                         # the gating kernel the front end emits
+        # the two gating kernels the front end emits when c' is evaluated before h' (h' then reads the stored c')
+        g = IRBuilder(2, 0)
         out = g.arg("f32")
-        gi, gf, go, gg, c = (g.arg("f32") for _ in range(5))
-        i, f, o_ = (g.op("sigmoid", g.ld(a_)) for a_ in (gi, gf, go))
-        cn = g.op("add", g.op("eltmul", f, g.ld(c)), g.op("eltmul", i, g.op("tanh", g.ld(gg))))
-        gh = IRBuilder(2, 0)
-        self.ir_c = None
-        # h_new = o * tanh(c_new) recomputes c_new inside its own kernel, exactly as Array::eval lowers it
-        outh = gh.arg("f32")
-        hi_, hf, ho, hg, hc = (gh.arg("f32") for _ in range(5))
-        i2, f2, o2 = (gh.op("sigmoid", gh.ld(a_)) for a_ in (hi_, hf, ho))
-        cn2 = gh.op("add", gh.op("eltmul", f2, gh.ld(hc)), gh.op("eltmul", i2, gh.op("tanh", gh.ld(hg))))
-        gh.st(outh, gh.op("eltmul", o2, gh.op("tanh", cn2)))
+        gi, gf, gg, c = (g.arg("f32") for _ in range(4))
+        cn = g.op("add", g.op("eltmul", g.op("sigmoid", g.ld(gf)), g.ld(c)),
+                  g.op("eltmul", g.op("sigmoid", g.ld(gi)), g.op("tanh", g.ld(gg))))
         g.st(out, cn)
+        gh = IRBuilder(2, 0)
+        outh = gh.arg("f32")
+        ho, hc = gh.arg("f32"), gh.arg("f32")
+        gh.st(outh, gh.op("eltmul", gh.op("sigmoid", gh.ld(ho)), gh.op("tanh", gh.ld(hc))))
         self.h_gate_c = L.compile(g.text())
         self.h_gate_h = L.compile(gh.text())
         self.scaling = "weak"
-        self.launches_per_step = 5
+        self.launches_per_step = 4
 
     def describe(self):
         return {"workload": "C2 LSTM cell step: gates = dot(x,Wx)+dot(h,Wh)+b, c' = sig(f)*c + sig(i)*tanh(g), "
                             "h' = sig(o)*tanh(c'); fp32, B=256 H=1024 per GPU, x,h,c ~ N(0,1), W ~ N(0,0.02), b = 0",
                 "l2": "activations rotate over %d sets; the two weight matrices are reused every step (as in an RNN) "
                       "and stay in L2" % self.nset,
-                "kernels_per_step": "2 TF32 splits (x, h), 1 tcgen05 3xTF32 GEMM accumulating x.Wx + h.Wh with '+ b' as epilogue, 2 fused gating kernels",
+                "kernels_per_step": "1 TF32 split of x and h, 1 tcgen05 3xTF32 GEMM accumulating x.Wx + h.Wh with '+ b' as epilogue, 2 fused gating kernels (c', then h' from the stored c')",
                 "parallelism": "batch sharded: each of %d GPU(s) runs its own B=256 shard, weights replicated, no collective" % self.world}
 
     def bytes_per_step(self):
@@ -430,14 +427,14 @@ class Lstm(Workload):
     def launch_step(self, i, stream):
         L, B, H, k = self.lib, self.B, self.H, i % self.nset
         d = self.device
-        L.gemm_split_tf32(self.x[k], B, H, H, self.parts[0], self.parts[1], device=d, stream=stream)
-        L.gemm_split_tf32(self.h[k], B, H, H, self.parts[2], self.parts[3], device=d, stream=stream)
+        L.gemm_split_tf32_pair(self.x[k], self.h[k], B, H, H, H, *self.parts, device=d, stream=stream)
         self.launch_gemm(stream)
         gs = [4 * H, 1]
         G = self.gates
-        for hsh, out in ((self.h_gate_h, self.h_new[k]), (self.h_gate_c, self.c_new[k])):
-            L.launch(hsh, (B, H), [out, G, G, G, G, self.c[k]], strides=[None, gs, gs, gs, gs, None],
-                     offsets=[0, 0, H, 2 * H, 3 * H, 0], device=d, stream=stream)
+        L.launch(self.h_gate_c, (B, H), [self.c_new[k], G, G, G, self.c[k]], strides=[None, gs, gs, gs, None],
+                 offsets=[0, 0, H, 3 * H, 0], device=d, stream=stream)                      # i, f, g slices
+        L.launch(self.h_gate_h, (B, H), [self.h_new[k], G, self.c_new[k]], strides=[None, gs, None],
+                 offsets=[0, 2 * H, 0], device=d, stream=stream)                             # o slice
 
     def launch_gemm(self, stream):
         B, H, P, W = self.B, self.H, self.parts, self.W
@@ -482,7 +479,8 @@ class Lstm(Workload):
         g = op.tanh(gates[:, 3 * H:4 * H])
         c_new = f * c + i_ * g
         h_new = o * op.tanh(c_new)
-        self.last = (h_new.numpy(out=self.host["h_out"]), c_new.numpy(out=self.host["c_out"]))
+        c_out = c_new.numpy(out=self.host["c_out"])          # c' first: h' then reads it instead of recomputing it
+        self.last = (h_new.numpy(out=self.host["h_out"]), c_out)
 
     def verify(self):
         sys.path.insert(0, os.path.join(ROOT, "oracle"))

@@ -76,6 +76,8 @@ class Library:
                                                ctypes.c_void_p]
         c.dalib200_scan.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int64,
                                     ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64]
+        c.dalib200_gemm_split_tf32_pair.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p] + \
+            [ctypes.c_int64] * 4 + [ctypes.c_void_p] * 4
         c.dalib200_gemm_error_flag.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
         c.dalib200_last_gemm_kernel.restype = ctypes.c_size_t
         c.dalib200_last_gemm_kernel.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
@@ -244,6 +246,11 @@ class Library:
         self.check(self.c.dalib200_scan(device, ctypes.c_void_p(stream or 0), dtype, op, int(bool(inclusive)), rows, cols,
                                         self._ptr(x), cols if in_row_stride is None else in_row_stride, self._ptr(out),
                                         (cols + (0 if inclusive else 1)) if out_row_stride is None else out_row_stride))
+
+    def gemm_split_tf32_pair(self, x0, x1, rows, cols, ld0, ld1, hi0, lo0, hi1, lo1, device=0, stream=None):
+        self.check(self.c.dalib200_gemm_split_tf32_pair(device, ctypes.c_void_p(stream or 0), self._ptr(x0), self._ptr(x1), rows,
+                                                        cols, ld0, ld1, self._ptr(hi0), self._ptr(lo0), self._ptr(hi1),
+                                                        self._ptr(lo1)))
 
     def gemm_error_flag(self, device=0):
         f = ctypes.c_int(0)

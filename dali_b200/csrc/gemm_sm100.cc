@@ -23,6 +23,8 @@ static const char* kGemmSkeleton =
 
 cudaError_t split_tf32(cudaStream_t stream, const float* x, long long rows, long long cols, long long ld, bool transpose,
                        float* hi, float* lo);
+cudaError_t split_tf32_pair(cudaStream_t stream, const float* x0, const float* x1, long long rows, long long cols, long long ld0,
+                            long long ld1, float* hi0, float* lo0, float* hi1, float* lo1);
 
 namespace {
 
@@ -471,6 +473,23 @@ int dalib200_gemm_split_tf32(int device, void* stream, const float* x, int64_t r
     if (transpose && rows % 4) { set_error("dalib200_gemm_split_tf32: transposed output needs rows % 4 == 0"); return DALIB200_ERR_INVALID; }
     if (split_tf32((cudaStream_t)stream, x, rows, cols, ld, transpose != 0, hi, lo) != cudaSuccess) {
         set_error("split_tf32 launch failed");
+        return DALIB200_ERR_CUDA;
+    }
+    return DALIB200_OK;
+}
+
+int dalib200_gemm_split_tf32_pair(int device, void* stream, const float* x0, const float* x1, int64_t rows, int64_t cols,
+                                  int64_t ld0, int64_t ld1, float* hi0, float* lo0, float* hi1, float* lo1) {
+    DeviceRestore restore_device;
+    int ord = device_ordinal(device);
+    if (ord < 0) { set_error("device index out of range"); return dalib200_device_count() ? DALIB200_ERR_INVALID : DALIB200_ERR_NO_DEVICE; }
+    const void* ptrs[6] = {x0, x1, hi0, lo0, hi1, lo1};
+    bool ok = cols % 4 == 0 && ld0 % 4 == 0 && ld1 % 4 == 0 && rows >= 0 && cols >= 0;
+    for (const void* q : ptrs) ok = ok && q && ((uintptr_t)q & 15) == 0;
+    if (!ok) { set_error("dalib200_gemm_split_tf32_pair: needs 16-byte aligned pointers and cols, ld multiples of 4"); return DALIB200_ERR_INVALID; }
+    cudaSetDevice(ord);
+    if (split_tf32_pair((cudaStream_t)stream, x0, x1, rows, cols, ld0, ld1, hi0, lo0, hi1, lo1) != cudaSuccess) {
+        set_error("split_tf32_pair launch failed");
         return DALIB200_ERR_CUDA;
     }
     return DALIB200_OK;

@@ -27,6 +27,30 @@ split_tf32_kernel(const float* __restrict__ x, long long rows, long long cols4, 
     }
 }
 
+// two operands of the same shape in one launch (blockIdx.y picks the operand): the x and h of a
+// recurrent cell, which are split anew every step
+struct SplitPair {
+    const float* x[2];
+    long long ld4[2];
+    float4* hi[2];
+    float4* lo[2];
+};
+__global__ void __launch_bounds__(256) split_tf32_pair_kernel(const SplitPair p, long long rows, long long cols4) {
+    const int w = blockIdx.y;
+    const long long total = rows * cols4;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / cols4, c = i - r * cols4;
+        const float4 v = reinterpret_cast<const float4*>(p.x[w])[r * p.ld4[w] + c];
+        float4 h, l;
+        h.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u); l.x = v.x - h.x;
+        h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u); l.y = v.y - h.y;
+        h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u); l.z = v.z - h.z;
+        h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u); l.w = v.w - h.w;
+        p.hi[w][i] = h;
+        p.lo[w][i] = l;
+    }
+}
+
 // same, writing the parts TRANSPOSED ([cols, rows], tight): 32 x 32 tiles through shared memory
 __global__ void __launch_bounds__(256)
 split_tf32_transpose_kernel(const float* __restrict__ x, long long rows, long long cols, long long ld, float* __restrict__ hi,
@@ -73,6 +97,21 @@ cudaError_t split_tf32(cudaStream_t stream, const float* x, long long rows, long
     if (blocks > 148 * 16) blocks = 148 * 16;
     split_tf32_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, rows, cols / 4, ld / 4, reinterpret_cast<float4*>(hi),
                                                             reinterpret_cast<float4*>(lo));
+    return cudaGetLastError();
+}
+
+cudaError_t split_tf32_pair(cudaStream_t stream, const float* x0, const float* x1, long long rows, long long cols, long long ld0,
+                            long long ld1, float* hi0, float* lo0, float* hi1, float* lo1) {
+    const long long total = rows * (cols / 4);
+    if (total == 0) return cudaSuccess;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    SplitPair p;
+    p.x[0] = x0; p.x[1] = x1;
+    p.ld4[0] = ld0 / 4; p.ld4[1] = ld1 / 4;
+    p.hi[0] = reinterpret_cast<float4*>(hi0); p.hi[1] = reinterpret_cast<float4*>(hi1);
+    p.lo[0] = reinterpret_cast<float4*>(lo0); p.lo[1] = reinterpret_cast<float4*>(lo1);
+    split_tf32_pair_kernel<<<dim3((unsigned)blocks, 2), 256, 0, stream>>>(p, rows, cols / 4);
     return cudaGetLastError();
 }
 

@@ -450,8 +450,13 @@ struct SplitParts {
     }
 };
 
-// returns the (hi, lo) parts of a contiguous-row fp32 view; nullptr if the layout cannot be split in place
-std::shared_ptr<SplitParts> split_operand(BufferView* b, bool transpose, memory::Device device, int dev) {
+// A split that has its (hi, lo) buffers but has not been launched yet: two of one shape go out as one launch.
+struct PendingSplit { std::shared_ptr<SplitParts> parts; const float* x = nullptr; };
+
+// returns the (hi, lo) parts of a contiguous-row fp32 view; nullptr if the layout cannot be split in place.
+// With `pending` the split kernel of an operand that was not cached is left to the caller (launch_pending).
+std::shared_ptr<SplitParts> split_operand(BufferView* b, bool transpose, memory::Device device, int dev,
+                                          std::vector<PendingSplit>* pending = nullptr) {
     std::vector<int> st = b->normalized_strides();
     const int64_t rows = b->shape_[0], cols = b->shape_[1], ld = st[0];
     if (st[1] != 1 && cols != 1) return nullptr;
@@ -471,11 +476,34 @@ std::shared_ptr<SplitParts> split_operand(BufferView* b, bool transpose, memory:
     parts->offset = b->offset_; parts->rows = rows; parts->cols = cols; parts->ld = ld; parts->transposed = transpose;
     check(dalib200_alloc(dev, parts->bytes, &parts->hi), "dalib200_alloc");
     check(dalib200_alloc(dev, parts->bytes, &parts->lo), "dalib200_alloc");
-    check(dalib200_gemm_split_tf32(dev, nullptr, x, rows, cols, ld, transpose ? 1 : 0, (float*)parts->hi, (float*)parts->lo),
-          "dalib200_gemm_split_tf32");
+    if (pending && !transpose) {
+        PendingSplit ps;
+        ps.parts = parts;
+        ps.x = x;
+        pending->push_back(ps);
+    } else {
+        check(dalib200_gemm_split_tf32(dev, nullptr, x, rows, cols, ld, transpose ? 1 : 0, (float*)parts->hi, (float*)parts->lo),
+              "dalib200_gemm_split_tf32");
+    }
     slot = parts;
     b->memory_->derived_version() = b->memory_->version();
     return parts;
+}
+
+void launch_pending(const std::vector<PendingSplit>& pending, int dev) {
+    size_t i = 0;
+    if (pending.size() == 2 && pending[0].parts->rows == pending[1].parts->rows && pending[0].parts->cols == pending[1].parts->cols) {
+        const SplitParts &a = *pending[0].parts, &b = *pending[1].parts;
+        check(dalib200_gemm_split_tf32_pair(dev, nullptr, pending[0].x, pending[1].x, a.rows, a.cols, a.ld, b.ld, (float*)a.hi,
+                                            (float*)a.lo, (float*)b.hi, (float*)b.lo),
+              "dalib200_gemm_split_tf32_pair");
+        i = 2;
+    }
+    for (; i < pending.size(); ++i) {
+        const SplitParts& a = *pending[i].parts;
+        check(dalib200_gemm_split_tf32(dev, nullptr, pending[i].x, a.rows, a.cols, a.ld, 0, (float*)a.hi, (float*)a.lo),
+              "dalib200_gemm_split_tf32");
+    }
 }
 
 // first reduction reachable from `a` through elementwise nodes and views
@@ -628,10 +656,16 @@ bool try_fused_gemm(const Array& dest, OPERATOR_T op, const Array& value, const 
     }
     const int dev = device_index(device);
     std::shared_ptr<SplitParts> parts[4];
-    for (int p = 0; p < np; ++p) {
-        parts[2 * p] = split_operand(a[p], false, device, dev);
+    std::vector<PendingSplit> pending;       // left operands not split yet: x and h of a cell go out as one launch
+    bool splittable = true;
+    for (int p = 0; p < np && splittable; ++p) {
+        parts[2 * p] = split_operand(a[p], false, device, dev, &pending);
         parts[2 * p + 1] = split_operand(b[p], true, device, dev);
-        if (!parts[2 * p] || !parts[2 * p + 1]) return false;
+        splittable = parts[2 * p] && parts[2 * p + 1];
+    }
+    launch_pending(pending, dev);             // also when giving up: the cached parts must hold what they promise
+    if (!splittable) return false;
+    for (int p = 0; p < np; ++p) {
         pa_hi[p] = parts[2 * p]->hi; pa_lo[p] = parts[2 * p]->lo;
         pb_hi[p] = parts[2 * p + 1]->hi; pb_lo[p] = parts[2 * p + 1]->lo;
         ld[p] = k[p];

@@ -218,6 +218,11 @@ int dalib200_gemm_fused_sum(int device, void* stream, int ab_dtype, int n_pairs,
  * when transposing). */
 int dalib200_gemm_split_tf32(int device, void* stream, const float* x,
                              int64_t rows, int64_t cols, int64_t ld, int transpose, float* hi, float* lo);
+/* The same for TWO operands of one shape in a single launch, without transposition
+ * (the x and h of a recurrent cell, split anew every step). */
+int dalib200_gemm_split_tf32_pair(int device, void* stream, const float* x0, const float* x1,
+                                  int64_t rows, int64_t cols, int64_t ld0, int64_t ld1,
+                                  float* hi0, float* lo0, float* hi1, float* lo1);
 
 /* Synchronises `device` and reads the word tensor-core kernels raise when one of
  * their bounded waits expires (0 = none; 1 producer, 2 MMA issuer, 3 epilogue);
