@@ -4,11 +4,12 @@
  *
  * Plain-C restatement of the reference's CPU algorithm for the hot path
  * (lazy expression -> JIT -> run on memory::Device::cpu()).  Parity is PINNED:
- * oracle/check_oracle_vs_ref.py compares every function here with the
- * reference's own CPU path (oracle/_ref, built from the reference sources by
- * oracle/build_ref.sh) and tests/test_oracle.py re-checks it against the
- * fixtures that script committed under tests/golden/ and against the
- * known-answer cases of the reference's own suite
+ * tests/golden/make_golden.py ran the reference's own CPU path (oracle/_ref,
+ * built from the reference sources by oracle/build_ref.sh) on seeded inputs and
+ * committed the outputs as tests/golden/reference_cpu.npz; tests/test_oracle.py
+ * checks every function here against those fixtures (bit for bit where the
+ * arithmetic is the reference's own) and against the known-answer cases of the
+ * reference's own suite
  * (dali/array/tests/tests.cpp:1120-1361, dali/array/tests/dot_tests.cpp:10-118).
  *
  * What each function follows:
@@ -23,6 +24,8 @@
  *   softmax       dali/array/op/softmax.cpp:5-8 evaluated as the reference
  *                 does: temporaries for the row max, exp(a - max) and its row sum
  *   gather        dali/array/op/gather.cpp:45-65, gather_from_rows.cpp:53-78
+ *   scan          dali/array/op/scan.cpp:47-77 (left-to-right running reduction)
+ *   one_hot, diag dali/array/op/one_hot.cpp:41-46, eye.cpp:33-38
  *   gemm          row-major C = A.B as dali/array/gemm/cpu_gemm.cpp:22-84 asks
  *                 of CBLAS; here with a double accumulator (CBLAS itself is a
  *                 third-party dependency with no pinned version, so only the
