@@ -405,6 +405,12 @@ def set_dry_run(on):
     _c().c.dali_lazy_set_dry_run(int(bool(on)))
 
 
+def eval_together(*arrays, wait=True):
+    """Evaluates several lazy arrays of one shape in one kernel where their trees allow it (not in the reference)."""
+    hs = (_H * len(arrays))(*[a._h.value for a in arrays])
+    _check(_c().c.dali_array_eval_together(hs, len(arrays), int(wait)))
+
+
 def set_seed(seed):
     """utils::random::set_seed: the seeds of the random operators built from now on."""
     _check(_c().c.dali_random_set_seed(int(seed)))

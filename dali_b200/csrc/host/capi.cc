@@ -81,6 +81,18 @@ int dali_array_borrow_host(void* data, const int64_t* shape, int ndim, int dtype
     });
 }
 
+int dali_array_eval_together(const dali_array_t* arrays, int n, int wait) {
+    return guard([&]() {
+        std::vector<Array> v;
+        for (int i = 0; i < n; ++i) v.push_back(arrays[i]->a);
+        lazy::eval_together(v);
+        if (wait && n > 0 && !lazy::dry_run()) {
+            memory::Device d = v[0].preferred_device();
+            if (d.is_gpu()) lazy::check(dalib200_sync(lazy::device_index(d), nullptr), "dalib200_sync");
+        }
+    });
+}
+
 int dali_array_load(const char* path, dali_array_t* out) {
     return guard([&]() { *out = wrap(Array::load(std::string(path))); });
 }

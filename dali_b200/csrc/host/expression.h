@@ -146,6 +146,9 @@ namespace lazy {
 // Runs dest <op>= value as one or more fused kernels (temporaries only where a
 // subtree cannot share the root's iteration space) on dest's device.
 void run_assignment(const Array& dest, OPERATOR_T op, const Array& value);
+// Evaluates several lazy arrays of one shape in one kernel where their trees allow it (an extension: the
+// reference evaluates one Array per kernel); otherwise one after the other.  Does not synchronise.
+void eval_together(const std::vector<Array>& arrays);
 // Number of kernels / GEMMs launched by this thread's evaluations so far, and the
 // description of the last fused kernel (for tests, in the spirit of the scope
 // counting in dali/array/tests/dot_tests.cpp:17-35).

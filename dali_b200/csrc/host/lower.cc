@@ -860,4 +860,46 @@ void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) 
     L.launch();
 }
 
+// Several lazy arrays of one shape in ONE kernel: what their trees share (the c' that h' = o * tanh(c')
+// is built from) is computed once and every root is stored.  The reference has no such call -- there each
+// eval() is a kernel of its own; anything this cannot fuse (reductions, products or scans at a root, differing
+// shapes) is evaluated one by one exactly as Array::eval would.
+void eval_together(const std::vector<Array>& arrays) {
+    std::vector<const Array*> roots;
+    for (const Array& a : arrays) {
+        DALI_ASSERT(!a.is_stateless(), "eval_together on a stateless Array");
+        if (a.is_buffer()) continue;
+        roots.push_back(&a);
+    }
+    bool fusable = roots.size() > 1;
+    for (const Array* a : roots) {
+        const Expression* e = a->expression().get();
+        FoundReduce fr;
+        find_reduce(*a, false, &fr);
+        fusable = fusable && e->kind_ == N_ELEMENTWISE && !fr.node && e->ndim() > 0 && e->shape_ == roots[0]->expression()->shape_ &&
+                  e->numel() > 0;
+    }
+    if (!fusable) {
+        for (const Array* a : roots) a->eval(false);
+        return;
+    }
+    const memory::Device device = roots[0]->preferred_device();
+    std::vector<int64_t> space;
+    for (int d : roots[0]->shape()) space.push_back(d);
+    const int rank = (int)space.size();
+    Lowerer L(space, 0, device);
+    std::vector<Array> dests;
+    for (const Array* a : roots) {
+        Array value(a->expression());
+        int v = L.visit(value, identity_map(rank));
+        Array dest(value.shape(), value.dtype(), device);
+        int leaf = L.leaf_for(as<BufferView>(dest), identity_map(rank), true, false, 0, 0, 0);
+        L.keep_alive.push_back(dest);
+        L.body.push_back("st " + std::to_string(leaf) + " assign v" + std::to_string(v));
+        dests.push_back(dest);
+    }
+    L.launch();
+    for (size_t i = 0; i < roots.size(); ++i) roots[i]->set_expression(dests[i].expression());
+}
+
 }  // namespace lazy

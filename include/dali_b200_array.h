@@ -33,6 +33,9 @@ int dali_array_from_host(const void* data, const int64_t* shape, int ndim, int d
  * The memory must stay alive and unchanged until every expression that reads it has been
  * evaluated; page-locked memory reaches the GPU by DMA without a staging copy. */
 int dali_array_borrow_host(void* data, const int64_t* shape, int ndim, int dtype, dali_array_t* out);
+/* Not in the reference: evaluates several lazy arrays of one shape in ONE kernel when their trees are elementwise
+ * (shared sub-expressions are computed once, every array is stored), one after the other otherwise. */
+int dali_array_eval_together(const dali_array_t* arrays, int n, int wait);
 /* NumPy .npy files, the reference's on-disk format (Array::load / Array::save, array.cpp:253-359): float32,
  * float64 and int32, C or Fortran order on load (a Fortran-ordered file comes back as a transposed view),
  * C order on save. */

@@ -156,6 +156,31 @@ def test_lstm_cell_lowering():
     assert launched(c_new) == {"kernels": 1, "gemms": 0, "temporaries": 0}
 
 
+def test_lstm_cell_outputs_together_are_one_gemm_and_one_kernel():
+    from dali_b200.array import eval_together
+    B, H = 32, 64
+    x, h, c = (Array(np.zeros((B, H), np.float32)) for _ in range(3))
+    Wx, Wh = (Array(np.zeros((H, 4 * H), np.float32)) for _ in range(2))
+    b = Array(np.zeros((4 * H,), np.float32))
+    gates = op.dot(x, Wx) + op.dot(h, Wh) + b[None, :]
+    i, f, o = (op.sigmoid(gates[:, k * H:(k + 1) * H]) for k in range(3))
+    g = op.tanh(gates[:, 3 * H:4 * H])
+    c_new = f * c + i * g
+    h_new = o * op.tanh(c_new)
+    before = lazy_stats()
+    eval_together(c_new, h_new)
+    after = lazy_stats()
+    assert {k: after[k] - before[k] for k in after} == {"kernels": 1, "gemms": 1, "temporaries": 1}
+    assert c_new.is_buffer() and h_new.is_buffer()
+    ir = last_ir()
+    assert ir.count("st ") == 2 and ir.count(" ld ") == 5 and ir.count("op tanh") == 2      # c' computed once
+    # what cannot share a kernel is evaluated one by one
+    s, m = op.sum(x, [-1]), x * 2.0
+    before = lazy_stats()
+    eval_together(s, m)
+    assert lazy_stats()["kernels"] - before["kernels"] == 2
+
+
 def test_lstm_gating_on_slices_is_one_map_kernel():
     H = 128
     g = Array(np.zeros((16, 4 * H), np.float32))

@@ -389,3 +389,29 @@ def test_npy_load_compute_save(tmp_path):
     np.testing.assert_array_equal(af.numpy(), c)
     (op.tanh(af) + ac).save(tmp_path / "out.npy")           # evaluated on the device, written from the host copy
     np.testing.assert_allclose(np.load(tmp_path / "out.npy"), np.tanh(c) + c, rtol=1e-5)
+
+
+def test_lstm_cell_outputs_evaluated_together(golden):
+    """eval_together(c', h'): one GEMM launch and one kernel that stores both; same numbers as evaluating them one
+    by one, and as the reference's outputs."""
+    from dali_b200.array import eval_together
+    x, h, c, Wx, Wh, b = (golden["lstm/" + k] for k in ("x", "h", "c", "Wx", "Wh", "b"))
+    H = x.shape[1]
+
+    def cell():
+        gates = op.dot(Array(x), Array(Wx)) + op.dot(Array(h), Array(Wh)) + Array(b)[None, :]
+        i, f, o = (op.sigmoid(gates[:, k * H:(k + 1) * H]) for k in range(3))
+        g = op.tanh(gates[:, 3 * H:4 * H])
+        c_new = f * Array(c) + i * g
+        return c_new, o * op.tanh(c_new)
+
+    c1, h1 = cell()
+    before = lazy_stats()
+    eval_together(c1, h1)
+    after = lazy_stats()
+    assert after["kernels"] - before["kernels"] == 1
+    c2, h2 = cell()
+    np.testing.assert_array_equal(c1.numpy(), c2.numpy())
+    np.testing.assert_array_equal(h1.numpy(), h2.numpy())
+    np.testing.assert_allclose(c1.numpy(), golden["lstm/c_new"], rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(h1.numpy(), golden["lstm/h_new"], rtol=1e-5, atol=1e-6)
