@@ -32,6 +32,7 @@ struct GemmVariant {
     int esize;      // 2 bf16, 4 tf32
     int split;      // 3xTF32
     int bm, bn, bk, stages;
+    int slices = 1; // the epilogue reads this many column slices of the product per output element
     int pair = 0;   // two CTAs (cta_group::2) share a 2*bm x bn tile, each staging half of the B tile
     bool b_kmajor() const { return split != 0; }   // the fp32 path transposes B while splitting it
     bool ncat() const { return split != 0 && bn <= 64; }   // b_hi | b_lo read as one operand of 2 * bn columns
@@ -57,13 +58,15 @@ struct GemmVariant {
         o << "gemm.e" << esize << ".s" << split << ".m" << bm << ".n" << bn << ".k" << bk << ".st" << stages;
         if (pair) o << ".pair";
         if (ncat()) o << ".ncat";
+        if (slices > 1) o << ".sl" << slices;
         return o.str();
     }
 };
 
 const char* red_c(DType t) { return dtype_c_name(t); }
 
-// EPILOGUE_CHUNK(row, col0, acc, nvalid): thread-local 32-wide slab of one output row
+// EPILOGUE_CHUNK(row, col0, acc, nvalid): thread-local slab of GEMM_CHUNK columns of one output row; `acc`
+// holds the accumulator of slice q in acc[q * GEMM_CHUNK ..]
 bool epilogue_macro(const Program& p, std::string* out, std::string* err) {
     if (!p.has_acc || p.nreduce != 0 || p.rank != 2) { *err = "epilogue program must be 'space 2 0' and read 'acc'"; return false; }
     if (p.has_indirect || p.n_reductions || p.has_iota) { *err = "epilogue program may not gather, reduce or use iota args"; return false; }
@@ -85,10 +88,10 @@ bool epilogue_macro(const Program& p, std::string* out, std::string* err) {
         if (s.kind == S_ST && s.aop != A_ASSIGN) a = s.arg;
         if (a < 0 || loaded[a]) continue;
         loaded[a] = true;
-        o << "  float in" << a << "[32]; gemm_io::load_chunk(a" << a << ", (col0), " << W(3 * a + 2) << ", in" << a << ", (nvalid)); \\\n";
+        o << "  float in" << a << "[GEMM_CHUNK]; gemm_io::load_chunk(a" << a << ", (col0), " << W(3 * a + 2) << ", in" << a << ", (nvalid)); \\\n";
     }
     for (const Stmt& s : p.stmts)
-        if (s.kind == S_ST) o << "  float out" << s.arg << "[32]; \\\n";
+        if (s.kind == S_ST) o << "  float out" << s.arg << "[GEMM_CHUNK]; \\\n";
     for (const Stmt& s : p.stmts) {
         if (s.kind == S_SC)
             o << "  const " << red_c(s.dtype) << " v" << s.id << " = *reinterpret_cast<const " << red_c(s.dtype) << "*>(&"
@@ -99,11 +102,11 @@ bool epilogue_macro(const Program& p, std::string* out, std::string* err) {
             o << "  const " << red_c(s.dtype) << " v" << s.id << " = (" << red_c(s.dtype) << ")(" << lit << "); \\\n";
         }
     }
-    o << "  _Pragma(\"unroll\") for (int j = 0; j < 32; ++j) { \\\n";
+    o << "  _Pragma(\"unroll\") for (int j = 0; j < GEMM_CHUNK; ++j) { \\\n";
     for (const Stmt& s : p.stmts) {
         const std::string T = red_c(s.dtype);
         switch (s.kind) {
-            case S_ACC: o << "    const float v" << s.id << " = acc[j]; \\\n"; break;
+            case S_ACC: o << "    const float v" << s.id << " = acc[" << s.arg << " * GEMM_CHUNK + j]; \\\n"; break;
             case S_LD: o << "    const " << T << " v" << s.id << " = (" << T << ")in" << s.arg << "[j]; \\\n"; break;
             case S_CAST: o << "    const " << T << " v" << s.id << " = (" << T << ")v" << s.in[0] << "; \\\n"; break;
             case S_OP: {
@@ -148,26 +151,26 @@ bool epilogue_macro(const Program& p, std::string* out, std::string* err) {
 const char* kGemmIo = R"IO(
 namespace gemm_io {
 DEV bool aligned16(const void* p) { return (reinterpret_cast<unsigned long long>(p) & 15ull) == 0; }
-// 32 consecutive columns of one row, element stride cs, as fp32
+// GEMM_CHUNK consecutive columns of one row, element stride cs, as fp32
 DEV void load_chunk(const float* p, long long col0, long long cs, float* dst, int nvalid) {
-    if (cs == 1 && nvalid == 32 && aligned16(p + col0)) {
+    if (cs == 1 && nvalid == GEMM_CHUNK && aligned16(p + col0)) {
         const float4* q = reinterpret_cast<const float4*>(p + col0);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { float4 t = q[i]; dst[4 * i] = t.x; dst[4 * i + 1] = t.y; dst[4 * i + 2] = t.z; dst[4 * i + 3] = t.w; }
+        for (int i = 0; i < GEMM_CHUNK / 4; ++i) { float4 t = q[i]; dst[4 * i] = t.x; dst[4 * i + 1] = t.y; dst[4 * i + 2] = t.z; dst[4 * i + 3] = t.w; }
     } else if (cs == 0) {
         const float t = p[0];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) dst[i] = t;
+        for (int i = 0; i < GEMM_CHUNK; ++i) dst[i] = t;
     } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) dst[i] = i < nvalid ? p[(col0 + i) * cs] : 0.0f;
+        for (int i = 0; i < GEMM_CHUNK; ++i) dst[i] = i < nvalid ? p[(col0 + i) * cs] : 0.0f;
     }
 }
 DEV void load_chunk(const unsigned short* p, long long col0, long long cs, float* dst, int nvalid) {
-    if (cs == 1 && nvalid == 32 && aligned16(p + col0)) {
+    if (cs == 1 && nvalid == GEMM_CHUNK && aligned16(p + col0)) {
         const uint4* q = reinterpret_cast<const uint4*>(p + col0);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < GEMM_CHUNK / 8; ++i) {
             uint4 t = q[i];
             unsigned w[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
@@ -175,39 +178,39 @@ DEV void load_chunk(const unsigned short* p, long long col0, long long cs, float
         }
     } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) dst[i] = i < nvalid ? gemm::bf16_to_f32(p[cs == 0 ? 0 : (col0 + i) * cs]) : 0.0f;
+        for (int i = 0; i < GEMM_CHUNK; ++i) dst[i] = i < nvalid ? gemm::bf16_to_f32(p[cs == 0 ? 0 : (col0 + i) * cs]) : 0.0f;
     }
 }
 template <typename T> DEV void load_chunk(const T* p, long long col0, long long cs, float* dst, int nvalid) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) dst[i] = i < nvalid ? (float)p[cs == 0 ? 0 : (col0 + i) * cs] : 0.0f;
+    for (int i = 0; i < GEMM_CHUNK; ++i) dst[i] = i < nvalid ? (float)p[cs == 0 ? 0 : (col0 + i) * cs] : 0.0f;
 }
 DEV void store_chunk(float* p, long long col0, long long cs, const float* src, int nvalid) {
-    if (cs == 1 && nvalid == 32 && aligned16(p + col0)) {
+    if (cs == 1 && nvalid == GEMM_CHUNK && aligned16(p + col0)) {
         float4* q = reinterpret_cast<float4*>(p + col0);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) q[i] = make_float4(src[4 * i], src[4 * i + 1], src[4 * i + 2], src[4 * i + 3]);
+        for (int i = 0; i < GEMM_CHUNK / 4; ++i) q[i] = make_float4(src[4 * i], src[4 * i + 1], src[4 * i + 2], src[4 * i + 3]);
     } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) if (i < nvalid) p[(col0 + i) * cs] = src[i];
+        for (int i = 0; i < GEMM_CHUNK; ++i) if (i < nvalid) p[(col0 + i) * cs] = src[i];
     }
 }
 DEV void store_chunk(unsigned short* p, long long col0, long long cs, const float* src, int nvalid) {
-    if (cs == 1 && nvalid == 32 && aligned16(p + col0)) {
+    if (cs == 1 && nvalid == GEMM_CHUNK && aligned16(p + col0)) {
         uint4* q = reinterpret_cast<uint4*>(p + col0);
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < GEMM_CHUNK / 8; ++i)
             q[i] = make_uint4(gemm::pack_bf16x2(src[8 * i], src[8 * i + 1]), gemm::pack_bf16x2(src[8 * i + 2], src[8 * i + 3]),
                               gemm::pack_bf16x2(src[8 * i + 4], src[8 * i + 5]), gemm::pack_bf16x2(src[8 * i + 6], src[8 * i + 7]));
     } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
+        for (int i = 0; i < GEMM_CHUNK; ++i)
             if (i < nvalid) p[(col0 + i) * cs] = (unsigned short)(gemm::pack_bf16x2(src[i], 0.0f) & 0xffffu);
     }
 }
 template <typename T> DEV void store_chunk(T* p, long long col0, long long cs, const float* src, int nvalid) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) if (i < nvalid) p[(col0 + i) * cs] = (T)src[i];
+    for (int i = 0; i < GEMM_CHUNK; ++i) if (i < nvalid) p[(col0 + i) * cs] = (T)src[i];
 }
 }  // namespace gemm_io
 )IO";
@@ -223,6 +226,7 @@ bool gemm_source(void* ctx, std::string* src, std::string* err) {
     o << "#define GEMM_BM " << c->v.bm << "\n#define GEMM_BN " << c->v.bn << "\n#define GEMM_BK " << c->v.bk << "\n";
     o << "#define GEMM_STAGES " << c->v.stages << "\n#define GEMM_ESIZE " << c->v.esize << "\n#define GEMM_SPLIT " << c->v.split << "\n";
     o << "#define GEMM_IDESC " << c->v.idesc() << "u\n";
+    o << "#define GEMM_SLICES " << c->v.slices << "\n";
     o << "#define GEMM_NCAT " << (c->v.ncat() ? 1 : 0) << "\n#define GEMM_IDESC_WIDE " << c->v.idesc(2 * c->v.bn) << "u\n";
     o << "#define GEMM_B_KMAJOR " << (c->v.b_kmajor() ? 1 : 0) << "\n#define GEMM_PAIR " << c->v.pair << "\n";
     int words = 3 * (int)c->p->args.size() + (int)c->p->scalars.size();
@@ -314,10 +318,24 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
         return DALIB200_ERR_INVALID;
     }
     if (3 * n_arrays + n_scalars > 64) { set_error("gemm_fused: too many epilogue operands"); return DALIB200_ERR_TOO_LARGE; }
-    GemmSourceCtx ctx{&prog, choose_variant(bf16, m, n)};
+    const int slices = prog.acc_slices;
+    if (slices > 1 && (bf16 || (slices != 2 && slices != 4))) {
+        set_error("gemm_fused: an epilogue over column slices of the product needs fp32 operands and 2 or 4 slices");
+        return DALIB200_ERR_UNSUPPORTED;
+    }
+    GemmSourceCtx ctx{&prog, choose_variant(bf16, m, slices > 1 ? (int64_t)n * slices : n)};
+    if (slices > 1) {
+        // 64 accumulator columns = 64 / slices output columns x slices; row blocks of 16 or 32 keep the swizzle groups whole
+        ctx.v.bn = 64;
+        ctx.v.slices = slices;
+        const size_t budget = 200 * 1024;
+        ctx.v.stages = (int)(budget / ctx.v.stage_bytes());
+        if (ctx.v.stages > 8) ctx.v.stages = 8;
+    }
     const GemmVariant& v = ctx.v;
+    const uint64_t b_cols = (uint64_t)n * (uint64_t)slices;      // columns of the product (rows of the transposed B)
     std::ostringstream key;
-    key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + "|sm_100a|gemm-8|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" +
+    key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + "|sm_100a|gemm-9|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" +
                                                      std::to_string(fnv1a(device_prelude())));
     tl_gemm_variant = std::string(bf16 ? "tcgen05.bf16 " : "tcgen05.tf32x3 ") + v.key() + (n_pairs > 1 ? " x2" : "");
     note_gemm_kernel(tl_gemm_variant);
@@ -334,8 +352,9 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
         bool ok = make_map(&tm[4 * pi + 0], bf16, g.a, k, (uint64_t)m, (uint64_t)g.lda, (uint32_t)v.bk, (uint32_t)v.bm, &err) &&
                   make_map(&tm[4 * pi + 2], bf16, g.a_lo ? g.a_lo : g.a, k, (uint64_t)m, (uint64_t)g.lda, (uint32_t)v.bk, (uint32_t)v.bm, &err);
         if (ok && v.b_kmajor())
-            ok = make_map(&tm[4 * pi + 1], bf16, g.b, k, (uint64_t)n, (uint64_t)g.ldb, (uint32_t)v.bk, (uint32_t)v.bn, &err) &&
-                 make_map(&tm[4 * pi + 3], bf16, g.b_lo ? g.b_lo : g.b, k, (uint64_t)n, (uint64_t)g.ldb, (uint32_t)v.bk, (uint32_t)v.bn, &err);
+            ok = make_map(&tm[4 * pi + 1], bf16, g.b, k, b_cols, (uint64_t)g.ldb, (uint32_t)v.bk, (uint32_t)(v.bn / slices), &err) &&
+                 make_map(&tm[4 * pi + 3], bf16, g.b_lo ? g.b_lo : g.b, k, b_cols, (uint64_t)g.ldb, (uint32_t)v.bk,
+                          (uint32_t)(v.bn / slices), &err);
         else if (ok)
             ok = make_map(&tm[4 * pi + 1], bf16, g.b, (uint64_t)n, k, (uint64_t)g.ldb, sw, (uint32_t)v.bk, &err) &&
                  make_map(&tm[4 * pi + 3], bf16, g.b_lo ? g.b_lo : g.b, (uint64_t)n, k, (uint64_t)g.ldb, sw, (uint32_t)v.bk, &err);
@@ -362,7 +381,7 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
     // persistent CTAs (CTA pairs), at most one per SM (SM pair); they take the tiles round robin
     const int64_t rows_per_tile = (int64_t)v.bm * (v.pair ? 2 : 1);
     p.tiles_m = (unsigned)((m + rows_per_tile - 1) / rows_per_tile);
-    p.tiles_n = (unsigned)((n + v.bn - 1) / v.bn);
+    p.tiles_n = (unsigned)((n + v.bn / slices - 1) / (v.bn / slices));
     const uint64_t total_tiles = (uint64_t)p.tiles_m * p.tiles_n;
     if (total_tiles > 0x7fffffffull) { set_error("gemm_fused: too many output tiles"); return DALIB200_ERR_TOO_LARGE; }
     int sms = 0;
@@ -397,6 +416,13 @@ int dalib200_gemm_fused_sum(int device, void* stream, int ab_dtype, int n_pairs,
     const bool bf16 = ab_dtype == DALIB200_BF16;
     const int es = bf16 ? 2 : 4;
     const bool compile_only = device < 0;
+    // an epilogue that reads S column slices per output element: n is the width of one slice, B has S * n columns
+    int64_t n_total = n;
+    {
+        Program prog;
+        if (!find_program(epilogue_hash, &prog)) { set_error("unknown epilogue hash"); return DALIB200_ERR_NOT_FOUND; }
+        n_total = n * prog.acc_slices;
+    }
     bool presplit = !bf16 && a_lo && b_lo && a_lo[0] && b_lo[0];
     GemmPair pairs[2];
     for (int p = 0; p < n_pairs; ++p) {
@@ -408,7 +434,7 @@ int dalib200_gemm_fused_sum(int device, void* stream, int ab_dtype, int n_pairs,
         if (!a[p] || !b[p] || k[p] < 0) { set_error("dalib200_gemm_fused: bad operand pair"); return DALIB200_ERR_INVALID; }
         // what TMA needs: 16-byte aligned bases and row pitches
         if (((uintptr_t)a[p] & 15) || ((uintptr_t)b[p] & 15) || (lda[p] * es) % 16 || (ldb[p] * es) % 16 || lda[p] < k[p] ||
-            ldb[p] < (presplit ? k[p] : n) || (lo_a && ((uintptr_t)a_lo[p] & 15)) || (lo_b && ((uintptr_t)b_lo[p] & 15)) ||
+            ldb[p] < (presplit ? k[p] : n_total) || (lo_a && ((uintptr_t)a_lo[p] & 15)) || (lo_b && ((uintptr_t)b_lo[p] & 15)) ||
             m > 2147483647LL || n > 2147483647LL || k[p] > 2147483647LL) {
             set_error("dalib200_gemm_fused: operands must be row-major with 16-byte aligned base and row pitch");
             return DALIB200_ERR_UNSUPPORTED;
@@ -426,13 +452,13 @@ int dalib200_gemm_fused_sum(int device, void* stream, int ab_dtype, int n_pairs,
     size_t bytes[8] = {0};
     int rc = DALIB200_OK;
     for (int p = 0; p < n_pairs && rc == DALIB200_OK; ++p) {
-        if (k[p] % 4 || n % 4) { set_error("dalib200_gemm_fused: fp32 operands need k and n to be multiples of 4"); rc = DALIB200_ERR_UNSUPPORTED; break; }
+        if (k[p] % 4 || n_total % 4) { set_error("dalib200_gemm_fused: fp32 operands need k and n to be multiples of 4"); rc = DALIB200_ERR_UNSUPPORTED; break; }
         bytes[4 * p] = bytes[4 * p + 1] = (size_t)m * k[p] * 4;
-        bytes[4 * p + 2] = bytes[4 * p + 3] = (size_t)k[p] * n * 4;
+        bytes[4 * p + 2] = bytes[4 * p + 3] = (size_t)k[p] * n_total * 4;
         for (int j = 0; j < 4 && rc == DALIB200_OK; ++j) rc = dalib200_alloc(device, bytes[4 * p + j], &tmp[4 * p + j]);
         if (rc != DALIB200_OK) break;
         if (split_tf32((cudaStream_t)stream, (const float*)a[p], m, k[p], lda[p], false, (float*)tmp[4 * p], (float*)tmp[4 * p + 1]) != cudaSuccess ||
-            split_tf32((cudaStream_t)stream, (const float*)b[p], k[p], n, ldb[p], true, (float*)tmp[4 * p + 2], (float*)tmp[4 * p + 3]) != cudaSuccess) {
+            split_tf32((cudaStream_t)stream, (const float*)b[p], k[p], n_total, ldb[p], true, (float*)tmp[4 * p + 2], (float*)tmp[4 * p + 3]) != cudaSuccess) {
             set_error("split_tf32 launch failed");
             rc = DALIB200_ERR_CUDA;
         }

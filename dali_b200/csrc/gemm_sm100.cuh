@@ -19,6 +19,10 @@
 //                     issues a_hi.[b_hi | b_lo] (GEMM_IDESC_WIDE) and a_lo.b_hi: two instructions and one
 //                     read of a_hi instead of three and two.  Each round-robin accumulator then has its own
 //                     correction accumulator in the columns next to it.
+//   GEMM_SLICES       S > 1 (fp32 K-major path): the epilogue's space is [M, N] and it reads S values per output
+//                     element, the product's columns q*N + col for q < S (the four gates of an LSTM unit).  A tile
+//                     then covers GEMM_BN / S output columns; its B tile is fetched as S row blocks of the
+//                     (transposed) operand, so accumulator column q * (GEMM_BN / S) + j is slice q of output j
 //   GEMM_IDESC        tcgen05 instruction descriptor
 // and a macro EPILOGUE_CHUNK(row, col0, acc, nvalid) generated from the
 // expression that consumes the product.
@@ -55,6 +59,11 @@ struct GemmP {
 };
 
 #define GEMM_THREADS 192
+#ifndef GEMM_SLICES
+#define GEMM_SLICES 1
+#endif
+#define GEMM_TILE_N (GEMM_BN / GEMM_SLICES)                  /* output columns of a tile */
+#define GEMM_CHUNK (GEMM_SLICES > 1 ? GEMM_TILE_N : 32)      /* output columns an epilogue call handles */
 #define GEMM_RASTER 8u
 #ifndef GEMM_PAIR
 #define GEMM_PAIR 0
@@ -282,7 +291,7 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
         const unsigned band_w = p.tiles_n - band_n0 < GEMM_RASTER ? p.tiles_n - band_n0 : GEMM_RASTER;
         const unsigned in_band = lin - band * GEMM_RASTER * p.tiles_m;
         *m0 = ((long long)(in_band / band_w) * (GEMM_PAIR ? 2 : 1) + cta_rank) * GEMM_BM;     // this CTA's rows
-        *n0 = (long long)(band_n0 + in_band % band_w) * GEMM_BN;
+        *n0 = (long long)(band_n0 + in_band % band_w) * GEMM_TILE_N;
     };
 
     if (threadIdx.x == 0) {
@@ -331,7 +340,11 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
 #else
                 mbar_expect_tx(&full_bar[s], GEMM_STAGE_BYTES);
                 tma_load_2d(st, mA, &full_bar[s], kx, (int)m0);
-#if GEMM_B_KMAJOR
+#if GEMM_B_KMAJOR && GEMM_SLICES > 1
+#pragma unroll
+                for (int q = 0; q < GEMM_SLICES; ++q)      // slice q of these output columns: rows q*N + n0 .. of the transposed operand
+                    tma_load_2d(bt + q * GEMM_TILE_N * 128, mB, &full_bar[s], kx, (int)(q * p.N + n0));
+#elif GEMM_B_KMAJOR
                 tma_load_2d(bt, mB, &full_bar[s], kx, (int)n0);
 #else
 #pragma unroll
@@ -349,7 +362,11 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
                 unsigned char* blo = alo + GEMM_A_TILE_BYTES;
 #endif
                 tma_load_2d(alo, mAlo, &full_bar[s], kx, (int)m0);
-#if GEMM_B_KMAJOR
+#if GEMM_B_KMAJOR && GEMM_SLICES > 1
+#pragma unroll
+                for (int q = 0; q < GEMM_SLICES; ++q)
+                    tma_load_2d(blo + q * GEMM_TILE_N * 128, mBlo, &full_bar[s], kx, (int)(q * p.N + n0));
+#elif GEMM_B_KMAJOR
                 tma_load_2d(blo, mBlo, &full_bar[s], kx, (int)n0);
 #else
 #pragma unroll
@@ -432,6 +449,39 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
             }
             fence_after_sync();
             const long long row = m0 + warp * 32 + lane;
+#if GEMM_SLICES > 1
+            {
+                // all GEMM_BN accumulator columns of this row: slice q of output column j sits at q * GEMM_TILE_N + j
+                float acc[GEMM_BN];
+#pragma unroll
+                for (int c = 0; c < GEMM_BN; c += 32) {
+                    if (num_kb > 0) {
+                        const unsigned lane_base = tmem_base + as * GEMM_ACC_COLS + ((unsigned)(warp * 32) << 16) + (unsigned)c;
+                        tmem_ld32(lane_base, acc + c);
+                        const int used = num_kb < GEMM_NACC ? num_kb : GEMM_NACC;
+                        float part[32];
+                        for (int a = 1; a < (GEMM_NCAT ? 2 * used : used); ++a) {
+                            tmem_ld32(lane_base + (unsigned)(a * GEMM_BN), part);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) acc[c + i] += part[i];
+                        }
+#if !GEMM_NCAT
+                        tmem_ld32(lane_base + (unsigned)(GEMM_NACC * GEMM_BN), part);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) acc[c + i] += part[i];
+#endif
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) acc[c + i] = 0.0f;
+                    }
+                }
+                const long long col0 = n0;
+                if (row < p.M && col0 < p.N) {
+                    const int nvalid = (p.N - col0) < GEMM_CHUNK ? (int)(p.N - col0) : GEMM_CHUNK;
+                    EPILOGUE_CHUNK(row, col0, acc, nvalid)
+                }
+            }
+#else
 #pragma unroll 1
             for (int c = 0; c < GEMM_BN; c += 32) {
                 float acc[32];
@@ -468,6 +518,7 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
                     EPILOGUE_CHUNK(row, col0, acc, nvalid)
                 }
             }
+#endif      // GEMM_SLICES
             if (num_kb > 0) {
                 // this warp has read its part of the accumulator stage: hand it back to the MMA issuer
                 fence_before_sync();

@@ -228,8 +228,11 @@ bool parse_program(const std::string& text, Program* out, std::string* err) {
             }
             s.kind = x ? S_LDX : S_LD;
         } else if (k == "acc") {
-            if (t.size() != 3 || s.dtype != F32) return fail("expected 'v<k> f32 acc'");
+            if ((t.size() != 3 && t.size() != 4) || s.dtype != F32) return fail("expected 'v<k> f32 acc [slice]'");
             if (p.nreduce != 0 || p.rank != 2) return fail("'acc' needs 'space 2 0'");
+            s.arg = 0;     // which column slice of the product (see Program::acc_slices)
+            if (t.size() == 4 && (!parse_int(t[3], &s.arg) || s.arg < 0 || s.arg > 7)) return fail("bad accumulator slice");
+            if (s.arg + 1 > p.acc_slices) p.acc_slices = s.arg + 1;
             s.kind = S_ACC;
             p.has_acc = true;
         } else if (k == "sc") {

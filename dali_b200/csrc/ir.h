@@ -83,6 +83,7 @@ struct Program {
     bool has_indirect = false;
     bool has_iota = false;
     bool has_acc = false;          // reads the GEMM accumulator: an epilogue program
+    int acc_slices = 1;            // 'acc q': the space is [m, n] and slice q is the product's columns q*n .. q*n + n - 1
     bool has_bf16 = false;
     std::string text;              // canonical source text (for collision checks)
 };

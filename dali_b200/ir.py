@@ -36,9 +36,10 @@ class IRBuilder:
     def sc(self, j):
         return self._val(self.scalars[j], "sc %d" % j)
 
-    def acc(self):
-        """The GEMM accumulator at (row, col) -- epilogue programs only."""
-        return self._val("f32", "acc")
+    def acc(self, slice_=0):
+        """The GEMM accumulator at (row, col) -- epilogue programs only.  With slices, `acc q` is the product's
+        column q * n + col (n = the width of the program's space)."""
+        return self._val("f32", "acc" if slice_ == 0 else "acc %d" % slice_)
 
     def const(self, dtype, literal):
         return self._val(dtype, "const %s" % literal)
@@ -130,4 +131,21 @@ def gemm_store_ir(out_dtype="f32", op="assign"):
     b = IRBuilder(2, 0)
     out = b.arg(out_dtype)
     b.st(out, b.acc(), op)
+    return b.text()
+
+
+def lstm_cell_epilogue_ir():
+    """The whole LSTM gating as the epilogue of gates = x.Wx + h.Wh: per output (row, unit) the four accumulator
+    slices i, f, o, g plus their biases, c' = sigmoid(f)*c + sigmoid(i)*tanh(g), h' = sigmoid(o)*tanh(c').
+    args (c_new, h_new, b_i, b_f, b_o, b_g, c); the gates matrix is never written."""
+    b = IRBuilder(2, 0)
+    cn, hn = b.arg("f32"), b.arg("f32")
+    bias = [b.arg("f32") for _ in range(4)]
+    c = b.arg("f32")
+    pre = [b.op("add", b.acc(q), b.ld(bias[q])) for q in range(4)]
+    i, f, o = (b.op("sigmoid", pre[q]) for q in range(3))
+    g = b.op("tanh", pre[3])
+    cnew = b.op("add", b.op("eltmul", f, b.ld(c)), b.op("eltmul", i, g))
+    b.st(cn, cnew)
+    b.st(hn, b.op("eltmul", o, b.op("tanh", cnew)))
     return b.text()

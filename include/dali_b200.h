@@ -194,6 +194,12 @@ int dalib200_gemm_fused(int device, void* stream, int ab_dtype,
                         const int64_t* const* strides, int n_arrays,
                         const void* const* scalars, int n_scalars);
 
+/* Column slices.  An epilogue program may read `acc q` for q < S (S = 2 or 4, fp32
+ * operands): its space is then [m, n] and `acc q` at (row, col) is the product's
+ * column q*n + col, so B has S*n columns.  One output element sees S accumulator
+ * values -- the four gates of an LSTM unit -- and the product itself is never
+ * written: the reference materialises dot(x,Wx) + dot(h,Wh) + b as a [B,4H] array
+ * and reads it back through four column slices (layers/lstm.cpp:226-263). */
 /* The same with the accumulator summed over n_pairs (1 or 2) operand pairs,
  *     acc[m,n] = A_0[m,k_0] . B_0[k_0,n] + A_1[m,k_1] . B_1[k_1,n],
  * in ONE launch and one accumulator: dot(x,Wx) + dot(h,Wh) of a recurrent cell

@@ -10,7 +10,7 @@ import pytest
 import torch
 
 import dali_oracle as oracle
-from dali_b200.ir import IRBuilder, gemm_bias_tanh_ir, gemm_store_ir
+from dali_b200.ir import IRBuilder, gemm_bias_tanh_ir, gemm_store_ir, lstm_cell_epilogue_ir
 
 pytestmark = pytest.mark.gpu
 
@@ -133,6 +133,31 @@ def test_two_products_in_one_accumulator(lib, shape):
     e2.st(o2, e2.op("add", e2.op("add", e2.acc(), e2.ld(first)), e2.ld(bias2)))
     lib.gemm_fused(0, m, n, k2, d[2], k2, d[3], n, lib.compile(e2.text()), [two, two, dev(b)], strides=[None, None, [0, 1]])
     np.testing.assert_allclose(got, host(two), rtol=1e-5, atol=1e-5 * float(bound.max()))
+
+
+@pytest.mark.parametrize("shape", [(64, 128), (256, 1024), (200, 72), (130, 40)])
+def test_lstm_gating_as_the_epilogue_of_the_gate_products(lib, shape):
+    """The four gate slices of x.Wx + h.Wh meet in the epilogue (acc 0..3): c' and h' come out of the GEMM
+    kernel, the [B,4H] gates matrix is never written.  Against the oracle's gating on fp64-accumulated gates;
+    ragged B and H (H not a multiple of the 16 units a tile covers)."""
+    B, H = shape
+    rng = np.random.default_rng(B + H)
+    x, h, c = (rng.standard_normal((B, H)).astype(np.float32) for _ in range(3))
+    Wx, Wh = ((rng.standard_normal((H, 4 * H)) * 0.05).astype(np.float32) for _ in range(2))
+    b = (rng.standard_normal(4 * H) * 0.1).astype(np.float32)
+    c_new, h_new = torch.full((B, H), -7.0, device="cuda"), torch.full((B, H), -7.0, device="cuda")
+    bd, d = dev(b), [dev(v) for v in (x, Wx, h, Wh)]
+    row = [0, 1]
+    lib.gemm_fused_sum(0, B, H, [(H, d[0], H, d[1], 4 * H), (H, d[2], H, d[3], 4 * H)], lib.compile(lstm_cell_epilogue_ir()),
+                       [c_new, h_new, bd, bd, bd, bd, dev(c)], strides=[None, None, row, row, row, row, None],
+                       offsets=[0, 0, 0, H, 2 * H, 3 * H, 0])
+    got_c, got_h = host(c_new), host(h_new)
+    assert lib.gemm_error_flag() == 0
+    assert ".sl4" in lib.last_gemm_kernel()
+    gates = (x.astype(np.float64) @ Wx + h.astype(np.float64) @ Wh + b).astype(np.float32)
+    want_c, want_h = oracle.lstm_gating(gates, c)
+    np.testing.assert_allclose(got_c, want_c, rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(got_h, want_h, rtol=1e-5, atol=1e-5)
 
 
 def test_two_bf16_products_in_one_accumulator(lib):
