@@ -259,6 +259,22 @@ bool make_map(CUtensorMap* map, bool bf16, const void* base, uint64_t inner, uin
     return true;
 }
 
+// fp32 [slices][cols][k] view of a transposed operand (row pitch ld_elems): box = all slices x box_cols x box_k
+bool make_map_sliced(CUtensorMap* map, const void* base, uint64_t k, uint64_t cols, uint64_t slices, uint64_t ld_elems,
+                     uint32_t box_k, uint32_t box_cols, std::string* err) {
+    static EncodeTiledFn encode = reinterpret_cast<EncodeTiledFn>(driver_entry("cuTensorMapEncodeTiled"));
+    if (!encode) { *err = "cuTensorMapEncodeTiled unavailable"; return false; }
+    cuuint64_t dims[3] = {k, cols, slices};
+    cuuint64_t strides[2] = {ld_elems * 4, cols * ld_elems * 4};
+    cuuint32_t box[3] = {box_k, box_cols, (cuuint32_t)slices};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { *err = "cuTensorMapEncodeTiled (3-D) failed with CUresult " + std::to_string((int)r); return false; }
+    return true;
+}
+
 GemmVariant choose_variant(bool bf16, int64_t m, int64_t n) {
     GemmVariant v;
     v.esize = bf16 ? 2 : 4;
@@ -335,7 +351,7 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
     const GemmVariant& v = ctx.v;
     const uint64_t b_cols = (uint64_t)n * (uint64_t)slices;      // columns of the product (rows of the transposed B)
     std::ostringstream key;
-    key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + "|sm_100a|gemm-9|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" +
+    key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + "|sm_100a|gemm-10|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" +
                                                      std::to_string(fnv1a(device_prelude())));
     tl_gemm_variant = std::string(bf16 ? "tcgen05.bf16 " : "tcgen05.tf32x3 ") + v.key() + (n_pairs > 1 ? " x2" : "");
     note_gemm_kernel(tl_gemm_variant);
@@ -351,7 +367,12 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
         const uint64_t k = (uint64_t)g.k;
         bool ok = make_map(&tm[4 * pi + 0], bf16, g.a, k, (uint64_t)m, (uint64_t)g.lda, (uint32_t)v.bk, (uint32_t)v.bm, &err) &&
                   make_map(&tm[4 * pi + 2], bf16, g.a_lo ? g.a_lo : g.a, k, (uint64_t)m, (uint64_t)g.lda, (uint32_t)v.bk, (uint32_t)v.bm, &err);
-        if (ok && v.b_kmajor())
+        if (ok && v.b_kmajor() && slices > 1)
+            ok = make_map_sliced(&tm[4 * pi + 1], g.b, k, (uint64_t)n, (uint64_t)slices, (uint64_t)g.ldb, (uint32_t)v.bk,
+                                 (uint32_t)(v.bn / slices), &err) &&
+                 make_map_sliced(&tm[4 * pi + 3], g.b_lo ? g.b_lo : g.b, k, (uint64_t)n, (uint64_t)slices, (uint64_t)g.ldb,
+                                 (uint32_t)v.bk, (uint32_t)(v.bn / slices), &err);
+        else if (ok && v.b_kmajor())
             ok = make_map(&tm[4 * pi + 1], bf16, g.b, k, b_cols, (uint64_t)g.ldb, (uint32_t)v.bk, (uint32_t)(v.bn / slices), &err) &&
                  make_map(&tm[4 * pi + 3], bf16, g.b_lo ? g.b_lo : g.b, k, b_cols, (uint64_t)g.ldb, (uint32_t)v.bk,
                           (uint32_t)(v.bn / slices), &err);

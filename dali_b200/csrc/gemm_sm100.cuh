@@ -21,8 +21,8 @@
 //                     correction accumulator in the columns next to it.
 //   GEMM_SLICES       S > 1 (fp32 K-major path): the epilogue's space is [M, N] and it reads S values per output
 //                     element, the product's columns q*N + col for q < S (the four gates of an LSTM unit).  A tile
-//                     then covers GEMM_BN / S output columns; its B tile is fetched as S row blocks of the
-//                     (transposed) operand, so accumulator column q * (GEMM_BN / S) + j is slice q of output j
+//                     then covers GEMM_BN / S output columns; its B tile is one 3-D TMA copy of the
+//                     (transposed) operand seen as [slice][column][k], so accumulator column q * (GEMM_BN / S) + j is slice q of output j
 //   GEMM_IDESC        tcgen05 instruction descriptor
 // and a macro EPILOGUE_CHUNK(row, col0, acc, nvalid) generated from the
 // expression that consumes the product.
@@ -141,6 +141,11 @@ DEV void tma_load_2d(void* dst, const TensorMap* map, unsigned long long* bar, i
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+DEV void tma_load_3d(void* dst, const TensorMap* map, unsigned long long* bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
 }
 #if GEMM_PAIR
 // the copy lands in THIS CTA's shared memory and reports its bytes to the barrier at shared::cluster
@@ -341,9 +346,8 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
                 mbar_expect_tx(&full_bar[s], GEMM_STAGE_BYTES);
                 tma_load_2d(st, mA, &full_bar[s], kx, (int)m0);
 #if GEMM_B_KMAJOR && GEMM_SLICES > 1
-#pragma unroll
-                for (int q = 0; q < GEMM_SLICES; ++q)      // slice q of these output columns: rows q*N + n0 .. of the transposed operand
-                    tma_load_2d(bt + q * GEMM_TILE_N * 128, mB, &full_bar[s], kx, (int)(q * p.N + n0));
+                // the transposed operand as [slice][column][k]: one copy brings the GEMM_TILE_N rows of every slice
+                tma_load_3d(bt, mB, &full_bar[s], kx, (int)n0, 0);
 #elif GEMM_B_KMAJOR
                 tma_load_2d(bt, mB, &full_bar[s], kx, (int)n0);
 #else
@@ -363,9 +367,7 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
 #endif
                 tma_load_2d(alo, mAlo, &full_bar[s], kx, (int)m0);
 #if GEMM_B_KMAJOR && GEMM_SLICES > 1
-#pragma unroll
-                for (int q = 0; q < GEMM_SLICES; ++q)
-                    tma_load_2d(blo + q * GEMM_TILE_N * 128, mBlo, &full_bar[s], kx, (int)(q * p.N + n0));
+                tma_load_3d(blo, mBlo, &full_bar[s], kx, (int)n0, 0);
 #elif GEMM_B_KMAJOR
                 tma_load_2d(blo, mBlo, &full_bar[s], kx, (int)n0);
 #else

@@ -19,6 +19,7 @@
 #include <cmath>
 #include <cstring>
 #include <map>
+#include <set>
 #include <sstream>
 
 #include "../../../include/dali_b200.h"
@@ -110,6 +111,11 @@ struct Lowerer {
     std::vector<Array> keep_alive;
     // the node whose value is the GEMM accumulator (epilogue programs): a MatMul, or the sum of two of them
     const Expression* acc_node = nullptr;
+    // > 0: the program's space is [m, slice_width] and the accumulator node, seen through a column slice that
+    // starts at q * slice_width, is the value `acc q` (gating over the four gate blocks of an LSTM product)
+    int64_t slice_width = 0;
+    std::set<int> slices_seen;
+    bool slice_fail = false;
 
     Lowerer(const std::vector<int64_t>& space_, int nreduce_, memory::Device dev)
         : space(space_), rank((int)space_.size()), nreduce(nreduce_), n_outer(rank - nreduce_), device(dev) {}
@@ -224,7 +230,10 @@ struct Lowerer {
             }
             case N_ELEMENTWISE: {
                 Elementwise* w = static_cast<Elementwise*>(e.get());
-                if (e.get() == acc_node && is_identity(m)) { id = new_value(DTYPE_FLOAT, true, "acc"); break; }
+                if (e.get() == acc_node) {
+                    const std::string t = acc_text(m);
+                    if (!t.empty()) { id = new_value(DTYPE_FLOAT, true, t); break; }
+                }
                 std::vector<int> in;
                 bool is_elem = false;
                 for (const Array& arg : w->arguments_) {
@@ -252,7 +261,8 @@ struct Lowerer {
                 const Array& arg = v->arguments_[0];
                 // a slice / broadcast of something that contains a product: evaluate that something
                 // once (GEMM with its elementwise surroundings as epilogue) and view the result
-                if (contains_matmul(arg)) materialize(arg);
+                // (unless the product is this program's accumulator and the view one of its column slices)
+                if (contains_matmul(arg) && !(slice_width > 0 && acc_node && contains_node(arg, acc_node))) materialize(arg);
                 IndexMap am(v->dims_.size());
                 for (size_t k = 0; k < v->dims_.size(); ++k) {
                     const ViewDim& d = v->dims_[k];
@@ -328,7 +338,8 @@ struct Lowerer {
                 id = visit(materialize(a), m);
                 break;
             case N_MATMUL: {
-                if (e.get() == acc_node && is_identity(m)) id = new_value(DTYPE_FLOAT, true, "acc");
+                const std::string t = e.get() == acc_node ? acc_text(m) : std::string();
+                if (!t.empty()) id = new_value(DTYPE_FLOAT, true, t);
                 else id = visit(materialize(a), m);
                 break;
             }
@@ -338,6 +349,28 @@ struct Lowerer {
         memo[key] = id;
         memo_nodes.push_back(e);
         return id;
+    }
+
+    // the accumulator node reached through map m: "acc" / "acc q", or "" when m is not one the GEMM epilogue can serve
+    std::string acc_text(const IndexMap& m) {
+        if (is_identity(m) && slice_width == 0) return "acc";
+        if (slice_width > 0 && (int)m.size() == 2 && m[0].src == 0 && m[0].mult == 1 && m[0].off == 0 && m[1].src == 1 &&
+            m[1].mult == 1 && m[1].off >= 0 && m[1].off % slice_width == 0) {
+            const int q = (int)(m[1].off / slice_width);
+            slices_seen.insert(q);
+            return q == 0 ? "acc" : "acc " + std::to_string(q);
+        }
+        if (slice_width > 0) slice_fail = true;
+        return "";
+    }
+
+    static bool contains_node(const Array& a, const Expression* node) {
+        if (a.is_stateless()) return false;
+        Expression* e = a.expression().get();
+        if (e == node) return true;
+        if (e->kind_ != N_ELEMENTWISE) return false;
+        for (const Array& arg : e->arguments_) if (contains_node(arg, node)) return true;
+        return false;
     }
 
     static bool is_identity(const IndexMap& m) {
@@ -598,26 +631,39 @@ void run_scan(const Array& dest, OPERATOR_T op, Scan* sc) {
 // tcgen05 GEMM whose epilogue is the tree.  false = this layout is not one the tensor-core path
 // takes (the caller goes on with the general path); operands of the products have then already
 // been evaluated, which is harmless.
-bool try_fused_gemm(const Array& dest, OPERATOR_T op, const Array& value, const Expression* acc) {
+// the operand buffers of the product(s) behind an accumulator node
+struct GemmOperands {
+    int np = 0;
+    BufferView *a[2] = {nullptr, nullptr}, *b[2] = {nullptr, nullptr};
+    std::vector<Array> keep;
+    int64_t m = 0, n = 0, k[2] = {0, 0};
+};
+bool gemm_operands(const Expression* acc, GemmOperands* g) {
     std::vector<const Expression*> products;
     if (acc->kind_ == N_MATMUL) products.push_back(acc);
     else for (const Array& arg : acc->arguments_) products.push_back(arg.expression().get());
-    const int np = (int)products.size();
-    BufferView *a[2] = {nullptr, nullptr}, *b[2] = {nullptr, nullptr};
-    std::vector<Array> operands;
-    int64_t m = 0, n = 0, k[2] = {0, 0};
-    for (int p = 0; p < np; ++p) {
+    g->np = (int)products.size();
+    for (int p = 0; p < g->np; ++p) {
         Array left = products[p]->arguments_[0], right = products[p]->arguments_[1];
         if (!left.is_buffer()) left.eval(false);
         if (!right.is_buffer()) right.eval(false);
-        a[p] = as<BufferView>(left);
-        b[p] = as<BufferView>(right);
-        if (!a[p] || !b[p]) return false;
-        operands.push_back(left);
-        operands.push_back(right);
-        m = a[p]->shape_[0]; k[p] = a[p]->shape_[1]; n = b[p]->shape_[1];
-        if (m == 0 || n == 0 || k[p] == 0) return false;
+        g->a[p] = as<BufferView>(left);
+        g->b[p] = as<BufferView>(right);
+        if (!g->a[p] || !g->b[p]) return false;
+        g->keep.push_back(left);
+        g->keep.push_back(right);
+        g->m = g->a[p]->shape_[0]; g->k[p] = g->a[p]->shape_[1]; g->n = g->b[p]->shape_[1];
+        if (g->m == 0 || g->n == 0 || g->k[p] == 0) return false;
     }
+    return true;
+}
+
+bool launch_gemm_program(Lowerer& L, const GemmOperands& g, int64_t m, int64_t n);
+
+bool try_fused_gemm(const Array& dest, OPERATOR_T op, const Array& value, const Expression* acc) {
+    GemmOperands g;
+    if (!gemm_operands(acc, &g)) return false;
+    const int64_t m = g.m, n = g.n;
     memory::Device device = dest.preferred_device();
 
     Lowerer L({m, n}, 0, device);
@@ -631,6 +677,17 @@ bool try_fused_gemm(const Array& dest, OPERATOR_T op, const Array& value, const 
     if (op != OPERATOR_T_EQL) L.leaves[leaf].read = true;
     L.keep_alive.push_back(dest);
     L.body.push_back("st " + std::to_string(leaf) + " " + ir_assign(op) + " v" + std::to_string(v));
+    return launch_gemm_program(L, g, m, n);
+}
+
+// Registers the epilogue program L holds, splits the operands and launches the GEMM over the [m, n] space
+// (n = the width of one column slice when the program reads several).
+bool launch_gemm_program(Lowerer& L, const GemmOperands& g, int64_t m, int64_t n) {
+    const int np = g.np;
+    BufferView* const* a = g.a;
+    BufferView* const* b = g.b;
+    const int64_t* k = g.k;
+    const memory::Device device = L.device;
     const std::string text = L.ir_text();
     const uint64_t hash = dalib::fnv1a(text);
     if (!dalib200_is_loaded(hash)) check(dalib200_compile(hash, text.c_str(), text.size()), "dalib200_compile");
@@ -640,7 +697,7 @@ bool try_fused_gemm(const Array& dest, OPERATOR_T op, const Array& value, const 
     if (tl_dry_run) {
         void* fake[16];
         for (auto& p : fake) p = (void*)(uintptr_t)4096;
-        if (L.leaves.size() > 16 || n % 4) return false;
+        if (L.leaves.size() > 16 || n % 4) return false;     // (a multiple of 4 per slice is one for the whole product too)
         for (int p = 0; p < np; ++p) {
             if (k[p] % 4) return false;
             pa_hi[p] = pa_lo[p] = pb_hi[p] = pb_lo[p] = fake[0];
@@ -860,6 +917,59 @@ void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) 
     L.launch();
 }
 
+namespace {
+// a product (or a sum of two) reachable from `a` through elementwise nodes AND views
+void find_acc_through_views(const Array& a, const Expression** out) {
+    if (*out || a.is_stateless()) return;
+    Expression* e = a.expression().get();
+    if (e->kind_ == N_MATMUL) { *out = e; return; }
+    if (e->kind_ == N_ELEMENTWISE) {
+        find_matmul_sum(a, out);
+        if (*out) return;
+    }
+    if (e->kind_ != N_ELEMENTWISE && e->kind_ != N_VIEW) return;
+    for (const Array& arg : e->arguments_) find_acc_through_views(arg, out);
+}
+
+// Elementwise roots of shape [m, n] that read a product of S * n columns only through its S column blocks
+// (i, f, o, g of an LSTM cell): ONE GEMM launch whose epilogue computes and stores every root; the product
+// itself is never written.  false = not that pattern (the caller goes on with the general path).
+bool try_sliced_gemm(const std::vector<const Array*>& roots) {
+    const Expression* acc = nullptr;
+    for (const Array* r : roots) find_acc_through_views(*r, &acc);
+    if (!acc || acc->dtype_ != DTYPE_FLOAT || roots[0]->ndim() != 2) return false;
+    GemmOperands g;
+    if (!gemm_operands(acc, &g)) return false;
+    const int64_t m = g.m, n = roots[0]->shape()[1];
+    if (roots[0]->shape()[0] != m || n <= 0 || g.n % n != 0) return false;
+    const int64_t slices = g.n / n;
+    if (slices != 2 && slices != 4) return false;
+    for (const Array* r : roots)
+        if (r->dtype() != DTYPE_FLOAT) return false;
+    const memory::Device device = roots[0]->preferred_device();
+    Lowerer L({m, n}, 0, device);
+    L.acc_node = acc;
+    L.slice_width = n;
+    std::vector<Array> dests;
+    for (const Array* r : roots) {
+        Array value(r->expression());
+        int v = L.visit(value, identity_map(2));
+        if (L.slice_fail || L.types[v] != DTYPE_FLOAT) return false;
+        Array dest(value.shape(), DTYPE_FLOAT, device);
+        int leaf = L.leaf_for(as<BufferView>(dest), identity_map(2), true, false, 0, 0, 0);
+        L.keep_alive.push_back(dest);
+        L.body.push_back("st " + std::to_string(leaf) + " assign v" + std::to_string(v));
+        dests.push_back(dest);
+    }
+    if ((int64_t)L.slices_seen.size() != slices) return false;       // every block of the product is used
+    for (const Leaf& leaf : L.leaves)
+        if (leaf.iota) return false;
+    if (!launch_gemm_program(L, g, m, n)) return false;
+    for (size_t i = 0; i < roots.size(); ++i) roots[i]->set_expression(dests[i].expression());
+    return true;
+}
+}  // namespace
+
 // Several lazy arrays of one shape in ONE kernel: what their trees share (the c' that h' = o * tanh(c')
 // is built from) is computed once and every root is stored.  The reference has no such call -- there each
 // eval() is a kernel of its own; anything this cannot fuse (reductions, products or scans at a root, differing
@@ -883,6 +993,7 @@ void eval_together(const std::vector<Array>& arrays) {
         for (const Array* a : roots) a->eval(false);
         return;
     }
+    if (try_sliced_gemm(roots)) return;
     const memory::Device device = roots[0]->preferred_device();
     std::vector<int64_t> space;
     for (int d : roots[0]->shape()) space.push_back(d);

@@ -409,9 +409,9 @@ def test_lstm_cell_outputs_evaluated_together(golden):
     before = lazy_stats()
     eval_together(c1, h1)
     after = lazy_stats()
-    assert after["kernels"] - before["kernels"] == 1
+    assert after["kernels"] - before["kernels"] == 0 and after["gemms"] - before["gemms"] == 1    # the gating is the GEMM's epilogue
     c2, h2 = cell()
-    np.testing.assert_array_equal(c1.numpy(), c2.numpy())
-    np.testing.assert_array_equal(h1.numpy(), h2.numpy())
+    np.testing.assert_allclose(c1.numpy(), c2.numpy(), rtol=1e-6, atol=1e-6)     # c2, h2: evaluated one by one, gates materialised
+    np.testing.assert_allclose(h1.numpy(), h2.numpy(), rtol=1e-6, atol=1e-6)
     np.testing.assert_allclose(c1.numpy(), golden["lstm/c_new"], rtol=1e-5, atol=1e-6)
     np.testing.assert_allclose(h1.numpy(), golden["lstm/h_new"], rtol=1e-5, atol=1e-6)
