@@ -32,10 +32,11 @@ struct GemmVariant {
     int esize;      // 2 bf16, 4 tf32
     int split;      // 3xTF32
     int bm, bn, bk, stages;
+    int ksplit = 0; // a cluster of two CTAs per tile, one operand pair each, partial sums exchanged through DSMEM
     int slices = 1; // the epilogue reads this many column slices of the product per output element
     int pair = 0;   // two CTAs (cta_group::2) share a 2*bm x bn tile, each staging half of the B tile
     bool b_kmajor() const { return split != 0; }   // the fp32 path transposes B while splitting it
-    bool ncat() const { return split != 0 && bn <= 64; }   // b_hi | b_lo read as one operand of 2 * bn columns
+    bool ncat() const { return split != 0 && (bn <= 64 || ksplit); }   // b_hi | b_lo read as one operand of 2 * bn columns
     unsigned idesc(int n_cols = 0) const {
         if (!n_cols) n_cols = bn;
         unsigned fmt = esize == 2 ? 1u : 2u;       // kind::f16: 1 = bf16; kind::tf32: 2 = tf32
@@ -52,13 +53,15 @@ struct GemmVariant {
     size_t stage_bytes() const {
         return (size_t)(split ? 2 : 1) * ((size_t)bm * bk * esize + (size_t)(bn / (pair ? 2 : 1)) * bk * esize);
     }
-    size_t smem_bytes() const { return stages * stage_bytes() + 1024; }
+    size_t xchg_bytes() const { return ksplit ? (size_t)bm * (bn / 2) * 4 : 0; }     // half a tile of fp32 partial sums
+    size_t smem_bytes() const { return stages * stage_bytes() + xchg_bytes() + 1024; }
     std::string key() const {
         std::ostringstream o;
         o << "gemm.e" << esize << ".s" << split << ".m" << bm << ".n" << bn << ".k" << bk << ".st" << stages;
         if (pair) o << ".pair";
         if (ncat()) o << ".ncat";
         if (slices > 1) o << ".sl" << slices;
+        if (ksplit) o << ".ksplit";
         return o.str();
     }
 };
@@ -226,14 +229,15 @@ bool gemm_source(void* ctx, std::string* src, std::string* err) {
     o << "#define GEMM_BM " << c->v.bm << "\n#define GEMM_BN " << c->v.bn << "\n#define GEMM_BK " << c->v.bk << "\n";
     o << "#define GEMM_STAGES " << c->v.stages << "\n#define GEMM_ESIZE " << c->v.esize << "\n#define GEMM_SPLIT " << c->v.split << "\n";
     o << "#define GEMM_IDESC " << c->v.idesc() << "u\n";
-    o << "#define GEMM_SLICES " << c->v.slices << "\n";
+    if (const char* e = std::getenv("DALI_B200_GEMM_EXPERIMENT")) o << "#define GEMM_EXPERIMENT " << std::atoi(e) << "\n";
+    o << "#define GEMM_SLICES " << c->v.slices << "\n#define GEMM_KSPLIT " << c->v.ksplit << "\n";
     o << "#define GEMM_NCAT " << (c->v.ncat() ? 1 : 0) << "\n#define GEMM_IDESC_WIDE " << c->v.idesc(2 * c->v.bn) << "u\n";
     o << "#define GEMM_B_KMAJOR " << (c->v.b_kmajor() ? 1 : 0) << "\n#define GEMM_PAIR " << c->v.pair << "\n";
     int words = 3 * (int)c->p->args.size() + (int)c->p->scalars.size();
     o << "#define GEMM_EPI_WORDS " << (words < 1 ? 1 : words) << "\n";
     // the io helpers need gemm:: conversions, which the skeleton defines: split the skeleton at its kernel
     std::string skel(kGemmSkeleton);
-    size_t cut = skel.find("extern \"C\" __global__");
+    size_t cut = skel.find("//@EPILOGUE@");
     o << skel.substr(0, cut) << kGemmIo << macro << skel.substr(cut);
     *src = o.str();
     return true;
@@ -347,11 +351,20 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
         const size_t budget = 200 * 1024;
         ctx.v.stages = (int)(budget / ctx.v.stage_bytes());
         if (ctx.v.stages > 8) ctx.v.stages = 8;
+        // two operand pairs and four slices (the LSTM cell): one CTA per pair on a 128-column tile, the halves meet
+        // through distributed shared memory -- each CTA pulls 2/3 of the operand bytes of the single-CTA form
+        const char* ks = std::getenv("DALI_B200_GEMM_KSPLIT");
+        if (n_pairs == 2 && slices == 4 && pairs[0].a_lo && !(ks && ks[0] == '0')) {
+            ctx.v.ksplit = 1;
+            ctx.v.bn = 128;
+            ctx.v.stages = 3;
+        }
     }
     const GemmVariant& v = ctx.v;
     const uint64_t b_cols = (uint64_t)n * (uint64_t)slices;      // columns of the product (rows of the transposed B)
     std::ostringstream key;
-    key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + "|sm_100a|gemm-10|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" +
+    if (const char* e = std::getenv("DALI_B200_GEMM_EXPERIMENT")) key << "x" << std::atoi(e) << "_";
+    key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + "|sm_100a|gemm-11|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" +
                                                      std::to_string(fnv1a(device_prelude())));
     tl_gemm_variant = std::string(bf16 ? "tcgen05.bf16 " : "tcgen05.tf32x3 ") + v.key() + (n_pairs > 1 ? " x2" : "");
     note_gemm_kernel(tl_gemm_variant);
@@ -407,9 +420,10 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
     if (total_tiles > 0x7fffffffull) { set_error("gemm_fused: too many output tiles"); return DALIB200_ERR_TOO_LARGE; }
     int sms = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device_ordinal(device)) != cudaSuccess || sms < 2) sms = 148;
-    uint64_t workers = (uint64_t)(v.pair ? sms / 2 : sms);
+    const bool cluster = v.pair || v.ksplit;       // two CTAs per worker
+    uint64_t workers = (uint64_t)(cluster ? sms / 2 : sms);
     if (workers > total_tiles) workers = total_tiles;
-    const unsigned gx = (unsigned)(workers * (v.pair ? 2 : 1)), gy = 1;
+    const unsigned gx = (unsigned)(workers * (cluster ? 2 : 1)), gy = 1;
     return launch_function(device, fn, gx, gy, 192, (unsigned)v.smem_bytes(), stream, params);
 }
 

@@ -23,6 +23,11 @@
 //                     element, the product's columns q*N + col for q < S (the four gates of an LSTM unit).  A tile
 //                     then covers GEMM_BN / S output columns; its B tile is one 3-D TMA copy of the
 //                     (transposed) operand seen as [slice][column][k], so accumulator column q * (GEMM_BN / S) + j is slice q of output j
+//   GEMM_KSPLIT       1 (with GEMM_SPLIT, GEMM_NCAT, GEMM_SLICES = 4, two operand pairs): a cluster of two CTAs
+//                     shares an output tile; CTA r accumulates operand pair r (x.Wx or h.Wh) over the whole
+//                     tile, the halves meet through distributed shared memory and each CTA finishes half of
+//                     the tile's columns.  Per CTA this halves the operand bytes pulled from L2, which is what
+//                     bounds the M = 256 products (separate kernel body: dali_gemm_kernel below)
 //   GEMM_IDESC        tcgen05 instruction descriptor
 // and a macro EPILOGUE_CHUNK(row, col0, acc, nvalid) generated from the
 // expression that consumes the product.
@@ -63,11 +68,16 @@ struct GemmP {
 #define GEMM_SLICES 1
 #endif
 #define GEMM_TILE_N (GEMM_BN / GEMM_SLICES)                  /* output columns of a tile */
-#define GEMM_CHUNK (GEMM_SLICES > 1 ? GEMM_TILE_N : 32)      /* output columns an epilogue call handles */
+#ifndef GEMM_KSPLIT
+#define GEMM_KSPLIT 0
+#endif
+/* output columns an epilogue call handles (with a K split each CTA of the pair finishes half of the tile's columns) */
+#define GEMM_CHUNK (GEMM_KSPLIT ? GEMM_TILE_N / 2 : GEMM_SLICES > 1 ? GEMM_TILE_N : 32)
 #define GEMM_RASTER 8u
 #ifndef GEMM_PAIR
 #define GEMM_PAIR 0
 #endif
+#define GEMM_CLUSTER (GEMM_PAIR || GEMM_KSPLIT)      /* the kernel runs as clusters of two CTAs */
 #if GEMM_PAIR
 #define GEMM_CG "2"
 #define GEMM_BN_LOCAL (GEMM_BN / 2)                          /* columns of B this CTA stages */
@@ -92,7 +102,10 @@ struct GemmP {
 #ifndef GEMM_NCAT
 #define GEMM_NCAT 0
 #endif
-#if GEMM_SPLIT && GEMM_NCAT
+#if GEMM_SPLIT && GEMM_NCAT && GEMM_KSPLIT
+#define GEMM_NACC 2                          /* 2 x (128 main + 128 correction columns) fill tensor memory */
+#define GEMM_ACC_SETS (2 * GEMM_NACC)
+#elif GEMM_SPLIT && GEMM_NCAT
 #define GEMM_NACC 3
 #define GEMM_ACC_SETS (2 * GEMM_NACC)        /* (main, correction) pairs side by side */
 #elif GEMM_SPLIT
@@ -137,6 +150,28 @@ DEV bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* abort
     }
 }
 
+#if GEMM_KSPLIT
+// the same with cluster scope: what the peer CTA wrote into this CTA's shared memory before it arrived is visible
+DEV bool mbar_test_cluster(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+DEV bool mbar_wait_cluster(unsigned long long* bar, unsigned parity, volatile int* abort_flag) {
+    if (mbar_test_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_test_cluster(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > 2000000000LL) return false;
+    }
+}
+#endif
+
 DEV void tma_load_2d(void* dst, const TensorMap* map, unsigned long long* bar, int x, int y) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -155,6 +190,8 @@ DEV void tma_load_2d_pair(void* dst, const TensorMap* map, unsigned bar_cluster,
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster), "r"(x), "r"(y) : "memory");
 }
+#endif
+#if GEMM_CLUSTER
 DEV unsigned cluster_ctarank() {
     unsigned r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -254,6 +291,202 @@ DEV unsigned pack_bf16x2(float lo, float hi) {
 DEV float bf16_to_f32(unsigned short b) { return __uint_as_float(((unsigned)b) << 16); }
 
 }  // namespace gemm
+
+//@EPILOGUE@  (the host side puts the chunk I/O helpers and the EPILOGUE_CHUNK macro here)
+
+#if GEMM_KSPLIT
+// ---------------------------------------------------------------------------------------------------
+// K split over a cluster of two CTAs (see GEMM_KSPLIT above).  Tile = GEMM_BM rows x GEMM_TILE_N output
+// columns x GEMM_SLICES slices; accumulator column q * GEMM_TILE_N + j is slice q of output column j.
+// CTA r finishes output columns [r * GEMM_CHUNK, (r + 1) * GEMM_CHUNK) of the tile (GEMM_CHUNK = GEMM_TILE_N / 2
+// here): it keeps its own partial sums for them, receives the peer's through `xchg` and sends the peer the
+// partial sums of the other half.  xchg[i][t] is the i-th float4 of row t: conflict-free on both sides.
+#define GEMM_XCHG_VEC (GEMM_SLICES * GEMM_CHUNK / 4)            /* float4 per row and direction */
+#define GEMM_XCHG_BYTES (GEMM_XCHG_VEC * GEMM_BM * 16)
+
+extern "C" __global__ void __launch_bounds__(GEMM_THREADS, 1) __cluster_dims__(2, 1, 1)
+dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ TensorMap tmB,
+                 const __grid_constant__ TensorMap tmAlo, const __grid_constant__ TensorMap tmBlo,
+                 const __grid_constant__ TensorMap tmA2, const __grid_constant__ TensorMap tmB2,
+                 const __grid_constant__ TensorMap tmA2lo, const __grid_constant__ TensorMap tmB2lo,
+                 const __grid_constant__ GemmP p) {
+    using namespace gemm;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<unsigned long long>(smem_raw) + 1023) & ~1023ull);
+    float4* xchg = reinterpret_cast<float4*>(tiles + (size_t)GEMM_STAGES * GEMM_STAGE_BYTES);
+    __shared__ __align__(8) unsigned long long full_bar[GEMM_STAGES];
+    __shared__ __align__(8) unsigned long long empty_bar[GEMM_STAGES];
+    __shared__ __align__(8) unsigned long long acc_full;      // MMA -> epilogue: this CTA's partial sums are complete
+    __shared__ __align__(8) unsigned long long acc_empty;     // epilogue -> MMA: they have been read
+    __shared__ __align__(8) unsigned long long xchg_full;     // the peer has written its half into this CTA's xchg
+    __shared__ __align__(8) unsigned long long xchg_free;     // the peer has read what this CTA wrote into the peer's xchg
+    __shared__ unsigned tmem_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned cta_rank = cluster_ctarank(), peer = cta_rank ^ 1u;
+    const unsigned worker = blockIdx.x >> 1, n_workers = gridDim.x >> 1;
+    const unsigned total_tiles = p.tiles_m * p.tiles_n;
+    // CTA r works on operand pair r over the whole tile
+    const TensorMap* mA = cta_rank ? &tmA2 : &tmA;
+    const TensorMap* mB = cta_rank ? &tmB2 : &tmB;
+    const TensorMap* mAlo = cta_rank ? &tmA2lo : &tmAlo;
+    const TensorMap* mBlo = cta_rank ? &tmB2lo : &tmBlo;
+    const int num_kb = (int)(((cta_rank ? p.K2 : p.K) + GEMM_BK - 1) / GEMM_BK);
+
+    auto tile_origin = [&](unsigned lin, long long* m0, long long* n0) {
+        const unsigned band = lin / (GEMM_RASTER * p.tiles_m);
+        const unsigned band_n0 = band * GEMM_RASTER;
+        const unsigned band_w = p.tiles_n - band_n0 < GEMM_RASTER ? p.tiles_n - band_n0 : GEMM_RASTER;
+        const unsigned in_band = lin - band * GEMM_RASTER * p.tiles_m;
+        *m0 = (long long)(in_band / band_w) * GEMM_BM;
+        *n0 = (long long)(band_n0 + in_band % band_w) * GEMM_TILE_N;
+    };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < GEMM_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(&acc_full, 1);
+        mbar_init(&acc_empty, 4);
+        mbar_init(&xchg_full, 128);      // every epilogue thread of the peer arrives after its stores
+        mbar_init(&xchg_free, 128);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) tmem_alloc(&tmem_slot, GEMM_TMEM_COLS);
+    fence_before_sync();
+    __syncthreads();
+    cluster_sync();      // the peer's barriers exist before anything is sent to them
+    fence_after_sync();
+    const unsigned tmem_base = tmem_slot;
+
+    if (warp == 4 && lane == 0) {
+        // ------------------------------------------------------------ TMA producer: a_hi, [b_hi | b_lo], a_lo
+        unsigned it = 0;
+        bool ok = true;
+        for (unsigned t = worker; t < total_tiles && ok; t += n_workers) {
+            long long m0, n0;
+            tile_origin(t, &m0, &n0);
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const unsigned s = it % GEMM_STAGES;
+                if (!mbar_wait(&empty_bar[s], ((it / GEMM_STAGES) & 1u) ^ 1u, &abort_flag)) { atomicExch(p.err, 1); abort_flag = 1; ok = false; break; }
+                unsigned char* st = tiles + (size_t)s * GEMM_STAGE_BYTES;
+                mbar_expect_tx(&full_bar[s], GEMM_STAGE_BYTES);
+                const int kx = kb * GEMM_BK;
+                tma_load_2d(st, mA, &full_bar[s], kx, (int)m0);
+                tma_load_3d(st + GEMM_A_TILE_BYTES, mB, &full_bar[s], kx, (int)n0, 0);
+                tma_load_3d(st + GEMM_A_TILE_BYTES + GEMM_B_TILE_BYTES, mBlo, &full_bar[s], kx, (int)n0, 0);
+                tma_load_2d(st + GEMM_A_TILE_BYTES + 2 * GEMM_B_TILE_BYTES, mAlo, &full_bar[s], kx, (int)m0);
+            }
+        }
+    } else if (warp == 5 && lane == 0) {
+        // ------------------------------------------------------------ MMA issuer (one per CTA, its own tensor core)
+        unsigned it = 0, done = 0;
+        bool ok = true;
+        for (unsigned t = worker; t < total_tiles && ok && num_kb > 0; t += n_workers, ++done) {
+            if (!mbar_wait(&acc_empty, (done & 1u) ^ 1u, &abort_flag)) { atomicExch(p.err, 5); abort_flag = 1; ok = false; break; }
+            fence_after_sync();
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const unsigned s = it % GEMM_STAGES;
+                if (!mbar_wait(&full_bar[s], (it / GEMM_STAGES) & 1u, &abort_flag)) { atomicExch(p.err, 2); abort_flag = 1; ok = false; break; }
+                fence_after_sync();
+                const unsigned a_addr = smem_u32(tiles + (size_t)s * GEMM_STAGE_BYTES);
+                const unsigned b_addr = a_addr + GEMM_A_TILE_BYTES;
+                const unsigned alo_addr = b_addr + 2 * GEMM_B_TILE_BYTES;
+#pragma unroll
+                for (int k = 0; k < GEMM_BK / GEMM_UMMA_K; ++k) {
+                    const unsigned long long ad = smem_desc(a_addr + k * 32, 0, 1024);
+                    const unsigned long long bd = smem_desc(b_addr + k * 32, 0, 1024);
+                    const unsigned long long ald = smem_desc(alo_addr + k * 32, 0, 1024);
+                    const unsigned pair0 = tmem_base + (unsigned)((kb % GEMM_NACC) * 2 * GEMM_BN);
+                    umma(pair0, ad, bd, GEMM_IDESC_WIDE, (kb >= GEMM_NACC || k > 0) ? 1u : 0u);     // a_hi.[b_hi | b_lo]
+                    umma(pair0 + GEMM_BN, ald, bd, GEMM_IDESC, 1u);                                 // a_lo.b_hi
+                }
+                umma_commit(&empty_bar[s]);
+            }
+            if (ok) umma_commit(&acc_full);
+        }
+    } else if (warp < 4) {
+        // ------------------------------------------------------------ exchange + epilogue
+        const int trow = warp * 32 + lane;                        // row of the tile = TMEM lane
+        const unsigned peer_xchg = map_to_cta(xchg, peer);
+        const unsigned peer_full = map_to_cta(&xchg_full, peer), peer_free = map_to_cta(&xchg_free, peer);
+        unsigned done = 0;
+        bool ok = true;
+        for (unsigned t = worker; t < total_tiles && ok; t += n_workers, ++done) {
+            long long m0, n0;
+            tile_origin(t, &m0, &n0);
+            if (num_kb > 0 && !mbar_wait(&acc_full, done & 1u, &abort_flag)) { if (lane == 0) atomicExch(p.err, 3); abort_flag = 1; ok = false; break; }
+            // the peer must have read what the previous tile left in its xchg
+            if (!mbar_wait_cluster(&xchg_free, (done & 1u) ^ 1u, &abort_flag)) { if (lane == 0) atomicExch(p.err, 6); abort_flag = 1; ok = false; break; }
+            fence_after_sync();
+            float mine[GEMM_SLICES * GEMM_CHUNK];                 // [slice][column of this CTA's half]
+#pragma unroll
+            for (int q = 0; q < GEMM_SLICES; ++q) {
+                // the GEMM_TILE_N (= 32) accumulator columns of slice q, summed over the accumulator sets
+                float v[32];
+                if (num_kb > 0) {
+                    const unsigned lane_base = tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)(q * GEMM_TILE_N);
+                    tmem_ld32(lane_base, v);
+                    const int used = num_kb < GEMM_NACC ? num_kb : GEMM_NACC;
+                    float part[32];
+                    for (int a = 1; a < 2 * used; ++a) {
+                        tmem_ld32(lane_base + (unsigned)(a * GEMM_BN), part);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] += part[i];
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+                }
+                // keep this CTA's half, send the other half to the peer
+#pragma unroll
+                for (int j = 0; j < GEMM_CHUNK; ++j) mine[q * GEMM_CHUNK + j] = cta_rank ? v[GEMM_CHUNK + j] : v[j];
+#pragma unroll
+                for (int g4 = 0; g4 < GEMM_CHUNK / 4; ++g4) {
+                    const int src = (cta_rank ? 0 : GEMM_CHUNK) + 4 * g4;
+                    const unsigned dst = peer_xchg + (unsigned)(((q * (GEMM_CHUNK / 4) + g4) * GEMM_BM + trow) * 16);
+                    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};"
+                                 ::"r"(dst), "f"(v[src]), "f"(v[src + 1]), "f"(v[src + 2]), "f"(v[src + 3]) : "memory");
+                }
+            }
+            if (num_kb > 0) {
+                // this warp has read its part of tensor memory: the MMA issuer may start the next tile
+                fence_before_sync();
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty)) : "memory");
+            }
+            // tell the peer its xchg holds this thread's share, then wait for the peer's share in ours
+            asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(peer_full) : "memory");
+            if (!mbar_wait_cluster(&xchg_full, done & 1u, &abort_flag)) { if (lane == 0) atomicExch(p.err, 7); abort_flag = 1; ok = false; break; }
+#pragma unroll
+            for (int i = 0; i < GEMM_XCHG_VEC; ++i) {
+                const float4 r = xchg[i * GEMM_BM + trow];
+                mine[4 * i] += r.x; mine[4 * i + 1] += r.y; mine[4 * i + 2] += r.z; mine[4 * i + 3] += r.w;
+            }
+            // our xchg may be overwritten for the next tile
+            asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(peer_free) : "memory");
+            const long long row = m0 + trow, col0 = n0 + (long long)cta_rank * GEMM_CHUNK;
+            if (row < p.M && col0 < p.N) {
+                const int nvalid = (p.N - col0) < GEMM_CHUNK ? (int)(p.N - col0) : GEMM_CHUNK;
+                EPILOGUE_CHUNK(row, col0, mine, nvalid)
+            }
+        }
+    }
+    // ---------------------------------------------------------------- teardown
+    fence_before_sync();
+    __syncthreads();
+    if (abort_flag) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) { }
+        __syncthreads();
+    }
+    cluster_sync();      // the peer may still be storing into this CTA's xchg or arriving on its barriers
+    if (warp == 5) {
+        fence_after_sync();
+        tmem_dealloc(tmem_base, GEMM_TMEM_COLS);
+    }
+}
+#else   // !GEMM_KSPLIT
 
 extern "C" __global__ void __launch_bounds__(GEMM_THREADS, 1)
 #if GEMM_PAIR
@@ -409,10 +642,16 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
                     // [main | correction] pair kb % GEMM_NACC: a_hi.[b_hi | b_lo] writes both halves (the first
                     // use overwrites), a_lo.b_hi adds into the correction half
                     const unsigned pair0 = acc0 + (unsigned)((kb % GEMM_NACC) * 2 * GEMM_BN);
-                    umma(pair0, ad, bd, GEMM_IDESC_WIDE, (kb >= GEMM_NACC || k > 0) ? 1u : 0u);
                     const unsigned alo_addr = b_addr + 2 * GEMM_B_TILE_BYTES;
                     const unsigned long long ald = smem_desc(alo_addr + k * 32, 0, 1024);
+#if defined(GEMM_EXPERIMENT) && GEMM_EXPERIMENT == 2
+                    if (kb < GEMM_NACC && k == 0) {       // loads only: just enough MMAs to define the accumulators
+#endif
+                    umma(pair0, ad, bd, GEMM_IDESC_WIDE, (kb >= GEMM_NACC || k > 0) ? 1u : 0u);
                     umma(pair0 + GEMM_BN, ald, bd, GEMM_IDESC, 1u);
+#if defined(GEMM_EXPERIMENT) && GEMM_EXPERIMENT == 2
+                    }
+#endif
 #elif GEMM_SPLIT
                     // main products: accumulator kb % GEMM_NACC (its first use overwrites)
                     umma(acc0 + (unsigned)((kb % GEMM_NACC) * GEMM_BN), ad, bd, GEMM_IDESC, (kb >= GEMM_NACC || k > 0) ? 1u : 0u);
@@ -548,3 +787,4 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
         tmem_dealloc(tmem_base, GEMM_TMEM_COLS);
     }
 }
+#endif  // GEMM_KSPLIT

@@ -135,11 +135,14 @@ def test_two_products_in_one_accumulator(lib, shape):
     np.testing.assert_allclose(got, host(two), rtol=1e-5, atol=1e-5 * float(bound.max()))
 
 
-@pytest.mark.parametrize("shape", [(64, 128), (256, 1024), (200, 72), (130, 40)])
-def test_lstm_gating_as_the_epilogue_of_the_gate_products(lib, shape):
+@pytest.mark.parametrize("ksplit", ["1", "0"])
+@pytest.mark.parametrize("shape", [(64, 128), (256, 1024), (200, 72), (130, 40), (384, 2048)])
+def test_lstm_gating_as_the_epilogue_of_the_gate_products(lib, shape, ksplit, monkeypatch):
     """The four gate slices of x.Wx + h.Wh meet in the epilogue (acc 0..3): c' and h' come out of the GEMM
     kernel, the [B,4H] gates matrix is never written.  Against the oracle's gating on fp64-accumulated gates;
-    ragged B and H (H not a multiple of the 16 units a tile covers)."""
+    ragged B and H (H not a multiple of the units a tile covers).  ksplit = 1: a cluster of two CTAs per tile, one
+    operand pair each, partial sums exchanged through distributed shared memory; 0: one CTA accumulates both pairs."""
+    monkeypatch.setenv("DALI_B200_GEMM_KSPLIT", ksplit)
     B, H = shape
     rng = np.random.default_rng(B + H)
     x, h, c = (rng.standard_normal((B, H)).astype(np.float32) for _ in range(3))
@@ -153,11 +156,15 @@ def test_lstm_gating_as_the_epilogue_of_the_gate_products(lib, shape):
                        offsets=[0, 0, 0, H, 2 * H, 3 * H, 0])
     got_c, got_h = host(c_new), host(h_new)
     assert lib.gemm_error_flag() == 0
-    assert ".sl4" in lib.last_gemm_kernel()
+    assert ".sl4" in lib.last_gemm_kernel() and lib.last_gemm_kernel().count(".ksplit") == int(ksplit)
     gates = (x.astype(np.float64) @ Wx + h.astype(np.float64) @ Wh + b).astype(np.float32)
     want_c, want_h = oracle.lstm_gating(gates, c)
-    np.testing.assert_allclose(got_c, want_c, rtol=1e-5, atol=1e-5)
-    np.testing.assert_allclose(got_h, want_h, rtol=1e-5, atol=1e-5)
+    # the gates carry the product's error, bounded by 1e-5 * (|x|.|Wx| + |h|.|Wh|) (measured: 40 times smaller); the
+    # gating has slope <= ~1.25 in every gate for |c| <= 5, so outputs are held to 2.5e-7 of that sum (1.3e-5 at
+    # B=256, H=1024) -- far below what a misplaced slice or a lost partial sum would cause (O(0.1))
+    bound = float((np.abs(x).astype(np.float64) @ np.abs(Wx) + np.abs(h).astype(np.float64) @ np.abs(Wh)).max())
+    np.testing.assert_allclose(got_c, want_c, rtol=1e-5, atol=2.5e-7 * bound + 1e-6)
+    np.testing.assert_allclose(got_h, want_h, rtol=1e-5, atol=2.5e-7 * bound + 1e-6)
 
 
 def test_two_bf16_products_in_one_accumulator(lib):
