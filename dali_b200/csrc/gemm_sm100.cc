@@ -424,7 +424,8 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
     uint64_t workers = (uint64_t)(cluster ? sms / 2 : sms);
     if (workers > total_tiles) workers = total_tiles;
     const unsigned gx = (unsigned)(workers * (cluster ? 2 : 1)), gy = 1;
-    return launch_function(device, fn, gx, gy, 192, (unsigned)v.smem_bytes(), stream, params);
+    // the kernel waits for its predecessor (griddepcontrol.wait) after its own set-up: barriers, tensor memory
+    return launch_function(device, fn, gx, gy, 192, (unsigned)v.smem_bytes(), stream, params, /*dependent=*/true);
 }
 
 }  // namespace dalib

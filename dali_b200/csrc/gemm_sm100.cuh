@@ -358,6 +358,11 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
     cluster_sync();      // the peer's barriers exist before anything is sent to them
     fence_after_sync();
     const unsigned tmem_base = tmem_slot;
+    // Launched as a programmatic dependent, everything above overlapped the tail of the kernel before this one in
+    // the stream; nothing below may run before that kernel has completed and its writes are visible.  The kernel
+    // after this one may begin its own set-up from here on (it waits the same way before it touches memory).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 4 && lane == 0) {
         // ------------------------------------------------------------ TMA producer: a_hi, [b_hi | b_lo], a_lo
@@ -547,6 +552,11 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
 #endif
     fence_after_sync();
     const unsigned tmem_base = tmem_slot;
+    // Launched as a programmatic dependent, everything above overlapped the tail of the kernel before this one in
+    // the stream; nothing below may run before that kernel has completed and its writes are visible.  The kernel
+    // after this one may begin its own set-up from here on (it waits the same way before it touches memory).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 4 && lane == 0) {
         // ------------------------------------------------------------ TMA producer

@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "runtime.h"
+
 namespace dalib {
 
 __global__ void __launch_bounds__(256)
@@ -36,6 +38,10 @@ struct SplitPair {
     float4* lo[2];
 };
 __global__ void __launch_bounds__(256) split_tf32_pair_kernel(const SplitPair p, long long rows, long long cols4) {
+    // launched as a programmatic dependent: wait for the kernel before this one, then let the GEMM that follows
+    // start setting itself up (it waits for this grid to complete before it reads hi / lo)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int w = blockIdx.y;
     const long long total = rows * cols4;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -111,8 +117,15 @@ cudaError_t split_tf32_pair(cudaStream_t stream, const float* x0, const float* x
     p.ld4[0] = ld0 / 4; p.ld4[1] = ld1 / 4;
     p.hi[0] = reinterpret_cast<float4*>(hi0); p.hi[1] = reinterpret_cast<float4*>(hi1);
     p.lo[0] = reinterpret_cast<float4*>(lo0); p.lo[1] = reinterpret_cast<float4*>(lo1);
-    split_tf32_pair_kernel<<<dim3((unsigned)blocks, 2), 256, 0, stream>>>(p, rows, cols / 4);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks, 2);
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    if (dependent_launch_enabled()) { cfg.attrs = &attr; cfg.numAttrs = 1; }
+    return cudaLaunchKernelEx(&cfg, split_tf32_pair_kernel, p, rows, cols / 4);
 }
 
 }  // namespace dalib

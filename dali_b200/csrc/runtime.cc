@@ -427,8 +427,16 @@ void count_launch() {
     ++s.n_launches;
 }
 
+bool dependent_launch_enabled() {
+    static const bool on = [] {
+        const char* e = std::getenv("DALI_B200_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 int launch_function(int device, void* function, unsigned gx, unsigned gy, unsigned threads, unsigned smem_bytes,
-                    void* stream, void** params) {
+                    void* stream, void** params, bool dependent) {
     int ord = device_ordinal(device);
     if (ord < 0) { set_error("device index out of range"); return DALIB200_ERR_INVALID; }
     CUDA_OK(cudaSetDevice(ord));
@@ -439,7 +447,26 @@ int launch_function(int device, void* function, unsigned gx, unsigned gy, unsign
         CUresult r = set_attr((CUfunction)function, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)smem_bytes);
         if (r != CUDA_SUCCESS) { set_error("cuFuncSetAttribute(max dynamic smem): " + cu_err(r)); return DALIB200_ERR_CUDA; }
     }
-    CUresult r = g_drv.LaunchKernel((CUfunction)function, gx, gy, 1, threads, 1, 1, smem_bytes, (CUstream)stream, params, nullptr);
+    typedef CUresult (*LaunchExFn)(const CUlaunchConfig*, CUfunction, void**, void**);
+    static LaunchExFn launch_ex = reinterpret_cast<LaunchExFn>(driver_entry("cuLaunchKernelEx"));
+    CUresult r;
+    if (dependent && launch_ex && dependent_launch_enabled()) {
+        CUlaunchAttribute attr;
+        std::memset(&attr, 0, sizeof attr);
+        attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+        attr.value.programmaticStreamSerializationAllowed = 1;
+        CUlaunchConfig cfg;
+        std::memset(&cfg, 0, sizeof cfg);
+        cfg.gridDimX = gx; cfg.gridDimY = gy; cfg.gridDimZ = 1;
+        cfg.blockDimX = threads; cfg.blockDimY = 1; cfg.blockDimZ = 1;
+        cfg.sharedMemBytes = smem_bytes;
+        cfg.hStream = (CUstream)stream;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        r = launch_ex(&cfg, (CUfunction)function, params, nullptr);
+    } else {
+        r = g_drv.LaunchKernel((CUfunction)function, gx, gy, 1, threads, 1, 1, smem_bytes, (CUstream)stream, params, nullptr);
+    }
     if (r != CUDA_SUCCESS) { set_error("cuLaunchKernel: " + cu_err(r)); return DALIB200_ERR_CUDA; }
     count_launch();
     return DALIB200_OK;

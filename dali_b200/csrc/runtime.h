@@ -64,8 +64,12 @@ typedef bool (*SourceFn)(void* ctx, std::string* source, std::string* err);
 int acquire_kernel(int device, const std::string& key, const char* entry_name, SourceFn make_source, void* ctx,
                    void** function, size_t* cubin_size);
 // cuLaunchKernel / cuFuncSetAttribute(max dynamic shared memory) on the bound device.
+// dependent = true: programmatic dependent launch -- the kernel may start while its predecessor in the stream
+// is still finishing and must itself execute griddepcontrol.wait before it touches global memory.
 int launch_function(int device, void* function, unsigned gx, unsigned gy, unsigned threads, unsigned smem_bytes,
-                    void* stream, void** params);
+                    void* stream, void** params, bool dependent = false);
+// DALI_B200_PDL != 0 (default on): kernels that are written for it are launched as programmatic dependents
+bool dependent_launch_enabled();
 // Driver entry point by name (nullptr if unavailable).
 void* driver_entry(const char* name);
 int device_ordinal(int device);            // CUDA ordinal of bound device, -1 if not bound
