@@ -229,7 +229,6 @@ bool gemm_source(void* ctx, std::string* src, std::string* err) {
     o << "#define GEMM_BM " << c->v.bm << "\n#define GEMM_BN " << c->v.bn << "\n#define GEMM_BK " << c->v.bk << "\n";
     o << "#define GEMM_STAGES " << c->v.stages << "\n#define GEMM_ESIZE " << c->v.esize << "\n#define GEMM_SPLIT " << c->v.split << "\n";
     o << "#define GEMM_IDESC " << c->v.idesc() << "u\n";
-    if (const char* e = std::getenv("DALI_B200_GEMM_EXPERIMENT")) o << "#define GEMM_EXPERIMENT " << std::atoi(e) << "\n";
     o << "#define GEMM_SLICES " << c->v.slices << "\n#define GEMM_KSPLIT " << c->v.ksplit << "\n";
     o << "#define GEMM_NCAT " << (c->v.ncat() ? 1 : 0) << "\n#define GEMM_IDESC_WIDE " << c->v.idesc(2 * c->v.bn) << "u\n";
     o << "#define GEMM_B_KMAJOR " << (c->v.b_kmajor() ? 1 : 0) << "\n#define GEMM_PAIR " << c->v.pair << "\n";
@@ -363,7 +362,6 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
     const GemmVariant& v = ctx.v;
     const uint64_t b_cols = (uint64_t)n * (uint64_t)slices;      // columns of the product (rows of the transposed B)
     std::ostringstream key;
-    if (const char* e = std::getenv("DALI_B200_GEMM_EXPERIMENT")) key << "x" << std::atoi(e) << "_";
     key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + "|sm_100a|gemm-11|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" +
                                                      std::to_string(fnv1a(device_prelude())));
     tl_gemm_variant = std::string(bf16 ? "tcgen05.bf16 " : "tcgen05.tf32x3 ") + v.key() + (n_pairs > 1 ? " x2" : "");

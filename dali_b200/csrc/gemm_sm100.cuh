@@ -654,14 +654,8 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
                     const unsigned pair0 = acc0 + (unsigned)((kb % GEMM_NACC) * 2 * GEMM_BN);
                     const unsigned alo_addr = b_addr + 2 * GEMM_B_TILE_BYTES;
                     const unsigned long long ald = smem_desc(alo_addr + k * 32, 0, 1024);
-#if defined(GEMM_EXPERIMENT) && GEMM_EXPERIMENT == 2
-                    if (kb < GEMM_NACC && k == 0) {       // loads only: just enough MMAs to define the accumulators
-#endif
                     umma(pair0, ad, bd, GEMM_IDESC_WIDE, (kb >= GEMM_NACC || k > 0) ? 1u : 0u);
                     umma(pair0 + GEMM_BN, ald, bd, GEMM_IDESC, 1u);
-#if defined(GEMM_EXPERIMENT) && GEMM_EXPERIMENT == 2
-                    }
-#endif
 #elif GEMM_SPLIT
                     // main products: accumulator kb % GEMM_NACC (its first use overwrites)
                     umma(acc0 + (unsigned)((kb % GEMM_NACC) * GEMM_BN), ad, bd, GEMM_IDESC, (kb >= GEMM_NACC || k > 0) ? 1u : 0u);
