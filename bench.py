@@ -363,7 +363,7 @@ class Lstm(Workload):
     """BASELINE config 2: fused LSTM cell step, fp32, B=256 H=1024 per GPU."""
     name = "lstm"
     B, H = 256, 1024
-    dominant_traffic_bytes = 73.6e6      # profiles/gemm_tcgen05_kernels.md: 71.4 MB read + 2.3 MB written per launch
+    dominant_traffic_bytes = 75.8e6      # profiles/gemm_tcgen05_kernels.md: 72.4 MB read + 3.4 MB written per launch
     dominant_traffic_note = "ncu capture with a cold L2 (64 MB of split weights read from DRAM); in the timed loop the weights stay in L2"
     e2e_api = "page-locked host arrays -> lazy Array/op:: expression -> eval -> host arrays (C++ front end through its C binding)"
 
