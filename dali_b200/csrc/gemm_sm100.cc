@@ -350,11 +350,16 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
         const size_t budget = 200 * 1024;
         ctx.v.stages = (int)(budget / ctx.v.stage_bytes());
         if (ctx.v.stages > 8) ctx.v.stages = 8;
-        // two operand pairs and four slices (the LSTM cell): one CTA per pair on a 128-column tile, the halves meet
-        // through distributed shared memory -- each CTA pulls 2/3 of the operand bytes of the single-CTA form
+    }
+    // Two pre-split fp32 operand pairs (the sum of two products: an LSTM's x.Wx + h.Wh), plain or with four slices:
+    // one CTA per pair on a 128-column tile, the halves meet through distributed shared memory -- each CTA pulls
+    // 2/3 of the operand bytes of the single-CTA form, and operand delivery is what bounds these products.
+    {
         const char* ks = std::getenv("DALI_B200_GEMM_KSPLIT");
-        if (n_pairs == 2 && slices == 4 && pairs[0].a_lo && !(ks && ks[0] == '0')) {
+        const int64_t b_total = (int64_t)n * slices;
+        if (!bf16 && n_pairs == 2 && (slices == 4 || slices == 1) && pairs[0].a_lo && b_total >= 128 && !(ks && ks[0] == '0')) {
             ctx.v.ksplit = 1;
+            ctx.v.slices = slices;
             ctx.v.bn = 128;
             ctx.v.stages = 3;
         }
@@ -362,7 +367,7 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
     const GemmVariant& v = ctx.v;
     const uint64_t b_cols = (uint64_t)n * (uint64_t)slices;      // columns of the product (rows of the transposed B)
     std::ostringstream key;
-    key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + "|sm_100a|gemm-11|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" +
+    key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + "|sm_100a|gemm-12|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" +
                                                      std::to_string(fnv1a(device_prelude())));
     tl_gemm_variant = std::string(bf16 ? "tcgen05.bf16 " : "tcgen05.tf32x3 ") + v.key() + (n_pairs > 1 ? " x2" : "");
     note_gemm_kernel(tl_gemm_variant);

@@ -23,7 +23,7 @@
 //                     element, the product's columns q*N + col for q < S (the four gates of an LSTM unit).  A tile
 //                     then covers GEMM_BN / S output columns; its B tile is one 3-D TMA copy of the
 //                     (transposed) operand seen as [slice][column][k], so accumulator column q * (GEMM_BN / S) + j is slice q of output j
-//   GEMM_KSPLIT       1 (with GEMM_SPLIT, GEMM_NCAT, GEMM_SLICES = 4, two operand pairs): a cluster of two CTAs
+//   GEMM_KSPLIT       1 (with GEMM_SPLIT, GEMM_NCAT, GEMM_BN = 128, GEMM_SLICES = 1 or 4, two operand pairs): a cluster of two CTAs
 //                     shares an output tile; CTA r accumulates operand pair r (x.Wx or h.Wh) over the whole
 //                     tile, the halves meet through distributed shared memory and each CTA finishes half of
 //                     the tile's columns.  Per CTA this halves the operand bytes pulled from L2, which is what
@@ -72,7 +72,7 @@ struct GemmP {
 #define GEMM_KSPLIT 0
 #endif
 /* output columns an epilogue call handles (with a K split each CTA of the pair finishes half of the tile's columns) */
-#define GEMM_CHUNK (GEMM_KSPLIT ? GEMM_TILE_N / 2 : GEMM_SLICES > 1 ? GEMM_TILE_N : 32)
+#define GEMM_CHUNK (GEMM_KSPLIT && GEMM_SLICES > 1 ? GEMM_TILE_N / 2 : GEMM_SLICES > 1 ? GEMM_TILE_N : 32)
 #define GEMM_RASTER 8u
 #ifndef GEMM_PAIR
 #define GEMM_PAIR 0
@@ -298,10 +298,12 @@ DEV float bf16_to_f32(unsigned short b) { return __uint_as_float(((unsigned)b) <
 // ---------------------------------------------------------------------------------------------------
 // K split over a cluster of two CTAs (see GEMM_KSPLIT above).  Tile = GEMM_BM rows x GEMM_TILE_N output
 // columns x GEMM_SLICES slices; accumulator column q * GEMM_TILE_N + j is slice q of output column j.
-// CTA r finishes output columns [r * GEMM_CHUNK, (r + 1) * GEMM_CHUNK) of the tile (GEMM_CHUNK = GEMM_TILE_N / 2
-// here): it keeps its own partial sums for them, receives the peer's through `xchg` and sends the peer the
-// partial sums of the other half.  xchg[i][t] is the i-th float4 of row t: conflict-free on both sides.
-#define GEMM_XCHG_VEC (GEMM_SLICES * GEMM_CHUNK / 4)            /* float4 per row and direction */
+// CTA r finishes output columns [r * GEMM_FIN, (r + 1) * GEMM_FIN) of the tile (of every slice): it keeps its own
+// partial sums for them, receives the peer's through `xchg` and sends the peer the partial sums of the other half.
+// xchg[i][t] is the i-th float4 of row t: conflict-free on both sides.  GEMM_BN is 128 here: with four slices a
+// 32-column accumulator group is one slice (16 columns each way), without slices two groups go each way.
+#define GEMM_FIN (GEMM_TILE_N / 2)                              /* output columns per slice this CTA finishes */
+#define GEMM_XCHG_VEC (GEMM_BN / 2 / 4)                         /* float4 per row and direction */
 #define GEMM_XCHG_BYTES (GEMM_XCHG_VEC * GEMM_BM * 16)
 
 extern "C" __global__ void __launch_bounds__(GEMM_THREADS, 1) __cluster_dims__(2, 1, 1)
@@ -378,8 +380,13 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
                 mbar_expect_tx(&full_bar[s], GEMM_STAGE_BYTES);
                 const int kx = kb * GEMM_BK;
                 tma_load_2d(st, mA, &full_bar[s], kx, (int)m0);
+#if GEMM_SLICES > 1
                 tma_load_3d(st + GEMM_A_TILE_BYTES, mB, &full_bar[s], kx, (int)n0, 0);
                 tma_load_3d(st + GEMM_A_TILE_BYTES + GEMM_B_TILE_BYTES, mBlo, &full_bar[s], kx, (int)n0, 0);
+#else
+                tma_load_2d(st + GEMM_A_TILE_BYTES, mB, &full_bar[s], kx, (int)n0);
+                tma_load_2d(st + GEMM_A_TILE_BYTES + GEMM_B_TILE_BYTES, mBlo, &full_bar[s], kx, (int)n0);
+#endif
                 tma_load_2d(st + GEMM_A_TILE_BYTES + 2 * GEMM_B_TILE_BYTES, mAlo, &full_bar[s], kx, (int)m0);
             }
         }
@@ -424,13 +431,13 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
             // the peer must have read what the previous tile left in its xchg
             if (!mbar_wait_cluster(&xchg_free, (done & 1u) ^ 1u, &abort_flag)) { if (lane == 0) atomicExch(p.err, 6); abort_flag = 1; ok = false; break; }
             fence_after_sync();
-            float mine[GEMM_SLICES * GEMM_CHUNK];                 // [slice][column of this CTA's half]
+            float mine[GEMM_BN / 2];                              // [slice][column of this CTA's half]
 #pragma unroll
-            for (int q = 0; q < GEMM_SLICES; ++q) {
-                // the GEMM_TILE_N (= 32) accumulator columns of slice q, summed over the accumulator sets
+            for (int q = 0; q < GEMM_BN / 32; ++q) {
+                // accumulator columns 32 q .. 32 q + 31, summed over the accumulator sets
                 float v[32];
                 if (num_kb > 0) {
-                    const unsigned lane_base = tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)(q * GEMM_TILE_N);
+                    const unsigned lane_base = tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)(q * 32);
                     tmem_ld32(lane_base, v);
                     const int used = num_kb < GEMM_NACC ? num_kb : GEMM_NACC;
                     float part[32];
@@ -443,16 +450,31 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = 0.0f;
                 }
-                // keep this CTA's half, send the other half to the peer
+#if GEMM_SLICES > 1
+                // the group is slice q (GEMM_TILE_N = 32): keep this CTA's 16 columns, send the other 16
 #pragma unroll
-                for (int j = 0; j < GEMM_CHUNK; ++j) mine[q * GEMM_CHUNK + j] = cta_rank ? v[GEMM_CHUNK + j] : v[j];
+                for (int j = 0; j < GEMM_FIN; ++j) mine[q * GEMM_FIN + j] = cta_rank ? v[GEMM_FIN + j] : v[j];
 #pragma unroll
-                for (int g4 = 0; g4 < GEMM_CHUNK / 4; ++g4) {
-                    const int src = (cta_rank ? 0 : GEMM_CHUNK) + 4 * g4;
-                    const unsigned dst = peer_xchg + (unsigned)(((q * (GEMM_CHUNK / 4) + g4) * GEMM_BM + trow) * 16);
+                for (int g4 = 0; g4 < GEMM_FIN / 4; ++g4) {
+                    const int src = (cta_rank ? 0 : GEMM_FIN) + 4 * g4;
+                    const unsigned dst = peer_xchg + (unsigned)(((q * (GEMM_FIN / 4) + g4) * GEMM_BM + trow) * 16);
                     asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};"
                                  ::"r"(dst), "f"(v[src]), "f"(v[src + 1]), "f"(v[src + 2]), "f"(v[src + 3]) : "memory");
                 }
+#else
+                // no slices: groups 0, 1 are CTA 0's columns, groups 2, 3 CTA 1's -- a group is kept or sent whole
+                if ((unsigned)(q >> 1) == cta_rank) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) mine[(q & 1) * 32 + j] = v[j];
+                } else {
+#pragma unroll
+                    for (int g4 = 0; g4 < 8; ++g4) {
+                        const unsigned dst = peer_xchg + (unsigned)((((q & 1) * 8 + g4) * GEMM_BM + trow) * 16);
+                        asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};"
+                                     ::"r"(dst), "f"(v[4 * g4]), "f"(v[4 * g4 + 1]), "f"(v[4 * g4 + 2]), "f"(v[4 * g4 + 3]) : "memory");
+                    }
+                }
+#endif
             }
             if (num_kb > 0) {
                 // this warp has read its part of tensor memory: the MMA issuer may start the next tile
@@ -470,10 +492,15 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
             }
             // our xchg may be overwritten for the next tile
             asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(peer_free) : "memory");
-            const long long row = m0 + trow, col0 = n0 + (long long)cta_rank * GEMM_CHUNK;
-            if (row < p.M && col0 < p.N) {
-                const int nvalid = (p.N - col0) < GEMM_CHUNK ? (int)(p.N - col0) : GEMM_CHUNK;
-                EPILOGUE_CHUNK(row, col0, mine, nvalid)
+            const long long row = m0 + trow;
+#pragma unroll 1
+            for (int sub = 0; sub < GEMM_FIN / GEMM_CHUNK; ++sub) {       // one call with slices, two 32-column calls without
+                const long long col0 = n0 + (long long)cta_rank * GEMM_FIN + sub * GEMM_CHUNK;
+                if (row < p.M && col0 < p.N) {
+                    const int nvalid = (p.N - col0) < GEMM_CHUNK ? (int)(p.N - col0) : GEMM_CHUNK;
+                    const float* acc_sub = mine + sub * GEMM_CHUNK;
+                    EPILOGUE_CHUNK(row, col0, acc_sub, nvalid)
+                }
             }
         }
     }
