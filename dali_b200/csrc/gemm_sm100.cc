@@ -327,9 +327,33 @@ struct GemmPair {
     int64_t lda, ldb;
 };
 
-int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n, const GemmPair* pairs, int n_pairs,
+int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n, const GemmPair* pairs_in, int n_pairs,
                       uint64_t epilogue_hash, void* const* array_data, const int64_t* offsets, const int64_t* const* strides,
                       int n_arrays, const void* const* scalars, int n_scalars, bool compile_only) {
+    // One pre-split fp32 product with few output tiles (small M): its K range becomes two operand pairs, so that the
+    // cluster form below applies -- the two halves of K on the two CTAs of a pair.  (Row-major K-major operands: the
+    // second half is the same matrix 16-byte aligned further along its rows.)
+    GemmPair halves[2];
+    const GemmPair* pairs = pairs_in;
+    {
+        const char* ks = std::getenv("DALI_B200_GEMM_KSPLIT");
+        const int64_t k = pairs_in[0].k;
+        const int64_t tiles128 = ((m + 127) / 128) * ((n + 127) / 128);
+        if (!bf16 && n_pairs == 1 && pairs_in[0].a_lo && pairs_in[0].b_lo && k >= 256 && k % 64 == 0 && n >= 128 &&
+            tiles128 < 120 && !(ks && ks[0] == '0')) {
+            const int64_t k1 = k / 2;
+            halves[0] = pairs_in[0];
+            halves[0].k = k1;
+            halves[1] = pairs_in[0];
+            halves[1].k = k - k1;
+            halves[1].a = (const float*)pairs_in[0].a + k1;
+            halves[1].a_lo = (const float*)pairs_in[0].a_lo + k1;
+            halves[1].b = (const float*)pairs_in[0].b + k1;
+            halves[1].b_lo = (const float*)pairs_in[0].b_lo + k1;
+            pairs = halves;
+            n_pairs = 2;
+        }
+    }
     Program prog;
     if (!find_program(epilogue_hash, &prog)) { set_error("unknown epilogue hash"); return DALIB200_ERR_NOT_FOUND; }
     if (n_arrays != (int)prog.args.size() || n_scalars != (int)prog.scalars.size()) {
