@@ -131,6 +131,7 @@ struct Gen {
         o << "struct P { long long w[" << L.total << "]; };\n";
         o << "#define NT " << v.threads << "\n#define VEC " << v.vec << "\n#define UNROLL " << v.unroll << "\n";
         o << "extern \"C\" __global__ void __launch_bounds__(NT) dali_kernel(const __grid_constant__ P p) {\n";
+        o << "  kernel_entry();\n";
         o << "  const i64 R = " << W(L.w_R) << "; const i64 C = " << W(L.w_C) << ";\n";
         o << "  const int tid = threadIdx.x;\n";
         for (size_t a = 0; a < p.args.size(); ++a) {

@@ -278,6 +278,15 @@ DEV void atomic_exch(float* p, float v) { atomicExch(p, v); }
 DEV void atomic_exch(int* p, int v) { atomicExch(p, v); }
 DEV void atomic_exch(double* p, double v) { atomicExch((unsigned long long*)p, (unsigned long long)__double_as_longlong(v)); }
 
+// First statement of every generated kernel.  Kernels are launched as programmatic dependents: their CTAs may
+// become resident while the kernel before them in the stream is still draining; nothing may touch global memory
+// before that kernel has completed (griddepcontrol.wait), and the kernel after this one is allowed to line up
+// the same way from here on.  Without the launch attribute both instructions do nothing.
+DEV void kernel_entry() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // 128-bit global access; callers guarantee 16-byte alignment.
 template <typename T, int N> struct alignas(sizeof(T) * N) Vec { T x[N]; };
 template <typename T, int N> DEV Vec<T, N> vload(const T* p) { return *reinterpret_cast<const Vec<T, N>*>(p); }

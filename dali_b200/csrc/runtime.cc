@@ -372,8 +372,27 @@ static int do_launch(uint64_t hash, int device, void* stream, const int64_t* spa
     }
     CUDA_OK(cudaSetDevice(s.devices[device].ordinal));
     void* params[] = {plan.words.data()};
-    CUresult r = g_drv.LaunchKernel(fn, plan.grid_x, plan.grid_y, 1, (unsigned)plan.variant.threads, 1, 1, 0,
-                                    (CUstream)stream, params, nullptr);
+    typedef CUresult (*LaunchExFn)(const CUlaunchConfig*, CUfunction, void**, void**);
+    static LaunchExFn launch_ex = reinterpret_cast<LaunchExFn>(driver_entry("cuLaunchKernelEx"));
+    CUresult r;
+    if (launch_ex && dependent_launch_enabled()) {
+        // programmatic dependent launch: every generated kernel begins with griddepcontrol.wait (prelude: kernel_entry)
+        CUlaunchAttribute attr;
+        std::memset(&attr, 0, sizeof attr);
+        attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+        attr.value.programmaticStreamSerializationAllowed = 1;
+        CUlaunchConfig cfg;
+        std::memset(&cfg, 0, sizeof cfg);
+        cfg.gridDimX = plan.grid_x; cfg.gridDimY = plan.grid_y; cfg.gridDimZ = 1;
+        cfg.blockDimX = (unsigned)plan.variant.threads; cfg.blockDimY = 1; cfg.blockDimZ = 1;
+        cfg.hStream = (CUstream)stream;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        r = launch_ex(&cfg, fn, params, nullptr);
+    } else {
+        r = g_drv.LaunchKernel(fn, plan.grid_x, plan.grid_y, 1, (unsigned)plan.variant.threads, 1, 1, 0, (CUstream)stream,
+                               params, nullptr);
+    }
     if (r != CUDA_SUCCESS) { set_error("cuLaunchKernel(" + tl_variant + "): " + cu_err(r)); return DALIB200_ERR_CUDA; }
     ++s.n_launches;
     return DALIB200_OK;
