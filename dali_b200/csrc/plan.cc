@@ -269,7 +269,7 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
         if (v.threads < T) v.threads = T;
         int rpc = v.threads / T;
         long long gx = (R + rpc - 1) / rpc;
-        out.grid_x = (unsigned)std::min<long long>(gx, (long long)kSMs * 32);
+        out.grid_x = (unsigned)std::min<long long>(gx, (long long)kSMs * env_int("DALI_B200_ROW_CTAS_PER_SM", 32));
         v.unroll = 1; v.tx = 0; v.ty = 0;
     } else if (v.kind == K_ALL) {
         v.threads = env_int("DALI_B200_ALL_THREADS", 256);
