@@ -772,9 +772,11 @@ void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) 
         View* v = static_cast<View*>(value.expression().get());
         bool pure = true;
         std::vector<int> used(v->ndim(), -1);
+        const std::vector<int>& arg_shape = v->arguments_[0].shape();
         for (size_t k = 0; k < v->dims_.size(); ++k) {
             const ViewDim& d = v->dims_[k];
-            if (d.src < 0 || d.off != 0 || d.step != 1 || used[d.src] >= 0) { pure = false; break; }
+            // a permutation / squeeze only: a slice that starts at 0 with step 1 but stops early is not one
+            if (d.src < 0 || d.off != 0 || d.step != 1 || used[d.src] >= 0 || v->shape_[d.src] != arg_shape[k]) { pure = false; break; }
             used[d.src] = (int)k;
         }
         for (int d = 0; pure && d < v->ndim(); ++d)

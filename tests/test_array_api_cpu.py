@@ -317,3 +317,14 @@ def test_two_equal_subtrees_keep_their_own_temporaries():
     assert launched(p) == {"kernels": 5, "gemms": 0, "temporaries": 4}
     ir = last_ir()
     assert ir.count("arg ") == 6 and ir.count(" ld ") == 5          # a, 2 maxima, 2 sums read; one result written
+
+
+def test_prefix_slice_of_a_lazy_value_is_not_a_pure_reindexing():
+    """b[:, 0:4] of a lazy [130, 9] value starts at 0 with step 1 but is narrower: it must be lowered as a slice,
+    not peeled off the root like a transpose."""
+    a = Array(np.zeros((130, 9), np.float32))
+    w = op.tanh(a)[:, 0:4]
+    assert w.shape == (130, 4)
+    assert launched(w) == {"kernels": 1, "gemms": 0, "temporaries": 0}
+    t = op.tanh(a).transpose()                      # a real permutation still is peeled: one kernel, transposed store
+    assert launched(t) == {"kernels": 1, "gemms": 0, "temporaries": 0}
