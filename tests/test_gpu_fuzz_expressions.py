@@ -126,3 +126,73 @@ def test_random_trees_before_evaluation(seed):
     w, wn = g.unary(r, rn)
     check(w.numpy(), wn, "stacked")
     check(a.numpy(), n, "root after its consumers")
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_index_work_is_bit_exact(seed):
+    """argmax / argmin (first occurrence on ties), gather, gather_from_rows, scatter-add through a gathered view,
+    integer running sums and one_hot on random int32 data: every answer equal to numpy's, bit for bit."""
+    from dali_b200.array import DTYPE_INT32
+    rng = np.random.default_rng(5000 + seed)
+    rows, cols = int(rng.integers(1, 70)), int(rng.integers(1, 300))
+    x = rng.integers(-5, 6, (rows, cols)).astype(np.int32)             # many ties
+    a = Array(x)
+    np.testing.assert_array_equal(op.argmax(a, 1).numpy(), x.argmax(1))
+    np.testing.assert_array_equal(op.argmin(a, 0).numpy(), x.argmin(0))
+    assert int(op.argmax(a).numpy()) == int(x.argmax())
+    np.testing.assert_array_equal(op.max(a, [0]).numpy(), x.max(0))
+    np.testing.assert_array_equal(op.sum(a, [1]).numpy(), x.sum(1, dtype=np.int32))
+    np.testing.assert_array_equal(op.cumsum(a).numpy(), np.cumsum(x, axis=1, dtype=np.int32))
+    idx = rng.integers(0, rows, (int(rng.integers(1, 50)),)).astype(np.int32)
+    np.testing.assert_array_equal(op.gather(a, Array(idx)).numpy(), x[idx])
+    np.testing.assert_array_equal(op.gather(a + 1, Array(idx)).numpy(), (x + 1)[idx])       # lazy source
+    ridx = rng.integers(0, cols, (rows,)).astype(np.int32)
+    np.testing.assert_array_equal(op.gather_from_rows(a, Array(ridx)).numpy(), x[np.arange(rows), ridx])
+    dest_np = rng.integers(-3, 4, (rows, cols)).astype(np.int32)
+    dest = Array(dest_np.copy())
+    g = dest[Array(idx)]
+    g += Array(x[idx])
+    g.eval()
+    want = dest_np.copy()
+    np.add.at(want, idx, x[idx])
+    np.testing.assert_array_equal(dest.numpy(), want)
+    depth = int(rng.integers(1, 12))
+    k = rng.integers(0, depth, (rows,)).astype(np.int32)
+    oh = op.one_hot(Array(k), depth, Array(3, DTYPE_INT32), Array(-1, DTYPE_INT32)).numpy()
+    np.testing.assert_array_equal(oh, np.where(np.arange(depth)[None, :] == k[:, None], 3, -1))
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_products_with_epilogues(seed):
+    """dot inside elementwise trees at random (often ragged) shapes: tensor-core path with the tree as epilogue where
+    the layout allows it, the general kernel otherwise; sums of two products; products of transposed views.
+    Against fp64 numpy within 1e-5 of |A|.|B| (plus the functors' 2e-5)."""
+    rng = np.random.default_rng(7000 + seed)
+    m, k, n = (int(rng.integers(1, 40)) * int(rng.choice([1, 4, 8])) for _ in range(3))
+    A = (rng.standard_normal((m, k)) * 0.5).astype(np.float32)
+    B = (rng.standard_normal((k, n)) * 0.5).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    res = rng.standard_normal((m, n)).astype(np.float32)
+    a, b = Array(A), Array(B)
+    A64, B64 = A.astype(np.float64), B.astype(np.float64)
+    bound = np.abs(A64) @ np.abs(B64)
+    tol = 1e-5 * bound + 2e-5
+
+    def close(got, want):
+        assert got.shape == want.shape
+        assert np.all(np.abs(got - want) <= tol + 2e-5 * np.abs(want)), float(np.max(np.abs(got - want)))
+
+    close(op.dot(a, b).numpy(), A64 @ B64)
+    close((op.dot(a, b) + Array(bias)[None, :]).numpy(), A64 @ B64 + bias)
+    close((Array(res) - op.dot(a, b) * Array(0.5, DTYPE_FLOAT)).numpy(), res - 0.5 * (A64 @ B64))
+    d = Array(res.copy())
+    d += op.dot(a, b)
+    close(d.numpy(), res + A64 @ B64)
+    close(op.dot(Array(np.ascontiguousarray(A.T)).transpose(), b).numpy(), A64 @ B64)        # transposed view as operand
+    k2 = int(rng.integers(1, 30)) * 4
+    A2 = (rng.standard_normal((m, k2)) * 0.5).astype(np.float32)
+    B2 = (rng.standard_normal((k2, n)) * 0.5).astype(np.float32)
+    two = op.tanh(op.dot(a, b) + op.dot(Array(A2), Array(B2)) + Array(bias)[None, :]).numpy()
+    want = np.tanh(A64 @ B64 + A2.astype(np.float64) @ B2.astype(np.float64) + bias)
+    bound2 = bound + np.abs(A2).astype(np.float64) @ np.abs(B2).astype(np.float64)
+    assert np.all(np.abs(two - want) <= 1e-5 * bound2 + 4e-5)
