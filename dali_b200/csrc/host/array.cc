@@ -59,7 +59,22 @@ Slice Slice::normalize_and_check(const Slice& s, int dim) {
                     std::to_string(dim));
     return r;
 }
+Slice::Slice(int start_, int end_, int step_) : has_start(true), has_end(true), start(start_), end(end_), step(step_) {
+    if ((start >= 0 && end >= 0) || (start < 0 && end < 0))
+        DALI_ASSERT(start < end, "Slice start (" + std::to_string(start) + ") must be less than end (" + std::to_string(end) + ")");
+    DALI_ASSERT(step != 0, "slice step cannot be zero");
+}
+
+bool Slice::contains(int index) const {
+    DALI_ASSERT(has_end, "can only compute size of slice if end index is specified.");
+    DALI_ASSERT(start >= 0 && end >= 0, "slice length can only be use with positive indexing.");
+    const bool in_range = start <= index && index < end;
+    const bool good_jump = step > 0 ? (index - start) % step == 0 : (end - 1 - index) % (-step) == 0;
+    return in_range && good_jump;
+}
+
 int Slice::size() const {
+    DALI_ASSERT(has_end, "can only compute size of slice if end index is specified.");
     int span = end - start;
     int st = step > 0 ? step : -step;
     return (span + st - 1) / st;

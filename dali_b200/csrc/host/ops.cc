@@ -496,6 +496,11 @@ Array bernoulli_normalized(Array prob, const std::vector<int>& shape) {
     return bernoulli(prob, shape) * eltinv(prob.dtype() == DTYPE_INT32 ? unsafe_cast(prob, DTYPE_DOUBLE) : prob);
 }
 
+Array control_dependency(Array condition, Array result) {
+    if (!condition.is_stateless() && !condition.is_buffer()) condition.eval(false);
+    return result;
+}
+
 // ---------------------------------------------------------------- assignment
 Array assign(const Array& left, OPERATOR_T op, const Array& right) {
     if (op == OPERATOR_T_LSE) return autoreduce_assign(left, right);

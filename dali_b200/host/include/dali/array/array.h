@@ -122,10 +122,13 @@ struct Slice {
     int start, end, step;
     Slice() : has_start(false), has_end(false), start(0), end(0), step(1) {}
     Slice(int end_) : has_start(false), has_end(true), start(0), end(end_), step(1) {}
-    Slice(int start_, int end_, int step_ = 1) : has_start(true), has_end(true), start(start_), end(end_), step(step_) {}
+    // start and end of one sign must be ordered, the step cannot be zero (dali/array/slice.cpp:25-38)
+    Slice(int start_, int end_, int step_ = 1);
     // resolves negative / missing bounds against a dimension size and checks the range
     static Slice normalize_and_check(const Slice&, int dim_size);
     int size() const;
+    // whether walking the slice visits `index` (a negative step walks [start, end) backwards; slice.cpp:79-92)
+    bool contains(int index) const;
 };
 
 class Expression;

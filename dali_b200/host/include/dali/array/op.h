@@ -141,6 +141,11 @@ Array normal(Array loc, Array scale, const std::vector<int>& shape);
 Array bernoulli(Array prob, const std::vector<int>& shape);
 Array bernoulli_normalized(Array prob, const std::vector<int>& shape);
 
+// expression/control_flow.h:33: `result`, evaluated no earlier than `condition`.  The reference threads a
+// ControlFlow node through views of pending assignments; here a pending assignment is run when something first looks
+// through it, so the dependency is discharged at once: `condition` is evaluated now and `result` returned as it is.
+Array control_dependency(Array condition, Array result);
+
 // ---- assignment
 Array assign(const Array& left, OPERATOR_T operator_t, const Array& right);
 Array autoreduce_assign(const Array& left, const Array& right);

@@ -182,6 +182,86 @@ static void lstm_cell() {
         }
 }
 
+// tests.cpp:372-468, 470-550: views of a [2,3,4] arange: shapes, offsets, strides, sums, in-place update of a strided view
+static Array build_234_arange() { return op::arange(24).reshape({2, 3, 4}); }
+static void views_of_an_arange() {
+    Array x = build_234_arange();
+    CHECK(x.contiguous_memory());
+    Array p0 = x.pluck_axis(0, 1);
+    CHECK(p0.shape() == std::vector<int>({3, 4}) && p0.number_of_elements() == 12 && p0.offset() == 12 && p0.strides().empty());
+    Array p1 = x.pluck_axis(1, 2);
+    CHECK(p1.shape() == std::vector<int>({2, 4}) && p1.offset() == 8 && p1.strides() == std::vector<int>({12, 1}));
+    Array p2 = x.pluck_axis(2, 1);
+    CHECK(p2.shape() == std::vector<int>({2, 3}) && p2.offset() == 1 && p2.strides() == std::vector<int>({12, 4}));
+    CHECK(x.memory().get() == p1.memory().get() && !p1.contiguous_memory());
+    CHECK((int)x.pluck_axis(0, 0).sum() == 66);
+    CHECK((int)p1.sum() == 8 + 9 + 10 + 11 + 20 + 21 + 22 + 23);
+    CHECK((int)p2.sum() == 1 + 5 + 9 + 13 + 17 + 21);
+    p2 += 1;                                                     // tests.cpp:517-530
+    CHECK((int)p2.sum() == 6 + 1 + 5 + 9 + 13 + 17 + 21);
+    CHECK((int)x[0][0][1] == 2 && (int)x[0][0][0] == 0);
+    Array y = build_234_arange();
+    Array sliced = y[Slice(0, -1)][2][Slice(0, 4, -2)];          // tests.cpp:548-553
+    CHECK((int)sliced.sum() == 20);
+    CHECK(Slice(0, 5).size() == 5 && Slice(0, 5, 2).size() == 3 && Slice(0, 5, -2).size() == 3 && Slice(0, 7, -3).size() == 3);
+    CHECK(Slice(0, 12, 2).contains(0) && !Slice(0, 12, 2).contains(1) && !Slice(0, 12, -2).contains(0) && Slice(0, 12, -2).contains(1));
+    CHECK_THROWS(Slice(0, 2, 0));
+    Array r({2, 3, 4}, DTYPE_INT32);                              // tests.cpp:424-434
+    CHECK(r.reshape({6, -1}).shape() == std::vector<int>({6, 4}) && r.reshape({-1, 2}).shape() == std::vector<int>({12, 2}));
+    CHECK_THROWS(r.reshape({-1, -1}));
+    CHECK_THROWS(r.reshape({-1, 5}));
+}
+
+// tests.cpp:555-585 in small: every (start, end, step) slice of every dim, sums against a host loop
+static void double_striding() {
+    Array x = op::uniform(Array(-1000), Array(1000), {2, 3, 4});
+    x.eval();
+    int host[24];
+    for (int i = 0; i < 24; ++i) host[i] = (int)x(i);
+    auto slices = [](int dim) {
+        std::vector<Slice> out;
+        for (int start = 0; start < dim; ++start)
+            for (int end = start + 1; end <= dim; ++end)
+                for (int step = -2; step < 3; ++step)
+                    if (step != 0) out.push_back(Slice(start, end, step));
+        return out;
+    };
+    int n = 0;
+    for (auto& s0 : slices(2))
+        for (auto& s1 : slices(3))
+            for (auto& s2 : slices(4)) {
+                if ((n++ % 7) != 0) continue;                     // every seventh combination: ~700 kernels otherwise
+                Array sliced = x[s0][s1][s2];
+                int want = 0;
+                for (int i = 0; i < 2; ++i)
+                    for (int j = 0; j < 3; ++j)
+                        for (int k = 0; k < 4; ++k)
+                            if (s0.contains(i) && s1.contains(j) && s2.contains(k)) want += host[i * 12 + j * 4 + k];
+                CHECK((int)sliced.sum() == want);
+            }
+}
+
+// tests.cpp:388-421: copies and references
+static void copies() {
+    Array original = op::arange(9).reshape({3, 3});
+    Array copy(original, true);
+    copy += 1;
+    for (int i = 0; i < 9; ++i) CHECK((int)original(i) != (int)copy(i));
+    Array original2 = op::arange(9).reshape({3, 3});
+    Array view(original2, false);
+    view += 2;
+    for (int i = 0; i < 9; ++i) CHECK((int)original2(i) == (int)view(i));
+}
+
+// expression/control_flow.h:33: a result that must see a pending in-place update
+static void control_dependency() {
+    Array x = Array::zeros({4}, DTYPE_INT32);
+    Array update = x;
+    update += 3;                                   // lazy: nothing has run yet
+    Array y = op::control_dependency(update, x) * 2;
+    for (int i = 0; i < 4; ++i) CHECK((int)y[i] == 6);
+}
+
 // tests.cpp:124-125, 438-440, 613: shape and rank violations surface as std::runtime_error
 static void errors() {
     Array a({3, 4}), b({4, 3});
@@ -202,6 +282,10 @@ int main() {
         one_hot();
         outer_and_scans();
         lstm_cell();
+        control_dependency();
+        views_of_an_arange();
+        double_striding();
+        copies();
         errors();
     } catch (const std::exception& e) {
         std::printf("EXCEPTION: %s\n", e.what());
