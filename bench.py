@@ -1022,7 +1022,7 @@ def main():
             torch.cuda.empty_cache()
             wl = build(name)
             wl.verify()
-            mo = measure(wl, torch, world, 10, 3, lib, False, local)
+            mo = measure(wl, torch, world, 24, 3, lib, False, local)      # 24: whole steps on each of the softmax lanes
             ro = roofline_of(wl, mo, lib)
             entry = {"workload": wl.describe()["workload"], "ms_per_step": mo["ms_per_step"],
                      "gbs": wl.bytes_per_step() / (mo["ms_per_step"] * 1e-3) / 1e9,
