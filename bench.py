@@ -3,9 +3,9 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
 One "step" is one pass of a fused expression over one batch of synthetic
-input.  Prints ONE JSON line (rank 0).  Workloads (BASELINE.json configs):
+input.  Prints ONE JSON line (rank 0).  Workloads (the benchmark configurations):
 
-  lstm     (default, BASELINE config 2) fused LSTM cell step, fp32 B=256 H=1024:
+  lstm     (default, configuration 2) fused LSTM cell step, fp32 B=256 H=1024:
            gates = dot(x,Wx)+dot(h,Wh)+b on the tensor cores (3xTF32, second GEMM
            with "+ first + b" as epilogue), then the fused sigmoid/tanh gating
   softmax  (config 1) exp(a - max(a,-1)) / sum(...) on fp32 [4096,1024]
@@ -168,7 +168,7 @@ class Workload:
 
 
 class Chain(Workload):
-    """BASELINE config 5: long elementwise chain + all-axis sum, strong-scaled over the ranks."""
+    """Benchmark configuration 5: long elementwise chain + all-axis sum, strong-scaled over the ranks."""
     name = "chain"
     TOTAL = 1 << 31
 
@@ -254,7 +254,7 @@ class Chain(Workload):
 
 
 class Softmax(Workload):
-    """BASELINE config 1: naive fused softmax on fp32 [4096,1024]."""
+    """Benchmark configuration 1: naive fused softmax on fp32 [4096,1024]."""
     name = "softmax"
     ROWS, COLS = 4096, 1024
 
@@ -360,7 +360,7 @@ class GraphStepper:
 
 
 class Lstm(Workload):
-    """BASELINE config 2: fused LSTM cell step, fp32, B=256 H=1024 per GPU."""
+    """Benchmark configuration 2: fused LSTM cell step, fp32, B=256 H=1024 per GPU."""
     name = "lstm"
     B, H = 256, 1024
     dominant_traffic_bytes = 75.8e6      # profiles/gemm_tcgen05_kernels.md: 72.4 MB read + 3.4 MB written per launch
@@ -500,7 +500,7 @@ class Lstm(Workload):
 
 
 class Gemm(Workload):
-    """BASELINE config 4: tanh(dot(A,B)+bias), bf16 8192^3, fp32 accumulate, bf16 out."""
+    """Benchmark configuration 4: tanh(dot(A,B)+bias), bf16 8192^3, fp32 accumulate, bf16 out."""
     name = "gemm"
     e2e_api = "C ABI with caller-managed copies (page-locked host -> device, dalib200_gemm_fused, device -> page-locked host, sync)"
     N = 8192
@@ -590,7 +590,7 @@ class Gemm(Workload):
 
 
 class ReduceAxis0(Workload):
-    """BASELINE config 3 (the strided case): sum over axis 0 of fp32 [8192,8192]."""
+    """Benchmark configuration 3 (the strided case): sum over axis 0 of fp32 [8192,8192]."""
     name = "reduce"
     N = 8192
 
@@ -662,7 +662,7 @@ class ReduceAxis0(Workload):
 
 
 class Cumsum(Workload):
-    """Running sum along the rows of fp32 [8192,8192] (op::cumsum; not one of the BASELINE configs: the first of
+    """Running sum along the rows of fp32 [8192,8192] (op::cumsum; not one of the five benchmark configurations: the first of
     the operators either side of the path, measured to the same bar)."""
     name = "scan"
     N = 8192

@@ -153,7 +153,7 @@ static void outer_and_scans() {
     CHECK((int)p[9] == 3628800);
 }
 
-// BASELINE config 2 in miniature: the LSTM cell written with op::, against plain loops
+// Benchmark configuration 2 in miniature: the LSTM cell written with op::, against plain loops
 static void lstm_cell() {
     const int B = 4, H = 8;
     utils::random::set_seed(7);

@@ -1,4 +1,4 @@
-"""BASELINE sizes through size-independent properties, through the C ABI: exact inputs (integer-valued
+"""The benchmark configurations at full size through size-independent properties, through the C ABI: exact inputs (integer-valued
 floats, whose partial sums are exact in fp32 whatever the order), a checksum of checksums, and
 sortedness of arg-reduction answers.  Small-size parity with the oracle is in the other GPU tests."""
 import numpy as np
