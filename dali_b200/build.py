@@ -103,9 +103,20 @@ def build_program(source, output):
     lib = build()
     inc = os.path.join(HERE, "host", "include")
     if _newer(output, [source, lib]):
-        _run(["g++", "-std=c++14", "-O1", "-I" + inc, source, "-o", output, "-L" + LIBDIR, "-ldali_b200",
+        _run(["g++", "-std=c++14", "-O1", "-I" + inc, "-I" + os.path.join(HERE, "..", "include"), source, "-o", output,
+              "-L" + LIBDIR, "-ldali_b200",
               "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + LIBDIR])
     return output
+
+
+def build_programs():
+    """The C++ programs of the package (dali_b200/host/programs): built next to the library."""
+    out = []
+    pdir = os.path.join(HERE, "host", "programs")
+    for f in sorted(os.listdir(pdir)):
+        if f.endswith(".cpp"):
+            out.append(build_program(os.path.join(pdir, f), os.path.join(LIBDIR, f[:-4])))
+    return out
 
 
 if __name__ == "__main__":

@@ -301,6 +301,40 @@ void Array::eval(bool wait) const {
     }
 }
 
+Array Array::borrow_host(void* buffer, const std::vector<int>& shape, DType dtype) {
+    int64_t n = 1;
+    for (int d : shape) n *= d;
+    auto mem = std::make_shared<memory::SynchronizedMemory>((size_t)n * size_of_dtype(dtype), shape.empty() ? 1 : shape.back());
+    mem->borrow_buffer(memory::Device::cpu(), buffer);
+    return Array(shape, mem, 0, std::vector<int>(), dtype);
+}
+
+void Array::to_host(void* out, bool wait) const {
+    Array c = ascontiguousarray();
+    c.eval(false);      // the copy below is ordered behind the kernels on the device's stream
+    const size_t bytes = (size_t)c.numel() * size_of_dtype(c.dtype());
+    BufferView* b = as<BufferView>(c);
+    const size_t skip = (size_t)b->offset_ * size_of_dtype(b->dtype_);
+    if (!b->memory_->is_fresh(memory::Device::cpu())) {
+        const int g = b->memory_->fresh_gpu();
+        if (g >= 0) {
+            const char* src = (const char*)b->memory_->readonly_data(memory::Device::gpu(g)) + skip;
+            lazy::check(dalib200_memcpy_d2h(g, out, src, bytes, nullptr), "dalib200_memcpy_d2h");
+            if (wait) lazy::check(dalib200_sync(g, nullptr), "dalib200_sync");
+            return;
+        }
+    }
+    std::memcpy(out, (const char*)b->memory_->readonly_data(memory::Device::cpu()) + skip, bytes);
+}
+
+void Array::eval_together(const std::vector<Array>& arrays, bool wait) {
+    lazy::eval_together(arrays);
+    if (wait && !arrays.empty() && !lazy::dry_run()) {
+        memory::Device d = arrays[0].preferred_device();
+        if (d.is_gpu()) lazy::check(dalib200_sync(lazy::device_index(d), nullptr), "dalib200_sync");
+    }
+}
+
 std::shared_ptr<memory::SynchronizedMemory> Array::memory() const {
     require_state(*this, "memory()");
     if (!is_buffer()) eval();

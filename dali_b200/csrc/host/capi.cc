@@ -70,26 +70,14 @@ int dali_array_from_host(const void* data, const int64_t* shape, int ndim, int d
 }
 
 int dali_array_borrow_host(void* data, const int64_t* shape, int ndim, int dtype, dali_array_t* out) {
-    return guard([&]() {
-        DType dt = to_dtype(dtype);
-        std::vector<int> s = to_shape(shape, ndim);
-        int64_t n = 1;
-        for (int d : s) n *= d;
-        auto mem = std::make_shared<memory::SynchronizedMemory>((size_t)n * size_of_dtype(dt), s.empty() ? 1 : s.back());
-        mem->borrow_buffer(memory::Device::cpu(), data);
-        *out = wrap(Array(s, mem, 0, std::vector<int>(), dt));
-    });
+    return guard([&]() { *out = wrap(Array::borrow_host(data, to_shape(shape, ndim), to_dtype(dtype))); });
 }
 
 int dali_array_eval_together(const dali_array_t* arrays, int n, int wait) {
     return guard([&]() {
         std::vector<Array> v;
         for (int i = 0; i < n; ++i) v.push_back(arrays[i]->a);
-        lazy::eval_together(v);
-        if (wait && n > 0 && !lazy::dry_run()) {
-            memory::Device d = v[0].preferred_device();
-            if (d.is_gpu()) lazy::check(dalib200_sync(lazy::device_index(d), nullptr), "dalib200_sync");
-        }
+        Array::eval_together(v, wait != 0);
     });
 }
 
@@ -146,25 +134,9 @@ int dali_array_eval(dali_array_t a, int wait) {
 
 int dali_array_to_host(dali_array_t a, void* out, size_t capacity) {
     return guard([&]() {
-        Array c = a->a.ascontiguousarray();
-        c.eval();
-        size_t bytes = (size_t)c.numel() * size_of_dtype(c.dtype());
+        size_t bytes = (size_t)a->a.numel() * size_of_dtype(a->a.dtype());
         DALI_ASSERT(capacity >= bytes, "dali_array_to_host: output buffer too small");
-        BufferView* b = as<BufferView>(c);
-        const size_t skip = (size_t)b->offset_ * size_of_dtype(b->dtype_);
-        if (!b->memory_->is_fresh(memory::Device::cpu())) {
-            // the value lives on a GPU only: copy straight into the caller's buffer (DMA when it is
-            // page-locked) instead of through a host copy of the whole allocation
-            const int g = b->memory_->fresh_gpu();
-            if (g >= 0) {
-                const char* src = (const char*)b->memory_->readonly_data(memory::Device::gpu(g)) + skip;
-                lazy::check(dalib200_memcpy_d2h(g, out, src, bytes, nullptr), "dalib200_memcpy_d2h");
-                lazy::check(dalib200_sync(g, nullptr), "dalib200_sync");
-                return;
-            }
-        }
-        const char* base = (const char*)b->memory_->readonly_data(memory::Device::cpu()) + skip;
-        std::memcpy(out, base, bytes);
+        a->a.to_host(out);
     });
 }
 

@@ -767,6 +767,21 @@ int dalib200_free(int device, void* ptr, size_t bytes) {
     return DALIB200_OK;
 }
 
+int dalib200_host_alloc(size_t bytes, void** out) {
+    if (!out) { set_error("null out pointer"); return DALIB200_ERR_INVALID; }
+    if (dalib200_device_count() <= 0) { set_error("page-locked memory needs a bound CUDA device"); return DALIB200_ERR_NO_DEVICE; }
+    void* p = nullptr;
+    CUDA_OK(cudaHostAlloc(&p, bytes ? bytes : 1, cudaHostAllocPortable));
+    *out = p;
+    return DALIB200_OK;
+}
+
+int dalib200_host_free(void* ptr) {
+    if (!ptr) return DALIB200_OK;
+    CUDA_OK(cudaFreeHost(ptr));
+    return DALIB200_OK;
+}
+
 int dalib200_pool_clear(int device) {
     DeviceRestore restore_device;
     State& s = S();

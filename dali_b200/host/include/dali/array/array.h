@@ -175,6 +175,17 @@ class Array {
     static Array adopt_buffer(void* buffer, const std::vector<int>& shape, DType dtype,
                               memory::Device buffer_location = memory::Device::cpu(), const std::vector<int>& strides = {});
     void disown_buffer(memory::Device buffer_location = memory::Device::cpu());
+    // Not in the reference.  Wraps HOST memory the caller keeps owning (never copied, never freed here; page-locked
+    // memory reaches the GPU by DMA); it must stay alive and unchanged until what reads it has been evaluated.
+    static Array borrow_host(void* buffer, const std::vector<int>& shape, DType dtype);
+    // Not in the reference.  Evaluates and copies the value, C-contiguous, into caller memory; a value that lives
+    // on a GPU only goes straight there (no intermediate host copy).  wait = false leaves a copy into page-locked
+    // memory in flight on the device's stream (several results, one synchronisation at the end).
+    void to_host(void* out, bool wait = true) const;
+    // Not in the reference.  Evaluates several lazy arrays of one shape in ONE kernel where their trees allow it
+    // (what they share is computed once; an LSTM cell's c' and h' become one GEMM launch whose epilogue is the
+    // gating), one after the other otherwise.
+    static void eval_together(const std::vector<Array>& arrays, bool wait = true);
 
     // Optimise, lower and launch whatever this Array lazily stands for; afterwards it is a
     // plain buffer.  wait = true also synchronises the device.

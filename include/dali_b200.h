@@ -275,6 +275,13 @@ int dalib200_scan(int device, void* stream, int dtype, int op, int inclusive,
 #define DALIB200_NOALLOC_MAX_ELEMENTS ((int64_t)1 << 31)
 int dalib200_sum_f32_noalloc(int device, void* stream, const float* x, int64_t n, float* out);
 
+/* ---- page-locked host memory -------------------------------------------------
+ * Host buffers the GPUs reach by DMA (cudaHostAlloc, portable across the bound devices): inputs handed over
+ * with dali_array_borrow_host and results read with dali_array_to_host move without a staging copy.  The
+ * reference stages every transfer through pageable memory (memory_ops.cu.cpp:77-118). */
+int dalib200_host_alloc(size_t bytes, void** out);
+int dalib200_host_free(void* ptr);
+
 /* ---- device memory ---------------------------------------------------------
  * Replaces memory::bank::allocate / deposit / clear
  * (dali/array/memory/memory_bank.cpp:41-81) and memory::copy / clear
