@@ -231,7 +231,30 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
     // ---------------------------------------------------------------- geometry
     long long aux0 = 0, aux1 = 0;
     const long long groups = (C + vec - 1) / vec;
-    if (v.kind == K_MAP) {
+    // MAP with a transposed operand: read-only, unit stride along the (single) outer dim, strided along the inner one
+    bool map_tiled = false;
+    if (v.kind == K_MAP && v.nout == 1 && v.nin == 1 && !p.has_indirect && R >= 32 && C >= 32 && env_int("DALI_B200_MAP_TILE", 1)) {
+        bool others_fit = true;
+        for (int a = 0; a < nargs; ++a) {
+            if (p.args[a].iota) continue;
+            const bool transposed = v.cls[a] == 's' && v.ocls[a] == 'u' && !p.args[a].written;
+            if (transposed) map_tiled = true;
+            else if (v.cls[a] == 's') others_fit = false;      // strided some other way: the tile would not help it
+        }
+        map_tiled = map_tiled && others_fit;
+    }
+    if (map_tiled) {
+        for (int a = 0; a < nargs; ++a)
+            if (!p.args[a].iota && v.cls[a] == 's' && v.ocls[a] == 'u' && !p.args[a].written) v.cls[a] = 't';
+        v.tile = 1;
+        v.vec = 1;
+        v.threads = 256;
+        v.unroll = 1;
+        out.grid_x = (unsigned)((C + 31) / 32);
+        out.grid_y = (unsigned)std::min<long long>((R + 31) / 32, 65535);
+        if ((C + 31) / 32 > 2147483647LL) { *err = "launch: inner extent too large"; return false; }
+        v.T = 0; v.vpt = 0; v.tx = 0; v.ty = 0;
+    } else if (v.kind == K_MAP) {
         v.threads = 256;
         v.unroll = groups >= 1024 ? 4 : 1;
         int TX = (int)std::min<long long>(256, pow2_ceil((groups + v.unroll - 1) / v.unroll));

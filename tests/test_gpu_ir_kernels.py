@@ -324,3 +324,34 @@ def test_errors_are_statuses_not_crashes(lib):
         lib.launch(h, (4, 4, 4), [0, 0])           # wrong rank
     with pytest.raises(DaliB200Error):
         lib.launch(0xdeadbeef, (4, 4), [0, 0])     # unknown hash
+
+
+@pytest.mark.parametrize("shape", [(32, 32), (33, 65), (100, 257), (1024, 512), (5, 4000), (4000, 7)])
+def test_map_with_transposed_operands_uses_shared_memory_tiles(lib, shape):
+    """out = tanh(a^T) + b + bias[col] with a stored column-major: the transposed operand goes through 32 x 32
+    shared-memory tiles (coalesced on both sides); same numbers as numpy, ragged edges included.  Below 32 rows or
+    columns the plain strided kernel takes over."""
+    R, C = shape
+    rng = np.random.default_rng(R * 31 + C)
+    at = rng.standard_normal((C, R)).astype(np.float32)        # a^T in memory: a[r, c] = at[c, r]
+    b = rng.standard_normal((R, C)).astype(np.float32)
+    bias = rng.standard_normal(C).astype(np.float32)
+    e = IRBuilder(2, 0)
+    O, A, B, Bi = e.arg("f32"), e.arg("f32"), e.arg("f32"), e.arg("f32")
+    e.st(O, e.op("add", e.op("add", e.op("tanh", e.ld(A)), e.ld(B)), e.ld(Bi)))
+    h = lib.compile(e.text())
+    out = torch.full((R, C), -7.0, device="cuda")
+    lib.launch(h, (R, C), [out, dev(at), dev(b), dev(bias)], strides=[None, [1, R], None, [0, 1]])
+    torch.cuda.synchronize()
+    assert (".tile" in lib.last_variant()) == (R >= 32 and C >= 32)
+    np.testing.assert_allclose(out.cpu().numpy(), np.tanh(at.T) + b + bias, rtol=1e-5, atol=1e-6)
+    # two transposed operands and an in-place destination
+    e2 = IRBuilder(2, 0)
+    D, A2, B2 = e2.arg("f32"), e2.arg("f32"), e2.arg("f32")
+    e2.st(D, e2.op("eltmul", e2.ld(A2), e2.ld(B2)), "add")
+    h2 = lib.compile(e2.text())
+    bt = rng.standard_normal((C, R)).astype(np.float32)
+    d = dev(b.copy())
+    lib.launch(h2, (R, C), [d, dev(at), dev(bt)], strides=[None, [1, R], [1, R]])
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(d.cpu().numpy(), b + at.T * bt.T, rtol=1e-6, atol=1e-6)
