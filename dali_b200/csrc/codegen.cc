@@ -21,7 +21,7 @@ std::string Variant::key() const {
     std::ostringstream s;
     s << kind_name() << ".o" << nout << ".i" << nin << ".v" << vec << ".nt" << threads << ".T" << T
       << ".p" << vpt << ".u" << unroll << ".x" << tx << ".y" << ty << "." << cls << "." << ocls;
-    if (tile) s << ".tile";
+    if (tile) s << ".tile" << tile;
     return s.str();
 }
 
@@ -455,7 +455,7 @@ struct Gen {
     }
 
     // ======================================================================= MAP
-    // MAP over 32 x 32 tiles for trees that read a transposed operand (class 't': its unit stride runs along the
+    // MAP over TS x TS tiles (TS = 32 or 64) for trees that read a transposed operand (class 't': its unit stride runs along the
     // outer dim).  The reference reads such views element by element with a stride (dali/array/jit/array_view.h
     // strided views); here the tile of every transposed operand is read along ITS contiguous direction into shared
     // memory and handed to the threads transposed, so both the reads and the writes are coalesced.
@@ -463,36 +463,41 @@ struct Gen {
         header();
         std::set<int> need = pass_needed(0, false, nullptr);
         std::set<int> largs = args_loaded_in(need, 0);
+        o << "#define TS " << v.tile << "\n";
         for (int a : largs)
-            if (v.cls[a] == 't') o << "  __shared__ " << argT(a) << " tile" << a << "[32][33];\n";
-        o << "  const int tx = tid & 31, ty = tid >> 5;      // 32 x 8 threads, four rows of the tile each\n";
-        o << "  const i64 c0 = (i64)blockIdx.x * 32;\n";
-        o << "  for (i64 r0 = (i64)blockIdx.y * 32; r0 < R; r0 += (i64)gridDim.y * 32) {\n";
+            if (v.cls[a] == 't') o << "  __shared__ " << argT(a) << " tile" << a << "[TS][TS + 1];\n";
+        o << "  const int tx = tid & 31, ty = tid >> 5;      // 32 x 8 threads, TS * TS / 256 elements of the tile each\n";
+        o << "  const i64 c0 = (i64)blockIdx.x * TS;\n";
+        o << "  for (i64 r0 = (i64)blockIdx.y * TS; r0 < R; r0 += (i64)gridDim.y * TS) {\n";
         for (int a : largs) {
             if (v.cls[a] != 't') continue;
-            o << "    _Pragma(\"unroll\") for (int k = 0; k < 4; ++k) {\n";
-            o << "      const i64 sc = c0 + ty + 8 * k, sr = r0 + tx;     // consecutive threads walk the outer dim\n";
-            o << "      tile" << a << "[ty + 8 * k][tx] = (sc < C && sr < R) ? a" << a << "[sr * " << W(L.arg_rs(a, 0)) << " + sc * "
+            o << "    _Pragma(\"unroll\") for (int k = 0; k < TS / 8; ++k)\n";
+            o << "      _Pragma(\"unroll\") for (int j = 0; j < TS / 32; ++j) {\n";
+            o << "        const i64 sc = c0 + ty + 8 * k, sr = r0 + tx + 32 * j;     // consecutive threads walk the outer dim\n";
+            o << "        tile" << a << "[ty + 8 * k][tx + 32 * j] = (sc < C && sr < R) ? a" << a << "[sr * " << W(L.arg_rs(a, 0)) << " + sc * "
               << W(L.arg_cs(a, 0, v.nout)) << "] : (" << argT(a) << ")0;\n";
-            o << "    }\n";
+            o << "      }\n";
         }
         o << "    __syncthreads();\n";
-        o << "    _Pragma(\"unroll\") for (int k = 0; k < 4; ++k) {\n";
-        o << "      const i64 r = r0 + ty + 8 * k, c = c0 + tx;\n";
-        o << "      if (r < R && c < C) {\n";
+        o << "    _Pragma(\"unroll\") for (int k = 0; k < TS / 8; ++k) {\n";
+        o << "      const i64 r = r0 + ty + 8 * k;\n";
+        o << "      if (r < R) {\n";
         row_offsets("        ", "r");
+        o << "        _Pragma(\"unroll\") for (int j = 0; j < TS / 32; ++j) {\n";
+        o << "          const i64 c = c0 + tx + 32 * j;\n";
+        o << "          if (c < C) {\n";
         for (int a : largs) {
-            o << "        Vec<" << argT(a) << ", VEC> q" << a << ";\n";
-            if (v.cls[a] == 't') o << "        q" << a << ".x[0] = tile" << a << "[tx][ty + 8 * k];\n";
-            else emit_arg_load("        ", a, "q" + std::to_string(a), "c", false);
+            o << "            Vec<" << argT(a) << ", VEC> q" << a << ";\n";
+            if (v.cls[a] == 't') o << "            q" << a << ".x[0] = tile" << a << "[tx + 32 * j][ty + 8 * k];\n";
+            else emit_arg_load("            ", a, "q" + std::to_string(a), "c", false);
         }
         GroupCtx g;
-        g.ind = "        ";
+        g.ind = "            ";
         g.c = "c";
         g.skip_loads = true;
         g.hoist_idx = "";
         emit_group(0, need, g);
-        o << "      }\n    }\n    __syncthreads();\n  }\n}\n";
+        o << "          }\n        }\n      }\n    }\n    __syncthreads();\n  }\n}\n";
         (void)err;
         return true;
     }

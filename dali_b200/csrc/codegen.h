@@ -42,7 +42,7 @@ struct Variant {
     int vpt = 0;             // row: vector groups per thread kept in registers (0 = streaming)
     int unroll = 4;          // map / all / col: independent groups in flight per thread
     int tx = 32, ty = 8;     // col: threads along outer / along the reduced dim
-    int tile = 0;            // map: 32 x 32 tiles, operands of class 't' are read through a shared-memory transpose
+    int tile = 0;            // map: edge of the square tiles (0, 32 or 64); operands of class 't' are read through a shared-memory transpose
     std::string cls;         // per arg inner-stride class: u(nit) z(ero) s(trided) t(ransposed: unit stride along the OUTER dim)
     std::string ocls;        // col: per arg outer-stride class
     std::string key() const; // text folded into the cache key

@@ -560,6 +560,19 @@ void find_reduce(const Array& a, bool through_view, FoundReduce* out) {
     }
 }
 
+// nothing but elementwise nodes, views and leaves below `a`
+bool only_elementwise(const Array& a) {
+    if (a.is_stateless()) return true;
+    Expression* e = a.expression().get();
+    switch (e->kind_) {
+        case N_BUFFER: case N_SCALAR: case N_IOTA: return true;
+        case N_ELEMENTWISE: case N_VIEW:
+            for (const Array& arg : e->arguments_) if (!only_elementwise(arg)) return false;
+            return true;
+        default: return false;
+    }
+}
+
 // dest (op)= left . right through the GEMM entry point of the C ABI (reference:
 // CublasGemmImpl::run, dali/array/gemm/cublas_gemm.cu:112-185, which ignores the
 // operator and always overwrites; here += and -= accumulate as
@@ -768,7 +781,10 @@ void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) 
     if (value.is_assignment()) value.eval(false);
 
     // ---- peel pure re-indexing views off the root: dest = view(x)  ->  inverse_view(dest) = x
-    while (value.expression()->kind_ == N_VIEW && dest.is_buffer()) {
+    // (x keeps its own iteration space, which its reductions / products need).  A tree of nothing but elementwise
+    // nodes and views is left alone: the view folds into its leaves' strides, the destination is written in its
+    // own order and transposed leaves are read through shared-memory tiles.
+    while (value.expression()->kind_ == N_VIEW && dest.is_buffer() && !only_elementwise(value.expression()->arguments_[0])) {
         View* v = static_cast<View*>(value.expression().get());
         bool pure = true;
         std::vector<int> used(v->ndim(), -1);

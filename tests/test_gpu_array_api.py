@@ -415,3 +415,24 @@ def test_lstm_cell_outputs_evaluated_together(golden):
     np.testing.assert_allclose(h1.numpy(), h2.numpy(), rtol=1e-6, atol=1e-6)
     np.testing.assert_allclose(c1.numpy(), golden["lstm/c_new"], rtol=1e-5, atol=1e-6)
     np.testing.assert_allclose(h1.numpy(), golden["lstm/h_new"], rtol=1e-5, atol=1e-6)
+
+
+# ---- a transposed elementwise tree is written in the destination's order (tests.cpp:560-640 transpose / dimshuffle) --
+def test_transposed_elementwise_tree_reads_through_tiles():
+    rng = np.random.default_rng(5)
+    a_np = rng.standard_normal((300, 520)).astype(np.float32)
+    b_np = rng.standard_normal((520, 300)).astype(np.float32)
+    a, b = Array(a_np), Array(b_np)
+    got = op.tanh(a).transpose()
+    assert launched(got) == {"kernels": 1, "gemms": 0, "temporaries": 0}
+    assert "tile" in last_variant()
+    np.testing.assert_allclose(got.numpy(), np.tanh(a_np).T, rtol=1e-5, atol=1e-6)
+    mixed = (op.sigmoid(a).transpose() * b + 1.0)
+    np.testing.assert_allclose(mixed.numpy(), (1 / (1 + np.exp(-a_np))).T * b_np + 1.0, rtol=1e-5, atol=1e-6)
+    # a reduction under the transpose keeps its own iteration space
+    s = op.sum(a, [1], True).transpose()
+    np.testing.assert_allclose(s.numpy(), a_np.sum(1, keepdims=True).T, rtol=1e-5, atol=1e-5)
+    # three dimensions: the swap of the two outer ones keeps unit stride inside
+    c_np = rng.standard_normal((5, 7, 64)).astype(np.float32)
+    got3 = op.exp(Array(c_np)).transpose([1, 0, 2])
+    np.testing.assert_allclose(got3.numpy(), np.exp(c_np).swapaxes(0, 1), rtol=1e-5, atol=1e-6)
