@@ -347,6 +347,17 @@ class _Op:
     def outer(self, a, b):
         return Array._new(_c().c.dali_op_outer, a._h, b._h)
 
+    def concatenate(self, arrays, axis=0):
+        arrays = [_wrap(a) for a in arrays]
+        hs = (_H * len(arrays))(*[a._h.value for a in arrays])
+        return Array._new(_c().c.dali_op_concatenate, hs, len(arrays), int(axis))
+
+    def hstack(self, arrays):
+        return self.concatenate(arrays, -1)
+
+    def vstack(self, arrays):
+        return self.concatenate(arrays, 0)
+
     def _random(self, kind, a, b, shape):
         a, b = _wrap(a), _wrap(b)
         return Array._new(_c().c.dali_op_random, kind.encode(), a._h, b._h, _shape_arg(shape), len(shape))

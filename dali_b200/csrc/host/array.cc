@@ -392,6 +392,19 @@ memory::Device device_promotion(const Array& a, const Array& b) {
 
 // ------------------------------------------------------------------ views
 // result[i...] = a[off_k + step_k * i_{src_k}] with the given output shape
+static Array make_view(const Array& a, const std::vector<int>& shape, const std::vector<ViewDim>& dims);
+
+// A view of a lazy value that is being written to: the value is evaluated into a buffer first -- its handle, and
+// every handle that shares its state, now names that buffer -- and the view is taken of the buffer (reference:
+// expression.cpp:48-56 turns the owner of any view into an assignment to a fresh buffer).
+Array lazy::writable_view(const Array& dest) {
+    if (dest.is_stateless() || dest.expression()->kind_ != N_VIEW) return dest;
+    View* v = static_cast<View*>(dest.expression().get());
+    Array base = v->arguments_[0];
+    base.eval(false);
+    return make_view(base, v->shape_, v->dims_);
+}
+
 static Array make_view(const Array& a, const std::vector<int>& shape, const std::vector<ViewDim>& dims) {
     require_state(a, "view");
     DALI_ASSERT((int)dims.size() == a.ndim(), "internal: view map rank mismatch");
@@ -771,23 +784,23 @@ void Array::print(std::basic_ostream<char>& stream, const int& indent, const boo
 }
 
 // minimal .npy (format 1.0) reader / writer for <f4 <f8 <i4
-Array Array::load(const std::string& fname) {
-    std::ifstream f(fname, std::ios::binary);
-    DALI_ASSERT(f.good(), "npy_load: Error! Unable to open file " + fname);
+namespace {
+// the .npy reader over any byte source: read(dst, n) returns the bytes it delivered
+template <typename Read>
+Array load_npy(Read read, const std::string& what) {
     char magic[10];
-    f.read(magic, 10);
-    DALI_ASSERT(f.good() && std::memcmp(magic, "\x93NUMPY", 6) == 0, "npy_load: " + fname + " is not a .npy file");
+    DALI_ASSERT(read(magic, 10) == 10 && std::memcmp(magic, "\x93NUMPY", 6) == 0, "npy_load: " + what + " is not a .npy file");
     size_t hlen = (unsigned char)magic[8] | ((unsigned char)magic[9] << 8);
     if (magic[6] >= 2) {
         char extra[2];
-        f.read(extra, 2);
+        DALI_ASSERT(read(extra, 2) == 2, "npy_load: truncated header in " + what);
         hlen |= ((size_t)(unsigned char)extra[0] << 16) | ((size_t)(unsigned char)extra[1] << 24);
     }
     std::string header(hlen, ' ');
-    f.read(&header[0], (std::streamsize)hlen);
+    DALI_ASSERT(read(&header[0], hlen) == hlen, "npy_load: truncated header in " + what);
     auto find_val = [&](const std::string& key) {
         size_t p = header.find(key);
-        DALI_ASSERT(p != std::string::npos, "npy_load: malformed header in " + fname);
+        DALI_ASSERT(p != std::string::npos, "npy_load: malformed header in " + what);
         return header.substr(header.find(':', p) + 1);
     };
     std::string descr = find_val("'descr'");
@@ -795,7 +808,7 @@ Array Array::load(const std::string& fname) {
     if (descr.find("f4") != std::string::npos) dtype = DTYPE_FLOAT;
     else if (descr.find("f8") != std::string::npos) dtype = DTYPE_DOUBLE;
     else if (descr.find("i4") != std::string::npos) dtype = DTYPE_INT32;
-    else throw std::runtime_error("can only load numpy arrays with dtype float, double or int32 (" + fname + ")");
+    else throw std::runtime_error("can only load numpy arrays with dtype float, double or int32 (" + what + ")");
     bool fortran = find_val("'fortran_order'").find("True") < 8;
     std::string shp = find_val("'shape'");
     shp = shp.substr(shp.find('(') + 1, shp.find(')') - shp.find('(') - 1);
@@ -809,17 +822,39 @@ Array Array::load(const std::string& fname) {
     }
     int64_t n = 1;
     for (int s : shape) n *= s;
-    void* buf = std::malloc((size_t)n * size_of_dtype(dtype) + 1);
-    f.read((char*)buf, (std::streamsize)(n * size_of_dtype(dtype)));
-    DALI_ASSERT(f.gcount() == (std::streamsize)(n * size_of_dtype(dtype)), "npy_load: truncated file " + fname);
+    const size_t bytes = (size_t)n * size_of_dtype(dtype);
+    void* buf = std::malloc(bytes + 1);
+    if (read((char*)buf, bytes) != bytes) {
+        std::free(buf);
+        throw std::runtime_error("npy_load: truncated file " + what);
+    }
     if (fortran) {
         std::vector<int> rs(shape.rbegin(), shape.rend());
         return Array::adopt_buffer(buf, rs, dtype).transpose();
     }
     return Array::adopt_buffer(buf, shape, dtype);
 }
+}  // namespace
 
-void Array::save(const std::string& fname, const Array& arr) {
+Array Array::load(const std::string& fname) {
+    std::ifstream f(fname, std::ios::binary);
+    DALI_ASSERT(f.good(), "npy_load: Error! Unable to open file " + fname);
+    return load_npy([&](char* dst, size_t n) { f.read(dst, (std::streamsize)n); return (size_t)f.gcount(); }, fname);
+}
+
+// reads one array from the current position of an open file (several arrays can follow one another)
+Array Array::load(FILE* fp) {
+    DALI_ASSERT(fp != nullptr, "npy_load: null FILE*");
+    return load_npy([&](char* dst, size_t n) { return std::fread(dst, 1, n, fp); }, "<FILE*>");
+}
+
+void Array::save(const std::string& fname, const Array& arr, const std::ios_base::openmode& mode) {
+    std::ofstream f(fname, std::ios::binary | mode);
+    DALI_ASSERT(f.good(), "cannot open " + fname + " for writing");
+    Array::save(f, arr);
+}
+
+void Array::save(std::basic_ostream<char>& f, const Array& arr) {
     Array c = arr.ascontiguousarray();
     c.eval();
     BufferView* b = as<BufferView>(c);
@@ -832,8 +867,6 @@ void Array::save(const std::string& fname, const Array& arr) {
     std::string header = h.str();
     while ((10 + header.size() + 1) % 64 != 0) header += ' ';
     header += '\n';
-    std::ofstream f(fname, std::ios::binary);
-    DALI_ASSERT(f.good(), "cannot open " + fname + " for writing");
     f.write("\x93NUMPY\x01\x00", 8);
     unsigned short len = (unsigned short)header.size();
     f.write((const char*)&len, 2);

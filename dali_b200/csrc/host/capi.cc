@@ -258,6 +258,13 @@ int dali_op_one_hot(dali_array_t indices, int depth, dali_array_t on_value, dali
 int dali_op_outer(dali_array_t a, dali_array_t b, dali_array_t* out) {
     return guard([&]() { *out = wrap(op::outer(a->a, b->a)); });
 }
+int dali_op_concatenate(const dali_array_t* arrays, int n, int axis, dali_array_t* out) {
+    return guard([&]() {
+        std::vector<Array> v;
+        for (int i = 0; i < n; ++i) v.push_back(arrays[i]->a);
+        *out = wrap(op::concatenate(v, axis));
+    });
+}
 int dali_op_scan(dali_array_t a, const char* reducer, int inclusive, dali_array_t* out) {
     return guard([&]() { *out = wrap(op::axis_scan(a->a, reducer, inclusive != 0)); });
 }

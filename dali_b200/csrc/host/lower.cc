@@ -779,6 +779,7 @@ void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) 
     Array value = value_in;
     if (dest.is_assignment()) dest.eval(false);
     if (value.is_assignment()) value.eval(false);
+    if (dest.expression()->kind_ == N_VIEW) dest = writable_view(dest);
 
     // ---- peel pure re-indexing views off the root: dest = view(x)  ->  inverse_view(dest) = x
     // (x keeps its own iteration space, which its reductions / products need).  A tree of nothing but elementwise

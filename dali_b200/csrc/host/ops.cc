@@ -501,6 +501,49 @@ Array control_dependency(Array condition, Array result) {
     return result;
 }
 
+// ---------------------------------------------------------------- concatenate
+// The pieces are written into consecutive slices of one new array (reference: dali/array/op/concatenate.cpp:10-73,
+// a ControlFlow node over one assignment per piece).  Here the assignments are evaluated together when the call is
+// made; dims of size 1 outside the axis broadcast to the common shape as in the reference.
+Array concatenate(const std::vector<Array>& arrays, int axis) {
+    DALI_ASSERT(!arrays.empty(), "concatenate must receive at least one array.");
+    if (arrays.size() == 1) return arrays[0];
+    const int ndim = arrays[0].ndim();
+    DALI_ASSERT(ndim > 0, "concatenate requires arrays with ndim > 0 (got " + arrays[0].expression_name() + ").");
+    if (axis < 0) axis += ndim;
+    DALI_ASSERT(axis >= 0 && axis < ndim, "concatenation axis must be >= 0 and < arrays[0].ndim = " + std::to_string(ndim) +
+                                              ", but got axis = " + std::to_string(axis) + ".");
+    std::vector<int> common = arrays[0].shape();
+    int total = 0;
+    for (const Array& a : arrays) {
+        DALI_ASSERT(a.ndim() == ndim, "all the input arrays must have the same dimensionality (expected ndim = " +
+                                          std::to_string(ndim) + ", got " + std::to_string(a.ndim()) + ").");
+        for (int d = 0; d < ndim; ++d) {
+            if (d == axis) continue;
+            if (common[d] == 1) common[d] = a.shape()[d];
+            DALI_ASSERT(common[d] == a.shape()[d] || a.shape()[d] == 1,
+                        "all the input array dimensions must match exactly outside of the concatenation axis, but got " +
+                            a.expression_name() + ".");
+        }
+        total += a.shape()[axis];
+    }
+    std::vector<int> out_shape = common;
+    out_shape[axis] = total;
+    Array result(out_shape, arrays[0].dtype(), arrays[0].preferred_device());
+    std::vector<Array> assignments;
+    int so_far = 0;
+    for (Array a : arrays) {
+        common[axis] = a.shape()[axis];
+        if (a.shape() != common) a = a.broadcast_to_shape(common);
+        assignments.push_back(op::assign(result.pluck_axis(axis, Slice(so_far, so_far + common[axis])), OPERATOR_T_EQL, a));
+        so_far += common[axis];
+    }
+    Array::eval_together(assignments, false);
+    return result;
+}
+Array hstack(const std::vector<Array>& arrays) { return concatenate(arrays, -1); }
+Array vstack(const std::vector<Array>& arrays) { return concatenate(arrays, 0); }
+
 // ---------------------------------------------------------------- assignment
 Array assign(const Array& left, OPERATOR_T op, const Array& right) {
     if (op == OPERATOR_T_LSE) return autoreduce_assign(left, right);

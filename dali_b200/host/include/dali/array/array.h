@@ -14,12 +14,17 @@
 #define DALI_ARRAY_ARRAY_H
 
 #include <cstdint>
+#include <cstdio>
 #include <initializer_list>
 #include <iostream>
 #include <memory>
 #include <stdexcept>
 #include <string>
 #include <vector>
+
+#include "dali/utils/assert2.h"
+#include "dali/utils/make_message.h"
+#include "dali/utils/print_utils.h"
 
 // ------------------------------------------------------------------ dtype
 enum DType { DTYPE_FLOAT = 0, DTYPE_DOUBLE = 1, DTYPE_INT32 = 2 };
@@ -192,7 +197,9 @@ class Array {
     void eval(bool wait = true) const;
 
     static Array load(const std::string& fname);                 // .npy
-    static void save(const std::string& fname, const Array& arr);
+    static Array load(FILE* fp);                                 // one array from the file's current position
+    static void save(const std::string& fname, const Array& arr, const std::ios_base::openmode& mode = std::ios_base::out);
+    static void save(std::basic_ostream<char>& stream, const Array& arr);
 
     static bool equals(const Array& left, const Array& right);
     static bool allclose(const Array& left, const Array& right, const double& atolerance);

@@ -127,6 +127,10 @@ Array diag(const Array& diag, int rows, int cols);
 Array one_hot(const Array& indices, int depth, const Array& on_value, const Array& off_value);
 // op/outer.h: out[i, j] = a.ravel()[i] * b.ravel()[j]
 Array outer(const Array& a, const Array& b);
+// op/concatenate.h: the arrays one after another along `axis` (negative counts from the back)
+Array concatenate(const std::vector<Array>& arrays, int axis = 0);
+Array hstack(const std::vector<Array>& arrays);      // axis -1
+Array vstack(const std::vector<Array>& arrays);      // axis 0
 // op/scan.h: running reduction over the last dim; exclusive results are one element longer
 Array axis_scan(const Array& a, const std::string& reducer_name, bool inclusive);
 Array cumsum(const Array& a, bool inclusive = true);

@@ -88,6 +88,8 @@ int dali_op_gather_from_rows(dali_array_t source, dali_array_t indices, dali_arr
 int dali_op_diag(dali_array_t diag, int rows, int cols, dali_array_t* out);
 int dali_op_one_hot(dali_array_t indices, int depth, dali_array_t on_value, dali_array_t off_value, dali_array_t* out);
 int dali_op_outer(dali_array_t a, dali_array_t b, dali_array_t* out);
+/* op/concatenate.h:7-9: the arrays one after another along `axis` (hstack = axis -1, vstack = axis 0) */
+int dali_op_concatenate(const dali_array_t* arrays, int n, int axis, dali_array_t* out);
 int dali_op_scan(dali_array_t a, const char* reducer, int inclusive, dali_array_t* out);
 int dali_op_arange(dali_array_t start, dali_array_t stop, dali_array_t step, dali_array_t* out);
 /* op/random.h: kind = uniform (a = low, b = high) | normal (a = loc, b = scale) | bernoulli | bernoulli_normalized

@@ -436,3 +436,21 @@ def test_transposed_elementwise_tree_reads_through_tiles():
     c_np = rng.standard_normal((5, 7, 64)).astype(np.float32)
     got3 = op.exp(Array(c_np)).transpose([1, 0, 2])
     np.testing.assert_allclose(got3.numpy(), np.exp(c_np).swapaxes(0, 1), rtol=1e-5, atol=1e-6)
+
+
+# ---- writing into a view of a lazy value evaluates the value into a buffer first (expression.cpp:48-56) ----
+def test_assigning_into_a_view_of_a_lazy_value_materialises_it():
+    rng = np.random.default_rng(6)
+    a_np = rng.standard_normal((4, 5)).astype(np.float32)
+    lazy = op.tanh(Array(a_np))          # not evaluated
+    alias = lazy                          # a second handle on the same state
+    lazy[1].assign(Array(7.0, DTYPE_FLOAT)).eval()
+    want = np.tanh(a_np)
+    want[1] = 7.0
+    np.testing.assert_allclose(lazy.numpy(), want, rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(alias.numpy(), want, rtol=1e-5, atol=1e-6)
+    col = lazy[:, 2]
+    col += 1.0
+    col.eval()
+    want[:, 2] += 1.0
+    np.testing.assert_allclose(lazy.numpy(), want, rtol=1e-5, atol=1e-6)

@@ -132,3 +132,31 @@ def test_float_cumsum_error_bound():
     assert np.all(np.abs(got - want) <= bound)
     ref = oracle.scan("sum", x, True)                    # the reference's own left-to-right fp32 order, same bound
     assert np.all(np.abs(ref - want) <= bound)
+
+
+# ---- op::concatenate / hstack / vstack (dali/array/op/concatenate.cpp:10-73; tests.cpp ConcatenateTests) ----
+def test_concatenate_along_every_axis_with_lazy_and_broadcast_pieces():
+    rng = np.random.default_rng(11)
+    a_np = rng.standard_normal((3, 4, 5)).astype(np.float32)
+    b_np = rng.standard_normal((3, 2, 5)).astype(np.float32)
+    c_np = rng.standard_normal((3, 1, 5)).astype(np.float32)
+    a, b, c = Array(a_np), Array(b_np), Array(c_np)
+    got = op.concatenate([a, op.tanh(b), c], 1)
+    np.testing.assert_allclose(got.numpy(), np.concatenate([a_np, np.tanh(b_np), c_np], 1), rtol=1e-5, atol=1e-6)
+    for axis in (0, 2, -1):
+        np.testing.assert_array_equal(op.concatenate([a, a], axis).numpy(), np.concatenate([a_np, a_np], axis))
+    m_np = rng.standard_normal((6, 7)).astype(np.float32)
+    m = Array(m_np)
+    np.testing.assert_array_equal(op.hstack([m, m[:, 0:3]]).numpy(), np.hstack([m_np, m_np[:, 0:3]]))
+    np.testing.assert_array_equal(op.vstack([m, m[::-1]]).numpy(), np.vstack([m_np, m_np[::-1]]))
+    # a dim of size 1 outside the axis broadcasts to the common shape
+    row = Array(m_np[0:1])
+    np.testing.assert_array_equal(op.hstack([m, row]).numpy(), np.hstack([m_np, np.broadcast_to(m_np[0:1], (6, 7))]))
+    ints = Array(np.arange(6, dtype=np.int32))
+    np.testing.assert_array_equal(op.concatenate([ints, ints + 6]).numpy(), np.arange(12, dtype=np.int32))
+    with pytest.raises(RuntimeError):
+        op.concatenate([a, m], 0)
+    with pytest.raises(RuntimeError):
+        op.concatenate([a, a], 3)
+    with pytest.raises(RuntimeError):
+        op.concatenate([], 0)
