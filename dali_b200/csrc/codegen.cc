@@ -459,7 +459,46 @@ struct Gen {
     // outer dim).  The reference reads such views element by element with a stride (dali/array/jit/array_view.h
     // strided views); here the tile of every transposed operand is read along ITS contiguous direction into shared
     // memory and handed to the threads transposed, so both the reads and the writes are coalesced.
+    // The same trees when everything is 4 bytes wide and 16-byte aligned (tile = 4): no shared memory.  A thread owns a
+    // 4 x 4 block: four 128-bit loads of a transposed operand along ITS contiguous direction, the transpose happens
+    // in registers, four 128-bit stores along the destination's.  A warp is 8 threads along the rows x 4 along the
+    // columns, so it reads four full 128-byte lines per load and writes eight 64-byte segments per store.
+    bool gen_map_micro(std::string* err) {
+        header();
+        std::set<int> need = pass_needed(0, false, nullptr);
+        std::set<int> largs = args_loaded_in(need, 0);
+        o << "  const int lane = tid & 31, warp = tid >> 5;\n";
+        o << "  const i64 c = ((i64)blockIdx.x * 32 + warp * 4 + (lane >> 3)) * 4;     // 128 columns per CTA\n";
+        o << "  for (i64 rb = ((i64)blockIdx.y * 8 + (lane & 7)) * 4; rb < R; rb += (i64)gridDim.y * 32) {\n";
+        o << "    if (c < C) {\n";
+        for (int a : largs) {
+            if (v.cls[a] != 't') continue;
+            o << "      Vec<" << argT(a) << ", 4> t" << a << "_[4];\n";
+            o << "      _Pragma(\"unroll\") for (int j = 0; j < 4; ++j) t" << a << "_[j] = vload<" << argT(a) << ", 4>(a" << a
+              << " + rb * " << W(L.arg_rs(a, 0)) << " + (c + j) * " << W(L.arg_cs(a, 0, v.nout)) << ");\n";
+        }
+        o << "      _Pragma(\"unroll\") for (int i = 0; i < 4; ++i) {\n";
+        o << "        const i64 r = rb + i;\n";
+        row_offsets("        ", "r");
+        for (int a : largs) {
+            o << "        Vec<" << argT(a) << ", VEC> q" << a << ";\n";
+            if (v.cls[a] == 't')
+                o << "        _Pragma(\"unroll\") for (int j = 0; j < 4; ++j) q" << a << ".x[j] = t" << a << "_[j].x[i];\n";
+            else emit_arg_load("        ", a, "q" + std::to_string(a), "c", false);
+        }
+        GroupCtx g;
+        g.ind = "        ";
+        g.c = "c";
+        g.skip_loads = true;
+        g.hoist_idx = "";
+        emit_group(0, need, g);
+        o << "      }\n    }\n  }\n}\n";
+        (void)err;
+        return true;
+    }
+
     bool gen_map_tiled(std::string* err) {
+        if (v.tile == 4) return gen_map_micro(err);
         header();
         std::set<int> need = pass_needed(0, false, nullptr);
         std::set<int> largs = args_loaded_in(need, 0);

@@ -232,10 +232,14 @@ Array Array::adopt_buffer(void* buffer, const std::vector<int>& shape, DType dty
 void Array::disown_buffer(memory::Device loc) { memory()->disown_buffer(loc); }
 
 // ------------------------------------------------------------------ state
+Array::ArrayState::ArrayState(expression_ptr e) : expression_(e) {
+    if (e) shape_ = e->shape_;
+}
 expression_ptr Array::expression() const { return state_ ? state_->expression_ : nullptr; }
 void Array::set_expression(expression_ptr e) const {
-    if (!state_) state_ = std::make_shared<ArrayState>(e);
-    else state_->expression_ = e;
+    if (!state_) { state_ = std::make_shared<ArrayState>(e); return; }
+    state_->expression_ = e;
+    if (e && state_->shape_ != e->shape_) state_->shape_ = e->shape_;   // untouched (references stay valid) when equal
 }
 std::string Array::expression_name() const { return is_stateless() ? "" : expression()->name(); }
 std::string Array::full_expression_name() const { return is_stateless() ? "" : expression()->full_name(); }
@@ -256,7 +260,7 @@ bool Array::is_assignable() const {
 static void require_state(const Array& a, const char* what) {
     DALI_ASSERT(!a.is_stateless(), std::string(what) + " called on a stateless Array");
 }
-const std::vector<int>& Array::shape() const { require_state(*this, "shape()"); return expression()->shape_; }
+const std::vector<int>& Array::shape() const { require_state(*this, "shape()"); return state_->shape_; }
 DType Array::dtype() const { require_state(*this, "dtype()"); return expression()->dtype_; }
 int Array::ndim() const { return is_stateless() ? 0 : expression()->ndim(); }
 int64_t Array::numel() const { return is_stateless() ? 0 : expression()->numel(); }

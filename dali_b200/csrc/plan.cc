@@ -253,13 +253,29 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
             if (v.cls[a] == 't') tile_bytes += 64 * 65 * dtype_size(p.args[a].dtype);
         int ts = 32;
         if (env_int("DALI_B200_MAP_TILE", 1) == 64 && tile_bytes <= 40 * 1024) ts = 64;
-        v.tile = ts;
-        v.vec = 1;
+        // 4 x 4 register blocks when every operand is 4 bytes wide and 16-byte aligned along its contiguous direction
+        bool micro = R % 4 == 0 && C % 4 == 0 && env_int("DALI_B200_MAP_TILE", 1) == 1;
+        for (int a = 0; a < nargs && micro; ++a) {
+            if (p.args[a].iota) continue;
+            if (dtype_size(p.args[a].dtype) != 4) micro = false;
+            else if (v.cls[a] == 't') micro = ((uintptr_t)ptr[a]) % 16 == 0 && inner[0].stride[a] % 4 == 0;
+            else if (v.cls[a] == 'u') micro = aligned(a, 4, false);
+            else if (v.cls[a] != 'z') micro = false;
+        }
         v.threads = 256;
         v.unroll = 1;
-        out.grid_x = (unsigned)((C + ts - 1) / ts);
-        out.grid_y = (unsigned)std::min<long long>((R + ts - 1) / ts, 65535);
-        if ((C + ts - 1) / ts > 2147483647LL) { *err = "launch: inner extent too large"; return false; }
+        if (micro) {
+            v.tile = 4;
+            v.vec = 4;
+            out.grid_x = (unsigned)((C + 127) / 128);
+            out.grid_y = (unsigned)std::min<long long>((R + 31) / 32, 65535);
+        } else {
+            v.tile = ts;
+            v.vec = 1;
+            out.grid_x = (unsigned)((C + ts - 1) / ts);
+            out.grid_y = (unsigned)std::min<long long>((R + ts - 1) / ts, 65535);
+        }
+        if ((C + 31) / 32 > 2147483647LL) { *err = "launch: inner extent too large"; return false; }
         v.T = 0; v.vpt = 0; v.tx = 0; v.ty = 0;
     } else if (v.kind == K_MAP) {
         v.threads = 256;

@@ -143,9 +143,13 @@ template <typename Container> struct SlicingInProgress;
 // ------------------------------------------------------------------ Array
 class Array {
   public:
+    // shape_ is the state's own copy of the expression's shape: shape() hands out a reference to it, which stays
+    // valid when the expression is replaced by its evaluated buffer (callers of the reference hold such references
+    // across calls that evaluate the array, e.g. dali/array/gemm/tensordot_as_dot.h:82-103)
     struct ArrayState {
         mutable expression_ptr expression_;
-        explicit ArrayState(expression_ptr e) : expression_(e) {}
+        mutable std::vector<int> shape_;
+        explicit ArrayState(expression_ptr e);
     };
   private:
     mutable std::shared_ptr<ArrayState> state_;

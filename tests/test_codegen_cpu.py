@@ -146,3 +146,22 @@ def test_disk_cache_and_recompile_counters(L, tmp_path):
     L.cache_clear(False)
     L.precompile(h, (128, 128), 2)
     assert L.cache_stats()["compilations"] == after["compilations"] + 1
+
+
+def test_transposed_operands_pick_a_tiled_map_variant(L):
+    """A read-only operand whose unit stride runs along the outer dim: 4 x 4 register blocks when everything is
+    16-byte aligned, shared-memory tiles when the extents are ragged, the plain strided kernel for thin shapes.
+    Planning compiles the variant with NVRTC, so this also checks that each one builds."""
+    from dali_b200.ir import IRBuilder
+    e = IRBuilder(2, 0)
+    O, A, B = e.arg("f32"), e.arg("f32"), e.arg("f32")
+    e.st(O, e.op("add", e.op("tanh", e.ld(A)), e.ld(B)))
+    ir = e.text()
+    assert ".tile4" in variant_of(L, ir, (1024, 512), 3, strides=[None, [1, 1024], None])
+    assert ".tile32" in variant_of(L, ir, (100, 257), 3, strides=[None, [1, 100], None])
+    assert ".tile32" in variant_of(L, ir, (1024, 512), 3, strides=[None, [1, 1024], None], pointers=[4096, 8196, 12288])
+    assert ".tile" not in variant_of(L, ir, (5, 4000), 3, strides=[None, [1, 5], None])
+    e = IRBuilder(2, 0)
+    O, A = e.arg("f64"), e.arg("f64")
+    e.st(O, e.ld(A))
+    assert ".tile32" in variant_of(L, e.text(), (64, 64), 2, strides=[None, [1, 64]])

@@ -326,11 +326,11 @@ def test_errors_are_statuses_not_crashes(lib):
         lib.launch(0xdeadbeef, (4, 4), [0, 0])     # unknown hash
 
 
-@pytest.mark.parametrize("shape", [(32, 32), (33, 65), (100, 257), (1024, 512), (5, 4000), (4000, 7)])
+@pytest.mark.parametrize("shape", [(32, 32), (33, 65), (100, 257), (1024, 512), (36, 132), (64, 200), (5, 4000), (4000, 7)])
 def test_map_with_transposed_operands_uses_shared_memory_tiles(lib, shape):
-    """out = tanh(a^T) + b + bias[col] with a stored column-major: the transposed operand goes through 32 x 32
-    shared-memory tiles (coalesced on both sides); same numbers as numpy, ragged edges included.  Below 32 rows or
-    columns the plain strided kernel takes over."""
+    """out = tanh(a^T) + b + bias[col] with a stored column-major: the transposed operand goes through 4 x 4 register
+    blocks (extents multiples of 4: 128-bit accesses on both sides) or 32 x 32 shared-memory tiles (ragged extents);
+    same numbers as numpy.  Below 32 rows or columns the plain strided kernel takes over."""
     R, C = shape
     rng = np.random.default_rng(R * 31 + C)
     at = rng.standard_normal((C, R)).astype(np.float32)        # a^T in memory: a[r, c] = at[c, r]
@@ -344,6 +344,7 @@ def test_map_with_transposed_operands_uses_shared_memory_tiles(lib, shape):
     lib.launch(h, (R, C), [out, dev(at), dev(b), dev(bias)], strides=[None, [1, R], None, [0, 1]])
     torch.cuda.synchronize()
     assert (".tile" in lib.last_variant()) == (R >= 32 and C >= 32)
+    assert (".tile4" in lib.last_variant()) == (R >= 32 and C >= 32 and R % 4 == 0 and C % 4 == 0)
     np.testing.assert_allclose(out.cpu().numpy(), np.tanh(at.T) + b + bias, rtol=1e-5, atol=1e-6)
     # two transposed operands and an in-place destination
     e2 = IRBuilder(2, 0)
