@@ -486,13 +486,22 @@ struct SplitParts {
 // A split that has its (hi, lo) buffers but has not been launched yet: two of one shape go out as one launch.
 struct PendingSplit { std::shared_ptr<SplitParts> parts; const float* x = nullptr; };
 
-// returns the (hi, lo) parts of a contiguous-row fp32 view; nullptr if the layout cannot be split in place.
+// returns the (hi, lo) parts of an fp32 matrix view as the GEMM wants them (row-major for a left operand, transposed
+// for a right one); nullptr if the layout cannot be split in place.  The view is either row-contiguous or the pure
+// transpose of a row-contiguous matrix (x.transpose() in a backward pass): the latter is split from the matrix
+// underneath with the transposition flipped, so W^T as a right operand needs no transposition at all.
 // With `pending` the split kernel of an operand that was not cached is left to the caller (launch_pending).
 std::shared_ptr<SplitParts> split_operand(BufferView* b, bool transpose, memory::Device device, int dev,
                                           std::vector<PendingSplit>* pending = nullptr) {
     std::vector<int> st = b->normalized_strides();
-    const int64_t rows = b->shape_[0], cols = b->shape_[1], ld = st[0];
-    if (st[1] != 1 && cols != 1) return nullptr;
+    int64_t rows = b->shape_[0], cols = b->shape_[1], ld = st[0];
+    if (st[1] != 1 && cols != 1) {
+        if (st[0] != 1 && rows != 1) return nullptr;
+        std::swap(rows, cols);          // the matrix underneath: [cols, rows] of the view, row pitch st[1]
+        ld = st[1];
+        transpose = !transpose;
+    }
+    if (ld < cols) return nullptr;      // (a broadcast row or column)
     if (cols % 4 || ld % 4 || (transpose && rows % 4) || (b->offset_ % 4)) return nullptr;
     auto& slot = b->memory_->derived_data();
     if (slot && b->memory_->derived_version() == b->memory_->version()) {

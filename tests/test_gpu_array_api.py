@@ -454,3 +454,27 @@ def test_assigning_into_a_view_of_a_lazy_value_materialises_it():
     col.eval()
     want[:, 2] += 1.0
     np.testing.assert_allclose(lazy.numpy(), want, rtol=1e-5, atol=1e-6)
+
+
+# ---- products of transposed views (the backward passes of a layer: dX = dY . W^T, dW = X^T . dY) --------------
+def test_dot_of_transposed_views_goes_through_tensor_cores():
+    rng = np.random.default_rng(78)
+    M, K, N = 256, 512, 384
+    A = (rng.standard_normal((M, K)) * 0.5).astype(np.float32)
+    Bm = (rng.standard_normal((K, N)) * 0.05).astype(np.float32)
+    want = A.astype(np.float64) @ Bm
+    At, Bt = Array(np.ascontiguousarray(A.T)), Array(np.ascontiguousarray(Bm.T))
+    for left, right in ((At.T, Array(Bm)), (Array(A), Bt.T), (At.T, Bt.T)):
+        r = op.dot(left, right)
+        assert launched(r) == {"kernels": 0, "gemms": 1, "temporaries": 0}
+        assert last_variant().startswith("tcgen05.tf32x3")
+        np.testing.assert_allclose(r.numpy(), want, rtol=1e-5, atol=2e-5)
+    # accumulation into an existing gradient: dw <<= x^T . dy, then once more, then subtracted
+    d_np = rng.standard_normal((M, N)).astype(np.float32)
+    d = Array(d_np)
+    d += op.dot(At.T, Bt.T)
+    d.eval()
+    assert last_variant().startswith("tcgen05.tf32x3")
+    np.testing.assert_allclose(d.numpy(), d_np + want, rtol=1e-5, atol=3e-5)
+    d -= op.dot(Array(A), Array(Bm))
+    np.testing.assert_allclose(d.numpy(), d_np, rtol=1e-5, atol=5e-5)
