@@ -750,7 +750,78 @@ class Cumsum(Workload):
         return {"ms": times, "bytes": 2 * m * self.N * 4, "cores": 1, "kind": "reference", "sample": "4 of the 8192 rows (full length 8192)"}
 
 
-WORKLOADS = {"lstm": Lstm, "softmax": Softmax, "reduce": ReduceAxis0, "gemm": Gemm, "chain": Chain, "scan": Cumsum}
+class TransposedMap(Workload):
+    """y = tanh(x)^T for fp32 [8192,8192]: an elementwise tree under a transposing view (not one of the five benchmark
+    configurations: the strided-view side of every fused kernel, measured to the same bar)."""
+    name = "transpose"
+    N = 8192
+    kernel_name = "map skeleton, 4 x 4 register blocks: 128-bit loads along the operand's rows, 128-bit stores along the destination's"
+    e2e_api = "C ABI with caller-managed copies (page-locked host -> device, dalib200_launch, device -> page-locked host, sync)"
+
+    def __init__(self, *a):
+        super().__init__(*a)
+        import numpy as np
+        from dali_b200.ir import IRBuilder
+        self.np = np
+        t = self.torch
+        t.manual_seed(1234 + 7 + self.rank)
+        self.x = [t.randn(self.N, self.N, device="cuda") for _ in range(2)]    # 2 x 256 MiB > L2
+        self.out = t.empty(self.N, self.N, device="cuda")
+        e = IRBuilder(2, 0)
+        O, A = e.arg("f32"), e.arg("f32")
+        e.st(O, e.op("tanh", e.ld(A)))
+        self.h = self.lib.compile(e.text())
+        self.scaling = "weak"
+        self.launches_per_step = 1
+
+    def describe(self):
+        return {"workload": "y = tanh(x).transpose(), fp32 [8192,8192] ~ N(0,1) per GPU",
+                "l2": "two 256 MiB inputs alternate, 256 MiB output (768 MiB > L2)",
+                "parallelism": "independent matrices: each of %d GPU(s) transposes its own, no collective" % self.world}
+
+    def bytes_per_step(self):
+        return 2 * self.N * self.N * 4
+
+    def launch_step(self, i, stream):
+        # out[r, c] = tanh(x[c, r]): the operand is handed over with its strides swapped
+        self.lib.launch(self.h, (self.N, self.N), [self.out, self.x[i % 2]], strides=[None, [1, self.N]], stream=stream)
+
+    def step(self, i):
+        self.launch_step(i, self.stream)
+
+    def graph_fn(self):
+        return self.launch_step
+
+    def e2e_setup(self):
+        t = self.torch
+        self.hx = t.empty(self.N, self.N, pin_memory=True); self.hx.copy_(self.x[0])
+        self.hout = t.empty(self.N, self.N, pin_memory=True)
+        self.h2d = self.d2h = self.N * self.N * 4
+
+    def e2e_step(self, i):
+        self.x[0].copy_(self.hx, non_blocking=True)
+        self.launch_step(0, self.stream)
+        self.hout.copy_(self.out, non_blocking=True)
+        self.torch.cuda.synchronize()
+
+    def verify(self):
+        self.launch_step(0, self.stream)
+        self.torch.cuda.synchronize()
+        assert ".tile4" in self.lib.last_variant()
+        rows = [0, 4097, self.N - 1]
+        want = self.np.tanh(self.x[0][:, rows].cpu().numpy().astype(self.np.float64)).T
+        self.np.testing.assert_allclose(self.out[rows].cpu().numpy(), want, rtol=1e-5, atol=1e-6)
+
+    def cpu_baseline(self, tmpdir, reps):
+        m = 2048
+        self.np.save(os.path.join(tmpdir, "x.npy"), self.x[0][:m, :m].contiguous().cpu().numpy())
+        times = run_ref_driver("unary_t", ["tanh", "x.npy", "out.npy"], min(reps, 5), tmpdir)
+        if not times:
+            return None
+        return {"ms": times, "bytes": 2 * m * m * 4, "cores": 1, "kind": "reference", "sample": "a [2048,2048] corner (1/16 of the bytes)"}
+
+
+WORKLOADS = {"lstm": Lstm, "softmax": Softmax, "reduce": ReduceAxis0, "gemm": Gemm, "chain": Chain, "scan": Cumsum, "transpose": TransposedMap}
 
 
 # ----------------------------------------------------------------------------- main
@@ -807,6 +878,13 @@ def reference_arm(args):
             case, cargs, nbytes, flops = "gemm_tanh", ["A.npy", "B.npy", "bias.npy", "out.npy"], 3 * m * m * 2, 2.0 * m ** 3
             wl = "C4 tanh(dot(A,B)+bias), bf16 A,B [8192,8192] ~ N(0,0.02), bias ~ N(0,0.1), fp32 accumulate, bf16 out"
             sample, ncores, scaling, dtype = "2048^3 in fp32 per step (the reference has no bf16; 1/64 of the flops)", cores, "weak", "f32"
+        elif w == "transpose":
+            rng = np.random.default_rng(1241)
+            m = 2048
+            save("x.npy", rng.standard_normal((m, m)).astype(np.float32))
+            case, cargs, nbytes, flops = "unary_t", ["tanh", "x.npy", "out.npy"], 2 * m * m * 4, 0
+            wl = "y = tanh(x).transpose(), fp32 [8192,8192] ~ N(0,1) per GPU"
+            sample, ncores, scaling, dtype = "a [2048,2048] array per step (1/16 of the bytes)", 1, "weak", "f32"
         elif w == "scan":
             rng = np.random.default_rng(1240)
             m = 4
@@ -1042,7 +1120,7 @@ def main():
     others = None
     if args.workload == "lstm" and not args.no_others and world == 1:
         others = {}
-        for name in ("softmax", "reduce", "gemm", "chain", "scan"):
+        for name in ("softmax", "reduce", "gemm", "chain", "scan", "transpose"):
             del wl
             torch.cuda.empty_cache()
             wl = build(name)

@@ -258,6 +258,18 @@ int main(int argc, char** argv) {
     } else if (c == "outer" && n >= 3) {
         Array r = op::outer(load(a[0]), load(a[1])); r.eval();
         save(a[2], r);
+    } else if (c == "unary_t" && n >= 3) {
+        // y = contiguous copy of f(x)^T: an elementwise tree under a transposing view
+        auto t = unary_table();
+        if (!t.count(a[0])) { std::fprintf(stderr, "unknown unary %s\n", a[0]); return 2; }
+        Array x = load(a[1]);
+        Array r;
+        timed(reps_at(3), [&]() {
+            Array y = t[a[0]](x).transpose().ascontiguousarray();
+            y.eval();
+            r = y;
+        });
+        save(a[2], r);
     } else if (c == "scan" && n >= 4) {
         Array x = load(a[2]);
         const bool inclusive = std::atoi(a[1]) != 0, sum = std::string(a[0]) == "sum";
