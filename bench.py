@@ -44,6 +44,7 @@ DRAM_TRAFFIC_PER_ALGO_BYTE = {
     "softmax": 0.50,     # profiles/softmax_row_kernel.md: the 16 MiB output is still in L2 when the kernel ends
     "reduce": 1.0002,    # profiles/reduce_8192_row_col_all_kernels.md
     "scan": 0.905,       # profiles/scan_rows_kernel.md: the tail of the output is written back after the kernel ends
+    "transpose": 0.919,  # profiles/map_transposing_kernel.md: likewise
 }
 
 
