@@ -779,6 +779,21 @@ bool launch_gemm_program(Lowerer& L, const GemmOperands& g, int64_t m, int64_t n
     return true;
 }
 
+// Starts the host -> device copies of the buffers a tree reads before the tree is lowered: the copies (asynchronous
+// from page-locked memory) then run while the host builds the program.  A gather's or scatter's source is copied as
+// a whole too, as the launch would.
+void prefetch_inputs(const Array& a, const memory::Device& device, int depth = 0) {
+    if (a.is_stateless() || depth > 64 || !device.is_gpu()) return;
+    Expression* e = a.expression().get();
+    if (e->kind_ == N_BUFFER) {
+        BufferView* b = static_cast<BufferView*>(e);
+        if (!b->memory_->is_fresh(device) && b->memory_->is_fresh(memory::Device::cpu())) b->memory_->data(device, memory::AM_READONLY);
+        return;
+    }
+    if (e->kind_ == N_ASSIGN) return;      // evaluated on its own, with its own prefetch
+    for (const Array& arg : e->arguments_) prefetch_inputs(arg, device, depth + 1);
+}
+
 }  // namespace
 
 void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) {
@@ -789,6 +804,7 @@ void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) 
     if (dest.is_assignment()) dest.eval(false);
     if (value.is_assignment()) value.eval(false);
     if (dest.expression()->kind_ == N_VIEW) dest = writable_view(dest);
+    if (!tl_dry_run) prefetch_inputs(value, dest.preferred_device());
 
     // ---- peel pure re-indexing views off the root: dest = view(x)  ->  inverse_view(dest) = x
     // (x keeps its own iteration space, which its reductions / products need).  A tree of nothing but elementwise
@@ -1003,6 +1019,9 @@ bool try_sliced_gemm(const std::vector<const Array*>& roots) {
 // eval() is a kernel of its own; anything this cannot fuse (reductions, products or scans at a root, differing
 // shapes) is evaluated one by one exactly as Array::eval would.
 void eval_together(const std::vector<Array>& arrays) {
+    if (!tl_dry_run)
+        for (const Array& a : arrays)
+            if (!a.is_stateless() && !a.is_buffer()) prefetch_inputs(a, a.preferred_device());
     std::vector<const Array*> roots;
     for (const Array& a : arrays) {
         DALI_ASSERT(!a.is_stateless(), "eval_together on a stateless Array");
