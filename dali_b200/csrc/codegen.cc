@@ -94,8 +94,9 @@ struct Gen {
         return "(" + t + ")(" + lit + ")";
     }
 
-    // expression for a non-load, non-reduction value
-    std::string expr(const Stmt& s) const {
+    // expression for a non-load, non-reduction value; lane_blocks: inside the lane loop of emit_group, where every
+    // random node has an RngBlock rb<id> that its lanes share
+    std::string expr(const Stmt& s, bool lane_blocks = false) const {
         switch (s.kind) {
             case S_CONST: return literal(s);
             case S_SC: return "*reinterpret_cast<const " + ct(s.dtype) + "*>(&" + W(L.w_scalars + s.arg) + ")";
@@ -104,7 +105,8 @@ struct Gen {
                 if (s.name == "round" || s.name == "ceiling")
                     return "f_" + s.name + "<" + ct(s.dtype) + ">(" + vn(s.in[0]) + ")";
                 if (s.name == "rng_uniform" || s.name == "rng_normal")
-                    return "f_" + s.name + "<" + ct(s.dtype) + ">(" + vn(s.in[0]) + ", " + vn(s.in[1]) + ")";
+                    return "f_" + s.name + "<" + ct(s.dtype) + ">(" + vn(s.in[0]) + ", " + vn(s.in[1]) +
+                           (lane_blocks ? ", rb" + std::to_string(s.id) : std::string()) + ")";
                 if (s.name == "eltdiv" && s.in.size() == 2 && need_inv.count(s.in[1]) && s.elem && s.dtype == F32)
                     return vn(s.in[0]) + " * rinv" + std::to_string(s.in[1]);
                 std::string e = "f_" + s.name + "(" + vn(s.in[0]);
@@ -338,6 +340,9 @@ struct Gen {
             const Stmt& s = p.stmts[si];
             if (s.kind == S_ST) o << ind << "Vec<" << argT(s.arg) << ", VEC> out" << si << ";\n";
         }
+        for (const Stmt& s : p.stmts)
+            if (s.id >= 0 && need.count(s.id) && s.kind == S_OP && (s.name == "rng_uniform" || s.name == "rng_normal"))
+                o << ind << "RngBlock rb" << s.id << " = {0u, {0u, 0u, 0u, 0u}, 0};\n";
         o << ind << "_Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) {\n";
         const std::string in2 = ind + "  ";
         for (int id : g.cuts_rd) {
@@ -354,7 +359,7 @@ struct Gen {
                   << (arg_elem(s.arg) ? col_off(s.arg, g.c + " + j") : std::string("0")) << " + (i64)" << vn(s.in[0])
                   << " * " << W(L.arg_xs(s.arg)) << "];\n";
             } else {
-                o << in2 << "const " << ct(s.dtype) << " " << vn(s.id) << " = " << expr(s) << ";\n";
+                o << in2 << "const " << ct(s.dtype) << " " << vn(s.id) << " = " << expr(s, true) << ";\n";
             }
             if (g.cuts_wr.count(s.id))
                 o << in2 << "CV" << s.id << g.slot.substr(0, g.slot.size() ? g.slot.size() - 1 : 0)

@@ -292,8 +292,8 @@ template <typename T, int N> struct alignas(sizeof(T) * N) Vec { T x[N]; };
 template <typename T, int N> DEV Vec<T, N> vload(const T* p) { return *reinterpret_cast<const Vec<T, N>*>(p); }
 template <typename T, int N> DEV void vstore(T* p, const Vec<T, N>& v) { *reinterpret_cast<Vec<T, N>*>(p) = v; }
 
-// Counter-based random numbers: Philox4x32-10 (Salmon et al., SC'11) with counter = (element
-// index, 0, 0, 0) and key = (seed, 0).  Replaces the thrust generators the reference seeds per
+// Counter-based random numbers: Philox4x32-10 (Salmon et al., SC'11) with counter = (block, 0, 0, 0)
+// and key = (seed, 0); which block and words an element reads is stated at RngBlock below.  Replaces the thrust generators the reference seeds per
 // call on the GPU (dali/array/op/random.cu.cpp:153-232): being a pure function of (index,
 // seed) it fuses into whatever consumes the numbers (a dropout mask never touches memory) and
 // gives the same stream whatever the launch geometry.
@@ -309,34 +309,51 @@ DEV void philox4x32_10(unsigned c0, unsigned k0, unsigned out[4]) {
     }
     out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
 }
-// u in [0, 1): 24 bits for float, 53 for double
-template <typename T> DEV T f_rng_uniform(int index, int seed);
-template <> DEV float f_rng_uniform<float>(int index, int seed) {
-    unsigned x[4];
-    philox4x32_10((unsigned)index, (unsigned)seed, x);
-    return (float)(x[0] >> 8) * (1.0f / 16777216.0f);
+// Element i of a random array reads the Philox block and the words that its type needs:
+//   fp32 uniform            block i >> 2, word i & 3
+//   fp64 uniform, fp32 normal   block i >> 1, words 2 (i & 1) and 2 (i & 1) + 1
+//   fp64 normal             block i, all four words
+// so neighbouring elements share a block.  RngBlock keeps the last block of one random node across the lanes of a
+// thread's vector: four fp32 uniforms cost one Philox call (when the vector starts on a block boundary; two otherwise).
+struct RngBlock { unsigned id; unsigned w[4]; int valid; };
+DEV void rng_fetch(RngBlock& b, unsigned id, int seed) {
+    if (!b.valid || b.id != id) {
+        philox4x32_10(id, (unsigned)seed, b.w);
+        b.id = id;
+        b.valid = 1;
+    }
 }
-template <> DEV double f_rng_uniform<double>(int index, int seed) {
-    unsigned x[4];
-    philox4x32_10((unsigned)index, (unsigned)seed, x);
-    return ((double)(x[0] >> 5) * 67108864.0 + (double)(x[1] >> 6)) * (1.0 / 9007199254740992.0);
+DEV unsigned rng_word(const RngBlock& b, int k) { return k == 0 ? b.w[0] : (k == 1 ? b.w[1] : (k == 2 ? b.w[2] : b.w[3])); }
+DEV double rng_u53(unsigned hi, unsigned lo) { return (double)(hi >> 5) * 67108864.0 + (double)(lo >> 6); }
+// u in [0, 1): 24 bits for float, 53 for double
+template <typename T> DEV T f_rng_uniform(int index, int seed, RngBlock& b);
+template <> DEV float f_rng_uniform<float>(int index, int seed, RngBlock& b) {
+    rng_fetch(b, (unsigned)index >> 2, seed);
+    return (float)(rng_word(b, index & 3) >> 8) * (1.0f / 16777216.0f);
+}
+template <> DEV double f_rng_uniform<double>(int index, int seed, RngBlock& b) {
+    rng_fetch(b, (unsigned)index >> 1, seed);
+    const int k = (index & 1) * 2;
+    return rng_u53(rng_word(b, k), rng_word(b, k + 1)) * (1.0 / 9007199254740992.0);
 }
 // standard normal by Box-Muller on two uniforms of one Philox block: sqrt(-2 ln u1) cos(2 pi u2), u1 in (0, 1]
-template <typename T> DEV T f_rng_normal(int index, int seed);
-template <> DEV float f_rng_normal<float>(int index, int seed) {
-    unsigned x[4];
-    philox4x32_10((unsigned)index, (unsigned)seed, x);
-    const float u1 = ((float)(x[0] >> 8) + 1.0f) * (1.0f / 16777216.0f);
-    const float u2 = (float)(x[1] >> 8) * (1.0f / 16777216.0f);
+template <typename T> DEV T f_rng_normal(int index, int seed, RngBlock& b);
+template <> DEV float f_rng_normal<float>(int index, int seed, RngBlock& b) {
+    rng_fetch(b, (unsigned)index >> 1, seed);
+    const int k = (index & 1) * 2;
+    const float u1 = ((float)(rng_word(b, k) >> 8) + 1.0f) * (1.0f / 16777216.0f);
+    const float u2 = (float)(rng_word(b, k + 1) >> 8) * (1.0f / 16777216.0f);
     return sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
 }
-template <> DEV double f_rng_normal<double>(int index, int seed) {
-    unsigned x[4];
-    philox4x32_10((unsigned)index, (unsigned)seed, x);
-    const double u1 = ((double)(x[0] >> 5) * 67108864.0 + (double)(x[1] >> 6) + 1.0) * (1.0 / 9007199254740992.0);
-    const double u2 = ((double)(x[2] >> 5) * 67108864.0 + (double)(x[3] >> 6)) * (1.0 / 9007199254740992.0);
+template <> DEV double f_rng_normal<double>(int index, int seed, RngBlock& b) {
+    rng_fetch(b, (unsigned)index, seed);
+    const double u1 = (rng_u53(b.w[0], b.w[1]) + 1.0) * (1.0 / 9007199254740992.0);
+    const double u2 = rng_u53(b.w[2], b.w[3]) * (1.0 / 9007199254740992.0);
     return sqrt(-2.0 * log(u1)) * cospi(2.0 * u2);
 }
+// one element on its own (row-level statements, GEMM epilogues)
+template <typename T> DEV T f_rng_uniform(int index, int seed) { RngBlock b = {0u, {0u, 0u, 0u, 0u}, 0}; return f_rng_uniform<T>(index, seed, b); }
+template <typename T> DEV T f_rng_normal(int index, int seed) { RngBlock b = {0u, {0u, 0u, 0u, 0u}, 0}; return f_rng_normal<T>(index, seed, b); }
 
 // An argument with no memory behind it whose "element" at offset i is base + i: with the
 // per-dim strides every argument has, base + sum(index_d * stride_d) is any affine function

@@ -27,7 +27,7 @@ namespace dalib {
 static const char* kPrelude =
 #include "prelude_embed.inc"
     ;
-static const char* kCodegenVersion = "dali_b200-codegen-3";
+static const char* kCodegenVersion = "dali_b200-codegen-4";
 
 // ------------------------------------------------------------------ errors
 static thread_local std::string tl_error;

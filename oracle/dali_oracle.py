@@ -280,22 +280,35 @@ def philox4x32_10(counter, key):
     return [w.astype(np.uint32) for w in c]
 
 
+def _philox_words(n, seed, per_element):
+    """The words element i < n reads: fp32 uniforms take one word (block i >> 2, word i & 3), fp64 uniforms and fp32
+    normals two (block i >> 1, words 2 (i & 1), 2 (i & 1) + 1), fp64 normals the whole block i."""
+    i = np.arange(n, dtype=np.uint64)
+    shift = {1: 2, 2: 1, 4: 0}[per_element]
+    x = philox4x32_10((i >> np.uint64(shift), 0, 0, 0), (seed, 0))
+    words = np.stack(x, axis=1)                                   # [n, 4]
+    first = ((i & np.uint64((1 << shift) - 1)) * np.uint64(per_element)).astype(np.int64)
+    return [words[np.arange(n), first + k] for k in range(per_element)]
+
+
 def rng_uniform(n, seed, dtype=np.float32):
     """u[i] in [0, 1) for element index i < n."""
-    x = philox4x32_10((np.arange(n, dtype=np.uint64), 0, 0, 0), (seed, 0))
     if np.dtype(dtype) == np.float32:
-        return ((x[0] >> np.uint32(8)).astype(np.float32) * np.float32(1.0 / 16777216.0)).astype(np.float32)
-    hi, lo = (x[0] >> np.uint32(5)).astype(np.float64), (x[1] >> np.uint32(6)).astype(np.float64)
+        (w,) = _philox_words(n, seed, 1)
+        return ((w >> np.uint32(8)).astype(np.float32) * np.float32(1.0 / 16777216.0)).astype(np.float32)
+    w0, w1 = _philox_words(n, seed, 2)
+    hi, lo = (w0 >> np.uint32(5)).astype(np.float64), (w1 >> np.uint32(6)).astype(np.float64)
     return (hi * 67108864.0 + lo) * (1.0 / 9007199254740992.0)
 
 
 def rng_normal(n, seed, dtype=np.float32):
     """Box-Muller on two uniforms of the same Philox block: sqrt(-2 ln u1) cos(2 pi u2), u1 in (0, 1]."""
-    x = philox4x32_10((np.arange(n, dtype=np.uint64), 0, 0, 0), (seed, 0))
     if np.dtype(dtype) == np.float32:
-        u1 = ((x[0] >> np.uint32(8)).astype(np.float64) + 1.0) / 16777216.0
-        u2 = (x[1] >> np.uint32(8)).astype(np.float64) / 16777216.0
+        w0, w1 = _philox_words(n, seed, 2)
+        u1 = ((w0 >> np.uint32(8)).astype(np.float64) + 1.0) / 16777216.0
+        u2 = (w1 >> np.uint32(8)).astype(np.float64) / 16777216.0
     else:
+        x = _philox_words(n, seed, 4)
         u1 = ((x[0] >> np.uint32(5)).astype(np.float64) * 67108864.0 + (x[1] >> np.uint32(6)).astype(np.float64) + 1.0) / 9007199254740992.0
         u2 = ((x[2] >> np.uint32(5)).astype(np.float64) * 67108864.0 + (x[3] >> np.uint32(6)).astype(np.float64)) / 9007199254740992.0
     return (np.sqrt(-2.0 * np.log(u1)) * np.cos(2.0 * np.pi * u2)).astype(dtype)
