@@ -779,6 +779,61 @@ bool launch_gemm_program(Lowerer& L, const GemmOperands& g, int64_t m, int64_t n
     return true;
 }
 
+// A reduction over the trailing dims of few, very long rows.  The `row` skeleton gives a row to one CTA, which
+// leaves most of the machine idle when there are fewer rows than SMs; the `all` skeleton spreads ONE reduction
+// over every SM.  Such a reduction therefore runs as one all-axis reduction per row, and a tree around it (a
+// softmax over [4, 16M]) is evaluated reduction by reduction with an elementwise kernel at the end.
+// (not when the rows are read through a view or with a stride: a reduction over axis 0 arrives here as the last
+// axis of a transposed view, and the `col` skeleton reads that layout with 128-bit loads)
+bool reads_rows_contiguously(const Array& a, int depth = 0) {
+    if (a.is_stateless() || depth > 64) return false;
+    Expression* e = a.expression().get();
+    switch (e->kind_) {
+        case N_SCALAR: case N_IOTA: return true;
+        case N_BUFFER: {
+            BufferView* b = static_cast<BufferView*>(e);
+            return b->ndim() == 0 || b->shape_.back() == 1 || b->normalized_strides().back() == 1;
+        }
+        case N_ELEMENTWISE:
+            for (const Array& arg : e->arguments_) if (!reads_rows_contiguously(arg, depth + 1)) return false;
+            return true;
+        case N_VIEW: {
+            // which dim of the argument runs along the view's last dim?  none: a broadcast along the rows (a keepdims
+            // result), harmless; the argument's own last dim with step 1: look further down; anything else: strided
+            View* v = static_cast<View*>(e);
+            const int last = v->ndim() - 1;
+            int from = -1;
+            for (size_t k = 0; k < v->dims_.size(); ++k)
+                if (v->dims_[k].src == last && v->arguments_[0].shape()[k] != 1) from = (int)k;
+            if (from < 0) return true;
+            if (from != (int)v->dims_.size() - 1 || v->dims_[from].step != 1) return false;
+            return reads_rows_contiguously(v->arguments_[0], depth + 1);
+        }
+        default: return false;
+    }
+}
+
+bool few_long_rows(const Reduce* r) {
+    const Array& arg = r->arguments_[0];
+    const int lead = arg.ndim() - r->nreduce_;
+    if (lead < 1 || !reads_rows_contiguously(arg)) return false;
+    int64_t rows = 1, cols = 1;
+    for (int d = 0; d < arg.ndim(); ++d) (d < lead ? rows : cols) *= arg.shape()[d];
+    return rows >= 1 && ((rows <= 8 && cols >= (1 << 18)) || (rows <= 32 && cols >= (1 << 22)));
+}
+
+// evaluates, bottom up and in place (the handle then names the buffer), every such reduction below `a`
+void split_few_long_row_reductions(const Array& a, int depth = 0) {
+    if (a.is_stateless() || depth > 64) return;
+    Expression* e = a.expression().get();
+    if (e->kind_ != N_ELEMENTWISE && e->kind_ != N_VIEW && e->kind_ != N_REDUCE) return;
+    for (const Array& arg : e->arguments_) split_few_long_row_reductions(arg, depth + 1);
+    if (e->kind_ == N_REDUCE && few_long_rows(static_cast<Reduce*>(e))) {
+        a.eval(false);
+        ++tl_stats.temporaries;
+    }
+}
+
 // Starts the host -> device copies of the buffers a tree reads before the tree is lowered: the copies (asynchronous
 // from page-locked memory) then run while the host builds the program.  A gather's or scatter's source is copied as
 // a whole too, as the launch would.
@@ -850,6 +905,31 @@ void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) 
         if (!acc) find_matmul(value, &acc);
         if (acc && acc->dtype_ == DTYPE_FLOAT && try_fused_gemm(dest, op, value, acc)) return;
     }
+
+    // ---- reductions over few, very long rows: one all-axis reduction per row (see few_long_rows)
+    if (value.expression()->kind_ == N_REDUCE && dest.is_buffer() && few_long_rows(static_cast<Reduce*>(value.expression().get()))) {
+        Reduce* rd = static_cast<Reduce*>(value.expression().get());
+        const Array& arg = rd->arguments_[0];
+        split_few_long_row_reductions(arg);
+        const int lead = arg.ndim() - rd->nreduce_;
+        int64_t rows = 1;
+        for (int d = 0; d < lead; ++d) rows *= arg.shape()[d];
+        for (int64_t r = 0; r < rows; ++r) {
+            Array a_r = arg, d_r = dest;
+            int64_t rem = r, div = rows;
+            for (int d = 0; d < lead; ++d) {
+                div /= arg.shape()[d];
+                const int idx = (int)(rem / div);
+                rem %= div;
+                a_r = a_r.pluck_axis(0, idx);
+                d_r = d_r.pluck_axis(0, idx);
+            }
+            Array v_r(std::make_shared<Reduce>(rd->reducer_, a_r, rd->nreduce_, rd->arg_, rd->dtype_));
+            run_assignment(d_r, op, v_r);
+        }
+        return;
+    }
+    split_few_long_row_reductions(value);
 
     // ---- a running reduction at the root has its own kernel
     if (value.expression()->kind_ == N_SCAN && dest.is_buffer()) {

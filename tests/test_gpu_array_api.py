@@ -478,3 +478,34 @@ def test_dot_of_transposed_views_goes_through_tensor_cores():
     np.testing.assert_allclose(d.numpy(), d_np + want, rtol=1e-5, atol=3e-5)
     d -= op.dot(Array(A), Array(Bm))
     np.testing.assert_allclose(d.numpy(), d_np, rtol=1e-5, atol=5e-5)
+
+
+# ---- few, very long rows: one all-axis reduction per row instead of one CTA per row ---------------------------
+def test_reductions_over_few_very_long_rows():
+    rng = np.random.default_rng(21)
+    R, C = 3, (1 << 18) + 64
+    a_np = rng.standard_normal((R, C)).astype(np.float32)
+    a_np[1, 12345] = 9.5
+    a_np[2, C - 1] = 11.0
+    a = Array(a_np)
+    s = op.sum(a, [-1])
+    counts = launched(s)
+    assert counts["kernels"] == R and "all." in last_variant()
+    want = a_np.astype(np.float64).sum(1)
+    assert np.all(np.abs(s.numpy() - want) <= 1e-5 * np.abs(a_np).astype(np.float64).sum(1))
+    np.testing.assert_array_equal(op.max(a, [-1]).numpy(), a_np.max(1))
+    np.testing.assert_array_equal(op.argmax(a, -1).numpy(), a_np.argmax(1).astype(np.int32))
+    np.testing.assert_allclose(op.mean(a, [-1], True).numpy(), a_np.astype(np.float64).mean(1, keepdims=True), rtol=1e-4, atol=1e-6)
+    # a tree around the reductions: softmax, evaluated reduction by reduction, then one elementwise kernel
+    sm = op.softmax(a)
+    got = sm.numpy()
+    np.testing.assert_allclose(got, oracle.softmax(a_np), rtol=1e-5, atol=1e-12)
+    # accumulation into an existing vector, and leading dims [2, 2]
+    d_np = rng.standard_normal(R).astype(np.float32)
+    d = Array(d_np)
+    d += op.sum(a * a, [-1])
+    assert np.all(np.abs(d.numpy() - (d_np + (a_np.astype(np.float64) ** 2).sum(1))) <= 1e-5 * (1 + (a_np.astype(np.float64) ** 2).sum(1)))
+    b_np = rng.standard_normal((2, 2, 1 << 18)).astype(np.float32)
+    np.testing.assert_array_equal(op.min(Array(b_np), [-1]).numpy(), b_np.min(2))
+    one = Array(a_np[:1])
+    assert abs(float(op.sum(one, [-1]).numpy()[0]) - want[0]) <= 1e-5 * np.abs(a_np[0]).sum()
