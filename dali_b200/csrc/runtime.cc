@@ -310,6 +310,18 @@ static int get_scratch_locked(int device, void* stream, size_t bytes, size_t cou
     return DALIB200_OK;
 }
 
+int scratch_space(int device, void* stream, size_t bytes, void** out) {
+    State& s = S();
+    std::lock_guard<std::mutex> g(s.mu);
+    int rc = check_device(device);
+    if (rc != DALIB200_OK) return rc;
+    Scratch sc;
+    rc = get_scratch_locked(device, stream, bytes, 0, &sc);
+    if (rc != DALIB200_OK) return rc;
+    *out = sc.buf;
+    return DALIB200_OK;
+}
+
 static int get_function_locked(int device, const std::string& key, const KernelImage& img, CUfunction* fn,
                                const char* entry = "dali_kernel") {
     DeviceState& d = S().devices[device];

@@ -73,6 +73,9 @@ bool dependent_launch_enabled();
 // Driver entry point by name (nullptr if unavailable).
 void* driver_entry(const char* name);
 int device_ordinal(int device);            // CUDA ordinal of bound device, -1 if not bound
+// At least `bytes` of the cross-CTA exchange space of (device, stream): the space generated kernels use for their
+// partial results, valid until the next launch on that stream that asks for space.  Returns a dalib200_status.
+int scratch_space(int device, void* stream, size_t bytes, void** out);
 void count_launch();
 // One int per device that tensor-core kernels raise when a bounded wait expires.
 int* gemm_error_word(int device);

@@ -99,10 +99,12 @@ def test_running_reductions_against_the_reference(golden, inclusive):
     np.testing.assert_array_equal(op.cumprod(p, inclusive).numpy(), oracle.scan("prod", np.arange(1, 21, dtype=np.int32), inclusive))
 
 
-@pytest.mark.parametrize("shape", [(1, 1), (7, 3), (5, 128), (3, 1025), (1000, 37), (2, 100003), (1, 1 << 22)])
+@pytest.mark.parametrize("shape", [(1, 1), (7, 3), (300, 9), (64, 20), (5, 128), (33, 70), (5, 300), (3, 1025), (1000, 37),
+                                   (700, 20000), (3, 1 << 16), (2, 100003), (1, 1 << 22)])
 def test_scan_shapes_through_the_c_abi(lib, shape):
-    """Warp-per-row and CTA-per-row variants, ragged tiles, exact integer-valued floats so that any lost or
-    doubled element shows; running max / min bit-exact on random data."""
+    """Rows owned by 1 .. 32 lanes, by a CTA, or cut into pieces over many CTAs (few, very long rows); ragged
+    tiles; exact integer-valued floats so that any lost or doubled element shows; running max / min bit-exact on
+    random data."""
     rows, cols = shape
     rng = np.random.default_rng(rows * 7 + cols)
     x = rng.integers(-3, 4, shape).astype(np.float32)                          # partial sums stay exact in fp32
