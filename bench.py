@@ -931,6 +931,21 @@ def measure(wl, torch, world, steps, warmup, lib, sample_clocks=True, local=0):
     if stepper:
         for _ in range(2):
             stepper.replay()
+        # Untimed spin-up on top of the `warmup` steps: a step of tens of microseconds leaves a GPU that has just come
+        # out of idle no time to reach its clocks (one default run measured 59 us per LSTM step right after another
+        # process had left the GPU idle, 35 us otherwise).  ~150 ms of the same replays, no collective inside.
+        # Only for such short steps: a block of milliseconds has warmed the GPU up by itself, and a long spin-up
+        # would move a power-capped GEMM from its burst clocks to its sustained ones before the block is timed.
+        torch.cuda.synchronize()
+        t_spin = time.perf_counter()
+        stepper.replay()
+        torch.cuda.synchronize()
+        if time.perf_counter() - t_spin < 5e-3:
+            for _ in range(2000):
+                stepper.replay()
+                torch.cuda.synchronize()
+                if time.perf_counter() - t_spin > 0.15:
+                    break
     barrier()
     sampler = ClockSampler(local) if sample_clocks else None
     if sampler:
