@@ -929,23 +929,24 @@ def measure(wl, torch, world, steps, warmup, lib, sample_clocks=True, local=0):
     fn = wl.graph_fn()
     stepper = GraphStepper(torch, lambda i, st: fn(warmup + i, st), steps, getattr(wl, "lanes", 1)) if fn else None
     if stepper:
+        barrier()
+        t_spin = time.perf_counter()
         for _ in range(2):
             stepper.replay()
+        torch.cuda.synchronize()
         # Untimed spin-up on top of the `warmup` steps: a step of tens of microseconds leaves a GPU that has just come
         # out of idle no time to reach its clocks (one default run measured 59 us per LSTM step right after another
-        # process had left the GPU idle, 35 us otherwise).  ~150 ms of the same replays, no collective inside.
-        # Only for such short steps: a block of milliseconds has warmed the GPU up by itself, and a long spin-up
-        # would move a power-capped GEMM from its burst clocks to its sustained ones before the block is timed.
-        torch.cuda.synchronize()
-        t_spin = time.perf_counter()
-        stepper.replay()
-        torch.cuda.synchronize()
-        if time.perf_counter() - t_spin < 5e-3:
-            for _ in range(2000):
+        # process had left the GPU idle, 35 us otherwise).  ~150 ms of the same replays, the same number on every
+        # rank (a step may hold a collective).  Only for such short steps: a block of milliseconds has warmed the GPU
+        # up by itself, and more untimed work would move a power-capped GEMM from its burst clocks to its sustained
+        # ones before the block is timed.
+        est = torch.tensor([(time.perf_counter() - t_spin) / 2], dtype=torch.float64, device="cuda")
+        if world > 1:
+            torch.distributed.all_reduce(est, op=torch.distributed.ReduceOp.MAX)
+        est = max(float(est.item()), 1e-5)
+        if est < 5e-3:
+            for _ in range(min(2000, int(0.15 / est) + 1)):
                 stepper.replay()
-                torch.cuda.synchronize()
-                if time.perf_counter() - t_spin > 0.15:
-                    break
     barrier()
     sampler = ClockSampler(local) if sample_clocks else None
     if sampler:
@@ -1012,13 +1013,19 @@ def roofline_of(wl, m, lib):
     if dom and dom["bound"] == "tensor":
         path = os.path.join(ROOT, "MEASURED_PEAKS.json")
         peak = 1590.0
+        sustained = None
         src = "fallback 1.59 PFLOP/s"
         if os.path.exists(path):
             with open(path) as f:
-                peak = float(json.load(f)["bf16_tflops"])
+                peaks = json.load(f)
+            peak = float(peaks["bf16_tflops"])
+            sustained = peaks.get("bf16_tflops_sustained")
             src = "measured (MEASURED_PEAKS.json bf16_tflops, burst: kernel timed alone)"
         achieved = dom["work"] / (dom["ms"] * 1e-3) / 1e12
         out = {}
+        if os.path.exists(path) and sustained:
+            # the same kernel after seconds of load runs at the power cap's clocks: the fraction of that figure too
+            out["frac_of_sustained_peak"] = achieved / float(sustained)
         if "TF32" in dom["kernel"]:
             # three TF32 products per fp32 product, and the dense TF32 rate is half the bf16 rate the peak is measured in
             out["tensor_pipe_equivalent_frac"] = 6.0 * achieved / peak
@@ -1136,16 +1143,17 @@ def main():
     others = None
     if args.workload == "lstm" and not args.no_others and world == 1:
         others = {}
-        for name in ("softmax", "reduce", "gemm", "chain", "scan", "transpose"):
+        for name in ("gemm", "softmax", "reduce", "chain", "scan", "transpose"):   # the power-capped GEMM before the GPU is hot
             del wl
             torch.cuda.empty_cache()
+            time.sleep(1.0)      # each workload starts from a rested GPU, as its own `--workload` run would (power cap)
             wl = build(name)
             wl.verify()
             mo = measure(wl, torch, world, 24, 3, lib, False, local)      # 24: whole steps on each of the softmax lanes
             ro = roofline_of(wl, mo, lib)
             entry = {"workload": wl.describe()["workload"], "ms_per_step": mo["ms_per_step"],
                      "gbs": wl.bytes_per_step() / (mo["ms_per_step"] * 1e-3) / 1e9,
-                     "roofline": {k: ro[k] for k in ("bound", "achieved", "peak", "unit", "frac", "kernel")}}
+                     "roofline": {k: ro[k] for k in ("bound", "achieved", "peak", "unit", "frac", "frac_of_sustained_peak", "kernel") if k in ro}}
             if wl.flops_per_step():
                 entry["tflops"] = wl.flops_per_step() / (mo["ms_per_step"] * 1e-3) / 1e12
             others[name] = entry
