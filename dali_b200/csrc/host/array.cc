@@ -10,6 +10,7 @@
 #include <cstring>
 #include <fstream>
 #include <sstream>
+#include <unordered_set>
 
 #include "../../../include/dali_b200.h"
 #include "dali/array/op.h"
@@ -677,14 +678,36 @@ Array::operator double() const { return scalar_value<double>(); }
 Array::operator int() const { return scalar_value<int>(); }
 
 // ------------------------------------------------------------------ assignment
+// Does the value `a` read, through any handle in its tree (pending assignments included), the state `s`?  Handles
+// share their state, so once a new pending expression is installed in `s` every such handle names IT: a value that
+// reads the array it is assigned to (w -= step * dw with dw += w * ... still pending) would then read itself.
+static bool reaches_state(const Array& a, const Array::ArrayState* s, std::unordered_set<const Expression*>& seen, int depth = 0) {
+    if (a.is_stateless() || depth > 256) return false;
+    if (a.state().get() == s) return true;
+    const Expression* e = a.expression().get();
+    if (!seen.insert(e).second) return false;
+    for (const Array& arg : e->arguments_)
+        if (reaches_state(arg, s, seen, depth + 1)) return true;
+    return false;
+}
+static bool reads_itself(const Array& left, const Array& right) {
+    std::unordered_set<const Expression*> seen;
+    return reaches_state(right, left.state().get(), seen);
+}
+
 Array& Array::assign(const Array& other) {
     require_state(other, "assign");
     if (is_stateless()) {
         Array fresh(other.shape(), other.dtype(), other.preferred_device());
         state_ = fresh.state_;
     }
-    Array dest(expression());    // a new handle on what this Array is now
-    set_expression(std::make_shared<Assignment>(dest, OPERATOR_T_EQL, other));
+    // runs now, for the reasons given at inplace() below.  A view of a lazy value is a place once that value has been
+    // evaluated into a buffer (the handles on its state then name the buffer, lower.cc:writable_view)
+    if (expression()->kind_ == N_VIEW) set_expression(lazy::writable_view(*this).expression());
+    if (expression()->kind_ != N_BUFFER && expression()->kind_ != N_GATHER && expression()->kind_ != N_GATHER_ROWS) eval(false);
+    lazy::evaluate_shared_values(other);
+    Array update(std::make_shared<Assignment>(Array(expression()), OPERATOR_T_EQL, other));
+    update.eval(false);
     return *this;
 }
 void Array::copy_from(const Array& other) { assign(other); eval(false); }
@@ -696,16 +719,24 @@ void Array::clear() {
     else assign(Array(0.0));
 }
 
-static Array& inplace(Array& left, OPERATOR_T op, const Array& right) {
+// left (op)= right.  An update of a PLACE (a buffer, a view of one, a gather of one) runs when the statement is
+// written, not when the array is next read: the arrays the right-hand side reads may be overwritten by the
+// statements that follow (a solver clears the gradient right after the update that read it), and handles share
+// their state, so a pending update would read what they hold later.  The reference leaves such updates pending
+// (dali/array/array.cpp:722-726) and its own solvers then read cleared gradients.  With the update run the lazy
+// values below it that other handles name too (a solver's running averages) and, when the right-hand side is a
+// named lazy value (`named`: passed as an lvalue), that value itself are evaluated in place: they read the same arrays.
+// A lazy left-hand side is not a place: the operator is folded into its expression, as in the reference
+// (dali/array/jit/jit.cpp:1052-1078).
+static Array& inplace(Array& left, OPERATOR_T op, const Array& right, bool named = false) {
     DALI_ASSERT(!left.is_stateless(), "in-place operation on a stateless Array");
-    if (op == OPERATOR_T_LSE) {
-        Array r = op::autoreduce_assign(left, right);
-        left.set_expression(r.expression());
-        return left;
-    }
-    if (!left.is_assignable()) {
-        // a lazy value, not a place: fold the operator into the expression
-        // (dali/array/jit/jit.cpp:1052-1078, replace_assign_with_inplace)
+    if (left.expression()->kind_ == N_VIEW) left.set_expression(lazy::writable_view(left).expression());
+    if (!left.is_assignable() && !reads_itself(left, right)) {
+        if (op == OPERATOR_T_LSE) {
+            Array r = op::autoreduce_assign(left, right);
+            left.set_expression(r.expression());
+            return left;
+        }
         Array cur(left.expression());
         Array res;
         switch (op) {
@@ -718,13 +749,22 @@ static Array& inplace(Array& left, OPERATOR_T op, const Array& right) {
         left.set_expression(res.expression());
         return left;
     }
-    Array dest(left.expression());
-    left.set_expression(std::make_shared<Assignment>(dest, op, right));
+    if (left.expression()->kind_ != N_BUFFER && left.expression()->kind_ != N_GATHER && left.expression()->kind_ != N_GATHER_ROWS)
+        left.eval(false);                      // a pending assignment, or a lazy value that reads itself below
+    if (!right.is_stateless()) {
+        lazy::evaluate_shared_values(right);
+        if (named && !right.is_buffer() && right.expression()->kind_ != N_SCALAR) right.eval(false);
+    }
+    Array update = op == OPERATOR_T_LSE ? op::autoreduce_assign(left, right)
+                                        : Array(std::make_shared<Assignment>(Array(left.expression()), op, right));
+    update.eval(false);
     return left;
 }
 #define DALI_DEFINE_INPLACE(SYMBOL, OP)                                                             \
-    Array& operator SYMBOL(Array& left, const Array& right) { return inplace(left, OP, right); }    \
-    void operator SYMBOL(Array&& left, const Array& right) { Array l(left); inplace(l, OP, right); l.eval(false); }
+    Array& operator SYMBOL(Array& left, const Array& right) { return inplace(left, OP, right, true); }    \
+    Array& operator SYMBOL(Array& left, Array&& right) { return inplace(left, OP, right, false); }         \
+    void operator SYMBOL(Array&& left, const Array& right) { Array l(left); inplace(l, OP, right, true); l.eval(false); }  \
+    void operator SYMBOL(Array&& left, Array&& right) { Array l(left); inplace(l, OP, right, false); l.eval(false); }
 DALI_DEFINE_INPLACE(+=, OPERATOR_T_ADD)
 DALI_DEFINE_INPLACE(-=, OPERATOR_T_SUB)
 DALI_DEFINE_INPLACE(*=, OPERATOR_T_MUL)

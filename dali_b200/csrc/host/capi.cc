@@ -296,11 +296,11 @@ int dali_array_assign(dali_array_t dest, int op_code, dali_array_t value) {
     return guard([&]() {
         switch (op_code) {
             case 0: dest->a.assign(value->a); break;
-            case 1: dest->a += value->a; break;
-            case 2: dest->a -= value->a; break;
-            case 3: dest->a *= value->a; break;
-            case 4: dest->a /= value->a; break;
-            case 5: dest->a <<= value->a; break;
+            case 1: dest->a += Array(value->a); break;      // (a handle says nothing about being named: fused like a temporary)
+            case 2: dest->a -= Array(value->a); break;
+            case 3: dest->a *= Array(value->a); break;
+            case 4: dest->a /= Array(value->a); break;
+            case 5: dest->a <<= Array(value->a); break;
             default: throw std::runtime_error("unknown assignment operator code");
         }
     });

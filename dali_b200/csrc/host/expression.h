@@ -149,6 +149,8 @@ void run_assignment(const Array& dest, OPERATOR_T op, const Array& value);
 // dest when it is a buffer (or a scatter); for a view of a lazy value: that value evaluated into a buffer (all
 // handles that share its state see the buffer from now on) and the same view of the buffer (array.cc)
 Array writable_view(const Array& dest);
+// evaluates, in place, every lazy value below `value` that a second handle names
+void evaluate_shared_values(const Array& value);
 // Evaluates several lazy arrays of one shape in one kernel where their trees allow it (an extension: the
 // reference evaluates one Array per kernel); otherwise one after the other.  Does not synchronise.
 void eval_together(const std::vector<Array>& arrays);

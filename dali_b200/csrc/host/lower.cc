@@ -19,6 +19,7 @@
 #include <cmath>
 #include <cstring>
 #include <map>
+#include <unordered_map>
 #include <set>
 #include <sstream>
 
@@ -834,6 +835,50 @@ void split_few_long_row_reductions(const Array& a, int depth = 0) {
     }
 }
 
+// A lazy value that several handles name and whose tree has grown large is evaluated once, in place, instead of being
+// re-derived inside every kernel that reads it.  What this bounds: state that is carried from step to step as a lazy
+// expression of its own previous value (m = b1 * m + (1 - b1) * g in the reference's solvers,
+// dali/tensor/op/solver_updates/adam.cpp:31-34, never evaluated by the caller) would otherwise make every step's
+// program longer than the last one's, each a new kernel to compile.  Small shared values (the exp of a softmax, the
+// c' of an LSTM cell) stay fused.
+// "Large" is measured as depth (the longest chain of nodes): history makes a tree deeper with every step, while the
+// wide trees that should stay fused (an LSTM cell's gating: depth 9) do not get deep.
+// When one shared value has grown past the limit, every shared value of the tree that is more than a couple of nodes
+// deep is evaluated with it: the carried states of a solver then all restart from buffers in the same step, and the
+// steps that follow repeat a handful of program shapes instead of walking through every combination of phases.
+constexpr int kSharedDepthLimit = 16, kSharedDepthFloor = 4;
+int shared_depth(const Array& a, std::unordered_map<const Expression*, int>& depth_of, bool* over, int level = 0) {
+    if (a.is_stateless() || level > 256) return 0;
+    Expression* e = a.expression().get();
+    if (e->kind_ == N_BUFFER || e->kind_ == N_SCALAR || e->kind_ == N_IOTA || e->kind_ == N_ASSIGN) return 0;
+    auto it = depth_of.find(e);
+    if (it != depth_of.end()) return it->second;
+    int d = 0;
+    for (const Array& arg : e->arguments_) d = std::max(d, shared_depth(arg, depth_of, over, level + 1));
+    d += 1;
+    if (level > 0 && d >= kSharedDepthLimit && a.handle_count() > 1) *over = true;
+    depth_of[e] = d;
+    return d;
+}
+void evaluate_shared(const Array& a, const std::unordered_map<const Expression*, int>& depth_of, int floor, int level = 0) {
+    if (a.is_stateless() || level > 256) return;
+    Expression* e = a.expression().get();
+    auto it = depth_of.find(e);
+    if (it == depth_of.end()) return;                      // a leaf, or evaluated on the way here
+    const int d = it->second;
+    for (const Array& arg : e->arguments_) evaluate_shared(arg, depth_of, floor, level + 1);
+    if (level > 0 && d >= floor && a.handle_count() > 1 && !a.is_buffer()) {
+        a.eval(false);
+        ++tl_stats.temporaries;
+    }
+}
+void trim_shared_history(const Array& value) {
+    std::unordered_map<const Expression*, int> depth_of;
+    bool over = false;
+    shared_depth(value, depth_of, &over);
+    if (over) evaluate_shared(value, depth_of, kSharedDepthFloor);
+}
+
 // Starts the host -> device copies of the buffers a tree reads before the tree is lowered: the copies (asynchronous
 // from page-locked memory) then run while the host builds the program.  A gather's or scatter's source is copied as
 // a whole too, as the launch would.
@@ -850,6 +895,17 @@ void prefetch_inputs(const Array& a, const memory::Device& device, int depth = 0
 }
 
 }  // namespace
+
+// Every lazy value inside `value` that another handle also names is evaluated in place (see array.cc: an update that
+// reads its own destination runs at once, and the values it is built from -- a solver's running averages, rebound
+// every step to an expression of the gradient -- must be computed while the arrays they read still hold what they held
+// when the statements were written).
+void evaluate_shared_values(const Array& value) {
+    std::unordered_map<const Expression*, int> depth_of;
+    bool over = false;
+    shared_depth(value, depth_of, &over);
+    evaluate_shared(value, depth_of, 1);
+}
 
 void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) {
     DALI_ASSERT(!dest_in.is_stateless() && !value_in.is_stateless(), "assignment with a stateless Array");
@@ -930,6 +986,7 @@ void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) 
         return;
     }
     split_few_long_row_reductions(value);
+    trim_shared_history(value);
 
     // ---- a running reduction at the root has its own kernel
     if (value.expression()->kind_ == N_SCAN && dest.is_buffer()) {

@@ -158,6 +158,7 @@ class Array {
     expression_ptr expression() const;
     void set_expression(expression_ptr) const;
     std::shared_ptr<ArrayState> state() const { return state_; }
+    long handle_count() const { return state_.use_count(); }     // Arrays (user variables, node arguments) that share this state
     std::string expression_name() const;
     std::string full_expression_name() const;
 
@@ -296,9 +297,13 @@ class Array {
 };
 bool operator==(const Array& left, const Array& right);
 
+// (the Array&& forms take a right-hand side that is a temporary: an unnamed expression is fused into the update,
+// a named lazy value is evaluated in place first -- see array.cc:inplace)
 #define DALI_DECLARE_ARRAY_INTERACTION_INPLACE(SYMBOL) \
     Array& operator SYMBOL(Array& left, const Array& right); \
-    void operator SYMBOL(Array&& left, const Array& right);
+    Array& operator SYMBOL(Array& left, Array&& right); \
+    void operator SYMBOL(Array&& left, const Array& right); \
+    void operator SYMBOL(Array&& left, Array&& right);
 DALI_DECLARE_ARRAY_INTERACTION_INPLACE(+=)
 DALI_DECLARE_ARRAY_INTERACTION_INPLACE(-=)
 DALI_DECLARE_ARRAY_INTERACTION_INPLACE(*=)

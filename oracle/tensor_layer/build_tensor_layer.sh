@@ -16,8 +16,8 @@
 # Nothing of the reference is written anywhere but oracle/_ref/ (git-ignored).
 # Left out: op/cost.cpp (does not compile against the reference's own headers
 # either: op::eltmax, three-argument op::softmax and Array::insert_broadcast_axis
-# do not exist there), op/spatial.cpp (convolution / pooling: cuDNN side of the
-# reference) and solver.cpp.
+# do not exist there) and op/spatial.cpp (convolution / pooling: cuDNN side of the
+# reference).
 set -euo pipefail
 
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
@@ -53,12 +53,16 @@ mkdir -p "$OUT" "$STAGE/obj" "$STAGE/inc/dali/array/gemm" "$STAGE/inc/dali/array
 ln -s "$REF/dali/tensor" "$STAGE/inc/dali/tensor"
 ln -s "$REF/dali/array/gemm/tensordot_as_dot.h" "$STAGE/inc/dali/array/gemm/tensordot_as_dot.h"
 ln -s "$REF/dali/array/op/spatial_enums.h" "$STAGE/inc/dali/array/op/spatial_enums.h"
-# <cstddef> force-included: dali/tensor/tape.h names size_t without including it
-INC="-include cstddef -I$ROOT/dali_b200/host/include -I$HERE/include -I$STAGE/inc"
+# force-included standard headers: dali/tensor/tape.h names size_t, solver.cpp std::transform and
+# solver_updates/adam.cpp std::pow / sqrt without including <cstddef>, <algorithm>, <cmath>
+INC="-include cstddef -include algorithm -include cmath -I$ROOT/dali_b200/host/include -I$HERE/include -I$STAGE/inc"
 
 SRCS="dali/tensor/tape.cpp dali/tensor/tensor.cpp dali/tensor/op/unary.cpp dali/tensor/op/binary.cpp
       dali/tensor/op/reducers.cpp dali/tensor/op/dot.cpp dali/tensor/op/reshape.cpp dali/tensor/op/composite.cpp
-      dali/tensor/op/other.cpp dali/tensor/op/dropout.cpp dali/array/gemm/tensordot_as_dot.cpp"
+      dali/tensor/op/other.cpp dali/tensor/op/dropout.cpp dali/array/gemm/tensordot_as_dot.cpp
+      dali/tensor/solver.cpp dali/tensor/op/solver_updates/sgd.cpp dali/tensor/op/solver_updates/adagrad.cpp
+      dali/tensor/op/solver_updates/rmsprop.cpp dali/tensor/op/solver_updates/adadelta.cpp
+      dali/tensor/op/solver_updates/adam.cpp dali/tensor/op/solver_updates/clip_and_regularize.cpp"
 pids=""
 for src in $SRCS; do
     obj="$STAGE/obj/$(echo "$src" | tr '/' '_').o"

@@ -12,12 +12,14 @@
 #include <cmath>
 #include <cstdio>
 #include <functional>
+#include <memory>
 #include <string>
 #include <vector>
 
 #include "dali/array/array.h"
 #include "dali/array/op.h"
 #include "dali/tensor/op.h"
+#include "dali/tensor/solver.h"
 #include "dali/tensor/tape.h"
 #include "dali/tensor/tensor.h"
 #include "dali/utils/random.h"
@@ -399,6 +401,50 @@ static void tape_and_training() {
     CHECK((int)Array(op::all_close(W.w, W_true.w, 1e-3)) != 0);
 }
 
+// dali/tensor/tests.cpp:876-955 test_solver_trivial: every solver of dali/tensor/solver.cpp drives the norm of a
+// five-element vector below 0.1 within 200 steps (the reference's step sizes)
+static void solvers() {
+    typedef std::function<std::shared_ptr<solver::AbstractSolver>(vector<Tensor>)> create_solver_t;
+    struct Case { const char* name; create_solver_t create; };
+    const vector<Case> cases = {
+        {"sgd", [](vector<Tensor> p) { auto s = std::make_shared<solver::SGD>(p); s->step_size = 0.3; s->clip_norm = 0; return s; }},
+        {"adagrad", [](vector<Tensor> p) { auto s = std::make_shared<solver::AdaGrad>(p); s->step_size = 1; s->clip_norm = 0.0; return s; }},
+        {"rmsprop", [](vector<Tensor> p) { auto s = std::make_shared<solver::RMSProp>(p); s->step_size = 0.1; s->clip_norm = 0.0; return s; }},
+        {"rmspropmomentum", [](vector<Tensor> p) { auto s = std::make_shared<solver::RMSPropMomentum>(p); s->step_size = 0.5; s->momentum = 0.2; return s; }},
+        {"adadelta", [](vector<Tensor> p) { auto s = std::make_shared<solver::AdaDelta>(p); s->clip_norm = 0.0; s->rho = 0.1; return s; }},
+        {"adam", [](vector<Tensor> p) { auto s = std::make_shared<solver::Adam>(p); s->step_size = 0.005; return s; }},
+    };
+    const double initial[5] = {8.98117318, 1.38778046, -2.56764083, 7.99331316, 0.0};
+    for (const Case& c : cases) {
+        ++checks;
+        try {
+            graph::clear();
+            Tensor X({5}, DTYPE_DOUBLE);
+            for (int i = 0; i < 5; ++i) X.w(i).assign(initial[i]).eval();
+            vector<Tensor> params({X});
+            auto solver = c.create(params);
+            double last_error = (double)Array(X.L2_norm().w);
+            bool started_high = last_error > 10.0;
+            graph::clear();
+            int iter = 0;
+            for (; iter < 200 && last_error >= 0.1; ++iter) {
+                Tensor error = X.L2_norm();
+                error.grad();
+                graph::backward();
+                solver->step(params);
+                last_error = (double)Array(error.w);
+            }
+            const bool ok = started_high && last_error < 0.1;
+            std::printf("case solver %s: %s (norm %.4g after %d steps)\n", c.name, ok ? "ok" : "wrong", last_error, iter);
+            if (!ok) ++failures;
+        } catch (const std::runtime_error& e) {
+            graph::clear();
+            std::printf("case solver %s: throws\n  (%s)\n", c.name, e.what());
+            ++thrown;
+        }
+    }
+}
+
 // dali/tensor/tests.cpp:225-241 TensorIOTests.save_load_test
 static void save_and_load(const std::string& dir) {
     Tensor A = uniform(-2, 2, {3, 5});
@@ -429,6 +475,7 @@ int main(int argc, char** argv) {
     section("views", views_and_reshapes);
     section("lstm", lstm_cell_gradients);
     section("tape", tape_and_training);
+    section("solvers", solvers);
     section("io", [&dir]() { save_and_load(dir); });
     std::printf("{\"checks\": %d, \"failures\": %d, \"throws\": %d}\n", checks, failures, thrown);
     return failures == 0 ? 0 : 1;

@@ -203,19 +203,28 @@ def test_lstm_gating_on_slices_is_one_map_kernel():
 def test_inplace_and_scatter_lowering():
     a = Array(np.zeros((8, 8), np.float32))
     b = Array(np.zeros((8, 8), np.float32))
+    # an update of a place runs when it is written (the arrays it reads may change afterwards), as one kernel
+    before = lazy_stats()
     a += b * 2.0
-    assert launched(a) == {"kernels": 1, "gemms": 0, "temporaries": 0}
+    assert {k: lazy_stats()[k] - before[k] for k in before} == {"kernels": 1, "gemms": 0, "temporaries": 0}
+    assert launched(a) == {"kernels": 0, "gemms": 0, "temporaries": 0}
     assert "st 1 add" in last_ir() or "st 0 add" in last_ir()
     dest = Array.zeros((3,), DTYPE_INT32)
     idx = Array(np.array([0, 0, 1, 1, 1, 2], np.int32))
     gathered = dest[idx]
+    before = lazy_stats()
     gathered += 1
-    assert launched(gathered) == {"kernels": 1, "gemms": 0, "temporaries": 0}
+    assert {k: lazy_stats()[k] - before[k] for k in before} == {"kernels": 1, "gemms": 0, "temporaries": 0}
     assert "stx" in last_ir() and " add " in last_ir()
     lse = Array.zeros((2, 1), DTYPE_INT32)
     lse <<= Array.ones((2, 5), DTYPE_INT32)
-    lse.eval()
     assert "red sum" in last_ir()
+    # a lazy value is not a place: the operator is folded into its expression and nothing runs
+    lazy = op.tanh(a)
+    before = lazy_stats()
+    lazy += b
+    assert lazy_stats() == before
+    assert launched(lazy) == {"kernels": 1, "gemms": 0, "temporaries": 0}
 
 
 def test_index_ops_are_lazy_and_fuse_into_one_kernel():
@@ -312,8 +321,8 @@ def test_two_equal_subtrees_keep_their_own_temporaries():
         e = op.exp(a - op.max(a, [-1], True))
         return e / op.sum(e, [-1], True)
 
-    close = op.lessthanequal(op.abs(op.subtract(softmax(), softmax())), Array(1e-6, DTYPE_DOUBLE))
-    p = op.prod(close)
+    # (built in one expression: a large value that a second handle also names would be evaluated on its own first)
+    p = op.prod(op.lessthanequal(op.abs(op.subtract(softmax(), softmax())), Array(1e-6, DTYPE_DOUBLE)))
     assert launched(p) == {"kernels": 5, "gemms": 0, "temporaries": 4}
     ir = last_ir()
     assert ir.count("arg ") == 6 and ir.count(" ld ") == 5          # a, 2 maxima, 2 sums read; one result written
@@ -328,3 +337,36 @@ def test_prefix_slice_of_a_lazy_value_is_not_a_pure_reindexing():
     assert launched(w) == {"kernels": 1, "gemms": 0, "temporaries": 0}
     t = op.tanh(a).transpose()                      # a real permutation still is peeled: one kernel, transposed store
     assert launched(t) == {"kernels": 1, "gemms": 0, "temporaries": 0}
+
+
+def test_an_update_that_reads_the_array_it_updates_runs_at_once():
+    """w -= 0.1 * dw while dw += 2 * w is still pending: handles share their state, so a pending update of w
+    installed in w's state would be read back by dw's pending value (a cycle; the reference's solvers build exactly
+    this, dali/tensor/solver.cpp + op/solver_updates/sgd.cpp).  Such an update runs immediately instead."""
+    w = Array(np.ones((4, 5), np.float32))
+    dw = Array(np.zeros((4, 5), np.float32))
+    dw += w * 2.0
+    before = lazy_stats()
+    w -= dw * 0.1                       # reads dw, whose pending value reads w
+    ran = {k: lazy_stats()[k] - before[k] for k in before}
+    assert ran["kernels"] >= 1          # not left pending
+    assert launched(w) == {"kernels": 0, "gemms": 0, "temporaries": 0}
+    x = Array(np.ones((3,), np.float32))
+    x.assign(op.tanh(x) + x)            # x = f(x)
+    assert launched(x) == {"kernels": 0, "gemms": 0, "temporaries": 0}
+
+
+def test_large_shared_lazy_values_are_evaluated_once():
+    """State carried from step to step as a lazy expression of its own previous value (the m and v of the reference's
+    Adam, never evaluated by the caller) must not make every step's program longer than the last one's: a value that
+    another handle names and whose tree has grown past a couple of dozen nodes is evaluated in place."""
+    g = Array(np.ones((8, 8), np.float32))
+    w = Array(np.ones((8, 8), np.float32))
+    m = Array(np.zeros((8, 8), np.float32))
+    sizes = []
+    for step in range(12):
+        m = m * 0.9 + g * 0.1 + op.square(g) * 0.01          # rebinding: m is a lazy tree over the previous m
+        w -= m * 0.5
+        w.eval()
+        sizes.append(len(last_ir().splitlines()))
+    assert max(sizes) < 80 and max(sizes[6:]) <= max(sizes[:6])   # bounded, not growing with the step count

@@ -193,10 +193,9 @@ def test_gather_and_scatter(golden):
     # scatter_simple
     dest = Array.zeros((3,), DTYPE_INT32)
     gathered = dest[Array(np.array([0, 0, 1, 1, 1, 2], np.int32))]
-    gathered += 1
-    gathered.eval()
-    assert not gathered.is_buffer()
+    gathered += 1                      # the scatter runs when it is written
     np.testing.assert_array_equal(dest.numpy(), [2, 3, 1])
+    np.testing.assert_array_equal(gathered.numpy(), [2, 2, 3, 3, 3, 1])      # the gather reads what is there now
     # scatter_to_rows_simple
     vals = np.array([0, 0, 1, 1, 1, 2], np.int32)
     dest = Array.zeros((7, 3), DTYPE_INT32)
@@ -509,3 +508,15 @@ def test_reductions_over_few_very_long_rows():
     np.testing.assert_array_equal(op.min(Array(b_np), [-1]).numpy(), b_np.min(2))
     one = Array(a_np[:1])
     assert abs(float(op.sum(one, [-1]).numpy()[0]) - want[0]) <= 1e-5 * np.abs(a_np[0]).sum()
+
+
+def test_update_reading_its_own_destination_sees_the_old_value():
+    w_np = np.arange(20, dtype=np.float32).reshape(4, 5)
+    w, dw = Array(w_np), Array(np.ones((4, 5), np.float32))
+    dw += w * 2.0                       # pending
+    w -= dw * 0.1                       # reads dw, which reads w: runs at once on the old w
+    np.testing.assert_allclose(w.numpy(), w_np - 0.1 * (1.0 + 2.0 * w_np), rtol=1e-6)
+    np.testing.assert_allclose(dw.numpy(), 1.0 + 2.0 * w_np, rtol=1e-6)
+    x = Array(w_np[0].copy())
+    x.assign(op.tanh(x) + x)
+    np.testing.assert_allclose(x.numpy(), np.tanh(w_np[0]) + w_np[0], rtol=1e-6)
