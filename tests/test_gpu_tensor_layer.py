@@ -3,7 +3,7 @@ tensor_ops) built UNCHANGED from the reference checkout against this back end's 
 (oracle/tensor_layer/build_tensor_layer.sh -> oracle/_ref/), driven by tests/cpp/tensor_layer_smoke.cpp:
 analytic gradients from the reference's tape against central finite differences in double precision
 (tolerances per case in the program, the reference's own: 1e-5 .. 1e-2), an LSTM cell forward and backward
-at [256, 1024], a least-squares fit by gradient descent, .npy round trip.
+at [256, 1024], a least-squares fit by gradient descent, the reference's six solvers, .npy round trip.
 
 The binaries are made where the reference checkout is present; a machine without them skips."""
 import json
