@@ -226,12 +226,14 @@ static void dot_gradients() {
     gradient_same("inner", [](vector<Tensor>& xs) { return tensor_ops::inner(xs[0], xs[1]); }, {u, u2}, 1e-4);
     gradient_same("matrix_vector_dot", [](vector<Tensor>& xs) { return tensor_ops::matrix_vector_dot(xs[0], xs[1]); },
                   {A, uniform(-2.0, 2.0, {5})}, 1e-4);
+    gradient_same("dot of transposes", [](vector<Tensor>& xs) { return tensor_ops::dot(xs[1].transpose(), xs[0].transpose()); },
+                  {A, B}, 1e-4);
     Tensor S = uniform(-2.0, 2.0, {4, 4});
     gradient_same("self_dot", [](vector<Tensor>& xs) { return tensor_ops::dot(xs[0], xs[0]); }, {S}, 1e-4);
     Tensor T3 = uniform(-1.0, 1.0, {2, 3, 4}), T3b = uniform(-1.0, 1.0, {4, 3, 2});
+    gradient_same("tensordot", [](vector<Tensor>& xs) { return tensor_ops::tensordot(xs[0], xs[1], {1, 2}, {1, 0}); }, {T3, T3b}, 1e-4);
     {
-        // tensordot goes through dimshuffle + reshape of its operands (tensordot_as_dot.h): values only, no gradient
-        // reaches the operands through those temporary views (see views_and_reshapes)
+        // tensordot goes through dimshuffle + reshape of its operands (tensordot_as_dot.h): its values against loops
         graph::NoBackprop nb;
         Tensor td = tensor_ops::tensordot(T3, T3b, {1, 2}, {1, 0});
         vector<double> a = to_host(T3.w), b = to_host(T3b.w), got = to_host(td.w);
@@ -283,6 +285,15 @@ static void views_and_reshapes() {
         CHECK(std::fabs((double)Array(A.dw.sum()) - 24.0) < 1e-12);
         A.dw.clear();
     }
+    // gradients through views: the backward pass adds into a temporary handle on a view of the parent's dw; the update
+    // runs when it is written on this back end, so it lands (in the reference it stays pending in that handle and is
+    // lost with it, which is why the reference disables these tests)
+    gradient_same("slice", [](vector<Tensor>& xs) { return Tensor(xs[0][Slice(1, 3)]).tanh(); }, {A}, 1e-4);
+    gradient_same("column slices", [](vector<Tensor>& xs) {
+        return xs[0].pluck_axis(1, Slice(0, 3)) * xs[0].pluck_axis(1, Slice(3, 6)); }, {A}, 1e-4);
+    gradient_same("transpose", [](vector<Tensor>& xs) { return tensor_ops::dot(xs[0].transpose(), xs[0]); }, {A}, 1e-4);
+    gradient_same("reshape", [](vector<Tensor>& xs) { return xs[0].reshape({3, 8}).square(); }, {A}, 1e-4);
+    gradient_same("ravel", [](vector<Tensor>& xs) { return xs[0].ravel().sigmoid(); }, {A}, 1e-4);
     gradient_same("hstack", [](vector<Tensor>& xs) { return tensor_ops::hstack({xs[0], xs[1]}).square(); }, {A, B}, 1e-4);
     Tensor C = uniform(-2.0, 2.0, {2, 6});
     gradient_same("vstack", [](vector<Tensor>& xs) { return tensor_ops::vstack({xs[0], xs[1]}).tanh(); }, {A, C}, 1e-4);
@@ -306,8 +317,24 @@ static Tensor lstm_cell(vector<Tensor>& p) {
     return o * c_new.tanh();
 }
 
+// the same cell with one [H, 4H] weight matrix per input and the gates as column slices of one product (the
+// benchmark's layout): gradients flow through the slices
+static Tensor lstm_cell_sliced(vector<Tensor>& p, int H) {
+    Tensor gates = tensor_ops::multiple_dot_with_bias({p[0], p[1]}, {p[3], p[4]}, p[5]);
+    Tensor i = gates.pluck_axis(1, Slice(0, H)).sigmoid(), f = gates.pluck_axis(1, Slice(H, 2 * H)).sigmoid();
+    Tensor o = gates.pluck_axis(1, Slice(2 * H, 3 * H)).sigmoid(), g = gates.pluck_axis(1, Slice(3 * H, 4 * H)).tanh();
+    Tensor c_new = f * p[2] + i * g;
+    return o * c_new.tanh();
+}
+
 static void lstm_cell_gradients() {
     utils::random::set_seed(105);
+    {
+        const int B = 3, H = 4;
+        vector<Tensor> p = {uniform(-1, 1, {B, H}), uniform(-1, 1, {B, H}), uniform(-1, 1, {B, H}), uniform(-0.5, 0.5, {H, 4 * H}),
+                            uniform(-0.5, 0.5, {H, 4 * H}), uniform(-0.5, 0.5, {4 * H})[Broadcast()]};
+        gradient_same("lstm cell, sliced gates", [H](vector<Tensor>& xs) { return lstm_cell_sliced(xs, H); }, p, 1e-4);
+    }
     const int B = 3, H = 4;
     vector<Tensor> p = {uniform(-1, 1, {B, H}), uniform(-1, 1, {B, H}), uniform(-1, 1, {B, H})};
     for (int k = 0; k < 4; ++k) {
