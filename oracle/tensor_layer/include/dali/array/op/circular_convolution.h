@@ -1,8 +1,2 @@
-// Declaration only; the definition in shims.cpp throws (reference: dali/array/op/circular_convolution.h).
-#ifndef DALI_ARRAY_OP_CIRCULAR_CONVOLUTION_H
-#define DALI_ARRAY_OP_CIRCULAR_CONVOLUTION_H
-#include "dali/array/array.h"
-namespace op {
-Array circular_convolution(Array x, Array weights);
-}  // namespace op
-#endif
+// resolves the reference's include path; the declarations live in off_path_ops.h
+#include "dali/array/op/off_path_ops.h"

@@ -7,8 +7,9 @@
 // reference's translation units link, and throw when reached.
 #include <stdexcept>
 
-#include "dali/array/op/circular_convolution.h"
-#include "dali/array/op/top_k.h"
+#include <string>
+
+#include "dali/array/op/off_path_ops.h"
 
 namespace {
 [[noreturn]] void off_path(const char* name) {
