@@ -478,6 +478,8 @@ struct SplitParts {
     int64_t offset = 0, rows = 0, cols = 0, ld = 0;
     bool transposed = false;
     void *hi = nullptr, *lo = nullptr;
+    std::shared_ptr<SplitParts> older;      // the split kept before this one: a weight matrix is read as W going forward and
+                                            // as W^T going backward, and both splits stay valid while W does not change
     ~SplitParts() {
         if (hi) dalib200_free(device, hi, bytes);
         if (lo) dalib200_free(device, lo, bytes);
@@ -505,11 +507,14 @@ std::shared_ptr<SplitParts> split_operand(BufferView* b, bool transpose, memory:
     if (ld < cols) return nullptr;      // (a broadcast row or column)
     if (cols % 4 || ld % 4 || (transpose && rows % 4) || (b->offset_ % 4)) return nullptr;
     auto& slot = b->memory_->derived_data();
+    std::shared_ptr<SplitParts> previous;
     if (slot && b->memory_->derived_version() == b->memory_->version()) {
-        auto cached = std::static_pointer_cast<SplitParts>(slot);
-        if (cached->offset == b->offset_ && cached->rows == rows && cached->cols == cols && cached->ld == ld &&
-            cached->transposed == transpose && cached->device == dev)
-            return cached;
+        previous = std::static_pointer_cast<SplitParts>(slot);
+        for (std::shared_ptr<SplitParts> cached = previous; cached; cached = cached->older)
+            if (cached->offset == b->offset_ && cached->rows == rows && cached->cols == cols && cached->ld == ld &&
+                cached->transposed == transpose && cached->device == dev)
+                return cached;
+        previous->older.reset();            // two generations at most
     }
     const float* x = (const float*)b->memory_->data(device, memory::AM_READONLY) + b->offset_;
     if (((uintptr_t)x) & 15) return nullptr;
@@ -528,6 +533,7 @@ std::shared_ptr<SplitParts> split_operand(BufferView* b, bool transpose, memory:
         check(dalib200_gemm_split_tf32(dev, nullptr, x, rows, cols, ld, transpose ? 1 : 0, (float*)parts->hi, (float*)parts->lo),
               "dalib200_gemm_split_tf32");
     }
+    parts->older = previous;                // (empty when the matrix has changed since)
     slot = parts;
     b->memory_->derived_version() = b->memory_->version();
     return parts;
