@@ -687,27 +687,28 @@ class Cumsum(Workload):
     kernel_name = "scan_rows_kernel<float, sum, 256 threads per row, 128-bit> (dalib200_scan)"
     e2e_api = "C ABI with caller-managed copies (page-locked host -> device, dalib200_scan, device -> page-locked host, sync)"
 
-    def __init__(self, *a):
+    def __init__(self, *a, shape=None):
         super().__init__(*a)
         import numpy as np
         self.np = np
         t = self.torch
         t.manual_seed(1234 + 6 + self.rank)
-        self.x = [t.rand(self.N, self.N, device="cuda") * 2 - 1 for _ in range(2)]    # 2 x 256 MiB > L2
-        self.out = t.empty(self.N, self.N, device="cuda")
+        self.R, self.C = shape or (self.N, self.N)      # --scan-shape R,C: other shapes of the same 256 MiB (profiling)
+        self.x = [t.rand(self.R, self.C, device="cuda") * 2 - 1 for _ in range(2)]    # 2 x 256 MiB > L2
+        self.out = t.empty(self.R, self.C, device="cuda")
         self.scaling = "weak"
         self.launches_per_step = 1
 
     def describe(self):
-        return {"workload": "op::cumsum over the last axis of fp32 [8192,8192] ~ U(-1,1) per GPU (inclusive)",
+        return {"workload": "op::cumsum over the last axis of fp32 [%d,%d] ~ U(-1,1) per GPU (inclusive)" % (self.R, self.C),
                 "l2": "two 256 MiB inputs alternate, 256 MiB output (768 MiB > L2)",
                 "parallelism": "rows sharded: each of %d GPU(s) scans its own rows, no collective" % self.world}
 
     def bytes_per_step(self):
-        return 2 * self.N * self.N * 4
+        return 2 * self.R * self.C * 4
 
     def launch_step(self, i, stream):
-        self.lib.scan(0, 0, 1, self.N, self.N, self.x[i % 2], self.out, device=self.device, stream=stream)
+        self.lib.scan(0, 0, 1, self.R, self.C, self.x[i % 2], self.out, device=self.device, stream=stream)
 
     def step(self, i):
         self.launch_step(i, self.stream)
@@ -717,9 +718,9 @@ class Cumsum(Workload):
 
     def e2e_setup(self):
         t = self.torch
-        self.hx = t.empty(self.N, self.N, pin_memory=True); self.hx.copy_(self.x[0])
-        self.hout = t.empty(self.N, self.N, pin_memory=True)
-        self.h2d = self.d2h = self.N * self.N * 4
+        self.hx = t.empty(self.R, self.C, pin_memory=True); self.hx.copy_(self.x[0])
+        self.hout = t.empty(self.R, self.C, pin_memory=True)
+        self.h2d = self.d2h = self.R * self.C * 4
 
     def e2e_step(self, i):
         # the C ABI with caller-managed copies (page-locked host -> device, scan, device -> page-locked host)
@@ -733,7 +734,7 @@ class Cumsum(Workload):
         import dali_oracle as oracle
         self.launch_step(0, self.stream)
         self.torch.cuda.synchronize()
-        rows = [0, 4097, self.N - 1]
+        rows = sorted({0, self.R // 2, self.R - 1})
         x = self.x[0][rows].cpu().numpy()
         want = self.np.cumsum(x.astype(self.np.float64), axis=1)
         bound = 1e-5 * self.np.cumsum(self.np.abs(x).astype(self.np.float64), axis=1)
@@ -744,11 +745,11 @@ class Cumsum(Workload):
     def cpu_baseline(self, tmpdir, reps):
         # the reference's CPU scan takes time quadratic in the row length (18 s for [2048,2048]): a few full-length rows
         m = 4
-        self.np.save(os.path.join(tmpdir, "x.npy"), self.x[0][:m].contiguous().cpu().numpy())
+        self.np.save(os.path.join(tmpdir, "x.npy"), self.x[0][:m, :8192].contiguous().cpu().numpy())
         times = run_ref_driver("scan", ["sum", "1", "x.npy", "out.npy"], min(reps, 3), tmpdir)
         if not times:
             return None
-        return {"ms": times, "bytes": 2 * m * self.N * 4, "cores": 1, "kind": "reference", "sample": "4 of the 8192 rows (full length 8192)"}
+        return {"ms": times, "bytes": 2 * m * 8192 * 4, "cores": 1, "kind": "reference", "sample": "4 rows of 8192 elements"}
 
 
 class TransposedMap(Workload):
@@ -1054,6 +1055,7 @@ def main():
     ap.add_argument("--workload", default="lstm", choices=sorted(WORKLOADS))
     ap.add_argument("--elements", type=int, default=0, help="chain: total elements (profiling on a small case)")
     ap.add_argument("--gemm-n", type=int, default=0, help="gemm: matrix size (profiling on a small case)")
+    ap.add_argument("--scan-shape", default="", help="scan: R,C instead of 8192,8192 (the variants for short and for few, very long rows)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-others", action="store_true")
@@ -1085,6 +1087,8 @@ def main():
             kw["total"] = args.elements
         if name == "gemm" and args.gemm_n:
             kw["n"] = args.gemm_n
+        if name == "scan" and args.scan_shape:
+            kw["shape"] = tuple(int(v) for v in args.scan_shape.split(","))
         return WORKLOADS[name](lib, torch, rank, world, dev_index, **kw)
 
     wl = build(args.workload)
