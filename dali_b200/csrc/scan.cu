@@ -115,10 +115,19 @@ __global__ void __launch_bounds__(kThreads) scan_rows_kernel(const T* __restrict
         for (long long base = begin; base < end; base += (long long)G * kItems) {
             const long long i0 = base + (long long)g * kItems;
             alignas(16) T v[kItems];
-            const bool whole = live && i0 + kItems <= end;
-            if (VEC && whole) {
+            // 128-bit pieces that lie inside the row go as one access each (a row of four floats is one piece), the
+            // ragged rest element by element
+            constexpr int kPer16 = 16 / (int)sizeof(T);
+            if (VEC) {
 #pragma unroll
-                for (int q = 0; q < kChunks; ++q) reinterpret_cast<uint4*>(v)[q] = reinterpret_cast<const uint4*>(x + i0)[q];
+                for (int q = 0; q < kChunks; ++q) {
+                    if (live && i0 + (q + 1) * kPer16 <= end) {
+                        reinterpret_cast<uint4*>(v)[q] = reinterpret_cast<const uint4*>(x + i0)[q];
+                    } else {
+#pragma unroll
+                        for (int k = q * kPer16; k < (q + 1) * kPer16; ++k) v[k] = (live && i0 + k < end) ? x[i0 + k] : Op::template init<T>();
+                    }
+                }
             } else {
 #pragma unroll
                 for (int k = 0; k < kItems; ++k) v[k] = (live && i0 + k < end) ? x[i0 + k] : Op::template init<T>();
@@ -153,9 +162,17 @@ __global__ void __launch_bounds__(kThreads) scan_rows_kernel(const T* __restrict
             const T offset = Op::apply(carry, before);
 #pragma unroll
             for (int k = 0; k < kItems; ++k) v[k] = Op::apply(offset, v[k]);
-            if (VEC && whole) {
+            if (VEC) {
 #pragma unroll
-                for (int q = 0; q < kChunks; ++q) reinterpret_cast<uint4*>(y + i0)[q] = reinterpret_cast<const uint4*>(v)[q];
+                for (int q = 0; q < kChunks; ++q) {
+                    if (live && i0 + (q + 1) * kPer16 <= end) {
+                        reinterpret_cast<uint4*>(y + i0)[q] = reinterpret_cast<const uint4*>(v)[q];
+                    } else {
+#pragma unroll
+                        for (int k = q * kPer16; k < (q + 1) * kPer16; ++k)
+                            if (live && i0 + k < end) y[i0 + k] = v[k];
+                    }
+                }
             } else {
 #pragma unroll
                 for (int k = 0; k < kItems; ++k)
