@@ -5,22 +5,27 @@
 One "step" is one pass of a fused expression over one batch of synthetic
 input.  Prints ONE JSON line (rank 0).  Workloads (the benchmark configurations):
 
-  lstm     (default, configuration 2) fused LSTM cell step, fp32 B=256 H=1024:
-           gates = dot(x,Wx)+dot(h,Wh)+b on the tensor cores (3xTF32, second GEMM
-           with "+ first + b" as epilogue), then the fused sigmoid/tanh gating
+  chain    (default, configuration 5: the largest one) sum(sigmoid(x*w+b) * exp(-x*x))
+           over 2^31 fp32 elements, sharded over the GPUs (strong scaling); the partial
+           sums of the ranks meet inside the kernel through peer memory (NCCL all-reduce
+           where the ranks cannot address one another)
   softmax  (config 1) exp(a - max(a,-1)) / sum(...) on fp32 [4096,1024]
-  reduce   (config 3) sum over axis 0 of fp32 [8192,8192] (the strided case)
+  lstm     (config 2) fused LSTM cell step, fp32 B=256 H=1024: one tcgen05 3xTF32 GEMM
+           accumulating x.Wx + h.Wh whose epilogue is the whole gating
+  reduce   (config 3) --reduce-op sum|max|argmax over --axis -1|0|all of fp32 [8192,8192];
+           rows sharded over the GPUs, axis 0 and all end in an all-reduce of the partials
+           ((value, index) pairs for argmax)
   gemm     (config 4) tanh(dot(A,B)+bias), bf16 8192^3, fp32 accumulate
-  chain    (config 5) sum(sigmoid(x*w+b) * exp(-x*x)) over 2^31 fp32 elements,
-           sharded over the GPUs with an all-reduce of the partial sums
-The default run also measures the other four briefly and reports them under
-"other_workloads".
+  gather   rows of a [65536,256] fp32 table picked by 2^20 int32 indices (op::gather)
+The default run also measures the others (all nine reductions) at every N and
+reports them under "other_workloads", each with its own roofline, clocks, end-to-end
+figure and (N = 1) CPU baseline.
 
 `value` is whole-job algorithmic GB/s with inputs resident in HBM; `e2e` is the
-same metric through dalib200_launch_host with pinned HOST buffers (copies
-inside the timed region); `roofline` relates the dominant kernel to the
-measured HBM copy bandwidth; `cpu_baseline` is the reference's own CPU path
-(oracle/_ref) on a bounded sample, timed on this box's host cores.
+same metric through the public call with pinned HOST buffers (copies inside the
+timed region); `roofline` relates the dominant kernel to the measured HBM copy
+bandwidth (or the measured bf16 GEMM rate); `cpu_baseline` is the reference's own
+CPU path (oracle/_ref) on a bounded sample, timed on this box's host cores.
 """
 import argparse
 import json
@@ -36,15 +41,16 @@ sys.path.insert(0, ROOT)
 SM_COUNT = 148
 L2_BYTES = 126 * 1024 * 1024
 FALLBACK_HBM_GBS = 6650.0          # earlier measurement on this pool, used if MEASURED_PEAKS.json is absent
+F32, F64, I32 = 0, 1, 2
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised
-# under profiles/ (bytes per ALGORITHMIC byte, so it scales with the launch size)
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu captures of the dominant kernels
+# (bytes per ALGORITHMIC byte, so it scales with the launch size)
 DRAM_TRAFFIC_PER_ALGO_BYTE = {
-    "chain": 1.0004,     # profiles/chain_sum_all_kernel.md
-    "softmax": 0.50,     # profiles/softmax_row_kernel.md: the 16 MiB output is still in L2 when the kernel ends
-    "reduce": 1.0002,    # profiles/reduce_8192_row_col_all_kernels.md
-    "scan": 0.905,       # profiles/scan_rows_kernel.md: the tail of the output is written back after the kernel ends
-    "transpose": 0.919,  # profiles/map_transposing_kernel.md: likewise
+    "chain": 1.0004,
+    "softmax": 0.50,     # the 16 MiB output is still in L2 when the kernel ends
+    "reduce": 1.0002,
+    "scan": 0.905,       # the tail of the output is written back after the kernel ends
+    "transpose": 0.919,  # likewise
 }
 
 
@@ -133,45 +139,67 @@ def run_ref_driver(case, args, reps, tmpdir):
 
 # ----------------------------------------------------------------------------- workloads
 class Workload:
+    """One benchmark configuration.  `config(world, **kw)` is the `config` object of the JSON line, a function of the
+    command line only (the reference arm prints the same one); `reference_case(np, tmp, **kw)` writes a bounded sample
+    of the workload for the reference's CPU path and names the driver case that runs it."""
     name = ""
-    dominant_kernel = ""
+    scaling = "weak"
+    dtype = "f32"
+    launches_per_step = 1
+    hbm_metric = True          # `value` counts bytes that cross HBM (False: operands that stay in L2, or a tensor-bound step)
 
     def __init__(self, lib, torch, rank, world, device):
         self.lib, self.torch, self.rank, self.world, self.device = lib, torch, rank, world, device
         self.stream = torch.cuda.current_stream().cuda_stream
+        self.peer = world > 1 and lib.comm_transport() == "nccl+peer"
 
-    def describe(self):
+    def bytes_per_step(self):          # algorithmic bytes one step moves on THIS rank
         raise NotImplementedError
 
-    # algorithmic bytes one step moves on THIS rank
-    def bytes_per_step(self):
-        raise NotImplementedError
+    def flops_per_step(self):
+        return 0
 
     def step(self, i):
-        raise NotImplementedError
-
-    def e2e_setup(self):
-        raise NotImplementedError
-
-    def e2e_step(self, i):
-        raise NotImplementedError
+        self.launch_step(i, self.stream)
 
     def graph_fn(self):
-        """launch(i, stream) of one step's kernels when the step has no host-side part, else None."""
-        return None
+        """launch(i, stream) of one step's kernels when every launch can be captured (NCCL calls are left eager)."""
+        return self.launch_step if (self.world == 1 or self.peer or not self.has_collective()) else None
+
+    def has_collective(self):
+        return False
 
     def dominant(self):
         """(kernel name, bound, algorithmic work per launch, launch(i, stream)) or None = the step itself."""
         return None
 
-    def flops_per_step(self):
-        return 0
+
+def _collective_note(world):
+    return ("; partial results meet in peer memory inside / right after the kernel (NCCL where ranks cannot address one another)"
+            if world > 1 else "")
 
 
 class Chain(Workload):
     """Benchmark configuration 5: long elementwise chain + all-axis sum, strong-scaled over the ranks."""
     name = "chain"
+    scaling = "strong"
     TOTAL = 1 << 31
+
+    @staticmethod
+    def config(world, total=None, **kw):
+        total = total or Chain.TOTAL
+        n = total // world
+        return {"workload": "C5 sum(sigmoid(x*w+b)*exp(-x*x)), fp32 x ~ N(0,1), 2^%d elements total, w=0.5 b=0.1" % (total.bit_length() - 1),
+                "elements_per_gpu": n, "l2": "input per launch (%d MiB) larger than L2, no flush" % (n * 4 >> 20),
+                "parallelism": "elements sharded over %d GPU(s)%s" % (world, "; the ranks' partial sums are exchanged through peer "
+                               "memory inside the kernel that computes them (NCCL all-reduce where ranks cannot address one another)" if world > 1 else "")}
+
+    @staticmethod
+    def reference_case(np, tmp, **kw):
+        m = 1 << 24
+        np.save(os.path.join(tmp, "x.npy"), np.random.default_rng(1234 + 4).standard_normal(m).astype(np.float32))
+        return {"case": "chain", "args": ["x.npy", "0.5", "0.1", "out.npy"], "bytes": m * 4, "cores": 1,
+                "sample": "2^24 elements per step (1/128 of the workload; the reference's generated loop is single-threaded and its int sizes cap a chunk at 2^28)"}
 
     def __init__(self, *a, total=None):
         super().__init__(*a)
@@ -179,46 +207,47 @@ class Chain(Workload):
         from dali_b200.ir import chain_sum_ir
         self.np = np
         t = self.torch
-        self.n = (total or self.TOTAL) // self.world
+        self.total = total or self.TOTAL
+        self.n = self.total // self.world
         t.manual_seed(1234 + 4 + self.rank)
         self.x = t.randn(self.n, dtype=t.float32, device="cuda")
         self.out = t.zeros(1, dtype=t.float32, device="cuda")
-        self.h = self.lib.compile(chain_sum_ir())
+        self.h = self.lib.compile(chain_sum_ir(xrank=self.peer))
+        self.h_local = self.lib.compile(chain_sum_ir())
         self.w, self.b = np.float32(0.5), np.float32(0.1)
-        self.scaling = "strong"
-
-    def describe(self):
-        return {"workload": "C5 sum(sigmoid(x*w+b)*exp(-x*x)), fp32 x ~ N(0,1), 2^%d elements total, w=0.5 b=0.1"
-                            % ((self.n * self.world).bit_length() - 1),
-                "elements_per_gpu": self.n, "l2": "input per launch (%d MiB) larger than L2, no flush" % (self.n * 4 >> 20),
-                "parallelism": "elements sharded over %d GPU(s), NCCL all-reduce of the partial sums" % self.world}
+        self.launches_per_step = 1 if (self.world == 1 or self.peer) else 2
 
     def bytes_per_step(self):
         return self.n * 4
 
-    launches_per_step = 1
+    def has_collective(self):
+        return self.world > 1
 
     def launch_step(self, i, stream):
         self.lib.launch(self.h, (self.n,), [self.out, self.x], scalars=[self.w, self.b], device=self.device, stream=stream)
-
-    def step(self, i):
-        self.launch_step(i, self.stream)
-        if self.world > 1:
-            from dali_b200.sharding import combine_partials
-            combine_partials(self.out, "sum")           # NCCL all-reduce of one fp32 per rank
-
-    def graph_fn(self):
-        return self.launch_step if self.world == 1 else None
+        if self.world > 1 and not self.peer:
+            self.lib.allreduce(self.out, 1, F32, "sum", device=self.device, stream=stream)
 
     def e2e_setup(self):
         t = self.torch
         self.hx = t.empty(self.n, dtype=t.float32, pin_memory=True)
         self.hx.copy_(self.x)
         self.hout = t.zeros(1, dtype=t.float32, pin_memory=True)
+        self.dx = t.empty(self.n, dtype=t.float32, device="cuda") if self.world > 1 and not self.peer else None
         self.h2d, self.d2h = self.n * 4, 4
+        if self.dx is not None:
+            self.e2e_api = "C ABI with caller-managed copies (page-locked host -> device, dalib200_launch, dalib200_allreduce, device -> page-locked host, sync)"
 
     def e2e_step(self, i):
-        # host buffers in, host result out: alloc + H2D + kernel + D2H + sync inside the call
+        if self.dx is not None:
+            # (ranks that cannot address one another: the NCCL all-reduce needs the partial sum on the device)
+            self.dx.copy_(self.hx, non_blocking=True)
+            self.lib.launch(self.h_local, (self.n,), [self.out, self.dx], scalars=[self.w, self.b], device=self.device, stream=self.stream)
+            self.lib.allreduce(self.out, 1, F32, "sum", device=self.device, stream=self.stream)
+            self.hout.copy_(self.out, non_blocking=True)
+            self.torch.cuda.synchronize()
+            return
+        # host buffers in, host result out: alloc + H2D + kernel (with the ranks' exchange inside) + D2H + sync in one call
         import ctypes
         n = 2
         ptrs = (ctypes.c_void_p * n)(self.hout.data_ptr(), self.hx.data_ptr())
@@ -231,33 +260,46 @@ class Chain(Workload):
         self.lib.check(self.lib.c.dalib200_launch_host(ctypes.c_uint64(self.h), self.device, space, 1, ptrs, ext, offs, None, n, sc, 2))
 
     def verify(self):
-        """Order-independent check of the resident result against the oracle on a slice."""
+        """Order-independent check of the resident result against the oracle on a slice; with several ranks also the
+        combined sum against the ranks' own partial sums added up by torch.distributed."""
         sys.path.insert(0, os.path.join(ROOT, "oracle"))
         import dali_oracle as oracle
+        t = self.torch
         m = min(self.n, 1 << 22)
         xs = self.x[:m].contiguous()
-        o = self.torch.zeros(1, dtype=self.torch.float32, device="cuda")
-        self.lib.launch(self.h, (m,), [o, xs], scalars=[self.w, self.b], device=self.device, stream=self.stream)
-        self.torch.cuda.synchronize()
+        o = t.zeros(1, dtype=t.float32, device="cuda")
+        self.lib.launch(self.h_local, (m,), [o, xs], scalars=[self.w, self.b], device=self.device, stream=self.stream)
+        t.cuda.synchronize()
         s32, s64, sabs = oracle.chain_sum(xs.cpu().numpy(), 0.5, 0.1)
         assert abs(float(o.item()) - s64) <= 1e-5 * sabs, (float(o.item()), s64)
-
-    def cpu_baseline(self, tmpdir, reps):
-        np = self.np
-        m = 1 << 24
-        x = self.x[:m].cpu().numpy()
-        np.save(os.path.join(tmpdir, "x.npy"), x)
-        times = run_ref_driver("chain", ["x.npy", "0.5", "0.1", "out.npy"], reps, tmpdir)
-        if not times:
-            return None
-        return {"ms": times, "bytes": m * 4, "cores": 1, "kind": "reference",
-                "sample": "first 2^24 elements of the same x (reference's generated CPU loop is single-threaded)"}
+        if self.world > 1:
+            self.lib.launch(self.h_local, (self.n,), [o, self.x], scalars=[self.w, self.b], device=self.device, stream=self.stream)
+            part = o.double()
+            t.distributed.all_reduce(part)
+            self.step(0)
+            t.cuda.synchronize()
+            assert self.lib.comm_error_flag() == 0, "a rank did not arrive at the exchange in time"
+            assert abs(float(self.out.item()) - float(part.item())) <= 1e-6 * abs(float(part.item())), (float(self.out.item()), float(part.item()))
 
 
 class Softmax(Workload):
     """Benchmark configuration 1: naive fused softmax on fp32 [4096,1024]."""
     name = "softmax"
     ROWS, COLS = 4096, 1024
+    NBUF = 12     # 12 x (16 MiB in + 16 MiB out) = 384 MiB rotates through the 126 MiB L2
+
+    @staticmethod
+    def config(world, **kw):
+        return {"workload": "C1 exp(a-max(a,{-1},true))/sum(exped,{-1},true), fp32 [4096,1024] ~ N(0,1) per GPU",
+                "l2": "rotating over %d input/output buffer pairs (%d MiB) so every launch misses L2" % (Softmax.NBUF, Softmax.NBUF * 32),
+                "concurrency": "one stream: batch after batch",
+                "parallelism": "rows sharded: each of %d GPU(s) runs its own [4096,1024] batch, no collective" % world}
+
+    @staticmethod
+    def reference_case(np, tmp, **kw):
+        np.save(os.path.join(tmp, "a.npy"), np.random.default_rng(1234).standard_normal((4096, 1024)).astype(np.float32))
+        return {"case": "softmax_naive", "args": ["a.npy", "out.npy"], "bytes": 4096 * 1024 * 8, "cores": 1,
+                "sample": "the full [4096,1024] batch per step (the reference's generated loops are single-threaded)"}
 
     def __init__(self, *a):
         super().__init__(*a)
@@ -266,34 +308,31 @@ class Softmax(Workload):
         self.np = np
         t = self.torch
         t.manual_seed(1234 + 0 + self.rank)
-        self.nbuf = 12    # 12 x (16 MiB in + 16 MiB out) = 384 MiB rotates through the 126 MiB L2
+        self.nbuf = self.NBUF
         self.a = [t.randn(self.ROWS, self.COLS, dtype=t.float32, device="cuda") for _ in range(self.nbuf)]
         self.o = [t.empty(self.ROWS, self.COLS, dtype=t.float32, device="cuda") for _ in range(self.nbuf)]
         self.h = self.lib.compile(softmax_ir())
-        self.scaling = "weak"
-        self.lanes = int(os.environ.get("DALI_BENCH_SOFTMAX_LANES", "3"))   # independent batches on three streams
-
-    def describe(self):
-        return {"workload": "C1 exp(a-max(a,{-1},true))/sum(exped,{-1},true), fp32 [4096,1024] ~ N(0,1) per GPU",
-                "l2": "rotating over %d input/output buffer pairs (%d MiB) so every launch misses L2" %
-                      (self.nbuf, self.nbuf * 32),
-                "concurrency": "%d streams: consecutive batches are independent and may overlap" % self.lanes,
-                "parallelism": "rows sharded: each of %d GPU(s) runs its own [4096,1024] batch, no collective" % self.world}
 
     def bytes_per_step(self):
         return self.ROWS * self.COLS * 8
-
-    launches_per_step = 1
 
     def launch_step(self, i, stream):
         k = i % self.nbuf
         self.lib.launch(self.h, (self.ROWS, self.COLS), [self.o[k], self.a[k]], device=self.device, stream=stream)
 
-    def step(self, i):
-        self.launch_step(i, self.stream)
-
-    def graph_fn(self):
-        return self.launch_step
+    def extra(self, torch):
+        """The same kernel with consecutive (independent) batches on three streams, as a serving loop with several
+        requests in flight would issue them: GB/s."""
+        g = GraphStepper(torch, self.launch_step, 24, 3)
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(g.stream)
+        g.replay()
+        e1.record(g.stream)
+        torch.cuda.synchronize()
+        return {"three_streams_gbs": self.bytes_per_step() * 24 / (e0.elapsed_time(e1) * 1e-3) / 1e9}
 
     def e2e_setup(self):
         t = self.torch
@@ -319,15 +358,6 @@ class Softmax(Workload):
         got = self.o[0].cpu().numpy()
         want = oracle.softmax(self.a[0].cpu().numpy())
         assert self.np.allclose(got, want, rtol=1e-5, atol=1e-9)
-
-    def cpu_baseline(self, tmpdir, reps):
-        self.np.save(os.path.join(tmpdir, "a.npy"), self.a[0].cpu().numpy())
-        times = run_ref_driver("softmax_naive", ["a.npy", "out.npy"], reps, tmpdir)
-        if not times:
-            return None
-        return {"ms": times, "bytes": self.bytes_per_step(), "cores": 1, "kind": "reference",
-                "sample": "the full [4096,1024] batch"}
-
 
 
 class GraphStepper:
@@ -364,26 +394,49 @@ class Lstm(Workload):
     """Benchmark configuration 2: fused LSTM cell step, fp32, B=256 H=1024 per GPU."""
     name = "lstm"
     B, H = 256, 1024
-    dominant_traffic_bytes = 75.8e6      # profiles/gemm_tcgen05_kernels.md: 72.4 MB read + 3.4 MB written per launch
+    NSET = 6
+    hbm_metric = False         # the two weight matrices (32 of the 38.8 MB) are reused every step and stay in L2
+    launches_per_step = 2
+    dominant_traffic_bytes = 75.8e6      # ncu: 72.4 MB read + 3.4 MB written per launch with a cold L2
     dominant_traffic_note = "ncu capture with a cold L2 (64 MB of split weights read from DRAM); in the timed loop the weights stay in L2"
     e2e_api = ("page-locked host arrays -> lazy Array / op:: expression -> Array::eval_together -> host arrays, in C++ against "
                "the front end's headers (dali_b200/host/programs/lstm_cell_e2e.cpp)")
 
+    @staticmethod
+    def config(world, **kw):
+        return {"workload": "C2 LSTM cell step: gates = dot(x,Wx)+dot(h,Wh)+b, c' = sig(f)*c + sig(i)*tanh(g), "
+                            "h' = sig(o)*tanh(c'); fp32, B=256 H=1024 per GPU, x,h,c ~ N(0,1), W ~ N(0,0.02), b = 0",
+                "l2": "activations rotate over %d sets; the two weight matrices are reused every step (as in an RNN) "
+                      "and stay in L2: `value` counts their bytes too and is therefore not an HBM bandwidth" % Lstm.NSET,
+                "kernels_per_step": "1 TF32 split of x and h, 1 tcgen05 3xTF32 GEMM accumulating x.Wx + h.Wh whose epilogue is the whole gating (+ b, sigmoid / tanh, c', h'): the [B,4H] gates are never written",
+                "parallelism": "batch sharded: each of %d GPU(s) runs its own B=256 shard, weights replicated, no collective" % world}
+
+    @staticmethod
+    def reference_case(np, tmp, **kw):
+        rng = np.random.default_rng(1234 + 1)
+        B, H = Lstm.B, Lstm.H
+        for k in ("x", "h", "c"):
+            np.save(os.path.join(tmp, k + ".npy"), rng.standard_normal((B, H)).astype(np.float32))
+        for k in ("Wx", "Wh"):
+            np.save(os.path.join(tmp, k + ".npy"), (rng.standard_normal((H, 4 * H)) * 0.02).astype(np.float32))
+        np.save(os.path.join(tmp, "b.npy"), np.zeros((1, 4 * H), np.float32))
+        return {"case": "lstm", "args": ["x.npy", "h.npy", "c.npy", "Wx.npy", "Wh.npy", "b.npy", "c_out.npy", "h_out.npy"],
+                "bytes": 4 * (3 * B * H + 2 * H * 4 * H + 4 * H + 2 * B * H), "flops": 2.0 * 2 * B * H * 4 * H, "cores": os.cpu_count() or 1,
+                "sample": "the full B=256 H=1024 cell step (reference: 8 OpenBLAS sgemm on all host cores + 5 single-threaded JIT kernels)"}
+
     def __init__(self, *a):
         super().__init__(*a)
         import numpy as np
-        from dali_b200.ir import IRBuilder
         self.np = np
         t, B, H = self.torch, self.B, self.H
         t.manual_seed(1234 + 1 + self.rank)
-        self.nset = 6       # rotating activation sets; weights (2 x 16 MiB, split: 64 MiB) stay hot like in a real RNN
+        self.nset = self.NSET       # rotating activation sets; weights (2 x 16 MiB, split: 64 MiB) stay hot like in a real RNN
         self.x = [t.randn(B, H, device="cuda") for _ in range(self.nset)]
         self.h = [t.randn(B, H, device="cuda") for _ in range(self.nset)]
         self.c = [t.randn(B, H, device="cuda") for _ in range(self.nset)]
         self.Wx = t.randn(H, 4 * H, device="cuda") * 0.02
         self.Wh = t.randn(H, 4 * H, device="cuda") * 0.02
         self.b = t.zeros(4 * H, device="cuda")
-        self.gates = t.empty(B, 4 * H, device="cuda")
         self.c_new = [t.empty(B, H, device="cuda") for _ in range(self.nset)]
         self.h_new = [t.empty(B, H, device="cuda") for _ in range(self.nset)]
         L = self.lib
@@ -394,23 +447,9 @@ class Lstm(Workload):
             L.gemm_split_tf32(w, H, 4 * H, 4 * H, hi, lo, transpose=True, device=self.device)
             self.W[name] = (hi, lo)
         self.parts = [t.empty(B * H, device="cuda") for _ in range(4)]
-        e = IRBuilder(2, 0)
-        o, bias = e.arg("f32"), e.arg("f32")
-        e.st(o, e.op("add", e.acc(), e.ld(bias)))      # acc = x.Wx + h.Wh (one accumulator), + b
-        self.h_epi = L.compile(e.text())
         # what the front end emits for eval_together(c', h'): the gating is the epilogue of the gate products
         from dali_b200.ir import lstm_cell_epilogue_ir
         self.h_cell = L.compile(lstm_cell_epilogue_ir())
-        self.scaling = "weak"
-        self.launches_per_step = 2
-
-    def describe(self):
-        return {"workload": "C2 LSTM cell step: gates = dot(x,Wx)+dot(h,Wh)+b, c' = sig(f)*c + sig(i)*tanh(g), "
-                            "h' = sig(o)*tanh(c'); fp32, B=256 H=1024 per GPU, x,h,c ~ N(0,1), W ~ N(0,0.02), b = 0",
-                "l2": "activations rotate over %d sets; the two weight matrices are reused every step (as in an RNN) "
-                      "and stay in L2" % self.nset,
-                "kernels_per_step": "1 TF32 split of x and h, 1 tcgen05 3xTF32 GEMM accumulating x.Wx + h.Wh whose epilogue is the whole gating (+ b, sigmoid / tanh, c', h'): the [B,4H] gates are never written",
-                "parallelism": "batch sharded: each of %d GPU(s) runs its own B=256 shard, weights replicated, no collective" % self.world}
 
     def bytes_per_step(self):
         B, H = self.B, self.H
@@ -421,8 +460,7 @@ class Lstm(Workload):
 
     def launch_step(self, i, stream):
         L, B, H, k = self.lib, self.B, self.H, i % self.nset
-        d = self.device
-        L.gemm_split_tf32_pair(self.x[k], self.h[k], B, H, H, H, *self.parts, device=d, stream=stream)
+        L.gemm_split_tf32_pair(self.x[k], self.h[k], B, H, H, H, *self.parts, device=self.device, stream=stream)
         self.launch_gemm(stream, k)
 
     def launch_gemm(self, stream, k=0):
@@ -434,61 +472,31 @@ class Lstm(Workload):
                                 strides=[None, None, row, row, row, row, None], offsets=[0, 0, 0, H, 2 * H, 3 * H, 0],
                                 device=self.device, stream=stream)
 
-    def step(self, i):
-        self.launch_step(i, self.stream)
-
-    def graph_fn(self):
-        return self.launch_step
-
     def dominant(self):
-        """(name, bound, algorithmic work per launch, launcher) of the dominant kernel."""
         B, H = self.B, self.H
         return ("tcgen05 3xTF32 GEMM [256,1024]x[1024,4096] + [256,1024]x[1024,4096], one accumulator, LSTM gating as epilogue", "tensor",
                 2.0 * 2 * B * H * 4 * H, lambda i, stream: self.launch_gemm(stream))
 
     def e2e_external(self, warmup, steps):
         """ms per step of dali_b200/host/programs/lstm_cell_e2e.cpp: the cell through the C++ Array / op:: API with
-        page-locked host arrays in and out every step (the Python face of the same API, e2e_step below, adds
-        ~0.1 ms of ctypes calls per step)."""
+        page-locked host arrays in and out every step."""
         from dali_b200 import build as _build
         exe = os.path.join(ROOT, "dali_b200", "lib", "lstm_cell_e2e")
         if not os.path.exists(exe):
             _build.build_programs()
-        out = subprocess.run([exe, str(self.device), str(self.B), str(self.H), str(warmup), str(steps)], capture_output=True,
-                             text=True, timeout=600)
+        cmd = [exe, str(self.device), str(self.B), str(self.H), str(warmup), str(steps)]
+        ncpu = os.cpu_count() or 1
+        if self.world > 1 and ncpu >= 2 * self.world:
+            # every rank's host loop on cores of its own: with all ranks on the same few cores the step time of one
+            # rank depends on what the others are doing
+            per = ncpu // self.world
+            cmd = ["taskset", "-c", "%d-%d" % (self.rank * per, self.rank * per + per - 1)] + cmd
+        out = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
         if out.returncode != 0:
             raise RuntimeError("lstm_cell_e2e failed: " + out.stderr[-2000:])
         r = json.loads(out.stdout.strip().splitlines()[-1])
         self.h2d, self.d2h = r["h2d_bytes_per_step"], r["d2h_bytes_per_step"]
         return r["ms_per_step"]
-
-    def e2e_setup(self):
-        np = self.np
-        t = self.torch
-        self.pinned = {}
-        for k in ("x", "h", "c"):
-            self.pinned[k] = t.empty(self.B, self.H, pin_memory=True)
-            self.pinned[k].copy_(getattr(self, k)[0])
-        for k in ("h_out", "c_out"):
-            self.pinned[k] = t.empty(self.B, self.H, pin_memory=True)
-        self.host = {k: v.numpy() for k, v in self.pinned.items()}       # numpy views of the page-locked buffers
-        from dali_b200.array import Array, set_default_device
-        set_default_device(self.device)
-        self.fe = {"Wx": Array(self.Wx.cpu().numpy()), "Wh": Array(self.Wh.cpu().numpy()), "b": Array(self.b.cpu().numpy())}
-        self.h2d, self.d2h = 3 * self.B * self.H * 4, 2 * self.B * self.H * 4
-
-    def e2e_step(self, i):
-        # the call a user makes: (page-locked) host arrays in, lazy expression, eval, results back on the host
-        from dali_b200.array import Array, eval_together, op
-        H = self.H
-        x, h, c = (Array.borrow(self.host[k]) for k in ("x", "h", "c"))
-        gates = op.dot(x, self.fe["Wx"]) + op.dot(h, self.fe["Wh"]) + self.fe["b"][None, :]
-        i_, f, o = (op.sigmoid(gates[:, k * H:(k + 1) * H]) for k in range(3))
-        g = op.tanh(gates[:, 3 * H:4 * H])
-        c_new = f * c + i_ * g
-        h_new = o * op.tanh(c_new)
-        eval_together(c_new, h_new, wait=False)              # one GEMM launch + one gating kernel for both outputs
-        self.last = (h_new.numpy(out=self.host["h_out"]), c_new.numpy(out=self.host["c_out"]))
 
     def verify(self):
         sys.path.insert(0, os.path.join(ROOT, "oracle"))
@@ -503,25 +511,32 @@ class Lstm(Workload):
         assert np.allclose(self.c_new[0].cpu().numpy(), want_c, rtol=1e-5, atol=1e-5)
         assert np.allclose(self.h_new[0].cpu().numpy(), want_h, rtol=1e-5, atol=1e-5)
 
-    def cpu_baseline(self, tmpdir, reps):
-        np = self.np
-        for k in ("x", "h", "c"):
-            np.save(os.path.join(tmpdir, k + ".npy"), getattr(self, k)[0].cpu().numpy())
-        np.save(os.path.join(tmpdir, "Wx.npy"), self.Wx.cpu().numpy())
-        np.save(os.path.join(tmpdir, "Wh.npy"), self.Wh.cpu().numpy())
-        np.save(os.path.join(tmpdir, "b.npy"), self.b.cpu().numpy().reshape(1, -1))
-        times = run_ref_driver("lstm", ["x.npy", "h.npy", "c.npy", "Wx.npy", "Wh.npy", "b.npy", "c_out.npy", "h_out.npy"], reps, tmpdir)
-        if not times:
-            return None
-        return {"ms": times, "bytes": self.bytes_per_step(), "cores": os.cpu_count() or 1, "kind": "reference",
-                "sample": "the full B=256 H=1024 cell step (reference: 8 OpenBLAS sgemm on all host cores + 5 single-threaded JIT kernels)"}
-
 
 class Gemm(Workload):
     """Benchmark configuration 4: tanh(dot(A,B)+bias), bf16 8192^3, fp32 accumulate, bf16 out."""
     name = "gemm"
+    dtype = "bf16"
+    hbm_metric = False
     e2e_api = "C ABI with caller-managed copies (page-locked host -> device, dalib200_gemm_fused, device -> page-locked host, sync)"
     N = 8192
+
+    @staticmethod
+    def config(world, n=None, **kw):
+        n = n or Gemm.N
+        return {"workload": "C4 tanh(dot(A,B)+bias), bf16 A,B [%d,%d] ~ N(0,0.02), bias ~ N(0,0.1), fp32 accumulate, bf16 out" % (n, n),
+                "l2": "operands + output = %d MiB per launch, larger than L2" % (3 * n * n * 2 >> 20),
+                "parallelism": "rows of A sharded: each of %d GPU(s) runs its own [%d,%d] block, B and bias replicated, no collective" % (world, n, n)}
+
+    @staticmethod
+    def reference_case(np, tmp, **kw):
+        rng = np.random.default_rng(1237)
+        m = 2048
+        np.save(os.path.join(tmp, "A.npy"), (rng.standard_normal((m, m)) * 0.02).astype(np.float32))
+        np.save(os.path.join(tmp, "B.npy"), (rng.standard_normal((m, m)) * 0.02).astype(np.float32))
+        np.save(os.path.join(tmp, "bias.npy"), (rng.standard_normal(m) * 0.1).astype(np.float32))
+        return {"case": "gemm_tanh", "args": ["A.npy", "B.npy", "bias.npy", "out.npy"], "bytes": 3 * m * m * 2, "flops": 2.0 * m ** 3,
+                "cores": os.cpu_count() or 1, "max_reps": 3,
+                "sample": "2048^3 in fp32 per step (the reference has no bf16; 1/64 of the flops): OpenBLAS sgemm on all host cores + the reference's single-threaded tanh kernel"}
 
     def __init__(self, *a, n=None):
         super().__init__(*a)
@@ -536,13 +551,6 @@ class Gemm(Workload):
         self.bias = t.randn(n, device="cuda") * 0.1
         self.out = t.empty(n, n, device="cuda", dtype=t.bfloat16)
         self.h = self.lib.compile(gemm_bias_tanh_ir("bf16"))
-        self.scaling = "weak"
-        self.launches_per_step = 1
-
-    def describe(self):
-        return {"workload": "C4 tanh(dot(A,B)+bias), bf16 A,B [%d,%d] ~ N(0,0.02), bias ~ N(0,0.1), fp32 accumulate, bf16 out" % (self.n, self.n),
-                "l2": "operands + output = %d MiB per launch, larger than L2" % (3 * self.n * self.n * 2 >> 20),
-                "parallelism": "rows of A sharded: each of %d GPU(s) runs its own [%d,%d] block, B and bias replicated, no collective" % (self.world, self.n, self.n)}
 
     def bytes_per_step(self):
         return 3 * self.n * self.n * 2
@@ -554,12 +562,6 @@ class Gemm(Workload):
         n = self.n
         self.lib.gemm_fused(3, n, n, n, self.A, n, self.Bm, n, self.h, [self.out, self.bias], strides=[None, [0, 1]],
                             device=self.device, stream=stream)
-
-    def step(self, i):
-        self.launch_step(i, self.stream)
-
-    def graph_fn(self):
-        return self.launch_step
 
     def dominant(self):
         return ("tcgen05 bf16 GEMM + bias/tanh epilogue", "tensor", float(self.flops_per_step()), self.launch_step)
@@ -574,8 +576,6 @@ class Gemm(Workload):
         self.h2d, self.d2h = 2 * n * n * 2 + n * 4, n * n * 2
 
     def e2e_step(self, i):
-        # bf16 is not a dtype of the reference's Array: the user-facing call for it is the C ABI with
-        # caller-managed copies (pinned host -> device, fused GEMM, device -> pinned host)
         t = self.torch
         self.A.copy_(self.hA, non_blocking=True)
         self.Bm.copy_(self.hB, non_blocking=True)
@@ -585,98 +585,151 @@ class Gemm(Workload):
         t.cuda.synchronize()
 
     def verify(self):
-        np, n = self.np, self.n
+        """The WHOLE output against tanh(A.float() @ B.float() + bias) computed by torch in fp32 on the device (a checker,
+        not part of the path), plus three rows against the fp64 product."""
+        np, n, t = self.np, self.n, self.torch
         self.step(0)
-        self.torch.cuda.synchronize()
+        t.cuda.synchronize()
         assert self.lib.gemm_error_flag(self.device) == 0
+        prev = t.backends.cuda.matmul.allow_tf32
+        t.backends.cuda.matmul.allow_tf32 = False
+        bad = 0
+        for r0 in range(0, n, 2048):
+            want = t.tanh(self.A[r0:r0 + 2048].float() @ self.Bm.float() + self.bias)
+            bad += int((~t.isclose(self.out[r0:r0 + 2048].float(), want, rtol=1e-2, atol=4e-3)).sum().item())
+        t.backends.cuda.matmul.allow_tf32 = prev
+        assert bad == 0, "%d of %d outputs outside rtol 1e-2" % (bad, n * n)
         rows = [0, 129, n - 1]
         a = self.A[rows].float().cpu().numpy().astype(np.float64)
         want = np.tanh(a @ self.Bm.float().cpu().numpy().astype(np.float64) + self.bias.cpu().numpy())
         assert np.allclose(self.out[rows].float().cpu().numpy(), want, rtol=1e-2, atol=4e-3)
 
-    def cpu_baseline(self, tmpdir, reps):
-        np = self.np
-        m = 2048        # the reference has no bf16: fp32 sgemm + its fused add/tanh kernel on bf16-rounded inputs
-        np.save(os.path.join(tmpdir, "A.npy"), self.A[:m, :m].float().cpu().numpy())
-        np.save(os.path.join(tmpdir, "B.npy"), self.Bm[:m, :m].float().cpu().numpy())
-        np.save(os.path.join(tmpdir, "bias.npy"), self.bias[:m].cpu().numpy())
-        times = run_ref_driver("gemm_tanh", ["A.npy", "B.npy", "bias.npy", "out.npy"], min(reps, 3), tmpdir)
-        if not times:
-            return None
-        return {"ms": times, "bytes": 3 * m * m * 2, "flops": 2.0 * m ** 3, "cores": os.cpu_count() or 1, "kind": "reference",
-                "sample": "2048^3 fp32 (1/64 of the flops): OpenBLAS sgemm on all host cores + the reference's single-threaded tanh kernel"}
 
-
-class ReduceAxis0(Workload):
-    """Benchmark configuration 3 (the strided case): sum over axis 0 of fp32 [8192,8192]."""
+class Reduce(Workload):
+    """Benchmark configuration 3: sum / max / argmax over axis -1, axis 0 or all axes of fp32 [8192,8192] per GPU.
+    The rows of the logical [world * 8192, 8192] array are sharded: axis -1 needs no exchange, axis 0 ends in an
+    all-reduce of the [8192] partials and the all-axis forms in an exchange of one value (for argmax: of (value,
+    position) pairs, positions being those of the logical array)."""
     name = "reduce"
     N = 8192
+    e2e_api = "C ABI with caller-managed copies (page-locked host -> device, dalib200_launch [+ dalib200_allreduce], device -> page-locked host, sync)"
 
-    def __init__(self, *a):
+    @staticmethod
+    def config(world, op="sum", axis="0", **kw):
+        what = {"-1": "axis -1", "0": "axis 0", "all": "all axes"}[str(axis)]
+        if world == 1 or str(axis) == "-1":
+            par = "rows sharded over %d GPU(s), no collective" % world
+        elif op == "argmax":
+            par = "rows sharded over %d GPU(s); the ranks' (value, position) pairs are combined, lowest position among equals" % world
+        else:
+            par = "rows sharded over %d GPU(s); the partial results meet in an all-reduce" % world
+        return {"workload": "C3 op::%s over %s of fp32 [8192,8192] ~ U(-1,1) per GPU" % (op, what),
+                "l2": "two 256 MiB inputs alternate (512 MiB > L2)", "parallelism": par + _collective_note(world if str(axis) != "-1" else 1)}
+
+    @staticmethod
+    def reference_case(np, tmp, op="sum", axis="0", **kw):
+        m = 2048
+        np.save(os.path.join(tmp, "x.npy"), (np.random.default_rng(1236).random((m, m)) * 2 - 1).astype(np.float32))
+        return {"case": "reduce", "args": [op, str(axis), "x.npy", "out.npy"], "bytes": m * m * 4, "cores": 1,
+                "sample": "a [2048,2048] array per step (1/16 of the bytes; the reference's generated loop is single-threaded)"}
+
+    def __init__(self, *a, op="sum", axis="0"):
         super().__init__(*a)
         import numpy as np
-        from dali_b200.ir import reduce_ir
+        from dali_b200.ir import arg_pair_ir, reduce_ir
         self.np = np
-        t = self.torch
+        t, N, L = self.torch, self.N, self.lib
+        self.op, self.axis = op, str(axis)
+        assert op in ("sum", "max", "argmax") and self.axis in ("-1", "0", "all")
         t.manual_seed(1234 + 2 + self.rank)
-        self.x = [t.rand(self.N, self.N, device="cuda") * 2 - 1 for _ in range(2)]    # 2 x 256 MiB > L2
-        self.out = t.empty(self.N, device="cuda")
-        self.h = self.lib.compile(reduce_ir("sum", "f32", 2, 1))
-        self.scaling = "weak"
-        self.launches_per_step = 1
-
-    def describe(self):
-        return {"workload": "C3 op::sum over axis 0 of fp32 [8192,8192] ~ U(-1,1) per GPU",
-                "l2": "two 256 MiB inputs alternate (512 MiB > L2)",
-                "parallelism": "rows sharded over %d GPU(s); the [8192] partial sums meet in an all-reduce" % self.world}
+        self.x = [t.rand(N, N, device="cuda") * 2 - 1 for _ in range(2)]    # 2 x 256 MiB > L2
+        self.arg = op == "argmax"
+        self.kind = "max" if self.arg else op
+        n_out = 1 if self.axis == "all" else N
+        self.out = t.zeros(n_out, device="cuda", dtype=t.int32 if self.arg else t.float32)
+        self.vals = t.zeros(n_out, device="cuda")
+        self.collective = self.world > 1 and self.axis != "-1"
+        self.fused = self.collective and self.axis == "all" and self.peer
+        self.pair = self.collective and self.arg and not self.fused
+        self.rank_ir = 1 if self.axis == "all" else 2
+        # position of this rank's shard in the logical array: rows for axis 0, elements for all axes
+        offset = self.rank * N if self.axis == "0" else self.rank * N * N
+        self.scalars = [np.int32(offset)] if ((self.fused and self.arg) or self.pair) else None
+        if self.fused:
+            self.h = L.compile(reduce_ir(self.kind, "f32", 1, 1, self.arg, xrank=True))
+        elif self.pair:
+            self.h = L.compile(arg_pair_ir(self.kind, "f32", self.rank_ir, 1))
+        else:
+            self.h = L.compile(reduce_ir(self.kind, "f32", self.rank_ir, 1, self.arg))
+        self.h_local = L.compile(reduce_ir(self.kind, "f32", self.rank_ir, 1, self.arg))
+        self.launches_per_step = 2 if (self.collective and not self.fused) else 1
 
     def bytes_per_step(self):
         return self.N * self.N * 4
 
+    def has_collective(self):
+        return self.collective
+
+    def launch_kernel(self, h, outs, scalars, x, stream):
+        N, L = self.N, self.lib
+        if self.axis == "all":
+            L.launch(h, (N * N,), outs + [x], scalars=scalars, device=self.device, stream=stream)
+        elif self.axis == "0":
+            # the reduced axis comes last in the program's space: the matrix is handed over with its strides swapped
+            L.launch(h, (N, N), outs + [x], strides=[None] * len(outs) + [[1, N]], scalars=scalars, device=self.device, stream=stream)
+        else:
+            L.launch(h, (N, N), outs + [x], scalars=scalars, device=self.device, stream=stream)
+
     def launch_step(self, i, stream):
-        N = self.N
-        self.lib.launch(self.h, (N, N), [self.out, self.x[i % 2]], strides=[None, [1, N]], device=self.device, stream=stream)
-
-    def step(self, i):
-        self.launch_step(i, self.stream)
-        if self.world > 1:
-            from dali_b200.sharding import combine_partials
-            combine_partials(self.out, "sum")           # NCCL all-reduce of the [8192] partial sums
-
-    def graph_fn(self):
-        return self.launch_step if self.world == 1 else None
+        self.launch_kernel(self.h, [self.vals, self.out] if self.pair else [self.out], self.scalars, self.x[i % 2], stream)
+        if self.collective and not self.fused:
+            n = self.out.numel()
+            if self.pair:
+                self.lib.arg_allreduce(self.vals, self.out, n, F32, self.kind, device=self.device, stream=stream)
+            else:
+                self.lib.allreduce(self.out, n, F32, self.kind, device=self.device, stream=stream)
 
     def e2e_setup(self):
         t = self.torch
         self.hx = t.empty(self.N, self.N, pin_memory=True); self.hx.copy_(self.x[0])
-        self.hout = self.np.zeros(self.N, self.np.float32)
-        self.h2d, self.d2h = self.N * self.N * 4, self.N * 4
+        self.hout = t.zeros(self.out.numel(), dtype=self.out.dtype, pin_memory=True)
+        self.h2d, self.d2h = self.N * self.N * 4, self.out.numel() * 4
 
     def e2e_step(self, i):
-        import ctypes
-        N = self.N
-        ptrs = (ctypes.c_void_p * 2)(self.hout.ctypes.data, self.hx.data_ptr())
-        ext = (ctypes.c_int64 * 2)(N, N * N)
-        offs = (ctypes.c_int64 * 2)(0, 0)
-        space = (ctypes.c_int64 * 2)(N, N)
-        st1 = (ctypes.c_int64 * 2)(1, N)
-        st = (ctypes.POINTER(ctypes.c_int64) * 2)(None, ctypes.cast(st1, ctypes.POINTER(ctypes.c_int64)))
-        self.lib.check(self.lib.c.dalib200_launch_host(ctypes.c_uint64(self.h), self.device, space, 2, ptrs, ext, offs, st, 2, None, 0))
+        # page-locked host matrix in, host result out: H2D + kernel (+ the ranks' exchange) + D2H + sync
+        self.x[0].copy_(self.hx, non_blocking=True)
+        self.launch_step(0, self.stream)
+        self.hout.copy_(self.out, non_blocking=True)
+        self.torch.cuda.synchronize()
 
     def verify(self):
-        self.launch_step(0, self.stream)
-        self.torch.cuda.synchronize()
-        want = self.x[0].sum(0, dtype=self.torch.float64)
-        bound = 1e-5 * self.x[0].abs().sum(0, dtype=self.torch.float64)
-        assert bool(((self.out.double() - want).abs() <= bound).all())
-
-    def cpu_baseline(self, tmpdir, reps):
-        m = 2048
-        self.np.save(os.path.join(tmpdir, "x.npy"), self.x[0][:m, :m].contiguous().cpu().numpy())
-        times = run_ref_driver("reduce", ["sum", "0", "x.npy", "out.npy"], reps, tmpdir)
-        if not times:
-            return None
-        return {"ms": times, "bytes": m * m * 4, "cores": 1, "kind": "reference", "sample": "a [2048,2048] corner (1/16 of the bytes)"}
+        """The rank's own result of the op that is timed (before any exchange) against torch on the device as a checker:
+        sums within 1e-5 * sum|x| of the fp64 sum, max and argmax (first occurrence) exactly."""
+        t, N = self.torch, self.N
+        x = self.x[0]
+        self.launch_kernel(self.h_local, [self.out], None, x, self.stream)
+        t.cuda.synchronize()
+        dim = {"-1": 1, "0": 0}.get(self.axis)
+        if self.op == "sum":
+            want = x.sum(dtype=t.float64) if dim is None else x.sum(dim, dtype=t.float64)
+            bound = 1e-5 * (x.abs().sum(dtype=t.float64) if dim is None else x.abs().sum(dim, dtype=t.float64))
+            assert bool(((self.out.double() - want).abs() <= bound).all())
+        else:
+            m = x.max() if dim is None else x.max(dim).values
+            if self.op == "max":
+                assert bool((self.out == m).all())
+            else:
+                big = t.iinfo(t.int64).max
+                if dim is None:
+                    first = t.where(x.reshape(-1) == m, t.arange(N * N, device="cuda"), big).min()
+                else:
+                    pos = t.arange(N, device="cuda").reshape((N, 1) if dim == 0 else (1, N))
+                    first = t.where(x == m.unsqueeze(dim), pos, big).min(dim).values
+                assert bool((self.out.long() == first).all())
+        if self.collective:
+            self.step(0)
+            t.cuda.synchronize()
+            assert self.lib.comm_error_flag() == 0, "a rank did not arrive at the exchange in time"
 
 
 class Cumsum(Workload):
@@ -687,6 +740,20 @@ class Cumsum(Workload):
     kernel_name = "scan_rows_kernel<float, sum, 256 threads per row, 128-bit> (dalib200_scan)"
     e2e_api = "C ABI with caller-managed copies (page-locked host -> device, dalib200_scan, device -> page-locked host, sync)"
 
+    @staticmethod
+    def config(world, shape=None, **kw):
+        R, C = shape or (Cumsum.N, Cumsum.N)
+        return {"workload": "op::cumsum over the last axis of fp32 [%d,%d] ~ U(-1,1) per GPU (inclusive)" % (R, C),
+                "l2": "two 256 MiB inputs alternate, 256 MiB output (768 MiB > L2)",
+                "parallelism": "rows sharded: each of %d GPU(s) scans its own rows, no collective" % world}
+
+    @staticmethod
+    def reference_case(np, tmp, **kw):
+        m = 4
+        np.save(os.path.join(tmp, "x.npy"), (np.random.default_rng(1240).random((m, 8192)) * 2 - 1).astype(np.float32))
+        return {"case": "scan", "args": ["sum", "1", "x.npy", "out.npy"], "bytes": 2 * m * 8192 * 4, "cores": 1, "max_reps": 3,
+                "sample": "4 of the 8192 rows per step (the reference's CPU scan is quadratic in the row length)"}
+
     def __init__(self, *a, shape=None):
         super().__init__(*a)
         import numpy as np
@@ -696,25 +763,12 @@ class Cumsum(Workload):
         self.R, self.C = shape or (self.N, self.N)      # --scan-shape R,C: other shapes of the same 256 MiB (profiling)
         self.x = [t.rand(self.R, self.C, device="cuda") * 2 - 1 for _ in range(2)]    # 2 x 256 MiB > L2
         self.out = t.empty(self.R, self.C, device="cuda")
-        self.scaling = "weak"
-        self.launches_per_step = 1
-
-    def describe(self):
-        return {"workload": "op::cumsum over the last axis of fp32 [%d,%d] ~ U(-1,1) per GPU (inclusive)" % (self.R, self.C),
-                "l2": "two 256 MiB inputs alternate, 256 MiB output (768 MiB > L2)",
-                "parallelism": "rows sharded: each of %d GPU(s) scans its own rows, no collective" % self.world}
 
     def bytes_per_step(self):
         return 2 * self.R * self.C * 4
 
     def launch_step(self, i, stream):
         self.lib.scan(0, 0, 1, self.R, self.C, self.x[i % 2], self.out, device=self.device, stream=stream)
-
-    def step(self, i):
-        self.launch_step(i, self.stream)
-
-    def graph_fn(self):
-        return self.launch_step
 
     def e2e_setup(self):
         t = self.torch
@@ -723,7 +777,6 @@ class Cumsum(Workload):
         self.h2d = self.d2h = self.R * self.C * 4
 
     def e2e_step(self, i):
-        # the C ABI with caller-managed copies (page-locked host -> device, scan, device -> page-locked host)
         self.x[0].copy_(self.hx, non_blocking=True)
         self.launch_step(0, self.stream)
         self.hout.copy_(self.out, non_blocking=True)
@@ -742,15 +795,6 @@ class Cumsum(Workload):
         assert self.np.all(self.np.abs(got - want) <= bound)
         assert self.np.all(self.np.abs(oracle.scan("sum", x, True) - want) <= bound)
 
-    def cpu_baseline(self, tmpdir, reps):
-        # the reference's CPU scan takes time quadratic in the row length (18 s for [2048,2048]): a few full-length rows
-        m = 4
-        self.np.save(os.path.join(tmpdir, "x.npy"), self.x[0][:m, :8192].contiguous().cpu().numpy())
-        times = run_ref_driver("scan", ["sum", "1", "x.npy", "out.npy"], min(reps, 3), tmpdir)
-        if not times:
-            return None
-        return {"ms": times, "bytes": 2 * m * 8192 * 4, "cores": 1, "kind": "reference", "sample": "4 rows of 8192 elements"}
-
 
 class TransposedMap(Workload):
     """y = tanh(x)^T for fp32 [8192,8192]: an elementwise tree under a transposing view (not one of the five benchmark
@@ -759,6 +803,19 @@ class TransposedMap(Workload):
     N = 8192
     kernel_name = "map skeleton, 4 x 4 register blocks: 128-bit loads along the operand's rows, 128-bit stores along the destination's"
     e2e_api = "C ABI with caller-managed copies (page-locked host -> device, dalib200_launch, device -> page-locked host, sync)"
+
+    @staticmethod
+    def config(world, **kw):
+        return {"workload": "y = tanh(x).transpose(), fp32 [8192,8192] ~ N(0,1) per GPU",
+                "l2": "two 256 MiB inputs alternate, 256 MiB output (768 MiB > L2)",
+                "parallelism": "independent matrices: each of %d GPU(s) transposes its own, no collective" % world}
+
+    @staticmethod
+    def reference_case(np, tmp, **kw):
+        m = 2048
+        np.save(os.path.join(tmp, "x.npy"), np.random.default_rng(1241).standard_normal((m, m)).astype(np.float32))
+        return {"case": "unary_t", "args": ["tanh", "x.npy", "out.npy"], "bytes": 2 * m * m * 4, "cores": 1, "max_reps": 5,
+                "sample": "a [2048,2048] array per step (1/16 of the bytes)"}
 
     def __init__(self, *a):
         super().__init__(*a)
@@ -773,26 +830,13 @@ class TransposedMap(Workload):
         O, A = e.arg("f32"), e.arg("f32")
         e.st(O, e.op("tanh", e.ld(A)))
         self.h = self.lib.compile(e.text())
-        self.scaling = "weak"
-        self.launches_per_step = 1
-
-    def describe(self):
-        return {"workload": "y = tanh(x).transpose(), fp32 [8192,8192] ~ N(0,1) per GPU",
-                "l2": "two 256 MiB inputs alternate, 256 MiB output (768 MiB > L2)",
-                "parallelism": "independent matrices: each of %d GPU(s) transposes its own, no collective" % self.world}
 
     def bytes_per_step(self):
         return 2 * self.N * self.N * 4
 
     def launch_step(self, i, stream):
         # out[r, c] = tanh(x[c, r]): the operand is handed over with its strides swapped
-        self.lib.launch(self.h, (self.N, self.N), [self.out, self.x[i % 2]], strides=[None, [1, self.N]], stream=stream)
-
-    def step(self, i):
-        self.launch_step(i, self.stream)
-
-    def graph_fn(self):
-        return self.launch_step
+        self.lib.launch(self.h, (self.N, self.N), [self.out, self.x[i % 2]], strides=[None, [1, self.N]], device=self.device, stream=stream)
 
     def e2e_setup(self):
         t = self.torch
@@ -814,111 +858,140 @@ class TransposedMap(Workload):
         want = self.np.tanh(self.x[0][:, rows].cpu().numpy().astype(self.np.float64)).T
         self.np.testing.assert_allclose(self.out[rows].cpu().numpy(), want, rtol=1e-5, atol=1e-6)
 
-    def cpu_baseline(self, tmpdir, reps):
-        m = 2048
-        self.np.save(os.path.join(tmpdir, "x.npy"), self.x[0][:m, :m].contiguous().cpu().numpy())
-        times = run_ref_driver("unary_t", ["tanh", "x.npy", "out.npy"], min(reps, 5), tmpdir)
-        if not times:
-            return None
-        return {"ms": times, "bytes": 2 * m * m * 4, "cores": 1, "kind": "reference", "sample": "a [2048,2048] corner (1/16 of the bytes)"}
+
+class GatherRows(Workload):
+    """op::gather: 2^20 int32 indices pick rows of a [65536,256] fp32 table (an embedding lookup; the index side of the
+    path, measured to the same bar).  Algorithmic bytes: every picked row read once and written once, plus the indices."""
+    name = "gather"
+    V, D, M = 65536, 256, 1 << 20
+    e2e_api = "C ABI with caller-managed copies (page-locked indices -> device, dalib200_launch, gathered rows -> page-locked host, sync)"
+
+    @staticmethod
+    def config(world, **kw):
+        return {"workload": "op::gather(table, indices): fp32 table [65536,256] ~ N(0,1), 2^20 int32 indices ~ U[0,65536) per GPU",
+                "l2": "the 64 MiB table fits L2; the 1 GiB of gathered rows written per step does not",
+                "parallelism": "indices sharded: each of %d GPU(s) gathers its own batch from a replicated table, no collective" % world}
+
+    @staticmethod
+    def reference_case(np, tmp, **kw):
+        rng = np.random.default_rng(1242)
+        np.save(os.path.join(tmp, "table.npy"), rng.standard_normal((GatherRows.V, GatherRows.D)).astype(np.float32))
+        np.save(os.path.join(tmp, "idx.npy"), rng.integers(0, GatherRows.V, 1 << 16).astype(np.int32))
+        return {"case": "gather", "args": ["table.npy", "idx.npy", "out.npy"], "bytes": (1 << 16) * (2 * GatherRows.D * 4 + 4), "cores": 1,
+                "timed_by_wall_clock": True,
+                "sample": "2^16 of the 2^20 indices per step (the reference's generated loop is single-threaded; wall clock of the whole driver process: loading the 64 MiB table and saving the result included)"}
+
+    def __init__(self, *a):
+        super().__init__(*a)
+        import numpy as np
+        from dali_b200.ir import IRBuilder
+        self.np = np
+        t = self.torch
+        t.manual_seed(1234 + 8 + self.rank)
+        self.table = t.randn(self.V, self.D, device="cuda")
+        self.idx = [t.randint(0, self.V, (self.M,), device="cuda", dtype=t.int32) for _ in range(2)]
+        self.out = t.empty(self.M, self.D, device="cuda")
+        e = IRBuilder(2, 0)
+        O, S, I = e.arg("f32"), e.arg("f32"), e.arg("i32")
+        e.st(O, e.ldx(S, e.ld(I)))
+        self.h = self.lib.compile(e.text())
+
+    def bytes_per_step(self):
+        return self.M * (2 * self.D * 4 + 4)
+
+    def launch_step(self, i, stream):
+        # out[i, j] = table[idx[i], j]: the table is addressed through the index (lead stride D), unit stride along j
+        self.lib.launch(self.h, (self.M, self.D), [self.out, self.table, self.idx[i % 2]],
+                        strides=[None, [0, 1, self.D], [1, 0]], device=self.device, stream=stream)
+
+    def e2e_setup(self):
+        t = self.torch
+        self.hidx = t.empty(self.M, dtype=t.int32, pin_memory=True); self.hidx.copy_(self.idx[0])
+        self.hout = t.empty(self.M, self.D, pin_memory=True)
+        self.h2d, self.d2h = self.M * 4, self.M * self.D * 4
+
+    def e2e_step(self, i):
+        self.idx[0].copy_(self.hidx, non_blocking=True)
+        self.launch_step(0, self.stream)
+        self.hout.copy_(self.out, non_blocking=True)
+        self.torch.cuda.synchronize()
+
+    def verify(self):
+        self.launch_step(0, self.stream)
+        self.torch.cuda.synchronize()
+        assert bool((self.out == self.table[self.idx[0].long()]).all())        # bit-exact
 
 
-WORKLOADS = {"lstm": Lstm, "softmax": Softmax, "reduce": ReduceAxis0, "gemm": Gemm, "chain": Chain, "scan": Cumsum, "transpose": TransposedMap}
+WORKLOADS = {"chain": Chain, "softmax": Softmax, "lstm": Lstm, "reduce": Reduce, "gemm": Gemm, "scan": Cumsum,
+             "transpose": TransposedMap, "gather": GatherRows}
+REDUCE_SWEEP = [(op, axis) for op in ("sum", "max", "argmax") for axis in ("-1", "0", "all")]
+
+
+def workload_kwargs(args, name):
+    kw = {}
+    if name == "chain" and args.elements:
+        kw["total"] = args.elements
+    if name == "gemm" and args.gemm_n:
+        kw["n"] = args.gemm_n
+    if name == "scan" and args.scan_shape:
+        kw["shape"] = tuple(int(v) for v in args.scan_shape.split(","))
+    if name == "reduce":
+        kw["op"], kw["axis"] = args.reduce_op, args.axis
+    return kw
 
 
 # ----------------------------------------------------------------------------- main
+def time_reference(cls, kw, reps, warmup):
+    """Per-repeat milliseconds of the reference's own CPU path on the workload's bounded sample, and the sample's description."""
+    import tempfile
+    import numpy as np
+    with tempfile.TemporaryDirectory() as tmp:
+        case = cls.reference_case(np, tmp, **kw)
+        reps = min(reps, case.get("max_reps", reps))
+        if case.get("timed_by_wall_clock"):
+            times = []
+            for _ in range(min(reps, 3) + 1):
+                t0 = time.perf_counter()
+                if run_ref_driver(case["case"], case["args"], 1, tmp) is None and not os.path.exists(ref_driver_paths()[0]):
+                    return None, case
+                times.append((time.perf_counter() - t0) * 1e3)
+            times = times[1:]
+        else:
+            times = run_ref_driver(case["case"], case["args"], reps + warmup, tmp)
+            times = times[warmup:] if times else None
+    return times, case
+
+
 def reference_arm(args):
     """--impl reference: the reference's own CPU implementation (oracle/_ref) on this box's host cores,
     same metric and config, a bounded sample per step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    import tempfile
-    import numpy as np
     drv, _ = ref_driver_paths()
     if not os.path.exists(drv):
         print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/ref_driver was not built (no reference checkout at build time)"}))
         return
-    cores = os.cpu_count() or 1
-    with tempfile.TemporaryDirectory() as tmp:
-        def save(name, arr):
-            np.save(os.path.join(tmp, name), arr)
-        w = args.workload
-        if w == "lstm":
-            rng = np.random.default_rng(1234 + 1)
-            B, H = 256, 1024
-            for k in ("x", "h", "c"):
-                save(k + ".npy", rng.standard_normal((B, H)).astype(np.float32))
-            for k in ("Wx", "Wh"):
-                save(k + ".npy", (rng.standard_normal((H, 4 * H)) * 0.02).astype(np.float32))
-            save("b.npy", np.zeros((1, 4 * H), np.float32))
-            case, cargs = "lstm", ["x.npy", "h.npy", "c.npy", "Wx.npy", "Wh.npy", "b.npy", "c_out.npy", "h_out.npy"]
-            nbytes = 4 * (3 * B * H + 2 * H * 4 * H + 4 * H + 2 * B * H)
-            flops = 2 * 2 * B * H * 4 * H
-            wl = ("C2 LSTM cell step: gates = dot(x,Wx)+dot(h,Wh)+b, c' = sig(f)*c + sig(i)*tanh(g), h' = sig(o)*tanh(c'); "
-                  "fp32, B=256 H=1024 per GPU, x,h,c ~ N(0,1), W ~ N(0,0.02), b = 0")
-            sample, ncores, scaling, dtype = "the full cell step (8 OpenBLAS sgemm on all host cores + 5 single-threaded JIT kernels)", cores, "weak", "f32"
-        elif w == "softmax":
-            rng = np.random.default_rng(1234)
-            save("a.npy", rng.standard_normal((4096, 1024)).astype(np.float32))
-            case, cargs, nbytes, flops = "softmax_naive", ["a.npy", "out.npy"], 4096 * 1024 * 8, 0
-            wl = "C1 exp(a-max(a,{-1},true))/sum(exped,{-1},true), fp32 [4096,1024] ~ N(0,1) per GPU"
-            sample, ncores, scaling, dtype = "the full [4096,1024] batch per step", 1, "weak", "f32"
-        elif w == "reduce":
-            rng = np.random.default_rng(1236)
-            m = 2048
-            save("x.npy", (rng.random((m, m)) * 2 - 1).astype(np.float32))
-            case, cargs, nbytes, flops = "reduce", ["sum", "0", "x.npy", "out.npy"], m * m * 4, 0
-            wl = "C3 op::sum over axis 0 of fp32 [8192,8192] ~ U(-1,1) per GPU"
-            sample, ncores, scaling, dtype = "a [2048,2048] array per step (1/16 of the bytes)", 1, "weak", "f32"
-        elif w == "gemm":
-            rng = np.random.default_rng(1237)
-            m = 2048
-            save("A.npy", (rng.standard_normal((m, m)) * 0.02).astype(np.float32))
-            save("B.npy", (rng.standard_normal((m, m)) * 0.02).astype(np.float32))
-            save("bias.npy", (rng.standard_normal(m) * 0.1).astype(np.float32))
-            case, cargs, nbytes, flops = "gemm_tanh", ["A.npy", "B.npy", "bias.npy", "out.npy"], 3 * m * m * 2, 2.0 * m ** 3
-            wl = "C4 tanh(dot(A,B)+bias), bf16 A,B [8192,8192] ~ N(0,0.02), bias ~ N(0,0.1), fp32 accumulate, bf16 out"
-            sample, ncores, scaling, dtype = "2048^3 in fp32 per step (the reference has no bf16; 1/64 of the flops)", cores, "weak", "f32"
-        elif w == "transpose":
-            rng = np.random.default_rng(1241)
-            m = 2048
-            save("x.npy", rng.standard_normal((m, m)).astype(np.float32))
-            case, cargs, nbytes, flops = "unary_t", ["tanh", "x.npy", "out.npy"], 2 * m * m * 4, 0
-            wl = "y = tanh(x).transpose(), fp32 [8192,8192] ~ N(0,1) per GPU"
-            sample, ncores, scaling, dtype = "a [2048,2048] array per step (1/16 of the bytes)", 1, "weak", "f32"
-        elif w == "scan":
-            rng = np.random.default_rng(1240)
-            m = 4
-            save("x.npy", (rng.random((m, 8192)) * 2 - 1).astype(np.float32))
-            case, cargs, nbytes, flops = "scan", ["sum", "1", "x.npy", "out.npy"], 2 * m * 8192 * 4, 0
-            wl = "op::cumsum over the last axis of fp32 [8192,8192] ~ U(-1,1) per GPU (inclusive)"
-            sample, ncores, scaling, dtype = "4 of the 8192 rows per step (the reference's CPU scan is quadratic in the row length)", 1, "weak", "f32"
-        else:
-            rng = np.random.default_rng(1234 + 4)
-            m = 1 << 24
-            save("x.npy", rng.standard_normal(m).astype(np.float32))
-            case, cargs, nbytes, flops = "chain", ["x.npy", "0.5", "0.1", "out.npy"], m * 4, 0
-            wl = "C5 sum(sigmoid(x*w+b)*exp(-x*x)), fp32 x ~ N(0,1), 2^31 elements total, w=0.5 b=0.1"
-            sample, ncores, scaling, dtype = "2^24 elements per step (1/128 of the workload; the reference's int sizes cap a chunk at 2^28)", 1, "strong", "f32"
-        times = run_ref_driver(case, cargs, args.warmup + args.steps, tmp)
-    timed = times[args.warmup:]
-    ms = sum(timed) / len(timed)
-    gbs = nbytes / (ms * 1e-3) / 1e9
+    cls = WORKLOADS[args.workload]
+    kw = workload_kwargs(args, args.workload)
+    times, case = time_reference(cls, kw, args.steps, args.warmup)
+    ms = sum(times) / len(times)
+    gbs = case["bytes"] / (ms * 1e-3) / 1e9
     line = {"metric": "fused_expr_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": scaling,
-            "vs_baseline": None, "dtype": dtype, "data": "synthetic", "impl": "reference",
-            "config": {"workload": wl},
-            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": ncores, "kind": "reference", "sample": sample},
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": cls.scaling,
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "reference",
+            "config": cls.config(args.gpus, **kw),
+            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": case["cores"], "kind": "reference", "sample": case["sample"]},
             "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    if flops:
-        line["gemm_tflops"] = flops / (ms * 1e-3) / 1e12
+    if case.get("flops"):
+        line["gemm_tflops"] = case["flops"] / (ms * 1e-3) / 1e12
     print(json.dumps(line))
 
 
-def measure(wl, torch, world, steps, warmup, lib, sample_clocks=True, local=0):
-    """Times exactly `steps` steps (device time, max over ranks).  Returns a dict."""
+def measure(wl, torch, world, steps, warmup, lib, local=0, min_blocks=5, clock_seconds=1.5):
+    """Times blocks of exactly `steps` steps (device time, max over ranks): the first block is the reported one, at
+    least `min_blocks` are run and their median is reported beside it.  Returns a dict."""
     def barrier():
         if world > 1:
             torch.distributed.barrier()
@@ -936,11 +1009,9 @@ def measure(wl, torch, world, steps, warmup, lib, sample_clocks=True, local=0):
             stepper.replay()
         torch.cuda.synchronize()
         # Untimed spin-up on top of the `warmup` steps: a step of tens of microseconds leaves a GPU that has just come
-        # out of idle no time to reach its clocks (one default run measured 59 us per LSTM step right after another
-        # process had left the GPU idle, 35 us otherwise).  ~150 ms of the same replays, the same number on every
-        # rank (a step may hold a collective).  Only for such short steps: a block of milliseconds has warmed the GPU
-        # up by itself, and more untimed work would move a power-capped GEMM from its burst clocks to its sustained
-        # ones before the block is timed.
+        # out of idle no time to reach its clocks.  ~150 ms of the same replays, the same number on every rank (a step
+        # may hold a collective).  Only for such short steps: a block of milliseconds has warmed the GPU up by itself,
+        # and more untimed work would move a power-capped GEMM from its burst clocks to its sustained ones.
         est = torch.tensor([(time.perf_counter() - t_spin) / 2], dtype=torch.float64, device="cuda")
         if world > 1:
             torch.distributed.all_reduce(est, op=torch.distributed.ReduceOp.MAX)
@@ -949,10 +1020,8 @@ def measure(wl, torch, world, steps, warmup, lib, sample_clocks=True, local=0):
             for _ in range(min(2000, int(0.15 / est) + 1)):
                 stepper.replay()
     barrier()
-    sampler = ClockSampler(local) if sample_clocks else None
-    if sampler:
-        sampler.start()
-    launches0 = lib.cache_stats()["launches"]
+    sampler = ClockSampler(local)
+    sampler.start()
     block_ms = []
 
     def one_block():
@@ -970,27 +1039,22 @@ def measure(wl, torch, world, steps, warmup, lib, sample_clocks=True, local=0):
         block_ms.append(ev0.elapsed_time(ev1))
 
     one_block()        # the reported block: exactly `steps` steps
-    # more blocks only to keep the GPU busy ~1.5 s while nvidia-smi samples the clocks; every rank must run
-    # the same number of them (each ends in a barrier), so the count is agreed on, not timed per rank
-    extra = 0
-    if sample_clocks:
-        extra = int(min(200, max(0, 1500.0 / max(block_ms[0], 1e-3))))
-        if world > 1:
-            cnt = torch.tensor([extra], dtype=torch.int64, device="cuda")
-            torch.distributed.all_reduce(cnt, op=torch.distributed.ReduceOp.MAX)
-            extra = int(cnt.item())
+    # more blocks: the median beside the reported figure, and a GPU kept busy while nvidia-smi samples the clocks;
+    # every rank must run the same number of them (each ends in a barrier), so the count is agreed on, not timed per rank
+    extra = int(min(200, max(min_blocks - 1, clock_seconds * 1e3 / max(block_ms[0], 1e-3))))
+    if world > 1:
+        cnt = torch.tensor([extra], dtype=torch.int64, device="cuda")
+        torch.distributed.all_reduce(cnt, op=torch.distributed.ReduceOp.MAX)
+        extra = int(cnt.item())
     for _ in range(extra):
         one_block()
-    clocks = sampler.stop() if sampler else None
-    # the reported figure is the FIRST timed block of exactly `steps` steps; later blocks only keep
-    # the GPU busy while nvidia-smi samples the clocks
-    t = torch.tensor([block_ms[0]], dtype=torch.float64, device="cuda")
+    clocks = sampler.stop()
+    t = torch.tensor([block_ms[0], sorted(block_ms)[len(block_ms) // 2]], dtype=torch.float64, device="cuda")
     if world > 1:
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-    ms_step = float(t.item()) / steps
-    res = {"ms_per_step": ms_step, "clocks": clocks, "graph": bool(stepper),
-           "gpu_launches": steps * getattr(wl, "launches_per_step", 1),
-           "median_block_ms_per_step": sorted(block_ms)[len(block_ms) // 2] / steps}
+    res = {"ms_per_step": float(t[0].item()) / steps, "clocks": clocks, "graph": bool(stepper),
+           "gpu_launches": steps * wl.launches_per_step,
+           "median_block_ms_per_step": float(t[1].item()) / steps, "blocks": len(block_ms)}
     # dominant kernel alone, replayed back to back
     dom = wl.dominant()
     if dom:
@@ -1043,7 +1107,55 @@ def roofline_of(wl, m, lib):
     return {"bound": "hbm", "achieved": achieved, "peak": peak_hbm, "unit": "GB/s", "frac": achieved / peak_hbm,
             "traffic": ratio * work if ratio else None,
             "peak_source": (kind + " (MEASURED_PEAKS.json hbm_gbs)") if kind == "measured" else "fallback 6.65 TB/s",
-            "kernel": getattr(wl, "kernel_name", None) or lib.last_variant(), "kernel_ms": ms}
+            "kernel": getattr(wl, "kernel_name", None) or lib.last_variant(), "kernel_ms": ms,
+            "note": "per rank: the step's kernel(s), the exchange between the ranks included" if wl.has_collective() else None}
+
+
+def end_to_end(wl, torch, world, steps):
+    """The same metric through the public call with page-locked HOST buffers, copies inside the timed region."""
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    job_bytes = wl.bytes_per_step() * world
+    external = getattr(wl, "e2e_external", None)
+    if external:
+        # the workload's end-to-end loop is a C++ program written against the front end's own headers
+        n_e2e = max(steps, 200)
+        barrier()
+        dt = external(5, n_e2e) * 1e-3
+        barrier()
+    else:
+        n_e2e = max(1, min(steps, 5))
+        wl.e2e_setup()
+        for i in range(2):
+            wl.e2e_step(i)
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(n_e2e):
+            wl.e2e_step(i)      # synchronous: returns after the result is back in host memory
+        barrier()
+        dt = (time.perf_counter() - t0) / n_e2e
+    te = torch.tensor([dt], dtype=torch.float64, device="cuda")
+    if world > 1:
+        torch.distributed.all_reduce(te, op=torch.distributed.ReduceOp.MAX)
+    return {"value": job_bytes / float(te.item()) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": wl.h2d,
+            "d2h_bytes_per_step": wl.d2h, "steps": n_e2e, "ms_per_step": float(te.item()) * 1e3,
+            "api": getattr(wl, "e2e_api", "dalib200_launch_host / C ABI with pinned host buffers (alloc from pool + H2D + "
+                                           "kernel + D2H + sync per step)")}
+
+
+def cpu_baseline_of(cls, kw):
+    times, case = time_reference(cls, kw, 8, 1)
+    if not times:
+        return None
+    best = sorted(times)[len(times) // 2]
+    cpu = {"value": case["bytes"] / (best * 1e-3) / 1e9, "unit": "GB/s", "cores": case["cores"], "kind": "reference",
+           "sample": case["sample"], "ms": best}
+    if case.get("flops"):
+        cpu["tflops"] = case["flops"] / (best * 1e-3) / 1e12
+    return cpu
 
 
 def main():
@@ -1052,10 +1164,12 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="lstm", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="chain", choices=sorted(WORKLOADS))
     ap.add_argument("--elements", type=int, default=0, help="chain: total elements (profiling on a small case)")
     ap.add_argument("--gemm-n", type=int, default=0, help="gemm: matrix size (profiling on a small case)")
     ap.add_argument("--scan-shape", default="", help="scan: R,C instead of 8192,8192 (the variants for short and for few, very long rows)")
+    ap.add_argument("--reduce-op", default="sum", choices=["sum", "max", "argmax"], help="reduce: the reducer")
+    ap.add_argument("--axis", default="0", choices=["-1", "0", "all"], help="reduce: the reduced axis")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-others", action="store_true")
@@ -1072,111 +1186,74 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
     torch.cuda.set_device(local)
+    lib = dali_b200.load_library()
+    lib.init(0)
+    transport = "none"
     if world > 1:
         import datetime
+        from dali_b200 import comm
         # a rank that falls out of step ends the run in two minutes, not ten
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local),
                                              timeout=datetime.timedelta(seconds=120))
-    lib = dali_b200.load_library()
-    lib.init(0)
+        comm.init_from_torch(lib, local)       # the library's own communicator: NCCL + the ranks' peer-memory mapping
+        transport = lib.comm_transport()
     dev_index = local      # the library indexes the devices it bound; one process per GPU uses its own
 
-    def build(name):
-        kw = {}
-        if name == "chain" and args.elements:
-            kw["total"] = args.elements
-        if name == "gemm" and args.gemm_n:
-            kw["n"] = args.gemm_n
-        if name == "scan" and args.scan_shape:
-            kw["shape"] = tuple(int(v) for v in args.scan_shape.split(","))
-        return WORKLOADS[name](lib, torch, rank, world, dev_index, **kw)
+    def run(name, kw, steps, warmup, cpu_wanted, e2e_wanted, clock_seconds):
+        wl = WORKLOADS[name](lib, torch, rank, world, dev_index, **kw)
+        wl.verify()
+        m = measure(wl, torch, world, steps, warmup, lib, local, clock_seconds=clock_seconds)
+        roofline = roofline_of(wl, m, lib)
+        if hasattr(wl, "extra"):
+            roofline.update(wl.extra(torch))
+        e2e = end_to_end(wl, torch, world, steps) if e2e_wanted else None
+        cpu = cpu_baseline_of(WORKLOADS[name], kw) if (cpu_wanted and rank == 0 and world == 1) else None
+        return {"wl": wl, "m": m, "roofline": roofline, "e2e": e2e, "cpu": cpu}
 
-    wl = build(args.workload)
-    wl.verify()
-    m = measure(wl, torch, world, args.steps, args.warmup, lib, True, local)
+    kw = workload_kwargs(args, args.workload)
+    main_res = run(args.workload, kw, args.steps, args.warmup, not args.no_cpu, not args.no_e2e, 1.5)
+    wl, m = main_res["wl"], main_res["m"]
     ms_step = m["ms_per_step"]
-    job_bytes = wl.bytes_per_step() * world
-    value = job_bytes / (ms_step * 1e-3) / 1e9
-    roofline = roofline_of(wl, m, lib)
+    value = wl.bytes_per_step() * world / (ms_step * 1e-3) / 1e9
+    line = {"metric": "fused_expr_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "median_block_ms_per_step": m["median_block_ms_per_step"],
+            "timed_blocks": m["blocks"], "higher_is_better": True, "scaling": wl.scaling,
+            "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+            "config": WORKLOADS[args.workload].config(world, **kw), "clocks": m["clocks"], "roofline": main_res["roofline"],
+            "cpu_baseline": main_res["cpu"], "e2e": main_res["e2e"],
+            "gpu_launches": int(m["gpu_launches"]), "timed_with": "CUDA graph replay of the step's launches" if m["graph"] else "eager launches",
+            "rank_exchange": transport}
+    if wl.hbm_metric:
+        line["pct_of_nominal_8TBs"] = 100.0 * value / world / 8000.0
+    if wl.flops_per_step():
+        line["gemm_tflops"] = wl.flops_per_step() * world / (ms_step * 1e-3) / 1e12
+    del wl, main_res
 
-    def barrier():
-        if world > 1:
-            torch.distributed.barrier()
-        torch.cuda.synchronize()
-
-    e2e = None
-    if not args.no_e2e:
-        n_e2e = max(1, min(args.steps, 5))
-        external = getattr(wl, "e2e_external", None)
-        if external:
-            # the workload's end-to-end loop is a C++ program written against the front end's own headers
-            barrier()
-            dt = external(3, max(n_e2e, 20)) * 1e-3
-            n_e2e = max(n_e2e, 20)
-            barrier()
-        else:
-            wl.e2e_setup()
-            for i in range(2):
-                wl.e2e_step(i)
-            barrier()
-            t0 = time.perf_counter()
-            for i in range(n_e2e):
-                wl.e2e_step(i)      # synchronous: returns after the result is back in host memory
-            barrier()
-            dt = (time.perf_counter() - t0) / n_e2e
-        te = torch.tensor([dt], dtype=torch.float64, device="cuda")
-        if world > 1:
-            torch.distributed.all_reduce(te, op=torch.distributed.ReduceOp.MAX)
-        e2e = {"value": job_bytes / float(te.item()) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": wl.h2d,
-               "d2h_bytes_per_step": wl.d2h, "steps": n_e2e, "ms_per_step": float(te.item()) * 1e3,
-               "api": getattr(wl, "e2e_api", "dalib200_launch_host / C ABI with pinned host buffers (alloc from pool + H2D + "
-                                              "kernel + D2H + sync per step)")}
-
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu:
-        import tempfile
-        with tempfile.TemporaryDirectory() as tmp:
-            r = wl.cpu_baseline(tmp, 8)
-        if r:
-            best = sorted(r["ms"])[len(r["ms"]) // 2]
-            cpu = {"value": r["bytes"] / (best * 1e-3) / 1e9, "unit": "GB/s", "cores": r["cores"], "kind": r["kind"],
-                   "sample": r["sample"], "ms": best}
-            if r.get("flops"):
-                cpu["tflops"] = r["flops"] / (best * 1e-3) / 1e12
-
-    others = None
-    if args.workload == "lstm" and not args.no_others and world == 1:
+    if args.workload == "chain" and not args.no_others and not args.elements:
         others = {}
-        for name in ("gemm", "softmax", "reduce", "chain", "scan", "transpose"):   # the power-capped GEMM before the GPU is hot
-            del wl
+        todo = [("gemm", {}), ("softmax", {}), ("lstm", {})] + [("reduce", {"op": o, "axis": a}) for o, a in REDUCE_SWEEP] + \
+               [("scan", {}), ("transpose", {}), ("gather", {})]       # the power-capped GEMM before the GPU is hot
+        for name, okw in todo:
             torch.cuda.empty_cache()
-            time.sleep(1.0)      # each workload starts from a rested GPU, as its own `--workload` run would (power cap)
-            wl = build(name)
-            wl.verify()
-            mo = measure(wl, torch, world, 24, 3, lib, False, local)      # 24: whole steps on each of the softmax lanes
-            ro = roofline_of(wl, mo, lib)
-            entry = {"workload": wl.describe()["workload"], "ms_per_step": mo["ms_per_step"],
-                     "gbs": wl.bytes_per_step() / (mo["ms_per_step"] * 1e-3) / 1e9,
-                     "roofline": {k: ro[k] for k in ("bound", "achieved", "peak", "unit", "frac", "frac_of_sustained_peak", "kernel") if k in ro}}
-            if wl.flops_per_step():
-                entry["tflops"] = wl.flops_per_step() / (mo["ms_per_step"] * 1e-3) / 1e12
-            others[name] = entry
-        wl = build("lstm")
+            time.sleep(0.5)      # each workload starts from a rested GPU, as its own `--workload` run would (power cap)
+            r = run(name, okw, 24, 3, not args.no_cpu, not args.no_e2e, 1.0)
+            w, mo = r["wl"], r["m"]
+            entry = {"config": WORKLOADS[name].config(world, **okw), "scaling": w.scaling, "ms_per_step": mo["ms_per_step"],
+                     "median_block_ms_per_step": mo["median_block_ms_per_step"],
+                     "value": w.bytes_per_step() * world / (mo["ms_per_step"] * 1e-3) / 1e9, "unit": "GB/s",
+                     "roofline": {k: v for k, v in r["roofline"].items() if v is not None}, "clocks": mo["clocks"],
+                     "e2e": r["e2e"], "cpu_baseline": r["cpu"], "gpu_launches": int(mo["gpu_launches"])}
+            if w.flops_per_step():
+                entry["tflops"] = w.flops_per_step() * world / (mo["ms_per_step"] * 1e-3) / 1e12
+            key = name if name != "reduce" else "reduce_%s_axis_%s" % (okw["op"], okw["axis"].replace("-1", "last"))
+            others[key] = entry
+            del w, r
+        line["other_workloads"] = others
 
     if rank == 0:
-        cfg = wl.describe()
-        line = {"metric": "fused_expr_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": wl.scaling,
-                "vs_baseline": None, "dtype": "bf16" if args.workload == "gemm" else "f32", "data": "synthetic",
-                "config": cfg, "clocks": m["clocks"], "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
-                "gpu_launches": int(m["gpu_launches"]), "timed_with": "CUDA graph replay of the step's launches" if m["graph"] else "eager launches",
-                "pct_of_nominal_8TBs": 100.0 * value / world / 8000.0}
-        if wl.flops_per_step():
-            line["gemm_tflops"] = wl.flops_per_step() * world / (ms_step * 1e-3) / 1e12
-        if others:
-            line["other_workloads"] = others
         print(json.dumps(line))
     if world > 1:
+        lib.comm_destroy()
         torch.distributed.destroy_process_group()
 
 

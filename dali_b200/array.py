@@ -36,6 +36,10 @@ def _c():
         c.dali_array_dtype.argtypes = [_H]
         c.dali_array_is_buffer.argtypes = [_H]
         c.dali_array_scalar.argtypes = [ctypes.c_double, ctypes.c_int, ctypes.POINTER(_H)]
+        c.dali_array_set_shard.argtypes = [_H, ctypes.c_int, ctypes.c_int64, ctypes.c_int64]
+        c.dali_array_get_shard.argtypes = [_H, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64)]
+        c.dali_lazy_collectives.restype = ctypes.c_size_t
+        c.dali_lazy_collectives.argtypes = [ctypes.POINTER(ctypes.c_int64), ctypes.c_char_p, ctypes.c_size_t]
         _lib = L
     return _lib
 
@@ -124,6 +128,28 @@ class Array:
         """Wraps device memory owned by the caller (e.g. a torch CUDA tensor's data_ptr())."""
         return Array._new(_c().c.dali_array_from_device, ctypes.c_void_p(int(ptr)), _shape_arg(shape), len(shape),
                           int(dtype), int(gpu))
+
+    # ---- sharding over the ranks of the communicator (dali_b200.comm) ---------------------------------------
+    @staticmethod
+    def scatter_rows(array):
+        """Keeps this rank's rows of a (global) numpy array and marks them as a shard along axis 0."""
+        arr = np.ascontiguousarray(array)
+        if arr.dtype not in _NP2D:
+            arr = arr.astype(np.float32 if arr.dtype.kind == "f" else np.int32)
+        return Array._new(_c().c.dali_array_scatter_rows, ctypes.c_void_p(arr.ctypes.data), _shape_arg(arr.shape), arr.ndim,
+                          _NP2D[arr.dtype])
+
+    def set_shard(self, axis, lo, total):
+        """Declares this array to be indices [lo, lo + extent) of `total` along `axis` of a logical array spread over the ranks."""
+        _check(_c().c.dali_array_set_shard(self._h, int(axis), ctypes.c_int64(lo), ctypes.c_int64(total)))
+        return self
+
+    @property
+    def shard(self):
+        """(axis, lo, total); axis < 0: not sharded."""
+        axis, lo, total = ctypes.c_int(-1), ctypes.c_int64(0), ctypes.c_int64(0)
+        _check(_c().c.dali_array_get_shard(self._h, ctypes.byref(axis), ctypes.byref(lo), ctypes.byref(total)))
+        return axis.value, lo.value, total.value
 
     # ---- inspection ---------------------------------------------------------------------
     @property
@@ -409,6 +435,14 @@ def lazy_stats():
     s = (ctypes.c_int64 * 3)()
     _c().c.dali_lazy_stats(s)
     return {"kernels": int(s[0]), "gemms": int(s[1]), "temporaries": int(s[2])}
+
+
+def collectives():
+    """(number of cross-rank combines issued by this thread's evaluations, description of the last one)."""
+    n = ctypes.c_int64(0)
+    buf = ctypes.create_string_buffer(1 << 12)
+    _c().c.dali_lazy_collectives(ctypes.byref(n), buf, len(buf))
+    return int(n.value), buf.value.decode()
 
 
 def set_dry_run(on):

@@ -22,7 +22,8 @@ CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-Wno-sign-compare", "-I" + 
 
 
 def _embed_prelude():
-    src = open(os.path.join(CSRC, "prelude.cuh")).read()
+    # the peer-exchange layout and its device helpers come first: generated kernels that reduce across ranks use them
+    src = "".join(open(os.path.join(CSRC, f)).read() + "\n" for f in ("peer.h", "peer_device.cuh", "prelude.cuh"))
     assert ')DALIPRELUDE"' not in src
     out = os.path.join(CSRC, "prelude_embed.inc")
     text = 'R"DALIPRELUDE(' + src + ')DALIPRELUDE"\n'
@@ -37,6 +38,21 @@ def _embed(src_name, out_name, tag):
     assert close not in src
     out = os.path.join(CSRC, out_name)
     text = 'R"' + tag + "(" + src + close + "\n"
+    if not os.path.exists(out) or open(out).read() != text:
+        with open(out, "w") as f:
+            f.write(text)
+
+
+def _embed_source_hash():
+    """A hash of everything that decides what a generated kernel looks like and how its parameter block is laid out:
+    part of every cache key, so that a cubin written by another build of the library is never loaded by this one."""
+    import hashlib
+    h = hashlib.sha256()
+    for f in ("codegen.cc", "codegen.h", "plan.cc", "ir.cc", "ir.h", "gemm_sm100.cc", "gemm_sm100.cuh", "peer.h", "peer_device.cuh",
+              "prelude.cuh"):
+        h.update(open(os.path.join(CSRC, f), "rb").read())
+    out = os.path.join(CSRC, "source_hash.inc")
+    text = '"' + h.hexdigest()[:16] + '"\n'
     if not os.path.exists(out) or open(out).read() != text:
         with open(out, "w") as f:
             f.write(text)
@@ -66,6 +82,7 @@ def build(force=False, verbose=False):
     os.makedirs(objdir, exist_ok=True)
     _embed_prelude()
     _embed("gemm_sm100.cuh", "gemm_embed.inc", "DALIGEMM")
+    _embed_source_hash()
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh", ".inc"))]
     headers += [os.path.join(HERE, "..", "include", f) for f in os.listdir(os.path.join(HERE, "..", "include"))]
     for d in (os.path.join(CSRC, "host"), os.path.join(HERE, "host", "include", "dali", "array")):

@@ -83,6 +83,23 @@ class Library:
         c.dalib200_last_gemm_kernel.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
         c.dalib200_cache_set_dir.argtypes = [ctypes.c_char_p]
         c.dalib200_cache_stats.argtypes = [ctypes.POINTER(ctypes.c_uint64)]
+        # ranks and collectives
+        self.HOST_ALLREDUCE = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_int)
+        self.HOST_ALLGATHER = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64)
+        c.dalib200_comm_unique_id.argtypes = [ctypes.c_void_p]
+        c.dalib200_comm_init_rank.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        c.dalib200_comm_init_host.argtypes = [ctypes.c_int, ctypes.c_int, self.HOST_ALLREDUCE, self.HOST_ALLGATHER, ctypes.c_void_p]
+        c.dalib200_comm_transport.restype = ctypes.c_size_t
+        c.dalib200_comm_transport.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
+        c.dalib200_comm_error_flag.argtypes = [ctypes.POINTER(ctypes.c_int)]
+        c.dalib200_shard_range.argtypes = [ctypes.c_int64, ctypes.c_int, ctypes.c_int, c_i64p, c_i64p]
+        c.dalib200_allreduce.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_int]
+        c.dalib200_arg_allreduce.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                             ctypes.c_int, ctypes.c_int]
+        c.dalib200_peer_emulate.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                            ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p), ctypes.c_int64,
+                                            ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
+        self._host_callbacks = None
         self._next_hash = 0x0da11b200
 
     # -- errors ---------------------------------------------------------------
@@ -261,6 +278,85 @@ class Library:
         buf = ctypes.create_string_buffer(512)
         self.c.dalib200_last_gemm_kernel(buf, len(buf))
         return buf.value.decode()
+
+    # -- ranks and collectives ---------------------------------------------------
+    OPS = {"sum": 0, "prod": 1, "max": 2, "min": 3}
+
+    def comm_unique_id(self):
+        buf = ctypes.create_string_buffer(128)
+        self.check(self.c.dalib200_comm_unique_id(buf))
+        return buf.raw
+
+    def comm_init_rank(self, device, world, rank, unique_id=None):
+        self.check(self.c.dalib200_comm_init_rank(device, world, rank, unique_id))
+
+    def comm_init_host(self, world, rank, allreduce, allgather):
+        """allreduce(buf_address, n, dtype, op) / allgather(send_address, recv_address, nbytes): Python callables on host
+        memory addresses; they return nothing and raise on failure."""
+        def ar(ctx, buf, n, dtype, op):
+            try:
+                allreduce(buf, n, dtype, op)
+                return 0
+            except Exception:       # the C side reports the failure as a status
+                return 1
+
+        def ag(ctx, send, recv, nbytes):
+            try:
+                allgather(send, recv, nbytes)
+                return 0
+            except Exception:
+                return 1
+        self._host_callbacks = (self.HOST_ALLREDUCE(ar), self.HOST_ALLGATHER(ag))      # kept alive for the C side
+        self.check(self.c.dalib200_comm_init_host(world, rank, self._host_callbacks[0], self._host_callbacks[1], None))
+
+    def comm_destroy(self):
+        self.check(self.c.dalib200_comm_destroy())
+        self._host_callbacks = None
+
+    def comm_world(self):
+        return self.c.dalib200_comm_world()
+
+    def comm_rank(self):
+        return self.c.dalib200_comm_rank()
+
+    def comm_transport(self):
+        buf = ctypes.create_string_buffer(512)
+        self.c.dalib200_comm_transport(buf, len(buf))
+        return buf.value.decode()
+
+    def comm_error_flag(self):
+        f = ctypes.c_int(0)
+        self.check(self.c.dalib200_comm_error_flag(ctypes.byref(f)))
+        return f.value
+
+    def shard_range(self, n, rank, world):
+        lo, hi = ctypes.c_int64(0), ctypes.c_int64(0)
+        self.check(self.c.dalib200_shard_range(n, rank, world, ctypes.byref(lo), ctypes.byref(hi)))
+        return lo.value, hi.value
+
+    @staticmethod
+    def _buf(x):
+        if isinstance(x, np.ndarray):
+            return ctypes.c_void_p(x.ctypes.data)
+        return ctypes.c_void_p(x.data_ptr() if hasattr(x, "data_ptr") else int(x))
+
+    def allreduce(self, buf, n, dtype, op, device=0, stream=None):
+        """buf: torch CUDA tensor / device address, or (device = -1, host transport) a numpy array."""
+        self.check(self.c.dalib200_allreduce(device, ctypes.c_void_p(stream or 0), self._buf(buf), n, dtype, self.OPS.get(op, op)))
+
+    def arg_allreduce(self, values, indices, n, dtype, op, device=0, stream=None):
+        self.check(self.c.dalib200_arg_allreduce(device, ctypes.c_void_p(stream or 0), self._buf(values), self._buf(indices), n,
+                                                 dtype, self.OPS.get(op, op)))
+
+    def peer_emulate(self, bufs, n, dtype, op, indices=None, repeats=1, device=0, stream=None):
+        """The peer-exchange protocol with len(bufs) virtual ranks in one kernel on one GPU; returns the error flag."""
+        world = len(bufs)
+        pb = (ctypes.c_void_p * world)(*[self._buf(b).value for b in bufs])
+        pi = (ctypes.c_void_p * world)(*[self._buf(i).value for i in indices]) if indices is not None else None
+        flag = ctypes.c_int(0)
+        self.check(self.c.dalib200_peer_emulate(device, ctypes.c_void_p(stream or 0), world, dtype, self.OPS.get(op, op),
+                                                int(indices is not None), pb, pi, n, repeats, ctypes.byref(flag)))
+        return flag.value
 
     # -- memory ---------------------------------------------------------------
     def alloc(self, nbytes, device=0):

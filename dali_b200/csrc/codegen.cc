@@ -22,6 +22,7 @@ std::string Variant::key() const {
     s << kind_name() << ".o" << nout << ".i" << nin << ".v" << vec << ".nt" << threads << ".T" << T
       << ".p" << vpt << ".u" << unroll << ".x" << tx << ".y" << ty << "." << cls << "." << ocls;
     if (tile) s << ".tile" << tile;
+    if (xrank) s << ".xrank";
     return s.str();
 }
 
@@ -783,6 +784,52 @@ struct Gen {
                 o << "    acc" << si << " = block_arg_reduce<" << red_struct(s.name) << ", NT>(acc" << si << ", sm" << si << ");\n";
         }
         o << "  }\n";
+        if (p.has_xrank) {
+            // One CTA of the launch reaches this point holding the rank's results.  Thread r stores them into this
+            // rank's slot on rank r (plain stores into peer memory over NVLink), raises the slot's flag there to this
+            // call's epoch and waits -- bounded -- until rank r's results have arrived in this GPU's own block; then
+            // every thread folds the slots of the own block in rank order, the same order on every rank.
+            int k = 0;
+            for (int si : reds) if (p.stmts[si].xrank) ++k;
+            if (k * 16 > 256) { *err = "more than 16 cross-rank reductions in one kernel"; return false; }
+            o << "  {\n";
+            o << "    const DaliPeerTable* const pt = reinterpret_cast<const DaliPeerTable*>(" << W(L.w_aux0) << ");\n";
+            o << "    __shared__ unsigned long long xr_epoch;\n";
+            o << "    if (tid == 0) xr_epoch = pt->epoch[1] + 1;\n";
+            o << "    __syncthreads();\n";
+            o << "    const unsigned long long epoch = xr_epoch;\n";
+            o << "    const int parity = (int)(epoch & 1);\n";
+            for (int si : reds) {
+                const Stmt& s = p.stmts[si];
+                if (s.xrank && s.kind == S_ARGRED && s.xrank_offset >= 0)
+                    o << "    acc" << si << ".i += (i64)" << vn(s.xrank_offset) << ";\n";
+            }
+            o << "    if (tid < pt->world) {\n";
+            o << "      char* const slot = dali_peer_fused_slot(pt->block[tid], parity, pt->rank);\n";
+            k = 0;
+            for (int si : reds) {
+                const Stmt& s = p.stmts[si];
+                if (!s.xrank) continue;
+                o << "      *reinterpret_cast<" << acc_type(s) << "*>(slot + " << 16 * k++ << ") = acc" << si << ";\n";
+            }
+            o << "      __threadfence_system();\n";
+            o << "      dali_peer_flag_release(dali_peer_fused_flag(pt->block[tid], parity, pt->rank), epoch);\n";
+            o << "      dali_peer_wait(dali_peer_fused_flag(pt->block[pt->rank], parity, tid), epoch, pt->wait_ns, pt->error);\n";
+            o << "    }\n";
+            o << "    __syncthreads();\n";
+            k = 0;
+            for (int si : reds) {
+                const Stmt& s = p.stmts[si];
+                if (!s.xrank) continue;
+                const std::string at = "reinterpret_cast<const " + acc_type(s) + "*>(dali_peer_fused_slot(pt->block[pt->rank], parity, r_) + " +
+                                       std::to_string(16 * k++) + ")";
+                o << "    { int r_ = 0; acc" << si << " = ld_cg(" << at << ");\n";
+                o << "      for (r_ = 1; r_ < pt->world; ++r_) acc" << si << " = " << acc_merge(s, "acc" + std::to_string(si), "ld_cg(" + at + ")") << "; }\n";
+            }
+            o << "    __syncthreads();\n";
+            o << "    if (tid == 0) pt->epoch[1] = epoch;\n";
+            o << "  }\n";
+        }
         for (int si : reds) {
             const Stmt& s = p.stmts[si];
             o << "  const " << ct(s.dtype) << " " << vn(s.id) << " = " << acc_result(s, "acc" + std::to_string(si)) << ";\n";

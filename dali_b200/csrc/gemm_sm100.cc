@@ -392,7 +392,9 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
     const uint64_t b_cols = (uint64_t)n * (uint64_t)slices;      // columns of the product (rows of the transposed B)
     // (the skeleton and the prelude are hashed once: tens of kilobytes of source, ~100 us per launch otherwise)
     static const std::string source_tag =
-        "|sm_100a|gemm-12|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" + std::to_string(fnv1a(device_prelude()));
+        std::string("|sm_100a|gemm|") +
+#include "source_hash.inc"
+        + "|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" + std::to_string(fnv1a(device_prelude()));
     std::ostringstream key;
     key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + source_tag);
     tl_gemm_variant = std::string(bf16 ? "tcgen05.bf16 " : "tcgen05.tf32x3 ") + v.key() + (n_pairs > 1 ? " x2" : "");

@@ -10,6 +10,10 @@
 #include "runtime.h"
 
 namespace dalib {
+// lo = x - hi, except for an infinite x: hi is then the infinity itself and inf - inf would turn every product with
+// this element into NaN where an fp32 GEMM gives +-inf; a zero low part keeps inf . y = inf (and inf . 0 = NaN, as there).
+__device__ __forceinline__ float tf32_lo(float v, float h) { return fabsf(h) == __int_as_float(0x7f800000) ? 0.0f : v - h; }
+
 
 __global__ void __launch_bounds__(256)
 split_tf32_kernel(const float* __restrict__ x, long long rows, long long cols4, long long ld4, float4* __restrict__ hi,
@@ -20,10 +24,10 @@ split_tf32_kernel(const float* __restrict__ x, long long rows, long long cols4, 
         const long long r = i / cols4, c = i - r * cols4;
         const float4 v = reinterpret_cast<const float4*>(x)[r * ld4 + c];
         float4 h, l;
-        h.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u); l.x = v.x - h.x;
-        h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u); l.y = v.y - h.y;
-        h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u); l.z = v.z - h.z;
-        h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u); l.w = v.w - h.w;
+        h.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u); l.x = tf32_lo(v.x, h.x);
+        h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u); l.y = tf32_lo(v.y, h.y);
+        h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u); l.z = tf32_lo(v.z, h.z);
+        h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u); l.w = tf32_lo(v.w, h.w);
         hi[i] = h;
         lo[i] = l;
     }
@@ -48,10 +52,10 @@ __global__ void __launch_bounds__(256) split_tf32_pair_kernel(const SplitPair p,
         const long long r = i / cols4, c = i - r * cols4;
         const float4 v = reinterpret_cast<const float4*>(p.x[w])[r * p.ld4[w] + c];
         float4 h, l;
-        h.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u); l.x = v.x - h.x;
-        h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u); l.y = v.y - h.y;
-        h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u); l.z = v.z - h.z;
-        h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u); l.w = v.w - h.w;
+        h.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u); l.x = tf32_lo(v.x, h.x);
+        h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u); l.y = tf32_lo(v.y, h.y);
+        h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u); l.z = tf32_lo(v.z, h.z);
+        h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u); l.w = tf32_lo(v.w, h.w);
         p.hi[w][i] = h;
         p.lo[w][i] = l;
     }
@@ -79,7 +83,7 @@ split_tf32_transpose_kernel(const float* __restrict__ x, long long rows, long lo
                 const float v = tile[tx][ty + 8 * i];
                 const float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
                 hi[c * rows + r] = h;
-                lo[c * rows + r] = v - h;
+                lo[c * rows + r] = tf32_lo(v, h);
             }
         }
         __syncthreads();

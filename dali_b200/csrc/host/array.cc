@@ -129,9 +129,6 @@ bool BufferView::contiguous() const {
     return true;
 }
 
-Reduce::Reduce(const std::string& reducer, const Array& a, int nreduce, bool arg, DType dtype)
-    : Expression(N_REDUCE, std::vector<int>(a.shape().begin(), a.shape().end() - nreduce), dtype, {a}),
-      reducer_(reducer), nreduce_(nreduce), arg_(arg) {}
 
 static std::vector<int> scan_shape(const Array& a, bool inclusive) {
     std::vector<int> s = a.shape();
@@ -139,7 +136,9 @@ static std::vector<int> scan_shape(const Array& a, bool inclusive) {
     return s;
 }
 Scan::Scan(const Array& a, const std::string& reducer, bool inclusive)
-    : Expression(N_SCAN, scan_shape(a, inclusive), a.dtype(), {a}), reducer_(reducer), inclusive_(inclusive) {}
+    : Expression(N_SCAN, scan_shape(a, inclusive), a.dtype(), {a}), reducer_(reducer), inclusive_(inclusive) {
+    DALI_ASSERT(shard_.axis != ndim() - 1, "a running reduction along the sharded axis is not supported (each rank holds only its part of every row)");
+}
 
 bool Iota::linear(int64_t* step) const {
     // walk from the innermost dim: stride[k] must equal step * (product of the extents after k)
@@ -161,7 +160,10 @@ static std::vector<int> gather_shape(const Array& source, const Array& indices) 
     return s;
 }
 Gather::Gather(const Array& source, const Array& indices)
-    : Expression(N_GATHER, gather_shape(source, indices), source.dtype(), {source, indices}) {}
+    : Expression(N_GATHER, gather_shape(source, indices), source.dtype(), {source, indices}) {
+    DALI_ASSERT(!source.shard().sharded(), "gather from a sharded source is not supported (the indices would name other ranks' rows)");
+    shard_ = indices.shard();          // out dims = the indices' dims, then the source's trailing dims
+}
 
 static std::vector<int> gather_rows_shape(const Array& source, const Array& indices) {
     std::vector<int> s = indices.shape();
@@ -169,10 +171,27 @@ static std::vector<int> gather_rows_shape(const Array& source, const Array& indi
     return s;
 }
 GatherFromRows::GatherFromRows(const Array& source, const Array& indices)
-    : Expression(N_GATHER_ROWS, gather_rows_shape(source, indices), source.dtype(), {source, indices}) {}
+    : Expression(N_GATHER_ROWS, gather_rows_shape(source, indices), source.dtype(), {source, indices}) {
+    const Shard s = source.shard(), i = indices.shard();
+    DALI_ASSERT(s.axis <= 0 && i.axis <= 0, "gather_from_rows: only the row dimension may be sharded");
+    DALI_ASSERT(!(s.sharded() && i.sharded()) || s == i, "gather_from_rows: source and indices are sharded differently");
+    shard_ = s.sharded() ? s : i;
+}
 
 MatMul::MatMul(const Array& left, const Array& right)
-    : Expression(N_MATMUL, {left.shape()[0], right.shape()[1]}, left.dtype(), {left, right}) {}
+    : Expression(N_MATMUL, {left.shape()[0], right.shape()[1]}, left.dtype(), {left, right}) {
+    const Shard l = left.shard(), r = right.shard();
+    if (l.axis == 1 || r.axis == 0) {
+        DALI_ASSERT(l.axis == 1 && r.axis == 0 && l.lo == r.lo && l.total == r.total,
+                    "dot: the contracted dimension must be sharded the same way on both operands");
+        partial_ = true;                // every rank ends up with the whole product
+    } else if (l.axis == 0) {
+        DALI_ASSERT(!r.sharded(), "dot: sharding along two dimensions of the product is not supported");
+        shard_ = l;
+    } else if (r.axis == 1) {
+        shard_ = r;
+    }
+}
 
 // ------------------------------------------------------------------ construction
 Array::Array() {}
@@ -187,6 +206,7 @@ Array::Array(const std::vector<int>& shape, std::shared_ptr<memory::Synchronized
 Array::Array(const Array& other, bool copy_memory) {
     if (copy_memory && !other.is_stateless()) {
         Array fresh(other.shape(), other.dtype(), other.preferred_device());
+        fresh.expression()->shard_ = other.shard();
         fresh.assign(other);
         fresh.eval();
         state_ = fresh.state_;
@@ -206,14 +226,14 @@ Array Array::zeros(const std::vector<int>& shape, DType dtype, memory::Device de
     as<BufferView>(out)->memory_->clear();   // zero on first touch
     return out;
 }
-Array Array::zeros_like(const Array& o) { return zeros(o.shape(), o.dtype(), o.preferred_device()); }
-Array Array::empty_like(const Array& o) { return Array(o.shape(), o.dtype(), o.preferred_device()); }
+Array Array::zeros_like(const Array& o) { Array r = zeros(o.shape(), o.dtype(), o.preferred_device()); r.expression()->shard_ = o.shard(); return r; }
+Array Array::empty_like(const Array& o) { Array r(o.shape(), o.dtype(), o.preferred_device()); r.expression()->shard_ = o.shard(); return r; }
 Array Array::ones(const std::vector<int>& shape, DType dtype, memory::Device dev) {
     Array out(shape, dtype, dev);
     out = 1;
     return out;
 }
-Array Array::ones_like(const Array& o) { return ones(o.shape(), o.dtype(), o.preferred_device()); }
+Array Array::ones_like(const Array& o) { Array r = ones(o.shape(), o.dtype(), o.preferred_device()); r.expression()->shard_ = o.shard(); return r; }
 
 Array Array::adopt_buffer(void* buffer, const std::vector<int>& shape, DType dtype, memory::Device loc,
                           const std::vector<int>& strides) {
@@ -297,6 +317,7 @@ void Array::eval(bool wait) const {
         set_expression(dest.expression());
     } else {
         Array dest(e->shape_, e->dtype_, preferred_device());
+        dest.expression()->shard_ = e->shard_;       // the result is the same part of the logical array as the value
         lazy::run_assignment(dest, OPERATOR_T_EQL, Array(e));
         set_expression(dest.expression());
     }
@@ -425,7 +446,9 @@ static Array make_view(const Array& a, const std::vector<int>& shape, const std:
             if (dims[k].src >= 0) nst[dims[k].src] += (int)(dims[k].step * st[k]);
         }
         // (the constructor drops the strides again when they are the contiguous ones)
-        return Array(std::make_shared<BufferView>(b->memory_, shape, b->dtype_, off, nst));
+        auto view = std::make_shared<BufferView>(b->memory_, shape, b->dtype_, off, nst);
+        view->shard_ = lazy::shard_through_view(b->shard_, b->shape_, dims, shape);
+        return Array(view);
     }
     if (e->kind_ == N_SCALAR) {
         return a;   // a scalar broadcasts by itself wherever it is used
@@ -602,6 +625,7 @@ Array Array::reshape(const std::vector<int>& new_shape_) const {
     }
     DALI_ASSERT(known == numel(), "New shape (" + shape_str(ns) + ") must have the same number of elements as previous shape (" + shape_str(shape()) + ")");
     if (ns == shape()) return *this;
+    const Shard reshaped = lazy::shard_through_reshape(shard(), shape(), ns);
     if (Iota* io = as<Iota>(*this)) {
         int64_t step;
         if (io->linear(&step)) {      // offset + step * linear index, whatever the shape
@@ -615,13 +639,16 @@ Array Array::reshape(const std::vector<int>& new_shape_) const {
     if (!src.is_buffer()) src.eval(false);
     if (!src.contiguous_memory()) src = src.ascontiguousarray();
     BufferView* b = as<BufferView>(src);
-    return Array(std::make_shared<BufferView>(b->memory_, ns, b->dtype_, b->offset_, std::vector<int>()));
+    auto out = std::make_shared<BufferView>(b->memory_, ns, b->dtype_, b->offset_, std::vector<int>());
+    out->shard_ = reshaped;
+    return Array(out);
 }
 Array Array::ravel() const { return reshape({-1}); }
 
 Array Array::ascontiguousarray() const {
     if (is_buffer() && as<BufferView>(*this)->contiguous()) return *this;
     Array out(shape(), dtype(), preferred_device());
+    out.expression()->shard_ = shard();
     lazy::run_assignment(out, OPERATOR_T_EQL, *this);
     return out;
 }

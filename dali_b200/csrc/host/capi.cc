@@ -324,6 +324,22 @@ int dali_lazy_stats(int64_t counts[3]) {
     counts[2] = lazy::stats().temporaries;
     return DALIB200_OK;
 }
+int dali_array_set_shard(dali_array_t a, int axis, int64_t lo, int64_t total) {
+    return guard([&]() { a->a.set_shard(axis, lo, total); });
+}
+int dali_array_get_shard(dali_array_t a, int* axis, int64_t* lo, int64_t* total) {
+    return guard([&]() {
+        const Shard s = a->a.shard();
+        *axis = s.axis; *lo = s.lo; *total = s.total;
+    });
+}
+int dali_array_scatter_rows(const void* data, const int64_t* global_shape, int ndim, int dtype, dali_array_t* out) {
+    return guard([&]() { *out = wrap(Array::scatter_rows(data, to_shape(global_shape, ndim), to_dtype(dtype))); });
+}
+size_t dali_lazy_collectives(int64_t* count, char* buffer, size_t capacity) {
+    if (count) *count = lazy::stats().collectives;
+    return copy_out(lazy::stats().last_collective, buffer, capacity);
+}
 size_t dali_lazy_last_ir(char* buffer, size_t capacity) { return copy_out(lazy::stats().last_ir, buffer, capacity); }
 size_t dali_lazy_last_variant(char* buffer, size_t capacity) { return copy_out(lazy::stats().last_variant, buffer, capacity); }
 

@@ -29,9 +29,9 @@ class Expression {
     std::vector<int> shape_;
     DType dtype_;
     std::vector<Array> arguments_;
+    Shard shard_;          // which part of a logical array spread over the ranks this value is (shard.cc)
 
-    Expression(NodeKind kind, const std::vector<int>& shape, DType dtype, const std::vector<Array>& arguments)
-        : kind_(kind), shape_(shape), dtype_(dtype), arguments_(arguments) {}
+    Expression(NodeKind kind, const std::vector<int>& shape, DType dtype, const std::vector<Array>& arguments);
     virtual ~Expression() {}
     int ndim() const { return (int)shape_.size(); }
     int64_t numel() const {
@@ -102,6 +102,10 @@ struct Reduce : public Expression {
     std::string reducer_;   // sum | prod | max | min
     int nreduce_;
     bool arg_;
+    // the folded dims include the sharded one: the local result is a partial one and the ranks' partials are combined
+    // (all_reduce; for arg_ the (value, index) pairs, xrank_offset_ being what makes a local flat index a global one)
+    bool xrank_ = false;
+    int64_t xrank_offset_ = 0;
     Reduce(const std::string& reducer, const Array& a, int nreduce, bool arg, DType dtype);
     std::string name() const override { return (arg_ ? "arg" : "") + reducer_; }
 };
@@ -110,8 +114,7 @@ struct Reduce : public Expression {
 struct ViewDim { int src; int64_t off; int64_t step; };
 struct View : public Expression {
     std::vector<ViewDim> dims_;    // one per dim of the argument
-    View(const Array& a, const std::vector<int>& shape, const std::vector<ViewDim>& dims)
-        : Expression(N_VIEW, shape, a.dtype(), {a}), dims_(dims) {}
+    View(const Array& a, const std::vector<int>& shape, const std::vector<ViewDim>& dims);
     std::string name() const override { return "View"; }
 };
 
@@ -127,6 +130,9 @@ struct GatherFromRows : public Expression {
 };
 
 struct MatMul : public Expression {
+    // the contracted dim is the sharded one (left cut along its columns, right along its rows): the local product is
+    // a partial sum and the ranks' partial products are added (the "GEMM reduce")
+    bool partial_ = false;
     MatMul(const Array& left, const Array& right);
     std::string name() const override { return "MatMul"; }
 };
@@ -134,8 +140,7 @@ struct MatMul : public Expression {
 // dest <op>= value; dest is a buffer view or a Gather / GatherFromRows of one (scatter).
 struct Assignment : public Expression {
     OPERATOR_T operator_t_;
-    Assignment(const Array& dest, OPERATOR_T op, const Array& value)
-        : Expression(N_ASSIGN, dest.shape(), dest.dtype(), {dest, value}), operator_t_(op) {}
+    Assignment(const Array& dest, OPERATOR_T op, const Array& value);
     std::string name() const override { return "Assignment"; }
 };
 
@@ -157,7 +162,7 @@ void eval_together(const std::vector<Array>& arrays);
 // Number of kernels / GEMMs launched by this thread's evaluations so far, and the
 // description of the last fused kernel (for tests, in the spirit of the scope
 // counting in dali/array/tests/dot_tests.cpp:17-35).
-struct Stats { long long kernels = 0, gemms = 0, temporaries = 0; std::string last_ir, last_variant; };
+struct Stats { long long kernels = 0, gemms = 0, temporaries = 0, collectives = 0; std::string last_ir, last_variant, last_collective; };
 Stats& stats();
 // Dry run (per thread): expressions are lowered, registered and compiled through NVRTC,
 // but nothing is allocated, copied or launched and results are undefined.  For
@@ -167,6 +172,13 @@ bool dry_run();
 void ensure_backend();    // dalib200_init once; throws std::runtime_error without a GPU
 int device_index(const memory::Device& d);
 void check(int status, const char* what);
+// ---- sharding rules (shard.cc)
+Shard shard_of_same_rank(const std::vector<Array>& arguments, int ndim, const std::string& what);
+Shard shard_through_view(const Shard& s, const std::vector<int>& arg_shape, const std::vector<ViewDim>& dims,
+                         const std::vector<int>& out_shape);
+Shard shard_through_reshape(const Shard& s, const std::vector<int>& from, const std::vector<int>& to);
+// number of elements of the logical array `a` is a part of
+int64_t global_numel(const Array& a);
 }  // namespace lazy
 
 #define DALI_ASSERT(cond, msg)                                                   \

@@ -57,7 +57,53 @@ int device_index(const memory::Device& d) {
     return d.number();
 }
 
+}  // namespace lazy
+
+namespace dalib { const void* comm_peer_table(int device); }
+
+namespace lazy {
 namespace {
+
+// The node whose cross-rank combine the caller appends itself (a sharded reduction or a product over the sharded
+// dimension at the root of an assignment): it is lowered like a local one.
+thread_local const Expression* tl_local_only = nullptr;
+
+bool needs_combine(const Expression* e) {
+    if (!e || e == tl_local_only) return false;
+    if (e->kind_ == N_REDUCE) return static_cast<const Reduce*>(e)->xrank_;
+    if (e->kind_ == N_MATMUL) return static_cast<const MatMul*>(e)->partial_;
+    return false;
+}
+
+bool contains_reduce(const Array& a, int depth = 0) {
+    if (a.is_stateless() || depth > 64) return false;
+    const Expression* e = a.expression().get();
+    if (e->kind_ == N_REDUCE) return true;
+    if (e->kind_ == N_BUFFER || e->kind_ == N_SCALAR || e->kind_ == N_IOTA) return false;
+    for (const Array& arg : e->arguments_) if (contains_reduce(arg, depth + 1)) return true;
+    return false;
+}
+
+// Can the partial results of this sharded reduction meet INSIDE the kernel that computes them?  Yes for an
+// all-axis reduction of purely elementwise work when the ranks' exchange blocks are mapped into one another
+// (transport "nccl+peer", or a world of one): the kernel's last CTA stores its partial into every rank's block,
+// waits -- bounded -- for theirs and folds them in rank order.  Otherwise the local kernel is followed by
+// dalib200_allreduce on its result.
+bool xrank_fusable(const Reduce* r, const memory::Device& device) {
+    if (r->nreduce_ != r->arguments_[0].ndim() || contains_reduce(r->arguments_[0])) return false;
+    const char* off = std::getenv("DALI_B200_XRANK_FUSE");
+    if (off && off[0] == '0') return false;
+    if (tl_dry_run) { const char* e = std::getenv("DALI_B200_DRYRUN_PEER"); return e && e[0] == '1'; }
+    return device.is_gpu() && dalib::comm_peer_table(device.number()) != nullptr;
+}
+
+const char* reducer_name_of(int op) { return op == DALIB200_OP_SUM ? "sum" : op == DALIB200_OP_PROD ? "prod" : op == DALIB200_OP_MAX ? "max" : "min"; }
+int reducer_op(const std::string& r) { return r == "sum" ? DALIB200_OP_SUM : r == "prod" ? DALIB200_OP_PROD : r == "max" ? DALIB200_OP_MAX : DALIB200_OP_MIN; }
+
+void note_collective(const std::string& what) {
+    ++tl_stats.collectives;
+    tl_stats.last_collective = what;
+}
 
 const char* ir_dtype(DType d) { return d == DTYPE_FLOAT ? "f32" : (d == DTYPE_DOUBLE ? "f64" : "i32"); }
 const char* ir_assign(OPERATOR_T op) {
@@ -281,9 +327,24 @@ struct Lowerer {
                     id = visit(materialize(a), m);
                     break;
                 }
+                // a reduction over the sharded dimension: the ranks' partial results meet inside this kernel where
+                // that is possible (see xrank_fusable), else it is evaluated on its own and combined after its kernel
+                const bool combine = needs_combine(r);
+                if (combine && !xrank_fusable(r, device)) {
+                    id = visit(materialize(a), m);
+                    break;
+                }
                 int v = visit(r->arguments_[0], identity_map(rank));
-                if (r->arg_) id = new_value(DTYPE_INT32, false, "argred " + r->reducer_ + " v" + std::to_string(v));
-                else id = new_value(r->dtype_, false, "red " + r->reducer_ + " v" + std::to_string(v));
+                std::string x = combine ? " xrank" : "";
+                if (combine && r->arg_) {
+                    // the local position becomes a position in the logical array before the pairs are exchanged
+                    const int slot = (int)scalars.size();
+                    scalars.push_back(std::make_pair(DTYPE_INT32, (double)r->xrank_offset_));
+                    x += " v" + std::to_string(new_value(DTYPE_INT32, false, "sc " + std::to_string(slot)));
+                }
+                if (combine) note_collective(std::string("in-kernel ") + (r->arg_ ? "arg" : "") + r->reducer_);
+                if (r->arg_) id = new_value(DTYPE_INT32, false, "argred " + r->reducer_ + " v" + std::to_string(v) + x);
+                else id = new_value(r->dtype_, false, "red " + r->reducer_ + " v" + std::to_string(v) + x);
                 break;
             }
             case N_GATHER:
@@ -555,6 +616,16 @@ void launch_pending(const std::vector<PendingSplit>& pending, int dev) {
     }
 }
 
+// a product (or one of the two of a sum) whose partial results still have to be added over the ranks: it cannot be
+// the accumulator of a fused epilogue (the epilogue would run on a partial sum)
+bool pending_partial(const Expression* acc) {
+    if (!acc) return false;
+    if (acc->kind_ == N_MATMUL) return needs_combine(acc);
+    for (const Array& arg : acc->arguments_)
+        if (!arg.is_stateless() && needs_combine(arg.expression().get())) return true;
+    return false;
+}
+
 // first reduction reachable from `a` through elementwise nodes and views
 struct FoundReduce { const Reduce* node = nullptr; bool through_view = false; };
 void find_reduce(const Array& a, bool through_view, FoundReduce* out) {
@@ -823,7 +894,7 @@ bool reads_rows_contiguously(const Array& a, int depth = 0) {
 bool few_long_rows(const Reduce* r) {
     const Array& arg = r->arguments_[0];
     const int lead = arg.ndim() - r->nreduce_;
-    if (lead < 1 || !reads_rows_contiguously(arg)) return false;
+    if (lead < 1 || r->xrank_ || !reads_rows_contiguously(arg)) return false;    // (a sharded reduction is combined once, as a whole)
     int64_t rows = 1, cols = 1;
     for (int d = 0; d < arg.ndim(); ++d) (d < lead ? rows : cols) *= arg.shape()[d];
     return rows >= 1 && ((rows <= 8 && cols >= (1 << 18)) || (rows <= 32 && cols >= (1 << 22)));
@@ -913,6 +984,77 @@ void evaluate_shared_values(const Array& value) {
     evaluate_shared(value, depth_of, 1);
 }
 
+namespace {
+// dest (op)= value, where value is a reduction over the sharded dimension or a product that contracts it.
+void run_with_combine(const Array& dest, OPERATOR_T op, const Array& value) {
+    Expression* e = value.expression().get();
+    const bool direct = op == OPERATOR_T_EQL && dest.is_buffer() && as<BufferView>(dest)->contiguous();
+    if (!direct) {
+        Array tmp(value.shape(), value.dtype(), dest.preferred_device());
+        run_with_combine(tmp, OPERATOR_T_EQL, value);
+        ++tl_stats.temporaries;
+        run_assignment(dest, op, tmp);
+        return;
+    }
+    const memory::Device device = dest.preferred_device();
+    BufferView* db = as<BufferView>(dest);
+    const int64_t n = db->numel();
+    struct Restore { const Expression* prev; ~Restore() { tl_local_only = prev; } } restore{tl_local_only};
+    tl_local_only = e;
+    if (e->kind_ == N_MATMUL) {
+        run_assignment(dest, OPERATOR_T_EQL, value);                    // the local product
+        note_collective("allreduce sum " + std::to_string(n) + " " + ir_dtype(dest.dtype()) + " (product over the sharded dimension)");
+        if (tl_dry_run || n == 0) return;
+        const int dev = device_index(device);
+        char* p = (char*)db->memory_->data(device, memory::AM_MUTABLE) + db->offset_ * size_of_dtype(dest.dtype());
+        check(dalib200_allreduce(dev, nullptr, p, n, (int)dest.dtype(), DALIB200_OP_SUM), "dalib200_allreduce");
+        return;
+    }
+    Reduce* r = static_cast<Reduce*>(e);
+    const int opcode = reducer_op(r->reducer_);
+    if (!r->arg_) {
+        run_assignment(dest, OPERATOR_T_EQL, value);                    // the rank's partial results
+        note_collective("allreduce " + r->reducer_ + " " + std::to_string(n) + " " + ir_dtype(dest.dtype()));
+        if (tl_dry_run || n == 0) return;
+        const int dev = device_index(device);
+        char* p = (char*)db->memory_->data(device, memory::AM_MUTABLE) + db->offset_ * size_of_dtype(dest.dtype());
+        check(dalib200_allreduce(dev, nullptr, p, n, (int)dest.dtype(), opcode), "dalib200_allreduce");
+        return;
+    }
+    // argmax / argmin: ONE local kernel yields the extreme value and its position in the logical array (local
+    // position + the shard's offset); the ranks' (value, position) pairs are then combined, lowest position among equals
+    const Array& arg = r->arguments_[0];
+    std::vector<int64_t> space;
+    for (int d : arg.shape()) space.push_back(d);
+    const int rank = (int)space.size();
+    Lowerer L(space, r->nreduce_, device);
+    const int v = L.visit(arg, identity_map(rank));
+    const DType vt = L.types[v];
+    const int best = L.new_value(vt, false, "red " + r->reducer_ + " v" + std::to_string(v));
+    const int pos = L.new_value(DTYPE_INT32, false, "argred " + r->reducer_ + " v" + std::to_string(v));
+    const int slot = (int)L.scalars.size();
+    L.scalars.push_back(std::make_pair(DTYPE_INT32, (double)r->xrank_offset_));
+    const int off = L.new_value(DTYPE_INT32, false, "sc " + std::to_string(slot));
+    const int global = L.new_value(DTYPE_INT32, false, "op add v" + std::to_string(pos) + " v" + std::to_string(off));
+    Array values(dest.shape(), vt, device);
+    const IndexMap out_map = identity_map(rank - r->nreduce_);
+    const int leaf_v = L.leaf_for(as<BufferView>(values), out_map, true, false, 0, 0, 0);
+    const int leaf_i = L.leaf_for(db, out_map, true, false, 0, 0, 0);
+    L.keep_alive.push_back(values);
+    L.keep_alive.push_back(dest);
+    L.body.push_back("st " + std::to_string(leaf_v) + " assign v" + std::to_string(best));
+    L.body.push_back("st " + std::to_string(leaf_i) + " assign v" + std::to_string(global));
+    L.launch();
+    ++tl_stats.temporaries;
+    note_collective("arg_allreduce " + r->reducer_ + " " + std::to_string(n) + " " + ir_dtype(vt));
+    if (tl_dry_run || n == 0) return;
+    const int dev = device_index(device);
+    void* pv = as<BufferView>(values)->memory_->data(device, memory::AM_MUTABLE);
+    int32_t* pi = (int32_t*)db->memory_->data(device, memory::AM_MUTABLE) + db->offset_;
+    check(dalib200_arg_allreduce(dev, nullptr, pv, pi, n, (int)vt, opcode), "dalib200_arg_allreduce");
+}
+}  // namespace
+
 void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) {
     DALI_ASSERT(!dest_in.is_stateless() && !value_in.is_stateless(), "assignment with a stateless Array");
     DALI_ASSERT(op != OPERATOR_T_LSE, "internal: <<= must be rewritten before it runs");
@@ -922,6 +1064,15 @@ void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) 
     if (value.is_assignment()) value.eval(false);
     if (dest.expression()->kind_ == N_VIEW) dest = writable_view(dest);
     if (!tl_dry_run) prefetch_inputs(value, dest.preferred_device());
+
+    // ---- the root needs the other ranks: a reduction over the sharded dimension that cannot finish inside its own
+    // kernel, or a product that contracts the sharded dimension.  The local part is computed into a contiguous
+    // buffer, the parts are combined there (every rank ends up with the same bits), then the operator is applied.
+    if (needs_combine(value.expression().get()) &&
+        !(value.expression()->kind_ == N_REDUCE && xrank_fusable(static_cast<Reduce*>(value.expression().get()), dest.preferred_device()))) {
+        run_with_combine(dest, op, value);
+        return;
+    }
 
     // ---- peel pure re-indexing views off the root: dest = view(x)  ->  inverse_view(dest) = x
     // (x keeps its own iteration space, which its reductions / products need).  A tree of nothing but elementwise
@@ -965,7 +1116,7 @@ void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) 
         const Expression* acc = nullptr;
         find_matmul_sum(value, &acc);
         if (!acc) find_matmul(value, &acc);
-        if (acc && acc->dtype_ == DTYPE_FLOAT && try_fused_gemm(dest, op, value, acc)) return;
+        if (acc && acc->dtype_ == DTYPE_FLOAT && !pending_partial(acc) && try_fused_gemm(dest, op, value, acc)) return;
     }
 
     // ---- reductions over few, very long rows: one all-axis reduction per row (see few_long_rows)
@@ -1124,7 +1275,7 @@ void find_acc_through_views(const Array& a, const Expression** out) {
 bool try_sliced_gemm(const std::vector<const Array*>& roots) {
     const Expression* acc = nullptr;
     for (const Array* r : roots) find_acc_through_views(*r, &acc);
-    if (!acc || acc->dtype_ != DTYPE_FLOAT || roots[0]->ndim() != 2) return false;
+    if (!acc || acc->dtype_ != DTYPE_FLOAT || roots[0]->ndim() != 2 || pending_partial(acc)) return false;
     GemmOperands g;
     if (!gemm_operands(acc, &g)) return false;
     const int64_t m = g.m, n = roots[0]->shape()[1];

@@ -260,12 +260,12 @@ Array min(const Array& x, const std::vector<int>& axes, bool k) { return axis_re
 Array mean(const Array& x) {
     Array s = all_reduce(x, "sum");
     if (s.dtype() == DTYPE_INT32) s = astype(s, DTYPE_DOUBLE);
-    return op::eltdiv(s, Array((int)x.numel()));
+    return op::eltdiv(s, Array((int)lazy::global_numel(x)));     // (of the logical array when x is one rank's shard)
 }
 Array mean(const Array& x, const std::vector<int>& axes, bool k) {
     Array s = axis_reduce(x, "sum", axes, k);
     if (s.dtype() == DTYPE_INT32) s = astype(s, DTYPE_DOUBLE);
-    return op::eltdiv(s, Array((int)(x.numel() / std::max<int64_t>(1, s.numel()))));
+    return op::eltdiv(s, Array((int)(lazy::global_numel(x) / std::max<int64_t>(1, lazy::global_numel(s)))));
 }
 Array L2_norm(const Array& x) {
     Array s = all_reduce(op::square(x), "sum");

@@ -274,7 +274,21 @@ bool parse_program(const std::string& text, Program* out, std::string* err) {
         } else if (k == "red" || k == "argred") {
             bool a = k == "argred";
             int v;
-            if (t.size() != 5 || !parse_value_ref(t[4], &v) || !value_ok(v)) return fail("malformed reduction");
+            if (t.size() < 5 || t.size() > (a ? 7u : 6u) || !parse_value_ref(t[4], &v) || !value_ok(v)) return fail("malformed reduction");
+            if (t.size() > 5) {
+                // 'xrank': the partial results of the ranks (dalib200_comm_init_rank) meet inside the kernel
+                if (t[5] != "xrank") return fail("expected 'xrank' after the reduced value");
+                if (p.nreduce != p.rank) return fail("a cross-rank reduction folds every dim of the space");
+                s.xrank = true;
+                p.has_xrank = true;
+                if (t.size() == 7) {
+                    int off;
+                    if (!parse_value_ref(t[6], &off) || !value_ok(off)) return fail("bad index offset");
+                    const Stmt& os = p.stmts[p.value_stmt[off]];
+                    if (os.dtype != I32 || (os.kind != S_SC && os.kind != S_CONST)) return fail("the index offset is an i32 scalar or constant");
+                    s.xrank_offset = off;
+                }
+            }
             s.name = t[3];
             if (a) {
                 if (s.name != "max" && s.name != "min") return fail("argred takes max|min");

@@ -21,8 +21,12 @@
 //                                           epilogue programs run by dalib200_gemm_fused
 //   v<k> <dtype> op <functor> v<a> [v<b>]   functor names as dali/array/functor.h
 //   v<k> <dtype> cast v<a>                  static_cast (functor::cast)
-//   v<k> <dtype> red <sum|prod|max|min> v<a>
-//   v<k> i32     argred <max|min> v<a>      first occurrence wins
+//   v<k> <dtype> red <sum|prod|max|min> v<a> [xrank]
+//   v<k> i32     argred <max|min> v<a> [xrank [v<o>]]   first occurrence wins
+//                                           xrank (all-axis programs only): this rank's result is a partial one; the
+//                                           kernel exchanges the partials of all ranks through peer memory and every
+//                                           rank continues with the combined value.  v<o>: i32 scalar added to the
+//                                           local position first, so that positions are those of the logical array
 //   st <arg> <assign|add|sub|mul|div> v<k>
 //   stx <arg> <assign|add|sub|mul|div> v<i> v<k>   scatter through index v<i>
 //   end
@@ -66,6 +70,8 @@ struct Stmt {
     int arg = -1;                // arg or scalar index
     std::string literal;         // const
     AssignOp aop = A_ASSIGN;
+    bool xrank = false;          // red / argred: combined over the ranks inside the kernel
+    int xrank_offset = -1;       // argred xrank: value number of the i32 scalar added to the local position, or -1
     // derived by analyse():
     bool elem = false;           // element level?
     int stage = 0;               // number of reductions on the longest path below
@@ -85,6 +91,7 @@ struct Program {
     bool has_acc = false;          // reads the GEMM accumulator: an epilogue program
     int acc_slices = 1;            // 'acc q': the space is [m, n] and slice q is the product's columns q*n .. q*n + n - 1
     bool has_bf16 = false;
+    bool has_xrank = false;        // some reduction is combined over the ranks inside the kernel
     std::string text;              // canonical source text (for collision checks)
 };
 

@@ -195,6 +195,8 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
     }
     bool all_ok = p.nreduce == p.rank && p.nreduce > 0 && p.max_stage <= 1 && !elem_stores && p.n_reductions > 0;
 
+    if (p.has_xrank && !all_ok) { *err = "launch: reductions across ranks run in the all-axis skeleton only (one level of reductions, no element stores)"; return false; }
+    v.xrank = p.has_xrank;
     if (p.nreduce == 0) v.kind = K_MAP;
     else if (all_ok) v.kind = K_ALL;
     else if (col_ok) v.kind = K_COL;

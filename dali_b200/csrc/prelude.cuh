@@ -115,11 +115,14 @@ DEV int f_safe_entropy_log(int a) { return (int)f_safe_entropy_log((double)a); }
 
 // 1 / (1 + exp(-a)): the denominator is in [1, inf], where the approximate
 // reciprocal is within 1 ulp and needs no slow path.
-DEV float f_sigmoid(float a) { return rcp_ge1(1.0f + fast_ex2(fminf(a * -1.4426950408889634f, 126.0f))); }
+// (the exponent is clamped so that 1 + 2^t stays finite; the clamp is a comparison, not fminf, so that a NaN operand
+// stays NaN as in the reference's 1 / (1 + exp(-a)): fminf would return the other operand)
+DEV float sigmoid_exponent(float t) { return t > 126.0f ? 126.0f : t; }
+DEV float f_sigmoid(float a) { return rcp_ge1(1.0f + fast_ex2(sigmoid_exponent(a * -1.4426950408889634f))); }
 DEV double f_sigmoid(double a) { return 1.0 / (1.0 + exp(-a)); }
 DEV int f_sigmoid(int a) { return (int)(1.0 / (1.0 + exp((double)-a))); }
 
-DEV float f_steep_sigmoid(float x, float g) { return rcp_ge1(1.0f + fast_ex2(fminf((-g * x) * 1.4426950408889634f, 126.0f))); }
+DEV float f_steep_sigmoid(float x, float g) { return rcp_ge1(1.0f + fast_ex2(sigmoid_exponent((-g * x) * 1.4426950408889634f))); }
 DEV double f_steep_sigmoid(double x, double g) { return 1.0 / (1.0 + exp(-g * x)); }
 DEV int f_steep_sigmoid(int x, int g) { return (int)(1.0 / (1.0 + exp((double)(-g * x)))); }
 

@@ -27,7 +27,12 @@ namespace dalib {
 static const char* kPrelude =
 #include "prelude_embed.inc"
     ;
-static const char* kCodegenVersion = "dali_b200-codegen-4";
+// Hash (made by the build) of the sources that decide the text of a generated kernel and the layout of its parameter
+// block -- code generator, launch planner, IR, GEMM skeleton and its host side, device prelude.  It is part of every
+// cache key: a cubin on disk is only ever loaded by a library built from the same sources as the one that wrote it.
+static const char* kCodegenVersion = "dali_b200-"
+#include "source_hash.inc"
+    ;
 
 // ------------------------------------------------------------------ errors
 static thread_local std::string tl_error;
@@ -381,6 +386,15 @@ static int do_launch(uint64_t hash, int device, void* stream, const int64_t* spa
         if (rc != DALIB200_OK) return rc;
         plan.words[L.w_scratch] = (long long)(uintptr_t)sc.buf;
         plan.words[L.w_counter] = (long long)(uintptr_t)sc.counters;
+    }
+    if (plan.variant.xrank) {
+        const void* table = comm_peer_table(device);
+        if (!table) {
+            set_error("this program combines a reduction across ranks inside the kernel: it needs a communicator whose ranks "
+                      "can address one another's memory (dalib200_comm_init_rank, transport \"nccl+peer\" or \"single\")");
+            return DALIB200_ERR_UNSUPPORTED;
+        }
+        plan.words[L.w_aux0] = (long long)(uintptr_t)table;
     }
     CUDA_OK(cudaSetDevice(s.devices[device].ordinal));
     void* params[] = {plan.words.data()};

@@ -77,6 +77,8 @@ int device_ordinal(int device);            // CUDA ordinal of bound device, -1 i
 // partial results, valid until the next launch on that stream that asks for space.  Returns a dalib200_status.
 int scratch_space(int device, void* stream, size_t bytes, void** out);
 void count_launch();
+// Device address of the peer table of the communicator's rank on `device` (comm.cc), nullptr without one.
+const void* comm_peer_table(int device);
 // One int per device that tensor-core kernels raise when a bounded wait expires.
 int* gemm_error_word(int device);
 // Remembers, per thread, which GEMM kernel served the last call (dalib200_last_gemm_kernel).

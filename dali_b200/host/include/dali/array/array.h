@@ -136,6 +136,21 @@ struct Slice {
     bool contains(int index) const;
 };
 
+// ------------------------------------------------------------------ sharding (not in the reference)
+// How an Array relates to the other ranks of the communicator (one process per GPU, include/dali_b200.h):
+// the local part of a logical array cut along `axis`, holding indices [lo, lo + local extent) of `total`.
+// axis < 0: every rank holds the whole array.  Replaces the reference's per-node device heuristic
+// (dali/array/jit/jit.cpp:367-385): placement is explicit, and ranks exchange data only where a reduction or a
+// product contracts the sharded dimension.
+struct Shard {
+    int axis;
+    int64_t lo, total;
+    Shard() : axis(-1), lo(0), total(0) {}
+    Shard(int axis_, int64_t lo_, int64_t total_) : axis(axis_), lo(lo_), total(total_) {}
+    bool sharded() const { return axis >= 0; }
+    bool operator==(const Shard& o) const { return axis == o.axis && (axis < 0 || (lo == o.lo && total == o.total)); }
+};
+
 class Expression;
 typedef std::shared_ptr<Expression> expression_ptr;
 template <typename Container> struct SlicingInProgress;
@@ -196,6 +211,18 @@ class Array {
     // (what they share is computed once; an LSTM cell's c' and h' become one GEMM launch whose epilogue is the
     // gating), one after the other otherwise.
     static void eval_together(const std::vector<Array>& arrays, bool wait = true);
+    // Not in the reference.  Declares this (evaluated) Array to be the rows [lo, lo + shape()[axis]) of a logical array
+    // of `total` rows along `axis` that is spread over the ranks of the communicator.  Elementwise work, views that
+    // leave the axis whole, reductions over other axes and dot(x, W) with a whole W stay local and keep the mark;
+    // a reduction over the axis (sum / prod / max / min / argmax / argmin, also all-axis) or a product that contracts it
+    // computes the local part and combines the parts of all ranks (dalib200_allreduce), giving every rank the whole
+    // result; argmax / argmin return indices of the logical array.  Indexing or slicing the axis, and gathering
+    // from a sharded source, throw: a rank only holds its own rows.
+    Array& set_shard(int axis, int64_t lo, int64_t total);
+    Shard shard() const;
+    // This rank's rows (dalib200_shard_range of the communicator's world and rank) of a C-contiguous host array of
+    // shape `global_shape`, marked as a shard along axis 0.
+    static Array scatter_rows(const void* host_data, const std::vector<int>& global_shape, DType dtype);
 
     // Optimise, lower and launch whatever this Array lazily stands for; afterwards it is a
     // plain buffer.  wait = true also synchronises the device.

@@ -50,11 +50,14 @@ class IRBuilder:
     def cast(self, dtype, v):
         return self._val(dtype, "cast v%d" % v)
 
-    def red(self, kind, v):
-        return self._val(self.types[v], "red %s v%d" % (kind, v))
+    def red(self, kind, v, xrank=False):
+        """xrank (all-axis programs): the ranks' partial results are combined inside the kernel."""
+        return self._val(self.types[v], "red %s v%d%s" % (kind, v, " xrank" if xrank else ""))
 
-    def argred(self, kind, v):
-        return self._val("i32", "argred %s v%d" % (kind, v))
+    def argred(self, kind, v, xrank=False, offset=None):
+        """xrank: as red; offset = an i32 scalar value added to the local position before the pairs are exchanged."""
+        tail = (" xrank" + (" v%d" % offset if offset is not None else "")) if xrank else ""
+        return self._val("i32", "argred %s v%d%s" % (kind, v, tail))
 
     def st(self, arg, v, op="assign"):
         self.body.append("st %d %s v%d" % (arg, op, v))
@@ -82,24 +85,40 @@ def softmax_ir():
     return b.text()
 
 
-def chain_sum_ir():
-    """sum(sigmoid(x*w+b) * exp(-x*x)) over all elements: args (out scalar, x), scalars (w, b)."""
+def chain_sum_ir(xrank=False):
+    """sum(sigmoid(x*w+b) * exp(-x*x)) over all elements: args (out scalar, x), scalars (w, b).  xrank: x is one
+    rank's shard and the partial sums of the ranks meet inside the kernel."""
     b = IRBuilder(1, 1)
     out, x = b.arg("f32", "R"), b.arg("f32")
     w, bb = b.scalar("f32"), b.scalar("f32")
     v = b.ld(x)
     sig = b.op("sigmoid", b.op("add", b.op("eltmul", v, b.sc(w)), b.sc(bb)))
     ex = b.op("exp", b.op("eltmul", b.op("negate", v), v))
-    b.st(out, b.red("sum", b.op("eltmul", sig, ex)))
+    b.st(out, b.red("sum", b.op("eltmul", sig, ex), xrank))
     return b.text()
 
 
-def reduce_ir(kind, dtype="f32", rank=2, nreduce=1, arg=False):
-    """out = reduce(x) over the innermost `nreduce` dims: args (out, x)."""
+def reduce_ir(kind, dtype="f32", rank=2, nreduce=1, arg=False, xrank=False):
+    """out = reduce(x) over the innermost `nreduce` dims: args (out, x).  xrank (nreduce == rank): combined over the
+    ranks inside the kernel; an arg-reduction then takes one i32 scalar, the offset of the rank's shard."""
     b = IRBuilder(rank, nreduce)
     out, x = b.arg("i32" if arg else dtype, "R"), b.arg(dtype)
     v = b.ld(x)
-    b.st(out, b.argred(kind, v) if arg else b.red(kind, v))
+    if arg and xrank:
+        b.st(out, b.argred(kind, v, True, b.sc(b.scalar("i32"))))
+    else:
+        b.st(out, b.argred(kind, v) if arg else b.red(kind, v, xrank))
+    return b.text()
+
+
+def arg_pair_ir(kind, dtype="f32", rank=2, nreduce=1):
+    """(extreme value, its position + offset) over the innermost `nreduce` dims in one kernel: args (values, positions,
+    x), scalar (offset i32) -- what a sharded argmax / argmin computes locally before dalib200_arg_allreduce."""
+    b = IRBuilder(rank, nreduce)
+    vals, pos, x = b.arg(dtype, "R"), b.arg("i32", "R"), b.arg(dtype)
+    v = b.ld(x)
+    b.st(vals, b.red(kind, v))
+    b.st(pos, b.op("add", b.argred(kind, v), b.sc(b.scalar("i32"))))
     return b.text()
 
 

@@ -275,6 +275,60 @@ int dalib200_scan(int device, void* stream, int dtype, int op, int inclusive,
 #define DALIB200_NOALLOC_MAX_ELEMENTS ((int64_t)1 << 31)
 int dalib200_sum_f32_noalloc(int device, void* stream, const float* x, int64_t n, float* out);
 
+/* ---- ranks and collectives ------------------------------------------------------
+ * One process per GPU, every process holding one shard of the batch (row) dimension.
+ * The reference has a slot per GPU in every buffer
+ * (dali/array/memory/synchronized_memory.h:46-49) but places each node on one device
+ * by a heuristic (dali/array/jit/jit.cpp:367-385) and cannot move data between GPUs
+ * (dali/array/memory/memory_ops.cu.cpp:120-125 asserts); these entry points are what
+ * replaces that heuristic: shards meet only where a reduction crosses the sharded
+ * dimension, in an all-reduce of the partial results.
+ *
+ * Set-up: rank 0 obtains an id with dalib200_comm_unique_id and hands its bytes to the
+ * other ranks by whatever means the launcher offers (torch.distributed, MPI, a file);
+ * every rank then calls dalib200_comm_init_rank (collective, blocking).  Payloads of up
+ * to 256 KiB per rank then travel as plain stores into peer memory over NVLink with a
+ * bounded wait (transport "nccl+peer"; a wait that expires after DALI_B200_PEER_WAIT_MS,
+ * default 10000, raises the word read by dalib200_comm_error_flag), larger ones and
+ * everything else through NCCL.  dalib200_comm_init_host instead runs every collective
+ * through caller-supplied functions on HOST buffers (device buffers are staged through
+ * page-locked memory): any fabric, and what the CPU tests use.  world == 1 needs no id. */
+#define DALIB200_COMM_ID_BYTES 128
+enum dalib200_reduce_op { DALIB200_OP_SUM = 0, DALIB200_OP_PROD = 1, DALIB200_OP_MAX = 2, DALIB200_OP_MIN = 3 };
+typedef int (*dalib200_host_allreduce_fn)(void* ctx, void* buf, int64_t n, int dtype, int op);       /* in place; 0 = ok */
+typedef int (*dalib200_host_allgather_fn)(void* ctx, const void* send, void* recv, int64_t bytes);   /* recv: world * bytes */
+int dalib200_comm_unique_id(void* id /* DALIB200_COMM_ID_BYTES */);
+int dalib200_comm_init_rank(int device, int world, int rank, const void* id);
+int dalib200_comm_init_host(int world, int rank, dalib200_host_allreduce_fn allreduce,
+                            dalib200_host_allgather_fn allgather, void* ctx);
+int dalib200_comm_destroy(void);
+int dalib200_comm_world(void);                       /* 0 without a communicator */
+int dalib200_comm_rank(void);                        /* -1 without a communicator */
+/* "none", "single", "nccl+peer", "nccl (<why the peer mapping is off>)", "host" */
+size_t dalib200_comm_transport(char* buffer, size_t capacity);
+/* Synchronises the communicator's device and reads the word a peer-exchange kernel raises
+ * when a rank did not arrive in time (0 = none); a non-zero word is cleared by the read. */
+int dalib200_comm_error_flag(int* flag);
+/* [lo, hi) of rank's contiguous share of n rows; the first n % world ranks hold one more. */
+int dalib200_shard_range(int64_t n, int rank, int world, int64_t* lo, int64_t* hi);
+/* buf[i] = op over the ranks of buf[i], in place, the same bits on every rank (contributions
+ * are folded in rank order).  dtype f32 / f64 / i32.  Asynchronous on `stream`; device < 0
+ * with the host transport: `buf` is host memory.  Every rank must call the collectives in
+ * the same order. */
+int dalib200_allreduce(int device, void* stream, void* buf, int64_t n, int dtype, int op);
+/* The combine of a sharded argmax / argmin: per element the extreme of `values` over the
+ * ranks (op max or min) and, in `indices`, the index that came with it; among equal values
+ * the lowest index wins, as in the reference's strict-improvement loop
+ * (dali/array/jit/all_reduce_kernel_utils.cpp:123-140).  Indices are global (each rank has
+ * added its shard's offset).  In place. */
+int dalib200_arg_allreduce(int device, void* stream, void* values, int32_t* indices, int64_t n, int dtype, int op);
+/* For tests on a box with fewer GPUs than ranks: runs the peer-exchange protocol of the two
+ * calls above `repeats` times with `world` (<= 8) virtual ranks inside ONE cooperative kernel
+ * on one device.  bufs / indices: host arrays of `world` device pointers (indices may be NULL
+ * when arg == 0).  *error_flag receives whether a wait expired. */
+int dalib200_peer_emulate(int device, void* stream, int world, int dtype, int op, int arg, void* const* bufs,
+                          int32_t* const* indices, int64_t n, int repeats, int* error_flag);
+
 /* ---- page-locked host memory -------------------------------------------------
  * Host buffers the GPUs reach by DMA (cudaHostAlloc, portable across the bound devices): inputs handed over
  * with dali_array_borrow_host and results read with dali_array_to_host move without a staging copy.  The

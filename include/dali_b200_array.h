@@ -106,6 +106,18 @@ int dali_array_assign(dali_array_t dest, int op, dali_array_t value);
  * newly created Arrays compute.  One process per GPU sets its own index. */
 int dali_set_default_device(int gpu);
 
+/* ---- sharding over the ranks of the communicator (include/dali_b200.h, "ranks and collectives").  Not in the
+ * reference, whose device placement is a per-node heuristic (dali/array/jit/jit.cpp:367-385).
+ * set_shard declares an evaluated array to be rows [lo, lo + extent) of a logical array of `total` rows along
+ * `axis` (axis < 0 removes the mark); the mark travels with everything derived from the array, and a reduction over
+ * that axis or a product that contracts it combines the ranks' partial results.  scatter_rows keeps this rank's rows
+ * (dalib200_shard_range) of a C-contiguous host array and marks them. */
+int dali_array_set_shard(dali_array_t a, int axis, int64_t lo, int64_t total);
+int dali_array_get_shard(dali_array_t a, int* axis, int64_t* lo, int64_t* total);
+int dali_array_scatter_rows(const void* data, const int64_t* global_shape, int ndim, int dtype, dali_array_t* out);
+/* number of cross-rank combines this thread's evaluations have issued and a description of the last one */
+size_t dali_lazy_collectives(int64_t* count, char* buffer, size_t capacity);
+
 /* ---- introspection of the lowering, for tests (kernels, gemms, temporaries launched by
  * this thread so far) and the IR / kernel variant of the last fused kernel ----------- */
 int dali_lazy_stats(int64_t counts[3]);
