@@ -1008,15 +1008,16 @@ def measure(wl, torch, world, steps, warmup, lib, local=0, min_blocks=5, clock_s
         for _ in range(2):
             stepper.replay()
         torch.cuda.synchronize()
-        # Untimed spin-up on top of the `warmup` steps: a step of tens of microseconds leaves a GPU that has just come
-        # out of idle no time to reach its clocks.  ~150 ms of the same replays, the same number on every rank (a step
-        # may hold a collective).  Only for such short steps: a block of milliseconds has warmed the GPU up by itself,
-        # and more untimed work would move a power-capped GEMM from its burst clocks to its sustained ones.
+        # Untimed spin-up on top of the `warmup` steps, ~150 ms of the same replays and the same number on every rank (a
+        # step may hold a collective): a GPU that has just come out of idle needs that long to settle at the clocks it
+        # then holds, and a strong-scaled step is 1 / N as long at N GPUs, so a fixed number of warm-up steps would
+        # time every N in a different power state.  Not for the tensor-bound GEMM, whose roofline is the burst rate of
+        # a kernel timed alone: more untimed work would move it to its sustained clocks before the block is timed.
         est = torch.tensor([(time.perf_counter() - t_spin) / 2], dtype=torch.float64, device="cuda")
         if world > 1:
             torch.distributed.all_reduce(est, op=torch.distributed.ReduceOp.MAX)
         est = max(float(est.item()), 1e-5)
-        if est < 5e-3:
+        if wl.name != "gemm":
             for _ in range(min(2000, int(0.15 / est) + 1)):
                 stepper.replay()
     barrier()

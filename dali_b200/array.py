@@ -412,6 +412,13 @@ class _Op:
     def astype(self, a, dtype):
         return a.astype(dtype)
 
+    def any_isnan(self, a, axes=None, keepdims=False):
+        """op::any_isnan (dali/array/op/reducers.cpp:66-75): max over isnan."""
+        return self.max(self.isnan(a), axes, keepdims)
+
+    def any_isinf(self, a, axes=None, keepdims=False):
+        return self.max(self.isinf(a), axes, keepdims)
+
     def __getattr__(self, name):
         unary = {"identity", "sqrt", "square", "abs", "sigmoid", "dsigmoid", "tanh", "dtanh", "relu", "relu_backward",
                  "eltinv", "exp", "log", "log_or_zero", "sign", "softplus", "softplus_backward", "cube", "rsqrt",
