@@ -452,6 +452,23 @@ def collectives():
     return int(n.value), buf.value.decode()
 
 
+class scope_trace:
+    """with scope_trace() as t: ...; t.names lists the trace scopes left inside the block, in order (Scope / ScopeObserver
+    of dali/utils/scope.h: one per computation, named after the evaluated expression, plus "get_function")."""
+
+    def __enter__(self):
+        _c().c.dali_scope_trace_start()
+        self.names = []
+        return self
+
+    def __exit__(self, *exc):
+        _c().c.dali_scope_trace_stop.restype = ctypes.c_size_t
+        buf = ctypes.create_string_buffer(1 << 20)
+        _c().c.dali_scope_trace_stop(buf, len(buf))
+        self.names = [n for n in buf.value.decode().split("\n") if n]
+        return False
+
+
 def set_dry_run(on):
     """Lower and compile only (no device work, results undefined): inspect fusion without a GPU."""
     _c().c.dali_lazy_set_dry_run(int(bool(on)))

@@ -85,9 +85,8 @@ def build(force=False, verbose=False):
     _embed_source_hash()
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh", ".inc"))]
     headers += [os.path.join(HERE, "..", "include", f) for f in os.listdir(os.path.join(HERE, "..", "include"))]
-    for d in (os.path.join(CSRC, "host"), os.path.join(HERE, "host", "include", "dali", "array")):
-        if os.path.isdir(d):
-            headers += [os.path.join(d, f) for f in os.listdir(d) if f.endswith(".h")]
+    for root, _, files in os.walk(os.path.join(HERE, "host", "include")):
+        headers += [os.path.join(root, f) for f in files if f.endswith(".h")]
     objs = []
     srcs = []
     for root, _, files in os.walk(CSRC):

@@ -14,7 +14,9 @@
 
 #include "../../../include/dali_b200.h"
 #include "dali/array/op.h"
-#include "expression.h"
+#include "dali/array/expression/computation.h"
+#include "dali/array/expression/expression.h"
+#include "dali/array/expression/optimization.h"
 
 // ------------------------------------------------------------------ dtype helpers
 int size_of_dtype(DType dtype) { return dtype == DTYPE_DOUBLE ? 8 : 4; }
@@ -297,30 +299,12 @@ std::vector<int> Array::subshape() const {
 
 void Array::eval(bool wait) const {
     require_state(*this, "eval()");
-    expression_ptr e = expression();
-    if (e->kind_ == N_BUFFER) return;
-    if (e->kind_ == N_ASSIGN) {
-        Assignment* a = static_cast<Assignment*>(e.get());
-        Array dest = a->arguments_[0];
-        lazy::run_assignment(dest, a->operator_t_, a->arguments_[1]);
-        // the node is replaced by its destination: evaluated once, remembered
-        if (dest.is_assignment()) dest.eval(false);
-        if (dest.is_buffer()) set_expression(dest.expression());
-        else {
-            // scatter through a gather: what remains is the (lazy) gather of the updated source
-            set_expression(dest.expression());
-        }
-    } else if (e->kind_ == N_SCALAR) {
-        ScalarValue* s = static_cast<ScalarValue*>(e.get());
-        Array dest(std::vector<int>(), s->dtype_, memory::default_preferred_device);
-        lazy::run_assignment(dest, OPERATOR_T_EQL, *this);
-        set_expression(dest.expression());
-    } else {
-        Array dest(e->shape_, e->dtype_, preferred_device());
-        dest.expression()->shard_ = e->shard_;       // the result is the same part of the logical array as the value
-        lazy::run_assignment(dest, OPERATOR_T_EQL, Array(e));
-        set_expression(dest.expression());
-    }
+    if (expression()->kind_ == N_BUFFER) return;
+    // optimize -> lower -> run (reference: array.cpp:232-245): the value becomes an assignment, the assignment a list
+    // of computations (user-registered implementations first, the fused-kernel lowering otherwise), and every
+    // computation replaces its assignment by the buffer it wrote
+    Array root = canonical(*this);
+    for (const std::shared_ptr<Computation>& step : convert_to_ops(root)) step->run_and_cleanup();
     if (wait && !lazy::dry_run()) {
         memory::Device d = preferred_device();
         if (d.is_gpu()) lazy::check(dalib200_sync(lazy::device_index(d), nullptr), "dalib200_sync");

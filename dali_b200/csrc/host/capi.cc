@@ -3,13 +3,15 @@
 #include <cstring>
 #include <functional>
 #include <map>
+#include <memory>
 
 #include "../../../include/dali_b200.h"
 #include "../../../include/dali_b200_array.h"
 #include "../runtime.h"
 #include "dali/array/op.h"
-#include "expression.h"
+#include "dali/array/expression/expression.h"
 #include "dali/utils/random.h"
+#include "dali/utils/scope.h"
 
 struct dali_array_s { Array a; };
 
@@ -339,6 +341,20 @@ int dali_array_scatter_rows(const void* data, const int64_t* global_shape, int n
 size_t dali_lazy_collectives(int64_t* count, char* buffer, size_t capacity) {
     if (count) *count = lazy::stats().collectives;
     return copy_out(lazy::stats().last_collective, buffer, capacity);
+}
+// names of the trace scopes left since dali_scope_trace_start, one per line
+static std::unique_ptr<ScopeObserver> g_trace_observer;
+static std::string g_trace;
+int dali_scope_trace_start(void) {
+    g_trace.clear();
+    g_trace_observer.reset(new ScopeObserver(nullptr, [](const ScopeObserver::State& state) {
+        if (!state.trace.empty()) g_trace += *state.trace.back() + "\n";
+    }));
+    return DALIB200_OK;
+}
+size_t dali_scope_trace_stop(char* buffer, size_t capacity) {
+    g_trace_observer.reset();
+    return copy_out(g_trace, buffer, capacity);
 }
 size_t dali_lazy_last_ir(char* buffer, size_t capacity) { return copy_out(lazy::stats().last_ir, buffer, capacity); }
 size_t dali_lazy_last_variant(char* buffer, size_t capacity) { return copy_out(lazy::stats().last_variant, buffer, capacity); }

@@ -26,7 +26,8 @@
 #include "../../../include/dali_b200.h"
 #include "../runtime.h"
 #include "dali/array/op.h"
-#include "expression.h"
+#include "dali/array/expression/expression.h"
+#include "dali/utils/scope.h"
 
 namespace lazy {
 
@@ -455,7 +456,10 @@ struct Lowerer {
     void launch() {
         const std::string text = ir_text();
         const uint64_t hash = dalib::fnv1a(text);
-        if (!dalib200_is_loaded(hash)) check(dalib200_compile(hash, text.c_str(), text.size()), "dalib200_compile");
+        {
+            DALI_SCOPE("get_function");        // as the reference's compile-or-load step (dali/array/jit/jit.cpp:1015)
+            if (!dalib200_is_loaded(hash)) check(dalib200_compile(hash, text.c_str(), text.size()), "dalib200_compile");
+        }
         const int n = (int)leaves.size();
         if (tl_dry_run) {
             // lower + compile only: aligned stand-in pointers, nothing touches a device

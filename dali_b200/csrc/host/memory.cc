@@ -7,7 +7,7 @@
 #include <mutex>
 
 #include "../../../include/dali_b200.h"
-#include "expression.h"
+#include "dali/array/expression/expression.h"
 
 namespace memory {
 

@@ -8,7 +8,7 @@
 
 #include "dali/array/op.h"
 #include "dali/utils/random.h"
-#include "expression.h"
+#include "dali/array/expression/expression.h"
 
 static std::string shape_str(const std::vector<int>& s) {
     std::ostringstream o;

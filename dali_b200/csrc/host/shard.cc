@@ -10,7 +10,7 @@
 #include <cstring>
 
 #include "../../../include/dali_b200.h"
-#include "expression.h"
+#include "dali/array/expression/expression.h"
 
 Expression::Expression(NodeKind kind, const std::vector<int>& shape, DType dtype, const std::vector<Array>& arguments)
     : kind_(kind), shape_(shape), dtype_(dtype), arguments_(arguments) {

@@ -12,8 +12,8 @@
 // ExpandDims / BroadcastedReshape / Squeeze / dimshuffle nodes
 // (dali/array/jit/reshape.cpp:11-280) and folds into leaf strides at lowering,
 // so a broadcast never forces a temporary.
-#ifndef DALI_B200_HOST_EXPRESSION_H
-#define DALI_B200_HOST_EXPRESSION_H
+#ifndef DALI_ARRAY_EXPRESSION_EXPRESSION_H
+#define DALI_ARRAY_EXPRESSION_EXPRESSION_H
 
 #include <memory>
 #include <string>

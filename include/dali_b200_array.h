@@ -118,6 +118,14 @@ int dali_array_scatter_rows(const void* data, const int64_t* global_shape, int n
 /* number of cross-rank combines this thread's evaluations have issued and a description of the last one */
 size_t dali_lazy_collectives(int64_t* count, char* buffer, size_t capacity);
 
+/* ---- trace scopes (dali/utils/scope.h:11-57): every computation opens a scope named after the expression it
+ * evaluates (dali/array/expression/computation.cpp:14-21); the compile-or-load step a scope "get_function"
+ * (dali/array/jit/jit.cpp:1015).  start begins recording, stop ends it and returns the names of the scopes that were
+ * left in between, one per line -- what dali/array/tests/dot_tests.cpp:17-35 counts to show that evaluating a product
+ * runs exactly one computation. */
+int dali_scope_trace_start(void);
+size_t dali_scope_trace_stop(char* buffer, size_t capacity);
+
 /* ---- introspection of the lowering, for tests (kernels, gemms, temporaries launched by
  * this thread so far) and the IR / kernel variant of the last fused kernel ----------- */
 int dali_lazy_stats(int64_t counts[3]);

@@ -18,7 +18,11 @@
 #include "dali/array/op/outer.h"
 #include "dali/array/op/scan.h"
 #include "dali/array/op/softmax.h"
+#include "dali/array/expression/computation.h"
+#include "dali/array/expression/expression.h"
+#include "dali/array/expression/optimization.h"
 #include "dali/utils/random.h"
+#include "dali/utils/scope.h"
 
 static int checks = 0, failures = 0;
 #define CHECK(cond)                                                                   \
@@ -271,8 +275,112 @@ static void errors() {
     CHECK_THROWS(op::one_hot(a, 3, 1.0, 0.0));
 }
 
+// dali/array/tests/dot_tests.cpp:10-35: a product of two evaluated operands runs exactly ONE computation, which a
+// ScopeObserver sees as one scope being left; nothing runs before eval() is called
+static void laziness_counted_by_scopes() {
+    Array a = Array::ones({2, 3}, DTYPE_FLOAT);
+    Array b = op::arange(12).reshape({4, 3}).astype(DTYPE_FLOAT);
+    b = b.transpose();
+    b.eval();
+    a.eval();
+    int computations = 0;
+    std::vector<std::string> names;
+    {
+        auto cb = ScopeObserver(NULL, [&](const ScopeObserver::State& state) {
+            computations += 1;
+            names.push_back(*state.trace.back());
+        });
+        Array c = op::dot(a, b);
+        CHECK(computations == 0);            // lazy: building the expression ran nothing
+        c.eval();
+        const float expected[] = {3, 12, 21, 30, 3, 12, 21, 30};
+        for (int i = 0; i < c.number_of_elements(); ++i) CHECK((float)c(i) == expected[i]);
+        CHECK(computations == 1);
+        CHECK(names.size() == 1 && names[0].find("MatMul") == 0);
+        // a fused softmax is one computation too (plus the compile-or-load step it contains)
+        computations = 0;
+        names.clear();
+        Array x = op::arange(10).reshape({2, 5}).astype(DTYPE_FLOAT);
+        x.eval();
+        computations = 0;
+        names.clear();
+        Array s = op::softmax(x, -1);
+        s.eval();
+        int jit = 0;
+        for (const std::string& n : names) jit += n == "get_function";
+        CHECK(computations - jit == 1 && jit == 1);
+    }
+    CHECK(!Scope::has_observers());
+}
+
+// computation.h:20-38: an implementation registered for a node class is asked first and may decline
+struct FillWithSeven : public Computation {
+    using Computation::Computation;
+    void run() override {
+        float* out = (float*)left_data(memory::Device::cpu());
+        for (int i = 0; i < left_.number_of_elements(); ++i) out[i] = 7.0f;
+        (void)argument_data(memory::Device::cpu(), 0);       // the value's first argument, fresh on the host
+    }
+};
+static bool g_claim_products = false;
+static int g_factory_calls = 0;
+static void plug_in_registry() {
+    register_implementation(typeid(MatMul).name(), [](Array dest, OPERATOR_T op, Array x, Array assignment) -> std::shared_ptr<Computation> {
+        ++g_factory_calls;
+        if (!g_claim_products || dest.dtype() != DTYPE_FLOAT) return nullptr;        // decline: the built-in GEMM runs
+        return std::make_shared<FillWithSeven>(dest, op, x, assignment);
+    });
+    Array a = Array::ones({4, 8}, DTYPE_FLOAT), b = Array::ones({8, 4}, DTYPE_FLOAT);
+    Array c = op::dot(a, b);
+    c.eval();
+    CHECK(g_factory_calls == 1);
+    CHECK((float)c[1][2] == 8.0f);
+    g_claim_products = true;
+    Array d = op::dot(a, b);
+    d.eval();
+    CHECK(g_factory_calls == 2);
+    CHECK((float)d[1][2] == 7.0f && (float)d[3][3] == 7.0f);
+    CHECK(d.is_buffer());
+    g_claim_products = false;
+    // the (name, predicate) form: only reductions to a scalar are claimed
+    static int scalar_reductions = 0;
+    register_implementation("count scalar reductions", [](const Array& v) { return as<Reduce>(v) != nullptr && v.ndim() == 0; },
+                            [](Array, OPERATOR_T, Array, Array) -> std::shared_ptr<Computation> { ++scalar_reductions; return nullptr; });
+    Array r = op::sum(a);
+    CHECK((float)r == 32.0f);
+    Array r2 = op::sum(a, {0});
+    r2.eval();
+    CHECK(scalar_reductions == 1);
+}
+
+// optimization.h:8-16: negate(negate(x)) is rewritten to x before anything is lowered
+static void registered_optimization() {
+    static int rewrites = 0;
+    register_optimization(
+        [](const Array& a) {
+            Elementwise* outer = as<Elementwise>(a);
+            if (!outer || outer->functor_ != "negate") return false;
+            Elementwise* inner = as<Elementwise>(outer->arguments_[0]);
+            return inner != nullptr && inner->functor_ == "negate";
+        },
+        [](const Array& a) { ++rewrites; return a.expression()->arguments_[0].expression()->arguments_[0]; }, "double negation");
+    Array x = op::arange(6).reshape({2, 3}).astype(DTYPE_FLOAT);
+    x.eval();
+    Array y = -(-(x * 2.0f));
+    Array z = canonical(y);
+    CHECK(rewrites == 1);
+    CHECK(z.is_assignment());
+    CHECK(right_args(z).size() == 2);                 // eltmul(x, 2): the two negations are gone
+    CHECK(z.expression_name() == "Assignment");
+    y.eval();
+    CHECK((float)y[1][2] == 10.0f);
+}
+
 int main() {
     try {
+        laziness_counted_by_scopes();
+        plug_in_registry();
+        registered_optimization();
         inplace_with_arange();
         eye_init();
         reducers();

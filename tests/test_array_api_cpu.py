@@ -370,3 +370,57 @@ def test_large_shared_lazy_values_are_evaluated_once():
         w.eval()
         sizes.append(len(last_ir().splitlines()))
     assert max(sizes) < 80 and max(sizes[6:]) <= max(sizes[:6])   # bounded, not growing with the step count
+
+
+def test_every_computation_opens_one_trace_scope():
+    """dali/array/tests/dot_tests.cpp:17-35 counts the scopes a ScopeObserver sees to show that a product is one
+    computation; the same count here, through the C binding of the observer (lowering only, nothing is launched)."""
+    from dali_b200.array import scope_trace
+    a, b = Array(np.ones((2, 3), np.float32)), Array(np.ones((3, 4), np.float32))
+    with scope_trace() as t:
+        c = op.dot(a, b)
+        assert t.names == []
+    with scope_trace() as t:
+        c.eval()
+    assert t.names == ["MatMul(Buffer, Buffer)"]
+    x = Array(np.ones((8, 16), np.float32))
+    with scope_trace() as t:
+        op.softmax(x).eval()
+    assert [n for n in t.names if n != "get_function"] == [
+        "eltdiv(exp(subtract(Buffer, View(max(Buffer)))), View(sum(exp(subtract(Buffer, View(max(Buffer)))))))"]
+    assert t.names.count("get_function") == 1
+    # a reduction that cannot share the root's kernel is a computation of its own
+    with scope_trace() as t:
+        (x / op.sum(x)).eval()
+    assert len([n for n in t.names if n != "get_function"]) == 2
+    with scope_trace() as t:
+        x.eval()                      # a buffer: nothing to do
+    assert t.names == []
+
+
+def test_shard_marks_travel_with_values_and_guard_the_axis():
+    x = Array(np.zeros((64, 32), np.float32))
+    x.set_shard(0, 64, 128)
+    assert x.shard == (0, 64, 128)
+    assert (x * 2.0 + 1.0).shard == (0, 64, 128)
+    assert x.T.shard == (1, 64, 128) and x[:, 3:9].shard == (0, 64, 128) and x[None].shard == (1, 64, 128)
+    assert x.reshape([64, 4, 8]).shard == (0, 64, 128) and x.reshape([-1]).shard == (0, 64 * 32, 128 * 32)
+    assert op.sum(x, [1]).shard == (0, 64, 128) and op.sum(x, [0]).shard[0] == -1 and op.sum(x).shard[0] == -1
+    assert op.softmax(x, -1).shard == (0, 64, 128)
+    w = Array(np.zeros((32, 16), np.float32))
+    assert op.dot(x, w).shard == (0, 64, 128)
+    assert op.dot(w.T, x.T).shard == (1, 64, 128)
+    assert op.dot(x.T, x).shard[0] == -1                       # contracts the sharded dimension: every rank gets the whole product
+    for bad in (lambda: x[3], lambda: x[2:10], lambda: x[::2], lambda: op.gather(x, Array(np.zeros(4, np.int32))),
+                lambda: op.dot(x.T, w[:, :16].T[:, :64] if False else Array(np.zeros((64, 8), np.float32))),
+                lambda: x.reshape([32, 64]), lambda: op.cumsum(x.T)):
+        with pytest.raises(DaliB200Error):
+            bad()
+    y = Array(np.zeros((64, 32), np.float32))
+    y.set_shard(0, 0, 128)
+    with pytest.raises(DaliB200Error, match="sharded differently"):
+        x + y
+    with pytest.raises(DaliB200Error):
+        x.set_shard(0, 100, 128)                                # rows [100, 164) do not lie inside [0, 128)
+    x.set_shard(-1, 0, 0)
+    assert x.shard[0] == -1 and x[3].shape == (32,)
