@@ -23,6 +23,7 @@ std::string Variant::key() const {
       << ".p" << vpt << ".u" << unroll << ".x" << tx << ".y" << ty << "." << cls << "." << ocls;
     if (tile) s << ".tile" << tile;
     if (xrank) s << ".xrank";
+    if (stage) s << ".stage" << stage;
     return s.str();
 }
 
@@ -158,23 +159,23 @@ struct Gen {
     }
 
     // ---- outer (row) offsets: defines i64 ro<a> for every arg, given row index expr `r`
-    void row_offsets(const std::string& ind, const std::string& r) {
+    void row_offsets(const std::string& ind, const std::string& r, const std::string& ro = "ro") {
         if (v.nout == 0) {
-            for (size_t a = 0; a < p.args.size(); ++a) o << ind << "const i64 ro" << a << " = 0;\n";
+            for (size_t a = 0; a < p.args.size(); ++a) o << ind << "const i64 " << ro << a << " = 0;\n";
             return;
         }
         if (v.nout == 1) {
             for (size_t a = 0; a < p.args.size(); ++a)
-                o << ind << "const i64 ro" << a << " = " << r << " * " << W(L.arg_rs((int)a, 0)) << ";\n";
+                o << ind << "const i64 " << ro << a << " = " << r << " * " << W(L.arg_rs((int)a, 0)) << ";\n";
             return;
         }
-        for (size_t a = 0; a < p.args.size(); ++a) o << ind << "i64 ro" << a << " = 0;\n";
+        for (size_t a = 0; a < p.args.size(); ++a) o << ind << "i64 " << ro << a << " = 0;\n";
         o << ind << "{ i64 t_ = " << r << ";\n";
         for (int k = v.nout - 1; k >= 0; --k) {
             o << ind << "  { const i64 q_ = t_ / " << W(L.w_oshape + k) << "; const i64 i_ = t_ - q_ * "
               << W(L.w_oshape + k) << "; t_ = q_;\n";
             for (size_t a = 0; a < p.args.size(); ++a)
-                o << ind << "    ro" << a << " += i_ * " << W(L.arg_rs((int)a, k)) << ";\n";
+                o << ind << "    " << ro << a << " += i_ * " << W(L.arg_rs((int)a, k)) << ";\n";
             o << ind << "  }\n";
         }
         o << ind << "}\n";
@@ -279,19 +280,20 @@ struct Gen {
     }
 
     // load of the vector group of arg a into variable `dst`
-    void emit_arg_load(const std::string& ind, int a, const std::string& dst, const std::string& c, bool declare) {
+    void emit_arg_load(const std::string& ind, int a, const std::string& dst, const std::string& c, bool declare,
+                       const std::string& ro = "ro") {
         const std::string T = argT(a);
         char k = v.nin > 1 ? 's' : v.cls[a];
         if (declare) o << ind << "Vec<" << T << ", VEC> " << dst << ";\n";
         if (v.vec > 1 && k == 'u') {
-            o << ind << dst << " = vload<" << T << ", VEC>(a" << a << " + ro" << a << " + " << c << ");\n";
+            o << ind << dst << " = vload<" << T << ", VEC>(a" << a << " + " << ro << a << " + " << c << ");\n";
         } else if (k == 'z' && v.nin == 1) {
-            o << ind << "{ const " << T << " t_ = a" << a << "[ro" << a << "];\n" << ind
+            o << ind << "{ const " << T << " t_ = a" << a << "[" << ro << a << "];\n" << ind
               << "  _Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) " << dst << ".x[j] = t_; }\n";
         } else if (v.nin > 1) {
-            o << ind << dst << ".x[0] = a" << a << "[ro" << a << " + co" << a << "];\n";
+            o << ind << dst << ".x[0] = a" << a << "[" << ro << a << " + co" << a << "];\n";
         } else {
-            o << ind << "_Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) " << dst << ".x[j] = a" << a << "[ro" << a
+            o << ind << "_Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) " << dst << ".x[j] = a" << a << "[" << ro << a
               << " + " << col_off(a, c + " + j") << "];\n";
         }
     }
@@ -602,21 +604,75 @@ struct Gen {
                 pass_needed(q, true, &cuts[q]);
                 all_cuts.insert(cuts[q].begin(), cuts[q].end());
             }
+        std::set<int> eargs;
+        if (cached) {
+            for (const Stmt& s : p.stmts)
+                if (s.kind == S_LD && s.elem) eargs.insert(s.arg);
+            for (const Stmt& s : p.stmts)
+                if (s.kind == S_ST && s.elem && s.aop != A_ASSIGN) eargs.insert(s.arg);
+        }
+        // Staging: every warp owns a ring of STAGES rows (per operand) in shared memory.  Lane 0 issues one bulk
+        // asynchronous copy per row and operand (cp.async.bulk, completion counted in bytes on the slot's mbarrier),
+        // STAGES rows ahead of the row the warp works on; the warp waits on the slot, moves the row into registers and
+        // hands the slot straight back to the copy engine.  Warps never synchronise with one another, so loads, the
+        // reduction chain and the stores of different rows overlap for the whole launch.
+        const bool staged = cached && v.stage > 0;
+        if (staged) {
+            if (T != 32 || v.nin != 1) { *err = "staged rows need one warp per row"; return false; }
+            o << "#define STAGES " << v.stage << "\n";
+            o << "  extern __shared__ __align__(128) unsigned char st_ring[];\n";
+            o << "  __shared__ unsigned long long st_bar[RPC][STAGES];\n";
+            o << "  const i64 st_slot = " << W(L.w_aux0) << ";        // bytes between two slots of the ring (a row, padded to 128 bytes)\n";
+            o << "  const i64 st_step = (i64)gridDim.x * RPC;        // rows between two consecutive rows of a warp\n";
+            int k = 0;
+            for (int a : eargs) {
+                o << "  unsigned char* const st_base" << a << " = st_ring + ((i64)" << k++ << " * RPC + sub) * STAGES * st_slot;\n";
+                o << "  const unsigned st_bytes" << a << " = (unsigned)(C * sizeof(" << argT(a) << "));\n";
+            }
+            o << "  unsigned st_total = 0;\n";
+            for (int a : eargs) o << "  st_total += st_bytes" << a << ";\n";
+            o << "  if (lane == 0) { _Pragma(\"unroll\") for (int d = 0; d < STAGES; ++d) stage_bar_init(&st_bar[sub][d]); }\n";
+            o << "  stage_fence_init();\n  __syncwarp();\n";
+            // (kernel_entry(), the wait on the kernel before this one in the stream, has run: global memory may be read)
+            o << "  if (lane == 0) {\n    _Pragma(\"unroll\") for (int d = 0; d < STAGES; ++d) {\n";
+            o << "      const i64 pf_r = (i64)blockIdx.x * RPC + sub + d * st_step;\n      if (pf_r < R) {\n";
+            row_offsets("        ", "pf_r", "rn");
+            o << "        stage_expect(&st_bar[sub][d], st_total);\n";
+            for (int a : eargs)
+                o << "        stage_copy(st_base" << a << " + d * st_slot, a" << a << " + rn" << a << ", st_bytes" << a << ", &st_bar[sub][d]);\n";
+            o << "      }\n    }\n  }\n";
+            o << "  int st_it = 0;\n";
+        }
         o << "  int parity = 0;\n";
         o << "  for (i64 rbase = (i64)blockIdx.x * RPC; rbase < R; rbase += (i64)gridDim.x * RPC, parity ^= 1) {\n";
         o << "    const i64 r = rbase + sub;\n    const bool rv = r < R;\n";
         o << "    const i64 rr = rv ? r : 0;\n";
         row_offsets("    ", "rr");
         if (cached) {
-            std::set<int> eargs;
-            for (const Stmt& s : p.stmts)
-                if (s.kind == S_LD && s.elem) eargs.insert(s.arg);
-            for (const Stmt& s : p.stmts)
-                if (s.kind == S_ST && s.elem && s.aop != A_ASSIGN) eargs.insert(s.arg);
             for (int a : eargs) o << "    Vec<" << argT(a) << ", VEC> LQ" << a << "[VPT];\n";
             for (int id : all_cuts) o << "    " << ct(val(id).dtype) << " CV" << id << "[VPT * VEC];\n";
         }
         std::set<int> loaded;
+        if (staged) {
+            o << "    const int st_d = st_it % STAGES;\n    const unsigned st_par = (unsigned)((st_it / STAGES) & 1);\n    ++st_it;\n";
+            o << "    if (rv) stage_wait(&st_bar[sub][st_d], st_par);\n";
+            o << "    _Pragma(\"unroll\") for (int i = 0; i < VPT; ++i) {\n";
+            o << "      const int c = (i * TROW + lane) * VEC;\n      if (rv && c < (int)C) {\n";
+            for (int a : eargs) {
+                o << "        LQ" << a << "[i] = *reinterpret_cast<const Vec<" << argT(a) << ", VEC>*>(st_base" << a
+                  << " + st_d * st_slot + (i64)c * sizeof(" << argT(a) << "));\n";
+                loaded.insert(a);
+            }
+            o << "      }\n    }\n";
+            o << "    __syncwarp();\n";
+            o << "    if (lane == 0) {\n      const i64 pf_r = r + STAGES * st_step;\n      if (pf_r < R) {\n";
+            row_offsets("        ", "pf_r", "rn");
+            o << "        stage_fence_reuse();\n";
+            o << "        stage_expect(&st_bar[sub][st_d], st_total);\n";
+            for (int a : eargs)
+                o << "        stage_copy(st_base" << a << " + st_d * st_slot, a" << a << " + rn" << a << ", st_bytes" << a << ", &st_bar[sub][st_d]);\n";
+            o << "      }\n    }\n";
+        }
         for (int q = 0; q <= npass; ++q) {
             o << "    // ---- stage " << q << "\n";
             emit_row_values("    ", q, "rv", true, "lane == 0");

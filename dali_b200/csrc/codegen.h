@@ -42,6 +42,8 @@ struct Variant {
     int vpt = 0;             // row: vector groups per thread kept in registers (0 = streaming)
     int unroll = 4;          // map / all / col: independent groups in flight per thread
     int tx = 32, ty = 8;     // col: threads along outer / along the reduced dim
+    int stage = 0;           // row, T = 32: every warp keeps a ring of `stage` rows in flight, copied into shared memory by
+                             // bulk asynchronous copies (cp.async.bulk + mbarrier) ahead of the rows it works on
     bool xrank = false;      // all: partial results are exchanged with the other ranks before the kernel finishes
     int tile = 0;            // map with operands of class 't': 32 / 64 = edge of the shared-memory tiles they are read through, 4 = 4 x 4 register blocks (128-bit accesses), 0 = none
     std::string cls;         // per arg inner-stride class: u(nit) z(ero) s(trided) t(ransposed: unit stride along the OUTER dim)

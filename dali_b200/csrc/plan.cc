@@ -298,7 +298,25 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
         // rows to fill the machine; wider otherwise.
         // Measured on [4096,1024] softmax: 4 vector groups per lane (T = 64) beats 8 (T = 32) and
         // 2 (T = 128); single-pass reductions ([8192,8192] sums) run best with 8.
-        const int max_vpt = (p.max_stage <= 1 && !elem_stores) ? 8 : 4;
+        // Rows that are transformed and written back (a softmax) and fit eight vector groups per lane: one warp per row,
+        // rows staged through shared memory by bulk asynchronous copies, a ring of `stage` rows per warp (see codegen).
+        // Needs every element-level operand that is read to be a plain row of memory: unit stride, rows that start on
+        // 16-byte boundaries.  Opt-in (DALI_B200_ROW_STAGE = ring depth): at [4096,1024] the staged kernel measured 7.5-8.5 us
+        // per launch against 7.1 us for the plain one (rows straight into registers, 2048 CTAs) -- what a 5 us kernel
+        // loses in one in-order stream is the hand-over from one launch to the next, not load latency inside it.
+        int stage = env_int("DALI_B200_ROW_STAGE", 0);
+        {
+            bool ok = stage > 0 && elem_stores && v.nin == 1 && vec > 1 && groups <= 8 * 32 && groups > 32 && !p.has_indirect &&
+                      R >= (long long)kSMs * 8 && (long long)8 * vec * (n_elem_args + p.n_reductions) <= 96 && n_elem_args >= 1;
+            for (int a = 0; a < nargs && ok; ++a) {
+                if (!arg_elem(a) || !p.args[a].read) continue;
+                if (p.args[a].iota || v.cls[a] != 'u' || !aligned(a, 16 / dtype_size(p.args[a].dtype), false) ||
+                    (C * dtype_size(p.args[a].dtype)) % 16 != 0)
+                    ok = false;
+            }
+            if (!ok) stage = 0;
+        }
+        const int max_vpt = (p.max_stage <= 1 && !elem_stores) || stage ? 8 : 4;
         int T = 32;
         while (T < 1024 && (groups + T - 1) / T > max_vpt) T <<= 1;
         while (T > 1 && groups <= T / 2) T >>= 1;                       // short rows: sub-warp groups
@@ -318,6 +336,24 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
         int rpc = v.threads / T;
         long long gx = (R + rpc - 1) / rpc;
         out.grid_x = (unsigned)std::min<long long>(gx, (long long)kSMs * env_int("DALI_B200_ROW_CTAS_PER_SM", 32));
+        if (stage && cached && T == 32) {
+            // 8 warps per CTA; the rings of a CTA: operands x 8 warps x stage x one padded row
+            v.threads = env_int("DALI_B200_ROW_THREADS", 256);
+            rpc = v.threads / 32;
+            long long slot = 0;
+            for (int a = 0; a < nargs; ++a)
+                if (arg_elem(a) && p.args[a].read) slot = std::max<long long>(slot, (C * dtype_size(p.args[a].dtype) + 127) / 128 * 128);
+            long long smem = slot * stage * rpc * n_elem_args;
+            while (smem > 200 * 1024 && stage > 1) { --stage; smem = slot * stage * rpc * n_elem_args; }
+            if (smem <= 200 * 1024) {
+                v.stage = stage;
+                aux0 = slot;
+                out.smem_bytes = (unsigned)smem;
+                const long long per_sm = std::max<long long>(1, std::min<long long>(200 * 1024 / smem, 2048 / v.threads));
+                gx = (R + rpc - 1) / rpc;
+                out.grid_x = (unsigned)std::min<long long>(gx, (long long)kSMs * env_int("DALI_B200_ROW_STAGE_CTAS", (int)per_sm));
+            }
+        }
         v.unroll = 1; v.tx = 0; v.ty = 0;
     } else if (v.kind == K_ALL) {
         v.threads = env_int("DALI_B200_ALL_THREADS", 256);

@@ -290,6 +290,37 @@ DEV void kernel_entry() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// Rows staged through shared memory by bulk asynchronous copies (the row skeleton's `stage` variant): one mbarrier
+// per ring slot counts the bytes of the copies that fill it.
+DEV unsigned stage_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+DEV void stage_bar_init(unsigned long long* bar) { asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(stage_smem(bar))); }
+// makes the initialised barriers visible to the copy engine
+DEV void stage_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+// orders this thread's (and, after __syncwarp, its warp's) reads of a slot before the copy engine's next write to it
+DEV void stage_fence_reuse() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+DEV void stage_expect(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(stage_smem(bar)), "r"(bytes) : "memory");
+}
+// global -> shared, 16-byte aligned on both sides, a multiple of 16 bytes; local memory only, no multicast
+DEV void stage_copy(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(stage_smem(dst)), "l"(src), "r"(bytes), "r"(stage_smem(bar)) : "memory");
+}
+// Waits for the slot's copies.  Bounded (about a second): a copy from valid memory always completes, so giving up only
+// keeps a kernel with a defect from spinning for ever; the row is then processed with whatever the slot holds.
+DEV void stage_wait(unsigned long long* bar, unsigned parity) {
+    unsigned ok = 0;
+    const long long t0 = clock64();
+    while (true) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(stage_smem(bar)), "r"(parity) : "memory");
+        if (ok || clock64() - t0 > 2000000000LL) return;
+    }
+}
+
 // 128-bit global access; callers guarantee 16-byte alignment.
 template <typename T, int N> struct alignas(sizeof(T) * N) Vec { T x[N]; };
 template <typename T, int N> DEV Vec<T, N> vload(const T* p) { return *reinterpret_cast<const Vec<T, N>*>(p); }

@@ -401,6 +401,13 @@ static int do_launch(uint64_t hash, int device, void* stream, const int64_t* spa
     typedef CUresult (*LaunchExFn)(const CUlaunchConfig*, CUfunction, void**, void**);
     static LaunchExFn launch_ex = reinterpret_cast<LaunchExFn>(driver_entry("cuLaunchKernelEx"));
     CUresult r;
+    if (plan.smem_bytes > 48 * 1024) {
+        static CUresult (*set_attr)(CUfunction, CUfunction_attribute, int) =
+            reinterpret_cast<CUresult (*)(CUfunction, CUfunction_attribute, int)>(driver_entry("cuFuncSetAttribute"));
+        if (!set_attr) { set_error("cuFuncSetAttribute unavailable"); return DALIB200_ERR_CUDA; }
+        r = set_attr(fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)plan.smem_bytes);
+        if (r != CUDA_SUCCESS) { set_error("cuFuncSetAttribute(max dynamic smem): " + cu_err(r)); return DALIB200_ERR_CUDA; }
+    }
     if (launch_ex && dependent_launch_enabled()) {
         // programmatic dependent launch: every generated kernel begins with griddepcontrol.wait (prelude: kernel_entry)
         CUlaunchAttribute attr;
@@ -411,12 +418,13 @@ static int do_launch(uint64_t hash, int device, void* stream, const int64_t* spa
         std::memset(&cfg, 0, sizeof cfg);
         cfg.gridDimX = plan.grid_x; cfg.gridDimY = plan.grid_y; cfg.gridDimZ = 1;
         cfg.blockDimX = (unsigned)plan.variant.threads; cfg.blockDimY = 1; cfg.blockDimZ = 1;
+        cfg.sharedMemBytes = plan.smem_bytes;
         cfg.hStream = (CUstream)stream;
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
         r = launch_ex(&cfg, fn, params, nullptr);
     } else {
-        r = g_drv.LaunchKernel(fn, plan.grid_x, plan.grid_y, 1, (unsigned)plan.variant.threads, 1, 1, 0, (CUstream)stream,
+        r = g_drv.LaunchKernel(fn, plan.grid_x, plan.grid_y, 1, (unsigned)plan.variant.threads, 1, 1, plan.smem_bytes, (CUstream)stream,
                                params, nullptr);
     }
     if (r != CUDA_SUCCESS) { set_error("cuLaunchKernel(" + tl_variant + "): " + cu_err(r)); return DALIB200_ERR_CUDA; }
