@@ -517,7 +517,8 @@ class Gemm(Workload):
     name = "gemm"
     dtype = "bf16"
     hbm_metric = False
-    e2e_api = "C ABI with caller-managed copies (page-locked host -> device, dalib200_gemm_fused, device -> page-locked host, sync)"
+    e2e_api = ("page-locked host arrays of bf16 -> lazy Array / op:: expression op::tanh(op::dot(A, B) + bias).astype(bf16) -> eval -> "
+               "host array (the Python face of the C++ front end)")
     N = 8192
 
     @staticmethod
@@ -569,20 +570,22 @@ class Gemm(Workload):
     def e2e_setup(self):
         t = self.torch
         n = self.n
-        self.hA = t.empty(n, n, dtype=t.bfloat16, pin_memory=True); self.hA.copy_(self.A)
-        self.hB = t.empty(n, n, dtype=t.bfloat16, pin_memory=True); self.hB.copy_(self.Bm)
+        # page-locked host buffers holding bf16 bit patterns, seen by numpy as uint16
+        self.hA, self.hB, self.hout = (t.empty(n, n, dtype=t.int16, pin_memory=True) for _ in range(3))
+        self.hA.copy_(self.A.view(t.int16)); self.hB.copy_(self.Bm.view(t.int16))
         self.hbias = t.empty(n, pin_memory=True); self.hbias.copy_(self.bias)
-        self.hout = t.empty(n, n, dtype=t.bfloat16, pin_memory=True)
+        self.bits = {k: getattr(self, k).numpy().view(self.np.uint16) for k in ("hA", "hB", "hout")}
+        from dali_b200.array import set_default_device
+        set_default_device(self.device)
         self.h2d, self.d2h = 2 * n * n * 2 + n * 4, n * n * 2
 
     def e2e_step(self, i):
-        t = self.torch
-        self.A.copy_(self.hA, non_blocking=True)
-        self.Bm.copy_(self.hB, non_blocking=True)
-        self.bias.copy_(self.hbias, non_blocking=True)
-        self.launch_step(i, self.stream)
-        self.hout.copy_(self.out, non_blocking=True)
-        t.cuda.synchronize()
+        # the call a user makes: page-locked host arrays in, the reference's expression on bf16 Arrays, the result back
+        from dali_b200.array import Array, DTYPE_BF16, op
+        A, B = Array.borrow(self.bits["hA"], DTYPE_BF16), Array.borrow(self.bits["hB"], DTYPE_BF16)
+        bias = Array.borrow(self.hbias.numpy())
+        y = op.tanh(op.dot(A, B) + bias[None, :]).astype(DTYPE_BF16)
+        y.numpy(out=self.bits["hout"])
 
     def verify(self):
         """The WHOLE output against tanh(A.float() @ B.float() + bias) computed by torch in fp32 on the device (a checker,

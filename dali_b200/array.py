@@ -16,9 +16,21 @@ import numpy as np
 
 from .capi import load_library
 
-DTYPE_FLOAT, DTYPE_DOUBLE, DTYPE_INT32 = 0, 1, 2
+DTYPE_FLOAT, DTYPE_DOUBLE, DTYPE_INT32, DTYPE_BF16 = 0, 1, 2, 3
 _NP2D = {np.dtype(np.float32): 0, np.dtype(np.float64): 1, np.dtype(np.int32): 2}
-_D2NP = {0: np.float32, 1: np.float64, 2: np.int32}
+_D2NP = {0: np.float32, 1: np.float64, 2: np.int32, 3: np.uint16}      # bf16 travels as its 16-bit patterns (numpy has no bf16)
+
+
+def to_bf16_bits(x):
+    """float32 array -> uint16 bf16 bit patterns, round to nearest even (NaN stays NaN)."""
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    return np.where(np.isnan(x), np.uint16(0x7FC0), r).astype(np.uint16)
+
+
+def from_bf16_bits(b):
+    """uint16 bf16 bit patterns -> the float32 values they stand for."""
+    return (np.ascontiguousarray(b, np.uint16).astype(np.uint32) << 16).view(np.float32)
 _H = ctypes.c_void_p
 _lib = None
 
@@ -70,11 +82,14 @@ class Array:
                 dtype = DTYPE_INT32 if isinstance(value, (int, np.integer)) else DTYPE_DOUBLE if isinstance(value, float) else DTYPE_FLOAT
             _check(L.c.dali_array_scalar(float(value), int(dtype), ctypes.byref(h)))
         else:
+            if dtype == DTYPE_BF16 and np.asarray(value).dtype != np.uint16:
+                value = to_bf16_bits(np.asarray(value, np.float32))           # floats are rounded to bf16
             arr = np.ascontiguousarray(value, dtype=_D2NP[dtype] if dtype is not None else None)
-            if arr.dtype not in _NP2D:
+            if arr.dtype not in _NP2D and dtype != DTYPE_BF16:
                 arr = arr.astype(np.float32 if arr.dtype.kind == "f" else np.int32)
+            code = DTYPE_BF16 if dtype == DTYPE_BF16 else _NP2D[arr.dtype]
             _check(L.c.dali_array_from_host(ctypes.c_void_p(arr.ctypes.data), _shape_arg(arr.shape), arr.ndim,
-                                            _NP2D[arr.dtype], ctypes.byref(h)))
+                                            code, ctypes.byref(h)))
         self._h = h
 
     def __del__(self):
@@ -104,13 +119,15 @@ class Array:
         return out
 
     @staticmethod
-    def borrow(array):
+    def borrow(array, dtype=None):
         """Wraps a C-contiguous numpy array WITHOUT copying it (page-locked memory then reaches the GPU by DMA);
-        the caller keeps it alive and unchanged until the expressions reading it have been evaluated."""
-        if not (isinstance(array, np.ndarray) and array.flags.c_contiguous and array.dtype in _NP2D):
-            raise TypeError("Array.borrow needs a C-contiguous float32 / float64 / int32 numpy array")
+        the caller keeps it alive and unchanged until the expressions reading it have been evaluated.
+        dtype=DTYPE_BF16: a uint16 array of bf16 bit patterns."""
+        bf16 = dtype == DTYPE_BF16 and isinstance(array, np.ndarray) and array.dtype == np.uint16
+        if not (isinstance(array, np.ndarray) and array.flags.c_contiguous and (array.dtype in _NP2D or bf16)):
+            raise TypeError("Array.borrow needs a C-contiguous float32 / float64 / int32 (or, as bf16, uint16) numpy array")
         out = Array._new(_c().c.dali_array_borrow_host, ctypes.c_void_p(array.ctypes.data), _shape_arg(array.shape),
-                         array.ndim, _NP2D[array.dtype])
+                         array.ndim, DTYPE_BF16 if bf16 else _NP2D[array.dtype])
         out._keep = array
         return out
 

@@ -379,7 +379,7 @@ struct Gen {
                   << ", " << vn(s.in[0]) << ", (i64)(" << g.argred_index << "));\n";
             } else if (s.kind == S_ST) {
                 std::string old = argvec(s.arg) + ".x[j]";
-                o << in2 << "out" << si << ".x[j] = " << assign_rhs(s.aop, old, vn(s.in[0])) << ";\n";
+                o << in2 << "out" << si << ".x[j] = (" << argT(s.arg) << ")(" << assign_rhs(s.aop, old, vn(s.in[0])) << ");\n";
             } else if (s.kind == S_STX) {
                 const std::string addr = "&a" + std::to_string(s.arg) + "[ro" + std::to_string(s.arg) + " + " +
                                          col_off(s.arg, g.c + " + j") + " + (i64)" + vn(s.in[0]) + " * " +
@@ -410,18 +410,18 @@ struct Gen {
             const Stmt& s = p.stmts[i];
             if (s.elem || s.stage != q) continue;
             if (s.kind == S_LD) {
-                o << ind << "const " << ct(s.dtype) << " " << vn(s.id) << " = " << valid << " ? a" << s.arg << "[ro"
+                o << ind << "const " << ct(s.dtype) << " " << vn(s.id) << " = " << valid << " ? (" << ct(s.dtype) << ")a" << s.arg << "[ro"
                   << s.arg << "] : (" << ct(s.dtype) << ")0;\n";
             } else if (s.kind == S_LDX) {
-                o << ind << "const " << ct(s.dtype) << " " << vn(s.id) << " = " << valid << " ? a" << s.arg << "[ro"
+                o << ind << "const " << ct(s.dtype) << " " << vn(s.id) << " = " << valid << " ? (" << ct(s.dtype) << ")a" << s.arg << "[ro"
                   << s.arg << " + (i64)" << vn(s.in[0]) << " * " << W(L.arg_xs(s.arg)) << "] : (" << ct(s.dtype)
                   << ")0;\n";
             } else if (s.kind == S_OP || s.kind == S_CAST) {
                 o << ind << "const " << ct(s.dtype) << " " << vn(s.id) << " = " << expr(s) << ";\n";
             } else if (s.kind == S_ST) {
                 const std::string dst = "a" + std::to_string(s.arg) + "[ro" + std::to_string(s.arg) + "]";
-                o << ind << "if (" << valid << (leader_only_stores ? " && " + leader : "") << ") " << dst << " = "
-                  << assign_rhs(s.aop, dst, vn(s.in[0])) << ";\n";
+                o << ind << "if (" << valid << (leader_only_stores ? " && " + leader : "") << ") " << dst << " = ("
+                  << argT(s.arg) << ")(" << assign_rhs(s.aop, dst, vn(s.in[0])) << ");\n";
                 continue;
             } else if (s.kind == S_STX) {
                 const std::string addr = "&a" + std::to_string(s.arg) + "[ro" + std::to_string(s.arg) + " + (i64)" +
@@ -895,7 +895,7 @@ struct Gen {
         for (const Stmt& s : p.stmts) {
             if (s.elem || s.stage != 0 || (s.kind != S_ST && s.kind != S_STX)) continue;
             const std::string dst = "a" + std::to_string(s.arg) + "[0]";
-            if (s.kind == S_ST) o << "  if (tid == 0) " << dst << " = " << assign_rhs(s.aop, dst, vn(s.in[0])) << ";\n";
+            if (s.kind == S_ST) o << "  if (tid == 0) " << dst << " = (" << argT(s.arg) << ")(" << assign_rhs(s.aop, dst, vn(s.in[0])) << ");\n";
         }
         emit_row_values("  ", 1, "true", true, "tid == 0");
         o << "}\n";

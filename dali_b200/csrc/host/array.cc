@@ -19,12 +19,19 @@
 #include "dali/array/expression/optimization.h"
 
 // ------------------------------------------------------------------ dtype helpers
-int size_of_dtype(DType dtype) { return dtype == DTYPE_DOUBLE ? 8 : 4; }
+int size_of_dtype(DType dtype) { return dtype == DTYPE_DOUBLE ? 8 : (dtype == DTYPE_BF16 ? 2 : 4); }
+static float bf16_bits_to_float(unsigned short bits) {
+    unsigned u = (unsigned)bits << 16;
+    float f;
+    std::memcpy(&f, &u, sizeof f);
+    return f;
+}
 std::string dtype_to_name(DType dtype) {
     switch (dtype) {
         case DTYPE_FLOAT: return "float";
         case DTYPE_DOUBLE: return "double";
         case DTYPE_INT32: return "int32";
+        case DTYPE_BF16: return "bfloat16";
     }
     return "unknown";
 }
@@ -162,7 +169,7 @@ static std::vector<int> gather_shape(const Array& source, const Array& indices) 
     return s;
 }
 Gather::Gather(const Array& source, const Array& indices)
-    : Expression(N_GATHER, gather_shape(source, indices), source.dtype(), {source, indices}) {
+    : Expression(N_GATHER, gather_shape(source, indices), value_dtype(source.dtype()), {source, indices}) {
     DALI_ASSERT(!source.shard().sharded(), "gather from a sharded source is not supported (the indices would name other ranks' rows)");
     shard_ = indices.shard();          // out dims = the indices' dims, then the source's trailing dims
 }
@@ -173,7 +180,7 @@ static std::vector<int> gather_rows_shape(const Array& source, const Array& indi
     return s;
 }
 GatherFromRows::GatherFromRows(const Array& source, const Array& indices)
-    : Expression(N_GATHER_ROWS, gather_rows_shape(source, indices), source.dtype(), {source, indices}) {
+    : Expression(N_GATHER_ROWS, gather_rows_shape(source, indices), value_dtype(source.dtype()), {source, indices}) {
     const Shard s = source.shard(), i = indices.shard();
     DALI_ASSERT(s.axis <= 0 && i.axis <= 0, "gather_from_rows: only the row dimension may be sharded");
     DALI_ASSERT(!(s.sharded() && i.sharded()) || s == i, "gather_from_rows: source and indices are sharded differently");
@@ -181,7 +188,7 @@ GatherFromRows::GatherFromRows(const Array& source, const Array& indices)
 }
 
 MatMul::MatMul(const Array& left, const Array& right)
-    : Expression(N_MATMUL, {left.shape()[0], right.shape()[1]}, left.dtype(), {left, right}) {
+    : Expression(N_MATMUL, {left.shape()[0], right.shape()[1]}, value_dtype(left.dtype()), {left, right}) {
     const Shard l = left.shard(), r = right.shard();
     if (l.axis == 1 || r.axis == 0) {
         DALI_ASSERT(l.axis == 1 && r.axis == 0 && l.lo == r.lo && l.total == r.total,
@@ -391,7 +398,7 @@ memory::Device Array::preferred_device() const {
 void Array::to_device(memory::Device device) const { memory()->to_device(device); }
 
 DType type_promotion(const Array& a, const Array& b) {
-    if (a.dtype() == b.dtype()) return a.dtype();
+    if (a.dtype() == b.dtype()) return value_dtype(a.dtype());      // (two bf16 operands compute in float)
     if (a.dtype() == DTYPE_DOUBLE || b.dtype() == DTYPE_DOUBLE) return DTYPE_DOUBLE;
     return DTYPE_FLOAT;
 }
@@ -681,6 +688,7 @@ T Array::scalar_value() const {
         case DTYPE_FLOAT: return (T)(*(const float*)base);
         case DTYPE_DOUBLE: return (T)(*(const double*)base);
         case DTYPE_INT32: return (T)(*(const int*)base);
+        case DTYPE_BF16: return (T)bf16_bits_to_float(*(const unsigned short*)base);
     }
     return T();
 }
@@ -819,6 +827,7 @@ void Array::print(std::basic_ostream<char>& stream, const int& indent, const boo
         switch (b->dtype_) {
             case DTYPE_FLOAT: return ((const float*)base)[i];
             case DTYPE_DOUBLE: return ((const double*)base)[i];
+            case DTYPE_BF16: return bf16_bits_to_float(((const unsigned short*)base)[i]);
             default: return ((const int*)base)[i];
         }
     };
@@ -910,7 +919,8 @@ void Array::save(const std::string& fname, const Array& arr, const std::ios_base
 }
 
 void Array::save(std::basic_ostream<char>& f, const Array& arr) {
-    Array c = arr.ascontiguousarray();
+    // (NumPy has no bf16: such an array is written as the float32 values it holds, exactly)
+    Array c = arr.dtype() == DTYPE_BF16 ? arr.astype(DTYPE_FLOAT).ascontiguousarray() : arr.ascontiguousarray();
     c.eval();
     BufferView* b = as<BufferView>(c);
     const char* base = (const char*)b->memory_->readonly_data(memory::Device::cpu()) + b->offset_ * size_of_dtype(b->dtype_);

@@ -34,7 +34,7 @@ std::vector<int> to_shape(const int64_t* shape, int ndim) {
 }
 
 DType to_dtype(int dtype) {
-    DALI_ASSERT(dtype >= 0 && dtype <= 2, "dtype must be 0 (float), 1 (double) or 2 (int32)");
+    DALI_ASSERT(dtype >= 0 && dtype <= 3, "dtype must be 0 (float), 1 (double), 2 (int32) or 3 (bf16, a storage type)");
     return (DType)dtype;
 }
 

@@ -106,7 +106,9 @@ void note_collective(const std::string& what) {
     tl_stats.last_collective = what;
 }
 
-const char* ir_dtype(DType d) { return d == DTYPE_FLOAT ? "f32" : (d == DTYPE_DOUBLE ? "f64" : "i32"); }
+// IR type names: of VALUES (bf16 is a storage type: a value read from a bf16 array is an f32) and of ARGS
+const char* ir_dtype(DType d) { return d == DTYPE_FLOAT || d == DTYPE_BF16 ? "f32" : (d == DTYPE_DOUBLE ? "f64" : "i32"); }
+const char* ir_arg_dtype(DType d) { return d == DTYPE_BF16 ? "bf16" : ir_dtype(d); }
 const char* ir_assign(OPERATOR_T op) {
     switch (op) {
         case OPERATOR_T_ADD: return "add";
@@ -170,6 +172,7 @@ struct Lowerer {
 
     int new_value(DType t, bool is_elem, const std::string& text) {
         int id = (int)types.size();
+        t = value_dtype(t);
         types.push_back(t);
         elem.push_back(is_elem);
         body.push_back("v" + std::to_string(id) + " " + ir_dtype(t) + " " + text);
@@ -297,7 +300,7 @@ struct Lowerer {
                                     w->functor_ == "rng_normal";
                     std::string text = "op " + w->functor_;
                     for (int v : in) {
-                        if (!converts && types[v] != w->dtype_) v = new_value(w->dtype_, elem[v], "cast v" + std::to_string(v));
+                        if (!converts && types[v] != value_dtype(w->dtype_)) v = new_value(w->dtype_, elem[v], "cast v" + std::to_string(v));
                         text += " v" + std::to_string(v);
                     }
                     id = new_value(w->dtype_, is_elem, text);
@@ -445,7 +448,7 @@ struct Lowerer {
         std::ostringstream o;
         o << "dali-ir 1\nspace " << rank << " " << nreduce << "\n";
         for (size_t i = 0; i < leaves.size(); ++i)
-            o << "arg " << i << " " << ir_dtype(leaves[i].dtype) << " " << (leaves[i].elem_level || nreduce == 0 ? "E" : "R")
+            o << "arg " << i << " " << ir_arg_dtype(leaves[i].dtype) << " " << (leaves[i].elem_level || nreduce == 0 ? "E" : "R")
               << (leaves[i].iota ? " iota" : "") << "\n";
         for (size_t j = 0; j < scalars.size(); ++j) o << "scalar " << j << " " << ir_dtype(scalars[j].first) << "\n";
         for (const std::string& line : body) o << line << "\n";
@@ -678,6 +681,8 @@ void run_matmul(const Array& dest, OPERATOR_T op, MatMul* mm) {
         run_assignment(dest, op, tmp);
         return;
     }
+    DALI_ASSERT(left.dtype() != DTYPE_BF16 && right.dtype() != DTYPE_BF16 && dest.dtype() != DTYPE_BF16,
+                "a bf16 product runs on the tensor cores only: both operands bf16, row-major with 16-byte aligned rows (no transposed or strided views)");
     DALI_ASSERT(dest.dtype() == left.dtype() && dest.dtype() == right.dtype(), "matmul operands and destination must share a dtype");
     BufferView* a = as<BufferView>(left);
     BufferView* b = as<BufferView>(right);
@@ -798,6 +803,57 @@ bool launch_gemm_program(Lowerer& L, const GemmOperands& g, int64_t m, int64_t n
     tl_stats.last_ir = text;
     const void *pa_hi[2], *pa_lo[2], *pb_hi[2], *pb_lo[2];
     int64_t ld[2];
+    // bf16 operands (both of every pair): one bf16 tensor-core pass straight from the arrays -- A [m,k] and B [k,n]
+    // row-major with pitches TMA can address; nothing is split
+    int n_bf16 = 0;
+    for (int p = 0; p < np; ++p) n_bf16 += (a[p]->dtype_ == DTYPE_BF16) + (b[p]->dtype_ == DTYPE_BF16);
+    if (n_bf16 != 0 && n_bf16 != 2 * np) return false;
+    if (n_bf16) {
+        int64_t lda[2], ldb[2];
+        for (int p = 0; p < np; ++p) {
+            std::vector<int> as_ = a[p]->normalized_strides(), bs = b[p]->normalized_strides();
+            if ((as_[1] != 1 && k[p] != 1) || (bs[1] != 1 && g.n != 1)) return false;
+            lda[p] = as_[0]; ldb[p] = bs[0];
+            if (lda[p] % 8 || ldb[p] % 8 || a[p]->offset_ % 8 || b[p]->offset_ % 8 || lda[p] < k[p] || ldb[p] < g.n) return false;
+        }
+        const int na = (int)L.leaves.size();
+        std::vector<void*> ptrs(na, (void*)(uintptr_t)4096);
+        std::vector<int64_t> offsets(na, 0);
+        std::vector<const int64_t*> strides(na, nullptr);
+        std::vector<double> sd(L.scalars.size());
+        std::vector<float> sf(L.scalars.size());
+        std::vector<int> si(L.scalars.size());
+        std::vector<const void*> sp(L.scalars.size());
+        for (size_t j = 0; j < L.scalars.size(); ++j) {
+            sd[j] = L.scalars[j].second; sf[j] = (float)sd[j]; si[j] = (int)sd[j];
+            sp[j] = L.scalars[j].first == DTYPE_DOUBLE ? (const void*)&sd[j] : (L.scalars[j].first == DTYPE_FLOAT ? (const void*)&sf[j] : (const void*)&si[j]);
+        }
+        int dev = -1;
+        if (!tl_dry_run) {
+            dev = device_index(device);
+            for (int p = 0; p < np; ++p) {
+                pa_hi[p] = (const char*)a[p]->memory_->data(device, memory::AM_READONLY) + a[p]->offset_ * 2;
+                pb_hi[p] = (const char*)b[p]->memory_->data(device, memory::AM_READONLY) + b[p]->offset_ * 2;
+            }
+            for (int pass = 0; pass < 2; ++pass)
+                for (int i = 0; i < na; ++i) {
+                    if ((pass == 1) != L.leaves[i].written) continue;
+                    ptrs[i] = L.leaves[i].memory->data(device, L.leaves[i].written ? memory::AM_MUTABLE : memory::AM_READONLY);
+                }
+        } else {
+            for (int p = 0; p < np; ++p) pa_hi[p] = pb_hi[p] = (void*)(uintptr_t)4096;
+        }
+        for (int i = 0; i < na; ++i) { offsets[i] = L.leaves[i].offset; strides[i] = L.leaves[i].strides.data(); }
+        int rc = dalib200_gemm_fused_sum(dev, nullptr, DALIB200_BF16, np, m, n, k, pa_hi, lda, pb_hi, ldb, nullptr, nullptr, hash,
+                                         ptrs.data(), offsets.data(), strides.data(), na, sp.data(), (int)sp.size());
+        if (rc == DALIB200_ERR_UNSUPPORTED) return false;
+        check(rc, "dalib200_gemm_fused_sum (bf16)");
+        ++tl_stats.gemms;
+        char buf[256];
+        dalib200_last_gemm_kernel(buf, sizeof buf);
+        tl_stats.last_variant = buf;
+        return true;
+    }
     if (tl_dry_run) {
         void* fake[16];
         for (auto& p : fake) p = (void*)(uintptr_t)4096;
@@ -1116,7 +1172,7 @@ void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) 
     }
 
     // ---- an elementwise tree around a product: tensor-core GEMM with the tree as its epilogue
-    if (dest.is_buffer() && dest.ndim() == 2 && dest.dtype() == DTYPE_FLOAT && value.shape() == dest.shape()) {
+    if (dest.is_buffer() && dest.ndim() == 2 && value_dtype(dest.dtype()) == DTYPE_FLOAT && value.shape() == dest.shape()) {
         const Expression* acc = nullptr;
         find_matmul_sum(value, &acc);
         if (!acc) find_matmul(value, &acc);
@@ -1170,10 +1226,10 @@ void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) 
     }
     if (ScalarValue* sv = as<ScalarValue>(value)) {
         // a host scalar takes the destination's type before it becomes a kernel argument
-        if (sv->dtype_ != dest.dtype()) {
+        if (sv->dtype_ != value_dtype(dest.dtype())) {
             double x = sv->value_;
             if (dest.dtype() == DTYPE_INT32) x = std::floor(x + 0.5);
-            value = Array(std::make_shared<ScalarValue>(x, dest.dtype()));
+            value = Array(std::make_shared<ScalarValue>(x, value_dtype(dest.dtype())));
         }
     }
     if (value.ndim() != 0 && value.shape() != dest.shape()) {
@@ -1219,8 +1275,8 @@ void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) 
     // ---- value
     IndexMap root_map = rank0_dest ? IndexMap() : identity_map(row_level_root ? rank - nreduce : (int)dest.shape().size());
     int v = value.ndim() == 0 ? L.visit(value, IndexMap()) : L.visit(value, root_map);
-    if (L.types[v] != dest.dtype()) {
-        // assignment converts; towards int32 it rounds, as op::astype does
+    if (L.types[v] != value_dtype(dest.dtype())) {
+        // assignment converts; towards int32 it rounds, as op::astype does (towards bf16 the store itself rounds)
         if (dest.dtype() == DTYPE_INT32) v = L.new_value(DTYPE_INT32, L.elem[v], "op round v" + std::to_string(v));
         else v = L.new_value(dest.dtype(), L.elem[v], "cast v" + std::to_string(v));
     }

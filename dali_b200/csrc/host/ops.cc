@@ -41,8 +41,12 @@ static std::string strip(const std::string& functor_name) {
 }
 
 // ---------------------------------------------------------------- elementwise
+// bf16 is a storage type: whatever is computed on a bf16 Array is computed on its float values
+static Array computed_in_float(const Array& a) { return a.dtype() == DTYPE_BF16 ? unsafe_cast(a, DTYPE_FLOAT) : a; }
+
 Array elementwise(Array a, const std::string& functor_name) {
     DALI_ASSERT(!a.is_stateless(), "elementwise operation on a stateless Array");
+    a = computed_in_float(a);
     return Array(std::make_shared<Elementwise>(strip(functor_name), std::vector<Array>({a}), a.shape(), a.dtype()));
 }
 
@@ -63,6 +67,8 @@ static std::vector<int> common_shape(const Array& a, const Array& b, const std::
 
 std::tuple<Array, Array> ensure_arguments_compatible(Array a, Array b, const std::string& functor_name, bool update_shape) {
     DALI_ASSERT(!a.is_stateless() && !b.is_stateless(), "binary operation on a stateless Array");
+    a = computed_in_float(a);
+    b = computed_in_float(b);
     if (update_shape) {
         DALI_ASSERT(a.ndim() == 0 || b.ndim() == 0 || a.ndim() == b.ndim(),
                     "Arguments to binary operation '" + functor_name + "' must have the same rank (got left.ndim = " +
@@ -90,6 +96,11 @@ Array elementwise(Array a, Array b, const std::string& functor_name) {
 
 Array unsafe_cast(Array a, DType type) {
     if (a.dtype() == type) return a;
+    if (type == DTYPE_BF16) {
+        // the float a bf16 store keeps; the node is typed bf16 so that evaluating it allocates 16-bit storage
+        Array f = unsafe_cast(a, DTYPE_FLOAT);
+        return Array(std::make_shared<Elementwise>("bf16_round", std::vector<Array>({f}), f.shape(), DTYPE_BF16));
+    }
     if (ScalarValue* s = as<ScalarValue>(a)) {
         double v = s->value_;
         if (type == DTYPE_INT32) v = (double)(int)v;
@@ -99,10 +110,12 @@ Array unsafe_cast(Array a, DType type) {
 }
 Array round(Array a) {
     if (a.dtype() == DTYPE_INT32) return a;
+    a = computed_in_float(a);
     return Array(std::make_shared<Elementwise>("round", std::vector<Array>({a}), a.shape(), DTYPE_INT32));
 }
 Array ceil(Array a) {
     if (a.dtype() == DTYPE_INT32) return a;
+    a = computed_in_float(a);
     return Array(std::make_shared<Elementwise>("ceiling", std::vector<Array>({a}), a.shape(), DTYPE_INT32));
 }
 Array astype(Array a, DType type) { return type == DTYPE_INT32 ? round(a) : unsafe_cast(a, type); }
@@ -181,14 +194,16 @@ static std::string reducer_short(const std::string& name) {
     return n;
 }
 
-Array all_reduce(const Array& a, const std::string& reducer_name) {
-    DALI_ASSERT(!a.is_stateless(), "reduction of a stateless Array");
+Array all_reduce(const Array& a_in, const std::string& reducer_name) {
+    DALI_ASSERT(!a_in.is_stateless(), "reduction of a stateless Array");
+    const Array a = computed_in_float(a_in);
     if (a.ndim() == 0) return a;
     return Array(std::make_shared<Reduce>(reducer_short(reducer_name), a, a.ndim(), false, a.dtype()));
 }
 
-Array axis_reduce(const Array& a, const std::string& reducer_name, const std::vector<int>& axes, bool keepdims) {
-    DALI_ASSERT(!a.is_stateless(), "reduction of a stateless Array");
+Array axis_reduce(const Array& a_in, const std::string& reducer_name, const std::vector<int>& axes, bool keepdims) {
+    DALI_ASSERT(!a_in.is_stateless(), "reduction of a stateless Array");
+    const Array a = computed_in_float(a_in);
     if (axes.empty()) return a;
     const int ndim = a.ndim();
     if (ndim == 0) return a;
@@ -222,15 +237,17 @@ Array axis_reduce(const Array& a, const std::string& reducer_name, const std::ve
     return res;
 }
 
-Array argument_all_reduce(const Array& a, const std::string& reducer_name) {
-    DALI_ASSERT(!a.is_stateless(), "reduction of a stateless Array");
+Array argument_all_reduce(const Array& a_in, const std::string& reducer_name) {
+    DALI_ASSERT(!a_in.is_stateless(), "reduction of a stateless Array");
+    const Array a = computed_in_float(a_in);
     if (a.ndim() == 0) return Array(0);
     // int32, where the reference mistypes the result as the input's dtype
     // (dali/array/op/reducer_operation.cpp:681-684)
     return Array(std::make_shared<Reduce>(reducer_short(reducer_name), a, a.ndim(), true, DTYPE_INT32));
 }
 
-Array argument_axis_reduce(const Array& a, const std::string& reducer_name, const int& axis) {
+Array argument_axis_reduce(const Array& a_in, const std::string& reducer_name, const int& axis) {
+    const Array a = computed_in_float(a_in);
     const int ndim = a.ndim();
     if (ndim == 0) return Array(0);
     int norm = axis < 0 ? axis + ndim : axis;
@@ -442,7 +459,7 @@ Array axis_scan(const Array& a, const std::string& reducer_name, bool inclusive)
     if (r == "minimum") r = "min";
     if (r == "product") r = "prod";
     DALI_ASSERT(r == "sum" || r == "prod" || r == "max" || r == "min", "axis_scan: unknown reducer " + reducer_name);
-    Array x = a.ndim() == 0 ? a.expand_dims(0) : a;
+    Array x = computed_in_float(a.ndim() == 0 ? a.expand_dims(0) : a);
     return Array(std::make_shared<Scan>(x, r, inclusive));
 }
 Array cumsum(const Array& a, bool inclusive) { return axis_scan(a, "reducers::sum", inclusive); }

@@ -22,7 +22,7 @@ const char* dtype_c_name(DType t) {
         case F32: return "float";
         case F64: return "double";
         case I32: return "int";
-        case BF16: return "__nv_bfloat16";
+        case BF16: return "bf16_t";
     }
     return "?";
 }
@@ -43,7 +43,7 @@ bool parse_dtype(const std::string& s, DType* out) {
     if (s == "f32") { *out = F32; return true; }
     if (s == "f64") { *out = F64; return true; }
     if (s == "i32") { *out = I32; return true; }
-    return false;   // bf16 is a GEMM operand type only, never an IR value type
+    return false;   // bf16 is a storage type of args only, never an IR value type
 }
 
 bool parse_arg_dtype(const std::string& s, DType* out) {
@@ -85,7 +85,9 @@ int functor_arity(const std::string& n) {
         "identity", "square", "cube", "sqrt_f", "rsqrt", "inv", "sigmoid", "dsigmoid", "tanh",
         "dtanh", "inverse_tanh", "exp", "log", "negative_log", "safe_entropy_log", "log_or_zero",
         "abs", "sign", "relu", "relu_backward", "softplus", "softplus_backward", "isnotanumber",
-        "isinfinity", "round", "ceiling", "negate", nullptr};
+        "isinfinity", "round", "ceiling", "negate",
+        "bf16_round",      // not a reference functor: the float a bf16 store would keep (astype(bf16) inside an expression)
+        nullptr};
     static const char* binary[] = {
         "add", "subtract", "eltmul", "eltdiv", "equals", "power", "fill", "div_grad", "threshold",
         "max_scalar", "min_scalar", "steep_sigmoid", "steep_sigmoid_backward", "clipped_relu",

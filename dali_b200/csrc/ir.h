@@ -8,8 +8,8 @@
 //   dali-ir 1
 //   space <rank> <nreduce>      iteration space; reductions fold the innermost
 //                               <nreduce> dims (0 = pure elementwise map)
-//   arg <i> <f32|f64|i32|bf16> <E|R>  (bf16: storage type of GEMM epilogue operands; loads
-//                               yield f32, stores take f32)
+//   arg <i> <f32|f64|i32|bf16> <E|R>  (bf16: a storage type -- loads yield f32, stores take f32 and round to
+//                               nearest even; no indirect stores)
 //                               i-th buffer.  E: indexed by the whole space,
 //                               R: indexed by the outer (non-reduced) dims only
 //   scalar <j> <dtype>          j-th run-time scalar (value read at launch)

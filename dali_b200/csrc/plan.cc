@@ -78,7 +78,8 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
                  const void* const* scalars, int n_scalars,
                  LaunchPlan* plan, std::string* err) {
     if (p.has_acc) { *err = "launch: this program reads a GEMM accumulator; run it through dalib200_gemm_fused"; return false; }
-    if (p.has_bf16) { *err = "launch: bf16 operands exist only in GEMM epilogue programs"; return false; }
+    for (const Stmt& st_ : p.stmts)
+        if (st_.kind == S_STX && p.args[st_.arg].dtype == BF16) { *err = "launch: no scatter into a bf16 array (there is no 16-bit atomic path)"; return false; }
     if (rank != p.rank) { *err = "launch: space rank differs from the program's"; return false; }
     if (n_arrays != (int)p.args.size()) { *err = "launch: wrong number of arrays"; return false; }
     if (n_scalars != (int)p.scalars.size()) { *err = "launch: wrong number of scalars"; return false; }
@@ -307,7 +308,7 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
         int stage = env_int("DALI_B200_ROW_STAGE", 0);
         {
             bool ok = stage > 0 && elem_stores && v.nin == 1 && vec > 1 && groups <= 8 * 32 && groups > 32 && !p.has_indirect &&
-                      R >= (long long)kSMs * 8 && (long long)8 * vec * (n_elem_args + p.n_reductions) <= 96 && n_elem_args >= 1;
+                      R >= (long long)kSMs * 16 && (long long)8 * vec * (n_elem_args + p.n_reductions) <= 96 && n_elem_args >= 1;
             for (int a = 0; a < nargs && ok; ++a) {
                 if (!arg_elem(a) || !p.args[a].read) continue;
                 if (p.args[a].iota || v.cls[a] != 'u' || !aligned(a, 16 / dtype_size(p.args[a].dtype), false) ||

@@ -16,6 +16,24 @@ typedef unsigned int u32;
 #define DALI_I32_MIN (-2147483647 - 1)
 #define DALI_EPS 1e-6
 
+// bf16 as a STORAGE type of kernel arguments (the reference has float, double and int32 only, dali/array/dtype.h:6-10):
+// a load yields the exact float, a store rounds to nearest even (NaN stays NaN); all arithmetic is fp32.
+struct bf16_t {
+    unsigned short bits;
+    DEV bf16_t() {}
+    DEV explicit bf16_t(float f) {
+        unsigned u = __float_as_uint(f);
+        if ((u & 0x7fffffffu) > 0x7f800000u) { bits = (unsigned short)((u >> 16) | 0x0040u); return; }
+        u += 0x7fffu + ((u >> 16) & 1u);
+        bits = (unsigned short)(u >> 16);
+    }
+    DEV explicit bf16_t(double f) : bf16_t((float)f) {}
+    DEV explicit bf16_t(int f) : bf16_t((float)f) {}
+    DEV operator float() const { return __uint_as_float((unsigned)bits << 16); }
+};
+// the value a bf16 store would keep, as a float (x.astype(bf16) inside a larger expression)
+DEV float f_bf16_round(float a) { return (float)bf16_t(a); }
+
 // ---------------------------------------------------------------- functors
 template <typename T> DEV T f_identity(T a) { return a; }
 template <typename T> DEV T f_negate(T a) { return -a; }

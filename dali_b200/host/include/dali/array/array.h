@@ -27,7 +27,13 @@
 #include "dali/utils/print_utils.h"
 
 // ------------------------------------------------------------------ dtype
-enum DType { DTYPE_FLOAT = 0, DTYPE_DOUBLE = 1, DTYPE_INT32 = 2 };
+// DTYPE_BF16 is not in the reference (dali/array/dtype.h:6-10 has the first three): a 16-bit STORAGE type.  Views of a
+// bf16 Array stay bf16; every computation on one runs in fp32 and yields a float Array (x.astype(DTYPE_BF16) or an
+// assignment into a bf16 Array round the result back, to nearest even); op::dot of two bf16 matrices is the bf16
+// tensor-core product with fp32 accumulation.
+enum DType { DTYPE_FLOAT = 0, DTYPE_DOUBLE = 1, DTYPE_INT32 = 2, DTYPE_BF16 = 3 };
+// the type arithmetic on `dtype` happens in (float for bf16, the type itself otherwise)
+inline DType value_dtype(DType dtype) { return dtype == DTYPE_BF16 ? DTYPE_FLOAT : dtype; }
 int size_of_dtype(DType dtype);
 std::string dtype_to_name(DType dtype);
 std::ostream& operator<<(std::ostream&, const DType&);

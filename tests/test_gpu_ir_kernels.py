@@ -366,7 +366,7 @@ def test_rows_staged_through_shared_memory_by_bulk_copies(lib, monkeypatch):
     from dali_b200.ir import softmax_ir
     monkeypatch.setenv("DALI_B200_ROW_STAGE", "3")
     rng = np.random.default_rng(17)
-    for rows, cols in ((2051, 1000), (1500, 512)):
+    for rows, cols in ((4099, 1000), (3000, 512)):
         a = rng.standard_normal((rows, cols)).astype(np.float32)
         out = torch.empty((rows, cols), device="cuda")
         lib.launch(lib.compile(softmax_ir()), (rows, cols), [out, dev(a)])
@@ -376,16 +376,16 @@ def test_rows_staged_through_shared_memory_by_bulk_copies(lib, monkeypatch):
     o, x, y = b.arg("f32"), b.arg("f32"), b.arg("f32")
     s = b.op("add", b.ld(x), b.ld(y))
     b.st(o, b.op("eltdiv", s, b.red("sum", s)))
-    xs, ys = (rng.random((1300, 640)).astype(np.float32) + 0.5 for _ in range(2))
-    out = torch.empty((1300, 640), device="cuda")
-    lib.launch(lib.compile(b.text()), (1300, 640), [out, dev(xs), dev(ys)])
+    xs, ys = (rng.random((2600, 640)).astype(np.float32) + 0.5 for _ in range(2))
+    out = torch.empty((2600, 640), device="cuda")
+    lib.launch(lib.compile(b.text()), (2600, 640), [out, dev(xs), dev(ys)])
     assert ".stage" in lib.last_variant(), lib.last_variant()
     want = (xs + ys) / (xs + ys).astype(np.float64).sum(1, keepdims=True)
     np.testing.assert_allclose(host(out), want, rtol=1e-5)
     # a view whose rows do not start on 16-byte boundaries falls back to the plain variant
-    a = rng.standard_normal((1400, 516)).astype(np.float32)
+    a = rng.standard_normal((2400, 516)).astype(np.float32)
     d = dev(a)
-    out = torch.empty((1400, 512), device="cuda")
-    lib.launch(lib.compile(softmax_ir()), (1400, 512), [out, d], strides=[None, [516, 1]], offsets=[0, 1])
+    out = torch.empty((2400, 512), device="cuda")
+    lib.launch(lib.compile(softmax_ir()), (2400, 512), [out, d], strides=[None, [516, 1]], offsets=[0, 1])
     assert ".stage" not in lib.last_variant()
     np.testing.assert_allclose(host(out), oracle.softmax(np.ascontiguousarray(a[:, 1:513])), rtol=1e-5, atol=1e-9)
