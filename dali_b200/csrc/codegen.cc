@@ -24,6 +24,7 @@ std::string Variant::key() const {
     if (tile) s << ".tile" << tile;
     if (xrank) s << ".xrank";
     if (stage) s << ".stage" << stage;
+    if (cluster > 1) s << ".cl" << cluster;
     return s.str();
 }
 
@@ -596,6 +597,16 @@ struct Gen {
             const Stmt& s = p.stmts[si];
             if (T > 32) o << "  __shared__ " << acc_type(s) << " sm" << si << "[2][NT / 32];\n";
         }
+        const bool clustered = v.cluster > 1;
+        if (clustered) {
+            if (cached || v.threads != T || v.nin != 1) { *err = "cluster rows: one streaming CTA per row slice"; return false; }
+            o << "#define CL " << v.cluster << "\n";
+            o << "  const unsigned cl_rank = cluster_rank();\n";
+            o << "  const i64 cl_per = ((C + (i64)CL * VEC - 1) / ((i64)CL * VEC)) * VEC;     // columns per CTA of the cluster\n";
+            o << "  const i64 cl_lo = (i64)cl_rank * cl_per;\n";
+            o << "  const i64 cl_hi = cl_lo + cl_per < C ? cl_lo + cl_per : C;\n";
+            for (int si : reds) o << "  __shared__ " << acc_type(p.stmts[si]) << " cx" << si << "[2][CL];\n";
+        }
         // cut analysis for the cached variant
         std::vector<std::set<int>> cuts(npass + 1);
         std::set<int> all_cuts;
@@ -644,6 +655,9 @@ struct Gen {
             o << "  int st_it = 0;\n";
         }
         o << "  int parity = 0;\n";
+        if (clustered)
+            o << "  for (i64 rbase = (i64)(blockIdx.x / CL); rbase < R; rbase += (i64)(gridDim.x / CL), parity ^= 1) {\n";
+        else
         o << "  for (i64 rbase = (i64)blockIdx.x * RPC; rbase < R; rbase += (i64)gridDim.x * RPC, parity ^= 1) {\n";
         o << "    const i64 r = rbase + sub;\n    const bool rv = r < R;\n";
         o << "    const i64 rr = rv ? r : 0;\n";
@@ -675,7 +689,7 @@ struct Gen {
         }
         for (int q = 0; q <= npass; ++q) {
             o << "    // ---- stage " << q << "\n";
-            emit_row_values("    ", q, "rv", true, "lane == 0");
+            emit_row_values("    ", q, "rv", true, clustered ? "lane == 0 && cl_rank == 0" : "lane == 0");
             if (q == npass) break;
             std::vector<int> sinks = pass_sinks(q);
             if (sinks.empty()) continue;
@@ -721,11 +735,32 @@ struct Gen {
                 emit_group(q, need, g);
                 o << "      }\n    }\n";
             } else {
-                o << "    if (rv) for (int c = lane * VEC; c < (int)C; c += TROW * VEC) {\n";
-                g.ind = "      ";
-                g.c = "c";
-                emit_group(q, need, g);
-                o << "    }\n";
+                const std::string lo = clustered ? "(int)cl_lo" : "0", hi = clustered ? "(int)cl_hi" : "(int)C";
+                if (v.nin == 1 && v.unroll > 1) {
+                    // UNROLL vector groups per thread and step, their loads issued before any of them is used: a
+                    // streamed row keeps enough bytes in flight per thread to cover the memory latency
+                    std::set<int> largs = args_loaded_in(need, q);
+                    o << "    if (rv) for (int cb = " << lo << " + lane * VEC; cb < " << hi << "; cb += TROW * VEC * UNROLL) {\n";
+                    for (int a : largs) o << "      Vec<" << argT(a) << ", VEC> q" << a << "[UNROLL];\n";
+                    o << "      _Pragma(\"unroll\") for (int u = 0; u < UNROLL; ++u) {\n";
+                    o << "        const int c = cb + u * TROW * VEC;\n        if (c < " << hi << ") {\n";
+                    for (int a : largs) emit_arg_load("          ", a, "q" + std::to_string(a) + "[u]", "c", false);
+                    o << "        }\n      }\n";
+                    o << "      _Pragma(\"unroll\") for (int u = 0; u < UNROLL; ++u) {\n";
+                    o << "        const int c = cb + u * TROW * VEC;\n        if (c < " << hi << ") {\n";
+                    g.ind = "          ";
+                    g.c = "c";
+                    g.skip_loads = true;
+                    g.hoist_idx = "[u]";
+                    emit_group(q, need, g);
+                    o << "        }\n      }\n    }\n";
+                } else {
+                    o << "    if (rv) for (int c = " << lo << " + lane * VEC; c < " << hi << "; c += TROW * VEC) {\n";
+                    g.ind = "      ";
+                    g.c = "c";
+                    emit_group(q, need, g);
+                    o << "    }\n";
+                }
             }
             // combine across the T threads of the row
             for (int si : sinks) {
@@ -733,7 +768,16 @@ struct Gen {
                 if (s.kind != S_RED && s.kind != S_ARGRED) continue;
                 const std::string buf = T > 32 ? "sm" + std::to_string(si) + "[parity]" : "nullptr";
                 const std::string bufT = T > 32 ? buf : "(" + acc_type(s) + "*)nullptr";
-                if (s.kind == S_RED)
+                if (clustered) {
+                    // the CTA's slice first, then the slices of the cluster's CTAs in rank order
+                    const std::string slots = "cx" + std::to_string(si) + "[parity]";
+                    if (s.kind == S_RED)
+                        o << "    const " << ct(s.dtype) << " " << vn(s.id) << " = cluster_fold<" << red_struct(s.name) << ", CL>(row_reduce<"
+                          << red_struct(s.name) << ", TROW>(acc" << si << ", " << bufT << "), " << slots << ", cl_rank);\n";
+                    else
+                        o << "    const int " << vn(s.id) << " = (int)cluster_arg_fold<" << red_struct(s.name) << ", CL>(row_arg_reduce<"
+                          << red_struct(s.name) << ", TROW>(acc" << si << ", " << bufT << "), " << slots << ", cl_rank).i;\n";
+                } else if (s.kind == S_RED)
                     o << "    const " << ct(s.dtype) << " " << vn(s.id) << " = row_reduce<" << red_struct(s.name)
                       << ", TROW>(acc" << si << ", " << bufT << ");\n";
                 else

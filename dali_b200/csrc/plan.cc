@@ -337,6 +337,29 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
         int rpc = v.threads / T;
         long long gx = (R + rpc - 1) / rpc;
         out.grid_x = (unsigned)std::min<long long>(gx, (long long)kSMs * env_int("DALI_B200_ROW_CTAS_PER_SM", 32));
+        // Few rows, each far too long for one CTA's registers: a thread-block cluster shares every row (see codegen).
+        // As many rows are in flight as fit L2 together (a softmax reads its row three times: the second and third
+        // pass then come from L2), and the cluster is made as wide as it takes to put those rows on every SM.
+        // Measured (softmax, fp32): [9,1M] 185 -> 35 us, [32,2M] 558 -> 277 us, [64,1M] 312 -> 207 us, [150,256K] 115 -> 104 us;
+        // with as many rows as SMs one CTA per row is as good ([300,128K]) or better ([1000,64K]).
+        if (!cached && v.nin == 1 && T >= 512 && !p.has_indirect && 2 * R <= 3 * kSMs && env_int("DALI_B200_ROW_CLUSTER", 1)) {
+            long long row_bytes = 0;
+            for (int a = 0; a < nargs; ++a)
+                if (arg_elem(a)) row_bytes += C * dtype_size(p.args[a].dtype);
+            long long in_flight = std::max<long long>(1, std::min<long long>(R, ((long long)env_int("DALI_B200_ROW_CLUSTER_L2_MB", 32) << 20) / std::max<long long>(1, row_bytes)));
+            in_flight = std::max<long long>(in_flight, std::min<long long>(R, (kSMs + 15) / 16));   // rows beyond L2's reach: fill the machine at least
+            int cl = 1;
+            while (cl < 16 && in_flight * cl * 2 <= 2 * kSMs) cl <<= 1;
+            cl = env_int("DALI_B200_ROW_CLUSTER_SIZE", cl);
+            if (cl >= 2 && C >= (long long)cl * 4096) {
+                v.cluster = cl;
+                v.T = T = 512;
+                v.threads = 512;
+                rpc = 1;
+                out.cluster = (unsigned)cl;
+                out.grid_x = (unsigned)(in_flight * cl);
+            }
+        }
         if (stage && cached && T == 32) {
             // 8 warps per CTA; the rings of a CTA: operands x 8 warps x stage x one padded row
             v.threads = env_int("DALI_B200_ROW_THREADS", 256);
@@ -355,7 +378,10 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
                 out.grid_x = (unsigned)std::min<long long>(gx, (long long)kSMs * env_int("DALI_B200_ROW_STAGE_CTAS", (int)per_sm));
             }
         }
-        v.unroll = 1; v.tx = 0; v.ty = 0;
+        // (streamed rows: hoisting the loads of 2-8 groups ahead of their use -- DALI_B200_ROW_UNROLL -- measured slower
+        // than the plain loop on [64,1M] and [150,256K] softmaxes, 0.25 and 0.20 ms against 0.21 and 0.115 ms)
+        v.unroll = (!cached && v.nin == 1) ? env_int("DALI_B200_ROW_UNROLL", 1) : 1;
+        v.tx = 0; v.ty = 0;
     } else if (v.kind == K_ALL) {
         v.threads = env_int("DALI_B200_ALL_THREADS", 256);
         v.unroll = env_int("DALI_B200_ALL_UNROLL", 4);

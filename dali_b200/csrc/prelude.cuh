@@ -285,6 +285,40 @@ template <typename Op, int T_, typename T> DEV ArgPair<T> row_arg_reduce(ArgPair
     return r;
 }
 
+// A row shared by the CTAs of a thread-block cluster (the row skeleton's `cluster` variant): every CTA reduces its
+// slice of the columns, stores the partial result into slot [its rank] of EVERY CTA of the cluster through distributed
+// shared memory, the cluster meets at its hardware barrier (no spinning: the CTAs of a cluster are co-scheduled), and
+// every CTA folds the slots in rank order -- the same order everywhere, so all CTAs continue with the same bits.
+DEV unsigned cluster_rank() { unsigned r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+DEV void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+template <typename T> DEV void cluster_store(T* local_slot, unsigned target, const T& v) {
+    unsigned remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((unsigned)__cvta_generic_to_shared(local_slot)), "r"(target));
+    const unsigned* w = reinterpret_cast<const unsigned*>(&v);
+#pragma unroll
+    for (int i = 0; i < (int)(sizeof(T) / 4); ++i)
+        asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(remote + 4u * i), "r"(w[i]) : "memory");
+}
+template <typename Op, int CL, typename T> DEV T cluster_fold(T partial, T* slots, unsigned rank) {
+    if (threadIdx.x < CL) cluster_store(&slots[rank], threadIdx.x, partial);
+    cluster_barrier();
+    T r = slots[0];
+#pragma unroll
+    for (int q = 1; q < CL; ++q) r = Op::apply(r, slots[q]);
+    return r;
+}
+template <typename Op, int CL, typename T> DEV ArgPair<T> cluster_arg_fold(ArgPair<T> partial, ArgPair<T>* slots, unsigned rank) {
+    if (threadIdx.x < CL) cluster_store(&slots[rank], threadIdx.x, partial);
+    cluster_barrier();
+    ArgPair<T> r = slots[0];
+#pragma unroll
+    for (int q = 1; q < CL; ++q) r = arg_merge<Op, T>(r, slots[q]);
+    return r;
+}
+
 // Whole-CTA reduction (NT threads, NT a multiple of 32); result valid in every
 // thread.  `buf` holds NT/32 entries.
 template <typename Op, int NT, typename T> DEV T block_reduce(T v, T* buf) { return row_reduce<Op, NT>(v, buf); }

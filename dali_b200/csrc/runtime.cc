@@ -401,27 +401,47 @@ static int do_launch(uint64_t hash, int device, void* stream, const int64_t* spa
     typedef CUresult (*LaunchExFn)(const CUlaunchConfig*, CUfunction, void**, void**);
     static LaunchExFn launch_ex = reinterpret_cast<LaunchExFn>(driver_entry("cuLaunchKernelEx"));
     CUresult r;
-    if (plan.smem_bytes > 48 * 1024) {
+    if (plan.smem_bytes > 32 * 1024) {      // (the kernel's static shared memory counts towards the 48 KiB default limit too)
         static CUresult (*set_attr)(CUfunction, CUfunction_attribute, int) =
             reinterpret_cast<CUresult (*)(CUfunction, CUfunction_attribute, int)>(driver_entry("cuFuncSetAttribute"));
         if (!set_attr) { set_error("cuFuncSetAttribute unavailable"); return DALIB200_ERR_CUDA; }
         r = set_attr(fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)plan.smem_bytes);
         if (r != CUDA_SUCCESS) { set_error("cuFuncSetAttribute(max dynamic smem): " + cu_err(r)); return DALIB200_ERR_CUDA; }
     }
-    if (launch_ex && dependent_launch_enabled()) {
+    if (plan.cluster > 8) {
+        static CUresult (*set_attr2)(CUfunction, CUfunction_attribute, int) =
+            reinterpret_cast<CUresult (*)(CUfunction, CUfunction_attribute, int)>(driver_entry("cuFuncSetAttribute"));
+        if (!set_attr2 || set_attr2(fn, CU_FUNC_ATTRIBUTE_NON_PORTABLE_CLUSTER_SIZE_ALLOWED, 1) != CUDA_SUCCESS) {
+            set_error("clusters of more than 8 CTAs are not available on this device");
+            return DALIB200_ERR_CUDA;
+        }
+    }
+    if (plan.cluster > 1 && !launch_ex) { set_error("cuLaunchKernelEx unavailable: cannot launch a thread-block cluster"); return DALIB200_ERR_CUDA; }
+    if (launch_ex && (dependent_launch_enabled() || plan.cluster > 1)) {
         // programmatic dependent launch: every generated kernel begins with griddepcontrol.wait (prelude: kernel_entry)
-        CUlaunchAttribute attr;
-        std::memset(&attr, 0, sizeof attr);
-        attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
-        attr.value.programmaticStreamSerializationAllowed = 1;
+        CUlaunchAttribute attrs[2];
+        std::memset(attrs, 0, sizeof attrs);
+        unsigned n_attrs = 0;
+        if (dependent_launch_enabled()) {
+            attrs[n_attrs].id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+            attrs[n_attrs].value.programmaticStreamSerializationAllowed = 1;
+            ++n_attrs;
+        }
+        if (plan.cluster > 1) {
+            attrs[n_attrs].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+            attrs[n_attrs].value.clusterDim.x = plan.cluster;
+            attrs[n_attrs].value.clusterDim.y = 1;
+            attrs[n_attrs].value.clusterDim.z = 1;
+            ++n_attrs;
+        }
         CUlaunchConfig cfg;
         std::memset(&cfg, 0, sizeof cfg);
         cfg.gridDimX = plan.grid_x; cfg.gridDimY = plan.grid_y; cfg.gridDimZ = 1;
         cfg.blockDimX = (unsigned)plan.variant.threads; cfg.blockDimY = 1; cfg.blockDimZ = 1;
         cfg.sharedMemBytes = plan.smem_bytes;
         cfg.hStream = (CUstream)stream;
-        cfg.attrs = &attr;
-        cfg.numAttrs = 1;
+        cfg.attrs = attrs;
+        cfg.numAttrs = n_attrs;
         r = launch_ex(&cfg, fn, params, nullptr);
     } else {
         r = g_drv.LaunchKernel(fn, plan.grid_x, plan.grid_y, 1, (unsigned)plan.variant.threads, 1, 1, plan.smem_bytes, (CUstream)stream,

@@ -25,6 +25,7 @@ struct LaunchPlan {
     unsigned grid_x = 1, grid_y = 1;
     size_t scratch_bytes = 0;       // cross-CTA exchange space this launch needs
     size_t counters = 0;            // ticket counters this launch needs
+    unsigned cluster = 0;           // CTAs per thread-block cluster (0 / 1: none)
     unsigned smem_bytes = 0;        // dynamic shared memory (the staged row variant's rings)
     bool empty = false;             // nothing to do (zero-sized space)
     std::string describe() const;

@@ -389,3 +389,38 @@ def test_rows_staged_through_shared_memory_by_bulk_copies(lib, monkeypatch):
     lib.launch(lib.compile(softmax_ir()), (2400, 512), [out, d], strides=[None, [516, 1]], offsets=[0, 1])
     assert ".stage" not in lib.last_variant()
     np.testing.assert_allclose(host(out), oracle.softmax(np.ascontiguousarray(a[:, 1:513])), rtol=1e-5, atol=1e-9)
+
+
+@pytest.mark.parametrize("shape", [(20, 200000), (9, 300001), (150, 65536), (3, 1 << 20)])
+def test_few_long_rows_shared_by_a_thread_block_cluster(lib, shape):
+    """Rows too long for one CTA's registers and too few to fill the machine one CTA each: the row skeleton's `cluster`
+    variant gives every row to a thread-block cluster, each CTA a slice of the columns, partial results exchanged through
+    distributed shared memory and folded in rank order.  Softmax, sum, max and argmax (first occurrence across the
+    CTAs' slices) against the oracle; rows whose length is not a multiple of the cluster's slices."""
+    import dali_oracle as oracle
+    from dali_b200.ir import softmax_ir
+    rows, cols = shape
+    rng = np.random.default_rng(rows + cols)
+    a = rng.standard_normal((rows, cols)).astype(np.float32)
+    a[0, cols - 7] = a[0, 11] = 9.5                       # a tie between the first and the last slice
+    d = dev(a)
+    out = torch.empty((rows, cols), device="cuda")
+    lib.launch(lib.compile(softmax_ir()), (rows, cols), [out, d])
+    assert ".cl" in lib.last_variant(), lib.last_variant()
+    # (held to the fp64 softmax: the reference's own sequential fp32 sum over rows this long is 1e-4 off)
+    e = np.exp(a.astype(np.float64) - a.max(1, keepdims=True))
+    np.testing.assert_allclose(host(out), e / e.sum(1, keepdims=True), rtol=1e-5, atol=1e-12)
+    for kind in ("sum", "max"):
+        o = torch.empty(rows, device="cuda")
+        lib.launch(lib.compile(reduce_ir(kind, "f32", 2, 1)), (rows, cols), [o, d])
+        assert ".cl" in lib.last_variant(), lib.last_variant()
+        if kind == "max":
+            np.testing.assert_array_equal(host(o), a.max(1))
+        else:
+            want, bound = oracle.sum_f64acc(a, 1)
+            assert np.all(np.abs(host(o) - want) <= 1e-5 * bound)
+    o = torch.empty(rows, device="cuda", dtype=torch.int32)
+    lib.launch(lib.compile(reduce_ir("max", "f32", 2, 1, True)), (rows, cols), [o, d])
+    got = host(o)
+    np.testing.assert_array_equal(got, oracle.argreduce("max", a, 1))
+    assert got[0] == 11
