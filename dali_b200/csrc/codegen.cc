@@ -25,6 +25,9 @@ std::string Variant::key() const {
     if (xrank) s << ".xrank";
     if (stage) s << ".stage" << stage;
     if (cluster > 1) s << ".cl" << cluster;
+    if (minb) s << ".mb" << minb;
+    if (xv.find('1') != std::string::npos) s << ".xv" << xv;
+    if (stream_out) s << ".cs";
     return s.str();
 }
 
@@ -136,7 +139,8 @@ struct Gen {
         o << "// dali_b200 generated kernel: " << v.key() << "\n";
         o << "struct P { long long w[" << L.total << "]; };\n";
         o << "#define NT " << v.threads << "\n#define VEC " << v.vec << "\n#define UNROLL " << v.unroll << "\n";
-        o << "extern \"C\" __global__ void __launch_bounds__(NT) dali_kernel(const __grid_constant__ P p) {\n";
+        if (v.minb) o << "extern \"C\" __global__ void __launch_bounds__(NT, " << v.minb << ") dali_kernel(const __grid_constant__ P p) {\n";
+        else o << "extern \"C\" __global__ void __launch_bounds__(NT) dali_kernel(const __grid_constant__ P p) {\n";
         o << "  kernel_entry();\n";
         o << "  const i64 R = " << W(L.w_R) << "; const i64 C = " << W(L.w_C) << ";\n";
         o << "  const int tid = threadIdx.x;\n";
@@ -303,7 +307,8 @@ struct Gen {
         const std::string T = argT(a);
         char k = v.nin > 1 ? 's' : v.cls[a];
         if (v.vec > 1 && k == 'u') {
-            o << ind << "vstore<" << T << ", VEC>(a" << a << " + ro" << a << " + " << c << ", " << src << ");\n";
+            // (stream_out: stores that do not displace a gather's table from L2 -- opt-in, see plan.cc)
+            o << ind << (v.stream_out ? "vstore_stream<" : "vstore<") << T << ", VEC>(a" << a << " + ro" << a << " + " << c << ", " << src << ");\n";
         } else if (v.nin > 1) {
             o << ind << "a" << a << "[ro" << a << " + co" << a << "] = " << src << ".x[0];\n";
         } else if (k == 'z') {
@@ -347,6 +352,21 @@ struct Gen {
         for (const Stmt& s : p.stmts)
             if (s.id >= 0 && need.count(s.id) && s.kind == S_OP && (s.name == "rng_uniform" || s.name == "rng_normal"))
                 o << ind << "RngBlock rb" << s.id << " = {0u, {0u, 0u, 0u, 0u}, 0};\n";
+        // A gathered row read with full-width loads: every lane of the vector group uses the same index (the index
+        // operand does not vary along the inner dim) and the row is aligned, so the group is one 128-bit load of the
+        // indexed row instead of VEC scalar ones (dali/array/op/gather.cpp:45-65 reads element by element).
+        std::set<int> vector_gathers;
+        if (v.vec > 1 && v.nin == 1 && !g.cached)
+            for (const Stmt& s : p.stmts) {
+                if (s.id < 0 || !need.count(s.id) || s.kind != S_LDX) continue;
+                const Stmt& ix = val(s.in[0]);
+                if ((int)v.xv.size() <= s.arg || v.xv[s.arg] != '1' || ix.kind != S_LD || !arg_elem(s.arg) || !arg_elem(ix.arg) ||
+                    v.cls[ix.arg] != 'z' || !largs.count(ix.arg))
+                    continue;
+                o << ind << "const Vec<" << argT(s.arg) << ", VEC> gx" << s.id << " = vload<" << argT(s.arg) << ", VEC>(a" << s.arg << " + ro"
+                  << s.arg << " + " << col_off(s.arg, g.c) << " + (i64)" << argvec(ix.arg) << ".x[0] * " << W(L.arg_xs(s.arg)) << ");\n";
+                vector_gathers.insert(s.id);
+            }
         o << ind << "_Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) {\n";
         const std::string in2 = ind + "  ";
         for (int id : g.cuts_rd) {
@@ -358,6 +378,8 @@ struct Gen {
             if (s.id < 0 || !need.count(s.id)) continue;
             if (s.kind == S_LD) {
                 o << in2 << "const " << ct(s.dtype) << " " << vn(s.id) << " = " << argvec(s.arg) << ".x[j];\n";
+            } else if (s.kind == S_LDX && vector_gathers.count(s.id)) {
+                o << in2 << "const " << ct(s.dtype) << " " << vn(s.id) << " = gx" << s.id << ".x[j];\n";
             } else if (s.kind == S_LDX) {
                 o << in2 << "const " << ct(s.dtype) << " " << vn(s.id) << " = a" << s.arg << "[ro" << s.arg << " + "
                   << (arg_elem(s.arg) ? col_off(s.arg, g.c + " + j") : std::string("0")) << " + (i64)" << vn(s.in[0])

@@ -44,11 +44,14 @@ struct Variant {
     int tx = 32, ty = 8;     // col: threads along outer / along the reduced dim
     int stage = 0;           // row, T = 32: every warp keeps a ring of `stage` rows in flight, copied into shared memory by
                              // bulk asynchronous copies (cp.async.bulk + mbarrier) ahead of the rows it works on
+    int minb = 0;            // col: CTAs per SM the grid was sized for; the kernel is compiled to fit that many (__launch_bounds__)
     int cluster = 0;         // row, streaming: a thread-block cluster of this many CTAs shares every row (each a slice of the
                              // columns), partial results meet through distributed shared memory
     bool xrank = false;      // all: partial results are exchanged with the other ranks before the kernel finishes
     int tile = 0;            // map with operands of class 't': 32 / 64 = edge of the shared-memory tiles they are read through, 4 = 4 x 4 register blocks (128-bit accesses), 0 = none
     std::string cls;         // per arg inner-stride class: u(nit) z(ero) s(trided) t(ransposed: unit stride along the OUTER dim)
+    bool stream_out = false; // map with a gather: element stores are streaming stores (evict-first in L2)
+    std::string xv;          // per arg: '1' = an indirectly read arg whose rows can be fetched with full-width vector loads
     std::string ocls;        // col: per arg outer-stride class
     std::string key() const; // text folded into the cache key
     const char* kind_name() const;

@@ -1,9 +1,10 @@
 // dalib200_sum_f32_noalloc: all-axis fp32 sum that allocates nothing.
 //
 // For callers that are not allowed to allocate device memory when they call
-// into this library: code running inside a CUDA-graph stream capture, a
-// real-time or interrupt-like host thread that must not take the allocator's
-// locks, or an embedding whose memory budget is fixed at load time.  The
+// into this library: a real-time or interrupt-like host thread that must not
+// take the allocator's locks or wait for the driver, an embedding whose memory
+// budget is fixed at load time, code that runs after the process has handed
+// all remaining device memory to something else.  The
 // regular path (dalib200_launch on an all-axis reduction) takes its cross-CTA
 // exchange space from an arena that grows with cudaMalloc on first use; this
 // entry point keeps that space in a fixed array inside the library image
@@ -27,6 +28,7 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kMaxCtas = 2048;                       // partials the scratch array can hold
+constexpr int kLaunchCtas = 148 * 8;                 // CTAs launched at most: one full wave of 256-thread CTAs on 148 SMs
 constexpr int kUnroll = 4;
 constexpr size_t kPartialBytes = kMaxCtas * sizeof(float);
 constexpr size_t kScratchBytes = kPartialBytes + 256;   // + one 256-byte line for the ticket counter
@@ -136,7 +138,8 @@ extern "C" int dalib200_sum_f32_noalloc(int device, void* stream, const float* x
     long long per_cta = (long long)kThreads * kUnroll * 4;
     long long ctas = (n + per_cta - 1) / per_cta;
     if (ctas < 1) ctas = 1;
-    if (ctas > kMaxCtas) ctas = kMaxCtas;
+    if (ctas > kLaunchCtas) ctas = kLaunchCtas;
+    static_assert(kLaunchCtas <= kMaxCtas, "one partial per launched CTA must fit the scratch array");
     sum_f32_noalloc_kernel<<<(unsigned)ctas, kThreads, 0, s>>>(x, (long long)n, out, partials, counter);
     e = cudaGetLastError();
     if (e != cudaSuccess) { dalib::set_error(std::string("sum_f32_noalloc_kernel launch: ") + cudaGetErrorString(e)); return DALIB200_ERR_CUDA; }

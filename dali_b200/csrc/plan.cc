@@ -230,6 +230,17 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
         }
     }
     v.vec = vec;
+    // indirectly read args (gather sources) whose indexed rows can be fetched with full-width vector loads
+    v.xv.assign(nargs, '0');
+    v.stream_out = v.kind == K_MAP && p.has_indirect && env_int("DALI_B200_GATHER_STREAM", 0);
+    // (opt-in: on 2^20 rows of 1 KiB gathered from a 64 MiB table the kernel is bound by the 1 GiB it writes -- 292 us with
+    // scalar gathers and plain stores, 326 us with 128-bit gathers, 314-320 us with streaming stores, DALI_B200_GATHER_STREAM)
+    if (vec > 1 && v.kind != K_COL && v.nin == 1 && env_int("DALI_B200_GATHER_VEC", 0))
+        for (int a = 0; a < nargs; ++a) {
+            if (!p.args[a].indirect || p.args[a].written || p.args[a].iota || !arg_elem(a)) continue;
+            const long long xs = strides && strides[a] ? strides[a][rank] : 1;
+            if (v.cls[a] == 'u' && xs % vec == 0 && aligned(a, vec, false) && dtype_size(p.args[a].dtype) * vec >= 8) v.xv[a] = '1';
+        }
 
     // ---------------------------------------------------------------- geometry
     long long aux0 = 0, aux1 = 0;
@@ -401,7 +412,15 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
         v.threads = v.tx * v.ty;
         v.unroll = env_int("DALI_B200_COL_UNROLL", 8);
         long long tiles = (R + (long long)v.tx * vec - 1) / ((long long)v.tx * vec);
-        long long S = ((long long)kSMs * env_int("DALI_B200_COL_CTAS_PER_SM", 8) + tiles - 1) / tiles;
+        // The grid is one wave: every SM holds `per_sm` CTAs for the whole launch.  A plain reduction is compiled to fit 8
+        // per SM (32 registers; without the bound max took 40 and its 1184 CTAs ran as a wave of 888 and a tail); an
+        // arg-reduction carries (value, 64-bit position) pairs and is sized for 5 per SM, what its 46 registers allow.
+        bool has_arg = false;
+        for (const Stmt& st_ : p.stmts) has_arg = has_arg || st_.kind == S_ARGRED;
+        int per_sm = env_int("DALI_B200_COL_CTAS_PER_SM", has_arg ? 5 : 8);
+        if (v.threads == 256 && p.stmts.size() <= 6) v.minb = per_sm;
+        long long S = has_arg ? std::max<long long>(1, (long long)kSMs * per_sm / tiles)
+                              : ((long long)kSMs * per_sm + tiles - 1) / tiles;
         long long maxS = std::max<long long>(1, C / (v.ty * 8));
         S = std::max<long long>(1, std::min<long long>(std::min<long long>(S, maxS), 256));
         long long per = (C + S - 1) / S;

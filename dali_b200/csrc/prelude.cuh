@@ -377,6 +377,12 @@ DEV void stage_wait(unsigned long long* bar, unsigned parity) {
 template <typename T, int N> struct alignas(sizeof(T) * N) Vec { T x[N]; };
 template <typename T, int N> DEV Vec<T, N> vload(const T* p) { return *reinterpret_cast<const Vec<T, N>*>(p); }
 template <typename T, int N> DEV void vstore(T* p, const Vec<T, N>& v) { *reinterpret_cast<Vec<T, N>*>(p) = v; }
+// the same as a streaming store (evict-first in L2): for outputs that are not read again while something else should stay cached
+template <typename T, int N> DEV void vstore_stream(T* p, const Vec<T, N>& v) {
+    if (sizeof(T) * N == 16) __stcs(reinterpret_cast<uint4*>(p), *reinterpret_cast<const uint4*>(&v));
+    else if (sizeof(T) * N == 8) __stcs(reinterpret_cast<uint2*>(p), *reinterpret_cast<const uint2*>(&v));
+    else *reinterpret_cast<Vec<T, N>*>(p) = v;
+}
 
 // Counter-based random numbers: Philox4x32-10 (Salmon et al., SC'11) with counter = (block, 0, 0, 0)
 // and key = (seed, 0); which block and words an element reads is stated at RngBlock below.  Replaces the thrust generators the reference seeds per

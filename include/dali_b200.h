@@ -44,7 +44,8 @@ enum dalib200_status {
 };
 
 /* element types.  0..2 are the reference's DType values
- * (dali/array/dtype.h:6-10); bf16 exists only as a GEMM operand/output. */
+ * (dali/array/dtype.h:6-10); bf16 is a storage type: kernel arguments and GEMM
+ * operands may be bf16, loads widen to fp32 exactly and stores round to nearest even. */
 enum dalib200_dtype {
     DALIB200_F32 = 0,
     DALIB200_F64 = 1,
@@ -257,9 +258,9 @@ int dalib200_scan(int device, void* stream, int dtype, int op, int inclusive,
  *
  * *out = sum of the n fp32 elements at x (device pointers), asynchronous on
  * `stream` -- the all-axis reduction of dalib200_launch, for callers that may
- * not allocate device memory at call time: a thread inside a CUDA-graph stream
- * capture, a latency-critical host thread that must stay away from allocator
- * locks, an embedding with a memory budget fixed at load time.  The cross-CTA
+ * not allocate device memory at call time: a latency-critical host thread that
+ * must stay away from allocator locks and driver calls that can block, an
+ * embedding with a memory budget fixed at load time.  The cross-CTA
  * exchange space lives in a fixed 8.25 KiB array inside the library image
  * (every GPU that loads the library holds it until exit); the call performs no
  * cudaMalloc / cudaFree and calls no allocating library routine.

@@ -1,6 +1,6 @@
 """dalib200_sum_f32_noalloc: the all-axis sum for callers that cannot allocate
-device memory at call time (inside a stream capture, on a latency-critical host
-thread, under a fixed memory budget).  Its exchange space is a fixed array in
+device memory at call time (a latency-critical host thread that must not take
+allocator locks, an embedding under a memory budget fixed at load time).  Its exchange space is a fixed array in
 the library image instead of the growable arena of dalib200_launch.
 
 Checked through the C ABI against the regular entry point (the generated
