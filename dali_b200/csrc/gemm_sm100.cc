@@ -394,7 +394,7 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
     static const std::string source_tag =
         std::string("|sm_100a|gemm|") +
 #include "source_hash.inc"
-        + "|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" + std::to_string(fnv1a(device_prelude()));
+        + "|" + std::to_string(fnv1a(kGemmSkeleton)) + "|" + std::to_string(fnv1a(device_prelude())) + "|" + nvrtc_defines_text();
     std::ostringstream key;
     key << std::hex << epilogue_hash << "_" << fnv1a(v.key() + source_tag);
     tl_gemm_variant = std::string(bf16 ? "tcgen05.bf16 " : "tcgen05.tf32x3 ") + v.key() + (n_pairs > 1 ? " x2" : "");

@@ -90,16 +90,26 @@ DEV int f_inv(int a) { return 1 / a; }
 // special-function pipe, not by HBM, with the libdevice versions.
 DEV float fast_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 DEV float fast_rcp(float x) { float y; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
-// 1 / y for y in [1, 2^127) on the FMA pipe: an exponent-flipping first guess (10 % off) and two cubic
-// steps r += r (e + e^2), e = 1 - y r, good to ~1.5e-7 relative.  A fused chain whose every element needs
-// two ex2 and a reciprocal is bound by the special-function unit (16 lanes per SM per clock); taking the
-// reciprocal off that unit leaves two operations per element on it.
+// 1 / y for y in [1, 2^127) on the FMA pipe: an exponent-flipping first guess (at most 5.06 % off), one cubic step
+// r += r (e + e^2), e = 1 - y r (error e^3 = 1.3e-4) and one Newton step r += r e (error squared): within 7.7e-8
+// relative over every mantissa.  A fused chain whose every element needs two ex2 and a reciprocal is bound by the
+// special-function unit (16 lanes per SM per clock); taking the reciprocal off that unit leaves two operations per
+// element on it.  (DALI_RCP_MUFU: the special-function reciprocal instead, one instruction; DALI_RCP_TWO_CUBIC: a second
+// cubic step in place of the Newton step, one more instruction for 6.0e-8.)
 DEV float rcp_ge1(float y) {
+#ifdef DALI_RCP_MUFU
+    return fast_rcp(y);
+#else
     float r = __int_as_float(0x7EF311C7 - __float_as_int(y));
     float e = fmaf(-y, r, 1.0f);
     r = fmaf(r, fmaf(e, e, e), r);
     e = fmaf(-y, r, 1.0f);
+#ifdef DALI_RCP_TWO_CUBIC
     return fmaf(r, fmaf(e, e, e), r);
+#else
+    return fmaf(r, e, r);
+#endif
+#endif
 }
 DEV float f_exp(float a) { return fast_ex2(a * 1.4426950408889634f); }
 DEV double f_exp(double a) { return exp(a); }
@@ -133,9 +143,13 @@ DEV int f_safe_entropy_log(int a) { return (int)f_safe_entropy_log((double)a); }
 
 // 1 / (1 + exp(-a)): the denominator is in [1, inf], where the approximate
 // reciprocal is within 1 ulp and needs no slow path.
-// (the exponent is clamped so that 1 + 2^t stays finite; the clamp is a comparison, not fminf, so that a NaN operand
-// stays NaN as in the reference's 1 / (1 + exp(-a)): fminf would return the other operand)
+// (the exponent is clamped so that 1 + 2^t stays finite; the clamp is min.NaN, one instruction that keeps a NaN operand
+// NaN as the reference's 1 / (1 + exp(-a)) does: fminf would return the other operand)
+#ifdef DALI_SIGMOID_SELECT
 DEV float sigmoid_exponent(float t) { return t > 126.0f ? 126.0f : t; }
+#else
+DEV float sigmoid_exponent(float t) { float y; asm("min.NaN.f32 %0, %1, 0f42FC0000;" : "=f"(y) : "f"(t)); return y; }
+#endif
 DEV float f_sigmoid(float a) { return rcp_ge1(1.0f + fast_ex2(sigmoid_exponent(a * -1.4426950408889634f))); }
 DEV double f_sigmoid(double a) { return 1.0 / (1.0 + exp(-a)); }
 DEV int f_sigmoid(int a) { return (int)(1.0 / (1.0 + exp((double)-a))); }

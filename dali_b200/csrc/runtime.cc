@@ -54,6 +54,26 @@ uint64_t fnv1a(const std::string& s, uint64_t h) {
 }
 
 // ------------------------------------------------------------------ NVRTC
+// DALI_B200_DEFINES="A,B=2": macros handed to every generated kernel (tuning switches of the device prelude).  The text
+// is part of the kernel cache key.
+std::string nvrtc_defines_text() {
+    const char* e = std::getenv("DALI_B200_DEFINES");
+    return e ? std::string(e) : std::string();
+}
+static std::vector<std::string> nvrtc_defines() {
+    std::vector<std::string> out;
+    std::string text = nvrtc_defines_text(), cur;
+    for (size_t i = 0; i <= text.size(); ++i) {
+        if (i == text.size() || text[i] == ',') {
+            if (!cur.empty()) out.push_back("-D" + cur);
+            cur.clear();
+        } else if (text[i] != ' ') {
+            cur.push_back(text[i]);
+        }
+    }
+    return out;
+}
+
 bool nvrtc_compile(const std::string& source, const std::string& name,
                    std::vector<char>* cubin, std::string* log) {
     nvrtcProgram prog;
@@ -61,8 +81,10 @@ bool nvrtc_compile(const std::string& source, const std::string& name,
     if (r != NVRTC_SUCCESS) { *log = std::string("nvrtcCreateProgram: ") + nvrtcGetErrorString(r); return false; }
     const char* arch = std::getenv("DALI_B200_ARCH");
     std::string arch_opt = std::string("--gpu-architecture=") + (arch && *arch ? arch : "sm_100a");
-    const char* opts[] = {arch_opt.c_str(), "--std=c++17", "-lineinfo", "--extra-device-vectorization"};
-    r = nvrtcCompileProgram(prog, 4, opts);
+    std::vector<std::string> defines = nvrtc_defines();
+    std::vector<const char*> opts = {arch_opt.c_str(), "--std=c++17", "-lineinfo", "--extra-device-vectorization"};
+    for (const std::string& d : defines) opts.push_back(d.c_str());
+    r = nvrtcCompileProgram(prog, (int)opts.size(), opts.data());
     size_t log_size = 0;
     nvrtcGetProgramLogSize(prog, &log_size);
     if (log_size > 1) {
@@ -190,7 +212,7 @@ static std::string kernel_key(uint64_t hash, const Variant& v) {
     // the device prelude is part of every kernel: its text is part of the key
     static const uint64_t prelude_hash = fnv1a(kPrelude);
     k << std::hex << hash << "_" << fnv1a(v.key() + "|sm_100a|" + kCodegenVersion + "|abi" +
-                                            std::to_string(DALIB200_ABI_VERSION) + "|" + std::to_string(prelude_hash));
+                                            std::to_string(DALIB200_ABI_VERSION) + "|" + std::to_string(prelude_hash) + "|" + nvrtc_defines_text());
     return k.str();
 }
 

@@ -40,6 +40,7 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
                  LaunchPlan* plan, std::string* err);
 
 // NVRTC: CUDA C++ -> sm_100a cubin.  Works without a GPU.
+std::string nvrtc_defines_text();      // DALI_B200_DEFINES: macros handed to every generated kernel; part of the cache keys
 bool nvrtc_compile(const std::string& source, const std::string& name,
                    std::vector<char>* cubin, std::string* log);
 

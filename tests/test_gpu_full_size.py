@@ -80,3 +80,21 @@ def test_config5_chain_sum_is_the_sum_of_its_parts(lib):
     chunk = torch.zeros(1, device="cuda")
     lib.launch(h, (1 << 24,), [chunk, x[:1 << 24]], scalars=[w, b])
     assert abs(float(chunk) - ref) <= 1e-5 * ref
+
+
+def test_config3_nine_reductions_on_uniform_8192_through_arrays():
+    """sum / max / argmax over axis -1, axis 0 and all axes of fp32 [8192,8192] ~ U(-1,1), evaluated through the Array front end,
+    against the oracle: sums within 1e-5 * sum|x| of the double-accumulated sum, max exactly, argmax bit-exact."""
+    import dali_oracle as oracle
+    from dali_b200.array import Array, op, last_variant
+    x = (np.random.default_rng(1236).random((N, N)) * 2 - 1).astype(np.float32)
+    X = Array(x)
+    for axis, skeleton in ((-1, "row."), (0, "col."), (None, "all.")):
+        axes = None if axis is None else [axis]
+        got = op.sum(X, axes).numpy().reshape(-1)
+        assert last_variant().startswith(skeleton)
+        s64, sabs = oracle.sum_f64acc(x, axis)
+        assert np.all(np.abs(got - s64.reshape(-1)) <= 1e-5 * sabs.reshape(-1))
+        np.testing.assert_array_equal(op.max(X, axes).numpy().reshape(-1), oracle.reduce("max", x, axis).reshape(-1))
+        am = op.argmax(X) if axis is None else op.argmax(X, axis)
+        np.testing.assert_array_equal(am.numpy().reshape(-1), oracle.argreduce("max", x, axis).reshape(-1))
