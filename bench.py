@@ -1018,6 +1018,10 @@ def measure(wl, torch, world, steps, warmup, lib, local=0, min_blocks=5, clock_s
     barrier()
     fn = wl.graph_fn()
     stepper = GraphStepper(torch, lambda i, st: fn(warmup + i, st), steps, getattr(wl, "lanes", 1)) if fn else None
+    # the clock sampler starts here, ahead of the spin-up: spawning it takes milliseconds, in which an idle GPU would drop
+    # out of the state the warm-up put it in; the timed block below follows the last untimed replay by one barrier only
+    sampler = ClockSampler(local)
+    sampler.start()
     if stepper:
         barrier()
         t_spin = time.perf_counter()
@@ -1037,8 +1041,6 @@ def measure(wl, torch, world, steps, warmup, lib, local=0, min_blocks=5, clock_s
             for _ in range(min(2000, int(0.15 / est) + 1)):
                 stepper.replay()
     barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
     block_ms = []
 
     def one_block():
@@ -1055,6 +1057,11 @@ def measure(wl, torch, world, steps, warmup, lib, local=0, min_blocks=5, clock_s
         barrier()
         block_ms.append(ev0.elapsed_time(ev1))
 
+    if stepper:
+        # the last of the warm-up is one block issued exactly like the timed ones (events, one replay, a barrier): the
+        # first block after the long back-to-back spin-up measured a fixed 15-40 us longer than every later one
+        one_block()
+        block_ms.clear()
     one_block()        # the reported block: exactly `steps` steps
     # more blocks: the median beside the reported figure, and a GPU kept busy while nvidia-smi samples the clocks;
     # every rank must run the same number of them (each ends in a barrier), so the count is agreed on, not timed per rank
@@ -1066,6 +1073,8 @@ def measure(wl, torch, world, steps, warmup, lib, local=0, min_blocks=5, clock_s
     for _ in range(extra):
         one_block()
     clocks = sampler.stop()
+    if os.environ.get("DALI_BENCH_BLOCKS"):
+        sys.stderr.write("blocks(ms/step) %s: %s\n" % (wl.name, " ".join("%.5f" % (b / steps) for b in block_ms[:40])))
     t = torch.tensor([block_ms[0], sorted(block_ms)[len(block_ms) // 2]], dtype=torch.float64, device="cuda")
     if world > 1:
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)

@@ -843,23 +843,31 @@ struct Gen {
         o << "  const i64 chunk = (i64)NT * VEC * UNROLL;\n";
         o << "  for (i64 cb = (i64)blockIdx.x * chunk; cb < C; cb += (i64)gridDim.x * chunk) {\n";
         bool hoist = v.nin == 1 && v.unroll > 1;
-        if (hoist) {
-            for (int a : largs) o << "    Vec<" << argT(a) << ", VEC> q" << a << "[UNROLL];\n";
-            o << "    _Pragma(\"unroll\") for (int u = 0; u < UNROLL; ++u) {\n";
-            o << "      const i64 c = cb + ((i64)u * NT + tid) * VEC;\n      if (c < C) {\n";
-            for (int a : largs) emit_arg_load("        ", a, "q" + std::to_string(a) + "[u]", "c", false);
-            o << "      }\n    }\n";
-        }
-        o << "    _Pragma(\"unroll\") for (int u = 0; u < UNROLL; ++u) {\n";
-        o << "      const i64 c = cb + ((i64)u * NT + tid) * VEC;\n      if (c < C) {\n";
-        GroupCtx g;
-        g.ind = "        ";
-        g.c = "c";
-        g.skip_loads = hoist;
-        g.hoist_idx = "[u]";
-        g.argred_index = "c + j";
-        emit_group(0, need, g);
-        o << "      }\n    }\n  }\n";
+        // (a variant whose full chunks skip the per-vector bounds checks executes 8 % fewer instructions on the fused
+        // chain and measured no faster: 1.56 ms against 1.54-1.57 ms over 2^31 elements)
+        auto emit_chunk = [&](bool checked) {
+            const std::string guard = checked ? "if (c < C) {\n" : "{\n";
+            if (hoist) {
+                for (int a : largs) o << "      Vec<" << argT(a) << ", VEC> q" << a << "[UNROLL];\n";
+                o << "      _Pragma(\"unroll\") for (int u = 0; u < UNROLL; ++u) {\n";
+                o << "        const i64 c = cb + ((i64)u * NT + tid) * VEC;\n        " << guard;
+                for (int a : largs) emit_arg_load("          ", a, "q" + std::to_string(a) + "[u]", "c", false);
+                o << "        }\n      }\n";
+            }
+            o << "      _Pragma(\"unroll\") for (int u = 0; u < UNROLL; ++u) {\n";
+            o << "        const i64 c = cb + ((i64)u * NT + tid) * VEC;\n        " << guard;
+            GroupCtx g;
+            g.ind = "          ";
+            g.c = "c";
+            g.skip_loads = hoist;
+            g.hoist_idx = "[u]";
+            g.argred_index = "c + j";
+            emit_group(0, need, g);
+            o << "        }\n      }\n";
+        };
+        o << "    {\n";
+        emit_chunk(true);
+        o << "    }\n  }\n";
         // CTA partials
         for (int si : reds) {
             const Stmt& s = p.stmts[si];

@@ -398,7 +398,16 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
         v.unroll = env_int("DALI_B200_ALL_UNROLL", 4);
         long long chunk = (long long)v.threads * vec * v.unroll;
         long long gx = (C + chunk - 1) / chunk;
-        out.grid_x = (unsigned)std::min<long long>(gx, (long long)kSMs * env_int("DALI_B200_ALL_CTAS_PER_SM", 8));
+        // One resident wave (148 x 8 CTAs) while a CTA then has at most 16 chunks; beyond that more, shorter CTAs, which the
+        // hardware hands to whichever SM frees up first: the fused chain over 2^31 elements takes 1.62 ms as one
+        // wave (CTAs of one SM progress unevenly and the last ones run with too few warps to hide the loads) and 1.50 ms
+        // as 16 waves; a 2^26-element sum is fastest as one wave (47 us; 50 / 53 / 59 us as 4 / 8 / 14 waves).  The work
+        // of a CTA depends on the grid only, so results stay bit-equal from run to run.
+        const long long wave = (long long)kSMs * env_int("DALI_B200_ALL_CTAS_PER_SM", 8);
+        const long long ctas = std::max(std::min(gx, wave),
+                                        std::min(gx / env_int("DALI_B200_ALL_CHUNKS_PER_CTA", 16),
+                                                 wave * env_int("DALI_B200_ALL_MAX_WAVES", 16)));
+        out.grid_x = (unsigned)ctas;
         out.scratch_bytes = (size_t)out.grid_x * 16 * std::max(1, p.n_reductions);
         out.counters = 1;
         v.T = 0; v.vpt = 0; v.tx = 0; v.ty = 0;
