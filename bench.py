@@ -419,7 +419,8 @@ class Lstm(Workload):
                             "h' = sig(o)*tanh(c'); fp32, B=256 H=1024 per GPU, x,h,c ~ N(0,1), W ~ N(0,0.02), b = 0",
                 "l2": "activations rotate over %d sets; the two weight matrices are reused every step (as in an RNN) "
                       "and stay in L2: `value` counts their bytes too and is therefore not an HBM bandwidth" % Lstm.NSET,
-                "kernels_per_step": "1 TF32 split of x and h, 1 tcgen05 3xTF32 GEMM accumulating x.Wx + h.Wh whose epilogue is the whole gating (+ b, sigmoid / tanh, c', h'): the [B,4H] gates are never written",
+                "kernels_per_step": "1 tcgen05 3xTF32 GEMM accumulating x.Wx + h.Wh whose epilogue is the whole gating (+ b, sigmoid / tanh, c', h'; the [B,4H] gates are never written) and which leaves h' as the two TF32 parts the next step reads, 1 TF32 split of the step's x",
+                "recurrence": "the timed loop is a recurrence: step t+1 reads step t's h' and c'; x_t rotates over the sets, and the split of x_(t+1) is issued on a second stream so that it runs beside step t's GEMM",
                 "parallelism": "batch sharded: each of %d GPU(s) runs its own B=256 shard, weights replicated, no collective" % world}
 
     @staticmethod
@@ -461,6 +462,22 @@ class Lstm(Workload):
         # what the front end emits for eval_together(c', h'): the gating is the epilogue of the gate products
         from dali_b200.ir import lstm_cell_epilogue_ir
         self.h_cell = L.compile(lstm_cell_epilogue_ir())
+        # the recurrent loop: state (c, h as its two TF32 parts) and the parts of x, each in two copies by step parity
+        self.h_cell_split = L.compile(lstm_cell_epilogue_ir(split_h=True))
+        self.xparts = [[t.empty(B * H, device="cuda") for _ in range(2)] for _ in range(2)]
+        self.hparts = [[t.empty(B * H, device="cuda") for _ in range(2)] for _ in range(2)]
+        self.c_state = [t.empty(B, H, device="cuda") for _ in range(2)]
+        self.h_state = [t.empty(B, H, device="cuda") for _ in range(2)]
+        self.side = t.cuda.Stream()
+        self.reset_state()
+
+    def reset_state(self):
+        """Step 0 starts from c[0] and h[0]."""
+        self.torch.cuda.synchronize()
+        self.c_state[0].copy_(self.c[0])
+        self.h_state[0].copy_(self.h[0])
+        self.lib.gemm_split_tf32(self.h[0], self.B, self.H, self.H, *self.hparts[0], device=self.device)
+        self.torch.cuda.synchronize()
 
     def bytes_per_step(self):
         B, H = self.B, self.H
@@ -469,10 +486,57 @@ class Lstm(Workload):
     def flops_per_step(self):
         return 2 * 2 * self.B * self.H * 4 * self.H
 
+    def split_x(self, i, stream):
+        self.lib.gemm_split_tf32(self.x[i % self.nset], self.B, self.H, self.H, *self.xparts[i % 2], device=self.device, stream=stream)
+
+    def launch_cell(self, i, stream):
+        """Step i of the recurrence: reads the parts of x_i and the state of parity i % 2, writes the state of the other parity."""
+        B, H, W, p = self.B, self.H, self.W, i % 2
+        X, Hp, q = self.xparts[p], self.hparts[p], 1 - p
+        row = [0, 1]
+        self.lib.gemm_fused_sum(0, B, H, [(H, X[0], H, W["Wx"][0], H, X[1], W["Wx"][1]),
+                                          (H, Hp[0], H, W["Wh"][0], H, Hp[1], W["Wh"][1])],
+                                self.h_cell_split,
+                                [self.c_state[q], self.h_state[q], self.b, self.b, self.b, self.b, self.c_state[p],
+                                 self.hparts[q][0], self.hparts[q][1]],
+                                strides=[None, None, row, row, row, row, None, None, None], offsets=[0, 0, 0, H, 2 * H, 3 * H, 0, 0, 0],
+                                device=self.device, stream=stream)
+
     def launch_step(self, i, stream):
-        L, B, H, k = self.lib, self.B, self.H, i % self.nset
-        L.gemm_split_tf32_pair(self.x[k], self.h[k], B, H, H, H, *self.parts, device=self.device, stream=stream)
-        self.launch_gemm(stream, k)
+        self.split_x(i, stream)
+        self.launch_cell(i, stream)
+
+    def graph_fn(self):
+        """One block of `block_steps` steps as the graph captures it: the cells follow one another on the main stream, the
+        split of the next step's x goes to a second stream (forked at the block's first step, joined by its last)."""
+        n = getattr(self, "block_steps", 0)
+        if n < 2:
+            return self.launch_step
+        t = self.torch
+        st = {"calls": 0, "x_ready": None, "prev_cell": None}
+
+        def fn(i, stream):
+            main = t.cuda.ExternalStream(stream)
+            pos = st["calls"] % n
+            st["calls"] += 1
+            if pos == 0:
+                self.side.wait_stream(main)                    # fork
+                self.split_x(i, self.side.cuda_stream)
+                st["x_ready"] = t.cuda.Event()
+                st["x_ready"].record(self.side)
+                st["prev_cell"] = None
+            main.wait_event(st["x_ready"])                     # the last step's wait joins the second stream
+            self.launch_cell(i, stream)
+            if pos + 1 < n:
+                done = t.cuda.Event()
+                done.record(main)
+                if st["prev_cell"] is not None:
+                    self.side.wait_event(st["prev_cell"])      # the cell before this one read the parts about to be overwritten
+                self.split_x(i + 1, self.side.cuda_stream)
+                st["x_ready"] = t.cuda.Event()
+                st["x_ready"].record(self.side)
+                st["prev_cell"] = done
+        return fn
 
     def launch_gemm(self, stream, k=0):
         B, H, P, W = self.B, self.H, self.parts, self.W
@@ -510,17 +574,27 @@ class Lstm(Workload):
         return r["ms_per_step"]
 
     def verify(self):
+        """Two steps of the recurrence from (x_0, h_0, c_0) against the oracle's gating of fp64 gate products, and the
+        parts the epilogue leaves of h' against h' itself (hi + lo is exact)."""
         sys.path.insert(0, os.path.join(ROOT, "oracle"))
         import dali_oracle as oracle
         np = self.np
-        self.step(0)
-        self.torch.cuda.synchronize()
-        assert self.lib.gemm_error_flag(self.device) == 0
-        x, h, c, Wx, Wh = (v.cpu().numpy().astype(np.float64) for v in (self.x[0], self.h[0], self.c[0], self.Wx, self.Wh))
-        gates = (x @ Wx + h @ Wh).astype(np.float32)
-        want_c, want_h = oracle.lstm_gating(gates, self.c[0].cpu().numpy())
-        assert np.allclose(self.c_new[0].cpu().numpy(), want_c, rtol=1e-5, atol=1e-5)
-        assert np.allclose(self.h_new[0].cpu().numpy(), want_h, rtol=1e-5, atol=1e-5)
+        self.reset_state()
+        Wx, Wh = (v.cpu().numpy().astype(np.float64) for v in (self.Wx, self.Wh))
+        h, c = self.h[0].cpu().numpy(), self.c[0].cpu().numpy()
+        for i in range(2):
+            self.step(i)
+            self.torch.cuda.synchronize()
+            assert self.lib.gemm_error_flag(self.device) == 0
+            gates = (self.x[i].cpu().numpy().astype(np.float64) @ Wx + h.astype(np.float64) @ Wh).astype(np.float32)
+            c, h = oracle.lstm_gating(gates, c)
+            q = (i + 1) % 2
+            got_c, got_h = self.c_state[q].cpu().numpy(), self.h_state[q].cpu().numpy()
+            assert np.allclose(got_c, c, rtol=1e-5, atol=1e-5 * (i + 1))
+            assert np.allclose(got_h, h, rtol=1e-5, atol=1e-5 * (i + 1))
+            hi, lo = (v.cpu().numpy().reshape(got_h.shape) for v in self.hparts[q])
+            assert np.array_equal(hi + lo, got_h) and np.array_equal(hi.view(np.uint32) & 0x1fff, np.zeros_like(hi, np.uint32))
+        self.reset_state()
 
 
 class Gemm(Workload):
@@ -1016,6 +1090,7 @@ def measure(wl, torch, world, steps, warmup, lib, local=0, min_blocks=5, clock_s
     for i in range(warmup):
         wl.step(i)
     barrier()
+    wl.block_steps = steps
     fn = wl.graph_fn()
     stepper = GraphStepper(torch, lambda i, st: fn(warmup + i, st), steps, getattr(wl, "lanes", 1)) if fn else None
     # the clock sampler starts here, ahead of the spin-up: spawning it takes milliseconds, in which an idle GPU would drop

@@ -87,6 +87,8 @@ int functor_arity(const std::string& n) {
         "abs", "sign", "relu", "relu_backward", "softplus", "softplus_backward", "isnotanumber",
         "isinfinity", "round", "ceiling", "negate",
         "bf16_round",      // not a reference functor: the float a bf16 store would keep (astype(bf16) inside an expression)
+        "tf32_hi", "tf32_lo",   // not reference functors: the two parts a 3xTF32 product takes of an fp32 operand, so that
+                                // the kernel that produces the operand can leave it split (a recurrent cell's next h)
         nullptr};
     static const char* binary[] = {
         "add", "subtract", "eltmul", "eltdiv", "equals", "power", "fill", "div_grad", "threshold",

@@ -33,6 +33,15 @@ struct bf16_t {
 };
 // the value a bf16 store would keep, as a float (x.astype(bf16) inside a larger expression)
 DEV float f_bf16_round(float a) { return (float)bf16_t(a); }
+// The two parts of an fp32 value that the 3xTF32 product multiplies: hi keeps the 10 mantissa bits TF32 carries (the low
+// 13 cleared), lo = a - hi is exact in fp32 and zero for an infinite a (inf - inf would be NaN).  Same arithmetic as the
+// stand-alone split kernels of the GEMM path.
+DEV float f_tf32_hi(float a) { return __uint_as_float(__float_as_uint(a) & 0xffffe000u); }
+DEV float f_tf32_lo(float a) { const float h = f_tf32_hi(a); return fabsf(h) == __int_as_float(0x7f800000) ? 0.0f : a - h; }
+DEV double f_tf32_hi(double a) { return (double)f_tf32_hi((float)a); }
+DEV double f_tf32_lo(double a) { return (double)f_tf32_lo((float)a); }
+DEV int f_tf32_hi(int a) { return a; }
+DEV int f_tf32_lo(int a) { return 0; }
 
 // ---------------------------------------------------------------- functors
 template <typename T> DEV T f_identity(T a) { return a; }

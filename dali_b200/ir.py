@@ -153,10 +153,12 @@ def gemm_store_ir(out_dtype="f32", op="assign"):
     return b.text()
 
 
-def lstm_cell_epilogue_ir():
+def lstm_cell_epilogue_ir(split_h=False):
     """The whole LSTM gating as the epilogue of gates = x.Wx + h.Wh: per output (row, unit) the four accumulator
     slices i, f, o, g plus their biases, c' = sigmoid(f)*c + sigmoid(i)*tanh(g), h' = sigmoid(o)*tanh(c').
-    args (c_new, h_new, b_i, b_f, b_o, b_g, c); the gates matrix is never written."""
+    args (c_new, h_new, b_i, b_f, b_o, b_g, c); the gates matrix is never written.  With split_h the args end with
+    (h_hi, h_lo): h' is also left as the two parts the next step's 3xTF32 product h'.Wh reads, so that a recurrent loop
+    needs no separate split of h."""
     b = IRBuilder(2, 0)
     cn, hn = b.arg("f32"), b.arg("f32")
     bias = [b.arg("f32") for _ in range(4)]
@@ -166,5 +168,10 @@ def lstm_cell_epilogue_ir():
     g = b.op("tanh", pre[3])
     cnew = b.op("add", b.op("eltmul", f, b.ld(c)), b.op("eltmul", i, g))
     b.st(cn, cnew)
-    b.st(hn, b.op("eltmul", o, b.op("tanh", cnew)))
+    hnew = b.op("eltmul", o, b.op("tanh", cnew))
+    b.st(hn, hnew)
+    if split_h:
+        hi, lo = b.arg("f32"), b.arg("f32")
+        b.st(hi, b.op("tf32_hi", hnew))
+        b.st(lo, b.op("tf32_lo", hnew))
     return b.text()

@@ -167,6 +167,45 @@ def test_lstm_gating_as_the_epilogue_of_the_gate_products(lib, shape, ksplit, mo
     np.testing.assert_allclose(got_h, want_h, rtol=1e-5, atol=2.5e-7 * bound + 1e-6)
 
 
+def test_lstm_epilogue_leaves_the_next_hidden_state_split(lib):
+    """lstm_cell_epilogue_ir(split_h=True): the epilogue also stores the two TF32 parts of h' (hi = the top 19 bits, lo = h' - hi,
+    exact).  Two steps of a recurrence in which the second step's h operand is what the first one's epilogue left, against the
+    oracle's gating of fp64 gate products."""
+    B, H = 256, 1024
+    rng = np.random.default_rng(5)
+    xs = [rng.standard_normal((B, H)).astype(np.float32) for _ in range(2)]
+    h, c = (rng.standard_normal((B, H)).astype(np.float32) for _ in range(2))
+    Wx, Wh = ((rng.standard_normal((H, 4 * H)) * 0.02).astype(np.float32) for _ in range(2))
+    b = (rng.standard_normal(4 * H) * 0.1).astype(np.float32)
+    bd = dev(b)
+    W = []
+    for w in (Wx, Wh):
+        hi, lo = torch.empty(4 * H * H, device="cuda"), torch.empty(4 * H * H, device="cuda")
+        lib.gemm_split_tf32(dev(w), H, 4 * H, 4 * H, hi, lo, transpose=True)
+        W.append((hi, lo))
+    xp = [torch.empty(B * H, device="cuda") for _ in range(2)]
+    hp = [[torch.empty(B * H, device="cuda") for _ in range(2)] for _ in range(2)]
+    cs = [dev(c), torch.empty((B, H), device="cuda")]
+    hs = [torch.empty((B, H), device="cuda") for _ in range(2)]
+    lib.gemm_split_tf32(dev(h), B, H, H, *hp[0])
+    prog = lib.compile(lstm_cell_epilogue_ir(split_h=True))
+    row = [0, 1]
+    for i in range(2):
+        p, q = i % 2, 1 - i % 2
+        lib.gemm_split_tf32(dev(xs[i]), B, H, H, *xp)
+        lib.gemm_fused_sum(0, B, H, [(H, xp[0], H, W[0][0], H, xp[1], W[0][1]), (H, hp[p][0], H, W[1][0], H, hp[p][1], W[1][1])], prog,
+                           [cs[q], hs[q], bd, bd, bd, bd, cs[p], hp[q][0], hp[q][1]],
+                           strides=[None, None, row, row, row, row, None, None, None], offsets=[0, 0, 0, H, 2 * H, 3 * H, 0, 0, 0])
+        assert lib.gemm_error_flag() == 0
+        gates = (xs[i].astype(np.float64) @ Wx + h.astype(np.float64) @ Wh + b).astype(np.float32)
+        c, h = oracle.lstm_gating(gates, c)
+        np.testing.assert_allclose(host(cs[q]), c, rtol=1e-5, atol=1e-5 * (i + 1))
+        np.testing.assert_allclose(host(hs[q]), h, rtol=1e-5, atol=1e-5 * (i + 1))
+        hi, lo = host(hp[q][0]).reshape(B, H), host(hp[q][1]).reshape(B, H)
+        np.testing.assert_array_equal(hi + lo, host(hs[q]))
+        assert not np.any(hi.view(np.uint32) & 0x1fff)
+
+
 def test_two_bf16_products_in_one_accumulator(lib):
     m, n, k1, k2 = 256, 512, 192, 320
     rng = np.random.default_rng(77)
