@@ -12,6 +12,11 @@
 #   oracle/_ref/cache/           the reference's JIT module cache (pre-warmed by
 #                                oracle/warm_ref_cache.sh so that a machine
 #                                without the checkout can still run the driver)
+#   oracle/_ref/libdali_ref_bound.so, ref_driver_bound
+#                                the same library and driver with the reference-side binding compiled in
+#                                (oracle/ref_binding/): a JITRunner and a MatMul of the reference's own graph
+#                                are computed by dali_b200/lib/libdali_b200.so.  Built only when that library
+#                                exists; libdali_ref.so itself stays the unmodified reference
 #
 # Nothing of the reference is written anywhere else; oracle/_ref/ is
 # git-ignored.  The reference's CMake build is NOT used (it needs GoogleTest,
@@ -37,8 +42,17 @@ if [ ! -d "$REF/dali/array" ]; then
     echo "build_ref: no reference checkout at $REF -- keeping whatever is in $OUT" >&2
     exit 0
 fi
+B200_LIB="$HERE/../dali_b200/lib/libdali_b200.so"
+bound_current() {
+    [ ! -f "$B200_LIB" ] && return 0          # nothing to bind to yet
+    [ -x "$OUT/ref_driver_bound" ] || return 1
+    for f in "$HERE"/ref_binding/* "$HERE/ref_driver.cpp" "$HERE/build_ref.sh" "$HERE/../include/dali_b200.h"; do
+        [ "$OUT/libdali_ref_bound.so" -nt "$f" ] || return 1
+    done
+    return 0
+}
 if [ -x "$OUT/ref_driver" ] && [ "$OUT/ref_driver" -nt "$HERE/ref_driver.cpp" ] \
-   && [ "$OUT/libdali_ref.so" -nt "$HERE/build_ref.sh" ] && [ -z "${FORCE:-}" ]; then
+   && [ "$OUT/libdali_ref.so" -nt "$HERE/build_ref.sh" ] && bound_current && [ -z "${FORCE:-}" ]; then
     echo "build_ref: $OUT is up to date"
     exit 0
 fi
@@ -122,3 +136,30 @@ $CXX -std=c++11 -O2 -w -include "$HERE/shims/fixups.h" -I"$STAGE" -I"$HERE/shims
     "$HERE/ref_driver.cpp" -o "$OUT/ref_driver" \
     -L"$OUT" -ldali_ref -Wl,-rpath,'$ORIGIN' $BLAS_ARGS -lz -ldl -lpthread
 echo "build_ref: built $OUT/libdali_ref.so and $OUT/ref_driver"
+
+# 8. the same library with the reference-side binding compiled in (oracle/ref_binding/README in the files' headers):
+#    patched copies of the two translation units that register the implementations of JITRunner and MatMul
+if [ -f "$B200_LIB" ]; then
+    mkdir -p "$STAGE/bound/dali/array/jit" "$STAGE/bound/dali/array/gemm" "$STAGE/obj_bound"
+    JIT="$STAGE/bound/dali/array/jit/jit.cpp"; GEMM="$STAGE/bound/dali/array/gemm/cpu_gemm.cpp"
+    cp "$STAGE/dali/array/jit/jit.cpp" "$JIT"; cp "$STAGE/dali/array/gemm/cpu_gemm.cpp" "$GEMM"
+    grep -q '^int registered_jit_runner_impl = register_implementation_default<JITRunner, JITRunnerImpl>();$' "$JIT"
+    grep -q '^int cpu_gemm_impl = register_implementation($' "$GEMM"
+    # the registration of JITRunnerImpl becomes the binding (which registers itself and keeps JITRunnerImpl as the path for
+    # what it does not take); the other places that create a JITRunnerImpl directly create the binding's class too
+    sed -i 's|^int registered_jit_runner_impl = register_implementation_default<JITRunner, JITRunnerImpl>();$|#include "jit_b200_binding.inc"|' "$JIT"
+    sed -i 's|std::make_shared<JITRunnerImpl>(|std::make_shared<b200_binding::B200RunnerImpl>(|g' "$JIT"
+    sed -i 's|^int cpu_gemm_impl = register_implementation($|#include "gemm_b200_binding.inc"\nint cpu_gemm_impl = register_implementation(|' "$GEMM"
+    sed -i '1i #include "binding_includes.h"' "$JIT" "$GEMM"
+    BFLAGS="$CXXFLAGS -I$HERE/ref_binding -I$HERE/../include"
+    $CXX $BFLAGS -I"$STAGE/dali/array/jit" -c "$JIT" -o "$STAGE/obj_bound/jit.o"
+    $CXX $BFLAGS -I"$STAGE/dali/array/gemm" -c "$GEMM" -o "$STAGE/obj_bound/cpu_gemm.o"
+    OBJS="$(ls "$STAGE"/obj/*.o | grep -v -e 'dali_array_jit_jit.cpp.o$' -e 'dali_array_gemm_cpu_gemm.cpp.o$')"
+    B200_DIR="$(cd "$(dirname "$B200_LIB")" && pwd)"
+    $CXX -shared -o "$OUT/libdali_ref_bound.so" $OBJS "$STAGE/obj_bound/jit.o" "$STAGE/obj_bound/cpu_gemm.o" $BLAS_ARGS \
+        -L"$B200_DIR" -ldali_b200 -Wl,-rpath,'$ORIGIN/../../dali_b200/lib' -lz -ldl -lpthread
+    $CXX -std=c++11 -O2 -w -include "$HERE/shims/fixups.h" -I"$STAGE" -I"$HERE/shims" -DREF_DRIVER_BOUND=1 \
+        "$HERE/ref_driver.cpp" -o "$OUT/ref_driver_bound" \
+        -L"$OUT" -ldali_ref_bound -L"$B200_DIR" -ldali_b200 -Wl,-rpath,'$ORIGIN' -Wl,-rpath,'$ORIGIN/../../dali_b200/lib' $BLAS_ARGS -lz -ldl -lpthread
+    echo "build_ref: built $OUT/libdali_ref_bound.so and $OUT/ref_driver_bound"
+fi

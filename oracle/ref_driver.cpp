@@ -43,6 +43,11 @@
 #include <map>
 #include <string>
 
+#ifdef REF_DRIVER_BOUND
+extern "C" void dali_b200_binding_stats(int* launched, int* fell_back);
+extern "C" int dali_b200_binding_gemms();
+#endif
+
 typedef std::chrono::steady_clock clk;
 static double ms(clk::time_point a, clk::time_point b) {
     return std::chrono::duration<double, std::milli>(b - a).count();
@@ -283,5 +288,11 @@ int main(int argc, char** argv) {
     } else {
         return usage();
     }
+#ifdef REF_DRIVER_BOUND
+    // ref_driver_bound (linked against libdali_ref_bound.so): how much of the case the binding took
+    int launched = 0, fell_back = 0;
+    dali_b200_binding_stats(&launched, &fell_back);
+    std::printf("BINDING launched=%d fell_back=%d gemms=%d\n", launched, fell_back, dali_b200_binding_gemms());
+#endif
     return 0;
 }
