@@ -270,6 +270,8 @@ struct Gen {
         std::set<int> cuts_rd, cuts_wr;
         std::string acc_suffix;    // "" or "[j]" (col kind keeps VEC accumulators)
         std::string argred_index;  // expression of the reduced-dim index of lane j
+        std::string argred_defer;  // non-empty: arg-reductions only park their operand in av<si><argred_defer>[j]; the caller
+                                   // folds a whole group of parked values at once (fold_deferred_args)
         bool skip_loads = false;   // loads were hoisted by the caller (map / all unrolling)
         std::string hoist_idx;     // "[u]" when loads were hoisted into arrays
     };
@@ -398,8 +400,11 @@ struct Gen {
                   << g.acc_suffix << ", " << vn(s.in[0]) << ");\n";
             } else if (s.kind == S_ARGRED) {
                 const Stmt& src = val(s.in[0]);
-                o << in2 << "arg_take<" << red_struct(s.name) << ", " << ct(src.dtype) << ">(acc" << si << g.acc_suffix
-                  << ", " << vn(s.in[0]) << ", (i64)(" << g.argred_index << "));\n";
+                if (!g.argred_defer.empty())
+                    o << in2 << "av" << si << g.argred_defer << "[j] = " << vn(s.in[0]) << ";\n";
+                else
+                    o << in2 << "arg_take<" << red_struct(s.name) << ", " << ct(src.dtype) << ">(acc" << si << g.acc_suffix
+                      << ", " << vn(s.in[0]) << ", (i64)(" << g.argred_index << "));\n";
             } else if (s.kind == S_ST) {
                 std::string old = argvec(s.arg) + ".x[j]";
                 o << in2 << "out" << si << ".x[j] = (" << argT(s.arg) << ")(" << assign_rhs(s.aop, old, vn(s.in[0])) << ");\n";
@@ -845,8 +850,21 @@ struct Gen {
         bool hoist = v.nin == 1 && v.unroll > 1;
         // (a variant whose full chunks skip the per-vector bounds checks executes 8 % fewer instructions on the fused
         // chain and measured no faster: 1.56 ms against 1.54-1.57 ms over 2^31 elements)
+        // Arg-reductions: taking every element into the (value, position) pair costs a compare and three selects plus the
+        // 64-bit position per element.  Instead the chunk's candidates are parked, one maximum (minimum) over all of
+        // them decides whether any beats the running value -- after the first chunks almost none does -- and only then
+        // are they taken one by one, in order, which keeps the first occurrence.
+        std::vector<int> argreds;
+        for (int si : reds) if (p.stmts[si].kind == S_ARGRED) argreds.push_back(si);
         auto emit_chunk = [&](bool checked) {
             const std::string guard = checked ? "if (c < C) {\n" : "{\n";
+            for (int si : argreds) {
+                const Stmt& s = p.stmts[si];
+                const std::string T = ct(val(s.in[0]).dtype);
+                o << "      " << T << " av" << si << "[UNROLL][VEC];\n";
+                o << "      _Pragma(\"unroll\") for (int u = 0; u < UNROLL; ++u) _Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) av" << si
+                  << "[u][j] = " << red_struct(s.name) << "::init<" << T << ">();\n";
+            }
             if (hoist) {
                 for (int a : largs) o << "      Vec<" << argT(a) << ", VEC> q" << a << "[UNROLL];\n";
                 o << "      _Pragma(\"unroll\") for (int u = 0; u < UNROLL; ++u) {\n";
@@ -862,8 +880,22 @@ struct Gen {
             g.skip_loads = hoist;
             g.hoist_idx = "[u]";
             g.argred_index = "c + j";
+            if (!argreds.empty()) g.argred_defer = "[u]";
             emit_group(0, need, g);
             o << "        }\n      }\n";
+            for (int si : argreds) {
+                const Stmt& s = p.stmts[si];
+                const std::string T = ct(val(s.in[0]).dtype), R = red_struct(s.name);
+                o << "      {\n        " << T << " m_ = av" << si << "[0][0];\n";
+                o << "        _Pragma(\"unroll\") for (int u = 0; u < UNROLL; ++u) _Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) m_ = "
+                  << R << "::pick(m_, av" << si << "[u][j]);\n";
+                o << "        if (" << R << "::better(m_, acc" << si << ".v)) {\n";
+                o << "          _Pragma(\"unroll\") for (int u = 0; u < UNROLL; ++u) {\n";
+                o << "            const i64 c = cb + ((i64)u * NT + tid) * VEC;\n";
+                o << "            _Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) arg_take<" << R << ", " << T << ">(acc" << si << ", av"
+                  << si << "[u][j], c + j);\n";
+                o << "          }\n        }\n      }\n";
+            }
         };
         o << "    {\n";
         emit_chunk(true);
@@ -1009,8 +1041,28 @@ struct Gen {
             for (int in : val(id).in)
                 if (!val(in).elem && val(in).kind != S_SC && val(in).kind != S_CONST) r0_in_loop.insert(in);
         if (!r0_in_loop.empty()) { *err = "col skeleton: element work may not use row-level loads"; return false; }
+        // arg-reductions: the rows in flight are parked and one maximum (minimum) per column decides whether any of them
+        // beats the column's running value (see the all-axis skeleton); the running sums / extremes of plain
+        // reductions in the same program go on as before
+        std::vector<int> argreds;
+        for (int si : reds) if (p.stmts[si].kind == S_ARGRED) argreds.push_back(si);
+        const bool defer = !argreds.empty();
         o << "  if (ov) {\n";
-        o << "    _Pragma(\"unroll " << v.unroll << "\") for (i64 c = c0 + ty; c < c1; c += TYI) {\n";
+        if (defer) {
+            o << "    for (i64 cb = c0 + ty; cb < c1; cb += (i64)TYI * " << v.unroll << ") {\n";
+            for (int si : argreds) {
+                const Stmt& s = p.stmts[si];
+                const std::string T = ct(val(s.in[0]).dtype);
+                o << "    " << T << " av" << si << "[" << v.unroll << "][VEC];\n";
+                o << "    _Pragma(\"unroll\") for (int u = 0; u < " << v.unroll << "; ++u) _Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) av"
+                  << si << "[u][j] = " << red_struct(s.name) << "::init<" << T << ">();\n";
+            }
+            o << "    _Pragma(\"unroll\") for (int u = 0; u < " << v.unroll << "; ++u) {\n";
+            o << "    const i64 c = cb + (i64)u * TYI;\n";
+            o << "    if (c < c1) {\n";
+        } else {
+            o << "    _Pragma(\"unroll " << v.unroll << "\") for (i64 c = c0 + ty; c < c1; c += TYI) {\n";
+        }
         for (int a : largs) {
             const std::string T = argT(a);
             char oc = v.ocls[a];
@@ -1033,8 +1085,23 @@ struct Gen {
             g.hoist_idx = "";
             g.acc_suffix = "[j]";
             g.argred_index = "c";
+            if (defer) g.argred_defer = "[u]";
             // emit_group's lane loop walks j over the OUTER lanes here
             emit_group(0, need, g);
+        }
+        if (defer) {
+            o << "    }\n    }\n";      // if (c < c1), for u
+            for (int si : argreds) {
+                const Stmt& s = p.stmts[si];
+                const std::string T = ct(val(s.in[0]).dtype), R = red_struct(s.name);
+                o << "    _Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) {\n";
+                o << "      " << T << " m_ = av" << si << "[0][j];\n";
+                o << "      _Pragma(\"unroll\") for (int u = 1; u < " << v.unroll << "; ++u) m_ = " << R << "::pick(m_, av" << si << "[u][j]);\n";
+                o << "      if (" << R << "::better(m_, acc" << si << "[j].v)) {\n";
+                o << "        _Pragma(\"unroll\") for (int u = 0; u < " << v.unroll << "; ++u) arg_take<" << R << ", " << T << ">(acc" << si
+                  << "[j], av" << si << "[u][j], cb + (i64)u * TYI);\n";
+                o << "      }\n    }\n";
+            }
         }
         o << "    }\n  }\n";
         // fold the TYI slices of the CTA

@@ -403,10 +403,15 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
         // wave (CTAs of one SM progress unevenly and the last ones run with too few warps to hide the loads) and 1.50 ms
         // as 16 waves; a 2^26-element sum is fastest as one wave (47 us; 50 / 53 / 59 us as 4 / 8 / 14 waves).  The work
         // of a CTA depends on the grid only, so results stay bit-equal from run to run.
+        // (whole waves only; a program with an arg-reduction, whose slow path makes CTAs uneven, goes to a second wave
+        // at half the work per CTA: argmax over 2^26 elements 48.3 us as one wave, 45.9 us as two)
         const long long wave = (long long)kSMs * env_int("DALI_B200_ALL_CTAS_PER_SM", 8);
-        const long long ctas = std::max(std::min(gx, wave),
-                                        std::min(gx / env_int("DALI_B200_ALL_CHUNKS_PER_CTA", 16),
-                                                 wave * env_int("DALI_B200_ALL_MAX_WAVES", 16)));
+        bool all_has_arg = false;
+        for (const Stmt& st_ : p.stmts) all_has_arg = all_has_arg || st_.kind == S_ARGRED;
+        const long long per_cta = env_int("DALI_B200_ALL_CHUNKS_PER_CTA", all_has_arg ? 8 : 16);
+        long long waves = (gx + per_cta * wave / 2) / (per_cta * wave);
+        waves = std::max<long long>(1, std::min<long long>(waves, env_int("DALI_B200_ALL_MAX_WAVES", 16)));
+        const long long ctas = std::min(gx, wave * waves);
         out.grid_x = (unsigned)ctas;
         out.scratch_bytes = (size_t)out.grid_x * 16 * std::max(1, p.n_reductions);
         out.counters = 1;
@@ -419,14 +424,16 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
         v.tx = env_int("DALI_B200_COL_TX", tx);
         v.ty = env_int("DALI_B200_COL_TY", 256 / v.tx);
         v.threads = v.tx * v.ty;
-        v.unroll = env_int("DALI_B200_COL_UNROLL", 8);
+        bool has_arg = false;
+        for (const Stmt& st_ : p.stmts) has_arg = has_arg || st_.kind == S_ARGRED;
+        // (arg-reductions park the rows in flight before they fold them: 4 rows and 4 CTAs per SM, 52.5 us on [8192,8192];
+        // 8 rows need 3 CTAs per SM, 56 us; more CTAs per SM spill -- 5: 62 us, 8: 102 us)
+        v.unroll = env_int("DALI_B200_COL_UNROLL", has_arg ? 4 : 8);
         long long tiles = (R + (long long)v.tx * vec - 1) / ((long long)v.tx * vec);
         // The grid is one wave: every SM holds `per_sm` CTAs for the whole launch.  A plain reduction is compiled to fit 8
         // per SM (32 registers; without the bound max took 40 and its 1184 CTAs ran as a wave of 888 and a tail); an
-        // arg-reduction carries (value, 64-bit position) pairs and is sized for 5 per SM, what its 46 registers allow.
-        bool has_arg = false;
-        for (const Stmt& st_ : p.stmts) has_arg = has_arg || st_.kind == S_ARGRED;
-        int per_sm = env_int("DALI_B200_COL_CTAS_PER_SM", has_arg ? 5 : 8);
+        // arg-reduction carries (value, 64-bit position) pairs and the parked rows, and is sized for 4 per SM.
+        int per_sm = env_int("DALI_B200_COL_CTAS_PER_SM", has_arg ? 4 : 8);
         if (v.threads == 256 && p.stmts.size() <= 6) v.minb = per_sm;
         long long S = has_arg ? std::max<long long>(1, (long long)kSMs * per_sm / tiles)
                               : ((long long)kSMs * per_sm + tiles - 1) / tiles;

@@ -226,12 +226,20 @@ struct RMax {
     template <typename T> static DEV T apply(T a, T b) { return a > b ? a : b; }
     static DEV float apply(float a, float b) { return fmaxf(a, b); }
     template <typename T> static DEV bool better(T a, T b) { return a > b; }
+    // the larger of two candidates with a NaN never winning (fmaxf / fmax / integer max): what arg-reductions use to
+    // ask of a whole group of elements at once whether any of them beats the running value
+    template <typename T> static DEV T pick(T a, T b) { return a > b ? a : b; }
+    static DEV float pick(float a, float b) { return fmaxf(a, b); }
+    static DEV double pick(double a, double b) { return fmax(a, b); }
 };
 struct RMin {
     template <typename T> static DEV T init() { return Lim<T>::hi(); }
     template <typename T> static DEV T apply(T a, T b) { return a < b ? a : b; }
     static DEV float apply(float a, float b) { return fminf(a, b); }
     template <typename T> static DEV bool better(T a, T b) { return a < b; }
+    template <typename T> static DEV T pick(T a, T b) { return a < b ? a : b; }
+    static DEV float pick(float a, float b) { return fminf(a, b); }
+    static DEV double pick(double a, double b) { return fmin(a, b); }
 };
 
 // (value, index) for argmax / argmin.  The reference keeps the FIRST index at
