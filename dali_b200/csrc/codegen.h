@@ -50,6 +50,7 @@ struct Variant {
     bool xrank = false;      // all: partial results are exchanged with the other ranks before the kernel finishes
     int tile = 0;            // map with operands of class 't': 32 / 64 = edge of the shared-memory tiles they are read through, 4 = 4 x 4 register blocks (128-bit accesses), 0 = none
     std::string cls;         // per arg inner-stride class: u(nit) z(ero) s(trided) t(ransposed: unit stride along the OUTER dim)
+    bool unchecked = false;  // all: chunks that lie wholly inside the data run without per-vector bounds checks
     bool stream_out = false; // map with a gather: element stores are streaming stores (evict-first in L2)
     std::string xv;          // per arg: '1' = an indirectly read arg whose rows can be fetched with full-width vector loads
     std::string ocls;        // col: per arg outer-stride class

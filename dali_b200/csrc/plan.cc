@@ -232,6 +232,7 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
     v.vec = vec;
     // indirectly read args (gather sources) whose indexed rows can be fetched with full-width vector loads
     v.xv.assign(nargs, '0');
+    v.unchecked = v.kind == K_ALL && env_int("DALI_B200_ALL_UNCHECKED", 1);
     v.stream_out = v.kind == K_MAP && p.has_indirect && env_int("DALI_B200_GATHER_STREAM", 0);
     // (opt-in: on 2^20 rows of 1 KiB gathered from a 64 MiB table the kernel is bound by the 1 GiB it writes -- 292 us with
     // scalar gathers and plain stores, 326 us with 128-bit gathers, 314-320 us with streaming stores, DALI_B200_GATHER_STREAM)
