@@ -667,6 +667,42 @@ bool only_elementwise(const Array& a) {
     }
 }
 
+// [first, last] element of the buffer that a view touches
+static void view_span(const BufferView* b, int64_t* lo, int64_t* hi) {
+    std::vector<int> st = b->normalized_strides();
+    *lo = *hi = b->offset_;
+    for (size_t d = 0; d < b->shape_.size(); ++d) {
+        if (b->shape_[d] <= 0) { *hi = *lo - 1; return; }       // empty view
+        const int64_t reach = (int64_t)(b->shape_[d] - 1) * st[d];
+        if (reach < 0) *lo += reach; else *hi += reach;
+    }
+}
+// Two views of one buffer whose element ranges intersect (a conservative test: interleaved views count as overlapping).
+static bool views_may_overlap(const BufferView* x, const BufferView* y) {
+    if (x->memory_ != y->memory_) return false;
+    int64_t xl, xh, yl, yh;
+    view_span(x, &xl, &xh);
+    view_span(y, &yl, &yh);
+    return xl <= yh && yl <= xh;
+}
+// Does a product below `a` (through elementwise nodes and views) read a buffer that `dest` is about to overwrite?
+// A GEMM reads every operand element many times while other CTAs already store results: dest = dot(dest, w) must go
+// through a temporary (the reference does not guard against it either; a numpy-like statement is well defined).
+static bool product_reads_destination(const Array& a, const BufferView* dest) {
+    if (a.is_stateless()) return false;
+    Expression* e = a.expression().get();
+    if (e->kind_ == N_MATMUL) {
+        for (const Array& operand : e->arguments_) {
+            if (BufferView* b = as<BufferView>(operand)) { if (views_may_overlap(b, dest)) return true; }
+            else if (product_reads_destination(operand, dest)) return true;
+        }
+        return false;
+    }
+    if (e->kind_ != N_ELEMENTWISE && e->kind_ != N_VIEW) return false;
+    for (const Array& arg : e->arguments_) if (product_reads_destination(arg, dest)) return true;
+    return false;
+}
+
 // dest (op)= left . right through the GEMM entry point of the C ABI (reference:
 // CublasGemmImpl::run, dali/array/gemm/cublas_gemm.cu:112-185, which ignores the
 // operator and always overwrites; here += and -= accumulate as
@@ -687,6 +723,14 @@ void run_matmul(const Array& dest, OPERATOR_T op, MatMul* mm) {
     BufferView* a = as<BufferView>(left);
     BufferView* b = as<BufferView>(right);
     BufferView* c = as<BufferView>(dest);
+    if (views_may_overlap(a, c) || views_may_overlap(b, c)) {
+        // the destination is one of the operands: product into a temporary, then the assignment
+        Array tmp(dest.shape(), dest.dtype(), dest.preferred_device());
+        Array product(std::make_shared<MatMul>(left, right));
+        run_assignment(tmp, OPERATOR_T_EQL, product);
+        run_assignment(dest, op, tmp);
+        return;
+    }
     const int64_t m = a->shape_[0], k = a->shape_[1], n = b->shape_[1];
     DALI_ASSERT(c->shape_.size() == 2 && c->shape_[0] == m && c->shape_[1] == n, "matmul destination has the wrong shape");
     if (m == 0 || n == 0) return;
@@ -1172,6 +1216,12 @@ void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) 
     }
 
     // ---- an elementwise tree around a product: tensor-core GEMM with the tree as its epilogue
+    if (dest.is_buffer() && product_reads_destination(value, as<BufferView>(dest))) {
+        Array tmp(dest.shape(), value_dtype(dest.dtype()), dest.preferred_device());
+        run_assignment(tmp, OPERATOR_T_EQL, value);
+        run_assignment(dest, op, tmp);
+        return;
+    }
     if (dest.is_buffer() && dest.ndim() == 2 && value_dtype(dest.dtype()) == DTYPE_FLOAT && value.shape() == dest.shape()) {
         const Expression* acc = nullptr;
         find_matmul_sum(value, &acc);
@@ -1286,6 +1336,33 @@ void run_assignment(const Array& dest_in, OPERATOR_T op, const Array& value_in) 
         int leaf = L.leaf_for(db, root_map, true, false, 0, 0, 0);
         if (nreduce > 0 && !row_level_root) L.leaves[leaf].elem_level = true;
         if (op != OPERATOR_T_EQL) L.leaves[leaf].read = true;
+        // The destination's buffer is also read through a DIFFERENT index map (a.assign(a.transpose()), a[1:] = a[:-1],
+        // a[0] = sum(a, 0)): other threads would overwrite elements this one still has to read.  The value goes to a
+        // temporary first.  (The same map is fine: every element is read and written by the same thread.)
+        {
+            const Leaf& w = L.leaves[leaf];
+            auto span = [&](const Leaf& l, int64_t* lo, int64_t* hi) {
+                *lo = *hi = l.offset;
+                for (int d = 0; d < rank; ++d) {
+                    const int64_t reach = (space[d] - 1) * l.strides[d];
+                    if (reach < 0) *lo += reach; else *hi += reach;
+                }
+            };
+            int64_t wl, wh;
+            span(w, &wl, &wh);
+            for (size_t i = 0; i < L.leaves.size(); ++i) {
+                const Leaf& r = L.leaves[i];
+                if ((int)i == leaf || r.iota || r.memory != w.memory) continue;
+                int64_t rl, rh;
+                span(r, &rl, &rh);
+                if (r.indirect || (rl <= wh && wl <= rh)) {
+                    Array tmp(dest.shape(), value_dtype(dest.dtype()), dest.preferred_device());
+                    run_assignment(tmp, OPERATOR_T_EQL, value);
+                    run_assignment(dest, op, tmp);
+                    return;
+                }
+            }
+        }
         L.keep_alive.push_back(dest);
         L.body.push_back("st " + std::to_string(leaf) + " " + ir_assign(op) + " v" + std::to_string(v));
     } else {

@@ -520,3 +520,41 @@ def test_update_reading_its_own_destination_sees_the_old_value():
     x = Array(w_np[0].copy())
     x.assign(op.tanh(x) + x)
     np.testing.assert_allclose(x.numpy(), np.tanh(w_np[0]) + w_np[0], rtol=1e-6)
+
+
+def test_destination_read_through_another_index_map_goes_through_a_temporary():
+    """a.assign(a.transpose()), a[1:] = a[:-1], a[0] = sum(a, 0) and a = dot(a, w): the destination's buffer is also an
+    operand under a different index map, so one kernel would read elements other threads have already overwritten.  The
+    value is evaluated into a temporary first (numpy semantics); the same map (a = a * 2, a += a) needs none."""
+    rng = np.random.default_rng(31)
+    x = rng.standard_normal((257, 257)).astype(np.float32)
+    a = Array(x)
+    a.assign(a.transpose())
+    np.testing.assert_array_equal(a.numpy(), x.T)
+    a = Array(x)
+    a[1:].assign(a[:-1])
+    want = x.copy()
+    want[1:] = x[:-1]
+    np.testing.assert_array_equal(a.numpy(), want)
+    a = Array(x)
+    a[0].assign(op.sum(a, [0]))
+    want = x.copy()
+    want[0] = x.sum(0, dtype=np.float64)
+    np.testing.assert_allclose(a.numpy()[0], want[0], rtol=1e-5, atol=1e-4)
+    np.testing.assert_array_equal(a.numpy()[1:], x[1:])
+    w = (rng.standard_normal((257, 257)) * 0.05).astype(np.float32)
+    a = Array(x)
+    a.assign(op.dot(a, Array(w)))
+    bound = np.abs(x).astype(np.float64) @ np.abs(w).astype(np.float64)
+    assert np.all(np.abs(a.numpy().astype(np.float64) - x.astype(np.float64) @ w.astype(np.float64)) <= 1e-5 * bound)
+    a = Array(x)
+    a.assign(op.tanh(op.dot(Array(w), a)))                    # fused GEMM + epilogue whose right operand is the destination
+    want = np.tanh(w.astype(np.float64) @ x.astype(np.float64))
+    np.testing.assert_allclose(a.numpy(), want, rtol=1e-4, atol=2e-5)
+    a = Array(x)
+    before = lazy_stats()
+    a.assign(a * 2.0)
+    a += a
+    after = lazy_stats()
+    np.testing.assert_array_equal(a.numpy(), x * 4.0)
+    assert after["kernels"] - before["kernels"] == 2          # no temporaries for identical maps
