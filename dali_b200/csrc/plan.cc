@@ -232,7 +232,7 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
     v.vec = vec;
     // indirectly read args (gather sources) whose indexed rows can be fetched with full-width vector loads
     v.xv.assign(nargs, '0');
-    v.unchecked = v.kind == K_ALL && env_int("DALI_B200_ALL_UNCHECKED", 1);
+    v.unchecked = false;     // decided with the grid below
     v.stream_out = v.kind == K_MAP && p.has_indirect && env_int("DALI_B200_GATHER_STREAM", 0);
     // (opt-in: on 2^20 rows of 1 KiB gathered from a 64 MiB table the kernel is bound by the 1 GiB it writes -- 292 us with
     // scalar gathers and plain stores, 326 us with 128-bit gathers, 314-320 us with streaming stores, DALI_B200_GATHER_STREAM)
@@ -399,21 +399,24 @@ bool plan_launch(const Program& p, const int64_t* space, int rank,
         v.unroll = env_int("DALI_B200_ALL_UNROLL", 4);
         long long chunk = (long long)v.threads * vec * v.unroll;
         long long gx = (C + chunk - 1) / chunk;
-        // One resident wave (148 x 8 CTAs) while a CTA then has at most 16 chunks; beyond that more, shorter CTAs, which the
+        // One resident wave (148 x 8 CTAs) for small inputs; beyond that more, shorter CTAs, which the
         // hardware hands to whichever SM frees up first: the fused chain over 2^31 elements takes 1.62 ms as one
         // wave (CTAs of one SM progress unevenly and the last ones run with too few warps to hide the loads) and 1.50 ms
-        // as 16 waves; a 2^26-element sum is fastest as one wave (47 us; 50 / 53 / 59 us as 4 / 8 / 14 waves).  The work
-        // of a CTA depends on the grid only, so results stay bit-equal from run to run.
-        // (whole waves only; a program with an arg-reduction, whose slow path makes CTAs uneven, goes to a second wave
-        // at half the work per CTA: argmax over 2^26 elements 48.3 us as one wave, 45.9 us as two)
+        // as 16 waves; a 2^26-element sum takes 50 / 53 / 59 us as 4 / 8 / 14 waves.  The work of a CTA depends on the
+        // grid only, so results stay bit-equal from run to run.
+        // (whole waves only, a CTA of about 8 chunks: 2^26 elements run as two waves -- sum 46.1 us against 46.7-47.4 us as
+        // one, argmax 45.9 against 48.3 us -- and the second wave evens out the SMs' finishing times, which is what the
+        // other ranks of a fused exchange wait for)
         const long long wave = (long long)kSMs * env_int("DALI_B200_ALL_CTAS_PER_SM", 8);
-        bool all_has_arg = false;
-        for (const Stmt& st_ : p.stmts) all_has_arg = all_has_arg || st_.kind == S_ARGRED;
-        const long long per_cta = env_int("DALI_B200_ALL_CHUNKS_PER_CTA", all_has_arg ? 8 : 16);
+        const long long per_cta = env_int("DALI_B200_ALL_CHUNKS_PER_CTA", 8);
         long long waves = (gx + per_cta * wave / 2) / (per_cta * wave);
         waves = std::max<long long>(1, std::min<long long>(waves, env_int("DALI_B200_ALL_MAX_WAVES", 16)));
         const long long ctas = std::min(gx, wave * waves);
         out.grid_x = (unsigned)ctas;
+        // full chunks without per-vector bounds checks: the loop body exists twice then, which pays when a CTA runs it
+        // often (2^31-element chain, 28 chunks per CTA: 1.504 -> 1.483 ms) and costs when it does not (2^26-element sum,
+        // 7 chunks per CTA: 54.9 -> 60.4 us)
+        v.unchecked = env_int("DALI_B200_ALL_UNCHECKED", gx >= 16 * ctas ? 1 : 0) != 0;
         out.scratch_bytes = (size_t)out.grid_x * 16 * std::max(1, p.n_reductions);
         out.counters = 1;
         v.T = 0; v.vpt = 0; v.tx = 0; v.ty = 0;
