@@ -2,6 +2,7 @@
 #include "codegen.h"
 
 #include <algorithm>
+#include <map>
 #include <set>
 #include <sstream>
 
@@ -68,6 +69,10 @@ struct Gen {
     std::set<int> need_inv;          // R-level f32 values whose reciprocal is precomputed
     std::vector<int> reds;           // stmt indices of reductions, program order
     std::vector<int> red_slot;       // per stmt index -> position in `reds`, or -1
+    std::map<int, int> red_from_arg; // col / all: a max (min) whose operand an argmax (argmin) of the same program also
+                                     // reduces -> that arg-reduction's stmt index.  Its running value IS the max, so the
+                                     // element loop accumulates nothing for it; the value is copied over after the loop
+                                     // (the pair programs of sharded arg-reductions: one reduction's work instead of two)
 
     Gen(const Program& p_, const Variant& v_) : p(p_), v(v_), L(p_, v_) {
         red_slot.assign(p.stmts.size(), -1);
@@ -82,6 +87,15 @@ struct Gen {
                 if (!d.elem) need_inv.insert(d.id);
             }
         }
+        if (v.kind == K_COL || v.kind == K_ALL)
+            for (int r : reds) {
+                const Stmt& s = p.stmts[r];
+                if (s.kind != S_RED || (s.name != "max" && s.name != "min")) continue;
+                for (int a : reds) {
+                    const Stmt& t = p.stmts[a];
+                    if (t.kind == S_ARGRED && t.name == s.name && t.in[0] == s.in[0] && t.stage == s.stage) { red_from_arg[r] = a; break; }
+                }
+            }
     }
 
     const Stmt& val(int id) const { return p.stmts[p.value_stmt[id]]; }
@@ -396,7 +410,9 @@ struct Gen {
         }
         for (int si : sinks) {
             const Stmt& s = p.stmts[si];
-            if (s.kind == S_RED) {
+            if (s.kind == S_RED && red_from_arg.count(si)) {
+                // nothing here: the value is taken from the arg-reduction's pair after the loop
+            } else if (s.kind == S_RED) {
                 o << in2 << "acc" << si << g.acc_suffix << " = " << red_struct(s.name) << "::apply(acc" << si
                   << g.acc_suffix << ", " << vn(s.in[0]) << ");\n";
             } else if (s.kind == S_ARGRED) {
@@ -910,6 +926,7 @@ struct Gen {
             emit_chunk(true);
             o << "    }\n  }\n";
         }
+        for (const auto& ra : red_from_arg) o << "  acc" << ra.first << " = acc" << ra.second << ".v;\n";
         // CTA partials
         for (int si : reds) {
             const Stmt& s = p.stmts[si];
@@ -1114,6 +1131,8 @@ struct Gen {
             }
         }
         o << "    }\n  }\n";
+        for (const auto& ra : red_from_arg)
+            o << "  _Pragma(\"unroll\") for (int j = 0; j < VEC; ++j) acc" << ra.first << "[j] = acc" << ra.second << "[j].v;\n";
         // fold the TYI slices of the CTA
         for (int si : reds) {
             const Stmt& s = p.stmts[si];

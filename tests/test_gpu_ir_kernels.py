@@ -424,3 +424,35 @@ def test_few_long_rows_shared_by_a_thread_block_cluster(lib, shape):
     got = host(o)
     np.testing.assert_array_equal(got, oracle.argreduce("max", a, 1))
     assert got[0] == 11
+
+
+@pytest.mark.parametrize("kind", ["max", "min"])
+@pytest.mark.parametrize("shape", [(300, 200), (2048, 1536)])
+def test_value_and_position_pairs_in_one_kernel(lib, kind, shape):
+    """arg_pair_ir: the extreme value and its first position (+ an offset) from one kernel -- what a rank computes of a sharded
+    argmax / argmin before the ranks' pairs are combined.  Over the last axis (row skeleton), over axis 0 (column skeleton,
+    where the extreme is read off the arg-reduction's running pair) and over all axes; integer-valued inputs with many ties."""
+    from dali_b200.ir import arg_pair_ir
+    R, C = shape
+    g = torch.Generator(device="cuda")
+    g.manual_seed(R + C)
+    x = torch.randint(-5, 6, (R, C), generator=g, device="cuda").float()
+    xn = x.cpu().numpy()
+    off = np.int32(1000)
+    pick, argpick = (np.max, np.argmax) if kind == "max" else (np.min, np.argmin)
+    h = lib.compile(arg_pair_ir(kind, "f32", 2, 1))
+    vals, pos = torch.empty(R, device="cuda"), torch.empty(R, dtype=torch.int32, device="cuda")
+    lib.launch(h, (R, C), [vals, pos, x], scalars=[off])
+    assert lib.last_variant().startswith("row.")
+    np.testing.assert_array_equal(vals.cpu().numpy(), pick(xn, axis=1))
+    np.testing.assert_array_equal(pos.cpu().numpy(), argpick(xn, axis=1) + 1000)
+    vals, pos = torch.empty(C, device="cuda"), torch.empty(C, dtype=torch.int32, device="cuda")
+    lib.launch(h, (C, R), [vals, pos, x], strides=[None, None, [1, C]], scalars=[off])
+    assert lib.last_variant().startswith("col.")
+    np.testing.assert_array_equal(vals.cpu().numpy(), pick(xn, axis=0))
+    np.testing.assert_array_equal(pos.cpu().numpy(), argpick(xn, axis=0) + 1000)
+    h2 = lib.compile(arg_pair_ir(kind, "f32", 2, 2))
+    vals, pos = torch.empty(1, device="cuda"), torch.empty(1, dtype=torch.int32, device="cuda")
+    lib.launch(h2, (R, C), [vals, pos, x], scalars=[off])
+    assert lib.last_variant().startswith("all.")
+    assert float(vals) == float(pick(xn)) and int(pos) == int(argpick(xn)) + 1000
