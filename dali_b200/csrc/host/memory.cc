@@ -135,7 +135,10 @@ void* SynchronizedMemory::data(const Device& device, AM mode) {
                 lazy::check(dalib200_sync(src, nullptr), "dalib200_sync");
             } else if (m->host_fresh) {
                 lazy::check(dalib200_memcpy_h2d(g, here, m->host, total_memory, nullptr), "dalib200_memcpy_h2d");
-                // the host buffer is pageable: the copy has been staged by the time the call returns
+                // A pageable host buffer has been staged by the time the call returns.  A page-locked one (borrow_host,
+                // dalib200_host_alloc) is read asynchronously by the copy engine: its owner must leave it untouched until
+                // a synchronising call has returned, and borrow it again after a host-side write (the device copy is
+                // marked fresh here and is not refreshed behind the caller's back).
             } else {
                 // fresh on another GPU only: stage through the host (the reference asserts here,
                 // dali/array/memory/memory_ops.cu.cpp:120-125)
