@@ -35,8 +35,9 @@ struct GemmVariant {
     int ksplit = 0; // a cluster of two CTAs per tile, one operand pair each, partial sums exchanged through DSMEM
     int slices = 1; // the epilogue reads this many column slices of the product per output element
     int pair = 0;   // two CTAs (cta_group::2) share a 2*bm x bn tile, each staging half of the B tile
+    int kpair = 0;  // with ksplit: clusters of four, a cta_group::2 pair per operand pair on a tile of 2*bm rows
     bool b_kmajor() const { return split != 0; }   // the fp32 path transposes B while splitting it
-    bool ncat() const { return split != 0 && (bn <= 64 || ksplit); }   // b_hi | b_lo read as one operand of 2 * bn columns
+    bool ncat() const { return split != 0 && (bn <= 64 || ksplit) && !kpair; }   // b_hi | b_lo read as one operand of 2 * bn columns
     unsigned idesc(int n_cols = 0) const {
         if (!n_cols) n_cols = bn;
         unsigned fmt = esize == 2 ? 1u : 2u;       // kind::f16: 1 = bf16; kind::tf32: 2 = tf32
@@ -47,11 +48,11 @@ struct GemmVariant {
         d |= 0u << 15;                             // A is K-major
         d |= (b_kmajor() ? 0u : 1u) << 16;         // B: K-major ([N,K]) or MN-major ([K,N])
         d |= (unsigned)(n_cols >> 3) << 17;
-        d |= (unsigned)(((pair ? 2 : 1) * bm) >> 4) << 24;
+        d |= (unsigned)((((pair || kpair) ? 2 : 1) * bm) >> 4) << 24;
         return d;
     }
     size_t stage_bytes() const {
-        return (size_t)(split ? 2 : 1) * ((size_t)bm * bk * esize + (size_t)(bn / (pair ? 2 : 1)) * bk * esize);
+        return (size_t)(split ? 2 : 1) * ((size_t)bm * bk * esize + (size_t)(bn / ((pair || kpair) ? 2 : 1)) * bk * esize);
     }
     size_t xchg_bytes() const { return ksplit ? (size_t)bm * (bn / 2) * 4 : 0; }     // half a tile of fp32 partial sums
     size_t smem_bytes() const { return stages * stage_bytes() + xchg_bytes() + 1024; }
@@ -62,6 +63,7 @@ struct GemmVariant {
         if (ncat()) o << ".ncat";
         if (slices > 1) o << ".sl" << slices;
         if (ksplit) o << ".ksplit";
+        if (kpair) o << ".kpair";
         return o.str();
     }
 };
@@ -232,6 +234,7 @@ bool gemm_source(void* ctx, std::string* src, std::string* err) {
     o << "#define GEMM_SLICES " << c->v.slices << "\n#define GEMM_KSPLIT " << c->v.ksplit << "\n";
     o << "#define GEMM_NCAT " << (c->v.ncat() ? 1 : 0) << "\n#define GEMM_IDESC_WIDE " << c->v.idesc(2 * c->v.bn) << "u\n";
     o << "#define GEMM_B_KMAJOR " << (c->v.b_kmajor() ? 1 : 0) << "\n#define GEMM_PAIR " << c->v.pair << "\n";
+    o << "#define GEMM_KPAIR " << c->v.kpair << "\n";
     int words = 3 * (int)c->p->args.size() + (int)c->p->scalars.size();
     o << "#define GEMM_EPI_WORDS " << (words < 1 ? 1 : words) << "\n";
     // the io helpers need gemm:: conversions, which the skeleton defines: split the skeleton at its kernel
@@ -264,12 +267,12 @@ bool make_map(CUtensorMap* map, bool bf16, const void* base, uint64_t inner, uin
 
 // fp32 [slices][cols][k] view of a transposed operand (row pitch ld_elems): box = all slices x box_cols x box_k
 bool make_map_sliced(CUtensorMap* map, const void* base, uint64_t k, uint64_t cols, uint64_t slices, uint64_t ld_elems,
-                     uint32_t box_k, uint32_t box_cols, std::string* err) {
+                     uint32_t box_k, uint32_t box_cols, uint32_t box_slices, std::string* err) {
     static EncodeTiledFn encode = reinterpret_cast<EncodeTiledFn>(driver_entry("cuTensorMapEncodeTiled"));
     if (!encode) { *err = "cuTensorMapEncodeTiled unavailable"; return false; }
     cuuint64_t dims[3] = {k, cols, slices};
     cuuint64_t strides[2] = {ld_elems * 4, cols * ld_elems * 4};
-    cuuint32_t box[3] = {box_k, box_cols, (cuuint32_t)slices};
+    cuuint32_t box[3] = {box_k, box_cols, box_slices};       // a CTA pair stages half of the slices each
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -386,6 +389,12 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
             ctx.v.slices = slices;
             ctx.v.bn = 128;
             ctx.v.stages = 3;
+            // CTA pairs inside the K split (clusters of four on tiles of 256 rows): opt-in, measured slower (see the skeleton)
+            const char* kp = std::getenv("DALI_B200_GEMM_KPAIR");
+            if (kp && kp[0] == '1' && m > 128) {
+                ctx.v.kpair = 1;
+                ctx.v.stages = 4;
+            }
         }
     }
     const GemmVariant& v = ctx.v;
@@ -413,13 +422,14 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
                   make_map(&tm[4 * pi + 2], bf16, g.a_lo ? g.a_lo : g.a, k, (uint64_t)m, (uint64_t)g.lda, (uint32_t)v.bk, (uint32_t)v.bm, &err);
         if (ok && v.b_kmajor() && slices > 1)
             ok = make_map_sliced(&tm[4 * pi + 1], g.b, k, (uint64_t)n, (uint64_t)slices, (uint64_t)g.ldb, (uint32_t)v.bk,
-                                 (uint32_t)(v.bn / slices), &err) &&
+                                 (uint32_t)(v.bn / slices), (uint32_t)(slices / (v.kpair ? 2 : 1)), &err) &&
                  make_map_sliced(&tm[4 * pi + 3], g.b_lo ? g.b_lo : g.b, k, (uint64_t)n, (uint64_t)slices, (uint64_t)g.ldb,
-                                 (uint32_t)v.bk, (uint32_t)(v.bn / slices), &err);
+                                 (uint32_t)v.bk, (uint32_t)(v.bn / slices), (uint32_t)(slices / (v.kpair ? 2 : 1)), &err);
         else if (ok && v.b_kmajor())
-            ok = make_map(&tm[4 * pi + 1], bf16, g.b, k, b_cols, (uint64_t)g.ldb, (uint32_t)v.bk, (uint32_t)(v.bn / slices), &err) &&
+            ok = make_map(&tm[4 * pi + 1], bf16, g.b, k, b_cols, (uint64_t)g.ldb, (uint32_t)v.bk,
+                          (uint32_t)(v.bn / slices / (v.kpair ? 2 : 1)), &err) &&
                  make_map(&tm[4 * pi + 3], bf16, g.b_lo ? g.b_lo : g.b, k, b_cols, (uint64_t)g.ldb, (uint32_t)v.bk,
-                          (uint32_t)(v.bn / slices), &err);
+                          (uint32_t)(v.bn / slices / (v.kpair ? 2 : 1)), &err);
         else if (ok)
             ok = make_map(&tm[4 * pi + 1], bf16, g.b, (uint64_t)n, k, (uint64_t)g.ldb, sw, (uint32_t)v.bk, &err) &&
                  make_map(&tm[4 * pi + 3], bf16, g.b_lo ? g.b_lo : g.b, (uint64_t)n, k, (uint64_t)g.ldb, sw, (uint32_t)v.bk, &err);
@@ -444,17 +454,17 @@ int gemm_fused_launch(int device, void* stream, bool bf16, int64_t m, int64_t n,
     // the kernel's GemmP has exactly GEMM_EPI_WORDS words; ours is a superset with the same prefix
     void* params[] = {&tm[0], &tm[1], &tm[2], &tm[3], &tm[4], &tm[5], &tm[6], &tm[7], &p};
     // persistent CTAs (CTA pairs), at most one per SM (SM pair); they take the tiles round robin
-    const int64_t rows_per_tile = (int64_t)v.bm * (v.pair ? 2 : 1);
+    const int64_t rows_per_tile = (int64_t)v.bm * ((v.pair || v.kpair) ? 2 : 1);
     p.tiles_m = (unsigned)((m + rows_per_tile - 1) / rows_per_tile);
     p.tiles_n = (unsigned)((n + v.bn / slices - 1) / (v.bn / slices));
     const uint64_t total_tiles = (uint64_t)p.tiles_m * p.tiles_n;
     if (total_tiles > 0x7fffffffull) { set_error("gemm_fused: too many output tiles"); return DALIB200_ERR_TOO_LARGE; }
     int sms = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device_ordinal(device)) != cudaSuccess || sms < 2) sms = 148;
-    const bool cluster = v.pair || v.ksplit;       // two CTAs per worker
-    uint64_t workers = (uint64_t)(cluster ? sms / 2 : sms);
+    const int per_worker = v.kpair ? 4 : (v.pair || v.ksplit) ? 2 : 1;       // CTAs of a cluster
+    uint64_t workers = (uint64_t)(sms / per_worker);
     if (workers > total_tiles) workers = total_tiles;
-    const unsigned gx = (unsigned)(workers * (cluster ? 2 : 1)), gy = 1;
+    const unsigned gx = (unsigned)(workers * per_worker), gy = 1;
     // the kernel waits for its predecessor (griddepcontrol.wait) after its own set-up: barriers, tensor memory
     return launch_function(device, fn, gx, gy, 192, (unsigned)v.smem_bytes(), stream, params, /*dependent=*/true);
 }

@@ -28,6 +28,16 @@
 //                     tile, the halves meet through distributed shared memory and each CTA finishes half of
 //                     the tile's columns.  Per CTA this halves the operand bytes pulled from L2, which is what
 //                     bounds the M = 256 products (separate kernel body: dali_gemm_kernel below)
+//   GEMM_KPAIR        1 (with GEMM_KSPLIT, GEMM_NCAT = 0): the K split over CTA PAIRS -- a cluster of four CTAs shares a tile of
+//                     256 rows: CTAs 2p and 2p + 1 form a cta_group::2 pair that accumulates operand pair p over the whole
+//                     tile (each stages its own 128 rows of A and HALF of the B tile, the even CTA issues one MMA for both
+//                     tensor cores), CTA 2p + h then exchanges partial sums with CTA 2(1 - p) + h, which holds the same
+//                     128 rows of the other operand pair.  Per CTA and K block 48 KB arrive by TMA instead of 64 KB and the
+//                     tensor core reads 72 KB instead of 80 KB from this SM's shared memory.  Opt-in (DALI_B200_GEMM_KPAIR=1):
+//                     correct, and slower than the plain K split on the LSTM cell (32.0 against 29.1 us): three 128-column
+//                     instructions per K step instead of a 256- and a 128-column one, and each costs 4.5 us over the 128
+//                     K steps -- the 32 KB it reads from shared memory at 128 B per clock, which is what bounds these
+//                     TF32 products (23.0 / 27.4 / 32.0 us with one / two / three of the instructions issued)
 //   GEMM_IDESC        tcgen05 instruction descriptor
 // and a macro EPILOGUE_CHUNK(row, col0, acc, nvalid) generated from the
 // expression that consumes the product.
@@ -77,8 +87,11 @@ struct GemmP {
 #ifndef GEMM_PAIR
 #define GEMM_PAIR 0
 #endif
-#define GEMM_CLUSTER (GEMM_PAIR || GEMM_KSPLIT)      /* the kernel runs as clusters of two CTAs */
-#if GEMM_PAIR
+#ifndef GEMM_KPAIR
+#define GEMM_KPAIR 0
+#endif
+#define GEMM_CLUSTER (GEMM_PAIR || GEMM_KSPLIT)      /* the kernel runs as clusters of two (GEMM_KPAIR: four) CTAs */
+#if GEMM_PAIR || GEMM_KPAIR
 #define GEMM_CG "2"
 #define GEMM_BN_LOCAL (GEMM_BN / 2)                          /* columns of B this CTA stages */
 #else
@@ -182,13 +195,24 @@ DEV void tma_load_3d(void* dst, const TensorMap* map, unsigned long long* bar, i
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
 }
-#if GEMM_PAIR
+#if GEMM_PAIR || GEMM_KPAIR
 // the copy lands in THIS CTA's shared memory and reports its bytes to the barrier at shared::cluster
 // address bar_cluster (the leader CTA's), as a CTA-pair MMA expects
 DEV void tma_load_2d_pair(void* dst, const TensorMap* map, unsigned bar_cluster, int x, int y) {
     asm volatile(
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster), "r"(x), "r"(y) : "memory");
+}
+DEV void tma_load_3d_pair(void* dst, const TensorMap* map, unsigned bar_cluster, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster), "r"(x), "r"(y), "r"(z) : "memory");
+}
+// arrives on the barrier at the same address in every CTA of the cluster whose bit is set in `mask` when every
+// tcgen05.mma issued so far by this thread has completed
+DEV void umma_commit_mask(unsigned long long* bar, unsigned short mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(mask) : "memory");
 }
 #endif
 #if GEMM_CLUSTER
@@ -306,7 +330,7 @@ DEV float bf16_to_f32(unsigned short b) { return __uint_as_float(((unsigned)b) <
 #define GEMM_XCHG_VEC (GEMM_BN / 2 / 4)                         /* float4 per row and direction */
 #define GEMM_XCHG_BYTES (GEMM_XCHG_VEC * GEMM_BM * 16)
 
-extern "C" __global__ void __launch_bounds__(GEMM_THREADS, 1) __cluster_dims__(2, 1, 1)
+extern "C" __global__ void __launch_bounds__(GEMM_THREADS, 1) __cluster_dims__(GEMM_KPAIR ? 4 : 2, 1, 1)
 dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ TensorMap tmB,
                  const __grid_constant__ TensorMap tmAlo, const __grid_constant__ TensorMap tmBlo,
                  const __grid_constant__ TensorMap tmA2, const __grid_constant__ TensorMap tmB2,
@@ -326,10 +350,18 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#if GEMM_KPAIR
+    // cluster rank = 2 * (operand pair) + (row half); the MMA pair is (2p, 2p + 1), the exchange partner has the same rows
+    const unsigned crank = cluster_ctarank();
+    const unsigned cta_rank = crank >> 1, half = crank & 1u, peer = crank ^ 2u, lead = crank & ~1u;
+    const unsigned worker = blockIdx.x >> 2, n_workers = gridDim.x >> 2;
+    const unsigned short pair_mask = (unsigned short)(3u << lead);
+#else
     const unsigned cta_rank = cluster_ctarank(), peer = cta_rank ^ 1u;
     const unsigned worker = blockIdx.x >> 1, n_workers = gridDim.x >> 1;
+#endif
     const unsigned total_tiles = p.tiles_m * p.tiles_n;
-    // CTA r works on operand pair r over the whole tile
+    // CTA r (GEMM_KPAIR: CTA pair r) works on operand pair r over the whole tile
     const TensorMap* mA = cta_rank ? &tmA2 : &tmA;
     const TensorMap* mB = cta_rank ? &tmB2 : &tmB;
     const TensorMap* mAlo = cta_rank ? &tmA2lo : &tmAlo;
@@ -341,14 +373,18 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
         const unsigned band_n0 = band * GEMM_RASTER;
         const unsigned band_w = p.tiles_n - band_n0 < GEMM_RASTER ? p.tiles_n - band_n0 : GEMM_RASTER;
         const unsigned in_band = lin - band * GEMM_RASTER * p.tiles_m;
+#if GEMM_KPAIR
+        *m0 = ((long long)(in_band / band_w) * 2 + half) * GEMM_BM;        // this CTA's 128 of the tile's 256 rows
+#else
         *m0 = (long long)(in_band / band_w) * GEMM_BM;
+#endif
         *n0 = (long long)(band_n0 + in_band % band_w) * GEMM_TILE_N;
     };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < GEMM_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(&acc_full, 1);
-        mbar_init(&acc_empty, 4);
+        mbar_init(&acc_empty, GEMM_KPAIR ? 8 : 4);      // GEMM_KPAIR: the epilogue warps of both CTAs report to the even one
         mbar_init(&xchg_full, 128);      // every epilogue thread of the peer arrives after its stores
         mbar_init(&xchg_free, 128);
         abort_flag = 0;
@@ -377,8 +413,26 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
                 const unsigned s = it % GEMM_STAGES;
                 if (!mbar_wait(&empty_bar[s], ((it / GEMM_STAGES) & 1u) ^ 1u, &abort_flag)) { atomicExch(p.err, 1); abort_flag = 1; ok = false; break; }
                 unsigned char* st = tiles + (size_t)s * GEMM_STAGE_BYTES;
-                mbar_expect_tx(&full_bar[s], GEMM_STAGE_BYTES);
                 const int kx = kb * GEMM_BK;
+#if GEMM_KPAIR
+                // stage = a_hi, b_hi, a_lo, b_lo with this CTA's HALF of the B tile's columns (slices 2 * half, 2 * half + 1 of
+                // a sliced tile); both CTAs' copies report to the even CTA's barrier, which it arms for both
+                if (half == 0) mbar_expect_tx(&full_bar[s], 2 * GEMM_STAGE_BYTES);
+                const unsigned bar = map_to_cta(&full_bar[s], lead);
+                unsigned char* bt = st + GEMM_A_TILE_BYTES;
+                unsigned char* alo = bt + GEMM_B_TILE_BYTES;
+                unsigned char* blo = alo + GEMM_A_TILE_BYTES;
+                tma_load_2d_pair(st, mA, bar, kx, (int)m0);
+                tma_load_2d_pair(alo, mAlo, bar, kx, (int)m0);
+#if GEMM_SLICES > 1
+                tma_load_3d_pair(bt, mB, bar, kx, (int)n0, (int)(half * (GEMM_SLICES / 2)));
+                tma_load_3d_pair(blo, mBlo, bar, kx, (int)n0, (int)(half * (GEMM_SLICES / 2)));
+#else
+                tma_load_2d_pair(bt, mB, bar, kx, (int)(n0 + half * GEMM_BN_LOCAL));
+                tma_load_2d_pair(blo, mBlo, bar, kx, (int)(n0 + half * GEMM_BN_LOCAL));
+#endif
+#else
+                mbar_expect_tx(&full_bar[s], GEMM_STAGE_BYTES);
                 tma_load_2d(st, mA, &full_bar[s], kx, (int)m0);
 #if GEMM_SLICES > 1
                 tma_load_3d(st + GEMM_A_TILE_BYTES, mB, &full_bar[s], kx, (int)n0, 0);
@@ -388,8 +442,44 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
                 tma_load_2d(st + GEMM_A_TILE_BYTES + GEMM_B_TILE_BYTES, mBlo, &full_bar[s], kx, (int)n0);
 #endif
                 tma_load_2d(st + GEMM_A_TILE_BYTES + 2 * GEMM_B_TILE_BYTES, mAlo, &full_bar[s], kx, (int)m0);
+#endif
             }
         }
+#if GEMM_KPAIR
+    } else if (warp == 5 && lane == 0 && half == 0) {
+        // ------------------------------------------------------------ MMA issuer of a CTA pair (the even CTA): every
+        // instruction runs on both tensor cores, reads the A rows of each CTA from that CTA's shared memory and the two
+        // halves of the B tile from both, and leaves each CTA's 128 rows of the product in its own tensor memory.
+        // Accumulators: the main products round robin over GEMM_NACC sets, the two correction products in one more.
+        unsigned it = 0, done = 0;
+        bool ok = true;
+        for (unsigned t = worker; t < total_tiles && ok && num_kb > 0; t += n_workers, ++done) {
+            if (!mbar_wait_cluster(&acc_empty, (done & 1u) ^ 1u, &abort_flag)) { atomicExch(p.err, 5); abort_flag = 1; ok = false; break; }
+            fence_after_sync();
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const unsigned s = it % GEMM_STAGES;
+                if (!mbar_wait(&full_bar[s], (it / GEMM_STAGES) & 1u, &abort_flag)) { atomicExch(p.err, 2); abort_flag = 1; ok = false; break; }
+                fence_after_sync();
+                const unsigned a_addr = smem_u32(tiles + (size_t)s * GEMM_STAGE_BYTES);
+                const unsigned b_addr = a_addr + GEMM_A_TILE_BYTES;
+                const unsigned alo_addr = b_addr + GEMM_B_TILE_BYTES;
+                const unsigned blo_addr = alo_addr + GEMM_A_TILE_BYTES;
+                const unsigned corr = tmem_base + (unsigned)(GEMM_NACC * GEMM_BN);
+#pragma unroll
+                for (int k = 0; k < GEMM_BK / GEMM_UMMA_K; ++k) {
+                    const unsigned long long ad = smem_desc(a_addr + k * 32, 0, 1024);
+                    const unsigned long long bd = smem_desc(b_addr + k * 32, 0, 1024);
+                    const unsigned long long ald = smem_desc(alo_addr + k * 32, 0, 1024);
+                    const unsigned long long bld = smem_desc(blo_addr + k * 32, 0, 1024);
+                    umma(tmem_base + (unsigned)((kb % GEMM_NACC) * GEMM_BN), ad, bd, GEMM_IDESC, (kb >= GEMM_NACC || k > 0) ? 1u : 0u);
+                    umma(corr, ald, bd, GEMM_IDESC, (kb > 0 || k > 0) ? 1u : 0u);     // a_lo . b_hi
+                    umma(corr, ad, bld, GEMM_IDESC, 1u);                              // a_hi . b_lo
+                }
+                umma_commit_mask(&empty_bar[s], pair_mask);      // the stage is free in both CTAs
+            }
+            if (ok) umma_commit_mask(&acc_full, pair_mask);      // both CTAs' epilogues may read their rows
+        }
+#else
     } else if (warp == 5 && lane == 0) {
         // ------------------------------------------------------------ MMA issuer (one per CTA, its own tensor core)
         unsigned it = 0, done = 0;
@@ -417,6 +507,7 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
             }
             if (ok) umma_commit(&acc_full);
         }
+#endif
     } else if (warp < 4) {
         // ------------------------------------------------------------ exchange + epilogue
         const int trow = warp * 32 + lane;                        // row of the tile = TMEM lane
@@ -441,11 +532,22 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
                     tmem_ld32(lane_base, v);
                     const int used = num_kb < GEMM_NACC ? num_kb : GEMM_NACC;
                     float part[32];
+#if GEMM_KPAIR
+                    for (int a = 1; a < used; ++a) {                                      // main sets
+                        tmem_ld32(lane_base + (unsigned)(a * GEMM_BN), part);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] += part[i];
+                    }
+                    tmem_ld32(lane_base + (unsigned)(GEMM_NACC * GEMM_BN), part);         // corrections
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] += part[i];
+#else
                     for (int a = 1; a < 2 * used; ++a) {
                         tmem_ld32(lane_base + (unsigned)(a * GEMM_BN), part);
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] += part[i];
                     }
+#endif
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = 0.0f;
@@ -480,7 +582,11 @@ dali_gemm_kernel(const __grid_constant__ TensorMap tmA, const __grid_constant__ 
                 // this warp has read its part of tensor memory: the MMA issuer may start the next tile
                 fence_before_sync();
                 __syncwarp();
+#if GEMM_KPAIR
+                if (lane == 0) asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(map_to_cta(&acc_empty, lead)) : "memory");
+#else
                 if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty)) : "memory");
+#endif
             }
             // tell the peer its xchg holds this thread's share, then wait for the peer's share in ours
             asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(peer_full) : "memory");

@@ -135,13 +135,18 @@ def test_two_products_in_one_accumulator(lib, shape):
     np.testing.assert_allclose(got, host(two), rtol=1e-5, atol=1e-5 * float(bound.max()))
 
 
-@pytest.mark.parametrize("ksplit", ["1", "0"])
+@pytest.mark.parametrize("ksplit", ["1", "0", "pairs"])
 @pytest.mark.parametrize("shape", [(64, 128), (256, 1024), (200, 72), (130, 40), (384, 2048)])
 def test_lstm_gating_as_the_epilogue_of_the_gate_products(lib, shape, ksplit, monkeypatch):
     """The four gate slices of x.Wx + h.Wh meet in the epilogue (acc 0..3): c' and h' come out of the GEMM
     kernel, the [B,4H] gates matrix is never written.  Against the oracle's gating on fp64-accumulated gates;
     ragged B and H (H not a multiple of the units a tile covers).  ksplit = 1: a cluster of two CTAs per tile, one
     operand pair each, partial sums exchanged through distributed shared memory; 0: one CTA accumulates both pairs."""
+    # "pairs": the K split over cta_group::2 pairs (clusters of four CTAs on tiles of 256 rows), an opt-in variant
+    pairs = ksplit == "pairs"
+    if pairs:
+        ksplit = "1"
+        monkeypatch.setenv("DALI_B200_GEMM_KPAIR", "1")
     monkeypatch.setenv("DALI_B200_GEMM_KSPLIT", ksplit)
     B, H = shape
     rng = np.random.default_rng(B + H)
@@ -157,6 +162,7 @@ def test_lstm_gating_as_the_epilogue_of_the_gate_products(lib, shape, ksplit, mo
     got_c, got_h = host(c_new), host(h_new)
     assert lib.gemm_error_flag() == 0
     assert ".sl4" in lib.last_gemm_kernel() and lib.last_gemm_kernel().count(".ksplit") == int(ksplit)
+    assert lib.last_gemm_kernel().count(".kpair") == int(pairs and B > 128)
     gates = (x.astype(np.float64) @ Wx + h.astype(np.float64) @ Wh + b).astype(np.float32)
     want_c, want_h = oracle.lstm_gating(gates, c)
     # the gates carry the product's error, bounded by 1e-5 * (|x|.|Wx| + |h|.|Wh|) (measured: 40 times smaller); the
