@@ -424,3 +424,25 @@ def test_shard_marks_travel_with_values_and_guard_the_axis():
         x.set_shard(0, 100, 128)                                # rows [100, 164) do not lie inside [0, 128)
     x.set_shard(-1, 0, 0)
     assert x.shard[0] == -1 and x[3].shape == (32,)
+
+
+def test_overlapping_source_and_destination_lower_through_a_temporary():
+    """The destination's buffer read through another index map (transpose in place, a shifted slice, a reduction of the array
+    into one of its own rows, a product into one of its operands) takes one more launch for the temporary; identical maps
+    (a = f(a), a += a) do not."""
+    def ran(statement):
+        before = lazy_stats()
+        statement()
+        after = lazy_stats()
+        return {k: after[k] - before[k] for k in before}
+    a = Array(np.zeros((64, 64), np.float32))
+    assert ran(lambda: a.assign(a.transpose()))["kernels"] == 2
+    assert ran(lambda: a[1:].assign(a[:-1]))["kernels"] == 2
+    assert ran(lambda: a[0].assign(op.sum(a, [0])))["kernels"] == 2
+    w = Array(np.zeros((64, 64), np.float32))
+    r = ran(lambda: a.assign(op.dot(a, w)))
+    assert r["gemms"] == 1 and r["kernels"] == 1              # product into a temporary, then the copy
+    assert ran(lambda: a.assign(a * 2.0))["kernels"] == 1
+    assert ran(lambda: a.__iadd__(a))["kernels"] == 1
+    b = Array(np.zeros((128, 64), np.float32))
+    assert ran(lambda: b[:64].assign(b[64:]))["kernels"] == 1   # disjoint halves of one buffer

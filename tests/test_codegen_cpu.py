@@ -165,3 +165,39 @@ def test_transposed_operands_pick_a_tiled_map_variant(L):
     O, A = e.arg("f64"), e.arg("f64")
     e.st(O, e.ld(A))
     assert ".tile32" in variant_of(L, e.text(), (64, 64), 2, strides=[None, [1, 64]])
+
+
+def test_all_axis_grid_follows_the_work_per_cta(L):
+    """The all-axis skeleton runs in whole waves of 148 x 8 CTAs, about 8 chunks of 4096 elements to a CTA, at most 16
+    waves; full chunks skip their bounds checks (.nc) only where a CTA runs 16 or more of them."""
+    import re
+
+    def grid(v):
+        return int(re.search(r"grid=(\d+)x1", v).group(1))
+    v = variant_of(L, chain_sum_ir(), (1 << 20,), 2)
+    assert grid(v) == 256 and ".nc" not in v                  # 256 chunks: one CTA each, far less than a wave
+    v = variant_of(L, reduce_ir("sum", "f32", 2, 2), (8192, 8192), 2)
+    assert grid(v) == 2 * 1184 and ".nc" not in v             # 2^26 elements: two waves
+    v = variant_of(L, chain_sum_ir(), (1 << 28,), 2)
+    assert grid(v) == 7 * 1184 and ".nc" not in v
+    v = variant_of(L, chain_sum_ir(), (1 << 31,), 2)
+    assert grid(v) == 16 * 1184 and v.split(" ")[0].endswith(".nc")
+
+
+def test_pair_programs_read_the_extreme_off_the_arg_reduction(L, tmp_path):
+    """arg_pair_ir (max and argmax of one operand): in the column and all-axis skeletons the element loop accumulates the
+    arg-reduction only; the max is copied from its running pair after the loop."""
+    from dali_b200.ir import arg_pair_ir
+    old_dir = L.cache_get_dir()
+    L.cache_set_dir(str(tmp_path))
+    try:
+        N = 1024
+        h = L.compile(arg_pair_ir("max", "f32", 2, 1) + "# pair test\n")
+        L.precompile(h, (N, N), 3, strides=[None, None, [1, N]])
+        assert L.last_variant().startswith("col.")
+        src = "".join(open(str(p)).read() for p in tmp_path.glob("*.cu"))
+        body = src[src.index("dali_kernel"):]
+        assert re.search(r"acc\d+\[j\] = acc\d+\[j\]\.v;", body)
+        assert "RMax::apply(acc" not in body.split("fold")[0].split("__syncthreads")[0]
+    finally:
+        L.cache_set_dir(old_dir)
