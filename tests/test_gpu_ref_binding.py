@@ -33,11 +33,17 @@ def inputs(tmp):
     np.save(os.path.join(tmp, "u.npy"), (rng.random((96, 200)) * 2 - 1).astype(np.float32))
     np.save(os.path.join(tmp, "x.npy"), rng.standard_normal(1 << 16).astype(np.float32))
     np.save(os.path.join(tmp, "b.npy"), (rng.standard_normal((320, 64)) * 0.1).astype(np.float32))
+    np.save(os.path.join(tmp, "src.npy"), rng.standard_normal((500, 48)).astype(np.float32))
+    np.save(os.path.join(tmp, "idx.npy"), rng.integers(0, 500, (300,)).astype(np.int32))
+    np.save(os.path.join(tmp, "idxr.npy"), rng.integers(0, 48, (500,)).astype(np.int32))
+    np.save(os.path.join(tmp, "v.npy"), rng.standard_normal(130).astype(np.float32))
+    np.save(os.path.join(tmp, "w.npy"), rng.standard_normal(70).astype(np.float32))
 
 
 CASES = [(["softmax_naive", "a.npy"], "close"), (["softmax", "a.npy"], "close"), (["chain", "x.npy", "0.5", "0.1"], "close"),
          (["unary", "tanh", "a.npy"], "close"), (["unary", "sigmoid", "a.npy"], "close"), (["binary", "eltmul", "a.npy", "a.npy"], "close"),
-         (["dot", "a.npy", "b.npy"], "close")]
+         (["dot", "a.npy", "b.npy"], "close"), (["gather", "src.npy", "idx.npy"], "exact"),
+         (["gather_rows", "src.npy", "idxr.npy"], "exact"), (["outer", "v.npy", "w.npy"], "exact")]
 for _op in ("sum", "max", "argmax", "min", "argmin", "mean", "l2"):
     for _ax in ("-1", "0", "all"):
         CASES.append((["reduce", _op, _ax, "u.npy"], "exact" if _op in ("max", "min", "argmax", "argmin") else "close"))
