@@ -43,7 +43,8 @@ def inputs(tmp):
 CASES = [(["softmax_naive", "a.npy"], "close"), (["softmax", "a.npy"], "close"), (["chain", "x.npy", "0.5", "0.1"], "close"),
          (["unary", "tanh", "a.npy"], "close"), (["unary", "sigmoid", "a.npy"], "close"), (["binary", "eltmul", "a.npy", "a.npy"], "close"),
          (["dot", "a.npy", "b.npy"], "close"), (["gather", "src.npy", "idx.npy"], "exact"),
-         (["gather_rows", "src.npy", "idxr.npy"], "exact"), (["outer", "v.npy", "w.npy"], "exact")]
+         (["gather_rows", "src.npy", "idxr.npy"], "exact"), (["outer", "v.npy", "w.npy"], "exact"),
+         (["one_hot", "idx.npy", "500", "2.5", "-0.5"], "exact")]
 for _op in ("sum", "max", "argmax", "min", "argmin", "mean", "l2"):
     for _ax in ("-1", "0", "all"):
         CASES.append((["reduce", _op, _ax, "u.npy"], "exact" if _op in ("max", "min", "argmax", "argmin") else "close"))
