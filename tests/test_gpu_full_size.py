@@ -76,6 +76,14 @@ def test_config5_chain_sum_is_the_sum_of_its_parts(lib):
     total = float(parts.double().sum())
     # every term is positive and below 1: sum |y| = the sum itself
     assert abs(float(whole) - total) <= 1e-5 * total
+    # a length that ends inside a chunk: the launch runs unchecked full chunks and one checked, partial chunk
+    m = n - 3 * 4096 - 8
+    head, tail = torch.zeros(1, device="cuda"), torch.zeros(1, device="cuda")
+    lib.launch(h, (m,), [head, x[:m]], scalars=[w, b])
+    assert ".nc" in lib.last_variant()
+    lib.launch(h, (n - m,), [tail, x[m:]], scalars=[w, b])
+    torch.cuda.synchronize()
+    assert abs(float(whole) - (float(head) + float(tail))) <= 1e-5 * total
     ref = float((torch.sigmoid(x[:1 << 24].double() * 0.5 + 0.1) * torch.exp(-x[:1 << 24].double() ** 2)).sum())
     chunk = torch.zeros(1, device="cuda")
     lib.launch(h, (1 << 24,), [chunk, x[:1 << 24]], scalars=[w, b])
