@@ -297,8 +297,12 @@ def test_epilogue_with_strided_destination_scalars_and_residual(lib):
     assert np.all(got[:, 1::2] == -1.0)
 
 
-def test_full_size_linearity_property(lib):
-    """Config-4 size: (A . B)[rows] for a few probe rows equals the fp64 product of those rows."""
+@pytest.mark.parametrize("pair", ["1", "0"])
+def test_full_size_product_whole_output(lib, pair, monkeypatch):
+    """Config-4 size, CTA-pair and single-CTA kernels: the WHOLE [8192,8192] output against tanh(A . B + bias) computed in
+    fp32 on the device (torch as the checker; a tile the persistent scheduler mis-assigned would show), and six probe rows
+    against the fp64 product."""
+    monkeypatch.setenv("DALI_B200_GEMM_PAIR", pair)
     n = 8192
     g = torch.Generator(device="cuda").manual_seed(1237)
     A = (torch.randn(n, n, device="cuda", generator=g) * 0.02).bfloat16()
@@ -308,6 +312,15 @@ def test_full_size_linearity_property(lib):
     lib.gemm_fused(3, n, n, n, A, n, B, n, lib.compile(gemm_bias_tanh_ir("bf16")), [out, bias], strides=[None, [0, 1]])
     torch.cuda.synchronize()
     assert lib.gemm_error_flag() == 0
+    assert lib.last_gemm_kernel().endswith(".pair") == (pair == "1")
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        want_all = torch.tanh(A.float() @ B.float() + bias)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    assert bool(((out.float() - want_all).abs() <= 1e-2 * want_all.abs() + 4e-3).all())
+    del want_all
     rows = [0, 1, 127, 128, 4095, 8191]
     a = A[rows].float().cpu().numpy().astype(np.float64)
     want = np.tanh(a @ B.float().cpu().numpy().astype(np.float64) + bias.cpu().numpy())
